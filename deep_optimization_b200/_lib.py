@@ -1,0 +1,62 @@
+"""ctypes binding of libact_b200.so (the C ABI declared in include/act_b200.h).
+
+The library is the only compute path of this package.  Loading fails loudly
+when the shared object is missing; there is no CPU or PyTorch fallback.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libact_b200.so")
+
+ACT_DTYPE_F32, ACT_DTYPE_BF16, ACT_DTYPE_F16 = 0, 1, 2
+ACT_FLAG_ROUND_NEAREST = 1
+ACT_FLAG_REF_COMPAT = 2
+ACT_FLAG_REF_CLAMP = 4
+ACT_FLAG_REF_TANH = 8
+ACT_FLAG_META_BF16 = 16
+
+# every symbol include/act_b200.h declares, with its ctypes signature
+_vp, _i32, _i64, _u64, _f32 = (ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_uint64,
+                               ctypes.c_float)
+SIGNATURES = {
+    "act_quant_pack": ([_vp, _i32, _i64, _i32, _i32, _vp, _u64, _u64, _i32, _f32, _vp, _vp, _vp, _vp], _i32),
+    "act_dequant_unpack": ([_vp, _vp, _vp, _i64, _i32, _i32, _i32, _vp, _vp], _i32),
+    "act_pack_bits": ([_vp, _i64, _i32, _i32, _vp, _vp], _i32),
+    "act_unpack_bits": ([_vp, _i64, _i32, _i32, _vp, _vp], _i32),
+    "act_minmax": ([_vp, _i32, _i64, _i64, _vp, _vp, _vp], _i32),
+    "act_calc_precision": ([_vp, _vp, _vp, _i64, ctypes.c_double], _i32),
+    "act_strerror": ([_i32], ctypes.c_char_p),
+    "act_abi_version": ([], _i32),
+}
+
+_lib = None
+
+
+class ActLibraryError(RuntimeError):
+    """Raised when the C ABI returns a non-zero code."""
+
+
+def load() -> ctypes.CDLL:
+    """Load libact_b200.so; raises if it has not been built (python -m deep_optimization_b200.build)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(
+                f"{LIB_PATH} is missing: build it with `python -m deep_optimization_b200.build` "
+                "(needs nvcc); this package has no fallback path")
+        lib = ctypes.CDLL(LIB_PATH)
+        for name, (argtypes, restype) in SIGNATURES.items():
+            fn = getattr(lib, name)          # AttributeError if the symbol is not exported
+            fn.argtypes = argtypes
+            fn.restype = restype
+        _lib = lib
+    return _lib
+
+
+def check(code: int, what: str) -> None:
+    if code != 0:
+        msg = load().act_strerror(code).decode()
+        raise ActLibraryError(f"{what}: {msg} (code {code})")

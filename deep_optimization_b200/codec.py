@@ -1,0 +1,156 @@
+"""Tensor-level entry to the CUDA codec: thin argument marshalling over the C ABI.
+
+PyTorch supplies device memory and the current stream; every byte of arithmetic
+happens in libact_b200.so.  Functions here mirror the four codec operators of
+Activation_Compression/act_triton_kernel.py:336-433 with the grouped layout
+`[N, G, group_size]` already applied by the caller.
+"""
+from __future__ import annotations
+
+import itertools
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+
+_DTYPES = {torch.float32: _lib.ACT_DTYPE_F32, torch.bfloat16: _lib.ACT_DTYPE_BF16,
+           torch.float16: _lib.ACT_DTYPE_F16}
+
+# successive hash-noise calls draw disjoint counter ranges of one stream
+_offset_counter = itertools.count()
+_default_seed = 0x5EED
+_next_offset = 0
+
+
+def manual_seed(seed: int) -> None:
+    """Seed of the in-kernel counter hash used when no noise tensor is passed."""
+    global _default_seed, _next_offset
+    _default_seed = int(seed) & 0xFFFFFFFFFFFFFFFF
+    _next_offset = 0
+
+
+def _bits_consts(bits: int, group_size: int):
+    """Same contract as Activation_Compression/act_triton_kernel.py:328-334."""
+    if bits not in (1, 2, 4, 8):
+        raise ValueError(f"bits must be one of (1,2,4,8). got {bits}")
+    vpw = 32 // bits
+    return vpw, group_size // vpw, (1 << bits) - 1
+
+
+def _require_cuda(t: torch.Tensor, name: str) -> None:
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor: the codec has no CPU path")
+
+
+def _stream_ptr(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def quant_pack(x: torch.Tensor, bits: int, group_size: int, noise: Optional[torch.Tensor] = None,
+               seed: Optional[int] = None, offset: Optional[int] = None, flags: int = 0,
+               clamp_alpha: float = 0.0) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """x: [..., group_size]-groupable tensor (numel % group_size == 0), fp32/bf16/fp16.
+    Returns (packed int32 [NG, group_size*bits/32], scale fp32 [NG], min fp32 [NG])."""
+    global _next_offset
+    _, nwords, _ = _bits_consts(bits, group_size)
+    _require_cuda(x, "x")
+    if x.dtype not in _DTYPES:
+        raise TypeError(f"unsupported activation dtype {x.dtype}")
+    x = x.contiguous()
+    if x.numel() % group_size:
+        raise ValueError("numel must be a multiple of group_size")
+    ng = x.numel() // group_size
+    packed = torch.empty((ng, nwords), dtype=torch.int32, device=x.device)
+    scale = torch.empty((ng,), dtype=torch.float32, device=x.device)
+    mn = torch.empty((ng,), dtype=torch.float32, device=x.device)
+    if noise is not None:
+        _require_cuda(noise, "noise")
+        noise = noise.to(torch.float32).contiguous()
+        if noise.numel() != x.numel():
+            raise ValueError("noise must have as many elements as x")
+    if seed is None:
+        seed = _default_seed
+    if offset is None:
+        offset = _next_offset
+        _next_offset += (x.numel() + 3) // 4
+    with torch.cuda.device(x.device):
+        rc = _lib.load().act_quant_pack(
+            x.data_ptr(), _DTYPES[x.dtype], ng, group_size, bits,
+            noise.data_ptr() if noise is not None else None,
+            seed & 0xFFFFFFFFFFFFFFFF, offset & 0xFFFFFFFFFFFFFFFF, flags, float(clamp_alpha),
+            packed.data_ptr(), scale.data_ptr(), mn.data_ptr(), _stream_ptr(x))
+    _lib.check(rc, "act_quant_pack")
+    return packed, scale, mn
+
+
+def dequant_unpack(packed: torch.Tensor, scale: torch.Tensor, mn: torch.Tensor, bits: int,
+                   group_size: int, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """Inverse of quant_pack; returns [NG, group_size] of out_dtype."""
+    _bits_consts(bits, group_size)
+    _require_cuda(packed, "packed")
+    packed = packed.contiguous()
+    scale = scale.to(torch.float32).contiguous()
+    mn = mn.to(torch.float32).contiguous()
+    ng = scale.numel()
+    y = torch.empty((ng, group_size), dtype=out_dtype, device=packed.device)
+    with torch.cuda.device(packed.device):
+        rc = _lib.load().act_dequant_unpack(packed.data_ptr(), scale.data_ptr(), mn.data_ptr(), ng,
+                                            group_size, bits, _DTYPES[out_dtype], y.data_ptr(),
+                                            _stream_ptr(packed))
+    _lib.check(rc, "act_dequant_unpack")
+    return y
+
+
+def pack_bits(x: torch.Tensor, bits: int, group_size: int) -> torch.Tensor:
+    """int8 [NG*group_size] -> int32 words (mask / ready-made code packing)."""
+    _, nwords, _ = _bits_consts(bits, group_size)
+    _require_cuda(x, "x")
+    x = x.to(torch.int8).contiguous()
+    ng = x.numel() // group_size
+    packed = torch.empty((ng, nwords), dtype=torch.int32, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = _lib.load().act_pack_bits(x.data_ptr(), ng, group_size, bits, packed.data_ptr(),
+                                       _stream_ptr(x))
+    _lib.check(rc, "act_pack_bits")
+    return packed
+
+
+def unpack_bits(packed: torch.Tensor, bits: int, n_groups: int, group_size: int) -> torch.Tensor:
+    _bits_consts(bits, group_size)
+    _require_cuda(packed, "packed")
+    packed = packed.contiguous()
+    y = torch.empty((n_groups, group_size), dtype=torch.int8, device=packed.device)
+    with torch.cuda.device(packed.device):
+        rc = _lib.load().act_unpack_bits(packed.data_ptr(), n_groups, group_size, bits,
+                                         y.data_ptr(), _stream_ptr(packed))
+    _lib.check(rc, "act_unpack_bits")
+    return y
+
+
+def minmax(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Per-row (min, max) over the last dimension of a 2-D or 3-D tensor
+    (Activation_Compression/cpp_extension/src/min_max_kernel.cu:114-141)."""
+    _require_cuda(x, "x")
+    x = x.contiguous()
+    cols = x.shape[-1]
+    rows = x.numel() // cols
+    mn = torch.empty(x.shape[:-1], dtype=torch.float32, device=x.device)
+    mx = torch.empty(x.shape[:-1], dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = _lib.load().act_minmax(x.data_ptr(), _DTYPES[x.dtype], rows, cols, mn.data_ptr(),
+                                    mx.data_ptr(), _stream_ptr(x))
+    _lib.check(rc, "act_minmax")
+    return mn, mx
+
+
+def calc_precision(b: torch.Tensor, C: torch.Tensor, w: torch.Tensor, target: float) -> torch.Tensor:
+    """Greedy bit allocation on CPU int32 tensors, in place on b
+    (Activation_Compression/cpp_extension/src/calc_precision.cc:10-53)."""
+    for t, n in ((b, "b"), (C, "C"), (w, "w")):
+        if t.device.type != "cpu" or not t.is_contiguous() or t.dtype != torch.int32:
+            raise RuntimeError(f"{n} must be a contiguous CPU int32 tensor")
+    rc = _lib.load().act_calc_precision(b.data_ptr(), C.data_ptr(), w.data_ptr(), b.numel(),
+                                        float(target))
+    _lib.check(rc, "act_calc_precision")
+    return b

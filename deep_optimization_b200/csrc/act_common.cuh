@@ -1,0 +1,120 @@
+// Shared device helpers of the activation-compression kernels (sm_100a only).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/act_b200.h"
+
+#if defined(__CUDA_ARCH__) && (__CUDA_ARCH__ < 1000)
+#error "this library is written for sm_100a only"
+#endif
+
+namespace act {
+
+constexpr int kWarp = 32;
+constexpr int kTileElems = 1024;          // elements one warp handles per iteration
+constexpr uint32_t kMagicBits = 0x4B000000u;   // bit pattern of 2^23
+constexpr float kMagic = 8388608.0f;           // 2^23
+constexpr uint32_t kHashMul = 0xD256D193u;
+constexpr uint32_t kHashWeyl = 0x9E3779B9u;
+constexpr int kHashRounds = 4;
+
+__device__ __forceinline__ uint4 ldg_nc_v4(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+// streaming variant: the line is not kept in L1 once consumed
+__device__ __forceinline__ uint4 ldg_stream_v4(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ void stg_stream_v4(void* p, uint4 v) {
+    asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};"
+                 :: "l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+// NaN-propagating fp32 min/max; -0 orders below +0
+__device__ __forceinline__ float fmin_nan(float a, float b) {
+    float d; asm("min.NaN.f32 %0, %1, %2;" : "=f"(d) : "f"(a), "f"(b)); return d;
+}
+__device__ __forceinline__ float fmax_nan(float a, float b) {
+    float d; asm("max.NaN.f32 %0, %1, %2;" : "=f"(d) : "f"(a), "f"(b)); return d;
+}
+
+// Host side: splitmix64 finaliser that turns the caller's seed into the hash key.
+__host__ __device__ inline uint64_t hash_key(uint64_t seed) {
+    uint64_t z = seed + 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+
+// Four rounds of a 2x32 multiply-xor network: 64 output bits per 64-bit counter.
+__device__ __forceinline__ void hash_2x32(uint64_t ctr, uint32_t key_lo, uint32_t key_hi,
+                                          uint32_t& o0, uint32_t& o1) {
+    uint32_t L = (uint32_t)ctr;
+    uint32_t R = (uint32_t)(ctr >> 32) ^ key_hi;
+    uint32_t k = key_lo;
+#pragma unroll
+    for (int r = 0; r < kHashRounds; ++r) {
+        const uint32_t hi = __umulhi(kHashMul, L);
+        const uint32_t lo = kHashMul * L;
+        L = hi ^ k ^ R;
+        R = lo;
+        k += kHashWeyl;
+    }
+    o0 = L; o1 = R;
+}
+
+// 16-bit field -> float holding the integer h exactly (2^23 + h, minus 2^23)
+__device__ __forceinline__ float u16_lo_as_float(uint32_t w) {
+    return __uint_as_float(__byte_perm(w, kMagicBits, 0x7410)) - kMagic;
+}
+__device__ __forceinline__ float u16_hi_as_float(uint32_t w) {
+    return __uint_as_float(__byte_perm(w, kMagicBits, 0x7432)) - kMagic;
+}
+
+// a / s, correctly rounded, from y = RN(1/s): two Newton corrections on the
+// quotient with exact FMA residuals.  Valid while nothing under- or overflows;
+// callers keep s inside [2^-60, 2^60].
+__device__ __forceinline__ float div_by_scale(float a, float s, float y) {
+    float q = __fmul_rn(a, y);
+    float r = __fmaf_rn(-s, q, a);
+    q = __fmaf_rn(r, y, q);
+    r = __fmaf_rn(-s, q, a);
+    q = __fmaf_rn(r, y, q);
+    return q;
+}
+
+// clamp(floor(t), 0, qmax) with NaN -> 0, the general (slow) form
+__device__ __forceinline__ uint32_t code_from_t(float t, int qmax) {
+    if (!(t >= 0.0f)) return 0u;
+    if (t >= (float)(qmax + 1)) return (uint32_t)qmax;
+    return (uint32_t)floorf(t);
+}
+
+template <int DT> struct ElemT;
+template <> struct ElemT<ACT_DTYPE_F32>  { static constexpr int bytes = 4; };
+template <> struct ElemT<ACT_DTYPE_BF16> { static constexpr int bytes = 2; };
+template <> struct ElemT<ACT_DTYPE_F16>  { static constexpr int bytes = 2; };
+
+// widen the two 16-bit halves of a packed register to fp32 (exact)
+template <int DT> __device__ __forceinline__ float widen_lo(uint32_t v);
+template <int DT> __device__ __forceinline__ float widen_hi(uint32_t v);
+template <> __device__ __forceinline__ float widen_lo<ACT_DTYPE_BF16>(uint32_t v) { return __uint_as_float(v << 16); }
+template <> __device__ __forceinline__ float widen_hi<ACT_DTYPE_BF16>(uint32_t v) { return __uint_as_float(v & 0xFFFF0000u); }
+template <> __device__ __forceinline__ float widen_lo<ACT_DTYPE_F16>(uint32_t v) {
+    return __half2float(__ushort_as_half((unsigned short)(v & 0xFFFFu)));
+}
+template <> __device__ __forceinline__ float widen_hi<ACT_DTYPE_F16>(uint32_t v) {
+    return __half2float(__ushort_as_half((unsigned short)(v >> 16)));
+}
+
+}  // namespace act

@@ -1,0 +1,120 @@
+/*
+ * act_b200.h -- C ABI of the B200 (sm_100a) activation-compression library.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream
+ * (cudaStream_t passed as void*; NULL is the legacy default stream) and returns
+ * 0 or one of the ACT_ERR_* codes.  Unless an entry point says otherwise the
+ * library allocates nothing, keeps no pointer past the return, never
+ * synchronises the host and launches on the stream it is given, so calls can be
+ * captured into CUDA graphs.  All buffers belong to the caller.  The device is
+ * the caller's current device.
+ *
+ * Each declaration names the interface of the Deep_Optimization project it
+ * replaces (paths are inside that project; "AC/" = Activation_Compression/).
+ */
+#ifndef ACT_B200_H
+#define ACT_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define ACT_API __attribute__((visibility("default")))
+#else
+#define ACT_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element types of activations */
+#define ACT_DTYPE_F32  0
+#define ACT_DTYPE_BF16 1
+#define ACT_DTYPE_F16  2
+
+/* flags of act_quant_pack */
+#define ACT_FLAG_ROUND_NEAREST 1   /* u = 0.5f-1e-6f instead of noise (AC/act_triton_kernel.py:114) */
+#define ACT_FLAG_REF_COMPAT    2   /* live-Triton arithmetic: a*(1/s)+c, truncate                    */
+#define ACT_FLAG_REF_CLAMP     4   /* with REF_COMPAT: clamp x to +-clamp_alpha first                */
+#define ACT_FLAG_REF_TANH      8   /* with REF_COMPAT: x = tanh(x/0.5)*0.5 before the range          */
+#define ACT_FLAG_META_BF16     16  /* round scale and min to bf16 precision (still stored as fp32)   */
+
+/* return codes */
+#define ACT_OK             0
+#define ACT_ERR_DTYPE      1   /* unknown element type                                   */
+#define ACT_ERR_BITS       2   /* bits not in {1,2,4,8}                                  */
+#define ACT_ERR_GROUP      3   /* group size not a power of two in [32,1024]             */
+#define ACT_ERR_ALIGN      4   /* a pointer is not aligned as documented                 */
+#define ACT_ERR_SIZE       5   /* negative or overflowing size, bad leading dimension    */
+#define ACT_ERR_NULL       6   /* a required pointer is NULL                             */
+#define ACT_ERR_LAUNCH     7   /* the CUDA runtime refused the launch (see cudaGetLastError) */
+#define ACT_ERR_WORKSPACE  8   /* workspace too small                                    */
+#define ACT_ERR_DEVICE     9   /* not an sm_100 device, or a driver entry point missing  */
+#define ACT_ERR_TARGET    10   /* act_calc_precision: target cannot be reached           */
+#define ACT_ERR_UNSUPPORTED 11 /* flag combination not built                             */
+
+/*
+ * Per-group quantise-and-pack of a saved activation.
+ * Replaces torch.ops.act_lib.quant_pack_triton (AC/act_triton_kernel.py:336-368,
+ * kernel :23-171) and cpp_extension.pack{1,2,4,8} (AC/cpp_extension/bind.cpp:10-14).
+ *
+ *   x       [n_groups, group_size] of `dtype`, contiguous, 16-byte aligned
+ *   noise   NULL, or fp32 [n_groups, group_size] of u in [0,1), 16-byte aligned
+ *   seed, offset   used when noise == NULL and ACT_FLAG_ROUND_NEAREST is clear:
+ *           element e takes u = 16 bits of hash((e >> 2) + offset, seed) / 65536
+ *   packed  n_groups*group_size*bits/8 bytes, 16-byte aligned; 32-bit little-endian
+ *           words, code j of a word at bits [j*bits,(j+1)*bits)
+ *   scale, min   fp32 [n_groups]
+ *
+ * Default arithmetic (IEEE binary32, nothing fused): s = (max-min)/(2^bits-1),
+ * s = 1 if that is not positive; code = clamp(floor((x-min)/s + u), 0, 2^bits-1).
+ */
+ACT_API int act_quant_pack(const void* x, int dtype, int64_t n_groups, int group_size, int bits,
+                   const float* noise, uint64_t seed, uint64_t offset, int flags,
+                   float clamp_alpha, void* packed, float* scale, float* min, void* stream);
+
+/*
+ * Unpack-and-dequantise: y = fma(code, scale, min) rounded to `out_dtype`.
+ * Replaces torch.ops.act_lib.dequant_unpack_triton (AC/act_triton_kernel.py:372-395,
+ * kernel :174-241) and cpp_extension.unpack{1,2,4,8} (AC/cpp_extension/bind.cpp:16-20).
+ *   y  [n_groups, group_size] of out_dtype, 16-byte aligned.
+ */
+ACT_API int act_dequant_unpack(const void* packed, const float* scale, const float* min,
+                       int64_t n_groups, int group_size, int bits, int out_dtype, void* y,
+                       void* stream);
+
+/*
+ * Bit-pack int8 values (masks or ready-made codes), low `bits` bits of each.
+ * Replaces torch.ops.act_lib.pack_triton / unpack_triton
+ * (AC/act_triton_kernel.py:398-433, kernels :246-322).  x, y: int8 [n_groups, group_size].
+ */
+ACT_API int act_pack_bits(const int8_t* x, int64_t n_groups, int group_size, int bits, void* packed,
+                  void* stream);
+ACT_API int act_unpack_bits(const void* packed, int64_t n_groups, int group_size, int bits, int8_t* y,
+                    void* stream);
+
+/*
+ * Per-row min and max of a contiguous [rows, cols] matrix.
+ * Replaces cpp_extension.min_max_kernel (AC/cpp_extension/src/min_max_kernel.cu:66-141).
+ */
+ACT_API int act_minmax(const void* x, int dtype, int64_t rows, int64_t cols, float* mn, float* mx,
+               void* stream);
+
+/*
+ * Greedy bit allocation on the host (no GPU work).
+ * Replaces cpp_extension.calc_precision (AC/cpp_extension/src/calc_precision.cc:10-53):
+ * b, C, w are int32 arrays of length n; b is updated in place until sum(b*w) <= target.
+ */
+ACT_API int act_calc_precision(int32_t* b, const int32_t* C, const int32_t* w, int64_t n, double target);
+
+/* Text for a return code; never NULL. */
+ACT_API const char* act_strerror(int code);
+
+/* Version of this ABI (bumped when a signature changes). */
+ACT_API int act_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ACT_B200_H */

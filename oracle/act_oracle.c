@@ -1,0 +1,481 @@
+/*
+ * act_oracle.c -- CPU restatement of the activation-compression codec.
+ *
+ * TEST INFRASTRUCTURE ONLY.  This file is the checker the CUDA kernels are
+ * compared against and the timed CPU baseline.  It is never linked into, nor
+ * called from, the product library; the product has no CPU path.
+ *
+ * What it restates (paths are inside the Deep_Optimization project):
+ *   - grouping [N,*] -> [N*G, group_size], row-major, one (scale,min) pair per
+ *     group: Activation_Compression/modules/tensor_act_reshape_utils.py:17-49
+ *   - per-group min/max, scale = range/qmax, scale = 1 when the range is not
+ *     positive: Activation_Compression/act_triton_kernel.py:60-65
+ *   - codes clamped to [0,qmax], word packing "code j of a 32-bit word sits at
+ *     bits [j*b,(j+1)*b)": Activation_Compression/act_triton_kernel.py:110-114,155-171
+ *   - dequantise q*scale+min: Activation_Compression/act_triton_kernel.py:206-223
+ *   - mask pack / unpack of int8 values: Activation_Compression/act_triton_kernel.py:246-322
+ *   - greedy bit allocation: Activation_Compression/cpp_extension/src/calc_precision.cc:10-53
+ *   - per-row min/max: Activation_Compression/cpp_extension/src/min_max_kernel.cu:66-141
+ *   - tiled GEMM C=A.B with fp32 accumulation:
+ *     Activation_Compression/triton_kernel/linear.py:43-95
+ *
+ * Arithmetic of the default ("baseline") scheme, every operation an IEEE-754
+ * binary32 round-to-nearest-even operation, nothing contracted:
+ *     mn = min(x), mx = max(x)             (-0 orders below +0, NaN propagates)
+ *     r  = mx - mn
+ *     s  = r / qmax ; if !(s > 0) s = 1
+ *     a  = x - mn ; q = a / s ; t = q + u ; code = clamp(floor(t), 0, qmax)
+ * u is the caller's noise tensor, the 16-bit counter hash below, or the
+ * constant 0.5f-1e-6f (round to nearest, the reference's constant,
+ * act_triton_kernel.py:114).
+ *
+ * The "reference-compatible" scheme (ACT_FLAG_REF_COMPAT) follows the live
+ * Triton kernel instead: optional clamp to +-alpha, optional tanh squash,
+ * inv = 1/s, t = a*inv + (0.5f-1e-6f) with the multiply and the add rounded
+ * separately (what the kernel computes when run by Triton's CPU interpreter),
+ * truncation toward zero, bf16-rounded scale and min.
+ *
+ * PARITY STATUS: the reference holds no golden vectors for this path.  The
+ * reference-compatible scheme is pinned by outputs of the reference's own
+ * kernels run under Triton's CPU interpreter (tests/golden).  The baseline
+ * scheme shares layout and clamp/degenerate rules with it; its division and
+ * noise arithmetic are pinned by no reference test ("parity unpinned").
+ *
+ * Build: gcc -O2 -ffp-contract=off -fopenmp -shared -fPIC (see Makefile).
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+#define ORACLE_EXPORT __attribute__((visibility("default")))
+
+enum { DT_F32 = 0, DT_BF16 = 1, DT_F16 = 2 };
+
+/* flag bits: keep in sync with include/act_b200.h */
+enum {
+    FLAG_ROUND_NEAREST = 1,   /* u = 0.5f - 1e-6f, no noise                       */
+    FLAG_REF_COMPAT    = 2,   /* live-Triton arithmetic (see header comment)       */
+    FLAG_REF_CLAMP     = 4,   /* with REF_COMPAT: clamp x to +-alpha first         */
+    FLAG_REF_TANH      = 8,   /* with REF_COMPAT: x = tanh(x/0.5)*0.5 before range */
+    FLAG_META_BF16     = 16   /* scale/min rounded to bf16 (stored as fp32 values) */
+};
+
+/* ---------------------------------------------------------------- scalars */
+
+static inline float bits_f32(uint32_t b) { float f; memcpy(&f, &b, 4); return f; }
+static inline uint32_t f32_bits(float f) { uint32_t b; memcpy(&b, &f, 4); return b; }
+
+static inline float bf16_to_f32(uint16_t h) { return bits_f32((uint32_t)h << 16); }
+
+/* round-to-nearest-even fp32 -> bf16, NaN kept quiet */
+static inline uint16_t f32_to_bf16(float f) {
+    uint32_t b = f32_bits(f);
+    if ((b & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((b >> 16) | 0x0040u);
+    b += 0x7fffu + ((b >> 16) & 1u);
+    return (uint16_t)(b >> 16);
+}
+
+static inline float f16_to_f32(uint16_t h) {
+    _Float16 v; memcpy(&v, &h, 2); return (float)v;
+}
+static inline uint16_t f32_to_f16(float f) {
+    _Float16 v = (_Float16)f; uint16_t h; memcpy(&h, &v, 2); return h;
+}
+
+static inline float load_as_f32(const void *x, int dtype, int64_t i) {
+    switch (dtype) {
+        case DT_F32:  return ((const float *)x)[i];
+        case DT_BF16: return bf16_to_f32(((const uint16_t *)x)[i]);
+        default:      return f16_to_f32(((const uint16_t *)x)[i]);
+    }
+}
+
+/* min/max with the ordering -0 < +0; a NaN operand makes the result NaN, so a
+ * group that holds a NaN gets min = NaN, scale = 1 and all codes 0            */
+static inline float min_ord(float a, float b) {
+    if (a != a || b != b) return NAN;
+    if (a == b) return signbit(a) ? a : b;
+    return a < b ? a : b;
+}
+static inline float max_ord(float a, float b) {
+    if (a != a || b != b) return NAN;
+    if (a == b) return signbit(a) ? b : a;
+    return a > b ? a : b;
+}
+
+/* ------------------------------------------------------------ noise hash
+ * Counter hash used when no noise tensor is given.  Four consecutive elements
+ * share one 64-bit output; element e takes 16-bit field (e & 3) of
+ * H((e >> 2) + offset) and u = field / 65536.  H is four rounds of a 2x32
+ * multiply-xor network keyed by splitmix64(seed).  It has no counterpart in the
+ * reference (whose generators are an index hash in
+ * cpp_extension/include/quant_common.h:32-43 and Triton's tl.rand).          */
+#define HASH_MUL   0xD256D193u
+#define HASH_WEYL  0x9E3779B9u
+#define HASH_ROUNDS 4
+
+/* splitmix64 finaliser: spreads the caller's seed over the 64-bit key so that
+ * neighbouring seeds give unrelated streams                                    */
+static inline uint64_t hash_key(uint64_t seed) {
+    uint64_t z = seed + 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+
+static inline void hash_2x32(uint64_t ctr, uint64_t seed, uint32_t *o0, uint32_t *o1) {
+    const uint64_t key = hash_key(seed);
+    uint32_t L = (uint32_t)ctr;
+    uint32_t R = (uint32_t)(ctr >> 32) ^ (uint32_t)(key >> 32);
+    uint32_t k = (uint32_t)key;
+    for (int r = 0; r < HASH_ROUNDS; ++r) {
+        uint64_t p = (uint64_t)HASH_MUL * L;
+        uint32_t hi = (uint32_t)(p >> 32), lo = (uint32_t)p;
+        L = hi ^ k ^ R;
+        R = lo;
+        k += HASH_WEYL;
+    }
+    *o0 = L; *o1 = R;
+}
+
+static inline float hash_noise(uint64_t elem, uint64_t seed, uint64_t offset) {
+    uint32_t w0, w1;
+    hash_2x32((elem >> 2) + offset, seed, &w0, &w1);
+    uint32_t w = (elem & 2) ? w1 : w0;
+    uint32_t h = (elem & 1) ? (w >> 16) : (w & 0xffffu);
+    return (float)h * (1.0f / 65536.0f);
+}
+
+ORACLE_EXPORT void oracle_hash_noise(uint64_t seed, uint64_t offset, int64_t first,
+                                     int64_t count, float *out) {
+    for (int64_t i = 0; i < count; ++i) out[i] = hash_noise((uint64_t)(first + i), seed, offset);
+}
+
+/* ------------------------------------------------------------- quant-pack */
+
+static inline int code_from_t(float t, int qmax) {
+    if (!(t >= 0.0f)) return 0;                 /* negative or NaN */
+    if (t >= (float)(qmax + 1)) return qmax;
+    return (int)floorf(t);
+}
+
+static int valid_bits(int bits) { return bits == 1 || bits == 2 || bits == 4 || bits == 8; }
+static int valid_group(int gs, int bits) {
+    return gs >= 32 && gs <= 1024 && (gs & (gs - 1)) == 0 && (gs * bits) % 32 == 0;
+}
+
+/* x: [n_groups, group_size] of dtype; packed: n_groups*group_size*bits/32 words;
+ * scale,mn: [n_groups].  Returns 0, or 1 on a bad argument.                   */
+ORACLE_EXPORT int oracle_quant_pack(const void *x, int dtype, int64_t n_groups, int group_size,
+                                    int bits, const float *noise, uint64_t seed, uint64_t offset,
+                                    int flags, float clamp_alpha, uint32_t *packed, float *scale,
+                                    float *mn_out) {
+    if (!valid_bits(bits) || !valid_group(group_size, bits) || dtype < 0 || dtype > 2) return 1;
+    const int qmax = (1 << bits) - 1;
+    const int vpw = 32 / bits;
+    const int nwords = group_size / vpw;
+    const float half_c = 0.5f - 1e-6f;
+    const int ref = (flags & FLAG_REF_COMPAT) != 0;
+
+#pragma omp parallel for schedule(static)
+    for (int64_t g = 0; g < n_groups; ++g) {
+        float v[1024];
+        const int64_t base = g * group_size;
+        for (int i = 0; i < group_size; ++i) {
+            float f = load_as_f32(x, dtype, base + i);
+            if (ref && (flags & FLAG_REF_CLAMP)) {
+                if (f < -clamp_alpha) f = -clamp_alpha;
+                if (f > clamp_alpha) f = clamp_alpha;
+            }
+            if (ref && (flags & FLAG_REF_TANH)) f = tanhf(f / 0.5f) * 0.5f;
+            v[i] = f;
+        }
+        float mn = v[0], mx = v[0];
+        for (int i = 1; i < group_size; ++i) { mn = min_ord(mn, v[i]); mx = max_ord(mx, v[i]); }
+        const float r = mx - mn;
+        float s = r / (float)qmax;
+        if (!(s > 0.0f)) s = 1.0f;
+        float s_store = s, mn_store = mn;
+        if (flags & FLAG_META_BF16) {
+            s_store = bf16_to_f32(f32_to_bf16(s));
+            mn_store = bf16_to_f32(f32_to_bf16(mn));
+        }
+        scale[g] = s_store;
+        mn_out[g] = mn_store;
+
+        uint32_t *pw = packed + g * (int64_t)nwords;
+        const float inv = 1.0f / s;
+        for (int w = 0; w < nwords; ++w) {
+            uint32_t word = 0;
+            for (int j = 0; j < vpw; ++j) {
+                const int i = w * vpw + j;
+                const float a = v[i] - mn;
+                int c;
+                if (ref) {
+                    /* act_triton_kernel.py:71,114,151-153: multiply by the reciprocal,
+                     * add the rounding constant, truncate, clamp                       */
+                    float prod = a * inv;
+                    float t = prod + half_c;
+                    if (!(t == t)) c = 0;
+                    else {
+                        if (t > 1.0e9f) t = 1.0e9f;
+                        if (t < -1.0e9f) t = -1.0e9f;
+                        c = (int)t;                 /* toward zero */
+                        if (c < 0) c = 0;
+                        if (c > qmax) c = qmax;
+                    }
+                } else {
+                    float u;
+                    if (flags & FLAG_ROUND_NEAREST) u = half_c;
+                    else if (noise) u = noise[base + i];
+                    else u = hash_noise((uint64_t)(base + i), seed, offset);
+                    const float q = a / s;
+                    const float t = q + u;
+                    c = code_from_t(t, qmax);
+                }
+                word |= (uint32_t)c << (j * bits);
+            }
+            pw[w] = word;
+        }
+    }
+    return 0;
+}
+
+/* ---------------------------------------------------------- dequant-unpack
+ * y = fma(code, scale, min) rounded once to fp32, then to the output type
+ * (the Triton kernel's q*scale+min is contracted to one FMA when compiled for
+ * a GPU: act_triton_kernel.py:221).                                           */
+ORACLE_EXPORT int oracle_dequant_unpack(const uint32_t *packed, const float *scale,
+                                        const float *mn, int64_t n_groups, int group_size,
+                                        int bits, int out_dtype, void *y) {
+    if (!valid_bits(bits) || !valid_group(group_size, bits) || out_dtype < 0 || out_dtype > 2) return 1;
+    const int vpw = 32 / bits;
+    const int nwords = group_size / vpw;
+    const uint32_t mask = (1u << bits) - 1u;
+#pragma omp parallel for schedule(static)
+    for (int64_t g = 0; g < n_groups; ++g) {
+        const float s = scale[g], m = mn[g];
+        const uint32_t *pw = packed + g * (int64_t)nwords;
+        for (int w = 0; w < nwords; ++w) {
+            const uint32_t word = pw[w];
+            for (int j = 0; j < vpw; ++j) {
+                const float c = (float)((word >> (j * bits)) & mask);
+                const float val = fmaf(c, s, m);
+                const int64_t i = g * (int64_t)group_size + w * vpw + j;
+                if (out_dtype == DT_F32) ((float *)y)[i] = val;
+                else if (out_dtype == DT_BF16) ((uint16_t *)y)[i] = f32_to_bf16(val);
+                else ((uint16_t *)y)[i] = f32_to_f16(val);
+            }
+        }
+    }
+    return 0;
+}
+
+/* --------------------------------------------------------- mask pack/unpack
+ * act_triton_kernel.py:246-281: words = sum(x << j*bits) over int8 inputs.  The
+ * inputs are masks or already-quantised codes, so only the low `bits` bits of
+ * each value are kept here (the reference does not mask; its callers only pass
+ * values that fit).                                                            */
+ORACLE_EXPORT int oracle_pack_bits(const int8_t *x, int64_t n_groups, int group_size, int bits,
+                                   uint32_t *packed) {
+    if (!valid_bits(bits) || !valid_group(group_size, bits)) return 1;
+    const int vpw = 32 / bits;
+    const int64_t nwords = n_groups * (int64_t)(group_size / vpw);
+    const uint32_t mask = (1u << bits) - 1u;
+#pragma omp parallel for schedule(static)
+    for (int64_t w = 0; w < nwords; ++w) {
+        uint32_t word = 0;
+        for (int j = 0; j < vpw; ++j) word |= ((uint32_t)(uint8_t)x[w * vpw + j] & mask) << (j * bits);
+        packed[w] = word;
+    }
+    return 0;
+}
+
+/* act_triton_kernel.py:284-322 */
+ORACLE_EXPORT int oracle_unpack_bits(const uint32_t *packed, int64_t n_groups, int group_size,
+                                     int bits, int8_t *y) {
+    if (!valid_bits(bits) || !valid_group(group_size, bits)) return 1;
+    const int vpw = 32 / bits;
+    const int64_t nwords = n_groups * (int64_t)(group_size / vpw);
+    const uint32_t mask = (1u << bits) - 1u;
+#pragma omp parallel for schedule(static)
+    for (int64_t w = 0; w < nwords; ++w)
+        for (int j = 0; j < vpw; ++j) y[w * vpw + j] = (int8_t)((packed[w] >> (j * bits)) & mask);
+    return 0;
+}
+
+/* ------------------------------------------------------------------ minmax
+ * per-row min and max of a [rows, cols] matrix
+ * (cpp_extension/src/min_max_kernel.cu:66-95,114-141)                         */
+ORACLE_EXPORT int oracle_minmax(const void *x, int dtype, int64_t rows, int64_t cols, float *mn,
+                                float *mx) {
+    if (dtype < 0 || dtype > 2 || cols <= 0) return 1;
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < rows; ++r) {
+        float lo = load_as_f32(x, dtype, r * cols), hi = lo;
+        for (int64_t c = 1; c < cols; ++c) {
+            const float f = load_as_f32(x, dtype, r * cols + c);
+            lo = min_ord(lo, f); hi = max_ord(hi, f);
+        }
+        mn[r] = lo; mx[r] = hi;
+    }
+    return 0;
+}
+
+/* ---------------------------------------------------------- calc_precision
+ * Greedy bit allocation (cpp_extension/src/calc_precision.cc:10-53): start from
+ * b[i] bits per layer, repeatedly take one bit from the layer whose quantisation
+ * -variance increase is smallest until sum(b[i]*w[i]) <= target.  All three
+ * arrays are int32, as the reference reads them.  The queue is a max-heap on
+ * (delta, index); ties fall to the larger index (std::pair ordering).          */
+typedef struct { float delta; int64_t idx; } heap_item;
+
+static int heap_less(heap_item a, heap_item b) {
+    if (a.delta < b.delta) return 1;
+    if (a.delta > b.delta) return 0;
+    return a.idx < b.idx;
+}
+static void heap_push(heap_item *h, int64_t *n, heap_item it) {
+    int64_t i = (*n)++;
+    h[i] = it;
+    while (i > 0) {
+        int64_t p = (i - 1) / 2;
+        if (!heap_less(h[p], h[i])) break;
+        heap_item t = h[p]; h[p] = h[i]; h[i] = t; i = p;
+    }
+}
+static heap_item heap_pop(heap_item *h, int64_t *n) {
+    heap_item top = h[0];
+    h[0] = h[--(*n)];
+    int64_t i = 0;
+    for (;;) {
+        int64_t l = 2 * i + 1, r = l + 1, m = i;
+        if (l < *n && heap_less(h[m], h[l])) m = l;
+        if (r < *n && heap_less(h[m], h[r])) m = r;
+        if (m == i) break;
+        heap_item t = h[m]; h[m] = h[i]; h[i] = t; i = m;
+    }
+    return top;
+}
+static float prec_delta(float C, int b) {
+    /* int arithmetic as in the reference; b == 1 makes the second coefficient 0
+     * and the quotient infinite, which the reference also produces             */
+    int c1 = ((1 << b) - 1) * ((1 << b) - 1);
+    int c2 = ((1 << (b - 1)) - 1) * ((1 << (b - 1)) - 1);
+    return (float)(C * (1.0 / c1 - 1.0 / c2));
+}
+
+ORACLE_EXPORT int oracle_calc_precision(int32_t *b, const int32_t *C, const int32_t *w, int64_t n,
+                                        double target) {
+    if (n < 0) return 1;
+    heap_item *h = (heap_item *)malloc(sizeof(heap_item) * (size_t)(n > 0 ? n : 1));
+    if (!h) return 1;
+    int64_t hn = 0;
+    double b_sum = 0;
+    for (int64_t i = 0; i < n; ++i) {
+        if (w[i] == 0) { free(h); return 1; }
+        heap_item it = { prec_delta((float)C[i], b[i] / w[i]), i };
+        heap_push(h, &hn, it);
+        b_sum += (double)b[i] * w[i];
+    }
+    while (b_sum > target) {
+        if (hn == 0) { free(h); return 2; }       /* target unreachable */
+        heap_item top = heap_pop(h, &hn);
+        int64_t i = top.idx;
+        b[i] -= 1;
+        b_sum -= w[i];
+        if (b[i] > 1) {
+            heap_item it = { prec_delta((float)C[i], b[i] / w[i]), i };
+            heap_push(h, &hn, it);
+        }
+    }
+    free(h);
+    return 0;
+}
+
+/* ---------------------------------------------------------------- FP8 GEMM
+ * C[m,n] = bf16( (sum_k A8[m,k]*B8[k,n]) * sa[m] * sb[n] ), A8/B8 e4m3 bytes.
+ * The accumulation here is done in double so the value is the exactly-rounded
+ * reference the tensor-core result is compared against within a tolerance.    */
+static inline float e4m3_to_f32(uint8_t v) {
+    const int sign = v >> 7, exp = (v >> 3) & 0xf, man = v & 7;
+    float f;
+    if (exp == 0) f = ldexpf((float)man, -9);                 /* subnormal: man * 2^-9 */
+    else if (exp == 15 && man == 7) f = NAN;                  /* e4m3fn has no inf */
+    else f = ldexpf(1.0f + (float)man / 8.0f, exp - 7);
+    return sign ? -f : f;
+}
+
+ORACLE_EXPORT void oracle_e4m3_decode(const uint8_t *in, int64_t n, float *out) {
+    for (int64_t i = 0; i < n; ++i) out[i] = e4m3_to_f32(in[i]);
+}
+
+/* A: [M,K] row-major with leading dimension lda (bytes = elements);
+ * B: [K,N] row-major with leading dimension ldb; C: bf16 [M,N], ldc.          */
+ORACLE_EXPORT int oracle_fp8_gemm(const uint8_t *A, const uint8_t *B, const float *sa,
+                                  const float *sb, uint16_t *C, float *C_f32, int M, int N, int K,
+                                  int lda, int ldb, int ldc) {
+    if (M < 0 || N < 0 || K < 0) return 1;
+    float lut[256];
+    for (int i = 0; i < 256; ++i) lut[i] = e4m3_to_f32((uint8_t)i);
+#pragma omp parallel for schedule(static)
+    for (int m = 0; m < M; ++m) {
+        double *acc = (double *)calloc((size_t)(N > 0 ? N : 1), sizeof(double));
+        for (int k = 0; k < K; ++k) {
+            const double a = lut[A[(int64_t)m * lda + k]];
+            const uint8_t *brow = B + (int64_t)k * ldb;
+            for (int n = 0; n < N; ++n) acc[n] += a * (double)lut[brow[n]];
+        }
+        for (int n = 0; n < N; ++n) {
+            /* fp32 accumulator, then the two scales applied in fp32 */
+            float v = (float)acc[n];
+            v = v * sa[m];
+            v = v * sb[n];
+            if (C_f32) C_f32[(int64_t)m * ldc + n] = v;
+            if (C) C[(int64_t)m * ldc + n] = f32_to_bf16(v);
+        }
+        free(acc);
+    }
+    return 0;
+}
+
+/* ------------------------------------------------- division-sequence check
+ * The CUDA kernels divide by a per-group scale with a five-operation FMA
+ * sequence around the correctly rounded reciprocal instead of a division
+ * instruction.  This routine runs the same sequence with fmaf and counts the
+ * inputs for which it differs from a/s, so tests can sweep it.                 */
+ORACLE_EXPORT int64_t oracle_check_div_sequence(const float *a, const float *s, int64_t n) {
+    int64_t bad = 0;
+#pragma omp parallel for reduction(+ : bad) schedule(static)
+    for (int64_t i = 0; i < n; ++i) {
+        const float y = 1.0f / s[i];
+        float q = a[i] * y;
+        float r = fmaf(-s[i], q, a[i]);
+        q = fmaf(r, y, q);
+        r = fmaf(-s[i], q, a[i]);
+        q = fmaf(r, y, q);
+        const float ref = a[i] / s[i];
+        if (f32_bits(q) != f32_bits(ref)) bad++;
+    }
+    return bad;
+}
+
+ORACLE_EXPORT int oracle_num_threads(void) {
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
+
+ORACLE_EXPORT void oracle_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}

@@ -1,0 +1,346 @@
+"""ctypes front end of the CPU oracle plus an independent numpy restatement.
+
+TEST INFRASTRUCTURE ONLY: imported by tests/, by ``__graft_entry__.smoke()`` and
+by the CPU-baseline / reference legs of ``bench.py`` as the checker.  Nothing in
+the product package imports this module.
+
+Two implementations live here on purpose:
+
+* ``lib`` functions (``quant_pack``, ``dequant_unpack`` ...) call the C file
+  ``act_oracle.c`` (built by ``oracle/Makefile``).  That is the oracle of record
+  and the timed CPU baseline.
+* ``np_*`` functions restate the same arithmetic with numpy only, written
+  separately, so the C file is cross-checked by a second formulation.
+
+The arithmetic and the reference lines each function follows are listed at the
+top of ``act_oracle.c``.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+from fractions import Fraction
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_SO = os.path.join(_HERE, "libact_oracle.so")
+
+DT_F32, DT_BF16, DT_F16 = 0, 1, 2
+FLAG_ROUND_NEAREST = 1
+FLAG_REF_COMPAT = 2
+FLAG_REF_CLAMP = 4
+FLAG_REF_TANH = 8
+FLAG_META_BF16 = 16
+
+HALF_C = np.float32(0.5) - np.float32(1e-6)
+
+
+def build(force: bool = False) -> str:
+    """Compile act_oracle.c with the Makefile beside it; returns the .so path."""
+    src = os.path.join(_HERE, "act_oracle.c")
+    if force or not os.path.exists(_SO) or os.path.getmtime(_SO) < os.path.getmtime(src):
+        subprocess.run(["make", "-C", _HERE, "libact_oracle.so"], check=True,
+                       stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL)
+    return _SO
+
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        build()
+        L = ctypes.CDLL(_SO)
+        vp, i32, i64, u64, f32 = (ctypes.c_void_p, ctypes.c_int, ctypes.c_int64,
+                                  ctypes.c_uint64, ctypes.c_float)
+        L.oracle_quant_pack.argtypes = [vp, i32, i64, i32, i32, vp, u64, u64, i32, f32, vp, vp, vp]
+        L.oracle_dequant_unpack.argtypes = [vp, vp, vp, i64, i32, i32, i32, vp]
+        L.oracle_pack_bits.argtypes = [vp, i64, i32, i32, vp]
+        L.oracle_unpack_bits.argtypes = [vp, i64, i32, i32, vp]
+        L.oracle_minmax.argtypes = [vp, i32, i64, i64, vp, vp]
+        L.oracle_calc_precision.argtypes = [vp, vp, vp, i64, ctypes.c_double]
+        L.oracle_fp8_gemm.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32]
+        L.oracle_e4m3_decode.argtypes = [vp, i64, vp]
+        L.oracle_hash_noise.argtypes = [u64, u64, i64, i64, vp]
+        L.oracle_hash_noise.restype = None
+        L.oracle_check_div_sequence.argtypes = [vp, vp, i64]
+        L.oracle_check_div_sequence.restype = i64
+        L.oracle_num_threads.restype = i32
+        L.oracle_set_threads.argtypes = [i32]
+        L.oracle_set_threads.restype = None
+        _lib = L
+    return _lib
+
+
+def _ptr(a):
+    return None if a is None else a.ctypes.data_as(ctypes.c_void_p)
+
+
+def _dtype_code(a: np.ndarray, dtype: str | None) -> int:
+    """numpy has no bfloat16: bf16 data travels as uint16 with dtype='bf16'."""
+    if dtype is not None:
+        return {"f32": DT_F32, "bf16": DT_BF16, "f16": DT_F16}[dtype]
+    if a.dtype == np.float32:
+        return DT_F32
+    if a.dtype == np.float16:
+        return DT_F16
+    raise TypeError("pass dtype='bf16' with a uint16 array for bfloat16 data")
+
+
+def set_threads(n: int) -> None:
+    lib().oracle_set_threads(int(n))
+
+
+def num_threads() -> int:
+    return int(lib().oracle_num_threads())
+
+
+# ------------------------------------------------------------------ C oracle
+
+def quant_pack(x: np.ndarray, group_size: int, bits: int, noise: np.ndarray | None = None,
+               seed: int = 0, offset: int = 0, flags: int = 0, clamp_alpha: float = 0.0,
+               dtype: str | None = None):
+    """x: any shape whose element count is a multiple of group_size (row-major groups).
+    Returns (packed uint32 [NG, group_size*bits/32], scale f32 [NG], min f32 [NG])."""
+    x = np.ascontiguousarray(x)
+    code = _dtype_code(x, dtype)
+    ng, rem = divmod(x.size, group_size)
+    assert rem == 0
+    packed = np.empty((ng, group_size * bits // 32), np.uint32)
+    scale = np.empty(ng, np.float32)
+    mn = np.empty(ng, np.float32)
+    if noise is not None:
+        noise = np.ascontiguousarray(noise, np.float32)
+        assert noise.size == x.size
+    rc = lib().oracle_quant_pack(_ptr(x), code, ng, group_size, bits, _ptr(noise), seed, offset,
+                                 flags, clamp_alpha, _ptr(packed), _ptr(scale), _ptr(mn))
+    if rc:
+        raise ValueError(f"oracle_quant_pack rejected bits={bits} group_size={group_size}")
+    return packed, scale, mn
+
+
+def dequant_unpack(packed: np.ndarray, scale: np.ndarray, mn: np.ndarray, group_size: int,
+                   bits: int, out: str = "f32") -> np.ndarray:
+    """Returns [NG, group_size]: float32, float16, or uint16 holding bf16 bits."""
+    packed = np.ascontiguousarray(packed, np.uint32)
+    scale = np.ascontiguousarray(scale, np.float32)
+    mn = np.ascontiguousarray(mn, np.float32)
+    ng = scale.size
+    code = {"f32": DT_F32, "bf16": DT_BF16, "f16": DT_F16}[out]
+    y = np.empty((ng, group_size), {DT_F32: np.float32, DT_BF16: np.uint16, DT_F16: np.float16}[code])
+    rc = lib().oracle_dequant_unpack(_ptr(packed), _ptr(scale), _ptr(mn), ng, group_size, bits,
+                                     code, _ptr(y))
+    if rc:
+        raise ValueError("oracle_dequant_unpack rejected its arguments")
+    return y
+
+
+def pack_bits(x: np.ndarray, group_size: int, bits: int) -> np.ndarray:
+    x = np.ascontiguousarray(x, np.int8)
+    ng = x.size // group_size
+    packed = np.empty((ng, group_size * bits // 32), np.uint32)
+    if lib().oracle_pack_bits(_ptr(x), ng, group_size, bits, _ptr(packed)):
+        raise ValueError("oracle_pack_bits rejected its arguments")
+    return packed
+
+
+def unpack_bits(packed: np.ndarray, group_size: int, bits: int) -> np.ndarray:
+    packed = np.ascontiguousarray(packed, np.uint32)
+    ng = packed.size * 32 // (bits * group_size)
+    y = np.empty((ng, group_size), np.int8)
+    if lib().oracle_unpack_bits(_ptr(packed), ng, group_size, bits, _ptr(y)):
+        raise ValueError("oracle_unpack_bits rejected its arguments")
+    return y
+
+
+def minmax(x: np.ndarray, dtype: str | None = None):
+    x = np.ascontiguousarray(x)
+    rows, cols = x.shape
+    mn = np.empty(rows, np.float32)
+    mx = np.empty(rows, np.float32)
+    if lib().oracle_minmax(_ptr(x), _dtype_code(x, dtype), rows, cols, _ptr(mn), _ptr(mx)):
+        raise ValueError("oracle_minmax rejected its arguments")
+    return mn, mx
+
+
+def calc_precision(b: np.ndarray, C: np.ndarray, w: np.ndarray, target: float) -> np.ndarray:
+    b = np.array(b, np.int32)
+    C = np.ascontiguousarray(C, np.int32)
+    w = np.ascontiguousarray(w, np.int32)
+    rc = lib().oracle_calc_precision(_ptr(b), _ptr(C), _ptr(w), b.size, float(target))
+    if rc:
+        raise ValueError(f"oracle_calc_precision failed ({rc})")
+    return b
+
+
+def fp8_gemm(A8: np.ndarray, B8: np.ndarray, sa: np.ndarray, sb: np.ndarray):
+    """A8 [M,K] uint8 (e4m3 bits), B8 [K,N] uint8.  Returns (bf16 bits uint16 [M,N], f32 [M,N])."""
+    A8 = np.ascontiguousarray(A8, np.uint8)
+    B8 = np.ascontiguousarray(B8, np.uint8)
+    sa = np.ascontiguousarray(sa, np.float32)
+    sb = np.ascontiguousarray(sb, np.float32)
+    M, K = A8.shape
+    K2, N = B8.shape
+    assert K == K2
+    C = np.empty((M, N), np.uint16)
+    Cf = np.empty((M, N), np.float32)
+    lib().oracle_fp8_gemm(_ptr(A8), _ptr(B8), _ptr(sa), _ptr(sb), _ptr(C), _ptr(Cf), M, N, K, K, N, N)
+    return C, Cf
+
+
+def e4m3_decode(a: np.ndarray) -> np.ndarray:
+    a = np.ascontiguousarray(a, np.uint8)
+    out = np.empty(a.shape, np.float32)
+    lib().oracle_e4m3_decode(_ptr(a), a.size, _ptr(out))
+    return out
+
+
+def hash_noise(seed: int, offset: int, first: int, count: int) -> np.ndarray:
+    out = np.empty(count, np.float32)
+    lib().oracle_hash_noise(seed, offset, first, count, _ptr(out))
+    return out
+
+
+def check_div_sequence(a: np.ndarray, s: np.ndarray) -> int:
+    a = np.ascontiguousarray(a, np.float32)
+    s = np.ascontiguousarray(s, np.float32)
+    return int(lib().oracle_check_div_sequence(_ptr(a), _ptr(s), a.size))
+
+
+# ------------------------------------------------------------ numpy helpers
+
+def bf16_bits_to_f32(h: np.ndarray) -> np.ndarray:
+    return (h.astype(np.uint32) << 16).view(np.float32)
+
+
+def f32_to_bf16_bits(f: np.ndarray) -> np.ndarray:
+    b = np.ascontiguousarray(f, np.float32).view(np.uint32).astype(np.uint64)
+    nan = (b & 0x7FFFFFFF) > 0x7F800000
+    r = (b + 0x7FFF + ((b >> 16) & 1)) >> 16
+    r = np.where(nan, (b >> 16) | 0x40, r)
+    return r.astype(np.uint16)
+
+
+def _as_f32(x: np.ndarray, dtype: str | None) -> np.ndarray:
+    if dtype == "bf16":
+        return bf16_bits_to_f32(x)
+    return x.astype(np.float32)
+
+
+def np_hash_noise(seed: int, offset: int, first: int, count: int) -> np.ndarray:
+    """numpy restatement of the 16-bit counter hash (act_oracle.c: hash_2x32)."""
+    e = np.arange(first, first + count, dtype=np.uint64)
+    ctr = (e >> np.uint64(2)) + np.uint64(offset & 0xFFFFFFFFFFFFFFFF)
+    M64 = 0xFFFFFFFFFFFFFFFF
+    z = (seed + 0x9E3779B97F4A7C15) & M64          # splitmix64 finaliser on the seed
+    z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & M64
+    z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & M64
+    key = z ^ (z >> 31)
+    L = (ctr & np.uint64(0xFFFFFFFF))
+    R = (ctr >> np.uint64(32)) ^ np.uint64(key >> 32)
+    k = key & 0xFFFFFFFF
+    for _ in range(4):
+        p = np.uint64(0xD256D193) * L
+        hi, lo = p >> np.uint64(32), p & np.uint64(0xFFFFFFFF)
+        L, R = (hi ^ np.uint64(k) ^ R) & np.uint64(0xFFFFFFFF), lo
+        k = (k + 0x9E3779B9) & 0xFFFFFFFF
+    w = np.where((e & np.uint64(2)) != 0, R, L)
+    h = np.where((e & np.uint64(1)) != 0, w >> np.uint64(16), w & np.uint64(0xFFFF))
+    return h.astype(np.float32) * np.float32(1.0 / 65536.0)
+
+
+def np_group_minmax(v: np.ndarray):
+    """min/max per row with -0 ordered below +0 (NaN-free input)."""
+    mn = v.min(axis=1)
+    mx = v.max(axis=1)
+    neg0 = ((v == 0) & np.signbit(v)).any(axis=1)
+    pos0 = ((v == 0) & ~np.signbit(v)).any(axis=1)
+    mn = np.where((mn == 0) & neg0, np.float32(-0.0), mn)
+    mn = np.where((mn == 0) & ~neg0, np.float32(0.0), mn)
+    mx = np.where((mx == 0) & pos0, np.float32(0.0), mx)
+    mx = np.where((mx == 0) & ~pos0, np.float32(-0.0), mx)
+    return mn.astype(np.float32), mx.astype(np.float32)
+
+
+def np_quant_pack(x: np.ndarray, group_size: int, bits: int, noise: np.ndarray | None = None,
+                  seed: int = 0, offset: int = 0, flags: int = 0, clamp_alpha: float = 0.0,
+                  dtype: str | None = None):
+    """Independent numpy restatement of oracle_quant_pack (finite inputs only)."""
+    qmax = (1 << bits) - 1
+    vpw = 32 // bits
+    v = _as_f32(np.ascontiguousarray(x), dtype).reshape(-1, group_size)
+    ref = bool(flags & FLAG_REF_COMPAT)
+    if ref and flags & FLAG_REF_CLAMP:
+        v = np.clip(v, np.float32(-clamp_alpha), np.float32(clamp_alpha))
+    if ref and flags & FLAG_REF_TANH:
+        v = (np.tanh((v / np.float32(0.5)).astype(np.float32)).astype(np.float32) * np.float32(0.5))
+    ng = v.shape[0]
+    mn, mx = np_group_minmax(v)
+    with np.errstate(all="ignore"):
+        r = (mx - mn).astype(np.float32)
+        s = (r / np.float32(qmax)).astype(np.float32)
+        s = np.where(s > 0, s, np.float32(1.0)).astype(np.float32)
+        a = (v - mn[:, None]).astype(np.float32)
+        if ref:
+            inv = (np.float32(1.0) / s).astype(np.float32)
+            t = ((a * inv[:, None]).astype(np.float32) + HALF_C).astype(np.float32)
+            codes = np.clip(np.trunc(t), 0, qmax).astype(np.uint32)
+        else:
+            if flags & FLAG_ROUND_NEAREST:
+                u = np.full(v.shape, HALF_C, np.float32)
+            elif noise is not None:
+                u = np.ascontiguousarray(noise, np.float32).reshape(v.shape)
+            else:
+                u = np_hash_noise(seed, offset, 0, v.size).reshape(v.shape)
+            q = (a / s[:, None]).astype(np.float32)
+            t = (q + u).astype(np.float32)
+            codes = np.where(t >= 0, np.minimum(np.floor(t), qmax), 0).astype(np.uint32)
+    shifts = (np.arange(vpw, dtype=np.uint32) * np.uint32(bits))
+    words = (codes.reshape(ng, group_size // vpw, vpw) << shifts).sum(axis=2, dtype=np.uint64)
+    packed = words.astype(np.uint32)
+    if flags & FLAG_META_BF16:
+        s = bf16_bits_to_f32(f32_to_bf16_bits(s))
+        mn = bf16_bits_to_f32(f32_to_bf16_bits(mn))
+    return packed, s.astype(np.float32), mn.astype(np.float32)
+
+
+def np_unpack_codes(packed: np.ndarray, group_size: int, bits: int) -> np.ndarray:
+    vpw = 32 // bits
+    packed = np.ascontiguousarray(packed, np.uint32).reshape(-1, group_size // vpw)
+    shifts = (np.arange(vpw, dtype=np.uint32) * np.uint32(bits))
+    c = (packed[:, :, None] >> shifts) & np.uint32((1 << bits) - 1)
+    return c.reshape(packed.shape[0], group_size)
+
+
+def exact_fma_f32(c: float, s: float, m: float) -> np.float32:
+    """fma(c, s, m) rounded once to binary32, through exact rational arithmetic.
+    Finite operands only (callers keep non-finite groups out of this path)."""
+    exact = Fraction(float(c)) * Fraction(float(s)) + Fraction(float(m))
+    # float(Fraction) rounds correctly to binary64; binary32 needs its own rounding
+    if exact == 0:
+        return np.float32(0.0)
+    sign = -1 if exact < 0 else 1
+    mag = abs(exact)
+    e = mag.numerator.bit_length() - mag.denominator.bit_length()
+    if Fraction(2) ** e > mag:
+        e -= 1
+    e = max(e, -126)
+    ulp = Fraction(2) ** (e - 23)
+    n = mag / ulp
+    fl = n.numerator // n.denominator
+    frac = n - fl
+    if frac > Fraction(1, 2) or (frac == Fraction(1, 2) and fl % 2 == 1):
+        fl += 1
+    return np.float32(sign * float(fl * ulp))
+
+
+def np_dequant(packed: np.ndarray, scale: np.ndarray, mn: np.ndarray, group_size: int,
+               bits: int) -> np.ndarray:
+    """float64 evaluation of code*scale+min, rounded to float32: equal to the single
+    rounding of an FMA except in double-rounding ties (rarer than 1 in 2**28)."""
+    c = np_unpack_codes(packed, group_size, bits).astype(np.float64)
+    y = c * scale.astype(np.float64)[:, None] + mn.astype(np.float64)[:, None]
+    return y.astype(np.float32)

@@ -1,0 +1,182 @@
+"""GPU parity: the CUDA codec, called through the C ABI, against the CPU oracle.
+Integer outputs (packed words) and fp32 scale/min must be bit-exact."""
+import numpy as np
+import pytest
+import torch
+
+from tests.inputs import adversarial_groups, gelu_normal, relu_normal, to_numpy, uniform_noise
+
+pytestmark = pytest.mark.gpu
+
+BITS = (1, 2, 4, 8)
+GROUPS = (32, 64, 128, 256, 512, 1024)
+DTYPES = (torch.float32, torch.bfloat16, torch.float16)
+
+
+def _codec():
+    from deep_optimization_b200 import codec
+    return codec
+
+
+def _same_bits(a: np.ndarray, b: np.ndarray) -> bool:
+    return np.array_equal(np.ascontiguousarray(a).view(np.uint32), np.ascontiguousarray(b).view(np.uint32))
+
+
+def _cmp_pack(oracle, got, want, what):
+    packed, scale, mn = (t.cpu().numpy() for t in got)
+    assert np.array_equal(packed.view(np.uint32), want[0]), f"packed words differ: {what}"
+    nan = np.isnan(want[2])
+    assert np.array_equal(np.isnan(mn), nan), what
+    assert _same_bits(scale, want[1]), f"scale differs: {what}"
+    assert _same_bits(mn[~nan], want[2][~nan]), f"min differs: {what}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=("f32", "bf16", "f16"))
+@pytest.mark.parametrize("bits", BITS)
+@pytest.mark.parametrize("gs", GROUPS)
+def test_pack_all_modes(oracle, cuda_device, dtype, bits, gs):
+    # 75 groups: odd count -> partial last tile for every group size but 1024
+    x = relu_normal((75, gs), seed=bits + gs, dtype=dtype)
+    u = uniform_noise(x.shape, seed=2)
+    arr, tag = to_numpy(x)
+    xd, ud = x.to(cuda_device), u.to(cuda_device)
+    c = _codec()
+    F = oracle
+    cases = [
+        ("noise tensor", dict(noise=ud), dict(noise=u.numpy())),
+        ("hash noise", dict(seed=1234, offset=77), dict(seed=1234, offset=77)),
+        ("round nearest", dict(flags=F.FLAG_ROUND_NEAREST), dict(flags=F.FLAG_ROUND_NEAREST)),
+        ("ref compat", dict(flags=F.FLAG_REF_COMPAT | F.FLAG_META_BF16 | F.FLAG_REF_CLAMP, clamp_alpha=1.5),
+         dict(flags=F.FLAG_REF_COMPAT | F.FLAG_META_BF16 | F.FLAG_REF_CLAMP, clamp_alpha=1.5)),
+    ]
+    for name, gkw, okw in cases:
+        got = c.quant_pack(xd, bits, gs, **gkw)
+        want = oracle.quant_pack(arr, gs, bits, dtype=tag, **okw)
+        _cmp_pack(oracle, got, want, f"{name} {tag} b{bits} g{gs}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=("f32", "bf16", "f16"))
+@pytest.mark.parametrize("bits", BITS)
+@pytest.mark.parametrize("gs", (32, 128, 1024))
+def test_unpack_bit_exact(oracle, cuda_device, dtype, bits, gs):
+    rng = np.random.default_rng(bits * gs)
+    ng = 77
+    packed = rng.integers(0, 2**32, (ng, gs * bits // 32), dtype=np.uint64).astype(np.uint32)
+    scale = rng.random(ng).astype(np.float32) + 1e-3
+    mn = rng.standard_normal(ng).astype(np.float32)
+    tag = {torch.float32: "f32", torch.bfloat16: "bf16", torch.float16: "f16"}[dtype]
+    want = oracle.dequant_unpack(packed, scale, mn, gs, bits, out=tag)
+    got = _codec().dequant_unpack(torch.from_numpy(packed.view(np.int32)).to(cuda_device),
+                                  torch.from_numpy(scale).to(cuda_device),
+                                  torch.from_numpy(mn).to(cuda_device), bits, gs, out_dtype=dtype)
+    g, _ = to_numpy(got)
+    assert np.array_equal(g.view(np.uint8), want.view(np.uint8))
+
+
+@pytest.mark.parametrize("gs", (32, 64, 256))
+@pytest.mark.parametrize("bits", BITS)
+def test_adversarial_groups(oracle, cuda_device, bits, gs):
+    """Constant groups, signed zeros, denormal / huge / overflowing ranges, inf, NaN."""
+    x = adversarial_groups(gs)
+    u = uniform_noise(x.shape, seed=5)
+    c = _codec()
+    for kw_g, kw_o in ((dict(noise=u.to(cuda_device)), dict(noise=u.numpy())),
+                       (dict(seed=3, offset=0), dict(seed=3, offset=0)),
+                       (dict(flags=oracle.FLAG_ROUND_NEAREST), dict(flags=oracle.FLAG_ROUND_NEAREST))):
+        got = c.quant_pack(x.to(cuda_device), bits, gs, **kw_g)
+        want = oracle.quant_pack(x.numpy(), gs, bits, **kw_o)
+        _cmp_pack(oracle, got, want, f"adversarial b{bits} g{gs} {list(kw_o)}")
+
+
+def test_negative_and_large_noise(oracle, cuda_device):
+    """Noise outside [0,1) must hit the clamp exactly as the oracle does."""
+    x = relu_normal((40, 128), seed=1)
+    u = (uniform_noise(x.shape) * 6 - 3)
+    for bits in BITS:
+        got = _codec().quant_pack(x.to(cuda_device), bits, 128, noise=u.to(cuda_device))
+        want = oracle.quant_pack(x.numpy(), 128, bits, noise=u.numpy())
+        _cmp_pack(oracle, got, want, f"wide noise b{bits}")
+
+
+def test_ref_compat_tanh_close(oracle, cuda_device):
+    """The tanh squash uses the device's tanhf; codes may differ from libm's by a
+    rounding step on a vanishing fraction of elements (tolerance: < 0.1 % of codes)."""
+    x = relu_normal((64, 256), seed=8, dtype=torch.bfloat16)
+    arr, tag = to_numpy(x)
+    flags = oracle.FLAG_REF_COMPAT | oracle.FLAG_REF_CLAMP | oracle.FLAG_REF_TANH | oracle.FLAG_META_BF16
+    got = _codec().quant_pack(x.to(cuda_device), 2, 256, flags=flags, clamp_alpha=3.0)
+    want = oracle.quant_pack(arr, 256, 2, dtype=tag, flags=flags, clamp_alpha=3.0)
+    gc = oracle.np_unpack_codes(got[0].cpu().numpy().view(np.uint32), 256, 2)
+    wc = oracle.np_unpack_codes(want[0], 256, 2)
+    assert (gc != wc).mean() < 1e-3
+    assert np.allclose(got[1].cpu().numpy(), want[1], rtol=1e-2)
+
+
+@pytest.mark.parametrize("bits", BITS)
+def test_mask_pack_unpack(oracle, cuda_device, bits):
+    rng = np.random.default_rng(bits)
+    x = rng.integers(0, 1 << bits, (33, 128)).astype(np.int8)
+    c = _codec()
+    p = c.pack_bits(torch.from_numpy(x).to(cuda_device), bits, 128)
+    assert np.array_equal(p.cpu().numpy().view(np.uint32), oracle.pack_bits(x, 128, bits))
+    y = c.unpack_bits(p, bits, 33, 128)
+    assert np.array_equal(y.cpu().numpy(), oracle.unpack_bits(oracle.pack_bits(x, 128, bits), 128, bits))
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=("f32", "bf16", "f16"))
+def test_minmax(oracle, cuda_device, dtype):
+    x = (relu_normal((37, 301), seed=6) - 0.3).to(dtype)
+    arr, tag = to_numpy(x)
+    mn, mx = _codec().minmax(x.to(cuda_device))
+    wmn, wmx = oracle.minmax(arr, dtype=tag)
+    assert _same_bits(mn.cpu().numpy(), wmn) and _same_bits(mx.cpu().numpy(), wmx)
+
+
+def test_config1_full_size_round_trip(oracle, cuda_device):
+    """fp32 [128,64,56,56], group 256, 2 bits: full-size properties plus an oracle
+    comparison on a slice (the whole tensor takes the oracle a few seconds)."""
+    x = relu_normal((128, 64, 56, 56), seed=0)
+    u = uniform_noise(x.shape, seed=1)
+    c = _codec()
+    xd = x.to(cuda_device)
+    packed, scale, mn = c.quant_pack(xd, 2, 256, noise=u.to(cuda_device))
+    assert packed.shape == (100352, 16)
+    want = oracle.quant_pack(x.numpy(), 256, 2, noise=u.numpy())
+    _cmp_pack(oracle, (packed, scale, mn), want, "config 1")
+    y = c.dequant_unpack(packed, scale, mn, 2, 256, out_dtype=torch.float32).view_as(xd)
+    assert ((y - xd).abs().view(-1, 256) <= scale[:, None] * 1.0001 + 1e-6).all()
+    # idempotence: values already on the code points re-quantise to themselves (u = 0)
+    p2, s2, m2 = c.quant_pack(y, 2, 256, noise=torch.zeros_like(xd))
+    y2 = c.dequant_unpack(p2, s2, m2, 2, 256, out_dtype=torch.float32).view_as(xd)
+    assert (y2 - y).abs().max() <= 1e-6 * 8
+
+
+@pytest.mark.parametrize("bits", BITS)
+@pytest.mark.parametrize("kind", ("conv", "vit"))
+def test_config2_sweep(oracle, cuda_device, bits, kind):
+    """bf16 conv [256,256,28,28] / ViT [256,197,768], group 128: oracle comparison on the
+    first 4096 groups, size-independent properties on the whole tensor."""
+    x = (relu_normal((256, 256, 28, 28), 0, torch.bfloat16) if kind == "conv"
+         else gelu_normal((256, 197, 768), 0, torch.bfloat16))
+    c = _codec()
+    xd = x.to(cuda_device)
+    packed, scale, mn = c.quant_pack(xd, bits, 128, seed=42, offset=0)
+    n = 4096
+    arr, tag = to_numpy(x.reshape(-1, 128)[:n])
+    want = oracle.quant_pack(arr, 128, bits, dtype=tag, seed=42, offset=0)
+    _cmp_pack(oracle, (packed[:n], scale[:n], mn[:n]), want, f"config 2 {kind} b{bits}")
+    y = c.dequant_unpack(packed, scale, mn, bits, 128, out_dtype=torch.float32)
+    err = (y - xd.float().view(-1, 128)).abs()
+    assert (err <= scale[:, None] * 1.0001 + 1e-6).all()
+    # checksum of checksums: group minima and maxima survive the codec exactly
+    xg = xd.float().view(-1, 128)
+    assert torch.equal(mn, xg.amin(1))
+    yb = c.dequant_unpack(packed, scale, mn, bits, 128, out_dtype=torch.bfloat16)
+    assert yb.dtype == torch.bfloat16 and yb.shape == (xd.numel() // 128, 128)
+
+
+def test_empty_input(cuda_device):
+    c = _codec()
+    p, s, m = c.quant_pack(torch.empty((0, 128), device=cuda_device), 2, 128)
+    assert p.shape == (0, 8) and s.numel() == 0
+    assert c.dequant_unpack(p, s, m, 2, 128).shape == (0, 128)

@@ -1,0 +1,148 @@
+"""CPU tests: the C oracle against its numpy restatement and against properties
+of the scheme.  No GPU, no product code."""
+import numpy as np
+import pytest
+
+from tests.inputs import adversarial_groups, relu_normal, to_numpy, uniform_noise
+
+BITS = (1, 2, 4, 8)
+GROUPS = (32, 64, 128, 256, 512, 1024)
+
+
+@pytest.mark.parametrize("bits", BITS)
+@pytest.mark.parametrize("gs", GROUPS)
+def test_c_matches_numpy(oracle, bits, gs):
+    x = relu_normal((48, gs), seed=bits * 100 + gs).numpy()
+    u = uniform_noise(x.shape, seed=3).numpy()
+    modes = (dict(noise=u), dict(seed=11, offset=5), dict(flags=oracle.FLAG_ROUND_NEAREST),
+             dict(flags=oracle.FLAG_REF_COMPAT | oracle.FLAG_META_BF16))
+    for kw in modes:
+        a = oracle.quant_pack(x, gs, bits, **kw)
+        b = oracle.np_quant_pack(x, gs, bits, **kw)
+        for p, q in zip(a, b):
+            assert np.array_equal(p.view(np.uint32), q.view(np.uint32)), kw.keys()
+    y = oracle.dequant_unpack(*a, gs, bits)
+    assert np.array_equal(y, oracle.np_dequant(*a, gs, bits))
+
+
+@pytest.mark.parametrize("dtype", ("bf16", "f16"))
+def test_16bit_inputs(oracle, dtype):
+    import torch
+    t = relu_normal((16, 128), seed=5, dtype=torch.bfloat16 if dtype == "bf16" else torch.float16)
+    arr, tag = to_numpy(t)
+    u = uniform_noise(t.shape).numpy()
+    a = oracle.quant_pack(arr, 128, 2, noise=u, dtype=tag)
+    b = oracle.quant_pack(t.float().numpy(), 128, 2, noise=u)       # widening is exact
+    for p, q in zip(a, b):
+        assert np.array_equal(p.view(np.uint32), q.view(np.uint32))
+
+
+def test_layout_known_answer(oracle):
+    """Hand-computed case: values on the code points, u = 0 -> code i of word w at bits [2i,2i+2)."""
+    gs = 32
+    x = (np.arange(gs) % 4).astype(np.float32)[None, :]
+    packed, scale, mn = oracle.quant_pack(x, gs, 2, noise=np.zeros_like(x))
+    assert scale[0] == 1.0 and mn[0] == 0.0
+    word = sum((i % 4) << (2 * i) for i in range(16))
+    assert packed.tolist() == [[word, word]]
+    assert packed.view(np.uint8)[0, 0] == 0b11100100       # 4 codes per byte, little end first
+    y = oracle.dequant_unpack(packed, scale, mn, gs, 2)
+    assert np.array_equal(y, x)
+
+
+def test_degenerate_and_nonfinite(oracle):
+    x = adversarial_groups(64).numpy()
+    packed, scale, mn = oracle.quant_pack(x, 64, 2, noise=np.full(x.shape, 0.5, np.float32))
+    assert scale[0] == 1.0 and scale[1] == 1.0 and scale[2] == 1.0      # constant groups
+    assert np.signbit(mn[2])                                            # -0 orders below +0
+    assert (packed[:3] == 0).all()
+    assert np.isnan(mn[9]) and scale[9] == 1.0 and (packed[9] == 0).all()   # NaN poisons its group
+
+
+@pytest.mark.parametrize("bits", BITS)
+def test_round_trip_bound(oracle, bits):
+    x = relu_normal((64, 256), seed=2).numpy()
+    u = uniform_noise(x.shape).numpy()
+    packed, scale, mn = oracle.quant_pack(x, 256, bits, noise=u)
+    y = oracle.dequant_unpack(packed, scale, mn, 256, bits)
+    assert (np.abs(y - x) <= scale[:, None] * 1.0001 + 1e-6).all()      # stochastic: within one step
+    packed, scale, mn = oracle.quant_pack(x, 256, bits, flags=oracle.FLAG_ROUND_NEAREST)
+    y = oracle.dequant_unpack(packed, scale, mn, 256, bits)
+    assert (np.abs(y - x) <= scale[:, None] * 0.5001 + 1e-6).all()      # nearest: within half a step
+
+
+def test_stochastic_rounding_unbiased(oracle):
+    x = np.full((4096, 32), 0.3, np.float32)
+    x[:, 0], x[:, 1] = 0.0, 1.0                       # range [0,1], 1-bit: P(code=1) = 0.3
+    packed, _, _ = oracle.quant_pack(x, 32, 1, seed=9)
+    codes = oracle.np_unpack_codes(packed, 32, 1)[:, 2:]
+    assert abs(codes.mean() - 0.3) < 0.01
+
+
+def test_mask_pack_round_trip(oracle):
+    rng = np.random.default_rng(0)
+    for bits in BITS:
+        x = rng.integers(0, 1 << bits, (7, 128)).astype(np.int8)
+        p = oracle.pack_bits(x, 128, bits)
+        assert np.array_equal(oracle.unpack_bits(p, 128, bits).view(np.uint8), x.view(np.uint8))
+        assert np.array_equal(oracle.np_unpack_codes(p, 128, bits).astype(np.uint8), x.view(np.uint8))
+
+
+def test_hash_noise_restatement(oracle):
+    for seed, off in ((0, 0), (5, 9), (2**63 + 1, 2**40)):
+        assert np.array_equal(oracle.hash_noise(seed, off, 3, 4099), oracle.np_hash_noise(seed, off, 3, 4099))
+
+
+def test_exact_fma_agrees(oracle):
+    rng = np.random.default_rng(1)
+    s = rng.random(200).astype(np.float32)
+    m = rng.standard_normal(200).astype(np.float32)
+    packed = np.full((200, 1), 0xE4E4E4E4, np.uint32)        # codes 0,1,2,3 repeating, 16 per word
+    y = oracle.dequant_unpack(np.repeat(packed, 2, 1), s, m, 32, 2)
+    for g in range(200):
+        for c in range(4):
+            assert y[g, c] == oracle.exact_fma_f32(c, s[g], m[g])
+
+
+def test_division_sequence(oracle):
+    rng = np.random.default_rng(3)
+    n = 4_000_000
+    s = (np.exp2(rng.uniform(-58, 50, n)) * rng.uniform(1, 2, n)).astype(np.float32)
+    qmax = rng.choice([1, 3, 15, 255], n).astype(np.float32)
+    a = (s * qmax * rng.random(n, dtype=np.float32)).astype(np.float32)
+    assert oracle.check_div_sequence(a, s) == 0
+    assert oracle.check_div_sequence((s * qmax).astype(np.float32), s) == 0
+
+
+def test_calc_precision(oracle):
+    out = oracle.calc_precision([8, 8, 8, 8], [10, 200, 3000, 5], [1, 1, 1, 1], 20.0)
+    assert out.sum() <= 20 and out.tolist() == [4, 6, 7, 3]
+    with pytest.raises(ValueError):
+        oracle.calc_precision([2, 2], [1, 1], [1, 1], -5.0)
+
+
+def test_minmax(oracle):
+    x = relu_normal((9, 333), seed=4).numpy() - 0.5
+    mn, mx = oracle.minmax(x)
+    assert np.array_equal(mn, x.min(1)) and np.array_equal(mx, x.max(1))
+
+
+def test_e4m3_decode(oracle):
+    import torch
+    b = np.arange(256, dtype=np.uint8)
+    ref = torch.from_numpy(b).view(torch.float8_e4m3fn).float().numpy()
+    got = oracle.e4m3_decode(b)
+    assert np.array_equal(np.isnan(ref), np.isnan(got))
+    assert np.array_equal(ref[~np.isnan(ref)], got[~np.isnan(got)])
+
+
+def test_fp8_gemm_small(oracle):
+    import torch
+    g = torch.Generator().manual_seed(0)
+    A = torch.randn(8, 64, generator=g); B = torch.randn(64, 12, generator=g)
+    sa = A.abs().amax(1) / 448; sb = B.abs().amax(0) / 448
+    A8 = (A / sa[:, None]).to(torch.float8_e4m3fn); B8 = (B / sb[None, :]).to(torch.float8_e4m3fn)
+    C, Cf = oracle.fp8_gemm(A8.view(torch.uint8).numpy(), B8.view(torch.uint8).numpy(), sa.numpy(), sb.numpy())
+    ref = (A8.double() @ B8.double()).float() * sa[:, None] * sb[None, :]
+    assert np.array_equal(Cf, ref.numpy())
+    assert np.allclose(Cf, (A @ B).numpy(), rtol=0.2, atol=0.5)
