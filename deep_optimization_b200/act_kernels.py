@@ -1,0 +1,120 @@
+"""`torch.ops.act_lib.*` codec operators, backed by the sm_100a CUDA library.
+
+The operator names, positional schemas and return orders are those of
+Activation_Compression/act_triton_kernel.py:336-433 (there implemented in
+Triton), so callers such as `modules/module_utils.py` work unchanged:
+
+    quant_pack_triton(x[N,G,gs], bits, group_size, avg_alam, alam_bits, clamp, clamp_alpha)
+        -> (packed int32 [N*G, gs*bits/32], scale [N,G], min [N,G])
+    dequant_unpack_triton(packed, scale[N,G], xmin[N,G], bits, group_size, avg_alam, alam_bits)
+        -> bf16 [N,G,gs]
+    pack_triton(x int8 [N,G,gs], bits, group_size) -> int32 [N*G, gs*bits/32]
+    unpack_triton(packed, bits, N, G, group_size)  -> int8 [N,G,gs]
+
+Differences from the reference, on purpose:
+  * scale and min are fp32 (the reference stores bf16); `set_mode("ref_compat")`
+    switches to the live Triton arithmetic (clamp, tanh squash, round to nearest,
+    bf16-rounded scale/min) for recipes that depend on it.
+  * the default mode rounds stochastically with the in-kernel counter hash;
+    `noise=` supplies the uniform tensor instead, `seed=` pins the stream.
+  * the fake (meta) kernels have the real signatures, so FakeTensor tracing and
+    torch.compile see correct shapes and dtypes.
+The names keep their `_triton` suffix only because callers look them up by name.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib, codec
+from .codec import _bits_consts
+
+_MODE = "baseline"          # "baseline" | "nearest" | "ref_compat"
+
+
+def set_mode(mode: str) -> None:
+    """baseline: stochastic rounding, exact division (default).
+    nearest: same arithmetic with the constant 0.5-1e-6 instead of noise.
+    ref_compat: the reference's live arithmetic (clamp/tanh/truncate/bf16 meta)."""
+    global _MODE
+    if mode not in ("baseline", "nearest", "ref_compat"):
+        raise ValueError(f"unknown codec mode {mode!r}")
+    _MODE = mode
+
+
+def get_mode() -> str:
+    return _MODE
+
+
+def _no_alam(avg_alam: bool) -> None:
+    if avg_alam:
+        raise NotImplementedError("AVG_ALAM sub-group averaging is not built in this backend")
+
+
+@torch.library.custom_op("act_lib::quant_pack_triton", mutates_args=(), device_types="cuda")
+def quant_pack_triton(x: torch.Tensor, bits: int, group_size: int, avg_alam: bool, alam_bits: int,
+                      clamp: bool, clamp_alpha: float, noise: Optional[torch.Tensor] = None,
+                      seed: Optional[int] = None) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    _no_alam(avg_alam)
+    N, G, gs = x.shape
+    if gs != group_size:
+        raise ValueError(f"last dimension {gs} != group_size {group_size}")
+    flags, alpha = 0, 0.0
+    if _MODE == "nearest":
+        flags = _lib.ACT_FLAG_ROUND_NEAREST
+    elif _MODE == "ref_compat":
+        flags = _lib.ACT_FLAG_REF_COMPAT | _lib.ACT_FLAG_REF_TANH | _lib.ACT_FLAG_META_BF16
+        if clamp:
+            flags |= _lib.ACT_FLAG_REF_CLAMP
+            alpha = clamp_alpha
+    packed, scale, mn = codec.quant_pack(x, bits, group_size, noise=noise, seed=seed, flags=flags,
+                                         clamp_alpha=alpha)
+    return packed, scale.view(N, G), mn.view(N, G)
+
+
+@quant_pack_triton.register_fake
+def _(x, bits, group_size, avg_alam, alam_bits, clamp, clamp_alpha, noise=None, seed=None):
+    N, G = x.shape[:2]
+    _, nwords, _ = _bits_consts(bits, group_size)
+    return (x.new_empty((N * G, nwords), dtype=torch.int32),
+            x.new_empty((N, G), dtype=torch.float32), x.new_empty((N, G), dtype=torch.float32))
+
+
+@torch.library.custom_op("act_lib::dequant_unpack_triton", mutates_args=(), device_types="cuda")
+def dequant_unpack_triton(packed: torch.Tensor, scale: torch.Tensor, xmin: torch.Tensor, bits: int,
+                          group_size: int, avg_alam: bool, alam_bits: int) -> torch.Tensor:
+    _no_alam(avg_alam)
+    N, G = scale.shape
+    y = codec.dequant_unpack(packed, scale, xmin, bits, group_size, out_dtype=torch.bfloat16)
+    return y.view(N, G, group_size)
+
+
+@dequant_unpack_triton.register_fake
+def _(packed, scale, xmin, bits, group_size, avg_alam, alam_bits):
+    N, G = scale.shape
+    return packed.new_empty((N, G, group_size), dtype=torch.bfloat16)
+
+
+@torch.library.custom_op("act_lib::pack_triton", mutates_args=(), device_types="cuda")
+def pack_triton(x: torch.Tensor, bits: int, group_size: int) -> torch.Tensor:
+    if x.shape[-1] != group_size:
+        raise ValueError("last dimension must equal group_size")
+    return codec.pack_bits(x, bits, group_size)
+
+
+@pack_triton.register_fake
+def _(x, bits, group_size):
+    N, G, _ = x.shape
+    _, nwords, _ = _bits_consts(bits, group_size)
+    return x.new_empty((N * G, nwords), dtype=torch.int32)
+
+
+@torch.library.custom_op("act_lib::unpack_triton", mutates_args=(), device_types="cuda")
+def unpack_triton(packed: torch.Tensor, bits: int, N: int, G: int, group_size: int) -> torch.Tensor:
+    return codec.unpack_bits(packed, bits, N * G, group_size).view(N, G, group_size)
+
+
+@unpack_triton.register_fake
+def _(packed, bits, N, G, group_size):
+    return packed.new_empty((N, G, group_size), dtype=torch.int8)

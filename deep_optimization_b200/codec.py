@@ -7,7 +7,6 @@ Activation_Compression/act_triton_kernel.py:336-433 with the grouped layout
 """
 from __future__ import annotations
 
-import itertools
 from typing import Optional, Tuple
 
 import torch
@@ -18,7 +17,6 @@ _DTYPES = {torch.float32: _lib.ACT_DTYPE_F32, torch.bfloat16: _lib.ACT_DTYPE_BF1
            torch.float16: _lib.ACT_DTYPE_F16}
 
 # successive hash-noise calls draw disjoint counter ranges of one stream
-_offset_counter = itertools.count()
 _default_seed = 0x5EED
 _next_offset = 0
 
@@ -49,9 +47,12 @@ def _stream_ptr(t: torch.Tensor) -> int:
 
 def quant_pack(x: torch.Tensor, bits: int, group_size: int, noise: Optional[torch.Tensor] = None,
                seed: Optional[int] = None, offset: Optional[int] = None, flags: int = 0,
-               clamp_alpha: float = 0.0) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+               clamp_alpha: float = 0.0,
+               out: Optional[Tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = None
+               ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """x: [..., group_size]-groupable tensor (numel % group_size == 0), fp32/bf16/fp16.
-    Returns (packed int32 [NG, group_size*bits/32], scale fp32 [NG], min fp32 [NG])."""
+    Returns (packed int32 [NG, group_size*bits/32], scale fp32 [NG], min fp32 [NG]);
+    `out` supplies those three buffers instead of allocating them."""
     global _next_offset
     _, nwords, _ = _bits_consts(bits, group_size)
     _require_cuda(x, "x")
@@ -61,9 +62,16 @@ def quant_pack(x: torch.Tensor, bits: int, group_size: int, noise: Optional[torc
     if x.numel() % group_size:
         raise ValueError("numel must be a multiple of group_size")
     ng = x.numel() // group_size
-    packed = torch.empty((ng, nwords), dtype=torch.int32, device=x.device)
-    scale = torch.empty((ng,), dtype=torch.float32, device=x.device)
-    mn = torch.empty((ng,), dtype=torch.float32, device=x.device)
+    if out is not None:
+        packed, scale, mn = out
+        if (packed.dtype != torch.int32 or packed.numel() != ng * nwords or scale.numel() != ng
+                or mn.numel() != ng or scale.dtype != torch.float32 or mn.dtype != torch.float32
+                or not (packed.is_contiguous() and scale.is_contiguous() and mn.is_contiguous())):
+            raise ValueError("out buffers have the wrong size, dtype or layout")
+    else:
+        packed = torch.empty((ng, nwords), dtype=torch.int32, device=x.device)
+        scale = torch.empty((ng,), dtype=torch.float32, device=x.device)
+        mn = torch.empty((ng,), dtype=torch.float32, device=x.device)
     if noise is not None:
         _require_cuda(noise, "noise")
         noise = noise.to(torch.float32).contiguous()
@@ -73,7 +81,7 @@ def quant_pack(x: torch.Tensor, bits: int, group_size: int, noise: Optional[torc
         seed = _default_seed
     if offset is None:
         offset = _next_offset
-        _next_offset += (x.numel() + 3) // 4
+        _next_offset += 1
     with torch.cuda.device(x.device):
         rc = _lib.load().act_quant_pack(
             x.data_ptr(), _DTYPES[x.dtype], ng, group_size, bits,
@@ -85,15 +93,21 @@ def quant_pack(x: torch.Tensor, bits: int, group_size: int, noise: Optional[torc
 
 
 def dequant_unpack(packed: torch.Tensor, scale: torch.Tensor, mn: torch.Tensor, bits: int,
-                   group_size: int, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
-    """Inverse of quant_pack; returns [NG, group_size] of out_dtype."""
+                   group_size: int, out_dtype: torch.dtype = torch.bfloat16,
+                   out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Inverse of quant_pack; returns [NG, group_size] of out_dtype (written into `out` if given)."""
     _bits_consts(bits, group_size)
     _require_cuda(packed, "packed")
     packed = packed.contiguous()
     scale = scale.to(torch.float32).contiguous()
     mn = mn.to(torch.float32).contiguous()
     ng = scale.numel()
-    y = torch.empty((ng, group_size), dtype=out_dtype, device=packed.device)
+    if out is not None:
+        if out.dtype != out_dtype or out.numel() != ng * group_size or not out.is_contiguous():
+            raise ValueError("out buffer has the wrong size, dtype or layout")
+        y = out
+    else:
+        y = torch.empty((ng, group_size), dtype=out_dtype, device=packed.device)
     with torch.cuda.device(packed.device):
         rc = _lib.load().act_dequant_unpack(packed.data_ptr(), scale.data_ptr(), mn.data_ptr(), ng,
                                             group_size, bits, _DTYPES[out_dtype], y.data_ptr(),

@@ -1,0 +1,223 @@
+"""ACT controller: traces a model, decides bits / group size / padding per layer and
+swaps the supported modules for their compressed-activation versions.
+
+Public surface of Activation_Compression/controller.py:18-390: `Controller(model,
+config, train_loader, criterion, test)`, `.iterate()`, `.warp_model(graph_mode,
+quantizer)`, `.traced_model`, `.meta`, `.target_dict`, and the helpers
+`find_group_size`, `assign_tensor_meta`, `compute_activation_size_in_bytes`.
+Config keys are the reference's: default_bits, auto_precision, DIVISION,
+AVG_ALAM, AVG_ALAM_BTS, group_size, batch_size, fp8, analyze, depth_point_conv,
+rms_norm.  Differences: shapes are propagated on the meta device (no GPU needed
+to build the plan); the low-frequency-energy probe that picks DIVISION layers is
+a research analysis outside this path, so DIVISION applies to no layer unless
+`division_targets` lists them; `min_activation_mib` (default 10, the reference's
+constant) sets the size below which a layer is left alone.
+"""
+from __future__ import annotations
+
+import copy
+
+import torch
+import torch.fx as FX
+from torch import nn
+from torch.fx.passes.shape_prop import ShapeProp
+
+from .layers import DOConv1d, DOConv2d, DOConv3d, DODepthPointConv2d, DOLinear, RMSNorm
+from .modules.activations.act_layers import DOGELU, DOReLU_Variance, DOSiLU
+from .modules.normalization.normalization_layers import DOBatchNorm2d, DOSyncBatchNorm2d
+from .quantizer import Quantizer
+
+_SUPPORTED = (nn.Linear, nn.Conv1d, nn.Conv2d, nn.Conv3d, nn.BatchNorm2d, nn.SyncBatchNorm,
+              nn.ReLU, nn.ReLU6, nn.SiLU, nn.GELU)
+
+
+def assign_tensor_meta(node):
+    """tensor_meta of the first tensor argument of a node (controller.py:355-361)."""
+    for arg in node.args:
+        if isinstance(arg, torch.fx.Node) and arg.op != "get_attr":
+            tm = arg.meta.get("tensor_meta", None)
+            if tm is not None:
+                return tm
+    return None
+
+
+def find_group_size(S, bits, max_group=512, special=False):
+    """Largest of 512/256/128/64 (1024 too when `special`) dividing S; else 256 with
+    zero padding (controller.py:364-378)."""
+    groups = [1024, 512, 256, 128, 64] if special else [512, 256, 128, 64]
+    if bits in (1, 2, 4, 8):
+        for gs in groups:
+            if S % gs == 0:
+                return gs, False
+    return 256, True
+
+
+def compute_activation_size_in_bytes(node):
+    """Size in MiB of the node's output (controller.py:381-390; the name says bytes)."""
+    tm = node.meta.get("tensor_meta", None)
+    if tm is None:
+        return 0
+    numel = 1
+    for s in tm.shape:
+        numel *= s
+    return numel * torch.tensor([], dtype=tm.dtype).element_size() / (1024 ** 2)
+
+
+class Controller:
+    def __init__(self, model, config, train_loader=None, criterion=None, test=True, input_shape=None,
+                 device=None):
+        self.device = device if device is not None else ("cuda" if torch.cuda.is_available() else "cpu")
+        self.model = model.to(self.device)
+        self.config = config
+        self.train_loader = train_loader
+        self.criterion = criterion
+        if input_shape is None:
+            x, _ = next(iter(self.train_loader))
+            input_shape = x.shape[1:]
+        self.input_shape = tuple(input_shape)
+        self.quantizer = Quantizer(config, {})
+        self.quantizer.filter_tensors(self.model.named_parameters())
+        self.meta = {"group_size": config.get("group_size", 256), "fp8": config.get("fp8", False),
+                     "analyze": config.get("analyze", False)}
+        self.layer_clamp = 3.0
+        self.traced_model = None
+        self.target_dict = {}
+        if not test:
+            self.warp_model(quantizer=True)
+
+    def iterate(self, criterion=None, trainloader=None):
+        self.quantizer.iterate(self.model, criterion or self.criterion, trainloader or self.train_loader)
+
+    # ------------------------------------------------------------------ planning
+    def _plan(self, traced):
+        named = dict(traced.named_modules())
+        # shapes are propagated through a bf16 copy on the meta device (what autocast
+        # training sees), leaving the real parameters where they are
+        meta_model = copy.deepcopy(traced).to(device="meta", dtype=torch.bfloat16)
+        fake = torch.empty(self.config["batch_size"], *self.input_shape, dtype=torch.bfloat16, device="meta")
+        ShapeProp(meta_model).propagate(fake)
+        threshold = self.config.get("min_activation_mib", 10)
+        pairs = {}
+        for node in meta_model.graph.nodes:
+            if node.op != "call_module":
+                continue
+            mod = named[node.target]
+            if not isinstance(mod, _SUPPORTED):
+                continue
+            if compute_activation_size_in_bytes(node) <= threshold:
+                continue
+            tm = assign_tensor_meta(node)
+            if tm is None:
+                continue
+            pairs[node.target] = {"mod": mod, "tensor_meta": tm}
+        return pairs
+
+    def _layer_meta(self, target, mod, tm):
+        bits = self.quantizer.bits[target]
+        entry = {"tensor_meta": tm, "pack_only": False, "bits": bits}
+        if isinstance(mod, (nn.ReLU, nn.ReLU6)):
+            entry["pack_only"], entry["bits"] = True, 1
+        shape = tuple(tm.shape)
+        is_bn = isinstance(mod, (nn.BatchNorm2d, nn.SyncBatchNorm))
+        if len(shape) >= 3 and is_bn:
+            per = shape[0]
+            for d in shape[2:]:
+                per *= d
+            N = shape[1]
+        else:
+            per = 1
+            for d in shape[1:]:
+                per *= d
+            N = shape[0]
+        group_size, act_padding = find_group_size(per, bits, special=is_bn)
+        if is_bn:
+            # this backend groups the normalised tensor sample-major like every other
+            # layer, so the group size must divide a sample, not a channel
+            per_sample = 1
+            for d in shape[1:]:
+                per_sample *= d
+            group_size, act_padding = find_group_size(per_sample, bits, special=True)
+            N = shape[0]
+            per = per_sample
+        G = (per + group_size - 1) // group_size
+        entry.update({"group_size": group_size, "act_padding": act_padding, "N": N, "NG": N * G})
+        if self.config.get("AVG_ALAM", None) is not None and not isinstance(
+                mod, (nn.Linear, nn.Conv1d, nn.Conv2d, nn.Conv3d)):
+            entry.update({"AVG_ALAM": self.config["AVG_ALAM"], "ALAM_BITS": self.config["AVG_ALAM_BTS"]})
+        else:
+            entry.update({"AVG_ALAM": False, "ALAM_BITS": 0})
+        division = self.config.get("DIVISION", None)
+        entry["DIVISION"] = division if (division is not None and target in self.config.get("division_targets", ())) else None
+        return entry
+
+    def _replacement(self, target, mod):
+        kw = dict(target_name=target, meta=self.meta)
+        if isinstance(mod, nn.Linear):
+            new = DOLinear(mod.in_features, mod.out_features, clamp_alpha=self.layer_clamp, **kw)
+            if mod.bias is None:
+                new.bias = None
+        elif isinstance(mod, nn.Conv1d):
+            new = DOConv1d(mod.in_channels, mod.out_channels, mod.kernel_size, mod.stride, mod.padding,
+                           mod.dilation, mod.groups, mod.padding_mode, clamp_alpha=self.layer_clamp, **kw)
+        elif isinstance(mod, nn.Conv2d):
+            if self.config.get("depth_point_conv", False):
+                return DODepthPointConv2d(mod.in_channels, mod.out_channels, mod.kernel_size, mod.stride,
+                                          mod.padding, mod.dilation, mod.groups, mod.padding_mode,
+                                          acc_var=self.layer_clamp, **kw)
+            new = DOConv2d(mod.in_channels, mod.out_channels, mod.kernel_size, mod.stride, mod.padding,
+                           mod.dilation, mod.groups, mod.padding_mode, clamp_alpha=self.layer_clamp, **kw)
+        elif isinstance(mod, nn.Conv3d):
+            new = DOConv3d(mod.in_channels, mod.out_channels, mod.kernel_size, mod.stride, mod.padding,
+                           mod.dilation, mod.groups, mod.padding_mode, clamp_alpha=self.layer_clamp, **kw)
+        elif isinstance(mod, nn.SyncBatchNorm):
+            new = DOSyncBatchNorm2d(mod.num_features, mod.eps, mod.momentum, mod.affine,
+                                    mod.track_running_stats, mod.process_group, **kw)
+        elif isinstance(mod, nn.BatchNorm2d):
+            new = DOBatchNorm2d(mod.num_features, mod.eps, mod.momentum, mod.affine,
+                                mod.track_running_stats, **kw)
+        elif isinstance(mod, nn.ReLU6):
+            return DOReLU_Variance(inplace=False, relu=False, relu6=True, **kw)
+        elif isinstance(mod, nn.ReLU):
+            return DOReLU_Variance(inplace=False, relu=True, relu6=False, **kw)
+        elif isinstance(mod, nn.SiLU):
+            return DOSiLU(inplace=False, **kw)
+        elif isinstance(mod, nn.GELU):
+            return DOGELU(inplace=False, **kw)
+        else:
+            raise TypeError(type(mod))
+        with torch.no_grad():
+            for name in ("weight", "bias", "running_mean", "running_var", "num_batches_tracked"):
+                src, dst = getattr(mod, name, None), getattr(new, name, None)
+                if src is not None and dst is not None:
+                    dst.copy_(src)
+        return new
+
+    # ------------------------------------------------------------------ rewrite
+    def warp_model(self, graph_mode=False, quantizer=False):
+        traced = FX.symbolic_trace(self.model)
+        pairs = self._plan(traced)
+        self.target_dict = pairs
+        if quantizer:
+            self.quantizer.bits = {t: self.config["default_bits"] for t in pairs}
+            self.iterate()
+            self.meta["batch_size"] = self.config["batch_size"]
+            for target, d in pairs.items():
+                self.meta[f"{target}"] = self._layer_meta(target, d["mod"], d["tensor_meta"])
+            for target, d in pairs.items():
+                new_mod = self._replacement(target, d["mod"])
+                parent_path, _, child = target.rpartition(".")
+                setattr(traced.get_submodule(parent_path), child, new_mod)
+            if self.config.get("rms_norm", False):
+                for name, mod in list(traced.named_modules()):
+                    if isinstance(mod, nn.LayerNorm):
+                        parent_path, _, child = name.rpartition(".")
+                        setattr(traced.get_submodule(parent_path), child, RMSNorm(mod.normalized_shape[-1]))
+            traced.graph.eliminate_dead_code()
+            traced.graph.lint()
+            traced.recompile()
+        if graph_mode:
+            torch.backends.cuda.matmul.allow_tf32 = True
+            torch.backends.cudnn.allow_tf32 = True
+            torch.set_float32_matmul_precision("high")
+        self.traced_model = traced.to(self.device).train()
+        return self.traced_model

@@ -48,7 +48,7 @@ __device__ __forceinline__ float fmax_nan(float a, float b) {
     float d; asm("max.NaN.f32 %0, %1, %2;" : "=f"(d) : "f"(a), "f"(b)); return d;
 }
 
-// Host side: splitmix64 finaliser that turns the caller's seed into the hash key.
+// Host side: splitmix64 finaliser; the hash key is hash_key(hash_key(seed) + offset).
 __host__ __device__ inline uint64_t hash_key(uint64_t seed) {
     uint64_t z = seed + 0x9E3779B97F4A7C15ull;
     z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
@@ -64,10 +64,23 @@ __device__ __forceinline__ void hash_2x32(uint64_t ctr, uint32_t key_lo, uint32_
     uint32_t k = key_lo;
 #pragma unroll
     for (int r = 0; r < kHashRounds; ++r) {
-        const uint32_t hi = __umulhi(kHashMul, L);
-        const uint32_t lo = kHashMul * L;
-        L = hi ^ k ^ R;
-        R = lo;
+        const uint64_t p = (uint64_t)kHashMul * (uint64_t)L;      // one wide multiply
+        L = (uint32_t)(p >> 32) ^ k ^ R;
+        R = (uint32_t)p;
+        k += kHashWeyl;
+    }
+    o0 = L; o1 = R;
+}
+
+// the same network with the counter already split and key_hi folded into ctr_hi
+__device__ __forceinline__ void hash_2x32_split(uint32_t ctr_lo, uint32_t ctr_hi_x_key, uint32_t key_lo,
+                                                uint32_t& o0, uint32_t& o1) {
+    uint32_t L = ctr_lo, R = ctr_hi_x_key, k = key_lo;
+#pragma unroll
+    for (int r = 0; r < kHashRounds; ++r) {
+        const uint64_t p = (uint64_t)kHashMul * (uint64_t)L;
+        L = (uint32_t)(p >> 32) ^ k ^ R;
+        R = (uint32_t)p;
         k += kHashWeyl;
     }
     o0 = L; o1 = R;
@@ -79,6 +92,42 @@ __device__ __forceinline__ float u16_lo_as_float(uint32_t w) {
 }
 __device__ __forceinline__ float u16_hi_as_float(uint32_t w) {
     return __uint_as_float(__byte_perm(w, kMagicBits, 0x7432)) - kMagic;
+}
+
+// ---- packed fp32 pairs (sm_100 f32x2 instructions: one issue slot, two lanes) ----
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pack2(float a, float b) {
+    f32x2 r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b)); return r;
+}
+__device__ __forceinline__ f32x2 pack2u(uint32_t a, uint32_t b) {
+    f32x2 r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(a), "r"(b)); return r;
+}
+__device__ __forceinline__ void unpack2u(f32x2 v, uint32_t& a, uint32_t& b) {
+    asm("mov.b64 {%0, %1}, %2;" : "=r"(a), "=r"(b) : "l"(v));
+}
+__device__ __forceinline__ f32x2 add2_rn(f32x2 a, f32x2 b) {
+    f32x2 d; asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d;
+}
+__device__ __forceinline__ f32x2 add2_rm(f32x2 a, f32x2 b) {
+    f32x2 d; asm("add.rm.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d;
+}
+__device__ __forceinline__ f32x2 sub2_rn(f32x2 a, f32x2 b) {
+    f32x2 d; asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d;
+}
+__device__ __forceinline__ f32x2 mul2_rn(f32x2 a, f32x2 b) {
+    f32x2 d; asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d;
+}
+__device__ __forceinline__ f32x2 fma2_rn(f32x2 a, f32x2 b, f32x2 c) {
+    f32x2 d; asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c)); return d;
+}
+// the same division sequence as div_by_scale on two lanes; ns = (-s,-s), y = (1/s,1/s)
+__device__ __forceinline__ f32x2 div_by_scale2(f32x2 a, f32x2 ns, f32x2 y) {
+    f32x2 q = mul2_rn(a, y);
+    f32x2 r = fma2_rn(ns, q, a);
+    q = fma2_rn(r, y, q);
+    r = fma2_rn(ns, q, a);
+    q = fma2_rn(r, y, q);
+    return q;
 }
 
 // a / s, correctly rounded, from y = RN(1/s): two Newton corrections on the

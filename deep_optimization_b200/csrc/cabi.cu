@@ -30,10 +30,6 @@ int stream_grid_for(int64_t n_blocks_wanted, int blocks_per_sm) {
     return (int)g;
 }
 
-int pack_grid_for(int64_t n_tiles) {
-    return stream_grid_for((n_tiles + 7) / 8, 4);
-}
-
 }  // namespace act
 
 extern "C" const char* act_strerror(int code) {

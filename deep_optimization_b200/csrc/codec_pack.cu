@@ -10,6 +10,12 @@
 // packed bytes of a tile are staged through shared memory so that they leave
 // as 16-byte coalesced stores.
 //
+// The kernel is bound by instruction issue before it is bound by HBM (about a
+// dozen instructions per 2-byte element), so the per-element arithmetic runs on
+// f32x2 pairs, the next tile is loaded while the current one is encoded, and a
+// tile takes one warp-uniform branch between a branch-free fast path and the
+// verbatim IEEE slow path.
+//
 // HBM traffic per element: s_in bytes read, bits/8 written, 8/GS for scale+min.
 //
 // Replaces: Activation_Compression/act_triton_kernel.py:23-171 (quant_pack_kernel),
@@ -37,16 +43,220 @@ template <int BITS, int N> __host__ __device__ constexpr uint32_t magic_sum() {
     return s;
 }
 
+// acc + (v << sh) written as an integer multiply-add, which the FMA pipe can take
+__device__ __forceinline__ uint32_t shl_add(uint32_t v, int sh, uint32_t acc) {
+    uint32_t d;
+    asm("mad.lo.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(v), "r"(1u << sh), "r"(acc));
+    return d;
+}
+
+// the raw 16-byte vectors of one lane's four pieces
+template <int DT> struct RawTile { uint4 v[ElemT<DT>::bytes == 4 ? 8 : 4]; };
+
+template <int DT>
+__device__ __forceinline__ void load_raw(RawTile<DT>& r, const uint8_t* xb, int64_t group_e0,
+                                         int log2_L, int j) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int64_t e = group_e0 + (int64_t)((k << log2_L) + j) * 8;
+        if (ElemT<DT>::bytes == 4) {
+            r.v[2 * k] = ldg_nc_v4(xb + e * 4);
+            r.v[2 * k + 1] = ldg_nc_v4(xb + e * 4 + 16);
+        } else {
+            r.v[k] = ldg_nc_v4(xb + e * 2);
+        }
+    }
+}
+
+// min and max of the 32 packed 16-bit elements of a lane, NaN-propagating, -0 < +0
+template <int DT>
+__device__ __forceinline__ void minmax16(const RawTile<DT>& r, float& mn, float& mx) {
+    if (DT == ACT_DTYPE_BF16) {
+        __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&r.v[0].x), hi = lo;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const uint32_t w[4] = {r.v[k].x, r.v[k].y, r.v[k].z, r.v[k].w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const __nv_bfloat162 t = *reinterpret_cast<const __nv_bfloat162*>(&w[i]);
+                lo = __hmin2_nan(lo, t); hi = __hmax2_nan(hi, t);
+            }
+        }
+        mn = fmin_nan(__low2float(lo), __high2float(lo));
+        mx = fmax_nan(__low2float(hi), __high2float(hi));
+    } else {
+        __half2 lo = *reinterpret_cast<const __half2*>(&r.v[0].x), hi = lo;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const uint32_t w[4] = {r.v[k].x, r.v[k].y, r.v[k].z, r.v[k].w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const __half2 t = *reinterpret_cast<const __half2*>(&w[i]);
+                lo = __hmin2_nan(lo, t); hi = __hmax2_nan(hi, t);
+            }
+        }
+        mn = fmin_nan(__low2float(lo), __high2float(lo));
+        mx = fmax_nan(__low2float(hi), __high2float(hi));
+    }
+}
+
+template <int DT>
+__device__ __forceinline__ void zero_raw(RawTile<DT>& r) {
+#pragma unroll
+    for (int k = 0; k < (ElemT<DT>::bytes == 4 ? 8 : 4); ++k) r.v[k] = make_uint4(0u, 0u, 0u, 0u);
+}
+
+template <int DT>
+__device__ __forceinline__ void widen_raw(const RawTile<DT>& r, float (&xf)[32]) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        if (ElemT<DT>::bytes == 4) {
+            const uint4 a = r.v[2 * k], b = r.v[2 * k + 1];
+            xf[k * 8 + 0] = __uint_as_float(a.x); xf[k * 8 + 1] = __uint_as_float(a.y);
+            xf[k * 8 + 2] = __uint_as_float(a.z); xf[k * 8 + 3] = __uint_as_float(a.w);
+            xf[k * 8 + 4] = __uint_as_float(b.x); xf[k * 8 + 5] = __uint_as_float(b.y);
+            xf[k * 8 + 6] = __uint_as_float(b.z); xf[k * 8 + 7] = __uint_as_float(b.w);
+        } else {
+            constexpr int D16 = (DT == ACT_DTYPE_F32) ? ACT_DTYPE_BF16 : DT;
+            const uint4 a = r.v[k];
+            xf[k * 8 + 0] = widen_lo<D16>(a.x); xf[k * 8 + 1] = widen_hi<D16>(a.x);
+            xf[k * 8 + 2] = widen_lo<D16>(a.y); xf[k * 8 + 3] = widen_hi<D16>(a.y);
+            xf[k * 8 + 4] = widen_lo<D16>(a.z); xf[k * 8 + 5] = widen_hi<D16>(a.z);
+            xf[k * 8 + 6] = widen_lo<D16>(a.w); xf[k * 8 + 7] = widen_hi<D16>(a.w);
+        }
+    }
+}
+
+// eight consecutive fp32 noise values of one piece (zeros for a lane past the end)
+__device__ __forceinline__ void load_noise8(float (&u8)[8], const float* noise, int64_t e, bool valid) {
+    if (valid) {
+        const uint4 a = ldg_nc_v4(noise + e), b = ldg_nc_v4(noise + e + 4);
+        u8[0] = __uint_as_float(a.x); u8[1] = __uint_as_float(a.y);
+        u8[2] = __uint_as_float(a.z); u8[3] = __uint_as_float(a.w);
+        u8[4] = __uint_as_float(b.x); u8[5] = __uint_as_float(b.y);
+        u8[6] = __uint_as_float(b.z); u8[7] = __uint_as_float(b.w);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) u8[i] = 0.0f;
+    }
+}
+
+// ---- fast path: one piece (8 elements) -> BITS bytes -------------------------
+// Preconditions (checked per tile, warp-uniformly): the group's range is 0 or in
+// [2^-50, 2^50], so the FMA division is exact, t >= 0 and floor(t) <= QMAX
+// (8-bit hash noise needs one fminf for the upper bound).  floor is a round-down
+// add of 2^23; the code is then the low mantissa bits and the codes of a piece
+// are summed with shifts, the 2^23 patterns being subtracted once at the end.
+template <int BITS, int NM>
+__device__ __forceinline__ void encode_piece_fast(const float* xf8, const float* u8, f32x2 nmn2, f32x2 ns2,
+                                                  f32x2 y2, uint32_t ctr_lo, uint32_t ctr_hi, uint32_t key_lo,
+                                                  uint32_t& acc0, uint32_t& acc1)
+{
+    constexpr int QMAX = (1 << BITS) - 1;
+    const f32x2 magic2 = pack2(kMagic, kMagic);
+    uint32_t hw[4];
+    if (NM == kNoiseHash) {
+        // two 64-bit hash outputs = eight 16-bit noise fields; the counter's low
+        // bits are free of carries because a group starts on a multiple of 8 counters
+        hash_2x32_split(ctr_lo, ctr_hi, key_lo, hw[0], hw[1]);
+        hash_2x32_split(ctr_lo + 1u, ctr_hi, key_lo, hw[2], hw[3]);
+    }
+    uint32_t a0 = 0, a1 = 0;
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+        const f32x2 a2 = add2_rn(pack2(xf8[2 * p], xf8[2 * p + 1]), nmn2);
+        const f32x2 q2 = div_by_scale2(a2, ns2, y2);
+        f32x2 t2;
+        if (NM == kNoiseHash) {
+            const f32x2 uf2 = sub2_rn(pack2u(__byte_perm(hw[p], kMagicBits, 0x7410),
+                                             __byte_perm(hw[p], kMagicBits, 0x7432)), magic2);
+            t2 = fma2_rn(uf2, pack2(0x1p-16f, 0x1p-16f), q2);        // exact u, one rounding
+        } else if (NM == kNoiseTensor) {
+            // caller-supplied noise may lie outside [0,1) or be NaN: clamp t to [0,QMAX]
+            // first (NaN -> 0), after which the round-down add is floor again
+            uint32_t l, h; unpack2u(add2_rn(q2, pack2(u8[2 * p], u8[2 * p + 1])), l, h);
+            t2 = pack2(fminf(fmaxf(__uint_as_float(l), 0.0f), (float)QMAX),
+                       fminf(fmaxf(__uint_as_float(h), 0.0f), (float)QMAX));
+        } else {
+            t2 = add2_rn(q2, pack2(0.5f - 1e-6f, 0.5f - 1e-6f));
+        }
+        if (NM == kNoiseHash && BITS == 8) {
+            uint32_t l, h; unpack2u(t2, l, h);
+            t2 = pack2(fminf(__uint_as_float(l), (float)QMAX), fminf(__uint_as_float(h), (float)QMAX));
+        }
+        uint32_t tb0, tb1;
+        unpack2u(add2_rm(t2, magic2), tb0, tb1);
+        if (BITS == 8 && p >= 2) {
+            a1 = (p == 2) ? shl_add(tb1, 8, tb0) : shl_add(tb1, 24, shl_add(tb0, 16, a1));
+        } else {
+            a0 = (p == 0) ? shl_add(tb1, BITS, tb0)
+                          : shl_add(tb1, (2 * p + 1) * BITS, shl_add(tb0, 2 * p * BITS, a0));
+        }
+    }
+    if (BITS == 8) { acc0 = a0 - magic_sum<8, 4>(); acc1 = a1 - magic_sum<8, 4>(); }
+    else { acc0 = a0 - magic_sum<BITS, 8>(); acc1 = 0; }
+}
+
+// ---- slow path: the contract's arithmetic verbatim, any input ------------------
+template <int BITS, int NM>
+__device__ __forceinline__ void encode_piece_slow(const float* xf8, const float* u8, float mn, float s,
+                                                  uint32_t ctr_lo, uint32_t ctr_hi, uint32_t key_lo,
+                                                  uint32_t& acc0, uint32_t& acc1)
+{
+    constexpr int QMAX = (1 << BITS) - 1;
+    uint32_t hw[4] = {0u, 0u, 0u, 0u};
+    if (NM == kNoiseHash) {
+        hash_2x32_split(ctr_lo, ctr_hi, key_lo, hw[0], hw[1]);
+        hash_2x32_split(ctr_lo + 1u, ctr_hi, key_lo, hw[2], hw[3]);
+    }
+    acc0 = 0; acc1 = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const float a = __fsub_rn(xf8[i], mn);
+        const float q = __fdiv_rn(a, s);
+        float uu;
+        if (NM == kNoiseHash)
+            uu = __fmul_rn((i & 1) ? u16_hi_as_float(hw[i >> 1]) : u16_lo_as_float(hw[i >> 1]), 0x1p-16f);
+        else if (NM == kNoiseTensor) uu = u8[i];
+        else uu = 0.5f - 1e-6f;
+        const uint32_t c = code_from_t(__fadd_rn(q, uu), QMAX);
+        if (BITS == 8 && i >= 4) acc1 |= c << ((i - 4) * 8);
+        else acc0 |= c << (i * BITS);
+    }
+}
+
+// ---- reference-compatible path (act_triton_kernel.py:71,114,151-153): multiply by
+// the reciprocal, add 0.5-1e-6 (rounded separately), truncate, integer clamp ------
+template <int BITS>
+__device__ __forceinline__ void encode_piece_ref(const float* xf8, float mn, float y,
+                                                 uint32_t& acc0, uint32_t& acc1)
+{
+    constexpr int QMAX = (1 << BITS) - 1;
+    acc0 = 0; acc1 = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const float a = __fsub_rn(xf8[i], mn);
+        float t = __fadd_rn(__fmul_rn(a, y), 0.5f - 1e-6f);
+        int c = 0;
+        if (t == t) {
+            t = fminf(fmaxf(t, -1.0e9f), 1.0e9f);
+            c = min(max((int)t, 0), QMAX);
+        }
+        if (BITS == 8 && i >= 4) acc1 |= (uint32_t)c << ((i - 4) * 8);
+        else acc0 |= (uint32_t)c << (i * BITS);
+    }
+}
+
 template <int DT, int BITS, int NM>
-__global__ void __launch_bounds__(kPackThreads)
+__global__ void __launch_bounds__(kPackThreads, 3)
 quant_pack_kernel(const void* __restrict__ x_, const float* __restrict__ noise,
                   uint8_t* __restrict__ packed, float* __restrict__ scale_out,
                   float* __restrict__ min_out, int64_t n_elems, int log2_L,
-                  uint32_t key_lo, uint32_t key_hi, uint64_t offset, int flags, float clamp_alpha)
+                  uint32_t key_lo, uint32_t key_hi, int flags, float clamp_alpha)
 {
     constexpr int QMAX = (1 << BITS) - 1;
-    constexpr int EB = ElemT<DT>::bytes;
     constexpr int TILE_OUT = kTileElems * BITS / 8;          // packed bytes per tile
+    constexpr bool PREFETCH = ElemT<DT>::bytes == 2;          // 16 spare registers for 16-bit inputs
     __shared__ __align__(16) uint8_t stage[kPackWarps][TILE_OUT];
 
     const int lane = threadIdx.x & 31;
@@ -54,41 +264,35 @@ quant_pack_kernel(const void* __restrict__ x_, const float* __restrict__ noise,
     const int L = 1 << log2_L;                  // lanes per group
     const int j = lane & (L - 1);               // lane index inside the group
     const int g_local = lane >> log2_L;         // group index inside the tile
+    const int lane_e0 = g_local << (log2_L + 5);   // first element of the lane's group inside the tile
     const int64_t n_tiles = (n_elems + kTileElems - 1) / kTileElems;
     const int64_t warp_stride = (int64_t)gridDim.x * kPackWarps;
     const uint8_t* xb = static_cast<const uint8_t*>(x_);
     uint8_t* my_stage = stage[warp];
 
-    for (int64_t tile = (int64_t)blockIdx.x * kPackWarps + warp; tile < n_tiles; tile += warp_stride) {
+    int64_t tile = (int64_t)blockIdx.x * kPackWarps + warp;
+    RawTile<DT> raw;
+    if (tile < n_tiles) {
+        const int64_t e0 = tile * kTileElems + lane_e0;
+        if (e0 < n_elems) load_raw<DT>(raw, xb, e0, log2_L, j); else zero_raw<DT>(raw);
+    }
+
+    for (; tile < n_tiles; tile += warp_stride) {
         // element index of the lane's group and validity (groups never straddle n_elems)
-        const int64_t group_e0 = tile * kTileElems + ((int64_t)g_local << (log2_L + 5));
+        const int64_t group_e0 = tile * kTileElems + lane_e0;
         const bool valid = group_e0 < n_elems;
 
-        // ---- load 4 pieces of 8 elements, widened to fp32 ------------------
         float xf[32];
-        if (valid) {
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                const int64_t e = group_e0 + (int64_t)((k << log2_L) + j) * 8;
-                if (EB == 4) {
-                    const uint4 a = ldg_nc_v4(xb + e * 4);
-                    const uint4 b = ldg_nc_v4(xb + e * 4 + 16);
-                    xf[k * 8 + 0] = __uint_as_float(a.x); xf[k * 8 + 1] = __uint_as_float(a.y);
-                    xf[k * 8 + 2] = __uint_as_float(a.z); xf[k * 8 + 3] = __uint_as_float(a.w);
-                    xf[k * 8 + 4] = __uint_as_float(b.x); xf[k * 8 + 5] = __uint_as_float(b.y);
-                    xf[k * 8 + 6] = __uint_as_float(b.z); xf[k * 8 + 7] = __uint_as_float(b.w);
-                } else {
-                    const uint4 a = ldg_nc_v4(xb + e * 2);
-                    constexpr int D16 = (DT == ACT_DTYPE_F32) ? ACT_DTYPE_BF16 : DT;
-                    xf[k * 8 + 0] = widen_lo<D16>(a.x); xf[k * 8 + 1] = widen_hi<D16>(a.x);
-                    xf[k * 8 + 2] = widen_lo<D16>(a.y); xf[k * 8 + 3] = widen_hi<D16>(a.y);
-                    xf[k * 8 + 4] = widen_lo<D16>(a.z); xf[k * 8 + 5] = widen_hi<D16>(a.z);
-                    xf[k * 8 + 6] = widen_lo<D16>(a.w); xf[k * 8 + 7] = widen_hi<D16>(a.w);
-                }
+        widen_raw<DT>(raw, xf);
+        const RawTile<DT> raw_cur = raw;
+
+        // next tile's loads go out before this tile's arithmetic
+        const int64_t next_tile = tile + warp_stride;
+        if (PREFETCH) {
+            if (next_tile < n_tiles) {
+                const int64_t e0 = next_tile * kTileElems + lane_e0;
+                if (e0 < n_elems) load_raw<DT>(raw, xb, e0, log2_L, j); else zero_raw<DT>(raw);
             }
-        } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) xf[i] = 0.0f;
         }
 
         if (NM == kRefCompat) {
@@ -103,24 +307,31 @@ quant_pack_kernel(const void* __restrict__ x_, const float* __restrict__ noise,
             }
         }
 
-        // ---- group min / max ------------------------------------------------
-        float mn = xf[0], mx = xf[0];
+        // ---- group min / max (NaN propagates, -0 < +0) -------------------------
+        float mn, mx;
+        if (ElemT<DT>::bytes == 2 && NM != kRefCompat) {
+            // 16-bit inputs: min/max are exact in the input format, two elements per op
+            minmax16<DT>(raw_cur, mn, mx);
+        } else {
+            mn = xf[0]; mx = xf[0];
 #pragma unroll
-        for (int i = 1; i < 32; ++i) { mn = fmin_nan(mn, xf[i]); mx = fmax_nan(mx, xf[i]); }
+            for (int i = 1; i < 32; ++i) { mn = fmin_nan(mn, xf[i]); mx = fmax_nan(mx, xf[i]); }
+        }
         for (int off = L >> 1; off > 0; off >>= 1) {
             mn = fmin_nan(mn, __shfl_xor_sync(0xffffffffu, mn, off));
             mx = fmax_nan(mx, __shfl_xor_sync(0xffffffffu, mx, off));
         }
 
-        // ---- scale ------------------------------------------------------------
+        // ---- scale ----------------------------------------------------------------
         const float range = __fsub_rn(mx, mn);
         float s = (BITS == 1) ? range : __fdiv_rn(range, (float)QMAX);
         if (!(s > 0.0f)) s = 1.0f;
+        const float y = __frcp_rn(s);
         // the FMA division and the clamp-free packing need a finite range well inside
         // the normal numbers (then 2^-58 <= s <= 2^50); a denormal, huge, infinite or
-        // NaN range goes the slow way, which is the contract's arithmetic verbatim
+        // NaN range sends the whole tile the slow way
         const bool fast = (range == 0.0f) || (range >= 0x1p-50f && range <= 0x1p50f);
-        const float y = __frcp_rn(s);
+        const bool tile_fast = (NM != kRefCompat) && __all_sync(0xffffffffu, fast);
 
         if (valid && j == 0) {
             const int64_t g = group_e0 >> (log2_L + 5);
@@ -133,95 +344,44 @@ quant_pack_kernel(const void* __restrict__ x_, const float* __restrict__ noise,
             min_out[g] = mn_st;
         }
 
-        // ---- codes ------------------------------------------------------------
-        const int64_t hash_ctr0 = (int64_t)((uint64_t)(group_e0 >> 2) + offset);
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const int piece = (k << log2_L) + j;               // piece index inside the group
-            uint32_t acc0 = 0, acc1 = 0;
+        // ---- codes ------------------------------------------------------------------
+        // hash counter of the group's first element; the pieces add less than 8*L to
+        // its low word, which has log2(8*L) zero low bits, so no carry reaches ctr_hi
+        const uint64_t ctr0 = (uint64_t)group_e0 >> 2;
+        const uint32_t ctr_lo0 = (uint32_t)ctr0, ctr_hi = (uint32_t)(ctr0 >> 32) ^ key_hi;
+        const int stage_base = (g_local << (log2_L + 2));
 
-            if (NM == kRefCompat) {
-                // act_triton_kernel.py:71,114,151-153 with the multiply and the add
-                // rounded separately, truncation toward zero, integer clamp
-                const float half_c = 0.5f - 1e-6f;
+        if (tile_fast) {
+            const f32x2 nmn2 = pack2(-mn, -mn), ns2 = pack2(-s, -s), y2 = pack2(y, y);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const float a = __fsub_rn(xf[k * 8 + i], mn);
-                    float t = __fadd_rn(__fmul_rn(a, y), half_c);
-                    int c = 0;
-                    if (t == t) {
-                        t = fminf(fmaxf(t, -1.0e9f), 1.0e9f);
-                        c = min(max((int)t, 0), QMAX);
-                    }
-                    if (BITS == 8 && i >= 4) acc1 |= (uint32_t)c << ((i - 4) * 8);
-                    else acc0 |= (uint32_t)c << (i * BITS);
-                }
-            } else {
-                float u[8];
-                if (NM == kNoiseHash) {
-                    uint32_t w0, w1, w2, w3;
-                    const uint64_t c0 = (uint64_t)hash_ctr0 + (uint64_t)(piece * 2);
-                    hash_2x32(c0, key_lo, key_hi, w0, w1);
-                    hash_2x32(c0 + 1, key_lo, key_hi, w2, w3);
-                    u[0] = u16_lo_as_float(w0); u[1] = u16_hi_as_float(w0);
-                    u[2] = u16_lo_as_float(w1); u[3] = u16_hi_as_float(w1);
-                    u[4] = u16_lo_as_float(w2); u[5] = u16_hi_as_float(w2);
-                    u[6] = u16_lo_as_float(w3); u[7] = u16_hi_as_float(w3);
-                } else if (NM == kNoiseTensor) {
-                    if (valid) {
-                        const int64_t e = group_e0 + (int64_t)piece * 8;
-                        const uint4 a = ldg_nc_v4(noise + e);
-                        const uint4 b = ldg_nc_v4(noise + e + 4);
-                        u[0] = __uint_as_float(a.x); u[1] = __uint_as_float(a.y);
-                        u[2] = __uint_as_float(a.z); u[3] = __uint_as_float(a.w);
-                        u[4] = __uint_as_float(b.x); u[5] = __uint_as_float(b.y);
-                        u[6] = __uint_as_float(b.z); u[7] = __uint_as_float(b.w);
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) u[i] = 0.0f;
-                    }
-                }
-
-                if (NM != kNoiseTensor && fast) {
-                    // t >= 0 and floor(t) <= QMAX are guaranteed here (for 8-bit hash
-                    // noise one fminf restores the upper bound), so floor is a
-                    // round-down add of 2^23 and the code is the low mantissa bits
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const float a = __fsub_rn(xf[k * 8 + i], mn);
-                        const float q = div_by_scale(a, s, y);
-                        float t;
-                        if (NM == kNoiseHash) t = __fmaf_rn(u[i], 0x1p-16f, q);   // exact u*2^-16, one rounding
-                        else t = __fadd_rn(q, 0.5f - 1e-6f);
-                        if (NM == kNoiseHash && BITS == 8) t = fminf(t, (float)QMAX);
-                        const uint32_t tb = __float_as_uint(__fadd_rd(t, kMagic));
-                        if (BITS == 8 && i >= 4) acc1 += tb << ((i - 4) * 8);
-                        else acc0 += tb << (i * BITS);
-                    }
-                    if (BITS == 8) { acc0 -= magic_sum<8, 4>(); acc1 -= magic_sum<8, 4>(); }
-                    else acc0 -= magic_sum<BITS, 8>();
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const float a = __fsub_rn(xf[k * 8 + i], mn);
-                        const float q = fast ? div_by_scale(a, s, y) : __fdiv_rn(a, s);
-                        float uu;
-                        if (NM == kNoiseHash) uu = __fmul_rn(u[i], 0x1p-16f);
-                        else if (NM == kNoiseTensor) uu = u[i];
-                        else uu = 0.5f - 1e-6f;
-                        const uint32_t c = code_from_t(__fadd_rn(q, uu), QMAX);
-                        if (BITS == 8 && i >= 4) acc1 |= c << ((i - 4) * 8);
-                        else acc0 |= c << (i * BITS);
-                    }
-                }
+            for (int k = 0; k < 4; ++k) {
+                const int piece = (k << log2_L) + j;
+                uint32_t acc0, acc1;
+                float u8[8];
+                if (NM == kNoiseTensor) load_noise8(u8, noise, group_e0 + (int64_t)piece * 8, valid);
+                encode_piece_fast<BITS, NM>(xf + k * 8, u8, nmn2, ns2, y2, ctr_lo0 + (uint32_t)(piece * 2),
+                                            ctr_hi, key_lo, acc0, acc1);
+                PieceStore<BITS>::st(my_stage + (stage_base + piece) * BITS, acc0, acc1);
             }
-            // stage the piece's BITS bytes at its place inside the tile
-            const int tile_piece = (g_local << (log2_L + 2)) + piece;
-            PieceStore<BITS>::st(my_stage + tile_piece * BITS, acc0, acc1);
+        } else {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int piece = (k << log2_L) + j;
+                uint32_t acc0, acc1;
+                if (NM == kRefCompat) {
+                    encode_piece_ref<BITS>(xf + k * 8, mn, y, acc0, acc1);
+                } else {
+                    float u8[8];
+                    if (NM == kNoiseTensor) load_noise8(u8, noise, group_e0 + (int64_t)piece * 8, valid);
+                    encode_piece_slow<BITS, NM>(xf + k * 8, u8, mn, s, ctr_lo0 + (uint32_t)(piece * 2),
+                                                ctr_hi, key_lo, acc0, acc1);
+                }
+                PieceStore<BITS>::st(my_stage + (stage_base + piece) * BITS, acc0, acc1);
+            }
         }
         __syncwarp();
 
-        // ---- coalesced write-out of the tile's packed bytes -------------------
+        // ---- coalesced write-out of the tile's packed bytes ---------------------------
         const int64_t out_base = tile * (int64_t)TILE_OUT;
         const int64_t remain_e = n_elems - tile * kTileElems;
         if (remain_e >= kTileElems) {
@@ -237,56 +397,74 @@ quant_pack_kernel(const void* __restrict__ x_, const float* __restrict__ noise,
                     reinterpret_cast<const uint32_t*>(my_stage)[w];
         }
         __syncwarp();
+
+        if (!PREFETCH) {
+            if (next_tile < n_tiles) {
+                const int64_t e0 = next_tile * kTileElems + lane_e0;
+                if (e0 < n_elems) load_raw<DT>(raw, xb, e0, log2_L, j); else zero_raw<DT>(raw);
+            }
+        }
     }
 }
-
 // ------------------------------------------------------------------ launcher
+
+// blocks of one instantiation that fit on an SM (asked once per instantiation)
+template <int DT, int BITS, int NM>
+static int pack_blocks_per_sm() {
+    static int cached = 0;
+    if (cached == 0) {
+        int n = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, quant_pack_kernel<DT, BITS, NM>,
+                                                          kPackThreads, 0) != cudaSuccess || n < 1) n = 1;
+        cached = n;
+    }
+    return cached;
+}
+
+int stream_grid_for(int64_t n_blocks_wanted, int blocks_per_sm);   // cabi.cu
+
+template <int DT, int BITS, int NM>
+static cudaError_t launch_pack_one(const void* x, const float* noise, void* packed, float* scale,
+                                   float* mn, int64_t n_elems, int log2_L, uint64_t seed,
+                                   uint64_t offset, int flags, float clamp_alpha, cudaStream_t st)
+{
+    const uint64_t key = hash_key(hash_key(seed) + offset);
+    const int64_t n_tiles = (n_elems + kTileElems - 1) / kTileElems;
+    // persistent grid: exactly the resident blocks of one wave (or fewer for small inputs)
+    const int grid = stream_grid_for((n_tiles + kPackWarps - 1) / kPackWarps, pack_blocks_per_sm<DT, BITS, NM>());
+    quant_pack_kernel<DT, BITS, NM><<<grid, kPackThreads, 0, st>>>(
+        x, noise, static_cast<uint8_t*>(packed), scale, mn, n_elems, log2_L,
+        (uint32_t)key, (uint32_t)(key >> 32), flags, clamp_alpha);
+    return cudaGetLastError();
+}
 
 template <int DT, int BITS>
 static cudaError_t launch_pack_mode(int mode, const void* x, const float* noise, void* packed,
                                     float* scale, float* mn, int64_t n_elems, int log2_L,
                                     uint64_t seed, uint64_t offset, int flags, float clamp_alpha,
-                                    cudaStream_t st, int grid)
+                                    cudaStream_t st)
 {
-    const uint64_t key = hash_key(seed);
-    const uint32_t klo = (uint32_t)key, khi = (uint32_t)(key >> 32);
-    uint8_t* p = static_cast<uint8_t*>(packed);
     switch (mode) {
-        case kNoiseHash:
-            quant_pack_kernel<DT, BITS, kNoiseHash><<<grid, kPackThreads, 0, st>>>(
-                x, noise, p, scale, mn, n_elems, log2_L, klo, khi, offset, flags, clamp_alpha);
-            break;
-        case kNoiseTensor:
-            quant_pack_kernel<DT, BITS, kNoiseTensor><<<grid, kPackThreads, 0, st>>>(
-                x, noise, p, scale, mn, n_elems, log2_L, klo, khi, offset, flags, clamp_alpha);
-            break;
-        case kNoiseConst:
-            quant_pack_kernel<DT, BITS, kNoiseConst><<<grid, kPackThreads, 0, st>>>(
-                x, noise, p, scale, mn, n_elems, log2_L, klo, khi, offset, flags, clamp_alpha);
-            break;
-        default:
-            quant_pack_kernel<DT, BITS, kRefCompat><<<grid, kPackThreads, 0, st>>>(
-                x, noise, p, scale, mn, n_elems, log2_L, klo, khi, offset, flags, clamp_alpha);
-            break;
+        case kNoiseHash:   return launch_pack_one<DT, BITS, kNoiseHash>(x, noise, packed, scale, mn, n_elems, log2_L, seed, offset, flags, clamp_alpha, st);
+        case kNoiseTensor: return launch_pack_one<DT, BITS, kNoiseTensor>(x, noise, packed, scale, mn, n_elems, log2_L, seed, offset, flags, clamp_alpha, st);
+        case kNoiseConst:  return launch_pack_one<DT, BITS, kNoiseConst>(x, noise, packed, scale, mn, n_elems, log2_L, seed, offset, flags, clamp_alpha, st);
+        default:           return launch_pack_one<DT, BITS, kRefCompat>(x, noise, packed, scale, mn, n_elems, log2_L, seed, offset, flags, clamp_alpha, st);
     }
-    return cudaGetLastError();
 }
 
 template <int DT>
 static cudaError_t launch_pack_bits(int bits, int mode, const void* x, const float* noise,
                                     void* packed, float* scale, float* mn, int64_t n_elems,
                                     int log2_L, uint64_t seed, uint64_t offset, int flags,
-                                    float clamp_alpha, cudaStream_t st, int grid)
+                                    float clamp_alpha, cudaStream_t st)
 {
     switch (bits) {
-        case 1: return launch_pack_mode<DT, 1>(mode, x, noise, packed, scale, mn, n_elems, log2_L, seed, offset, flags, clamp_alpha, st, grid);
-        case 2: return launch_pack_mode<DT, 2>(mode, x, noise, packed, scale, mn, n_elems, log2_L, seed, offset, flags, clamp_alpha, st, grid);
-        case 4: return launch_pack_mode<DT, 4>(mode, x, noise, packed, scale, mn, n_elems, log2_L, seed, offset, flags, clamp_alpha, st, grid);
-        default: return launch_pack_mode<DT, 8>(mode, x, noise, packed, scale, mn, n_elems, log2_L, seed, offset, flags, clamp_alpha, st, grid);
+        case 1: return launch_pack_mode<DT, 1>(mode, x, noise, packed, scale, mn, n_elems, log2_L, seed, offset, flags, clamp_alpha, st);
+        case 2: return launch_pack_mode<DT, 2>(mode, x, noise, packed, scale, mn, n_elems, log2_L, seed, offset, flags, clamp_alpha, st);
+        case 4: return launch_pack_mode<DT, 4>(mode, x, noise, packed, scale, mn, n_elems, log2_L, seed, offset, flags, clamp_alpha, st);
+        default: return launch_pack_mode<DT, 8>(mode, x, noise, packed, scale, mn, n_elems, log2_L, seed, offset, flags, clamp_alpha, st);
     }
 }
-
-int pack_grid_for(int64_t n_tiles);   // defined in cabi.cu
 
 }  // namespace act
 
@@ -313,15 +491,13 @@ extern "C" int act_quant_pack(const void* x, int dtype, int64_t n_groups, int gr
     int log2_L = 0;
     while ((32 << log2_L) < group_size) ++log2_L;
     const int64_t n_elems = n_groups * group_size;
-    const int64_t n_tiles = (n_elems + kTileElems - 1) / kTileElems;
-    const int grid = pack_grid_for(n_tiles);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     cudaError_t e;
     if (dtype == ACT_DTYPE_F32)
-        e = launch_pack_bits<ACT_DTYPE_F32>(bits, mode, x, noise, packed, scale, mn, n_elems, log2_L, seed, offset, flags, clamp_alpha, st, grid);
+        e = launch_pack_bits<ACT_DTYPE_F32>(bits, mode, x, noise, packed, scale, mn, n_elems, log2_L, seed, offset, flags, clamp_alpha, st);
     else if (dtype == ACT_DTYPE_BF16)
-        e = launch_pack_bits<ACT_DTYPE_BF16>(bits, mode, x, noise, packed, scale, mn, n_elems, log2_L, seed, offset, flags, clamp_alpha, st, grid);
+        e = launch_pack_bits<ACT_DTYPE_BF16>(bits, mode, x, noise, packed, scale, mn, n_elems, log2_L, seed, offset, flags, clamp_alpha, st);
     else
-        e = launch_pack_bits<ACT_DTYPE_F16>(bits, mode, x, noise, packed, scale, mn, n_elems, log2_L, seed, offset, flags, clamp_alpha, st, grid);
+        e = launch_pack_bits<ACT_DTYPE_F16>(bits, mode, x, noise, packed, scale, mn, n_elems, log2_L, seed, offset, flags, clamp_alpha, st);
     return e == cudaSuccess ? ACT_OK : ACT_ERR_LAUNCH;
 }

@@ -26,10 +26,12 @@ template <> struct CodeLoad<2> { static __device__ __forceinline__ uint2 ld(cons
 template <> struct CodeLoad<4> { static __device__ __forceinline__ uint2 ld(const uint8_t* p) { return make_uint2(__ldg(reinterpret_cast<const uint32_t*>(p)), 0u); } };
 template <> struct CodeLoad<8> { static __device__ __forceinline__ uint2 ld(const uint8_t* p) { return __ldg(reinterpret_cast<const uint2*>(p)); } };
 
-template <int BITS> __device__ __forceinline__ uint32_t code_at(uint2 w, int i) {
+// bit pattern of the float 2^23 + code i of the piece (exact integer -> float)
+template <int BITS> __device__ __forceinline__ uint32_t code_bits_at(uint2 w, int i) {
     constexpr uint32_t MASK = (1u << BITS) - 1u;
-    if (BITS == 8) return ((i < 4 ? w.x : w.y) >> ((i & 3) * 8)) & MASK;
-    return (w.x >> (i * BITS)) & MASK;
+    if (BITS == 8) return __byte_perm(i < 4 ? w.x : w.y, kMagicBits, 0x7440 + (i & 3));   // byte -> low byte
+    if (i == 0) return (w.x & MASK) | kMagicBits;
+    return ((w.x >> (i * BITS)) & MASK) | kMagicBits;
 }
 
 template <int DT, int BITS>
@@ -38,60 +40,63 @@ dequant_unpack_kernel(const uint8_t* __restrict__ packed, const float* __restric
                       const float* __restrict__ mn, uint8_t* __restrict__ y, int64_t n_elems,
                       int log2_gs)
 {
+    constexpr int EB = ElemT<DT>::bytes;
     const int lane = threadIdx.x & 31;
-    const int64_t n_chunks = (n_elems + 255) >> 8;
+    const int64_t n_tiles = (n_elems + kTileElems - 1) / kTileElems;
     const int64_t warp_stride = (int64_t)gridDim.x * kUnpackWarps;
-    for (int64_t c4 = ((int64_t)blockIdx.x * kUnpackWarps + (threadIdx.x >> 5)) * 4; c4 < n_chunks;
-         c4 += warp_stride * 4) {
+    const f32x2 magic2 = pack2(kMagic, kMagic);
+    for (int64_t tile = (int64_t)blockIdx.x * kUnpackWarps + (threadIdx.x >> 5); tile < n_tiles;
+         tile += warp_stride) {
+        // per-tile 64-bit bases; everything inside the tile is 32-bit arithmetic
+        const int64_t tile_e0 = tile * kTileElems;
+        const int remain = (int)((n_elems - tile_e0) < kTileElems ? (n_elems - tile_e0) : kTileElems);
+        const uint8_t* p_tile = packed + tile * (kTileElems / 8 * BITS);
+        const float* s_tile = scale + (tile_e0 >> log2_gs);
+        const float* m_tile = mn + (tile_e0 >> log2_gs);
+        uint8_t* y_tile = y + tile_e0 * EB;
+
         uint2 w[4];
         float s[4], m[4];
-        bool ok[4];
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-            const int64_t e = ((c4 + k) << 8) + lane * 8;
-            ok[k] = e < n_elems;
-            if (ok[k]) {
-                w[k] = CodeLoad<BITS>::ld(packed + (e >> 3) * BITS);
-                const int64_t g = e >> log2_gs;
-                s[k] = __ldg(scale + g);
-                m[k] = __ldg(mn + g);
+            const int e = k * 256 + lane * 8;               // element inside the tile
+            if (e < remain) {
+                w[k] = CodeLoad<BITS>::ld(p_tile + (k * 32 + lane) * BITS);
+                s[k] = __ldg(s_tile + (e >> log2_gs));
+                m[k] = __ldg(m_tile + (e >> log2_gs));
             }
         }
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-            if (!ok[k]) continue;
-            const int64_t e = ((c4 + k) << 8) + lane * 8;
-            float v[8];
+            const int e = k * 256 + lane * 8;
+            if (e >= remain) continue;
+            const f32x2 s2 = pack2(s[k], s[k]), m2 = pack2(m[k], m[k]);
+            uint32_t o[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                // integer code -> float through the 2^23 bit pattern (exact)
-                const float cf = __uint_as_float(kMagicBits | code_at<BITS>(w[k], i)) - kMagic;
-                v[i] = __fmaf_rn(cf, s[k], m[k]);
+            for (int p = 0; p < 4; ++p) {
+                // codes -> floats through the 2^23 bit pattern, then one fused multiply-add
+                const f32x2 c2 = sub2_rn(pack2u(code_bits_at<BITS>(w[k], 2 * p),
+                                                code_bits_at<BITS>(w[k], 2 * p + 1)), magic2);
+                unpack2u(fma2_rn(c2, s2, m2), o[2 * p], o[2 * p + 1]);
             }
             if (DT == ACT_DTYPE_F32) {
-                uint4 a, b;
-                a.x = __float_as_uint(v[0]); a.y = __float_as_uint(v[1]);
-                a.z = __float_as_uint(v[2]); a.w = __float_as_uint(v[3]);
-                b.x = __float_as_uint(v[4]); b.y = __float_as_uint(v[5]);
-                b.z = __float_as_uint(v[6]); b.w = __float_as_uint(v[7]);
-                stg_stream_v4(y + e * 4, a);
-                stg_stream_v4(y + e * 4 + 16, b);
-            } else if (DT == ACT_DTYPE_BF16) {
-                uint4 a;
-                __nv_bfloat162 t;
-                t = __floats2bfloat162_rn(v[0], v[1]); a.x = *reinterpret_cast<uint32_t*>(&t);
-                t = __floats2bfloat162_rn(v[2], v[3]); a.y = *reinterpret_cast<uint32_t*>(&t);
-                t = __floats2bfloat162_rn(v[4], v[5]); a.z = *reinterpret_cast<uint32_t*>(&t);
-                t = __floats2bfloat162_rn(v[6], v[7]); a.w = *reinterpret_cast<uint32_t*>(&t);
-                stg_stream_v4(y + e * 2, a);
+                stg_stream_v4(y_tile + e * 4, make_uint4(o[0], o[1], o[2], o[3]));
+                stg_stream_v4(y_tile + e * 4 + 16, make_uint4(o[4], o[5], o[6], o[7]));
             } else {
                 uint4 a;
-                __half2 t;
-                t = __floats2half2_rn(v[0], v[1]); a.x = *reinterpret_cast<uint32_t*>(&t);
-                t = __floats2half2_rn(v[2], v[3]); a.y = *reinterpret_cast<uint32_t*>(&t);
-                t = __floats2half2_rn(v[4], v[5]); a.z = *reinterpret_cast<uint32_t*>(&t);
-                t = __floats2half2_rn(v[6], v[7]); a.w = *reinterpret_cast<uint32_t*>(&t);
-                stg_stream_v4(y + e * 2, a);
+                uint32_t* ap = &a.x;
+#pragma unroll
+                for (int p = 0; p < 4; ++p) {
+                    const float lo = __uint_as_float(o[2 * p]), hi = __uint_as_float(o[2 * p + 1]);
+                    if (DT == ACT_DTYPE_BF16) {
+                        const __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
+                        ap[p] = *reinterpret_cast<const uint32_t*>(&t);
+                    } else {
+                        const __half2 t = __floats2half2_rn(lo, hi);
+                        ap[p] = *reinterpret_cast<const uint32_t*>(&t);
+                    }
+                }
+                stg_stream_v4(y_tile + e * 2, a);
             }
         }
     }
@@ -187,15 +192,31 @@ int stream_grid_for(int64_t n_blocks_wanted, int blocks_per_sm);   // cabi.cu
 static bool bits_ok(int bits) { return bits == 1 || bits == 2 || bits == 4 || bits == 8; }
 static bool group_ok(int gs) { return gs >= 32 && gs <= 1024 && !(gs & (gs - 1)); }
 
+template <int DT, int BITS>
+static void launch_unpack_one(const uint8_t* p, const float* s, const float* m, uint8_t* y,
+                              int64_t n_elems, int log2_gs, cudaStream_t st)
+{
+    static int per_sm = 0;          // resident blocks of this instantiation, asked once
+    if (per_sm == 0) {
+        int n = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, dequant_unpack_kernel<DT, BITS>,
+                                                          kUnpackThreads, 0) != cudaSuccess || n < 1) n = 1;
+        per_sm = n;
+    }
+    const int64_t tiles = (n_elems + kTileElems - 1) / kTileElems;
+    const int grid = stream_grid_for((tiles + kUnpackWarps - 1) / kUnpackWarps, per_sm);
+    dequant_unpack_kernel<DT, BITS><<<grid, kUnpackThreads, 0, st>>>(p, s, m, y, n_elems, log2_gs);
+}
+
 template <int DT>
 static void launch_unpack(int bits, const uint8_t* p, const float* s, const float* m, uint8_t* y,
-                          int64_t n_elems, int log2_gs, int grid, cudaStream_t st)
+                          int64_t n_elems, int log2_gs, cudaStream_t st)
 {
     switch (bits) {
-        case 1: dequant_unpack_kernel<DT, 1><<<grid, kUnpackThreads, 0, st>>>(p, s, m, y, n_elems, log2_gs); break;
-        case 2: dequant_unpack_kernel<DT, 2><<<grid, kUnpackThreads, 0, st>>>(p, s, m, y, n_elems, log2_gs); break;
-        case 4: dequant_unpack_kernel<DT, 4><<<grid, kUnpackThreads, 0, st>>>(p, s, m, y, n_elems, log2_gs); break;
-        default: dequant_unpack_kernel<DT, 8><<<grid, kUnpackThreads, 0, st>>>(p, s, m, y, n_elems, log2_gs); break;
+        case 1: launch_unpack_one<DT, 1>(p, s, m, y, n_elems, log2_gs, st); break;
+        case 2: launch_unpack_one<DT, 2>(p, s, m, y, n_elems, log2_gs, st); break;
+        case 4: launch_unpack_one<DT, 4>(p, s, m, y, n_elems, log2_gs, st); break;
+        default: launch_unpack_one<DT, 8>(p, s, m, y, n_elems, log2_gs, st); break;
     }
 }
 
@@ -216,14 +237,12 @@ extern "C" int act_dequant_unpack(const void* packed, const float* scale, const 
     int log2_gs = 5;
     while ((1 << log2_gs) < group_size) ++log2_gs;
     const int64_t n_elems = n_groups * group_size;
-    const int64_t tiles = (n_elems + kTileElems - 1) / kTileElems;
-    const int grid = stream_grid_for((tiles + kUnpackWarps - 1) / kUnpackWarps, 8);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const uint8_t* p = static_cast<const uint8_t*>(packed);
     uint8_t* out = static_cast<uint8_t*>(y);
-    if (out_dtype == ACT_DTYPE_F32) launch_unpack<ACT_DTYPE_F32>(bits, p, scale, mn, out, n_elems, log2_gs, grid, st);
-    else if (out_dtype == ACT_DTYPE_BF16) launch_unpack<ACT_DTYPE_BF16>(bits, p, scale, mn, out, n_elems, log2_gs, grid, st);
-    else launch_unpack<ACT_DTYPE_F16>(bits, p, scale, mn, out, n_elems, log2_gs, grid, st);
+    if (out_dtype == ACT_DTYPE_F32) launch_unpack<ACT_DTYPE_F32>(bits, p, scale, mn, out, n_elems, log2_gs, st);
+    else if (out_dtype == ACT_DTYPE_BF16) launch_unpack<ACT_DTYPE_BF16>(bits, p, scale, mn, out, n_elems, log2_gs, st);
+    else launch_unpack<ACT_DTYPE_F16>(bits, p, scale, mn, out, n_elems, log2_gs, st);
     return cudaGetLastError() == cudaSuccess ? ACT_OK : ACT_ERR_LAUNCH;
 }
 

@@ -1,0 +1,71 @@
+"""The quantise boundary every save-for-backward Function calls.
+
+`quantize / dequantize / unified_quantize / unified_dequantize` keep the
+signatures, the `(tensors, 14-tuple meta)` return layout and the DIVISION
+residual of Activation_Compression/modules/module_utils.py:28-102; the kernels
+behind `torch.ops.act_lib.*` are the CUDA ones registered by `act_kernels`.
+
+q_meta order (module_utils.py:37,68):
+  (bits, pack_only, group_size, act_padding, N, G, new_H, new_W,
+   spatial_pad_elig, spatial_reshape_elig, channel_mean, avg_alam, alam_bits, ori_shape)
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+from .. import act_kernels  # noqa: F401  (registers torch.ops.act_lib.*)
+from .tensor_act_reshape_utils import (
+    spatical_aware_act_tensor_reshape,
+    spatical_aware_act_tensor_reshape_back,
+)
+
+
+def quantize(input, bits, pack_only, group_size, act_padding, N, avg_alam, alam_bits, clamp, clamp_alpha):
+    groups, N, G, new_H, new_W, ori_shape, pad_elig, reshape_elig, channel_mean = \
+        spatical_aware_act_tensor_reshape(input, Group_Size=group_size, act_padding=act_padding,
+                                          pack_only=pack_only)
+    if pack_only:
+        out = torch.ops.act_lib.pack_triton(groups, bits, group_size)
+        return (out, None, None), (bits, pack_only, group_size, act_padding, N, G, 0, 0, False, False,
+                                   channel_mean, None, None, ori_shape)
+    out, scaler, ema_min = torch.ops.act_lib.quant_pack_triton(groups, bits, group_size, avg_alam,
+                                                               alam_bits, clamp, clamp_alpha)
+    return (out, scaler, ema_min), (bits, pack_only, group_size, act_padding, N, G, new_H, new_W,
+                                    pad_elig, reshape_elig, channel_mean, avg_alam, alam_bits, ori_shape)
+
+
+def unified_quantize(input, input_l, target_name, meta, clamp, clamp_alpha):
+    m = meta[f"{target_name}"]
+    tensors, q_meta = quantize(input, m["bits"], m["pack_only"], m["group_size"], m["act_padding"],
+                               m["N"], m["AVG_ALAM"], m["ALAM_BITS"], clamp, clamp_alpha)
+    return tensors, q_meta, input_l
+
+
+def dequantize(quantized_tensor, quantized_meta):
+    q_input, q_scale, ema_mn = quantized_tensor
+    (q_bits, pack_only, group_size, act_padding, N, G, new_H, new_W, pad_elig, reshape_elig,
+     channel_mean, avg_alam, alam_bits, input_shape) = quantized_meta
+    if pack_only:
+        unpack = torch.ops.act_lib.unpack_triton(q_input, q_bits, N, G, group_size)
+    else:
+        unpack = torch.ops.act_lib.dequant_unpack_triton(q_input, q_scale, ema_mn, q_bits, group_size,
+                                                         avg_alam, alam_bits)
+    return spatical_aware_act_tensor_reshape_back(unpack, input_shape, group_size, new_H, new_W,
+                                                  act_padding, pad_elig, reshape_elig, channel_mean)
+
+
+def unified_dequantize(ori_quantized_tensor, ori_quantized_meta, input_l):
+    input_shape = ori_quantized_meta[-1]
+    x = dequantize(ori_quantized_tensor, ori_quantized_meta)
+    if input_l is None:
+        return x
+    # DIVISION: add back the nearest-upsampled low-pass part (module_utils.py:91-102)
+    if len(input_shape) == 4:
+        size = (input_shape[-2], input_shape[-1])
+    elif len(input_shape) == 3:
+        size = input_shape[2]
+    else:
+        size = input_shape[0]
+    low = F.interpolate(input_l.to(torch.bfloat16), size=size, mode="nearest")
+    return x + low.to(torch.bfloat16)

@@ -1,0 +1,55 @@
+"""Drop-in BatchNorm modules
+(Activation_Compression/modules/normalization/normalization_layers.py:8-109)."""
+import torch.distributed as dist
+from torch import nn
+
+from .normalization_ops import _DOBatchNorm, _DOSyncBatchNorm
+
+
+def _ema_factor(mod):
+    factor = 0.0 if mod.momentum is None else mod.momentum
+    if mod.training and mod.track_running_stats and mod.num_batches_tracked is not None:
+        mod.num_batches_tracked.add_(1)
+        if mod.momentum is None:
+            factor = 1.0 / float(mod.num_batches_tracked)
+    return factor
+
+
+class DOBatchNorm2d(nn.BatchNorm2d):
+    def __init__(self, num_features, eps=1e-05, momentum=0.1, affine=True, track_running_stats=True,
+                 group=0, target_name=None, meta={}):
+        super().__init__(num_features, eps, momentum, affine, track_running_stats)
+        self.target_name, self.meta, self.ema_grad_meta = target_name, meta, None
+
+    def forward(self, x):
+        if not self.training:
+            return super().forward(x)
+        self._check_input_dim(x)
+        return _DOBatchNorm.apply(x, self.weight, self.bias, self.running_mean, self.running_var,
+                                  _ema_factor(self), self.eps, self.target_name, self.meta,
+                                  self.ema_grad_meta)
+
+
+class DOSyncBatchNorm2d(nn.SyncBatchNorm):
+    def __init__(self, num_features, eps=1e-5, momentum=0.1, affine=True, track_running_stats=True,
+                 process_group=None, group=0, target_name=None, meta={}):
+        super().__init__(num_features, eps, momentum, affine, track_running_stats, process_group)
+        self.target_name, self.meta, self.ema_grad_meta = target_name, meta, None
+
+    def forward(self, x):
+        if not self.training:
+            return super().forward(x)
+        if not x.is_cuda:
+            raise ValueError("SyncBatchNorm expected input tensor to be on GPU")
+        self._check_input_dim(x)
+        factor = _ema_factor(self)
+        world_size, group = 1, None
+        if dist.is_available() and dist.is_initialized():
+            group = self.process_group if self.process_group else dist.group.WORLD
+            world_size = dist.get_world_size(group)
+        if world_size == 1:
+            return _DOBatchNorm.apply(x, self.weight, self.bias, self.running_mean, self.running_var,
+                                      factor, self.eps, self.target_name, self.meta, self.ema_grad_meta)
+        return _DOSyncBatchNorm.apply(x, self.weight, self.bias, self.running_mean, self.running_var,
+                                      self.eps, factor, group, world_size, self.target_name, self.meta,
+                                      self.ema_grad_meta)

@@ -1,0 +1,102 @@
+"""BatchNorm Function that saves the normalised activation compressed.
+
+Forward: per-channel batch statistics (fp32), x_hat = (x - mean) * invstd,
+y = x_hat * weight + bias; x_hat is stored through the codec.  Backward:
+dgamma = sum(dy * x_hat), dbeta = sum(dy),
+dx = weight * invstd / M * (M * dy - dbeta - x_hat * dgamma).
+Argument order and saved tensors follow
+Activation_Compression/modules/normalization/normalization_ops.py:10-171; the
+statistics and the element-wise maths are plain PyTorch here, the compressed
+state goes through the CUDA codec.  The SyncBN variant all-gathers
+(mean, invstd, count) per rank as normalization_ops.py:181-195 does.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+from torch.amp import custom_bwd, custom_fwd
+from torch.autograd import Function
+
+from ..module_utils import unified_dequantize, unified_quantize
+
+
+def _channel_view(t):
+    return [1, -1] + [1] * (t.dim() - 2)
+
+
+class _DOBatchNorm(Function):
+    @staticmethod
+    @custom_fwd(device_type="cuda")
+    def forward(ctx, input, weight, bias, running_mean, running_var, exponential_average_factor,
+                eps, target_name, meta, ema_grad_meta, process_group=None, world_size=1):
+        ctx.set_materialize_grads(False)
+        x = input.float()
+        dims = [0] + list(range(2, x.dim()))
+        count = x.numel() // x.shape[1]
+        var, mean = torch.var_mean(x, dim=dims, unbiased=False)
+        total = count
+        if world_size > 1:
+            # combine the per-rank statistics (count-weighted), one small all-gather
+            local = torch.cat([mean, var + mean * mean, mean.new_tensor([float(count)])])
+            gathered = [torch.empty_like(local) for _ in range(world_size)]
+            dist.all_gather(gathered, local, group=process_group)
+            g = torch.stack(gathered)
+            C = mean.numel()
+            counts = g[:, -1:]
+            total = counts.sum()
+            mean = (g[:, :C] * counts).sum(0) / total
+            var = (g[:, C:2 * C] * counts).sum(0) / total - mean * mean
+        invstd = torch.rsqrt(var + eps)
+        shape = _channel_view(x)
+        x_hat = (x - mean.view(shape)) * invstd.view(shape)
+        w = weight.float().view(shape) if weight is not None else 1.0
+        b = bias.float().view(shape) if bias is not None else 0.0
+        y = (x_hat * w + b).to(input.dtype)
+        if running_mean is not None:
+            n = float(total)
+            unbiased = var * (n / max(n - 1.0, 1.0))
+            running_mean.mul_(1.0 - exponential_average_factor).add_(mean, alpha=exponential_average_factor)
+            running_var.mul_(1.0 - exponential_average_factor).add_(unbiased, alpha=exponential_average_factor)
+        q_tensors, q_meta, _ = unified_quantize(x_hat.to(torch.bfloat16), None, target_name, meta,
+                                                clamp=False, clamp_alpha=0.0)
+        ctx.q_meta = q_meta
+        ctx.sync = (process_group, world_size)
+        ctx.save_for_backward(weight, q_tensors[0], q_tensors[1], q_tensors[2], invstd)
+        return y
+
+    @staticmethod
+    @custom_bwd(device_type="cuda")
+    def backward(ctx, dy):
+        weight, q_out, q_scale, q_min, invstd = ctx.saved_tensors
+        process_group, world_size = ctx.sync
+        x_hat = unified_dequantize((q_out, q_scale, q_min), ctx.q_meta, None).float()
+        g = dy.float()
+        dims = [0] + list(range(2, g.dim()))
+        shape = _channel_view(g)
+        dgamma = (g * x_hat).sum(dims)
+        dbeta = g.sum(dims)
+        M = float(g.numel() // g.shape[1])
+        sum_dg, sum_db = dgamma, dbeta
+        if world_size > 1:
+            both = torch.cat([dgamma, dbeta, dgamma.new_tensor([M])])
+            dist.all_reduce(both, group=process_group)
+            C = dgamma.numel()
+            sum_dg, sum_db, M = both[:C], both[C:2 * C], float(both[-1])
+        w = weight.float() if weight is not None else torch.ones_like(invstd)
+        dx = (w * invstd / M).view(shape) * (M * g - sum_db.view(shape) - x_hat * sum_dg.view(shape))
+        dw = dgamma.to(weight.dtype) if weight is not None else None
+        db = dbeta.to(weight.dtype) if weight is not None else None
+        return dx.to(dy.dtype), dw, db, None, None, None, None, None, None, None, None, None
+
+
+class _DOSyncBatchNorm(Function):
+    @staticmethod
+    def forward(ctx, input, weight, bias, running_mean, running_var, eps, momentum, process_group,
+                world_size, target_name, meta, ema_grad_meta):
+        raise RuntimeError("use _DOSyncBatchNorm.apply")
+
+    @staticmethod
+    def apply(input, weight, bias, running_mean, running_var, eps, momentum, process_group,
+              world_size, target_name, meta, ema_grad_meta):
+        return _DOBatchNorm.apply(input, weight, bias, running_mean, running_var, momentum, eps,
+                                  target_name, meta, ema_grad_meta, process_group, world_size)

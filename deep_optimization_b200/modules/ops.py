@@ -1,0 +1,181 @@
+"""Save-for-backward autograd Functions of the conv / linear layers.
+
+Each Function runs the stock forward op and stores the layer input compressed
+(`unified_quantize`) instead of the tensor itself; backward decompresses it
+(`unified_dequantize`) and computes the gradients with the stock gradient ops.
+Argument orders, saved-tensor orders and the returned gradient tuples follow
+Activation_Compression/modules/ops.py:200-387 (`_DOConvnd`), :390-435
+(`_DOConv{1,2,3}d`), :438-540 (`_DOLinear`) and :626-680 (`GroupPACTClampFn`).
+The dead experiments of that file (Hadamard, low-rank, LARS updates) are not
+carried over.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+from torch.amp import custom_bwd, custom_fwd
+from torch.autograd import Function
+from torch.nn.grad import (conv1d_input, conv1d_weight, conv2d_input, conv2d_weight,
+                           conv3d_input, conv3d_weight)
+from torch.nn.modules.utils import _pair, _single, _triple
+
+from .module_utils import unified_dequantize, unified_quantize
+
+_CONV_GRADS = {1: (conv1d_input, conv1d_weight), 2: (conv2d_input, conv2d_weight),
+               3: (conv3d_input, conv3d_weight)}
+
+
+class _DOConvnd(Function):
+    @staticmethod
+    def run_forward(ctx, forward_op, input, weight, learnable_scale, stride=1, padding=0, dilation=1,
+                    groups=1, clamp_alpha=3.0, target_name=None, meta=None, ema_grad_meta=None):
+        weight_master = weight
+        if torch.is_autocast_enabled("cuda"):
+            dt = torch.get_autocast_dtype("cuda")
+            input = input.to(dt)
+            weight_compute = weight.to(dt)
+        else:
+            weight_compute = weight_master
+        m = meta[f"{target_name}"]
+
+        # DIVISION: keep a low-pass copy (average pool) beside the compressed input
+        input_l = None
+        if m["DIVISION"] is not None and not m["pack_only"]:
+            k = min(input.shape[-2], input.shape[-1], m["DIVISION"]["pool_kernel_size"])
+            input_l = F.avg_pool2d(input.to(torch.bfloat16), k, stride=k, padding=0).to(torch.float8_e4m3fn)
+
+        q_tensors, q_meta, input_l = unified_quantize(input.to(torch.bfloat16), input_l, target_name, meta,
+                                                      clamp=True, clamp_alpha=clamp_alpha)
+        ctx.meta = stride, padding, dilation, groups, ema_grad_meta, clamp_alpha
+        ctx.save_for_backward(weight_master, q_tensors[0], q_tensors[1], q_tensors[2], input_l, learnable_scale)
+        ctx.q_inputs_meta = q_meta
+        return forward_op(input, weight_compute, bias=None, stride=stride, padding=padding,
+                          dilation=dilation, groups=groups)
+
+    @staticmethod
+    def run_backward(ctx, dy, dim, pad_fn):
+        q_meta = ctx.q_inputs_meta
+        stride, padding, dilation, groups, _, _ = ctx.meta
+        weight_master, q_out, q_scale, q_min, input_l, _ = ctx.saved_tensors
+        if torch.is_autocast_enabled("cuda"):
+            dy = dy.to(torch.get_autocast_dtype("cuda"))
+            weight_compute = weight_master.to(torch.bfloat16)
+        else:
+            weight_compute = weight_master
+        stride, padding, dilation = pad_fn(stride), pad_fn(padding), pad_fn(dilation)
+
+        x = unified_dequantize((q_out, q_scale, q_min), q_meta, input_l)
+        x = x.to(weight_compute.dtype)
+        dy = dy.to(weight_compute.dtype)
+        grad_input, grad_weight = _CONV_GRADS[dim]
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = grad_input(x.shape, weight_compute, dy, stride=stride, padding=padding,
+                            dilation=dilation, groups=groups)
+        if ctx.needs_input_grad[1]:
+            dw = grad_weight(x, weight_compute.shape, dy, stride=stride, padding=padding,
+                             dilation=dilation, groups=groups).to(weight_master.dtype)
+        return dx, dw, None, None, None, None, None, None, None, None, None
+
+
+def _make_conv(dim, fwd_op, pad_fn):
+    class _Conv(Function):
+        @staticmethod
+        @custom_fwd(device_type="cuda")
+        def forward(ctx, input, weight, learnable_scale, stride=1, padding=0, dilation=1, groups=1,
+                    clamp_alpha=3.0, target_name=None, meta=None, ema_grad_meta=None):
+            return _DOConvnd.run_forward(ctx, fwd_op, input, weight, learnable_scale, stride=stride,
+                                         padding=padding, dilation=dilation, groups=groups,
+                                         clamp_alpha=clamp_alpha, target_name=target_name, meta=meta,
+                                         ema_grad_meta=ema_grad_meta)
+
+        @staticmethod
+        @custom_bwd(device_type="cuda")
+        def backward(ctx, dy):
+            return _DOConvnd.run_backward(ctx, dy, dim, pad_fn)
+
+    _Conv.__name__ = _Conv.__qualname__ = f"_DOConv{dim}d"
+    return _Conv
+
+
+_DOConv1d = _make_conv(1, F.conv1d, _single)
+_DOConv2d = _make_conv(2, F.conv2d, _pair)
+_DOConv3d = _make_conv(3, F.conv3d, _triple)
+
+
+class _DOLinear(Function):
+    @staticmethod
+    @custom_fwd(device_type="cuda")
+    def forward(ctx, input, weight, clamp_alpha, target_name, meta, ema_grad_meta):
+        weight_master = weight
+        if torch.is_autocast_enabled("cuda"):
+            dt = torch.get_autocast_dtype("cuda")
+            input = input.to(dt)
+            weight_compute = weight.to(dt)
+        else:
+            weight_compute = weight_master
+        m = meta[f"{target_name}"]
+
+        input_l = None
+        if m["DIVISION"] is not None and input.ndim > 2 and not m["pack_only"]:
+            k = min(input.shape[2], m["DIVISION"]["pool_kernel_size"])
+            input_l = F.avg_pool1d(input.to(torch.bfloat16), k, stride=k, padding=0)
+
+        q_tensors, q_meta, input_l = unified_quantize(input, input_l, target_name, meta, clamp=True,
+                                                      clamp_alpha=clamp_alpha)
+        ctx.target_name = target_name
+        ctx.q_inputs_meta = q_meta
+        ctx.meta = input.shape, ema_grad_meta, clamp_alpha
+        ctx.save_for_backward(weight_master, q_tensors[0], q_tensors[1], q_tensors[2], input_l)
+        return F.linear(input, weight_compute, None)
+
+    @staticmethod
+    @custom_bwd(device_type="cuda")
+    def backward(ctx, dy):
+        q_meta = ctx.q_inputs_meta
+        input_shape, _, _ = ctx.meta
+        weight_master, q_out, q_scale, q_min, input_l = ctx.saved_tensors
+        if torch.is_autocast_enabled("cuda"):
+            dt = torch.get_autocast_dtype("cuda")
+            weight_compute = weight_master.to(dt)
+            dy = dy.to(dt)
+        else:
+            weight_compute = weight_master
+        x = unified_dequantize((q_out, q_scale, q_min), q_meta, input_l).to(weight_compute.dtype)
+        dy = dy.to(weight_compute.dtype)
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        x2 = x.reshape(-1, x.shape[-1])
+        dw = dx = None
+        if ctx.needs_input_grad[1]:
+            dw = dy2.T.mm(x2).to(weight_master.dtype)
+        if ctx.needs_input_grad[0]:
+            dx = dy2.mm(weight_compute).view(*input_shape)
+        return dx, dw, None, None, None, None
+
+
+class GroupPACTClampFn(Function):
+    """clamp(x, -alpha, alpha) whose backward mask (|x| <= alpha) is kept 1 bit per element."""
+
+    @staticmethod
+    @custom_fwd(device_type="cuda")
+    def forward(ctx, x, alpha, group_size, meta, target_name):
+        if torch.is_autocast_enabled("cuda"):
+            x = x.to(torch.get_autocast_dtype("cuda"))
+        alpha = float(alpha)
+        inside = (x.abs() <= alpha).to(torch.int8)
+        y = x.clamp(-alpha, alpha).to(torch.bfloat16)
+        key = f"{target_name}_clamp"
+        clamp_meta = {key: {"bits": 1, "pack_only": True, "group_size": group_size,
+                            "act_padding": meta[f"{target_name}"]["act_padding"],
+                            "N": meta[f"{target_name}"]["N"], "AVG_ALAM": False, "ALAM_BITS": 0}}
+        q_tensors, q_meta, _ = unified_quantize(inside, None, key, clamp_meta, clamp=False, clamp_alpha=alpha)
+        ctx.save_for_backward(q_tensors[0])
+        ctx.q_meta = q_meta
+        return y
+
+    @staticmethod
+    @custom_bwd(device_type="cuda")
+    def backward(ctx, dy):
+        (packed,) = ctx.saved_tensors
+        mask = unified_dequantize((packed, None, None), ctx.q_meta, None)
+        return (dy * mask.to(dy.dtype)).to(torch.bfloat16), None, None, None, None

@@ -62,7 +62,8 @@ extern "C" {
  *   x       [n_groups, group_size] of `dtype`, contiguous, 16-byte aligned
  *   noise   NULL, or fp32 [n_groups, group_size] of u in [0,1), 16-byte aligned
  *   seed, offset   used when noise == NULL and ACT_FLAG_ROUND_NEAREST is clear:
- *           element e takes u = 16 bits of hash((e >> 2) + offset, seed) / 65536
+ *           element e takes u = 16 bits of hash(e >> 2; key(seed, offset)) / 65536;
+ *           seed picks a family of streams, offset one stream (advance it per call)
  *   packed  n_groups*group_size*bits/8 bytes, 16-byte aligned; 32-bit little-endian
  *           words, code j of a word at bits [j*bits,(j+1)*bits)
  *   scale, min   fp32 [n_groups]

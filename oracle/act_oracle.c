@@ -110,8 +110,9 @@ static inline float max_ord(float a, float b) {
 /* ------------------------------------------------------------ noise hash
  * Counter hash used when no noise tensor is given.  Four consecutive elements
  * share one 64-bit output; element e takes 16-bit field (e & 3) of
- * H((e >> 2) + offset) and u = field / 65536.  H is four rounds of a 2x32
- * multiply-xor network keyed by splitmix64(seed).  It has no counterpart in the
+ * H(e >> 2) and u = field / 65536.  H is four rounds of a 2x32 multiply-xor
+ * network keyed by splitmix64(splitmix64(seed) + offset): seed picks a family
+ * of streams, offset one stream of it (callers advance it per call).  It has no counterpart in the
  * reference (whose generators are an index hash in
  * cpp_extension/include/quant_common.h:32-43 and Triton's tl.rand).          */
 #define HASH_MUL   0xD256D193u
@@ -127,8 +128,8 @@ static inline uint64_t hash_key(uint64_t seed) {
     return z ^ (z >> 31);
 }
 
-static inline void hash_2x32(uint64_t ctr, uint64_t seed, uint32_t *o0, uint32_t *o1) {
-    const uint64_t key = hash_key(seed);
+static inline void hash_2x32(uint64_t ctr, uint64_t seed, uint64_t offset, uint32_t *o0, uint32_t *o1) {
+    const uint64_t key = hash_key(hash_key(seed) + offset);
     uint32_t L = (uint32_t)ctr;
     uint32_t R = (uint32_t)(ctr >> 32) ^ (uint32_t)(key >> 32);
     uint32_t k = (uint32_t)key;
@@ -144,7 +145,7 @@ static inline void hash_2x32(uint64_t ctr, uint64_t seed, uint32_t *o0, uint32_t
 
 static inline float hash_noise(uint64_t elem, uint64_t seed, uint64_t offset) {
     uint32_t w0, w1;
-    hash_2x32((elem >> 2) + offset, seed, &w0, &w1);
+    hash_2x32(elem >> 2, seed, offset, &w0, &w1);
     uint32_t w = (elem & 2) ? w1 : w0;
     uint32_t h = (elem & 1) ? (w >> 16) : (w & 0xffffu);
     return (float)h * (1.0f / 65536.0f);

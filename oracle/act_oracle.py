@@ -233,12 +233,16 @@ def _as_f32(x: np.ndarray, dtype: str | None) -> np.ndarray:
 def np_hash_noise(seed: int, offset: int, first: int, count: int) -> np.ndarray:
     """numpy restatement of the 16-bit counter hash (act_oracle.c: hash_2x32)."""
     e = np.arange(first, first + count, dtype=np.uint64)
-    ctr = (e >> np.uint64(2)) + np.uint64(offset & 0xFFFFFFFFFFFFFFFF)
+    ctr = e >> np.uint64(2)
     M64 = 0xFFFFFFFFFFFFFFFF
-    z = (seed + 0x9E3779B97F4A7C15) & M64          # splitmix64 finaliser on the seed
-    z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & M64
-    z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & M64
-    key = z ^ (z >> 31)
+
+    def splitmix(v):
+        z = (v + 0x9E3779B97F4A7C15) & M64
+        z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & M64
+        z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & M64
+        return z ^ (z >> 31)
+
+    key = splitmix((splitmix(seed & M64) + (offset & M64)) & M64)
     L = (ctr & np.uint64(0xFFFFFFFF))
     R = (ctr >> np.uint64(32)) ^ np.uint64(key >> 32)
     k = key & 0xFFFFFFFF

@@ -1,0 +1,90 @@
+"""CPU tests of the host-side mirror of the reference interface: grouping helpers,
+operator registration (fake kernels), controller planning, bit-allocation policy."""
+import pytest
+import torch
+from torch import nn
+
+
+def test_reshape_round_trips():
+    from deep_optimization_b200.modules.tensor_act_reshape_utils import (
+        spatical_aware_act_tensor_reshape as fwd, spatical_aware_act_tensor_reshape_back as back)
+    cases = [((4, 6, 32, 48), 256, False), ((4, 6, 32, 48), 64, False), ((4, 6, 32, 48), 128, False),
+             ((4, 6, 30, 30), 256, True), ((3, 197, 7), 256, True), ((5, 1000), 256, True),
+             ((2, 8, 16, 48), 256, False)]           # H != W with spatial tiles
+    for shape, gs, pad in cases:
+        x = torch.randn(shape)
+        g, N, G, nh, nw, shp, pe, re_, cm = fwd(x, gs, pad, False)
+        assert g.shape == (N, G, gs) and g.is_contiguous()
+        y = back(g, shp, gs, nh, nw, pad, pe, re_, cm)
+        assert torch.equal(x, y), (shape, gs, pad)
+
+
+def test_spatial_tiles_are_tiles():
+    from deep_optimization_b200.modules.tensor_act_reshape_utils import spatical_aware_act_tensor_reshape
+    x = torch.arange(2 * 3 * 32 * 32, dtype=torch.float32).view(2, 3, 32, 32)
+    g, *_ = spatical_aware_act_tensor_reshape(x, 256, False, False)
+    assert torch.equal(g[0, 0].view(16, 16), x[0, 0, :16, :16])
+    assert torch.equal(g[0, 1].view(16, 16), x[0, 0, :16, 16:32])
+
+
+def test_ops_are_registered_with_real_schemas():
+    import deep_optimization_b200.act_kernels  # noqa: F401
+    from torch._subclasses.fake_tensor import FakeTensorMode
+    with FakeTensorMode():
+        x = torch.empty(4, 8, 128, dtype=torch.bfloat16, device="cuda")
+        p, s, m = torch.ops.act_lib.quant_pack_triton(x, 2, 128, False, 0, True, 3.0)
+        assert p.shape == (32, 8) and p.dtype == torch.int32 and s.shape == (4, 8) and m.dtype == torch.float32
+        y = torch.ops.act_lib.dequant_unpack_triton(p, s, m, 2, 128, False, 0)
+        assert y.shape == (4, 8, 128) and y.dtype == torch.bfloat16
+        mask = torch.empty(4, 8, 128, dtype=torch.int8, device="cuda")
+        pk = torch.ops.act_lib.pack_triton(mask, 1, 128)
+        assert pk.shape == (32, 4)
+        assert torch.ops.act_lib.unpack_triton(pk, 1, 4, 8, 128).shape == (4, 8, 128)
+        with pytest.raises(ValueError):
+            torch.ops.act_lib.quant_pack_triton(x, 3, 128, False, 0, True, 3.0)
+
+
+def test_find_group_size():
+    from deep_optimization_b200.controller import find_group_size
+    assert find_group_size(64 * 56 * 56, 2) == (512, False)
+    assert find_group_size(197 * 768, 2) == (256, False)
+    assert find_group_size(1000, 2) == (256, True)
+    assert find_group_size(1024 * 3, 2, special=True) == (1024, False)
+
+
+def test_controller_plans_and_swaps():
+    from deep_optimization_b200.controller import Controller
+    from deep_optimization_b200.layers import DOConv2d, DOLinear
+    from deep_optimization_b200.modules.activations.act_layers import DOReLU_Variance
+    from deep_optimization_b200.modules.normalization.normalization_layers import DOBatchNorm2d
+    model = nn.Sequential(nn.Conv2d(3, 64, 3, padding=1, bias=False), nn.BatchNorm2d(64), nn.ReLU(),
+                          nn.Conv2d(64, 64, 3, padding=1, bias=False), nn.Flatten(), nn.Linear(64 * 32 * 32, 10))
+    cfg = dict(default_bits=2, auto_precision=None, batch_size=64, min_activation_mib=1)
+    w0 = model[0].weight.detach().clone()
+    c = Controller(model, cfg, input_shape=(3, 32, 32), test=False, device="cpu")
+    t = c.traced_model
+    assert isinstance(t[0], DOConv2d) and isinstance(t[1], DOBatchNorm2d)
+    assert isinstance(t[2], DOReLU_Variance) and isinstance(t[3], DOConv2d)
+    assert isinstance(t[5], nn.Linear) and not isinstance(t[5], DOLinear)      # output too small
+    assert torch.equal(t[0].weight, w0)
+    m = c.meta["3"]
+    assert (m["bits"], m["group_size"], m["act_padding"], m["N"], m["pack_only"]) == (2, 512, False, 64, False)
+    assert c.meta["2"]["pack_only"] and c.meta["2"]["bits"] == 1
+    assert set(("AVG_ALAM", "ALAM_BITS", "DIVISION", "NG")) <= set(m)
+    # eval mode is the stock module path and runs on CPU
+    t.eval()
+    with torch.no_grad():
+        assert t(torch.randn(2, 3, 32, 32)).shape == (2, 10)
+
+
+def test_quantizer_policy():
+    from deep_optimization_b200.quantizer import Quantizer
+    q = Quantizer(dict(default_bits=4, auto_precision=None), {"a": None, "b": None})
+    q.iterate()
+    assert q.bits == {"a": 4, "b": 4}
+    assert [q.hessian2bit_lookup_table(v) for v in (10, 60, 300, 600, 2000)] == [1, 2, 3, 4, 8]
+    p = nn.Parameter(torch.zeros(3, 3))
+    q.filter_tensors([("p", p)])
+    assert not q.check_quantize(p)
+    assert q.check_quantize(torch.zeros(2, 3, requires_grad=True))
+    assert not q.check_quantize(torch.zeros(2, 3))
