@@ -62,7 +62,8 @@ def test_controller_plans_and_swaps():
     cfg = dict(default_bits=2, auto_precision=None, batch_size=64, min_activation_mib=1)
     w0 = model[0].weight.detach().clone()
     c = Controller(model, cfg, input_shape=(3, 32, 32), test=False, device="cpu")
-    t = c.traced_model
+    net = c.traced_model
+    t = [net.get_submodule(str(i)) for i in range(6)]
     assert isinstance(t[0], DOConv2d) and isinstance(t[1], DOBatchNorm2d)
     assert isinstance(t[2], DOReLU_Variance) and isinstance(t[3], DOConv2d)
     assert isinstance(t[5], nn.Linear) and not isinstance(t[5], DOLinear)      # output too small
@@ -72,9 +73,9 @@ def test_controller_plans_and_swaps():
     assert c.meta["2"]["pack_only"] and c.meta["2"]["bits"] == 1
     assert set(("AVG_ALAM", "ALAM_BITS", "DIVISION", "NG")) <= set(m)
     # eval mode is the stock module path and runs on CPU
-    t.eval()
+    net.eval()
     with torch.no_grad():
-        assert t(torch.randn(2, 3, 32, 32)).shape == (2, 10)
+        assert net(torch.randn(2, 3, 32, 32)).shape == (2, 10)
 
 
 def test_quantizer_policy():
