@@ -27,8 +27,10 @@ def quantize(input, bits, pack_only, group_size, act_padding, N, avg_alam, alam_
                                           pack_only=pack_only)
     if pack_only:
         out = torch.ops.act_lib.pack_triton(groups, bits, group_size)
-        return (out, None, None), (bits, pack_only, group_size, act_padding, N, G, 0, 0, False, False,
-                                   channel_mean, None, None, ori_shape)
+        # the reference records (0, 0, False, False) here although it grouped spatially,
+        # which scrambles masks on the way back; the real grouping is recorded instead
+        return (out, None, None), (bits, pack_only, group_size, act_padding, N, G, new_H, new_W, pad_elig,
+                                   reshape_elig, channel_mean, None, None, ori_shape)
     out, scaler, ema_min = torch.ops.act_lib.quant_pack_triton(groups, bits, group_size, avg_alam,
                                                                alam_bits, clamp, clamp_alpha)
     return (out, scaler, ema_min), (bits, pack_only, group_size, act_padding, N, G, new_H, new_W,
