@@ -17,6 +17,7 @@ ACT_FLAG_REF_COMPAT = 2
 ACT_FLAG_REF_CLAMP = 4
 ACT_FLAG_REF_TANH = 8
 ACT_FLAG_META_BF16 = 16
+ACT_GEMM_B_IS_NK = 1
 
 # every symbol include/act_b200.h declares, with its ctypes signature
 _vp, _i32, _i64, _u64, _f32 = (ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_uint64,
@@ -28,6 +29,9 @@ SIGNATURES = {
     "act_unpack_bits": ([_vp, _i64, _i32, _i32, _vp, _vp], _i32),
     "act_minmax": ([_vp, _i32, _i64, _i64, _vp, _vp, _vp], _i32),
     "act_calc_precision": ([_vp, _vp, _vp, _i64, ctypes.c_double], _i32),
+    "act_fp8_gemm_workspace": ([_i32, _i32, _i32, _i32], ctypes.c_size_t),
+    "act_fp8_gemm": ([_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _vp, ctypes.c_size_t, _vp], _i32),
+    "act_fp8_gemm_status": ([_vp, _i32], _i32),
     "act_strerror": ([_i32], ctypes.c_char_p),
     "act_abi_version": ([], _i32),
 }

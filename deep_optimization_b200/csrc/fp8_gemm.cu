@@ -1,0 +1,408 @@
+// FP8 (e4m3) GEMM with per-row / per-column fp32 scales and bf16 output, sm_100a:
+//     C[m,n] = bf16( (sum_k A[m,k] * B[k,n]) * sa[m] * sb[n] )
+//
+// One persistent CTA per SM, 192 threads in three roles:
+//   warp 0      TMA producer: one lane issues cp.async.bulk.tensor loads of the
+//               128x128 A tile and the 256x128 B^T tile of a k-block into a
+//               4-stage shared-memory ring (128-byte swizzle), mbarrier-tracked;
+//   warp 1      MMA issuer: one lane issues tcgen05.mma (kind::f8f6f4, M=128,
+//               N=256, K=32) with both operands from shared memory and the fp32
+//               accumulator in tensor memory; tcgen05.commit releases ring slots
+//               and hands finished accumulators to the epilogue;
+//   warps 2..5  epilogue: tcgen05.ld the accumulator (two 256-column buffers, so
+//               the next tile's MMAs overlap this tile's epilogue), apply the
+//               scales, convert to bf16, store 16-byte vectors.
+// No TMA multicast is used anywhere.  Every mbarrier wait is bounded: after the
+// limit the kernel raises an abort flag, records an error word, drains, frees
+// its tensor memory and returns.
+//
+// B is consumed K-major ([N,K], the layout of nn.Linear weights).  A [K,N]
+// operand, the layout of the reference's Triton_Linear
+// (Activation_Compression/triton_kernel/linear.py:43-95), is transposed into the
+// caller's workspace first.
+//
+// Bound: FP8 tensor throughput; flops = 2*M*N*K.
+#include <cuda.h>
+
+#include "act_common.cuh"
+
+namespace act {
+namespace gemm {
+
+constexpr int BM = 128, BN = 256, BK = 128;     // CTA tile; BK bytes = one 128-byte swizzle row
+constexpr int UMMA_K = 32;                      // K of one tcgen05.mma for 8-bit operands
+constexpr int STAGES = 4;
+constexpr int A_STAGE = BM * BK, B_STAGE = BN * BK;
+constexpr int THREADS = 192;
+constexpr int TMEM_COLS = 512;                  // two fp32 accumulators of 256 columns
+constexpr uint32_t SPIN_LIMIT = 1u << 24;       // polls of one mbarrier before giving up
+
+struct __align__(1024) Smem {
+    uint8_t a[STAGES][A_STAGE];
+    uint8_t b[STAGES][B_STAGE];
+    uint64_t full[STAGES], empty[STAGES], acc_full[2], acc_empty[2];
+    uint32_t tmem_base;
+    volatile uint32_t abort;
+};
+
+__device__ unsigned int g_gemm_error = 0;       // last abort reason (0 = none)
+
+// ---------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false (after raising the abort flag) when the barrier did
+// not flip within the limit or another role has already aborted.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, Smem* s, uint32_t code) {
+    for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (s->abort) return false;
+    }
+    s->abort = 1;
+    atomicExch(&g_gemm_error, code);
+    return false;
+}
+__device__ __forceinline__ void fence_barrier_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+                 " [%0], [%1, {%3, %4}], [%2];"
+                 :: "r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 :: "r"(smem_u32(dst_smem)), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+                 :: "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// arrives on the mbarrier once all tcgen05.mma issued so far by this thread are done
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                 :: "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+                 "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major operand tile stored as rows of 128
+// bytes with the 128-byte swizzle (what the TMA box writes): start address >> 4,
+// stride between 8-row groups 1024 bytes, descriptor version 1, layout type 2
+// (128-byte swizzle).  The leading-dimension offset is unused for this layout.
+__device__ __forceinline__ uint64_t make_kmajor_desc(const void* tile) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_u32(tile) & 0x3FFFF) >> 4);
+    d |= (uint64_t)1 << 16;                         // leading byte offset (ignored), encoded 1
+    d |= (uint64_t)(1024 >> 4) << 32;               // stride byte offset
+    d |= (uint64_t)1 << 46;                         // descriptor version
+    d |= (uint64_t)2 << 61;                         // SWIZZLE_128B
+    return d;
+}
+// Instruction descriptor: fp32 accumulate, A and B e4m3, both K-major, N>>3, M>>4.
+__host__ __device__ constexpr uint32_t make_idesc() {
+    return (1u << 4) | (0u << 7) | (0u << 10) | (0u << 15) | (0u << 16) |
+           ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+// ------------------------------------------------------------------ the kernel
+__global__ void __launch_bounds__(THREADS, 1)
+fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_bt,
+                const float* __restrict__ sa, const float* __restrict__ sb,
+                __nv_bfloat16* __restrict__ C, int M, int N, int K, int ldc)
+{
+    extern __shared__ uint8_t smem_raw[];
+    Smem* s = reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
+    const int n_work = m_tiles * n_tiles;
+    const int k_blocks = (K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < STAGES; ++i) { mbar_init(&s->full[i], 1); mbar_init(&s->empty[i], 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(&s->acc_full[i], 1); mbar_init(&s->acc_empty[i], 4); }
+        s->abort = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) tmem_alloc(&s->tmem_base, TMEM_COLS);      // whole warp, writes the base address to smem
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = s->tmem_base;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (int w = blockIdx.x; ok && w < n_work; w += gridDim.x) {
+                const int m0 = (w / n_tiles) * BM, n0 = (w % n_tiles) * BN;
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!(ok = mbar_wait(&s->empty[stage], phase ^ 1, s, 1))) break;
+                    mbar_expect_tx(&s->full[stage], A_STAGE + B_STAGE);   // out-of-range parts arrive as zeros
+                    tma_load_2d(s->a[stage], &map_a, &s->full[stage], kb * BK, m0);
+                    tma_load_2d(s->b[stage], &map_bt, &s->full[stage], kb * BK, n0);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // -------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc();
+            uint32_t stage = 0, phase = 0, acc_phase[2] = {0, 0};
+            bool ok = true;
+            int t = 0;
+            for (int w = blockIdx.x; ok && w < n_work; w += gridDim.x, ++t) {
+                const int buf = t & 1;
+                if (!(ok = mbar_wait(&s->acc_empty[buf], acc_phase[buf] ^ 1, s, 2))) break;
+                tc_fence_after();
+                const uint32_t d = tmem_base + (uint32_t)(buf * BN);
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!(ok = mbar_wait(&s->full[stage], phase, s, 3))) break;
+                    tc_fence_after();
+                    const uint64_t adesc = make_kmajor_desc(s->a[stage]);
+                    const uint64_t bdesc = make_kmajor_desc(s->b[stage]);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)      // +32 bytes along K = +2 in the address field
+                        umma_f8(d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) ? 1u : 0u);
+                    umma_commit(&s->empty[stage]);             // slot is free once these MMAs have read it
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+                umma_commit(&s->acc_full[buf]);                // accumulator complete
+                acc_phase[buf] ^= 1;
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------- epilogue
+        const int q = warp & 3;                                // TMEM lane quarter this warp may read
+        uint32_t full_phase[2] = {0, 0};
+        bool ok = true;
+        int t = 0;
+        for (int w = blockIdx.x; ok && w < n_work; w += gridDim.x, ++t) {
+            const int buf = t & 1;
+            const int m0 = (w / n_tiles) * BM, n0 = (w % n_tiles) * BN;
+            if (!(ok = mbar_wait(&s->acc_full[buf], full_phase[buf], s, 4))) break;
+            full_phase[buf] ^= 1;
+            tc_fence_after();
+            const int row = m0 + q * 32 + lane;
+            const float sa_row = row < M ? __ldg(sa + row) : 0.0f;
+            __nv_bfloat16* c_row = C + (size_t)row * ldc + n0;
+#pragma unroll 1
+            for (int chunk = 0; chunk < BN / 32; ++chunk) {
+                uint32_t r[32];
+                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + chunk * 32), r);
+                tmem_ld_wait();
+                const int col0 = n0 + chunk * 32;
+                if (row < M && col0 < N) {
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) {              // 8 columns = one 16-byte store
+                        const int col = col0 + v * 8;
+                        if (col >= N) break;
+                        const float4 s0 = __ldg(reinterpret_cast<const float4*>(sb + col));
+                        const float4 s1 = __ldg(reinterpret_cast<const float4*>(sb + col + 4));
+                        const float sc[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+                        uint32_t o[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const float lo = __fmul_rn(__fmul_rn(__uint_as_float(r[v * 8 + 2 * i]), sa_row), sc[2 * i]);
+                            const float hi = __fmul_rn(__fmul_rn(__uint_as_float(r[v * 8 + 2 * i + 1]), sa_row), sc[2 * i + 1]);
+                            const __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
+                            o[i] = *reinterpret_cast<const uint32_t*>(&p);
+                        }
+                        *reinterpret_cast<uint4*>(c_row + chunk * 32 + v * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&s->acc_empty[buf]);    // 4 epilogue warps release the buffer
+        }
+    }
+
+    // ---------------------------------------------------------------- teardown
+    if (s->abort) {
+        // give copies and MMAs still in flight time to land before the memory is released
+        for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+// ---------------------------------------------------------- [K,N] -> [N,K] bytes
+// 64x64 byte tiles through shared memory; both global sides move 4-byte words.
+__global__ void __launch_bounds__(256)
+transpose_u8_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, int K, int N, int ld_in, int ld_out)
+{
+    __shared__ uint8_t tile[64][68];                 // [n][k], padded
+    const int k0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;       // 16 x 16 threads, 4x4 bytes each
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int k = k0 + ty * 4 + i, n = n0 + tx * 4;
+        uint32_t w = 0;
+        if (k < K && n < N) w = *reinterpret_cast<const uint32_t*>(in + (size_t)k * ld_in + n);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) tile[tx * 4 + j][ty * 4 + i] = (uint8_t)(w >> (8 * j));
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int n = n0 + ty * 4 + i, k = k0 + tx * 4;
+        if (n < N && k < K)
+            *reinterpret_cast<uint32_t*>(out + (size_t)n * ld_out + k) =
+                *reinterpret_cast<const uint32_t*>(&tile[ty * 4 + i][tx * 4]);
+    }
+}
+
+}  // namespace gemm
+}  // namespace act
+
+// ------------------------------------------------------------------- host side
+namespace {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+// cuTensorMapEncodeTiled through the runtime's driver entry-point lookup, so the
+// library carries no link-time dependency on libcuda.
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// 2-D byte tensor [rows, cols] with row pitch ld, box = box_rows x 128 bytes, 128-byte swizzle
+bool make_map(CUtensorMap* map, const void* base, int rows, int cols, int ld, int box_rows) {
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld};
+    const cuuint32_t box[2] = {(cuuint32_t)act::gemm::BK, (cuuint32_t)box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int round_up(int v, int m) { return (v + m - 1) / m * m; }
+
+}  // namespace
+
+extern "C" size_t act_fp8_gemm_workspace(int M, int N, int K, int flags) {
+    (void)M;
+    if (flags & ACT_GEMM_B_IS_NK) return 0;
+    if (N <= 0 || K <= 0) return 0;
+    return (size_t)N * (size_t)round_up(K, 16);
+}
+
+extern "C" int act_fp8_gemm(const void* A, const void* B, const float* sa, const float* sb, void* C,
+                            int M, int N, int K, int lda, int ldb, int ldc, int flags,
+                            void* workspace, size_t ws_bytes, void* stream)
+{
+    using namespace act::gemm;
+    if (M < 0 || N < 0 || K < 0) return ACT_ERR_SIZE;
+    if (M == 0 || N == 0) return ACT_OK;
+    if (!A || !B || !sa || !sb || !C) return ACT_ERR_NULL;
+    const bool b_is_nk = (flags & ACT_GEMM_B_IS_NK) != 0;
+    // TMA needs 16-byte aligned bases and pitches; the epilogue stores 8 bf16 at a time
+    if (K == 0 || (K & 15) || (lda & 15) || lda < K || (N & 7) || (ldc & 7) || ldc < N) return ACT_ERR_SIZE;
+    if (b_is_nk ? ((ldb & 15) || ldb < K) : ((ldb & 3) || ldb < N || (N & 3))) return ACT_ERR_SIZE;
+    if (((uintptr_t)A | (uintptr_t)C | (uintptr_t)sb) & 15) return ACT_ERR_ALIGN;
+    if ((uintptr_t)B & (b_is_nk ? 15 : 3)) return ACT_ERR_ALIGN;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+    const uint8_t* bt = static_cast<const uint8_t*>(B);
+    int ldbt = ldb;
+    if (!b_is_nk) {
+        const size_t need = act_fp8_gemm_workspace(M, N, K, flags);
+        if (!workspace || ws_bytes < need) return ACT_ERR_WORKSPACE;
+        if ((uintptr_t)workspace & 15) return ACT_ERR_ALIGN;
+        ldbt = round_up(K, 16);
+        dim3 grid((N + 63) / 64, (K + 63) / 64);
+        transpose_u8_kernel<<<grid, 256, 0, st>>>(static_cast<const uint8_t*>(B), static_cast<uint8_t*>(workspace),
+                                                   K, N, ldb, ldbt);
+        if (cudaGetLastError() != cudaSuccess) return ACT_ERR_LAUNCH;
+        bt = static_cast<const uint8_t*>(workspace);
+    }
+
+    CUtensorMap map_a, map_bt;
+    if (!make_map(&map_a, A, M, K, lda, BM) || !make_map(&map_bt, bt, N, K, ldbt, BN)) return ACT_ERR_DEVICE;
+
+    static bool attr_set = false;
+    const int smem_bytes = (int)sizeof(Smem) + 1024;
+    if (!attr_set) {
+        if (cudaFuncSetAttribute(fp8_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess)
+            return ACT_ERR_DEVICE;
+        attr_set = true;
+    }
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    const int grid = tiles < sms ? tiles : sms;
+    fp8_gemm_kernel<<<grid, THREADS, smem_bytes, st>>>(map_a, map_bt, sa, sb, static_cast<__nv_bfloat16*>(C),
+                                                       M, N, K, ldc);
+    return cudaGetLastError() == cudaSuccess ? ACT_OK : ACT_ERR_LAUNCH;
+}
+
+// Reads (and optionally clears) the abort reason of the last GEMM on the current
+// device: 0 = none, 1..4 = which wait ran out (slot free, accumulator free, data
+// ready, accumulator ready).  Synchronises the device; for diagnostics only.
+extern "C" int act_fp8_gemm_status(unsigned int* out, int clear) {
+    if (!out) return ACT_ERR_NULL;
+    if (cudaMemcpyFromSymbol(out, act::gemm::g_gemm_error, sizeof(unsigned int)) != cudaSuccess) return ACT_ERR_DEVICE;
+    if (clear) {
+        const unsigned int zero = 0;
+        if (cudaMemcpyToSymbol(act::gemm::g_gemm_error, &zero, sizeof(zero)) != cudaSuccess) return ACT_ERR_DEVICE;
+    }
+    return ACT_OK;
+}

@@ -1,0 +1,69 @@
+"""FP8 e4m3 GEMM with per-row / per-column scales (tcgen05 kernel behind the C ABI).
+
+`fp8_gemm(A8, B8, sa, sb)` computes bf16((A8 @ B8) * sa[:,None] * sb[None,:]) for
+A8 [M,K] and B8 [K,N] (the operand layout of the reference's Triton_Linear,
+Activation_Compression/triton_kernel/linear.py:43-95) or, with `b_is_nk=True`,
+B8 given as [N,K] like an nn.Linear weight.  `quantize_e4m3` produces the
+operands and scales the way the evaluation configuration describes (amax / 448).
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+
+E4M3_MAX = 448.0
+
+
+def quantize_e4m3(x: torch.Tensor, dim: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Scale each slice along `dim` to the e4m3 range; returns (fp8 tensor, fp32 scales)."""
+    amax = x.abs().amax(dim=dim, keepdim=True).float().clamp_min(1e-12)
+    scale = amax / E4M3_MAX
+    q = (x.float() / scale).clamp(-E4M3_MAX, E4M3_MAX).to(torch.float8_e4m3fn)
+    return q, scale.squeeze(dim).contiguous()
+
+
+def workspace_bytes(M: int, N: int, K: int, b_is_nk: bool) -> int:
+    return int(_lib.load().act_fp8_gemm_workspace(M, N, K, _lib.ACT_GEMM_B_IS_NK if b_is_nk else 0))
+
+
+def fp8_gemm(A8: torch.Tensor, B8: torch.Tensor, sa: torch.Tensor, sb: torch.Tensor,
+             b_is_nk: bool = False, out: Optional[torch.Tensor] = None,
+             workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+    if not A8.is_cuda:
+        raise RuntimeError("fp8_gemm needs CUDA tensors: there is no CPU path")
+    if A8.dtype != torch.float8_e4m3fn or B8.dtype != torch.float8_e4m3fn:
+        raise TypeError("operands must be torch.float8_e4m3fn")
+    A8, B8 = A8.contiguous(), B8.contiguous()
+    M, K = A8.shape
+    N = B8.shape[0] if b_is_nk else B8.shape[1]
+    if (B8.shape[1] if b_is_nk else B8.shape[0]) != K:
+        raise ValueError("inner dimensions differ")
+    sa = sa.to(torch.float32).contiguous()
+    sb = sb.to(torch.float32).contiguous()
+    if sa.numel() != M or sb.numel() != N:
+        raise ValueError("sa must have M entries and sb N entries")
+    C = out if out is not None else torch.empty((M, N), dtype=torch.bfloat16, device=A8.device)
+    flags = _lib.ACT_GEMM_B_IS_NK if b_is_nk else 0
+    need = workspace_bytes(M, N, K, b_is_nk)
+    ws_ptr, ws_len = None, 0
+    if need:
+        if workspace is None or workspace.numel() * workspace.element_size() < need:
+            workspace = torch.empty(need, dtype=torch.uint8, device=A8.device)
+        ws_ptr, ws_len = workspace.data_ptr(), workspace.numel() * workspace.element_size()
+    with torch.cuda.device(A8.device):
+        rc = _lib.load().act_fp8_gemm(A8.data_ptr(), B8.data_ptr(), sa.data_ptr(), sb.data_ptr(), C.data_ptr(),
+                                      M, N, K, A8.stride(0), B8.stride(0), C.stride(0), flags, ws_ptr, ws_len,
+                                      torch.cuda.current_stream(A8.device).cuda_stream)
+    _lib.check(rc, "act_fp8_gemm")
+    return C
+
+
+def gemm_status(clear: bool = True) -> int:
+    """Abort reason of the last GEMM (0 = none).  Synchronises the device."""
+    import ctypes
+    v = ctypes.c_uint(0)
+    _lib.check(_lib.load().act_fp8_gemm_status(ctypes.byref(v), 1 if clear else 0), "act_fp8_gemm_status")
+    return int(v.value)

@@ -40,6 +40,9 @@ extern "C" {
 #define ACT_FLAG_REF_TANH      8   /* with REF_COMPAT: x = tanh(x/0.5)*0.5 before the range          */
 #define ACT_FLAG_META_BF16     16  /* round scale and min to bf16 precision (still stored as fp32)   */
 
+/* flags of act_fp8_gemm */
+#define ACT_GEMM_B_IS_NK 1         /* B is stored [N,K] (K contiguous, like nn.Linear weights)        */
+
 /* return codes */
 #define ACT_OK             0
 #define ACT_ERR_DTYPE      1   /* unknown element type                                   */
@@ -108,6 +111,25 @@ ACT_API int act_minmax(const void* x, int dtype, int64_t rows, int64_t cols, flo
  * b, C, w are int32 arrays of length n; b is updated in place until sum(b*w) <= target.
  */
 ACT_API int act_calc_precision(int32_t* b, const int32_t* C, const int32_t* w, int64_t n, double target);
+
+/*
+ * FP8 GEMM: C[m,n] = bf16( (sum_k A[m,k]*B[k,n]) * sa[m] * sb[n] ), A and B e4m3 bytes,
+ * fp32 accumulation in tensor memory (tcgen05), operands fed by TMA.
+ * Replaces Triton_Linear (AC/triton_kernel/linear.py:5-95), the reference's FP8-tuned
+ * tiled GEMM, and adds the per-row / per-column dequantisation scales.
+ *   A   [M,K] row-major, lda bytes per row (multiple of 16), 16-byte aligned
+ *   B   [K,N] row-major with ldb (default, the reference's layout; needs the workspace,
+ *       where it is transposed), or [N,K] with ACT_GEMM_B_IS_NK (ldb multiple of 16)
+ *   sa  fp32 [M], sb fp32 [N] (16-byte aligned), C bf16 [M,N] with ldc elements per row
+ *   K and lda multiples of 16; N and ldc multiples of 8.
+ *   workspace: act_fp8_gemm_workspace(M,N,K,flags) bytes, 16-byte aligned (may be NULL if 0).
+ */
+ACT_API size_t act_fp8_gemm_workspace(int M, int N, int K, int flags);
+ACT_API int act_fp8_gemm(const void* A, const void* B, const float* sa, const float* sb, void* C,
+                 int M, int N, int K, int lda, int ldb, int ldc, int flags,
+                 void* workspace, size_t ws_bytes, void* stream);
+/* Abort reason of the last GEMM on the current device (0 = none); synchronises. */
+ACT_API int act_fp8_gemm_status(unsigned int* out, int clear);
 
 /* Text for a return code; never NULL. */
 ACT_API const char* act_strerror(int code);
