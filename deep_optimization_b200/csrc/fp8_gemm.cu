@@ -1,7 +1,7 @@
 // FP8 (e4m3) GEMM with per-row / per-column fp32 scales and bf16 output, sm_100a:
 //     C[m,n] = bf16( (sum_k A[m,k] * B[k,n]) * sa[m] * sb[n] )
 //
-// One persistent CTA per SM, 192 threads in three roles:
+// One persistent CTA per SM, 320 threads in three roles:
 //   warp 0      TMA producer: one lane issues cp.async.bulk.tensor loads of the
 //               128x128 A tile and the 256x128 B^T tile of a k-block into a
 //               4-stage shared-memory ring (128-byte swizzle), mbarrier-tracked;
@@ -9,9 +9,10 @@
 //               N=256, K=32) with both operands from shared memory and the fp32
 //               accumulator in tensor memory; tcgen05.commit releases ring slots
 //               and hands finished accumulators to the epilogue;
-//   warps 2..5  epilogue: tcgen05.ld the accumulator (two 256-column buffers, so
-//               the next tile's MMAs overlap this tile's epilogue), apply the
-//               scales, convert to bf16, store 16-byte vectors.
+//   warps 2..9  epilogue: tcgen05.ld the accumulator (two 256-column buffers, so
+//               the next tile's MMAs overlap this tile's epilogue; loads of the
+//               next 32 columns overlap the arithmetic of the current ones),
+//               apply the scales, convert to bf16, store 16-byte vectors.
 // No TMA multicast is used anywhere.  Every mbarrier wait is bounded: after the
 // limit the kernel raises an abort flag, records an error word, drains, frees
 // its tensor memory and returns.
@@ -33,13 +34,15 @@ constexpr int BM = 128, BN = 256, BK = 128;     // CTA tile; BK bytes = one 128-
 constexpr int UMMA_K = 32;                      // K of one tcgen05.mma for 8-bit operands
 constexpr int STAGES = 4;
 constexpr int A_STAGE = BM * BK, B_STAGE = BN * BK;
-constexpr int THREADS = 192;
+constexpr int EPI_WARPS = 8;                    // two warps per TMEM lane quarter, 128 columns each
+constexpr int THREADS = 64 + EPI_WARPS * 32;
 constexpr int TMEM_COLS = 512;                  // two fp32 accumulators of 256 columns
 constexpr uint32_t SPIN_LIMIT = 1u << 24;       // polls of one mbarrier before giving up
 
 struct __align__(1024) Smem {
     uint8_t a[STAGES][A_STAGE];
     uint8_t b[STAGES][B_STAGE];
+    float sb[2][BN];                            // column scales of the tile in each accumulator buffer
     uint64_t full[STAGES], empty[STAGES], acc_full[2], acc_empty[2];
     uint32_t tmem_base;
     volatile uint32_t abort;
@@ -156,7 +159,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < STAGES; ++i) { mbar_init(&s->full[i], 1); mbar_init(&s->empty[i], 1); }
-        for (int i = 0; i < 2; ++i) { mbar_init(&s->acc_full[i], 1); mbar_init(&s->acc_empty[i], 4); }
+        for (int i = 0; i < 2; ++i) { mbar_init(&s->acc_full[i], 1); mbar_init(&s->acc_empty[i], EPI_WARPS); }
         s->abort = 0;
         fence_barrier_init();
     }
@@ -213,47 +216,63 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     } else {
         // ---------------------------------------------------------------- epilogue
         const int q = warp & 3;                                // TMEM lane quarter this warp may read
+        const int half = (warp - 2) >> 2;                      // which 128 columns of the tile
+        const int etid = threadIdx.x - 64;                     // 0..255 among the epilogue threads
         uint32_t full_phase[2] = {0, 0};
         bool ok = true;
         int t = 0;
-        for (int w = blockIdx.x; ok && w < n_work; w += gridDim.x, ++t) {
+        // Every epilogue warp walks every tile even after an abort (skipping the work), so
+        // that nobody is left waiting alone at the named barrier below.
+        for (int w = blockIdx.x; w < n_work; w += gridDim.x, ++t) {
             const int buf = t & 1;
             const int m0 = (w / n_tiles) * BM, n0 = (w % n_tiles) * BN;
-            if (!(ok = mbar_wait(&s->acc_full[buf], full_phase[buf], s, 4))) break;
-            full_phase[buf] ^= 1;
-            tc_fence_after();
+            // stage the tile's 256 column scales while the MMAs are still running
+            s->sb[buf][etid] = (n0 + etid < N) ? __ldg(sb + n0 + etid) : 0.0f;
+            asm volatile("bar.sync 1, %0;" :: "n"(EPI_WARPS * 32) : "memory");
             const int row = m0 + q * 32 + lane;
             const float sa_row = row < M ? __ldg(sa + row) : 0.0f;
-            __nv_bfloat16* c_row = C + (size_t)row * ldc + n0;
-#pragma unroll 1
-            for (int chunk = 0; chunk < BN / 32; ++chunk) {
-                uint32_t r[32];
-                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + chunk * 32), r);
+            const f32x2 sa2 = pack2(sa_row, sa_row);
+            if (ok) ok = mbar_wait(&s->acc_full[buf], full_phase[buf], s, 4);
+            if (!ok) continue;
+            full_phase[buf] ^= 1;
+            tc_fence_after();
+            const uint32_t t_base = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + half * 128);
+            __nv_bfloat16* c_row = C + (size_t)row * ldc + n0 + half * 128;
+            const float* sb_s = s->sb[buf] + half * 128;
+            uint32_t r[2][32];
+            tmem_ld32(t_base, r[0]);
+#pragma unroll
+            for (int chunk = 0; chunk < 4; ++chunk) {
                 tmem_ld_wait();
-                const int col0 = n0 + chunk * 32;
+                if (chunk + 1 < 4) tmem_ld32(t_base + (uint32_t)((chunk + 1) * 32), r[(chunk + 1) & 1]);
+                else {
+                    // the accumulator now lives in registers: hand the buffer back early
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&s->acc_empty[buf]);
+                }
+                const uint32_t* rc = r[chunk & 1];
+                const int col0 = n0 + half * 128 + chunk * 32;
                 if (row < M && col0 < N) {
 #pragma unroll
                     for (int v = 0; v < 4; ++v) {              // 8 columns = one 16-byte store
-                        const int col = col0 + v * 8;
-                        if (col >= N) break;
-                        const float4 s0 = __ldg(reinterpret_cast<const float4*>(sb + col));
-                        const float4 s1 = __ldg(reinterpret_cast<const float4*>(sb + col + 4));
-                        const float sc[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+                        if (col0 + v * 8 >= N) break;
+                        const float4 s0 = *reinterpret_cast<const float4*>(sb_s + chunk * 32 + v * 8);
+                        const float4 s1 = *reinterpret_cast<const float4*>(sb_s + chunk * 32 + v * 8 + 4);
+                        const f32x2 sc[4] = {pack2(s0.x, s0.y), pack2(s0.z, s0.w), pack2(s1.x, s1.y), pack2(s1.z, s1.w)};
                         uint32_t o[4];
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
-                            const float lo = __fmul_rn(__fmul_rn(__uint_as_float(r[v * 8 + 2 * i]), sa_row), sc[2 * i]);
-                            const float hi = __fmul_rn(__fmul_rn(__uint_as_float(r[v * 8 + 2 * i + 1]), sa_row), sc[2 * i + 1]);
-                            const __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
+                            // (acc * sa) * sb, each product rounded to fp32, two columns per instruction
+                            uint32_t lo, hi;
+                            unpack2u(mul2_rn(mul2_rn(pack2u(rc[v * 8 + 2 * i], rc[v * 8 + 2 * i + 1]), sa2), sc[i]), lo, hi);
+                            const __nv_bfloat162 p = __floats2bfloat162_rn(__uint_as_float(lo), __uint_as_float(hi));
                             o[i] = *reinterpret_cast<const uint32_t*>(&p);
                         }
                         *reinterpret_cast<uint4*>(c_row + chunk * 32 + v * 8) = make_uint4(o[0], o[1], o[2], o[3]);
                     }
                 }
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&s->acc_empty[buf]);    // 4 epilogue warps release the buffer
         }
     }
 
