@@ -43,6 +43,7 @@ struct __align__(1024) Smem {
     uint8_t a[STAGES][A_STAGE];
     uint8_t b[STAGES][B_STAGE];
     float sb[2][BN];                            // column scales of the tile in each accumulator buffer
+    uint8_t cstage[EPI_WARPS][32 * 64];         // per warp: 32 rows x 32 bf16, 16-byte pieces xor-swizzled
     uint64_t full[STAGES], empty[STAGES], acc_full[2], acc_empty[2];
     uint32_t tmem_base;
     volatile uint32_t abort;
@@ -237,7 +238,6 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             full_phase[buf] ^= 1;
             tc_fence_after();
             const uint32_t t_base = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + half * 128);
-            __nv_bfloat16* c_row = C + (size_t)row * ldc + n0 + half * 128;
             const float* sb_s = s->sb[buf] + half * 128;
             uint32_t r[2][32];
             tmem_ld32(t_base, r[0]);
@@ -253,25 +253,37 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 }
                 const uint32_t* rc = r[chunk & 1];
                 const int col0 = n0 + half * 128 + chunk * 32;
-                if (row < M && col0 < N) {
+                // scale, convert, and park the lane's 32 columns (64 bytes) in shared memory;
+                // piece v of row l sits at slot v ^ ((l >> 1) & 3): conflict-free both ways
+                uint8_t* my_stage = s->cstage[warp - 2];
 #pragma unroll
-                    for (int v = 0; v < 4; ++v) {              // 8 columns = one 16-byte store
-                        if (col0 + v * 8 >= N) break;
-                        const float4 s0 = *reinterpret_cast<const float4*>(sb_s + chunk * 32 + v * 8);
-                        const float4 s1 = *reinterpret_cast<const float4*>(sb_s + chunk * 32 + v * 8 + 4);
-                        const f32x2 sc[4] = {pack2(s0.x, s0.y), pack2(s0.z, s0.w), pack2(s1.x, s1.y), pack2(s1.z, s1.w)};
-                        uint32_t o[4];
+                for (int v = 0; v < 4; ++v) {
+                    const float4 s0 = *reinterpret_cast<const float4*>(sb_s + chunk * 32 + v * 8);
+                    const float4 s1 = *reinterpret_cast<const float4*>(sb_s + chunk * 32 + v * 8 + 4);
+                    const f32x2 sc[4] = {pack2(s0.x, s0.y), pack2(s0.z, s0.w), pack2(s1.x, s1.y), pack2(s1.z, s1.w)};
+                    uint32_t o[4];
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            // (acc * sa) * sb, each product rounded to fp32, two columns per instruction
-                            uint32_t lo, hi;
-                            unpack2u(mul2_rn(mul2_rn(pack2u(rc[v * 8 + 2 * i], rc[v * 8 + 2 * i + 1]), sa2), sc[i]), lo, hi);
-                            const __nv_bfloat162 p = __floats2bfloat162_rn(__uint_as_float(lo), __uint_as_float(hi));
-                            o[i] = *reinterpret_cast<const uint32_t*>(&p);
-                        }
-                        *reinterpret_cast<uint4*>(c_row + chunk * 32 + v * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+                    for (int i = 0; i < 4; ++i) {
+                        // (acc * sa) * sb, each product rounded to fp32, two columns per instruction
+                        uint32_t lo, hi;
+                        unpack2u(mul2_rn(mul2_rn(pack2u(rc[v * 8 + 2 * i], rc[v * 8 + 2 * i + 1]), sa2), sc[i]), lo, hi);
+                        const __nv_bfloat162 p = __floats2bfloat162_rn(__uint_as_float(lo), __uint_as_float(hi));
+                        o[i] = *reinterpret_cast<const uint32_t*>(&p);
                     }
+                    *reinterpret_cast<uint4*>(my_stage + lane * 64 + ((v ^ ((lane >> 1) & 3)) << 4)) =
+                        make_uint4(o[0], o[1], o[2], o[3]);
                 }
+                __syncwarp();
+                // write-out: each instruction covers 8 rows x 64 contiguous bytes (full sectors)
+#pragma unroll
+                for (int jj = 0; jj < 4; ++jj) {
+                    const int rl = jj * 8 + (lane >> 2), piece = lane & 3;
+                    const int grow = m0 + q * 32 + rl, gcol = col0 + piece * 8;
+                    const uint4 d = *reinterpret_cast<const uint4*>(my_stage + rl * 64 + ((piece ^ ((rl >> 1) & 3)) << 4));
+                    if (grow < M && gcol < N)
+                        *reinterpret_cast<uint4*>(C + (size_t)grow * ldc + gcol) = d;
+                }
+                __syncwarp();
             }
         }
     }
