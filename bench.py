@@ -36,8 +36,8 @@ ROTATE = 4                      # distinct buffer sets cycled through: working s
 METRIC = "act_quant_pack_unpack_GBps"
 UNIT = "GB/s"
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the pack kernel on this
-# workload, from an ncu capture (see profiles/); None until a capture exists.
-NCU_PACK_TRAFFIC_BYTES = None
+# workload, from the ncu capture summarised under profiles/.
+NCU_PACK_TRAFFIC_BYTES = 108_960_000      # profiles/quant_pack_bf16_g128_b2_ncu.md (mean of 2 launches)
 
 
 def algorithmic_bytes(n_elems: int, group: int, bits: int, elem_bytes: int):
@@ -67,7 +67,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                 "-lms", "100", "-i", str(self.index)],
+                 "-lms", "20", "-i", str(self.index)],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -103,7 +103,8 @@ class ClockSampler:
         return {"sm_mhz": sm[len(sm) // 2] if sm else None,
                 "sm_max_mhz": max(mx) if mx else None,
                 "power_w_max": max(power) if power else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "samples": len(sm), "reasons": sorted(reasons),
+                "note": "sampled every 20 ms over the timed region and an identical untimed continuation"}
 
 
 def load_peaks():
@@ -170,6 +171,62 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def _time_launches(fn, reps):
+    import torch
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(reps):
+        fn(i)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / reps
+
+
+def run_extras(dev):
+    """Untimed-region extras on rank 0: the fp32 configuration of the codec and the three
+    FP8 GEMM shapes.  Each number is the mean of back-to-back launches between two CUDA
+    events on the launch stream, buffers rotated so inputs do not sit in L2."""
+    import torch
+    from deep_optimization_b200 import codec
+    from deep_optimization_b200.gemm import fp8_gemm, quantize_e4m3
+    peak, _ = load_peaks()
+    out = {}
+    # fp32 [128,64,56,56], group 256, 2 bits
+    shape, gs, bits, rot = (128, 64, 56, 56), 256, 2, 4
+    n = 128 * 64 * 56 * 56
+    xs = [torch.relu(torch.randn(shape, device=dev)) for _ in range(rot)]
+    outs = [(torch.empty((n // gs, gs * bits // 32), dtype=torch.int32, device=dev),
+             torch.empty(n // gs, device=dev), torch.empty(n // gs, device=dev)) for _ in range(rot)]
+    ys = [torch.empty((n // gs, gs), device=dev) for _ in range(rot)]
+    pb, ub = algorithmic_bytes(n, gs, bits, 4)
+    tp = _time_launches(lambda i=0: codec.quant_pack(xs[i % rot], bits, gs, seed=3, offset=i, out=outs[i % rot]), 40)
+    tu = _time_launches(lambda i=0: codec.dequant_unpack(*outs[i % rot], bits, gs, out_dtype=torch.float32, out=ys[i % rot]), 40)
+    out["codec_fp32_128x64x56x56_g256_b2"] = {
+        "pack_GBps": pb / tp / 1e6, "pack_frac": pb / tp / 1e6 / peak,
+        "unpack_GBps": ub / tu / 1e6, "unpack_frac": ub / tu / 1e6 / peak,
+        "pack_plus_unpack_frac": (pb + ub) / (tp + tu) / 1e6 / peak}
+    del xs, outs, ys
+    # FP8 GEMM shapes (M, K, N); peak = nominal dense FP8 of a B200
+    gem = {}
+    for (M, K, N) in ((8192, 4096, 4096), (50432, 768, 3072), (50432, 3072, 768)):
+        A8, sa = quantize_e4m3(torch.randn(M, K, device=dev), 1)
+        B8, sb = quantize_e4m3(torch.randn(K, N, device=dev), 0)
+        C = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+        ws = torch.empty(N * K, dtype=torch.uint8, device=dev)
+        t = _time_launches(lambda i=0: fp8_gemm(A8, B8, sa, sb, out=C, workspace=ws), 20)
+        Bt = B8.t().contiguous()
+        t_nk = _time_launches(lambda i=0: fp8_gemm(A8, Bt, sa, sb, b_is_nk=True, out=C), 20)
+        fl = 2.0 * M * N * K
+        gem[f"M{M}_K{K}_N{N}"] = {"TFLOPs_B_kn": fl / t / 1e9, "TFLOPs_B_nk": fl / t_nk / 1e9,
+                                   "frac_of_nominal_fp8_4500": fl / t_nk / 1e9 / 4500.0}
+        del A8, B8, C, ws, Bt
+    out["fp8_gemm"] = gem
+    return out
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -231,6 +288,16 @@ def run_ours(args):
         codec.dequant_unpack(*outs[k], BITS, GROUP, out_dtype=torch.bfloat16, out=ys[k])
         ev[i][2].record()
     barrier()
+    if rank == 0:
+        # the timed region is short; keep the same load running (untimed) until the
+        # sampler has at least half a second of samples under load
+        t_end = time.perf_counter() + 0.5
+        i = K
+        while time.perf_counter() < t_end:
+            for _ in range(50):
+                step(i)
+                i += 1
+            torch.cuda.synchronize()
     total_ms = ev[0][0].elapsed_time(ev[K - 1][2])
     pack_ms = sum(e[0].elapsed_time(e[1]) for e in ev) / K
     unpack_ms = sum(e[1].elapsed_time(e[2]) for e in ev) / K
@@ -259,6 +326,10 @@ def run_ours(args):
     e1.record()
     barrier()
     e2e_ms = e0.elapsed_time(e1) / KE
+
+    extras = None
+    if rank == 0 and not args.no_extras:
+        extras = run_extras(dev)
 
     # ---- max over ranks ----------------------------------------------------------
     t = torch.tensor([total_ms, e2e_ms, pack_ms, unpack_ms], device=dev, dtype=torch.float64)
@@ -294,6 +365,8 @@ def run_ours(args):
             "gpu_launches": 2 * K,
             "clocks": clocks,
         }
+        if extras is not None:
+            line["other_configs"] = extras
         if world == 1 and not args.no_cpu_baseline:
             cores = os.cpu_count() or 1
             v, sample = cpu_baseline(host[0], cores)
@@ -312,6 +385,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="skip the fp32 codec and GEMM side measurements")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
