@@ -46,6 +46,7 @@ extern "C" const char* act_strerror(int code) {
         case ACT_ERR_DEVICE: return "device is not sm_100 or a driver entry point is missing";
         case ACT_ERR_TARGET: return "calc_precision: target cannot be reached";
         case ACT_ERR_UNSUPPORTED: return "flag combination not supported";
+        case ACT_ERR_STATIC_LIMIT: return "problem too large for the built-in scratch of act_fp8_gemm_static (N*K over 4 MiB)";
         default: return "unknown error code";
     }
 }

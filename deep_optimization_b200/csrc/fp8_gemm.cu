@@ -437,3 +437,38 @@ extern "C" int act_fp8_gemm_status(unsigned int* out, int clear) {
     }
     return ACT_OK;
 }
+
+// ------------------------------------------------- entry point that allocates nothing
+// Some callers of this library run where device memory cannot be requested at call
+// time: a plugin invoked from inside another framework's memory plan (all device
+// memory already handed out), a real-time loop whose rules forbid allocator calls
+// because their latency is unbounded.  For them the [K,N] -> [N,K] staging
+// buffer of the GEMM lives in the library image itself.  The array below is part of
+// every device's copy of the module from load until exit (4 MiB per GPU).
+constexpr size_t kStaticScratchBytes = 4u << 20;
+static __device__ __align__(256) uint8_t g_static_bt_scratch[kStaticScratchBytes];
+
+// Device address of the array on each device, looked up on first use.  In host code
+// the array's name is only a handle for this lookup, never a pointer to pass along.
+static uint8_t* g_static_scratch_ptr[64];
+
+extern "C" size_t act_fp8_gemm_static_limit(void) { return kStaticScratchBytes; }
+
+extern "C" int act_fp8_gemm_static(const void* A, const void* B, const float* sa, const float* sb, void* C,
+                                   int M, int N, int K, int lda, int ldb, int ldc, void* stream)
+{
+    if (M < 0 || N < 0 || K < 0) return ACT_ERR_SIZE;
+    if ((size_t)N * (size_t)round_up(K > 0 ? K : 1, 16) > kStaticScratchBytes) return ACT_ERR_STATIC_LIMIT;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return ACT_ERR_DEVICE;
+    uint8_t* scratch = g_static_scratch_ptr[dev];
+    if (!scratch) {
+        // once per device, with that device current (it is: cudaGetDevice just said so)
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_static_bt_scratch) != cudaSuccess || !p) return ACT_ERR_DEVICE;
+        scratch = static_cast<uint8_t*>(p);
+        g_static_scratch_ptr[dev] = scratch;
+    }
+    // B in the [K,N] layout; the shared array is the workspace of the ordinary entry point
+    return act_fp8_gemm(A, B, sa, sb, C, M, N, K, lda, ldb, ldc, 0, scratch, kStaticScratchBytes, stream);
+}

@@ -56,6 +56,7 @@ extern "C" {
 #define ACT_ERR_DEVICE     9   /* not an sm_100 device, or a driver entry point missing  */
 #define ACT_ERR_TARGET    10   /* act_calc_precision: target cannot be reached           */
 #define ACT_ERR_UNSUPPORTED 11 /* flag combination not built                             */
+#define ACT_ERR_STATIC_LIMIT 12 /* act_fp8_gemm_static: N*K exceeds the built-in scratch */
 
 /*
  * Per-group quantise-and-pack of a saved activation.
@@ -128,6 +129,21 @@ ACT_API size_t act_fp8_gemm_workspace(int M, int N, int K, int flags);
 ACT_API int act_fp8_gemm(const void* A, const void* B, const float* sa, const float* sb, void* C,
                  int M, int N, int K, int lda, int ldb, int ldc, int flags,
                  void* workspace, size_t ws_bytes, void* stream);
+/*
+ * The same GEMM for callers that must not allocate device memory (no counterpart in the
+ * reference; B is always [K,N]).  Its transpose scratch is a 4 MiB array built into the
+ * library, so it needs no workspace and calls no allocator, but N * K (K rounded up to 16)
+ * must not exceed act_fp8_gemm_static_limit() bytes; larger problems return
+ * ACT_ERR_STATIC_LIMIT.  The first call on each device looks the array's address up:
+ * make that call before starting any stream capture.  All calls on a device share the one
+ * array, so two calls whose GPU work can overlap (different streams) race on it; keep them
+ * on one stream or order them with events.  The array holds the previous call's bytes
+ * between calls; every call overwrites the part it reads.
+ */
+ACT_API size_t act_fp8_gemm_static_limit(void);
+ACT_API int act_fp8_gemm_static(const void* A, const void* B, const float* sa, const float* sb, void* C,
+                        int M, int N, int K, int lda, int ldb, int ldc, void* stream);
+
 /* Abort reason of the last GEMM on the current device (0 = none); synchronises. */
 ACT_API int act_fp8_gemm_status(unsigned int* out, int clear);
 
