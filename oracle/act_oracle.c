@@ -36,10 +36,14 @@
  * truncation toward zero, bf16-rounded scale and min.
  *
  * PARITY STATUS: the reference holds no golden vectors for this path.  The
- * reference-compatible scheme is pinned by outputs of the reference's own
- * kernels run under Triton's CPU interpreter (tests/golden).  The baseline
- * scheme shares layout and clamp/degenerate rules with it; its division and
- * noise arithmetic are pinned by no reference test ("parity unpinned").
+ * reference-compatible scheme (word layout, clamp, degenerate-range rule,
+ * rounding rule, group minimum, mask pack/unpack) is pinned bit-for-bit by
+ * outputs of the reference's own kernels run under Triton's CPU interpreter
+ * (tests/golden/reference_triton_codec.npz and the script beside it).  The
+ * baseline scheme shares layout and clamp/degenerate rules with it; its true
+ * division, noise and counter hash have no counterpart in any reference test:
+ * for those the parity is unpinned by the reference and rests on the two
+ * independent restatements (C and numpy) agreeing.
  *
  * Build: gcc -O2 -ffp-contract=off -fopenmp -shared -fPIC (see Makefile).
  */

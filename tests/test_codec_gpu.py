@@ -180,3 +180,25 @@ def test_empty_input(cuda_device):
     p, s, m = c.quant_pack(torch.empty((0, 128), device=cuda_device), 2, 128)
     assert p.shape == (0, 8) and s.numel() == 0
     assert c.dequant_unpack(p, s, m, 2, 128).shape == (0, 128)
+
+
+@pytest.mark.parametrize("bits", BITS)
+@pytest.mark.parametrize("gs", (64, 256))
+def test_cuda_against_reference_fixtures(oracle, cuda_device, bits, gs):
+    """The CUDA kernels in reference-compatible mode against outputs of the reference's own
+    Triton kernels (tests/golden/reference_triton_codec.npz, made under the CPU interpreter)."""
+    import os
+    fix = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "reference_triton_codec.npz"))
+    key = f"b{bits}_g{gs}"
+    x = torch.from_numpy(fix[key + "_x"].view(np.int16)).view(torch.bfloat16).to(cuda_device)
+    F = oracle
+    c = _codec()
+    for tag, flags, alpha in (("identity_n", F.FLAG_REF_COMPAT | F.FLAG_META_BF16, 0.0),
+                              ("identity_c", F.FLAG_REF_COMPAT | F.FLAG_META_BF16 | F.FLAG_REF_CLAMP, 1.0)):
+        packed, scale, mn = c.quant_pack(x, bits, gs, flags=flags, clamp_alpha=alpha)
+        assert np.array_equal(packed.cpu().numpy().view(np.uint32), fix[f"{key}_{tag}_packed"]), tag
+        assert np.array_equal(oracle.f32_to_bf16_bits(mn.cpu().numpy()), fix[f"{key}_{tag}_min"]), tag
+    mask = torch.from_numpy(fix[key + "_mask"]).to(cuda_device)
+    pk = c.pack_bits(mask, bits, gs)
+    assert np.array_equal(pk.cpu().numpy().view(np.uint32), fix[key + "_mask_packed"])
+    assert np.array_equal(c.unpack_bits(pk, bits, mask.shape[0], gs).cpu().numpy(), fix[key + "_mask_unpacked"])
