@@ -227,6 +227,66 @@ def run_extras(dev):
     return out
 
 
+def run_train(name, dev, world, local, steps=8, warmup=3, act=True, batch=256):
+    """One end-to-end configuration: `name` in (resnet50, vit_b16), ACT 2-bit on every
+    supported layer whose activation exceeds 10 MiB, bf16 autocast, batch 256 per GPU of
+    synthetic N(0,1) images with uniform labels, DDP (NCCL all-reduce) when world > 1.
+    Returns images/s over all ranks (device-timed, max over ranks) and peak memory."""
+    import torch
+    import torch.distributed as dist
+    from torch import nn
+    from deep_optimization_b200 import codec
+    from deep_optimization_b200.controller import Controller
+    from deep_optimization_b200.payload import resnet50, vit_b16
+    torch.manual_seed(0)
+    model = (resnet50() if name == "resnet50" else vit_b16()).to(dev)
+    if act:
+        cfg = dict(default_bits=2, auto_precision=None, batch_size=batch)
+        net = Controller(model, cfg, input_shape=(3, 224, 224), test=False, device=dev).traced_model
+    else:
+        net = model.train()
+    if world > 1:
+        net = nn.parallel.DistributedDataParallel(net, device_ids=[local], static_graph=True,
+                                                  bucket_cap_mb=25, broadcast_buffers=False)
+    if name == "resnet50":
+        opt = torch.optim.SGD(net.parameters(), lr=0.1, momentum=0.9)
+    else:
+        opt = torch.optim.AdamW(net.parameters(), lr=1e-3)
+    g = torch.Generator(device=dev).manual_seed(1234 + local)
+    x = torch.randn((batch, 3, 224, 224), device=dev, generator=g).to(torch.bfloat16)
+    y = torch.randint(0, 1000, (batch,), device=dev, generator=g)
+    codec.manual_seed(99)
+    torch.cuda.reset_peak_memory_stats(dev)
+
+    def one_step():
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            loss = nn.functional.cross_entropy(net(x), y)
+        opt.zero_grad(set_to_none=True)
+        loss.backward()
+        opt.step()
+        return loss
+
+    for _ in range(warmup):
+        one_step()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        loss = one_step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = torch.tensor([e0.elapsed_time(e1) / steps], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    out = {"img_per_s": batch * world / (ms.item() * 1e-3), "ms_per_step": ms.item(),
+           "peak_mem_GB": torch.cuda.max_memory_allocated(dev) / 2 ** 30, "final_loss": float(loss)}
+    del net, opt, model
+    torch.cuda.empty_cache()
+    return out
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -330,6 +390,14 @@ def run_ours(args):
     extras = None
     if rank == 0 and not args.no_extras:
         extras = run_extras(dev)
+    train = None
+    if not args.no_train:
+        # every rank takes part: these are the data-parallel end-to-end configurations
+        train = {"config": "batch 256 per GPU, bf16 autocast, synthetic images, ACT 2-bit via Controller",
+                 "resnet50_act2bit": run_train("resnet50", dev, world, local),
+                 "resnet50_no_act": run_train("resnet50", dev, world, local, act=False),
+                 "vit_b16_act2bit": run_train("vit_b16", dev, world, local),
+                 "vit_b16_no_act": run_train("vit_b16", dev, world, local, act=False)}
 
     # ---- max over ranks ----------------------------------------------------------
     t = torch.tensor([total_ms, e2e_ms, pack_ms, unpack_ms], device=dev, dtype=torch.float64)
@@ -367,6 +435,8 @@ def run_ours(args):
         }
         if extras is not None:
             line["other_configs"] = extras
+        if train is not None:
+            line["train"] = train
         if world == 1 and not args.no_cpu_baseline:
             cores = os.cpu_count() or 1
             v, sample = cpu_baseline(host[0], cores)
@@ -386,6 +456,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the fp32 codec and GEMM side measurements")
+    ap.add_argument("--no-train", action="store_true", help="skip the ResNet-50 / ViT-B/16 training steps")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
