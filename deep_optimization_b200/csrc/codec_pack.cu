@@ -168,8 +168,13 @@ __device__ __forceinline__ void encode_piece_fast(const float* xf8, const float*
         const f32x2 q2 = div_by_scale2(a2, ns2, y2);
         f32x2 t2;
         if (NM == kNoiseHash) {
-            const f32x2 uf2 = sub2_rn(pack2u(__byte_perm(hw[p], kMagicBits, 0x7410),
-                                             __byte_perm(hw[p], kMagicBits, 0x7432)), magic2);
+            // 16-bit fields -> floats on the conversion unit (keeps the ALU and FMA pipes free)
+            unsigned short h0, h1;
+            asm("mov.b32 {%0, %1}, %2;" : "=h"(h0), "=h"(h1) : "r"(hw[p]));
+            float u0, u1;
+            asm("cvt.rn.f32.u16 %0, %1;" : "=f"(u0) : "h"(h0));
+            asm("cvt.rn.f32.u16 %0, %1;" : "=f"(u1) : "h"(h1));
+            const f32x2 uf2 = pack2(u0, u1);
             t2 = fma2_rn(uf2, pack2(0x1p-16f, 0x1p-16f), q2);        // exact u, one rounding
         } else if (NM == kNoiseTensor) {
             // caller-supplied noise may lie outside [0,1) or be NaN: clamp t to [0,QMAX]
