@@ -18,6 +18,7 @@ ACT_FLAG_REF_CLAMP = 4
 ACT_FLAG_REF_TANH = 8
 ACT_FLAG_META_BF16 = 16
 ACT_GEMM_B_IS_NK = 1
+ACT_KIND_GELU, ACT_KIND_SILU = 1, 2
 
 # every symbol include/act_b200.h declares, with its ctypes signature
 _vp, _i32, _i64, _u64, _f32 = (ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_uint64,
@@ -27,6 +28,10 @@ SIGNATURES = {
     "act_dequant_unpack": ([_vp, _vp, _vp, _i64, _i32, _i32, _i32, _vp, _vp], _i32),
     "act_pack_bits": ([_vp, _i64, _i32, _i32, _vp, _vp], _i32),
     "act_unpack_bits": ([_vp, _i64, _i32, _i32, _vp, _vp], _i32),
+    "act_activation_fwd_quant_pack": ([_vp, _i32, _i32, _i64, _i32, _i32, _u64, _u64, _i32, _vp, _vp, _vp, _vp, _vp], _i32),
+    "act_relu_fwd_pack": ([_vp, _i32, _i64, _i32, _vp, _vp, _vp], _i32),
+    "act_relu_bwd_unpack": ([_vp, _vp, _i32, _i64, _vp, _vp], _i32),
+    "act_mul_dequant_unpack": ([_vp, _vp, _vp, _vp, _i32, _i64, _i32, _i32, _vp, _vp], _i32),
     "act_minmax": ([_vp, _i32, _i64, _i64, _vp, _vp, _vp], _i32),
     "act_calc_precision": ([_vp, _vp, _vp, _i64, ctypes.c_double], _i32),
     "act_fp8_gemm_workspace": ([_i32, _i32, _i32, _i32], ctypes.c_size_t),

@@ -118,3 +118,102 @@ def unpack_triton(packed: torch.Tensor, bits: int, N: int, G: int, group_size: i
 @unpack_triton.register_fake
 def _(packed, bits, N, G, group_size):
     return packed.new_empty((N, G, group_size), dtype=torch.int8)
+
+
+# ---- fused activation operators (Activation_Compression/modules/activations/
+# kernel_registration.py:43-94, 148-237, 262-319): same names, schemas and return orders ----
+
+@torch.library.custom_op("act_lib::relu_fwd_fused_pack", mutates_args=(), device_types="cuda")
+def relu_fwd_fused_pack(x: torch.Tensor, relu: bool, relu6: bool, bits: int,
+                        group_size: int) -> Tuple[torch.Tensor, torch.Tensor, int, int]:
+    if bits != 1:
+        raise ValueError("the fused ReLU mask is 1 bit per element")
+    N = x.shape[0]
+    G = x.numel() // N // group_size
+    y, packed = codec.relu_fwd_pack(x, relu6=(relu6 and not relu))
+    return y, packed.view(N * G, group_size // 32), N, G
+
+
+@relu_fwd_fused_pack.register_fake
+def _(x, relu, relu6, bits, group_size):
+    N = x.shape[0]
+    G = x.numel() // N // group_size
+    return torch.empty_like(x), x.new_empty((N * G, group_size // 32), dtype=torch.int32), N, G
+
+
+@torch.library.custom_op("act_lib::relu_bwd_fused_unpack", mutates_args=(), device_types="cuda")
+def relu_bwd_fused_unpack(packed: torch.Tensor, dy: torch.Tensor, bits: int, N: int, G: int,
+                          group_size: int) -> torch.Tensor:
+    return codec.relu_bwd_unpack(packed, dy)
+
+
+@relu_bwd_fused_unpack.register_fake
+def _(packed, dy, bits, N, G, group_size):
+    return torch.empty_like(dy)
+
+
+def _fused_act_fwd(x, kind, bits, group_size):
+    N = x.shape[0]
+    G = x.numel() // N // group_size
+    flags = _lib.ACT_FLAG_ROUND_NEAREST if _MODE != "baseline" else 0
+    y, packed, scale, mn = codec.activation_fwd_quant_pack(x, kind, bits, group_size, flags=flags)
+    return y, packed, scale.view(N, G), mn.view(N, G), N, G
+
+
+def _fused_act_fake(x, bits, group_size):
+    N = x.shape[0]
+    G = x.numel() // N // group_size
+    _, nwords, _ = _bits_consts(bits, group_size)
+    return (torch.empty_like(x), x.new_empty((N * G, nwords), dtype=torch.int32),
+            x.new_empty((N, G), dtype=torch.float32), x.new_empty((N, G), dtype=torch.float32), N, G)
+
+
+@torch.library.custom_op("act_lib::gelu_fwd_fused_quan_pack", mutates_args=(), device_types="cuda")
+def gelu_fwd_fused_quan_pack(x: torch.Tensor, bits: int, group_size: int
+                             ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, int, int]:
+    return _fused_act_fwd(x, "gelu", bits, group_size)
+
+
+@gelu_fwd_fused_quan_pack.register_fake
+def _(x, bits, group_size):
+    return _fused_act_fake(x, bits, group_size)
+
+
+@torch.library.custom_op("act_lib::gelu_bwd_fused_dequan_unpack", mutates_args=(), device_types="cuda")
+def gelu_bwd_fused_dequan_unpack(packed: torch.Tensor, dy: torch.Tensor, scale: torch.Tensor,
+                                 min: torch.Tensor, bits: int, N: int, G: int, group_size: int) -> torch.Tensor:
+    return codec.mul_dequant_unpack(packed, scale.reshape(-1), min.reshape(-1), dy, bits, group_size)
+
+
+@gelu_bwd_fused_dequan_unpack.register_fake
+def _(packed, dy, scale, min, bits, N, G, group_size):
+    return torch.empty_like(dy)
+
+
+@torch.library.custom_op("act_lib::silu_fwd_quan_pack", mutates_args=(), device_types="cuda")
+def silu_fwd_quan_pack(input: torch.Tensor, bits: int, group_size: int, pack_only: bool, avg_alam: bool,
+                       alam_bits: int) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, int,
+                                                int, int, int, bool, bool]:
+    _no_alam(avg_alam)
+    y, packed, scale, mn, N, G = _fused_act_fwd(input, "silu", bits, group_size)
+    return y, packed, scale, mn, N, G, 0, 0, False, False          # flat grouping
+
+
+@silu_fwd_quan_pack.register_fake
+def _(input, bits, group_size, pack_only, avg_alam, alam_bits):
+    return _fused_act_fake(input, bits, group_size) + (0, 0, False, False)
+
+
+@torch.library.custom_op("act_lib::silu_bwd_fused_dequan_unpack", mutates_args=(), device_types="cuda")
+def silu_bwd_fused_dequan_unpack(act_packed: torch.Tensor, dy: torch.Tensor, scale: torch.Tensor,
+                                 min: torch.Tensor, bits: int, N: int, G: int, group_size: int,
+                                 pack_only: bool, new_H: int, new_W: int, spatical_padding_eligibility: bool,
+                                 spatical_reshape_eligibility: bool, avg_alam: bool, alam_bits: int) -> torch.Tensor:
+    _no_alam(avg_alam)
+    return codec.mul_dequant_unpack(act_packed, scale.reshape(-1), min.reshape(-1), dy, bits, group_size)
+
+
+@silu_bwd_fused_dequan_unpack.register_fake
+def _(act_packed, dy, scale, min, bits, N, G, group_size, pack_only, new_H, new_W,
+      spatical_padding_eligibility, spatical_reshape_eligibility, avg_alam, alam_bits):
+    return torch.empty_like(dy)

@@ -168,3 +168,76 @@ def calc_precision(b: torch.Tensor, C: torch.Tensor, w: torch.Tensor, target: fl
                                         float(target))
     _lib.check(rc, "act_calc_precision")
     return b
+
+
+# ---------------------------------------------------------------- fused activation kernels
+
+def relu_fwd_pack(x: torch.Tensor, relu6: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+    """y = relu(x) (or the ReLU6 window) and the 1-bit mask as int32 words, one pass."""
+    _require_cuda(x, "x")
+    x = x.contiguous()
+    if x.numel() % 32:
+        raise ValueError("numel must be a multiple of 32")
+    y = torch.empty_like(x)
+    bits = torch.empty((x.numel() // 32,), dtype=torch.int32, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = _lib.load().act_relu_fwd_pack(x.data_ptr(), _DTYPES[x.dtype], x.numel(), int(relu6),
+                                           y.data_ptr(), bits.data_ptr(), _stream_ptr(x))
+    _lib.check(rc, "act_relu_fwd_pack")
+    return y, bits
+
+
+def relu_bwd_unpack(mask_bits: torch.Tensor, dy: torch.Tensor) -> torch.Tensor:
+    """dx = mask ? dy : 0."""
+    _require_cuda(dy, "dy")
+    dy = dy.contiguous()
+    dx = torch.empty_like(dy)
+    with torch.cuda.device(dy.device):
+        rc = _lib.load().act_relu_bwd_unpack(mask_bits.data_ptr(), dy.data_ptr(), _DTYPES[dy.dtype],
+                                             dy.numel(), dx.data_ptr(), _stream_ptr(dy))
+    _lib.check(rc, "act_relu_bwd_unpack")
+    return dx
+
+
+def activation_fwd_quant_pack(x: torch.Tensor, kind: str, bits: int, group_size: int,
+                              seed: Optional[int] = None, offset: Optional[int] = None, flags: int = 0):
+    """y = gelu/silu(x) and the packed derivative: (y, packed, scale, min)."""
+    global _next_offset
+    _, nwords, _ = _bits_consts(bits, group_size)
+    _require_cuda(x, "x")
+    x = x.contiguous()
+    if x.numel() % group_size:
+        raise ValueError("numel must be a multiple of group_size")
+    ng = x.numel() // group_size
+    y = torch.empty_like(x)
+    packed = torch.empty((ng, nwords), dtype=torch.int32, device=x.device)
+    scale = torch.empty((ng,), dtype=torch.float32, device=x.device)
+    mn = torch.empty((ng,), dtype=torch.float32, device=x.device)
+    if seed is None:
+        seed = _default_seed
+    if offset is None:
+        offset = _next_offset
+        _next_offset += 1
+    k = {"gelu": _lib.ACT_KIND_GELU, "silu": _lib.ACT_KIND_SILU}[kind]
+    with torch.cuda.device(x.device):
+        rc = _lib.load().act_activation_fwd_quant_pack(
+            x.data_ptr(), _DTYPES[x.dtype], k, ng, group_size, bits, seed & 0xFFFFFFFFFFFFFFFF,
+            offset & 0xFFFFFFFFFFFFFFFF, flags, y.data_ptr(), packed.data_ptr(), scale.data_ptr(),
+            mn.data_ptr(), _stream_ptr(x))
+    _lib.check(rc, "act_activation_fwd_quant_pack")
+    return y, packed, scale, mn
+
+
+def mul_dequant_unpack(packed: torch.Tensor, scale: torch.Tensor, mn: torch.Tensor, dy: torch.Tensor,
+                       bits: int, group_size: int) -> torch.Tensor:
+    """dx = dy * (code * scale + min): backward of an activation whose derivative was packed."""
+    _bits_consts(bits, group_size)
+    _require_cuda(dy, "dy")
+    dy = dy.contiguous()
+    dx = torch.empty_like(dy)
+    with torch.cuda.device(dy.device):
+        rc = _lib.load().act_mul_dequant_unpack(packed.data_ptr(), scale.data_ptr(), mn.data_ptr(),
+                                                dy.data_ptr(), _DTYPES[dy.dtype], dy.numel() // group_size,
+                                                group_size, bits, dx.data_ptr(), _stream_ptr(dy))
+    _lib.check(rc, "act_mul_dequant_unpack")
+    return dx

@@ -252,12 +252,39 @@ __device__ __forceinline__ void encode_piece_ref(const float* xf8, float mn, flo
     }
 }
 
-template <int DT, int BITS, int NM>
+// PRO selects a producer fused in front of the codec: kProNone quantises x itself;
+// kProGelu / kProSilu write y = act(x) to y_out and quantise the activation's derivative
+// (what backward multiplies dy with), replacing the reference's fused forward kernels
+// (Activation_Compression/modules/activations/kernel_implementation.py:184-342, 468-559).
+enum Producer { kProNone = 0, kProGelu = 1, kProSilu = 2 };
+
+__device__ __forceinline__ float tanh_fast(float v) {
+    float r; asm("tanh.approx.f32 %0, %1;" : "=f"(r) : "f"(v)); return r;
+}
+
+// y and dy/dx of the activation at x (fp32; the transcendental is the hardware approximation)
+template <int PRO>
+__device__ __forceinline__ void act_and_derivative(float x, float& y, float& d) {
+    if (PRO == kProGelu) {
+        const float k = 0.7978845608028654f, c = 0.044715f;
+        const float x2 = x * x;
+        const float th = tanh_fast(k * (x + c * x2 * x));
+        y = 0.5f * x * (1.0f + th);
+        d = 0.5f * (1.0f + th) + 0.5f * x * (1.0f - th * th) * k * (1.0f + 3.0f * c * x2);
+    } else {
+        const float sig = __fdividef(1.0f, 1.0f + __expf(-x));
+        y = x * sig;
+        d = sig * (1.0f + x * (1.0f - sig));
+    }
+}
+
+template <int DT, int BITS, int NM, int PRO = kProNone>
 __global__ void __launch_bounds__(kPackThreads, 3)
 quant_pack_kernel(const void* __restrict__ x_, const float* __restrict__ noise,
                   uint8_t* __restrict__ packed, float* __restrict__ scale_out,
                   float* __restrict__ min_out, int64_t n_elems, int log2_L,
-                  uint32_t key_lo, uint32_t key_hi, int flags, float clamp_alpha)
+                  uint32_t key_lo, uint32_t key_hi, int flags, float clamp_alpha,
+                  uint8_t* __restrict__ y_out = nullptr)
 {
     constexpr int QMAX = (1 << BITS) - 1;
     constexpr int TILE_OUT = kTileElems * BITS / 8;          // packed bytes per tile
@@ -300,6 +327,31 @@ quant_pack_kernel(const void* __restrict__ x_, const float* __restrict__ noise,
             }
         }
 
+        if (PRO != kProNone) {
+            // fused producer: emit y = act(x), keep the derivative for the codec
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                float yv[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) act_and_derivative<PRO>(xf[k * 8 + i], yv[i], xf[k * 8 + i]);
+                if (valid) {
+                    const int64_t e = group_e0 + (int64_t)((k << log2_L) + j) * 8;
+                    if (DT == ACT_DTYPE_F32) {
+                        stg_stream_v4(y_out + e * 4, make_uint4(__float_as_uint(yv[0]), __float_as_uint(yv[1]), __float_as_uint(yv[2]), __float_as_uint(yv[3])));
+                        stg_stream_v4(y_out + e * 4 + 16, make_uint4(__float_as_uint(yv[4]), __float_as_uint(yv[5]), __float_as_uint(yv[6]), __float_as_uint(yv[7])));
+                    } else {
+                        uint32_t o[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            if (DT == ACT_DTYPE_BF16) { const __nv_bfloat162 t = __floats2bfloat162_rn(yv[2 * i], yv[2 * i + 1]); o[i] = *reinterpret_cast<const uint32_t*>(&t); }
+                            else { const __half2 t = __floats2half2_rn(yv[2 * i], yv[2 * i + 1]); o[i] = *reinterpret_cast<const uint32_t*>(&t); }
+                        }
+                        stg_stream_v4(y_out + e * 2, make_uint4(o[0], o[1], o[2], o[3]));
+                    }
+                }
+            }
+        }
+
         if (NM == kRefCompat) {
             // pre-transform of the live Triton kernel (act_triton_kernel.py:55-58)
             if (flags & ACT_FLAG_REF_CLAMP) {
@@ -314,7 +366,7 @@ quant_pack_kernel(const void* __restrict__ x_, const float* __restrict__ noise,
 
         // ---- group min / max (NaN propagates, -0 < +0) -------------------------
         float mn, mx;
-        if (ElemT<DT>::bytes == 2 && NM != kRefCompat) {
+        if (ElemT<DT>::bytes == 2 && NM != kRefCompat && PRO == kProNone) {
             // 16-bit inputs: min/max are exact in the input format, two elements per op
             minmax16<DT>(raw_cur, mn, mx);
         } else {
@@ -504,5 +556,83 @@ extern "C" int act_quant_pack(const void* x, int dtype, int64_t n_groups, int gr
         e = launch_pack_bits<ACT_DTYPE_BF16>(bits, mode, x, noise, packed, scale, mn, n_elems, log2_L, seed, offset, flags, clamp_alpha, st);
     else
         e = launch_pack_bits<ACT_DTYPE_F16>(bits, mode, x, noise, packed, scale, mn, n_elems, log2_L, seed, offset, flags, clamp_alpha, st);
+    return e == cudaSuccess ? ACT_OK : ACT_ERR_LAUNCH;
+}
+
+// ------------------------------------------------ fused activation + derivative codec
+namespace act {
+
+template <int DT, int BITS, int NM, int PRO>
+static cudaError_t launch_fused_one(const void* x, void* y, void* packed, float* scale, float* mn,
+                                    int64_t n_elems, int log2_L, uint64_t seed, uint64_t offset,
+                                    cudaStream_t st)
+{
+    static int per_sm = 0;
+    if (per_sm == 0) {
+        int n = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, quant_pack_kernel<DT, BITS, NM, PRO>,
+                                                          kPackThreads, 0) != cudaSuccess || n < 1) n = 1;
+        per_sm = n;
+    }
+    const uint64_t key = hash_key(hash_key(seed) + offset);
+    const int64_t n_tiles = (n_elems + kTileElems - 1) / kTileElems;
+    const int grid = stream_grid_for((n_tiles + kPackWarps - 1) / kPackWarps, per_sm);
+    quant_pack_kernel<DT, BITS, NM, PRO><<<grid, kPackThreads, 0, st>>>(
+        x, nullptr, static_cast<uint8_t*>(packed), scale, mn, n_elems, log2_L,
+        (uint32_t)key, (uint32_t)(key >> 32), 0, 0.0f, static_cast<uint8_t*>(y));
+    return cudaGetLastError();
+}
+
+template <int DT, int BITS>
+static cudaError_t launch_fused_bits(int kind, bool nearest, const void* x, void* y, void* packed,
+                                     float* scale, float* mn, int64_t n, int l2, uint64_t seed,
+                                     uint64_t offset, cudaStream_t st)
+{
+    if (kind == ACT_KIND_GELU)
+        return nearest ? launch_fused_one<DT, BITS, kNoiseConst, kProGelu>(x, y, packed, scale, mn, n, l2, seed, offset, st)
+                       : launch_fused_one<DT, BITS, kNoiseHash, kProGelu>(x, y, packed, scale, mn, n, l2, seed, offset, st);
+    return nearest ? launch_fused_one<DT, BITS, kNoiseConst, kProSilu>(x, y, packed, scale, mn, n, l2, seed, offset, st)
+                   : launch_fused_one<DT, BITS, kNoiseHash, kProSilu>(x, y, packed, scale, mn, n, l2, seed, offset, st);
+}
+
+template <int DT>
+static cudaError_t launch_fused(int bits, int kind, bool nearest, const void* x, void* y, void* packed,
+                                float* scale, float* mn, int64_t n, int l2, uint64_t seed,
+                                uint64_t offset, cudaStream_t st)
+{
+    switch (bits) {
+        case 1: return launch_fused_bits<DT, 1>(kind, nearest, x, y, packed, scale, mn, n, l2, seed, offset, st);
+        case 2: return launch_fused_bits<DT, 2>(kind, nearest, x, y, packed, scale, mn, n, l2, seed, offset, st);
+        case 4: return launch_fused_bits<DT, 4>(kind, nearest, x, y, packed, scale, mn, n, l2, seed, offset, st);
+        default: return launch_fused_bits<DT, 8>(kind, nearest, x, y, packed, scale, mn, n, l2, seed, offset, st);
+    }
+}
+
+}  // namespace act
+
+extern "C" int act_activation_fwd_quant_pack(const void* x, int dtype, int kind, int64_t n_groups,
+                                             int group_size, int bits, uint64_t seed, uint64_t offset,
+                                             int flags, void* y, void* packed, float* scale, float* mn,
+                                             void* stream)
+{
+    using namespace act;
+    if (dtype != ACT_DTYPE_F32 && dtype != ACT_DTYPE_BF16 && dtype != ACT_DTYPE_F16) return ACT_ERR_DTYPE;
+    if (kind != ACT_KIND_GELU && kind != ACT_KIND_SILU) return ACT_ERR_UNSUPPORTED;
+    if (flags & ~ACT_FLAG_ROUND_NEAREST) return ACT_ERR_UNSUPPORTED;
+    if (bits != 1 && bits != 2 && bits != 4 && bits != 8) return ACT_ERR_BITS;
+    if (group_size < 32 || group_size > 1024 || (group_size & (group_size - 1))) return ACT_ERR_GROUP;
+    if (n_groups < 0 || n_groups > (INT64_MAX >> 12)) return ACT_ERR_SIZE;
+    if (n_groups == 0) return ACT_OK;
+    if (!x || !y || !packed || !scale || !mn) return ACT_ERR_NULL;
+    if (((uintptr_t)x | (uintptr_t)y | (uintptr_t)packed) & 15) return ACT_ERR_ALIGN;
+    int log2_L = 0;
+    while ((32 << log2_L) < group_size) ++log2_L;
+    const int64_t n = n_groups * group_size;
+    const bool nearest = (flags & ACT_FLAG_ROUND_NEAREST) != 0;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaError_t e;
+    if (dtype == ACT_DTYPE_F32) e = launch_fused<ACT_DTYPE_F32>(bits, kind, nearest, x, y, packed, scale, mn, n, log2_L, seed, offset, st);
+    else if (dtype == ACT_DTYPE_BF16) e = launch_fused<ACT_DTYPE_BF16>(bits, kind, nearest, x, y, packed, scale, mn, n, log2_L, seed, offset, st);
+    else e = launch_fused<ACT_DTYPE_F16>(bits, kind, nearest, x, y, packed, scale, mn, n, log2_L, seed, offset, st);
     return e == cudaSuccess ? ACT_OK : ACT_ERR_LAUNCH;
 }

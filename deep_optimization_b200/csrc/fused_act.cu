@@ -1,0 +1,236 @@
+// Producer/consumer-fused codec kernels for activations, sm_100a.
+//
+//   relu_fwd_pack:    y = x > 0 ? x : 0 (or the ReLU6 window) and the 1-bit mask, one pass
+//   relu_bwd_unpack:  dx = mask ? dy : 0, one pass
+//   act_bwd_dequant:  dx = dy * (code * scale + min), the backward of GELU / SiLU whose
+//                     quantised derivative was saved in forward
+//
+// They remove the extra passes a stand-alone codec costs: the int8 mask the reference's
+// unfused path writes and reads back, and the dequantised derivative tensor.
+// All three are streaming kernels: a warp takes 1024 elements as four chunks, a lane owns
+// 8 consecutive elements per chunk, every load and store instruction is contiguous.
+//
+// Replaces: Activation_Compression/modules/activations/kernel_implementation.py:34-143
+// (relu_variance_fwd_fused_pack_kernel, relu_bwd_fused_unpack_kernel) and :345-424, :562-618
+// (silu/gelu_bwd_fused_dequan_unpack_triton).
+#include "act_common.cuh"
+
+namespace act {
+
+constexpr int kFusedThreads = 256;
+
+template <int DT> struct Vec8 {          // 8 consecutive elements of a lane
+    uint4 a, b;                          // b only for fp32
+};
+template <int DT> __device__ __forceinline__ Vec8<DT> load8(const uint8_t* p, int64_t e) {
+    Vec8<DT> v;
+    if (ElemT<DT>::bytes == 4) { v.a = ldg_nc_v4(p + e * 4); v.b = ldg_nc_v4(p + e * 4 + 16); }
+    else { v.a = ldg_nc_v4(p + e * 2); v.b = make_uint4(0, 0, 0, 0); }
+    return v;
+}
+template <int DT> __device__ __forceinline__ void to_float8(const Vec8<DT>& v, float (&f)[8]) {
+    if (ElemT<DT>::bytes == 4) {
+        f[0] = __uint_as_float(v.a.x); f[1] = __uint_as_float(v.a.y); f[2] = __uint_as_float(v.a.z); f[3] = __uint_as_float(v.a.w);
+        f[4] = __uint_as_float(v.b.x); f[5] = __uint_as_float(v.b.y); f[6] = __uint_as_float(v.b.z); f[7] = __uint_as_float(v.b.w);
+    } else {
+        constexpr int D16 = (DT == ACT_DTYPE_F32) ? ACT_DTYPE_BF16 : DT;
+        f[0] = widen_lo<D16>(v.a.x); f[1] = widen_hi<D16>(v.a.x); f[2] = widen_lo<D16>(v.a.y); f[3] = widen_hi<D16>(v.a.y);
+        f[4] = widen_lo<D16>(v.a.z); f[5] = widen_hi<D16>(v.a.z); f[6] = widen_lo<D16>(v.a.w); f[7] = widen_hi<D16>(v.a.w);
+    }
+}
+template <int DT> __device__ __forceinline__ void store8(uint8_t* p, int64_t e, const float (&f)[8]) {
+    if (DT == ACT_DTYPE_F32) {
+        stg_stream_v4(p + e * 4, make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3])));
+        stg_stream_v4(p + e * 4 + 16, make_uint4(__float_as_uint(f[4]), __float_as_uint(f[5]), __float_as_uint(f[6]), __float_as_uint(f[7])));
+    } else {
+        uint32_t o[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            if (DT == ACT_DTYPE_BF16) { const __nv_bfloat162 t = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]); o[i] = *reinterpret_cast<const uint32_t*>(&t); }
+            else { const __half2 t = __floats2half2_rn(f[2 * i], f[2 * i + 1]); o[i] = *reinterpret_cast<const uint32_t*>(&t); }
+        }
+        stg_stream_v4(p + e * 2, make_uint4(o[0], o[1], o[2], o[3]));
+    }
+}
+
+// ---- ReLU forward: y and one mask bit per element (bit i of byte e/8 = element e) -----
+template <int DT>
+__global__ void __launch_bounds__(kFusedThreads)
+relu_fwd_pack_kernel(const uint8_t* __restrict__ x, uint8_t* __restrict__ y, uint8_t* __restrict__ bits,
+                     int64_t n_elems, int relu6)
+{
+    const int64_t n_pieces = n_elems >> 3;
+    const int64_t stride = (int64_t)gridDim.x * kFusedThreads;
+    for (int64_t p0 = (int64_t)blockIdx.x * kFusedThreads + threadIdx.x; p0 < n_pieces; p0 += stride * 4) {
+        Vec8<DT> v[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) if (p0 + k * stride < n_pieces) v[k] = load8<DT>(x, (p0 + k * stride) * 8);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int64_t p = p0 + k * stride;
+            if (p >= n_pieces) break;
+            float f[8];
+            to_float8<DT>(v[k], f);
+            uint32_t m = 0;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const bool keep = relu6 ? (f[i] > 0.0f && f[i] < 6.0f) : (f[i] > 0.0f);
+                m |= (uint32_t)keep << i;
+                f[i] = keep ? f[i] : 0.0f;
+            }
+            store8<DT>(y, p * 8, f);
+            bits[p] = (uint8_t)m;
+        }
+    }
+}
+
+// ---- ReLU backward: dx = mask ? dy : 0 ----------------------------------------------------
+template <int DT>
+__global__ void __launch_bounds__(kFusedThreads)
+relu_bwd_unpack_kernel(const uint8_t* __restrict__ bits, const uint8_t* __restrict__ dy,
+                       uint8_t* __restrict__ dx, int64_t n_elems)
+{
+    const int64_t n_pieces = n_elems >> 3;
+    const int64_t stride = (int64_t)gridDim.x * kFusedThreads;
+    for (int64_t p0 = (int64_t)blockIdx.x * kFusedThreads + threadIdx.x; p0 < n_pieces; p0 += stride * 4) {
+        Vec8<DT> v[4];
+        uint32_t m[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) if (p0 + k * stride < n_pieces) {
+            v[k] = load8<DT>(dy, (p0 + k * stride) * 8);
+            m[k] = __ldg(bits + p0 + k * stride);
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int64_t p = p0 + k * stride;
+            if (p >= n_pieces) break;
+            float f[8];
+            to_float8<DT>(v[k], f);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) f[i] = ((m[k] >> i) & 1u) ? f[i] : 0.0f;
+            store8<DT>(dx, p * 8, f);
+        }
+    }
+}
+
+// ---- backward of an activation whose quantised derivative was saved: dx = dy * deq ------
+template <int DT, int BITS>
+__global__ void __launch_bounds__(kFusedThreads)
+act_bwd_dequant_kernel(const uint8_t* __restrict__ packed, const float* __restrict__ scale,
+                       const float* __restrict__ mn, const uint8_t* __restrict__ dy,
+                       uint8_t* __restrict__ dx, int64_t n_elems, int log2_gs)
+{
+    constexpr uint32_t MASK = (1u << BITS) - 1u;
+    const int64_t n_pieces = n_elems >> 3;
+    const int64_t stride = (int64_t)gridDim.x * kFusedThreads;
+    for (int64_t p0 = (int64_t)blockIdx.x * kFusedThreads + threadIdx.x; p0 < n_pieces; p0 += stride * 2) {
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const int64_t p = p0 + k * stride;
+            if (p >= n_pieces) break;
+            const Vec8<DT> v = load8<DT>(dy, p * 8);
+            uint32_t w0, w1 = 0;
+            if (BITS == 8) { const uint2 t = __ldg(reinterpret_cast<const uint2*>(packed + p * 8)); w0 = t.x; w1 = t.y; }
+            else if (BITS == 4) w0 = __ldg(reinterpret_cast<const uint32_t*>(packed + p * 4));
+            else if (BITS == 2) w0 = __ldg(reinterpret_cast<const uint16_t*>(packed + p * 2));
+            else w0 = __ldg(packed + p);
+            const int64_t g = (p * 8) >> log2_gs;
+            const float s = __ldg(scale + g), m = __ldg(mn + g);
+            float f[8];
+            to_float8<DT>(v, f);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const uint32_t c = (BITS == 8) ? (((i < 4 ? w0 : w1) >> ((i & 3) * 8)) & MASK) : ((w0 >> (i * BITS)) & MASK);
+                const float cf = __uint_as_float(kMagicBits | c) - kMagic;
+                f[i] = __fmul_rn(f[i], __fmaf_rn(cf, s, m));          // dy * (code*scale + min)
+            }
+            store8<DT>(dx, p * 8, f);
+        }
+    }
+}
+
+int stream_grid_for(int64_t n_blocks_wanted, int blocks_per_sm);   // cabi.cu
+
+static bool dtype_ok(int d) { return d == ACT_DTYPE_F32 || d == ACT_DTYPE_BF16 || d == ACT_DTYPE_F16; }
+
+}  // namespace act
+
+extern "C" int act_relu_fwd_pack(const void* x, int dtype, int64_t n_elems, int relu6, void* y,
+                                 void* mask_bits, void* stream)
+{
+    using namespace act;
+    if (!dtype_ok(dtype)) return ACT_ERR_DTYPE;
+    if (n_elems < 0 || (n_elems & 31)) return ACT_ERR_SIZE;
+    if (n_elems == 0) return ACT_OK;
+    if (!x || !y || !mask_bits) return ACT_ERR_NULL;
+    if (((uintptr_t)x | (uintptr_t)y) & 15 || ((uintptr_t)mask_bits & 3)) return ACT_ERR_ALIGN;
+    const int grid = stream_grid_for(((n_elems >> 3) + kFusedThreads * 4 - 1) / (kFusedThreads * 4), 6);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const uint8_t* xi = static_cast<const uint8_t*>(x);
+    uint8_t* yo = static_cast<uint8_t*>(y);
+    uint8_t* bo = static_cast<uint8_t*>(mask_bits);
+    if (dtype == ACT_DTYPE_F32) relu_fwd_pack_kernel<ACT_DTYPE_F32><<<grid, kFusedThreads, 0, st>>>(xi, yo, bo, n_elems, relu6);
+    else if (dtype == ACT_DTYPE_BF16) relu_fwd_pack_kernel<ACT_DTYPE_BF16><<<grid, kFusedThreads, 0, st>>>(xi, yo, bo, n_elems, relu6);
+    else relu_fwd_pack_kernel<ACT_DTYPE_F16><<<grid, kFusedThreads, 0, st>>>(xi, yo, bo, n_elems, relu6);
+    return cudaGetLastError() == cudaSuccess ? ACT_OK : ACT_ERR_LAUNCH;
+}
+
+extern "C" int act_relu_bwd_unpack(const void* mask_bits, const void* dy, int dtype, int64_t n_elems,
+                                   void* dx, void* stream)
+{
+    using namespace act;
+    if (!dtype_ok(dtype)) return ACT_ERR_DTYPE;
+    if (n_elems < 0 || (n_elems & 31)) return ACT_ERR_SIZE;
+    if (n_elems == 0) return ACT_OK;
+    if (!dy || !dx || !mask_bits) return ACT_ERR_NULL;
+    if (((uintptr_t)dy | (uintptr_t)dx) & 15) return ACT_ERR_ALIGN;
+    const int grid = stream_grid_for(((n_elems >> 3) + kFusedThreads * 4 - 1) / (kFusedThreads * 4), 6);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const uint8_t* b = static_cast<const uint8_t*>(mask_bits);
+    const uint8_t* g = static_cast<const uint8_t*>(dy);
+    uint8_t* o = static_cast<uint8_t*>(dx);
+    if (dtype == ACT_DTYPE_F32) relu_bwd_unpack_kernel<ACT_DTYPE_F32><<<grid, kFusedThreads, 0, st>>>(b, g, o, n_elems);
+    else if (dtype == ACT_DTYPE_BF16) relu_bwd_unpack_kernel<ACT_DTYPE_BF16><<<grid, kFusedThreads, 0, st>>>(b, g, o, n_elems);
+    else relu_bwd_unpack_kernel<ACT_DTYPE_F16><<<grid, kFusedThreads, 0, st>>>(b, g, o, n_elems);
+    return cudaGetLastError() == cudaSuccess ? ACT_OK : ACT_ERR_LAUNCH;
+}
+
+namespace act {
+template <int DT>
+static void launch_act_bwd(int bits, const uint8_t* p, const float* s, const float* m, const uint8_t* dy,
+                           uint8_t* dx, int64_t n, int log2_gs, int grid, cudaStream_t st)
+{
+    switch (bits) {
+        case 1: act_bwd_dequant_kernel<DT, 1><<<grid, kFusedThreads, 0, st>>>(p, s, m, dy, dx, n, log2_gs); break;
+        case 2: act_bwd_dequant_kernel<DT, 2><<<grid, kFusedThreads, 0, st>>>(p, s, m, dy, dx, n, log2_gs); break;
+        case 4: act_bwd_dequant_kernel<DT, 4><<<grid, kFusedThreads, 0, st>>>(p, s, m, dy, dx, n, log2_gs); break;
+        default: act_bwd_dequant_kernel<DT, 8><<<grid, kFusedThreads, 0, st>>>(p, s, m, dy, dx, n, log2_gs); break;
+    }
+}
+}  // namespace act
+
+extern "C" int act_mul_dequant_unpack(const void* packed, const float* scale, const float* mn,
+                                      const void* dy, int dtype, int64_t n_groups, int group_size,
+                                      int bits, void* dx, void* stream)
+{
+    using namespace act;
+    if (!dtype_ok(dtype)) return ACT_ERR_DTYPE;
+    if (bits != 1 && bits != 2 && bits != 4 && bits != 8) return ACT_ERR_BITS;
+    if (group_size < 32 || group_size > 1024 || (group_size & (group_size - 1))) return ACT_ERR_GROUP;
+    if (n_groups < 0 || n_groups > (INT64_MAX >> 12)) return ACT_ERR_SIZE;
+    if (n_groups == 0) return ACT_OK;
+    if (!packed || !scale || !mn || !dy || !dx) return ACT_ERR_NULL;
+    if (((uintptr_t)dy | (uintptr_t)dx) & 15 || ((uintptr_t)packed & 7)) return ACT_ERR_ALIGN;
+    int log2_gs = 5;
+    while ((1 << log2_gs) < group_size) ++log2_gs;
+    const int64_t n = n_groups * group_size;
+    const int grid = stream_grid_for(((n >> 3) + kFusedThreads * 2 - 1) / (kFusedThreads * 2), 6);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const uint8_t* p = static_cast<const uint8_t*>(packed);
+    const uint8_t* g = static_cast<const uint8_t*>(dy);
+    uint8_t* o = static_cast<uint8_t*>(dx);
+    if (dtype == ACT_DTYPE_F32) launch_act_bwd<ACT_DTYPE_F32>(bits, p, scale, mn, g, o, n, log2_gs, grid, st);
+    else if (dtype == ACT_DTYPE_BF16) launch_act_bwd<ACT_DTYPE_BF16>(bits, p, scale, mn, g, o, n, log2_gs, grid, st);
+    else launch_act_bwd<ACT_DTYPE_F16>(bits, p, scale, mn, g, o, n, log2_gs, grid, st);
+    return cudaGetLastError() == cudaSuccess ? ACT_OK : ACT_ERR_LAUNCH;
+}

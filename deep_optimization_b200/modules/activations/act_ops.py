@@ -20,6 +20,14 @@ class _DOReLU(Function):
     @staticmethod
     @custom_fwd(device_type="cuda")
     def forward(ctx, input, relu, relu6, target_name, meta):
+        m = meta[f"{target_name}"]
+        ctx.fused = not m["act_padding"] and input.numel() % max(m["group_size"], 32) == 0
+        if ctx.fused:
+            # one pass: y and the 1-bit mask (act_ops.py:31-38 of the reference)
+            y, packed, N, G = torch.ops.act_lib.relu_fwd_fused_pack(input, relu, relu6, 1, m["group_size"])
+            ctx.meta_ngs = (N, G, m["group_size"])
+            ctx.save_for_backward(packed)
+            return y
         if relu6 and not relu:
             mask = (input > 0) & (input < 6)
         else:
@@ -37,6 +45,9 @@ class _DOReLU(Function):
     @custom_bwd(device_type="cuda")
     def backward(ctx, dy):
         (packed,) = ctx.saved_tensors
+        if ctx.fused:
+            N, G, gs = ctx.meta_ngs
+            return torch.ops.act_lib.relu_bwd_fused_unpack(packed, dy, 1, N, G, gs), None, None, None, None
         mask = unified_dequantize((packed, None, None), ctx.q_meta, None)
         return dy * mask.to(dy.dtype), None, None, None, None
 
@@ -48,8 +59,27 @@ def _save_derivative(ctx, deriv, target_name, meta):
     ctx.save_for_backward(q_tensors[0], q_tensors[1], q_tensors[2])
 
 
+def _fused_ok(input, m):
+    return not m["act_padding"] and not m.get("AVG_ALAM", False) and input.numel() % m["group_size"] == 0
+
+
+def _fused_forward(ctx, input, kind, m):
+    """activation + derivative codec in one kernel (flat grouping)."""
+    if kind == "gelu":
+        y, packed, scale, mn, N, G = torch.ops.act_lib.gelu_fwd_fused_quan_pack(input, m["bits"], m["group_size"])
+    else:
+        y, packed, scale, mn, N, G = torch.ops.act_lib.silu_fwd_quan_pack(input, m["bits"], m["group_size"],
+                                                                          False, False, 0)[:6]
+    ctx.fused_meta = (N, G, m["bits"], m["group_size"])
+    ctx.save_for_backward(packed, scale, mn)
+    return y
+
+
 def _apply_derivative(ctx, dy):
     packed, scale, mn = ctx.saved_tensors
+    if getattr(ctx, "fused_meta", None) is not None:
+        N, G, bits, gs = ctx.fused_meta
+        return torch.ops.act_lib.gelu_bwd_fused_dequan_unpack(packed, dy, scale, mn, bits, N, G, gs)
     deriv = unified_dequantize((packed, scale, mn), ctx.q_meta, None)
     return dy * deriv.to(dy.dtype)
 
@@ -58,6 +88,9 @@ class _DOSiLU(Function):
     @staticmethod
     @custom_fwd(device_type="cuda")
     def forward(ctx, input, target_name, meta):
+        ctx.fused_meta = None
+        if _fused_ok(input, meta[f"{target_name}"]):
+            return _fused_forward(ctx, input, "silu", meta[f"{target_name}"])
         x = input.float()
         sig = torch.sigmoid(x)
         y = (x * sig).to(input.dtype)
@@ -77,6 +110,9 @@ class _DOGELU(Function):
     @staticmethod
     @custom_fwd(device_type="cuda")
     def forward(ctx, input, target_name, meta):
+        ctx.fused_meta = None
+        if _fused_ok(input, meta[f"{target_name}"]):
+            return _fused_forward(ctx, input, "gelu", meta[f"{target_name}"])
         x = input.float()
         k = math.sqrt(2.0 / math.pi)
         inner = k * (x + 0.044715 * x * x * x)

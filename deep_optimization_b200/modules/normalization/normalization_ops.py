@@ -20,6 +20,22 @@ from torch.autograd import Function
 from ..module_utils import unified_dequantize, unified_quantize
 
 
+def sync_batch_stats(mean, var, count, process_group, world_size):
+    """Combine per-rank (mean, biased var, count) into the statistics of the global batch
+    with one all-gather of 2C+1 floats per rank (normalization_ops.py:181-195 of the
+    reference gathers mean, invstd and count the same way).  Returns (mean, var, total)."""
+    local = torch.cat([mean, var + mean * mean, mean.new_tensor([float(count)])])
+    gathered = [torch.empty_like(local) for _ in range(world_size)]
+    dist.all_gather(gathered, local, group=process_group)
+    g = torch.stack(gathered)
+    C = mean.numel()
+    counts = g[:, -1:]
+    total = counts.sum()
+    mean_all = (g[:, :C] * counts).sum(0) / total
+    var_all = (g[:, C:2 * C] * counts).sum(0) / total - mean_all * mean_all
+    return mean_all, var_all, total
+
+
 def _channel_view(t):
     return [1, -1] + [1] * (t.dim() - 2)
 
@@ -36,16 +52,7 @@ class _DOBatchNorm(Function):
         var, mean = torch.var_mean(x, dim=dims, unbiased=False)
         total = count
         if world_size > 1:
-            # combine the per-rank statistics (count-weighted), one small all-gather
-            local = torch.cat([mean, var + mean * mean, mean.new_tensor([float(count)])])
-            gathered = [torch.empty_like(local) for _ in range(world_size)]
-            dist.all_gather(gathered, local, group=process_group)
-            g = torch.stack(gathered)
-            C = mean.numel()
-            counts = g[:, -1:]
-            total = counts.sum()
-            mean = (g[:, :C] * counts).sum(0) / total
-            var = (g[:, C:2 * C] * counts).sum(0) / total - mean * mean
+            mean, var, total = sync_batch_stats(mean, var, count, process_group, world_size)
         invstd = torch.rsqrt(var + eps)
         shape = _channel_view(x)
         x_hat = (x - mean.view(shape)) * invstd.view(shape)

@@ -40,6 +40,10 @@ extern "C" {
 #define ACT_FLAG_REF_TANH      8   /* with REF_COMPAT: x = tanh(x/0.5)*0.5 before the range          */
 #define ACT_FLAG_META_BF16     16  /* round scale and min to bf16 precision (still stored as fp32)   */
 
+/* activation kinds of act_activation_fwd_quant_pack */
+#define ACT_KIND_GELU 1            /* tanh-approximated GELU */
+#define ACT_KIND_SILU 2
+
 /* flags of act_fp8_gemm */
 #define ACT_GEMM_B_IS_NK 1         /* B is stored [N,K] (K contiguous, like nn.Linear weights)        */
 
@@ -98,6 +102,35 @@ ACT_API int act_pack_bits(const int8_t* x, int64_t n_groups, int group_size, int
                   void* stream);
 ACT_API int act_unpack_bits(const void* packed, int64_t n_groups, int group_size, int bits, int8_t* y,
                     void* stream);
+
+/*
+ * Fused activation kernels (one pass instead of activation + mask/derivative + codec).
+ * Replace torch.ops.act_lib.relu_fwd_fused_pack / relu_bwd_fused_unpack
+ * (AC/modules/activations/kernel_registration.py:43-94, kernels kernel_implementation.py:34-143)
+ * and the backward halves silu/gelu_bwd_fused_dequan_unpack (kernel_registration.py:190-237,
+ * 285-319).  n_elems is a multiple of 32; mask_bits holds one bit per element in the word
+ * layout of act_pack_bits with bits = 1.
+ *   act_relu_fwd_pack:  y = x > 0 ? x : 0 (relu6: 0 < x < 6), mask bit = that condition
+ *   act_relu_bwd_unpack: dx = mask ? dy : 0
+ *   act_mul_dequant_unpack: dx = dy * fma(code, scale, min), fp32 product rounded to dtype
+ */
+ /*
+ * act_activation_fwd_quant_pack: y = act(x) and the quantise-and-pack of act'(x) in one
+ * pass (replaces gelu_fwd_fused_quan_pack / silu_fwd_quan_pack, kernel_registration.py:
+ * 148-188, 262-283).  Codes follow the default scheme of act_quant_pack applied to the fp32
+ * derivative; tanh and exp are the hardware approximations.  flags: 0 or ROUND_NEAREST.
+ */
+ACT_API int act_activation_fwd_quant_pack(const void* x, int dtype, int kind, int64_t n_groups,
+                                  int group_size, int bits, uint64_t seed, uint64_t offset,
+                                  int flags, void* y, void* packed, float* scale, float* min,
+                                  void* stream);
+ACT_API int act_relu_fwd_pack(const void* x, int dtype, int64_t n_elems, int relu6, void* y,
+                      void* mask_bits, void* stream);
+ACT_API int act_relu_bwd_unpack(const void* mask_bits, const void* dy, int dtype, int64_t n_elems,
+                        void* dx, void* stream);
+ACT_API int act_mul_dequant_unpack(const void* packed, const float* scale, const float* min,
+                           const void* dy, int dtype, int64_t n_groups, int group_size, int bits,
+                           void* dx, void* stream);
 
 /*
  * Per-row min and max of a contiguous [rows, cols] matrix.
