@@ -281,7 +281,7 @@ def run_train(name, dev, world, local, steps=8, warmup=3, act=True, batch=256):
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     out = {"img_per_s": batch * world / (ms.item() * 1e-3), "ms_per_step": ms.item(),
-           "peak_mem_GB": torch.cuda.max_memory_allocated(dev) / 2 ** 30, "final_loss": float(loss)}
+           "peak_mem_GB": torch.cuda.max_memory_allocated(dev) / 2 ** 30, "final_loss": float(loss.detach())}
     del net, opt, model
     torch.cuda.empty_cache()
     return out

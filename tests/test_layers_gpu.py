@@ -86,7 +86,8 @@ def test_linear_bn_relu_gelu_layers(cuda_device):
     assert torch.allclose(bn.running_var, rb.running_var, atol=1e-5)
     y.backward(g); yr.backward(g)
     assert (x.grad - xr.grad).abs().max() < 0.05
-    assert torch.allclose(bn.weight.grad, rb.weight.grad, rtol=0.05, atol=0.2)   # x_hat kept as bf16 + 8-bit codes
+    # x_hat is kept as bf16 + 8-bit stochastic codes: compare the gradient vectors as a whole
+    assert (bn.weight.grad - rb.weight.grad).norm() / rb.weight.grad.norm() < 0.03
 
 
 def test_controller_end_to_end_step(cuda_device):
