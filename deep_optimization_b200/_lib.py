@@ -9,7 +9,8 @@ import ctypes
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libact_b200.so")
+# ACT_B200_LIB points at another build of the same library (tuning experiments)
+LIB_PATH = os.environ.get("ACT_B200_LIB") or os.path.join(HERE, "libact_b200.so")
 
 ACT_DTYPE_F32, ACT_DTYPE_BF16, ACT_DTYPE_F16 = 0, 1, 2
 ACT_FLAG_ROUND_NEAREST = 1

@@ -26,7 +26,17 @@ namespace act {
 
 enum NoiseMode { kNoiseHash = 0, kNoiseTensor = 1, kNoiseConst = 2, kRefCompat = 3 };
 
-constexpr int kPackThreads = 256;
+// Launch shape: measured on B200, one block of 512 threads per SM with up to 128 registers
+// per thread beats more, smaller blocks (39.9 us against 41.3-44.8 us on the 2-bit bf16
+// workload): the kernel is bound by instruction issue, not by latency, so registers for
+// instruction-level parallelism matter more than resident warps.
+#ifndef ACT_PACK_THREADS
+#define ACT_PACK_THREADS 512
+#endif
+#ifndef ACT_PACK_MIN_BLOCKS
+#define ACT_PACK_MIN_BLOCKS 1
+#endif
+constexpr int kPackThreads = ACT_PACK_THREADS;
 constexpr int kPackWarps = kPackThreads / 32;
 
 template <int BITS> struct PieceStore;   // writes the BITS bytes of one 8-element piece to smem
@@ -279,7 +289,7 @@ __device__ __forceinline__ void act_and_derivative(float x, float& y, float& d) 
 }
 
 template <int DT, int BITS, int NM, int PRO = kProNone>
-__global__ void __launch_bounds__(kPackThreads, 3)
+__global__ void __launch_bounds__(kPackThreads, ACT_PACK_MIN_BLOCKS)
 quant_pack_kernel(const void* __restrict__ x_, const float* __restrict__ noise,
                   uint8_t* __restrict__ packed, float* __restrict__ scale_out,
                   float* __restrict__ min_out, int64_t n_elems, int log2_L,
