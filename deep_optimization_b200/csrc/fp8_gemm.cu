@@ -83,6 +83,21 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, Smem* 
     atomicExch(&g_gemm_error, code);
     return false;
 }
+// Warp-wide bounded wait: lane 0 polls (with a short sleep between polls, so the 256
+// epilogue threads do not flood the shared-memory pipe), the verdict is broadcast.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, Smem* s, uint32_t code) {
+    uint32_t ok = 1;
+    if ((threadIdx.x & 31) == 0) {
+        ok = 0;
+        for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+            if (mbar_try_wait(bar, parity)) { ok = 1; break; }
+            if (s->abort) break;
+            __nanosleep(32);
+        }
+        if (!ok && !s->abort) { s->abort = 1; atomicExch(&g_gemm_error, code); }
+    }
+    return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
 __device__ __forceinline__ void fence_barrier_init() {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
@@ -233,7 +248,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             const int row = m0 + q * 32 + lane;
             const float sa_row = row < M ? __ldg(sa + row) : 0.0f;
             const f32x2 sa2 = pack2(sa_row, sa_row);
-            if (ok) ok = mbar_wait(&s->acc_full[buf], full_phase[buf], s, 4);
+            if (ok) ok = mbar_wait_warp(&s->acc_full[buf], full_phase[buf], s, 4);
             if (!ok) continue;
             full_phase[buf] ^= 1;
             tc_fence_after();
