@@ -109,6 +109,15 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, u
                  " [%0], [%1, {%3, %4}], [%2];"
                  :: "r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
 }
+// bulk tensor store of a 2-D box from shared memory (async proxy); the box is clipped at
+// the tensor's edges, so partial tiles need no guards
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];"
+                 :: "l"(map), "r"(smem_u32(src)), "r"(c0), "r"(c1) : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                  :: "r"(smem_u32(dst_smem)), "r"(cols) : "memory");
@@ -163,8 +172,8 @@ __host__ __device__ constexpr uint32_t make_idesc() {
 // ------------------------------------------------------------------ the kernel
 __global__ void __launch_bounds__(THREADS, 1)
 fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_bt,
-                const float* __restrict__ sa, const float* __restrict__ sb,
-                __nv_bfloat16* __restrict__ C, int M, int N, int K, int ldc)
+                const __grid_constant__ CUtensorMap map_c,
+                const float* __restrict__ sa, const float* __restrict__ sb, int M, int N, int K)
 {
     extern __shared__ uint8_t smem_raw[];
     Smem* s = reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -271,36 +280,36 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 // scale, convert, and park the lane's 32 columns (64 bytes) in shared memory;
                 // piece v of row l sits at slot v ^ ((l >> 1) & 3): conflict-free both ways
                 uint8_t* my_stage = s->cstage[warp - 2];
+                uint32_t o[4][4];
 #pragma unroll
                 for (int v = 0; v < 4; ++v) {
                     const float4 s0 = *reinterpret_cast<const float4*>(sb_s + chunk * 32 + v * 8);
                     const float4 s1 = *reinterpret_cast<const float4*>(sb_s + chunk * 32 + v * 8 + 4);
                     const f32x2 sc[4] = {pack2(s0.x, s0.y), pack2(s0.z, s0.w), pack2(s1.x, s1.y), pack2(s1.z, s1.w)};
-                    uint32_t o[4];
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
                         // (acc * sa) * sb, each product rounded to fp32, two columns per instruction
                         uint32_t lo, hi;
                         unpack2u(mul2_rn(mul2_rn(pack2u(rc[v * 8 + 2 * i], rc[v * 8 + 2 * i + 1]), sa2), sc[i]), lo, hi);
                         const __nv_bfloat162 p = __floats2bfloat162_rn(__uint_as_float(lo), __uint_as_float(hi));
-                        o[i] = *reinterpret_cast<const uint32_t*>(&p);
+                        o[v][i] = *reinterpret_cast<const uint32_t*>(&p);
                     }
-                    *reinterpret_cast<uint4*>(my_stage + lane * 64 + ((v ^ ((lane >> 1) & 3)) << 4)) =
-                        make_uint4(o[0], o[1], o[2], o[3]);
                 }
+                // the previous chunk's bulk store must have read the stage before it is rewritten
+                if (lane == 0) tma_store_wait_read();
                 __syncwarp();
-                // write-out: each instruction covers 8 rows x 64 contiguous bytes (full sectors)
 #pragma unroll
-                for (int jj = 0; jj < 4; ++jj) {
-                    const int rl = jj * 8 + (lane >> 2), piece = lane & 3;
-                    const int grow = m0 + q * 32 + rl, gcol = col0 + piece * 8;
-                    const uint4 d = *reinterpret_cast<const uint4*>(my_stage + rl * 64 + ((piece ^ ((rl >> 1) & 3)) << 4));
-                    if (grow < M && gcol < N)
-                        *reinterpret_cast<uint4*>(C + (size_t)grow * ldc + gcol) = d;
-                }
+                for (int v = 0; v < 4; ++v)
+                    *reinterpret_cast<uint4*>(my_stage + lane * 64 + ((v ^ ((lane >> 1) & 3)) << 4)) =
+                        make_uint4(o[v][0], o[v][1], o[v][2], o[v][3]);
+                // the 32 x 32 chunk leaves as one bulk tensor store (64-byte swizzle = the xor
+                // pattern above); rows and columns past the edge of C are clipped by the copy
+                fence_proxy_async();
                 __syncwarp();
+                if (lane == 0 && col0 < N && m0 + q * 32 < M) tma_store_2d(&map_c, my_stage, col0, m0 + q * 32);
             }
         }
+        if (lane == 0) tma_store_wait_all();        // all of this warp's stores are complete before exit
     }
 
     // ---------------------------------------------------------------- teardown
@@ -368,6 +377,19 @@ EncodeTiledFn encode_tiled_fn() {
 }
 
 // 2-D byte tensor [rows, cols] with row pitch ld, box = box_rows x 128 bytes, 128-byte swizzle
+// C: bf16 [rows, cols], row pitch ld elements, box 32 x 32 elements, 64-byte swizzle
+bool make_map_c(CUtensorMap* map, void* base, int rows, int cols, int ld) {
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    const cuuint32_t box[2] = {32, 32};
+    const cuuint32_t estr[2] = {1, 1};
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 bool make_map(CUtensorMap* map, const void* base, int rows, int cols, int ld, int box_rows) {
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) return false;
@@ -421,8 +443,9 @@ extern "C" int act_fp8_gemm(const void* A, const void* B, const float* sa, const
         bt = static_cast<const uint8_t*>(workspace);
     }
 
-    CUtensorMap map_a, map_bt;
-    if (!make_map(&map_a, A, M, K, lda, BM) || !make_map(&map_bt, bt, N, K, ldbt, BN)) return ACT_ERR_DEVICE;
+    CUtensorMap map_a, map_bt, map_c;
+    if (!make_map(&map_a, A, M, K, lda, BM) || !make_map(&map_bt, bt, N, K, ldbt, BN) ||
+        !make_map_c(&map_c, C, M, N, ldc)) return ACT_ERR_DEVICE;
 
     static bool attr_set = false;
     const int smem_bytes = (int)sizeof(Smem) + 1024;
@@ -435,8 +458,7 @@ extern "C" int act_fp8_gemm(const void* A, const void* B, const float* sa, const
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
     const int grid = tiles < sms ? tiles : sms;
-    fp8_gemm_kernel<<<grid, THREADS, smem_bytes, st>>>(map_a, map_bt, sa, sb, static_cast<__nv_bfloat16*>(C),
-                                                       M, N, K, ldc);
+    fp8_gemm_kernel<<<grid, THREADS, smem_bytes, st>>>(map_a, map_bt, map_c, sa, sb, M, N, K);
     return cudaGetLastError() == cudaSuccess ? ACT_OK : ACT_ERR_LAUNCH;
 }
 
