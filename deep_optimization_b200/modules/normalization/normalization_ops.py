@@ -41,31 +41,41 @@ def _channel_view(t):
 
 
 class _DOBatchNorm(Function):
+    """Forward: batch statistics, x_hat = (x - mean) * invstd, y = x_hat * w + b; x_hat goes to
+    the codec.  Backward from the decoded x_hat only.  Single-GPU batches use PyTorch's native
+    batch-norm kernels for the statistics and the two normalisations (x_hat is batch norm
+    without affine; in backward x_hat is handed to the native backward as an input whose mean
+    is 0 and inverse deviation 1, and the result is scaled by the true inverse deviation)."""
+
     @staticmethod
     @custom_fwd(device_type="cuda")
     def forward(ctx, input, weight, bias, running_mean, running_var, exponential_average_factor,
                 eps, target_name, meta, ema_grad_meta, process_group=None, world_size=1):
         ctx.set_materialize_grads(False)
-        x = input.float()
-        dims = [0] + list(range(2, x.dim()))
-        count = x.numel() // x.shape[1]
-        var, mean = torch.var_mean(x, dim=dims, unbiased=False)
-        total = count
-        if world_size > 1:
+        C = input.shape[1]
+        shape = _channel_view(input)
+        count = input.numel() // C
+        if world_size == 1:
+            # one native kernel: x_hat and the saved statistics (running stats updated in place)
+            x_hat, mean, invstd = torch.native_batch_norm(input, None, None, running_mean, running_var,
+                                                           True, exponential_average_factor, eps)
+        else:
+            x = input.float()
+            dims = [0] + list(range(2, x.dim()))
+            var, mean = torch.var_mean(x, dim=dims, unbiased=False)
             mean, var, total = sync_batch_stats(mean, var, count, process_group, world_size)
-        invstd = torch.rsqrt(var + eps)
-        shape = _channel_view(x)
-        x_hat = (x - mean.view(shape)) * invstd.view(shape)
-        w = weight.float().view(shape) if weight is not None else 1.0
-        b = bias.float().view(shape) if bias is not None else 0.0
-        y = (x_hat * w + b).to(input.dtype)
-        if running_mean is not None:
-            n = float(total)
-            unbiased = var * (n / max(n - 1.0, 1.0))
-            running_mean.mul_(1.0 - exponential_average_factor).add_(mean, alpha=exponential_average_factor)
-            running_var.mul_(1.0 - exponential_average_factor).add_(unbiased, alpha=exponential_average_factor)
-        q_tensors, q_meta, _ = unified_quantize(x_hat.to(torch.bfloat16), None, target_name, meta,
-                                                clamp=False, clamp_alpha=0.0)
+            invstd = torch.rsqrt(var + eps)
+            x_hat = ((x - mean.view(shape)) * invstd.view(shape)).to(input.dtype)
+            if running_mean is not None:
+                n = float(total)
+                unbiased = var * (n / max(n - 1.0, 1.0))
+                running_mean.mul_(1.0 - exponential_average_factor).add_(mean, alpha=exponential_average_factor)
+                running_var.mul_(1.0 - exponential_average_factor).add_(unbiased, alpha=exponential_average_factor)
+        if weight is not None:
+            y = torch.addcmul(bias.to(x_hat.dtype).view(shape), x_hat, weight.to(x_hat.dtype).view(shape))
+        else:
+            y = x_hat
+        q_tensors, q_meta, _ = unified_quantize(x_hat, None, target_name, meta, clamp=False, clamp_alpha=0.0)
         ctx.q_meta = q_meta
         ctx.sync = (process_group, world_size)
         ctx.save_for_backward(weight, q_tensors[0], q_tensors[1], q_tensors[2], invstd)
@@ -76,19 +86,28 @@ class _DOBatchNorm(Function):
     def backward(ctx, dy):
         weight, q_out, q_scale, q_min, invstd = ctx.saved_tensors
         process_group, world_size = ctx.sync
-        x_hat = unified_dequantize((q_out, q_scale, q_min), ctx.q_meta, None).float()
+        x_hat = unified_dequantize((q_out, q_scale, q_min), ctx.q_meta, None)
+        shape = _channel_view(dy)
+        C = dy.shape[1]
+        if world_size == 1:
+            zeros = torch.zeros(C, device=dy.device, dtype=torch.float32)
+            ones = torch.ones(C, device=dy.device, dtype=torch.float32)
+            w = weight.float() if weight is not None else None
+            dx, dgamma, dbeta = torch.ops.aten.native_batch_norm_backward(
+                dy.contiguous(), x_hat.to(dy.dtype), w, None, None, zeros, ones, True, 0.0,
+                [True, weight is not None, weight is not None])
+            dx = dx * invstd.to(dx.dtype).view(shape)
+            dw = dgamma.to(weight.dtype) if weight is not None else None
+            db = dbeta.to(weight.dtype) if weight is not None else None
+            return dx, dw, db, None, None, None, None, None, None, None, None, None
         g = dy.float()
+        x_hat = x_hat.float()
         dims = [0] + list(range(2, g.dim()))
-        shape = _channel_view(g)
         dgamma = (g * x_hat).sum(dims)
         dbeta = g.sum(dims)
-        M = float(g.numel() // g.shape[1])
-        sum_dg, sum_db = dgamma, dbeta
-        if world_size > 1:
-            both = torch.cat([dgamma, dbeta, dgamma.new_tensor([M])])
-            dist.all_reduce(both, group=process_group)
-            C = dgamma.numel()
-            sum_dg, sum_db, M = both[:C], both[C:2 * C], float(both[-1])
+        both = torch.cat([dgamma, dbeta, dgamma.new_tensor([float(g.numel() // C)])])
+        dist.all_reduce(both, group=process_group)
+        sum_dg, sum_db, M = both[:C], both[C:2 * C], float(both[-1])
         w = weight.float() if weight is not None else torch.ones_like(invstd)
         dx = (w * invstd / M).view(shape) * (M * g - sum_db.view(shape) - x_hat * sum_dg.view(shape))
         dw = dgamma.to(weight.dtype) if weight is not None else None
