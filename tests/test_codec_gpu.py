@@ -202,3 +202,32 @@ def test_cuda_against_reference_fixtures(oracle, cuda_device, bits, gs):
     pk = c.pack_bits(mask, bits, gs)
     assert np.array_equal(pk.cpu().numpy().view(np.uint32), fix[key + "_mask_packed"])
     assert np.array_equal(c.unpack_bits(pk, bits, mask.shape[0], gs).cpu().numpy(), fix[key + "_mask_unpacked"])
+
+
+def test_cuda_graph_capture_and_replay(oracle, cuda_device):
+    """The entry points neither synchronise nor allocate, so a captured pack + unpack pair
+    replays on new data (the reference drives its training step from CUDA graphs,
+    Train/utils_train.py:92-180).  Noise stream and offset are frozen at capture time."""
+    c = _codec()
+    x = relu_normal((64, 4096), seed=3, dtype=torch.bfloat16).to(cuda_device)
+    static_x = x.clone()
+    ng = x.numel() // 128
+    outs = (torch.empty((ng, 8), dtype=torch.int32, device=cuda_device),
+            torch.empty(ng, device=cuda_device), torch.empty(ng, device=cuda_device))
+    y = torch.empty((ng, 128), dtype=torch.bfloat16, device=cuda_device)
+    c.quant_pack(static_x, 2, 128, seed=5, offset=9, out=outs)              # warm-up outside capture
+    c.dequant_unpack(*outs, 2, 128, out_dtype=torch.bfloat16, out=y)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        c.quant_pack(static_x, 2, 128, seed=5, offset=9, out=outs)
+        c.dequant_unpack(*outs, 2, 128, out_dtype=torch.bfloat16, out=y)
+    x2 = relu_normal((64, 4096), seed=4, dtype=torch.bfloat16).to(cuda_device)
+    static_x.copy_(x2)
+    g.replay()
+    torch.cuda.synchronize()
+    arr, tag = to_numpy(x2)
+    want = oracle.quant_pack(arr, 128, 2, dtype=tag, seed=5, offset=9)
+    _cmp_pack(oracle, outs, want, "graph replay")
+    wy = oracle.dequant_unpack(*want, 128, 2, out="bf16")
+    assert np.array_equal(to_numpy(y)[0], wy)
