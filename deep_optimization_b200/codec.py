@@ -241,3 +241,78 @@ def mul_dequant_unpack(packed: torch.Tensor, scale: torch.Tensor, mn: torch.Tens
                                                 group_size, bits, dx.data_ptr(), _stream_ptr(dy))
     _lib.check(rc, "act_mul_dequant_unpack")
     return dx
+
+
+# ---------------------------------------------------------------- fused batch-norm kernels
+
+def bn_fused_supported(x: torch.Tensor, group_size: int) -> bool:
+    """Shapes the fused batch-norm kernels take: [N, C, ...] with HW a multiple of 4."""
+    if x.dim() < 3 or not x.is_cuda or x.dtype not in _DTYPES:
+        return False
+    C = x.shape[1]
+    hw = x.numel() // (x.shape[0] * C)
+    return (hw % 4 == 0 and hw * (hw + 1024) < 2 ** 32 and C <= 4096
+            and x.numel() % group_size == 0)
+
+
+def bn_fwd_norm_quant_pack(x: torch.Tensor, mean: torch.Tensor, invstd: torch.Tensor,
+                           weight: Optional[torch.Tensor], bias: Optional[torch.Tensor], bits: int,
+                           group_size: int, seed: Optional[int] = None, offset: Optional[int] = None,
+                           flags: int = 0):
+    """y = (x - mean) * invstd * weight + bias and the packed x_hat: (y, packed, scale, min)."""
+    global _next_offset
+    _, nwords, _ = _bits_consts(bits, group_size)
+    x = x.contiguous()
+    N, C = x.shape[0], x.shape[1]
+    hw = x.numel() // (N * C)
+    ones = torch.ones_like(mean) if weight is None else weight.float()
+    zeros = torch.zeros_like(mean) if bias is None else bias.float()
+    params = torch.stack([mean.float(), invstd.float(), ones, zeros], dim=1).contiguous()
+    ng = x.numel() // group_size
+    y = torch.empty_like(x)
+    packed = torch.empty((ng, nwords), dtype=torch.int32, device=x.device)
+    scale = torch.empty((ng,), dtype=torch.float32, device=x.device)
+    mn = torch.empty((ng,), dtype=torch.float32, device=x.device)
+    if seed is None:
+        seed = _default_seed
+    if offset is None:
+        offset = _next_offset
+        _next_offset += 1
+    with torch.cuda.device(x.device):
+        rc = _lib.load().act_bn_fwd_norm_quant_pack(
+            x.data_ptr(), _DTYPES[x.dtype], N, C, hw, params.data_ptr(), group_size, bits,
+            seed & 0xFFFFFFFFFFFFFFFF, offset & 0xFFFFFFFFFFFFFFFF, flags, y.data_ptr(), packed.data_ptr(),
+            scale.data_ptr(), mn.data_ptr(), _stream_ptr(x))
+    _lib.check(rc, "act_bn_fwd_norm_quant_pack")
+    return y, packed, scale, mn
+
+
+def bn_bwd_reduce(packed: torch.Tensor, scale: torch.Tensor, mn: torch.Tensor, dy: torch.Tensor, bits: int,
+                  group_size: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """(sum dy * x_hat, sum dy) per channel, from the packed x_hat."""
+    dy = dy.contiguous()
+    N, C = dy.shape[0], dy.shape[1]
+    hw = dy.numel() // (N * C)
+    sums = torch.zeros(2 * C, dtype=torch.float32, device=dy.device)
+    with torch.cuda.device(dy.device):
+        rc = _lib.load().act_bn_bwd_reduce(packed.data_ptr(), scale.data_ptr(), mn.data_ptr(), dy.data_ptr(),
+                                           _DTYPES[dy.dtype], N, C, hw, group_size, bits, sums.data_ptr(),
+                                           _stream_ptr(dy))
+    _lib.check(rc, "act_bn_bwd_reduce")
+    return sums[:C], sums[C:]
+
+
+def bn_bwd_dx(packed: torch.Tensor, scale: torch.Tensor, mn: torch.Tensor, dy: torch.Tensor, k1: torch.Tensor,
+              k2: torch.Tensor, k3: torch.Tensor, bits: int, group_size: int) -> torch.Tensor:
+    """dx = k1[c] * dy - k2[c] - k3[c] * x_hat."""
+    dy = dy.contiguous()
+    N, C = dy.shape[0], dy.shape[1]
+    hw = dy.numel() // (N * C)
+    coef = torch.stack([k1.float(), k2.float(), k3.float(), torch.zeros_like(k1, dtype=torch.float32)], dim=1).contiguous()
+    dx = torch.empty_like(dy)
+    with torch.cuda.device(dy.device):
+        rc = _lib.load().act_bn_bwd_dx(packed.data_ptr(), scale.data_ptr(), mn.data_ptr(), dy.data_ptr(),
+                                       _DTYPES[dy.dtype], N, C, hw, group_size, bits, coef.data_ptr(),
+                                       dx.data_ptr(), _stream_ptr(dy))
+    _lib.check(rc, "act_bn_bwd_dx")
+    return dx

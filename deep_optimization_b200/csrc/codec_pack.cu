@@ -266,7 +266,16 @@ __device__ __forceinline__ void encode_piece_ref(const float* xf8, float mn, flo
 // kProGelu / kProSilu write y = act(x) to y_out and quantise the activation's derivative
 // (what backward multiplies dy with), replacing the reference's fused forward kernels
 // (Activation_Compression/modules/activations/kernel_implementation.py:184-342, 468-559).
-enum Producer { kProNone = 0, kProGelu = 1, kProSilu = 2 };
+enum Producer { kProNone = 0, kProGelu = 1, kProSilu = 2, kProBN = 3 };
+
+// Per-channel inputs of the batch-norm producer: x is [N, C, HW] contiguous and
+// params[c] = (mean, invstd, weight, bias).  The channel of element e is (e / HW) % C;
+// inside a lane's group it is found with two exact multiply-high divisions, which the
+// host enables only when HW*(HW+1024) < 2^32 and C*(C+260) < 2^32.
+struct BNArgs {
+    const float4* params;
+    uint32_t hw, c, magic_hw, magic_c;
+};
 
 __device__ __forceinline__ float tanh_fast(float v) {
     float r; asm("tanh.approx.f32 %0, %1;" : "=f"(r) : "f"(v)); return r;
@@ -281,10 +290,12 @@ __device__ __forceinline__ void act_and_derivative(float x, float& y, float& d) 
         const float th = tanh_fast(k * (x + c * x2 * x));
         y = 0.5f * x * (1.0f + th);
         d = 0.5f * (1.0f + th) + 0.5f * x * (1.0f - th * th) * k * (1.0f + 3.0f * c * x2);
-    } else {
+    } else if (PRO == kProSilu) {
         const float sig = __fdividef(1.0f, 1.0f + __expf(-x));
         y = x * sig;
         d = sig * (1.0f + x * (1.0f - sig));
+    } else {
+        y = x; d = x;
     }
 }
 
@@ -294,7 +305,7 @@ quant_pack_kernel(const void* __restrict__ x_, const float* __restrict__ noise,
                   uint8_t* __restrict__ packed, float* __restrict__ scale_out,
                   float* __restrict__ min_out, int64_t n_elems, int log2_L,
                   uint32_t key_lo, uint32_t key_hi, int flags, float clamp_alpha,
-                  uint8_t* __restrict__ y_out = nullptr)
+                  uint8_t* __restrict__ y_out = nullptr, BNArgs bn = BNArgs{nullptr, 1u, 1u, 0u, 0u})
 {
     constexpr int QMAX = (1 << BITS) - 1;
     constexpr int TILE_OUT = kTileElems * BITS / 8;          // packed bytes per tile
@@ -337,13 +348,38 @@ quant_pack_kernel(const void* __restrict__ x_, const float* __restrict__ noise,
             }
         }
 
+        // batch norm: plane index and offset inside the plane of the lane's group
+        uint32_t bn_c0 = 0, bn_r0 = 0;
+        if (PRO == kProBN) {
+            const uint64_t plane = (uint64_t)group_e0 / bn.hw;
+            bn_r0 = (uint32_t)((uint64_t)group_e0 - plane * bn.hw);
+            bn_c0 = (uint32_t)(plane % bn.c);
+        }
         if (PRO != kProNone) {
-            // fused producer: emit y = act(x), keep the derivative for the codec
+            // fused producer: emit y, keep what backward needs (derivative or x_hat) for the codec
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
                 float yv[8];
+                if (PRO == kProBN) {
 #pragma unroll
-                for (int i = 0; i < 8; ++i) act_and_derivative<PRO>(xf[k * 8 + i], yv[i], xf[k * 8 + i]);
+                    for (int h = 0; h < 2; ++h) {
+                        // four consecutive elements share a channel (HW is a multiple of 4)
+                        const uint32_t t = bn_r0 + (uint32_t)(((k << log2_L) + j) * 8 + h * 4);
+                        const uint32_t q = bn.magic_hw ? __umulhi(t, bn.magic_hw) : t / bn.hw;
+                        uint32_t cc = bn_c0 + q;
+                        cc -= (bn.magic_c ? __umulhi(cc, bn.magic_c) : cc / bn.c) * bn.c;
+                        const float4 p = __ldg(bn.params + cc);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const float xh = __fmul_rn(__fsub_rn(xf[k * 8 + h * 4 + i], p.x), p.y);   // x_hat
+                            yv[h * 4 + i] = __fadd_rn(__fmul_rn(xh, p.z), p.w);                       // affine
+                            xf[k * 8 + h * 4 + i] = xh;
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) act_and_derivative<PRO>(xf[k * 8 + i], yv[i], xf[k * 8 + i]);
+                }
                 if (valid) {
                     const int64_t e = group_e0 + (int64_t)((k << log2_L) + j) * 8;
                     if (DT == ACT_DTYPE_F32) {
@@ -644,5 +680,86 @@ extern "C" int act_activation_fwd_quant_pack(const void* x, int dtype, int kind,
     if (dtype == ACT_DTYPE_F32) e = launch_fused<ACT_DTYPE_F32>(bits, kind, nearest, x, y, packed, scale, mn, n, log2_L, seed, offset, st);
     else if (dtype == ACT_DTYPE_BF16) e = launch_fused<ACT_DTYPE_BF16>(bits, kind, nearest, x, y, packed, scale, mn, n, log2_L, seed, offset, st);
     else e = launch_fused<ACT_DTYPE_F16>(bits, kind, nearest, x, y, packed, scale, mn, n, log2_L, seed, offset, st);
+    return e == cudaSuccess ? ACT_OK : ACT_ERR_LAUNCH;
+}
+
+// ------------------------------------------------ fused batch-norm normalise + x_hat codec
+namespace act {
+
+// ceil(2^32 / d) for the multiply-high division, 0 when d is 1 (then a plain division is used)
+static uint32_t magic_for(uint32_t d) {
+    if (d <= 1) return 0;
+    return (uint32_t)(((1ull << 32) + d - 1) / d);
+}
+
+template <int DT, int BITS, int NM>
+static cudaError_t launch_bn_one(const void* x, void* y, void* packed, float* scale, float* mn,
+                                 int64_t n_elems, int log2_L, uint64_t seed, uint64_t offset,
+                                 BNArgs bn, cudaStream_t st)
+{
+    static int per_sm = 0;
+    if (per_sm == 0) {
+        int n = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, quant_pack_kernel<DT, BITS, NM, kProBN>,
+                                                          kPackThreads, 0) != cudaSuccess || n < 1) n = 1;
+        per_sm = n;
+    }
+    const uint64_t key = hash_key(hash_key(seed) + offset);
+    const int64_t n_tiles = (n_elems + kTileElems - 1) / kTileElems;
+    const int grid = stream_grid_for((n_tiles + kPackWarps - 1) / kPackWarps, per_sm);
+    quant_pack_kernel<DT, BITS, NM, kProBN><<<grid, kPackThreads, 0, st>>>(
+        x, nullptr, static_cast<uint8_t*>(packed), scale, mn, n_elems, log2_L,
+        (uint32_t)key, (uint32_t)(key >> 32), 0, 0.0f, static_cast<uint8_t*>(y), bn);
+    return cudaGetLastError();
+}
+
+template <int DT>
+static cudaError_t launch_bn(int bits, bool nearest, const void* x, void* y, void* packed, float* scale,
+                             float* mn, int64_t n, int l2, uint64_t seed, uint64_t offset, BNArgs bn,
+                             cudaStream_t st)
+{
+#define ACT_BN_CASE(B) \
+    return nearest ? launch_bn_one<DT, B, kNoiseConst>(x, y, packed, scale, mn, n, l2, seed, offset, bn, st) \
+                   : launch_bn_one<DT, B, kNoiseHash>(x, y, packed, scale, mn, n, l2, seed, offset, bn, st)
+    switch (bits) {
+        case 1: ACT_BN_CASE(1);
+        case 2: ACT_BN_CASE(2);
+        case 4: ACT_BN_CASE(4);
+        default: ACT_BN_CASE(8);
+    }
+#undef ACT_BN_CASE
+}
+
+}  // namespace act
+
+extern "C" int act_bn_fwd_norm_quant_pack(const void* x, int dtype, int64_t n_batch, int channels, int64_t hw,
+                                          const float* params, int group_size, int bits, uint64_t seed,
+                                          uint64_t offset, int flags, void* y, void* packed, float* scale,
+                                          float* mn, void* stream)
+{
+    using namespace act;
+    if (dtype != ACT_DTYPE_F32 && dtype != ACT_DTYPE_BF16 && dtype != ACT_DTYPE_F16) return ACT_ERR_DTYPE;
+    if (flags & ~ACT_FLAG_ROUND_NEAREST) return ACT_ERR_UNSUPPORTED;
+    if (bits != 1 && bits != 2 && bits != 4 && bits != 8) return ACT_ERR_BITS;
+    if (group_size < 32 || group_size > 1024 || (group_size & (group_size - 1))) return ACT_ERR_GROUP;
+    if (n_batch < 0 || channels <= 0 || hw <= 0) return ACT_ERR_SIZE;
+    // exactness of the multiply-high channel lookup, and channel-uniform groups of four
+    if ((hw & 3) || (uint64_t)hw * (uint64_t)(hw + 1024) >= (1ull << 32) ||
+        (uint64_t)channels * (uint64_t)(channels + 260) >= (1ull << 32)) return ACT_ERR_UNSUPPORTED;
+    const int64_t n = n_batch * channels * hw;
+    if (n > (INT64_MAX >> 4) || n % group_size) return ACT_ERR_SIZE;
+    if (n == 0) return ACT_OK;
+    if (!x || !y || !packed || !scale || !mn || !params) return ACT_ERR_NULL;
+    if (((uintptr_t)x | (uintptr_t)y | (uintptr_t)packed | (uintptr_t)params) & 15) return ACT_ERR_ALIGN;
+    int log2_L = 0;
+    while ((32 << log2_L) < group_size) ++log2_L;
+    BNArgs bn{reinterpret_cast<const float4*>(params), (uint32_t)hw, (uint32_t)channels,
+              magic_for((uint32_t)hw), magic_for((uint32_t)channels)};
+    const bool nearest = (flags & ACT_FLAG_ROUND_NEAREST) != 0;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaError_t e;
+    if (dtype == ACT_DTYPE_F32) e = launch_bn<ACT_DTYPE_F32>(bits, nearest, x, y, packed, scale, mn, n, log2_L, seed, offset, bn, st);
+    else if (dtype == ACT_DTYPE_BF16) e = launch_bn<ACT_DTYPE_BF16>(bits, nearest, x, y, packed, scale, mn, n, log2_L, seed, offset, bn, st);
+    else e = launch_bn<ACT_DTYPE_F16>(bits, nearest, x, y, packed, scale, mn, n, log2_L, seed, offset, bn, st);
     return e == cudaSuccess ? ACT_OK : ACT_ERR_LAUNCH;
 }

@@ -17,6 +17,7 @@ import torch.distributed as dist
 from torch.amp import custom_bwd, custom_fwd
 from torch.autograd import Function
 
+from ... import _lib, act_kernels, codec
 from ..module_utils import unified_dequantize, unified_quantize
 
 
@@ -55,6 +56,27 @@ class _DOBatchNorm(Function):
         C = input.shape[1]
         shape = _channel_view(input)
         count = input.numel() // C
+        m = meta[f"{target_name}"]
+        ctx.fused = None
+        if (world_size == 1 and not m["act_padding"] and not m.get("AVG_ALAM", False)
+                and codec.bn_fused_supported(input, m["group_size"])):
+            # fused path: one statistics pass, then normalise + affine + x_hat codec in one kernel
+            # (normalization_ops.py:71-98 of the reference: bn_fwd_reduce + bn_fwd_norm_quant_pack_fused)
+            x = input.contiguous()
+            mean, invstd = torch.batch_norm_stats(x, eps)
+            if running_mean is not None:
+                var = 1.0 / (invstd * invstd) - eps
+                n = float(count)
+                f = exponential_average_factor
+                running_mean.mul_(1.0 - f).add_(mean, alpha=f)
+                running_var.mul_(1.0 - f).add_(var * (n / max(n - 1.0, 1.0)), alpha=f)
+            flags = _lib.ACT_FLAG_ROUND_NEAREST if act_kernels.get_mode() != "baseline" else 0
+            y, packed, scale, mn = codec.bn_fwd_norm_quant_pack(x, mean, invstd, weight, bias, m["bits"],
+                                                                m["group_size"], flags=flags)
+            ctx.fused = (m["bits"], m["group_size"], count)
+            ctx.sync = (process_group, world_size)
+            ctx.save_for_backward(weight, packed, scale, mn, invstd)
+            return y
         if world_size == 1:
             # one native kernel: x_hat and the saved statistics (running stats updated in place)
             x_hat, mean, invstd = torch.native_batch_norm(input, None, None, running_mean, running_var,
@@ -86,6 +108,17 @@ class _DOBatchNorm(Function):
     def backward(ctx, dy):
         weight, q_out, q_scale, q_min, invstd = ctx.saved_tensors
         process_group, world_size = ctx.sync
+        if ctx.fused is not None:
+            # two kernels on the packed x_hat: per-channel sums, then dx (normalization_ops.py:145-163)
+            bits, gs, count = ctx.fused
+            dyc = dy.contiguous()
+            dgamma, dbeta = codec.bn_bwd_reduce(q_out, q_scale, q_min, dyc, bits, gs)
+            w = weight.float() if weight is not None else torch.ones_like(invstd)
+            k1 = w * invstd
+            dx = codec.bn_bwd_dx(q_out, q_scale, q_min, dyc, k1, k1 * dbeta / count, k1 * dgamma / count, bits, gs)
+            dw = dgamma.to(weight.dtype) if weight is not None else None
+            db = dbeta.to(weight.dtype) if weight is not None else None
+            return dx, dw, db, None, None, None, None, None, None, None, None, None
         x_hat = unified_dequantize((q_out, q_scale, q_min), ctx.q_meta, None)
         shape = _channel_view(dy)
         C = dy.shape[1]

@@ -133,6 +133,30 @@ ACT_API int act_mul_dequant_unpack(const void* packed, const float* scale, const
                            void* dx, void* stream);
 
 /*
+ * Fused batch-norm kernels on x [N, C, HW] with flat sample-major groups (replace
+ * bn_fwd_norm_quant_pack_fused, bn_bwd_reduce_dequant_unpack_fused and
+ * bn_bwd_dx_dequant_unpack_fused, AC/modules/normalization/kernel_registration.py:86-299).
+ * HW must be a multiple of 4 and N*C*HW a multiple of group_size.
+ *   act_bn_fwd_norm_quant_pack: params = fp32 [C][4] (mean, invstd, weight, bias);
+ *       x_hat = (x - mean) * invstd, y = x_hat * weight + bias (each step rounded to fp32),
+ *       y written in `dtype`, x_hat quantised with the default scheme of act_quant_pack.
+ *       Needs HW*(HW+1024) < 2^32 and C*(C+260) < 2^32, else ACT_ERR_UNSUPPORTED.
+ *   act_bn_bwd_reduce: sums fp32 [2*C], zeroed by the caller; adds sum(dy*x_hat) to sums[c]
+ *       and sum(dy) to sums[C+c] (atomic adds: the summation order is not fixed). C <= 4096.
+ *   act_bn_bwd_dx: coef = fp32 [C][4] (k1, k2, k3, unused); dx = k1*dy - k2 - k3*x_hat.
+ */
+ACT_API int act_bn_fwd_norm_quant_pack(const void* x, int dtype, int64_t n_batch, int channels, int64_t hw,
+                               const float* params, int group_size, int bits, uint64_t seed,
+                               uint64_t offset, int flags, void* y, void* packed, float* scale,
+                               float* min, void* stream);
+ACT_API int act_bn_bwd_reduce(const void* packed, const float* scale, const float* min, const void* dy,
+                      int dtype, int64_t n_batch, int channels, int64_t hw, int group_size, int bits,
+                      float* sums, void* stream);
+ACT_API int act_bn_bwd_dx(const void* packed, const float* scale, const float* min, const void* dy,
+                  int dtype, int64_t n_batch, int channels, int64_t hw, int group_size, int bits,
+                  const float* coef, void* dx, void* stream);
+
+/*
  * Per-row min and max of a contiguous [rows, cols] matrix.
  * Replaces cpp_extension.min_max_kernel (AC/cpp_extension/src/min_max_kernel.cu:66-141).
  */

@@ -77,3 +77,59 @@ def test_fused_paths_in_layers(cuda_device):
     yr = torch.nn.functional.gelu(xr, approximate="tanh"); yr.backward(g)
     assert torch.allclose(y, yr, atol=2e-3)
     assert (x.grad - xr.grad).abs().max() < 0.02 * g.abs().max()
+
+
+@pytest.mark.parametrize("dtype", (torch.float32, torch.bfloat16), ids=("f32", "bf16"))
+@pytest.mark.parametrize("shape", [(8, 16, 32, 32), (6, 24, 14, 14), (8, 5, 2, 2), (16, 64, 56, 56)])
+def test_bn_fused_forward(oracle, cuda_device, dtype, shape):
+    """x_hat = (x - mean) * invstd with both steps rounded to fp32: the packed codes, scale and
+    min must be bit-exact with the oracle applied to that fp32 tensor; y within the output
+    type's rounding of x_hat * w + b."""
+    from deep_optimization_b200 import codec
+    g = torch.Generator().manual_seed(5)
+    x = (torch.randn(shape, generator=g) * 2 + 0.5).to(dtype).to(cuda_device)
+    C = shape[1]
+    mean = torch.randn(C, generator=g).to(cuda_device)
+    invstd = (torch.rand(C, generator=g) + 0.5).to(cuda_device)
+    w = torch.randn(C, generator=g).to(cuda_device)
+    b = torch.randn(C, generator=g).to(cuda_device)
+    gs = 64 if x.numel() % 256 else 256
+    if x.numel() % gs:
+        gs = 32
+    assert codec.bn_fused_supported(x, gs)
+    y, packed, scale, mn = codec.bn_fwd_norm_quant_pack(x, mean, invstd, w, b, 2, gs, seed=3, offset=2)
+    view = [1, C, 1, 1]
+    x_hat = (x.float() - mean.view(view)) * invstd.view(view)           # fp32, two roundings
+    want = oracle.quant_pack(x_hat.cpu().numpy(), gs, 2, seed=3, offset=2)
+    assert np.array_equal(packed.cpu().numpy().view(np.uint32), want[0])
+    assert np.array_equal(scale.cpu().numpy().view(np.uint32), want[1].view(np.uint32))
+    assert np.array_equal(mn.cpu().numpy().view(np.uint32), want[2].view(np.uint32))
+    y_ref = x_hat * w.view(view) + b.view(view)
+    assert torch.equal(y, y_ref.to(dtype))
+
+
+@pytest.mark.parametrize("dtype", (torch.float32, torch.bfloat16), ids=("f32", "bf16"))
+@pytest.mark.parametrize("shape", [(8, 16, 32, 32), (6, 24, 14, 14), (8, 5, 2, 2)])
+@pytest.mark.parametrize("bits", (2, 8))
+def test_bn_fused_backward(cuda_device, dtype, shape, bits):
+    """Sums and dx from the packed x_hat equal the same formulas on the decoded tensor
+    (sums: fp32 accumulation in another order, relative 1e-4; dx: one output rounding)."""
+    from deep_optimization_b200 import codec
+    g = torch.Generator().manual_seed(6)
+    xh = torch.randn(shape, generator=g).to(cuda_device)
+    dy = torch.randn(shape, generator=g).to(dtype).to(cuda_device)
+    C = shape[1]
+    gs = 32
+    packed, scale, mn = codec.quant_pack(xh, bits, gs, seed=1, offset=0)
+    dec = codec.dequant_unpack(packed, scale, mn, bits, gs, out_dtype=torch.float32).view(shape)
+    s1, s2 = codec.bn_bwd_reduce(packed, scale, mn, dy, bits, gs)
+    dims = [0, 2, 3]
+    r1, r2 = (dy.float() * dec).sum(dims), dy.float().sum(dims)
+    assert torch.allclose(s1, r1, rtol=1e-4, atol=1e-3 * r1.abs().max().item())
+    assert torch.allclose(s2, r2, rtol=1e-4, atol=1e-3 * r2.abs().max().item() + 1e-3)
+    k1, k2, k3 = (torch.randn(C, generator=g).to(cuda_device) for _ in range(3))
+    dx = codec.bn_bwd_dx(packed, scale, mn, dy, k1, k2, k3, bits, gs)
+    view = [1, C, 1, 1]
+    want = k1.view(view) * dy.float() - k2.view(view) - k3.view(view) * dec
+    tol = 2.0 ** -7 if dtype == torch.bfloat16 else 1e-5
+    assert ((dx.float() - want).abs() <= tol * (1 + want.abs())).all()
