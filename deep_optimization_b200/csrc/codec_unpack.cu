@@ -102,6 +102,56 @@ dequant_unpack_kernel(const uint8_t* __restrict__ packed, const float* __restric
     }
 }
 
+// fp32 output: a lane owns 4 consecutive elements per store (one 16-byte vector), eight
+// stores per 1024-element tile, so each store instruction of the warp writes 512 contiguous
+// bytes.  The 4*BITS code bits of a lane never straddle a 32-bit word.
+template <int BITS>
+__global__ void __launch_bounds__(kUnpackThreads)
+dequant_unpack_f32_kernel(const uint32_t* __restrict__ packed, const float* __restrict__ scale,
+                          const float* __restrict__ mn, float* __restrict__ y, int64_t n_elems,
+                          int log2_gs)
+{
+    constexpr uint32_t MASK = (1u << BITS) - 1u;
+    const int lane = threadIdx.x & 31;
+    const int64_t n_tiles = (n_elems + kTileElems - 1) / kTileElems;
+    const int64_t warp_stride = (int64_t)gridDim.x * kUnpackWarps;
+    const f32x2 magic2 = pack2(kMagic, kMagic);
+    for (int64_t tile = (int64_t)blockIdx.x * kUnpackWarps + (threadIdx.x >> 5); tile < n_tiles;
+         tile += warp_stride) {
+        const int64_t tile_e0 = tile * kTileElems;
+        const int remain = (int)((n_elems - tile_e0) < kTileElems ? (n_elems - tile_e0) : kTileElems);
+        const uint32_t* p_tile = packed + tile * (kTileElems * BITS / 32);
+        const float* s_tile = scale + (tile_e0 >> log2_gs);
+        const float* m_tile = mn + (tile_e0 >> log2_gs);
+        float* y_tile = y + tile_e0;
+        uint32_t w[8];
+        float s[8], m[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const int e = k * 128 + lane * 4;
+            if (e < remain) {
+                w[k] = __ldg(p_tile + ((e * BITS) >> 5)) >> ((e * BITS) & 31);
+                s[k] = __ldg(s_tile + (e >> log2_gs));
+                m[k] = __ldg(m_tile + (e >> log2_gs));
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const int e = k * 128 + lane * 4;
+            if (e >= remain) continue;
+            const f32x2 s2 = pack2(s[k], s[k]), m2 = pack2(m[k], m[k]);
+            uint32_t o[4];
+#pragma unroll
+            for (int p = 0; p < 2; ++p) {
+                const f32x2 c2 = sub2_rn(pack2u(((w[k] >> (2 * p * BITS)) & MASK) | kMagicBits,
+                                                ((w[k] >> ((2 * p + 1) * BITS)) & MASK) | kMagicBits), magic2);
+                unpack2u(fma2_rn(c2, s2, m2), o[2 * p], o[2 * p + 1]);
+            }
+            stg_stream_v4(y_tile + e, make_uint4(o[0], o[1], o[2], o[3]));
+        }
+    }
+}
+
 // ---- int8 <-> bits -----------------------------------------------------------
 // A lane owns 16 consecutive int8 values (one 16-byte vector) = 2*BITS bytes of
 // packed output; 32-element word boundaries are respected because 16 | 32/BITS*BITS.
@@ -204,6 +254,20 @@ static void launch_unpack_one(const uint8_t* p, const float* s, const float* m, 
         per_sm = n;
     }
     const int64_t tiles = (n_elems + kTileElems - 1) / kTileElems;
+    if (DT == ACT_DTYPE_F32) {
+        // fully coalesced fp32 stores (needs the packed words 4-byte aligned, checked by the caller)
+        static int per_sm_f32 = 0;
+        if (per_sm_f32 == 0) {
+            int n = 0;
+            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, dequant_unpack_f32_kernel<BITS>,
+                                                              kUnpackThreads, 0) != cudaSuccess || n < 1) n = 1;
+            per_sm_f32 = n;
+        }
+        const int grid = stream_grid_for((tiles + kUnpackWarps - 1) / kUnpackWarps, per_sm_f32);
+        dequant_unpack_f32_kernel<BITS><<<grid, kUnpackThreads, 0, st>>>(
+            reinterpret_cast<const uint32_t*>(p), s, m, reinterpret_cast<float*>(y), n_elems, log2_gs);
+        return;
+    }
     const int grid = stream_grid_for((tiles + kUnpackWarps - 1) / kUnpackWarps, per_sm);
     dequant_unpack_kernel<DT, BITS><<<grid, kUnpackThreads, 0, st>>>(p, s, m, y, n_elems, log2_gs);
 }
