@@ -21,7 +21,9 @@ os.environ.setdefault("TRITON_INTERPRET", "1")
 import numpy as np
 import torch
 
-ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    raise SystemExit("usage: make_reference_fixtures.py /path/to/Deep_Optimization")
+ref_root = sys.argv[1]
 sys.path.insert(0, os.path.join(ref_root, "Activation_Compression"))
 import act_triton_kernel as ref  # noqa: E402
 from triton.language.extra import libdevice  # noqa: E402
