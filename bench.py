@@ -124,11 +124,12 @@ def make_inputs(seed: int):
 def cpu_baseline(x_host, threads: int, reps: int = 3, fraction: int = 4):
     """Times the CPU oracle on the first 1/fraction of the workload's groups."""
     import numpy as np
+    import torch
     from oracle import act_oracle as oracle
     oracle.set_threads(threads)
     arr = x_host.view(-1, GROUP)
     n_groups = arr.shape[0] // fraction
-    arr = arr[:n_groups].contiguous().view(__import__("torch").int16).numpy().view(np.uint16)
+    arr = arr[:n_groups].contiguous().view(torch.int16).numpy().view(np.uint16)
     best = float("inf")
     for _ in range(reps):
         t0 = time.perf_counter()

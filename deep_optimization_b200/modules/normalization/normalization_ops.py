@@ -148,11 +148,9 @@ class _DOBatchNorm(Function):
         return dx.to(dy.dtype), dw, db, None, None, None, None, None, None, None, None, None
 
 
-class _DOSyncBatchNorm(Function):
-    @staticmethod
-    def forward(ctx, input, weight, bias, running_mean, running_var, eps, momentum, process_group,
-                world_size, target_name, meta, ema_grad_meta):
-        raise RuntimeError("use _DOSyncBatchNorm.apply")
+class _DOSyncBatchNorm:
+    """Entry with the reference's argument order for the cross-rank variant
+    (normalization_ops.py:174-340 there); the work is `_DOBatchNorm` with a process group."""
 
     @staticmethod
     def apply(input, weight, bias, running_mean, running_var, eps, momentum, process_group,

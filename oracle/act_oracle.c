@@ -175,10 +175,33 @@ static int valid_group(int gs, int bits) {
 
 /* x: [n_groups, group_size] of dtype; packed: n_groups*group_size*bits/32 words;
  * scale,mn: [n_groups].  Returns 0, or 1 on a bad argument.                   */
+static int quant_pack_from(const void *x, int dtype, int64_t n_groups, int group_size,
+                           int bits, const float *noise, uint64_t seed, uint64_t offset,
+                           int flags, float clamp_alpha, uint32_t *packed, float *scale,
+                           float *mn_out, int64_t first_group);
+
 ORACLE_EXPORT int oracle_quant_pack(const void *x, int dtype, int64_t n_groups, int group_size,
                                     int bits, const float *noise, uint64_t seed, uint64_t offset,
                                     int flags, float clamp_alpha, uint32_t *packed, float *scale,
                                     float *mn_out) {
+    return quant_pack_from(x, dtype, n_groups, group_size, bits, noise, seed, offset, flags, clamp_alpha,
+                           packed, scale, mn_out, 0);
+}
+
+/* The same for a slice of a larger tensor: x, noise and the outputs start at group
+ * `first_group` of that tensor, whose element indices feed the counter hash. */
+ORACLE_EXPORT int oracle_quant_pack_slice(const void *x, int dtype, int64_t n_groups, int group_size,
+                                          int bits, const float *noise, uint64_t seed, uint64_t offset,
+                                          int flags, float clamp_alpha, uint32_t *packed, float *scale,
+                                          float *mn_out, int64_t first_group) {
+    return quant_pack_from(x, dtype, n_groups, group_size, bits, noise, seed, offset, flags, clamp_alpha,
+                           packed, scale, mn_out, first_group);
+}
+
+static int quant_pack_from(const void *x, int dtype, int64_t n_groups, int group_size,
+                           int bits, const float *noise, uint64_t seed, uint64_t offset,
+                           int flags, float clamp_alpha, uint32_t *packed, float *scale,
+                           float *mn_out, int64_t first_group) {
     if (!valid_bits(bits) || !valid_group(group_size, bits) || dtype < 0 || dtype > 2) return 1;
     const int qmax = (1 << bits) - 1;
     const int vpw = 32 / bits;
@@ -237,7 +260,7 @@ ORACLE_EXPORT int oracle_quant_pack(const void *x, int dtype, int64_t n_groups, 
                     float u;
                     if (flags & FLAG_ROUND_NEAREST) u = half_c;
                     else if (noise) u = noise[base + i];
-                    else u = hash_noise((uint64_t)(base + i), seed, offset);
+                    else u = hash_noise((uint64_t)(first_group * group_size + base + i), seed, offset);
                     const float q = a / s;
                     const float t = q + u;
                     c = code_from_t(t, qmax);

@@ -57,6 +57,7 @@ def lib() -> ctypes.CDLL:
         vp, i32, i64, u64, f32 = (ctypes.c_void_p, ctypes.c_int, ctypes.c_int64,
                                   ctypes.c_uint64, ctypes.c_float)
         L.oracle_quant_pack.argtypes = [vp, i32, i64, i32, i32, vp, u64, u64, i32, f32, vp, vp, vp]
+        L.oracle_quant_pack_slice.argtypes = [vp, i32, i64, i32, i32, vp, u64, u64, i32, f32, vp, vp, vp, i64]
         L.oracle_dequant_unpack.argtypes = [vp, vp, vp, i64, i32, i32, i32, vp]
         L.oracle_pack_bits.argtypes = [vp, i64, i32, i32, vp]
         L.oracle_unpack_bits.argtypes = [vp, i64, i32, i32, vp]
@@ -102,9 +103,10 @@ def num_threads() -> int:
 
 def quant_pack(x: np.ndarray, group_size: int, bits: int, noise: np.ndarray | None = None,
                seed: int = 0, offset: int = 0, flags: int = 0, clamp_alpha: float = 0.0,
-               dtype: str | None = None):
+               dtype: str | None = None, first_group: int = 0):
     """x: any shape whose element count is a multiple of group_size (row-major groups).
-    Returns (packed uint32 [NG, group_size*bits/32], scale f32 [NG], min f32 [NG])."""
+    Returns (packed uint32 [NG, group_size*bits/32], scale f32 [NG], min f32 [NG]).
+    `first_group` places x as a slice of a larger tensor (it shifts the hash counters)."""
     x = np.ascontiguousarray(x)
     code = _dtype_code(x, dtype)
     ng, rem = divmod(x.size, group_size)
@@ -115,8 +117,8 @@ def quant_pack(x: np.ndarray, group_size: int, bits: int, noise: np.ndarray | No
     if noise is not None:
         noise = np.ascontiguousarray(noise, np.float32)
         assert noise.size == x.size
-    rc = lib().oracle_quant_pack(_ptr(x), code, ng, group_size, bits, _ptr(noise), seed, offset,
-                                 flags, clamp_alpha, _ptr(packed), _ptr(scale), _ptr(mn))
+    rc = lib().oracle_quant_pack_slice(_ptr(x), code, ng, group_size, bits, _ptr(noise), seed, offset,
+                                       flags, clamp_alpha, _ptr(packed), _ptr(scale), _ptr(mn), first_group)
     if rc:
         raise ValueError(f"oracle_quant_pack rejected bits={bits} group_size={group_size}")
     return packed, scale, mn

@@ -231,3 +231,36 @@ def test_cuda_graph_capture_and_replay(oracle, cuda_device):
     _cmp_pack(oracle, outs, want, "graph replay")
     wy = oracle.dequant_unpack(*want, 128, 2, out="bf16")
     assert np.array_equal(to_numpy(y)[0], wy)
+
+
+def test_beyond_32bit_indices(oracle, cuda_device):
+    """Maximum sizes: 2^34 + 2^20 bf16 elements (34 GB), so element indices pass 2^32 and the
+    hash counters pass 2^32 as well.  Checked against the oracle on the first and on the last
+    2^20 elements (the oracle is told where the slice sits), plus group minima everywhere."""
+    free, _ = torch.cuda.mem_get_info(cuda_device)
+    n_tail = 1 << 20
+    n = (1 << 34) + n_tail
+    if free < n * 2 * 1.4:
+        pytest.skip("not enough free device memory for the 34 GB case")
+    base = relu_normal((n_tail,), seed=9, dtype=torch.bfloat16).to(cuda_device)
+    x = base.repeat(n // n_tail)
+    assert x.numel() == n
+    x[-n_tail:] = x[-n_tail:] * 0.5 + 0.25             # make the tail differ from the head
+    c = _codec()
+    gs, bits = 128, 2
+    packed, scale, mn = c.quant_pack(x, bits, gs, seed=77, offset=5)
+    ng_tail = n_tail // gs
+    for first in (0, (n - n_tail) // gs):
+        sl = x[first * gs: first * gs + n_tail]
+        arr, tag = to_numpy(sl)
+        want = oracle.quant_pack(arr, gs, bits, dtype=tag, seed=77, offset=5, first_group=first)
+        got = (packed[first: first + ng_tail], scale[first: first + ng_tail], mn[first: first + ng_tail])
+        _cmp_pack(oracle, got, want, f"slice at group {first}")
+    # size-independent property on the whole tensor, in slabs to bound temporary memory
+    slab = 1 << 28
+    for s0 in range(0, n, slab * 8):
+        xs = x[s0: s0 + slab].float().view(-1, gs)
+        assert torch.equal(mn[s0 // gs: s0 // gs + xs.shape[0]], xs.amin(1))
+    y = c.dequant_unpack(packed[-ng_tail:], scale[-ng_tail:], mn[-ng_tail:], bits, gs, out_dtype=torch.float32)
+    err = (y - x[-n_tail:].float().view(-1, gs)).abs()
+    assert (err <= scale[-ng_tail:, None] * 1.0001 + 1e-6).all()
