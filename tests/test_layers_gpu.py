@@ -108,3 +108,21 @@ def test_controller_end_to_end_step(cuda_device):
         opt.zero_grad(); loss.backward(); opt.step()
         losses.append(loss.item())
     assert all(l == l for l in losses) and min(losses[-3:]) < losses[0] - 0.05   # 2-bit activations still train
+
+
+def test_cpp_extension_mirror(cuda_device):
+    from deep_optimization_b200 import cpp_extension as cx
+    x = torch.relu(torch.randn(4, 6, 256, device=cuda_device)).to(torch.bfloat16)
+    for bits, pack, unpack in ((2, cx.pack2, cx.unpack2), (8, cx.pack8, cx.unpack8)):
+        out = torch.zeros(4 * 6 * 8 * bits, dtype=torch.int32, device=cuda_device)
+        scaler = torch.empty(4, 6, dtype=torch.bfloat16, device=cuda_device)
+        mn = torch.empty(24, dtype=torch.bfloat16, device=cuda_device)
+        pack(x, out, scaler, mn, 0.9)
+        y = torch.empty(4, 6, 256, dtype=torch.bfloat16, device=cuda_device)
+        unpack(out, y, scaler, mn, 4, 6, 4)
+        step = scaler.float().view(4, 6, 1)
+        assert ((y.float() - x.float()).abs() <= step * 1.05 + 0.02).all()
+    lo, hi = cx.min_max_kernel(x)
+    assert torch.equal(lo, x.float().amin(-1)) and torch.equal(hi, x.float().amax(-1))
+    with pytest.raises(NotImplementedError):
+        cx.pack3(x, None, None, None, 0.0)
