@@ -56,23 +56,8 @@ __host__ __device__ inline uint64_t hash_key(uint64_t seed) {
     return z ^ (z >> 31);
 }
 
-// Four rounds of a 2x32 multiply-xor network: 64 output bits per 64-bit counter.
-__device__ __forceinline__ void hash_2x32(uint64_t ctr, uint32_t key_lo, uint32_t key_hi,
-                                          uint32_t& o0, uint32_t& o1) {
-    uint32_t L = (uint32_t)ctr;
-    uint32_t R = (uint32_t)(ctr >> 32) ^ key_hi;
-    uint32_t k = key_lo;
-#pragma unroll
-    for (int r = 0; r < kHashRounds; ++r) {
-        const uint64_t p = (uint64_t)kHashMul * (uint64_t)L;      // one wide multiply
-        L = (uint32_t)(p >> 32) ^ k ^ R;
-        R = (uint32_t)p;
-        k += kHashWeyl;
-    }
-    o0 = L; o1 = R;
-}
-
-// the same network with the counter already split and key_hi folded into ctr_hi
+// Four rounds of a 2x32 multiply-xor network: 64 output bits per 64-bit counter,
+// the counter already split and key_hi folded into ctr_hi
 __device__ __forceinline__ void hash_2x32_split(uint32_t ctr_lo, uint32_t ctr_hi_x_key, uint32_t key_lo,
                                                 uint32_t& o0, uint32_t& o1) {
     uint32_t L = ctr_lo, R = ctr_hi_x_key, k = key_lo;
@@ -84,14 +69,6 @@ __device__ __forceinline__ void hash_2x32_split(uint32_t ctr_lo, uint32_t ctr_hi
         k += kHashWeyl;
     }
     o0 = L; o1 = R;
-}
-
-// 16-bit field -> float holding the integer h exactly (2^23 + h, minus 2^23)
-__device__ __forceinline__ float u16_lo_as_float(uint32_t w) {
-    return __uint_as_float(__byte_perm(w, kMagicBits, 0x7410)) - kMagic;
-}
-__device__ __forceinline__ float u16_hi_as_float(uint32_t w) {
-    return __uint_as_float(__byte_perm(w, kMagicBits, 0x7432)) - kMagic;
 }
 
 // ---- packed fp32 pairs (sm_100 f32x2 instructions: one issue slot, two lanes) ----

@@ -25,9 +25,17 @@
  *     r  = mx - mn
  *     s  = r / qmax ; if !(s > 0) s = 1
  *     a  = x - mn ; q = a / s ; t = q + u ; code = clamp(floor(t), 0, qmax)
- * u is the caller's noise tensor, the 16-bit counter hash below, or the
- * constant 0.5f-1e-6f (round to nearest, the reference's constant,
- * act_triton_kernel.py:114).
+ * u is the caller's noise tensor or the constant 0.5f-1e-6f (round to nearest,
+ * the reference's constant, act_triton_kernel.py:114).
+ *
+ * With neither (the "hash" mode, the product's default) the noise is one byte h
+ * per element from the counter hash below, and a regular group -- range 0 or in
+ * [2^-50, 2^50] -- is quantised in fixed point with 8 fraction bits:
+ *     y = 1 / s ; Q = RNE(a * y * 256), rounded once (v = fmaf(a, y, 2^15) and
+ *     Q = the low mantissa bits of v) ; code = (Q + h) >> 8        (<= qmax, no clamp)
+ * i.e. stochastic rounding of Q/256 with 8 noise bits.  An irregular group
+ * (denormal, huge, infinite or NaN range) uses the float formula above with
+ * u = h / 256.
  *
  * The "reference-compatible" scheme (ACT_FLAG_REF_COMPAT) follows the live
  * Triton kernel instead: optional clamp to +-alpha, optional tanh squash,
@@ -41,7 +49,7 @@
  * outputs of the reference's own kernels run under Triton's CPU interpreter
  * (tests/golden/reference_triton_codec.npz and the script beside it).  The
  * baseline scheme shares layout and clamp/degenerate rules with it; its true
- * division, noise and counter hash have no counterpart in any reference test:
+ * division, fixed-point hash mode and counter hash have no counterpart in any reference test:
  * for those the parity is unpinned by the reference and rests on the two
  * independent restatements (C and numpy) agreeing.
  *
@@ -112,12 +120,12 @@ static inline float max_ord(float a, float b) {
 }
 
 /* ------------------------------------------------------------ noise hash
- * Counter hash used when no noise tensor is given.  Four consecutive elements
- * share one 64-bit output; element e takes 16-bit field (e & 3) of
- * H(e >> 2) and u = field / 65536.  H is four rounds of a 2x32 multiply-xor
- * network keyed by splitmix64(splitmix64(seed) + offset): seed picks a family
- * of streams, offset one stream of it (callers advance it per call).  It has no counterpart in the
- * reference (whose generators are an index hash in
+ * Counter hash used when no noise tensor is given.  Eight consecutive elements
+ * (one 16-byte piece of 16-bit inputs) share one 64-bit output; element e takes
+ * byte (e & 7) of H(e >> 3), low word first.  H is four rounds of a 2x32
+ * multiply-xor network keyed by splitmix64(splitmix64(seed) + offset): seed picks
+ * a family of streams, offset one stream of it (callers advance it per call).
+ * It has no counterpart in the reference (whose generators are an index hash in
  * cpp_extension/include/quant_common.h:32-43 and Triton's tl.rand).          */
 #define HASH_MUL   0xD256D193u
 #define HASH_WEYL  0x9E3779B9u
@@ -147,17 +155,18 @@ static inline void hash_2x32(uint64_t ctr, uint64_t seed, uint64_t offset, uint3
     *o0 = L; *o1 = R;
 }
 
-static inline float hash_noise(uint64_t elem, uint64_t seed, uint64_t offset) {
+static inline uint32_t hash_byte(uint64_t elem, uint64_t seed, uint64_t offset) {
     uint32_t w0, w1;
-    hash_2x32(elem >> 2, seed, offset, &w0, &w1);
-    uint32_t w = (elem & 2) ? w1 : w0;
-    uint32_t h = (elem & 1) ? (w >> 16) : (w & 0xffffu);
-    return (float)h * (1.0f / 65536.0f);
+    hash_2x32(elem >> 3, seed, offset, &w0, &w1);
+    const uint32_t w = (elem & 4) ? w1 : w0;
+    return (w >> (8 * (elem & 3))) & 0xffu;
 }
 
+/* the noise as a fraction: h / 256 */
 ORACLE_EXPORT void oracle_hash_noise(uint64_t seed, uint64_t offset, int64_t first,
                                      int64_t count, float *out) {
-    for (int64_t i = 0; i < count; ++i) out[i] = hash_noise((uint64_t)(first + i), seed, offset);
+    for (int64_t i = 0; i < count; ++i)
+        out[i] = (float)hash_byte((uint64_t)(first + i), seed, offset) * (1.0f / 256.0f);
 }
 
 /* ------------------------------------------------------------- quant-pack */
@@ -237,6 +246,7 @@ static int quant_pack_from(const void *x, int dtype, int64_t n_groups, int group
 
         uint32_t *pw = packed + g * (int64_t)nwords;
         const float inv = 1.0f / s;
+        const int regular = (r == 0.0f) || (r >= 0x1p-50f && r <= 0x1p50f);
         for (int w = 0; w < nwords; ++w) {
             uint32_t word = 0;
             for (int j = 0; j < vpw; ++j) {
@@ -256,14 +266,22 @@ static int quant_pack_from(const void *x, int dtype, int64_t n_groups, int group
                         if (c < 0) c = 0;
                         if (c > qmax) c = qmax;
                     }
-                } else {
-                    float u;
-                    if (flags & FLAG_ROUND_NEAREST) u = half_c;
-                    else if (noise) u = noise[base + i];
-                    else u = hash_noise((uint64_t)(first_group * group_size + base + i), seed, offset);
+                } else if ((flags & FLAG_ROUND_NEAREST) || noise) {
+                    const float u = (flags & FLAG_ROUND_NEAREST) ? half_c : noise[base + i];
                     const float q = a / s;
                     const float t = q + u;
                     c = code_from_t(t, qmax);
+                } else {
+                    const uint32_t h = hash_byte((uint64_t)(first_group * group_size + base + i), seed, offset);
+                    if (regular) {
+                        /* one rounding onto the 2^-8 grid; 2^15 <= v < 2^16 for a regular group */
+                        const float v = fmaf(a, inv, 32768.0f);
+                        const uint32_t Q = f32_bits(v) - f32_bits(32768.0f);
+                        c = (int)((Q + h) >> 8);
+                    } else {
+                        const float t = a / s + (float)h * (1.0f / 256.0f);
+                        c = code_from_t(t, qmax);
+                    }
                 }
                 word |= (uint32_t)c << (j * bits);
             }

@@ -232,10 +232,10 @@ def _as_f32(x: np.ndarray, dtype: str | None) -> np.ndarray:
     return x.astype(np.float32)
 
 
-def np_hash_noise(seed: int, offset: int, first: int, count: int) -> np.ndarray:
-    """numpy restatement of the 16-bit counter hash (act_oracle.c: hash_2x32)."""
+def np_hash_bytes(seed: int, offset: int, first: int, count: int) -> np.ndarray:
+    """numpy restatement of the counter hash (act_oracle.c: hash_byte): one noise byte per element."""
     e = np.arange(first, first + count, dtype=np.uint64)
-    ctr = e >> np.uint64(2)
+    ctr = e >> np.uint64(3)
     M64 = 0xFFFFFFFFFFFFFFFF
 
     def splitmix(v):
@@ -253,9 +253,13 @@ def np_hash_noise(seed: int, offset: int, first: int, count: int) -> np.ndarray:
         hi, lo = p >> np.uint64(32), p & np.uint64(0xFFFFFFFF)
         L, R = (hi ^ np.uint64(k) ^ R) & np.uint64(0xFFFFFFFF), lo
         k = (k + 0x9E3779B9) & 0xFFFFFFFF
-    w = np.where((e & np.uint64(2)) != 0, R, L)
-    h = np.where((e & np.uint64(1)) != 0, w >> np.uint64(16), w & np.uint64(0xFFFF))
-    return h.astype(np.float32) * np.float32(1.0 / 65536.0)
+    w = np.where((e & np.uint64(4)) != 0, R, L)
+    return ((w >> (np.uint64(8) * (e & np.uint64(3)))) & np.uint64(0xFF)).astype(np.uint32)
+
+
+def np_hash_noise(seed: int, offset: int, first: int, count: int) -> np.ndarray:
+    """The hash noise as a fraction, h / 256."""
+    return np_hash_bytes(seed, offset, first, count).astype(np.float32) * np.float32(1.0 / 256.0)
 
 
 def np_group_minmax(v: np.ndarray):
@@ -295,15 +299,28 @@ def np_quant_pack(x: np.ndarray, group_size: int, bits: int, noise: np.ndarray |
             t = ((a * inv[:, None]).astype(np.float32) + HALF_C).astype(np.float32)
             codes = np.clip(np.trunc(t), 0, qmax).astype(np.uint32)
         else:
+            hashed = not (flags & FLAG_ROUND_NEAREST) and noise is None
             if flags & FLAG_ROUND_NEAREST:
                 u = np.full(v.shape, HALF_C, np.float32)
             elif noise is not None:
                 u = np.ascontiguousarray(noise, np.float32).reshape(v.shape)
             else:
-                u = np_hash_noise(seed, offset, 0, v.size).reshape(v.shape)
+                h = np_hash_bytes(seed, offset, 0, v.size).reshape(v.shape)
+                u = h.astype(np.float32) * np.float32(1.0 / 256.0)
             q = (a / s[:, None]).astype(np.float32)
             t = (q + u).astype(np.float32)
             codes = np.where(t >= 0, np.minimum(np.floor(t), qmax), 0).astype(np.uint32)
+            if hashed:
+                # regular groups: Q = RNE(a * (1/s) * 256) from the exact float64 product,
+                # code = (Q + h) >> 8; the others keep the float formula above
+                inv = (np.float32(1.0) / s).astype(np.float32)
+                z = a.astype(np.float64) * inv[:, None].astype(np.float64) * 256.0
+                fl = np.floor(z)
+                frac = z - fl
+                Q = fl + ((frac > 0.5) | ((frac == 0.5) & (np.mod(fl, 2) == 1)))
+                fx = ((Q.astype(np.int64) + h.astype(np.int64)) >> 8).astype(np.uint32)
+                regular = (r == 0) | ((r >= np.float32(2.0 ** -50)) & (r <= np.float32(2.0 ** 50)))
+                codes = np.where(regular[:, None], fx, codes)
     shifts = (np.arange(vpw, dtype=np.uint32) * np.uint32(bits))
     words = (codes.reshape(ng, group_size // vpw, vpw) << shifts).sum(axis=2, dtype=np.uint64)
     packed = words.astype(np.uint32)

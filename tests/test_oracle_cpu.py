@@ -93,6 +93,46 @@ def test_hash_noise_restatement(oracle):
         assert np.array_equal(oracle.hash_noise(seed, off, 3, 4099), oracle.np_hash_noise(seed, off, 3, 4099))
 
 
+def test_hash_noise_statistics(oracle):
+    """The noise bytes are uniform, free of pair structure at the lags the kernel's lane
+    layout produces, and unrelated across seeds and offsets (chi-square with 255 degrees of
+    freedom: mean 255, sd 22.6; the bound is mean + 5.5 sd)."""
+    n = 1 << 21
+    bound = 255 + 5.5 * 22.6
+    chi = lambda c, e: float(((c - e) ** 2 / e).sum())
+    streams = {}
+    for seed, off in ((0, 0), (1, 0), (0, 1), (12345, 999), (7, 2**40)):
+        h = oracle.np_hash_bytes(seed, off, 0, n).astype(np.int64)
+        streams[(seed, off)] = h
+        assert chi(np.bincount(h, minlength=256), n / 256) < bound
+        for lag in (1, 2, 3, 4, 7, 8, 9, 16, 64, 128, 1024):
+            c = np.bincount((h[:-lag] >> 4) * 16 + (h[lag:] >> 4), minlength=256)
+            assert chi(c, (n - lag) / 256) < bound, (seed, off, lag)
+            c = np.bincount((h[:-lag] & 15) * 16 + (h[lag:] & 15), minlength=256)
+            assert chi(c, (n - lag) / 256) < bound, (seed, off, lag)
+        u = h / 256.0
+        assert abs(u.mean() - 255 / 512) < 4 * 0.2887 / np.sqrt(n)
+    keys = list(streams)
+    for i in range(len(keys)):
+        for j in range(i + 1, len(keys)):
+            a, b = streams[keys[i]], streams[keys[j]]
+            assert abs(np.corrcoef(a, b)[0, 1]) < 5 / np.sqrt(n)
+            c = np.bincount((a >> 4) * 16 + (b >> 4), minlength=256)
+            assert chi(c, n / 256) < bound
+
+
+def test_hash_mode_is_unbiased_fixed_point(oracle):
+    """In hash mode the mean code over many noise streams is Q/256 = RNE(q*256)/256."""
+    x = np.linspace(0.0, 1.0, 128, dtype=np.float32).reshape(1, 128)
+    acc = np.zeros(128)
+    reps = 4000
+    for off in range(reps):
+        p, s, mn = oracle.quant_pack(x, 128, 2, seed=3, offset=off)
+        acc += oracle.np_unpack_codes(p, 128, 2)[0]
+    q = (x[0] - mn[0]) / s[0]
+    assert np.abs(acc / reps - q).max() < 4 * 0.5 / np.sqrt(reps) + 1 / 256
+
+
 def test_exact_fma_agrees(oracle):
     rng = np.random.default_rng(1)
     s = rng.random(200).astype(np.float32)
