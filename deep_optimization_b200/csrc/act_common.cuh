@@ -40,6 +40,32 @@ __device__ __forceinline__ void stg_stream_v4(void* p, uint4 v) {
                  :: "l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
+// Programmatic dependent launch.  A kernel started with launch_overlapped() may become
+// resident while the kernel before it in the stream is still draining; it must call
+// grid_dependency_wait() before its first global access (the wait returns once the earlier
+// grid has completed and its writes are visible; without the launch attribute it is a no-op),
+// and it lets its own successor in with grid_launch_dependents().
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+#ifndef ACT_NO_PDL
+#define ACT_NO_PDL 0
+#endif
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_overlapped(void (*kernel)(KArgs...), int grid, int block, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid, 1, 1);
+    cfg.blockDim = dim3((unsigned)block, 1, 1);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ACT_NO_PDL ? 0 : 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // NaN-propagating fp32 min/max; -0 orders below +0
 __device__ __forceinline__ float fmin_nan(float a, float b) {
     float d; asm("min.NaN.f32 %0, %1, %2;" : "=f"(d) : "f"(a), "f"(b)); return d;

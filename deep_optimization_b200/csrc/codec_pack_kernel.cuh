@@ -404,6 +404,8 @@ quant_pack_kernel(const void* __restrict__ x_, const float* __restrict__ noise,
 
     int64_t tile = (int64_t)blockIdx.x * kPackWarps + warp;
     RawTile<DT> raw_a, raw_b;
+    grid_dependency_wait();
+    grid_launch_dependents();
     if (tile < n_full) load_tile(raw_a, tile);
 
     // raw_cur holds this tile, raw_next receives the following one while this one is encoded
@@ -624,10 +626,10 @@ cudaError_t launch_pack_one(const void* x, const float* noise, void* packed, flo
     const int64_t n_tiles = (n_elems + kTileElems - 1) / kTileElems;
     // persistent grid: exactly the resident blocks of one wave (or fewer for small inputs)
     const int grid = stream_grid_for((n_tiles + PackCfg<DT>::warps - 1) / PackCfg<DT>::warps, pack_blocks_per_sm<DT, BITS, NM>());
-    quant_pack_kernel<DT, BITS, NM><<<grid, PackCfg<DT>::threads, 0, st>>>(
-        x, noise, static_cast<uint8_t*>(packed), scale, mn, n_elems, log2_L,
-        (uint32_t)key, (uint32_t)(key >> 32), flags, clamp_alpha);
-    return cudaGetLastError();
+    return launch_overlapped(quant_pack_kernel<DT, BITS, NM, kProNone>, grid, PackCfg<DT>::threads, st,
+                             x, noise, static_cast<uint8_t*>(packed), scale, mn, n_elems, log2_L,
+                             (uint32_t)key, (uint32_t)(key >> 32), flags, clamp_alpha,
+                             static_cast<uint8_t*>(nullptr), BNArgs{nullptr, 1u, 1u, 0u, 0u});
 }
 
 template <int DT, int BITS>
@@ -676,10 +678,10 @@ cudaError_t launch_fused_one(const void* x, void* y, void* packed, float* scale,
     const uint64_t key = hash_key(hash_key(seed) + offset);
     const int64_t n_tiles = (n_elems + kTileElems - 1) / kTileElems;
     const int grid = stream_grid_for((n_tiles + PackCfg<DT>::warps - 1) / PackCfg<DT>::warps, per_sm);
-    quant_pack_kernel<DT, BITS, NM, PRO><<<grid, PackCfg<DT>::threads, 0, st>>>(
-        x, nullptr, static_cast<uint8_t*>(packed), scale, mn, n_elems, log2_L,
-        (uint32_t)key, (uint32_t)(key >> 32), 0, 0.0f, static_cast<uint8_t*>(y));
-    return cudaGetLastError();
+    return launch_overlapped(quant_pack_kernel<DT, BITS, NM, PRO>, grid, PackCfg<DT>::threads, st,
+                             x, static_cast<const float*>(nullptr), static_cast<uint8_t*>(packed), scale, mn,
+                             n_elems, log2_L, (uint32_t)key, (uint32_t)(key >> 32), 0, 0.0f,
+                             static_cast<uint8_t*>(y), BNArgs{nullptr, 1u, 1u, 0u, 0u});
 }
 
 template <int DT, int BITS>
@@ -731,10 +733,10 @@ cudaError_t launch_bn_one(const void* x, void* y, void* packed, float* scale, fl
     const uint64_t key = hash_key(hash_key(seed) + offset);
     const int64_t n_tiles = (n_elems + kTileElems - 1) / kTileElems;
     const int grid = stream_grid_for((n_tiles + PackCfg<DT>::warps - 1) / PackCfg<DT>::warps, per_sm);
-    quant_pack_kernel<DT, BITS, NM, kProBN><<<grid, PackCfg<DT>::threads, 0, st>>>(
-        x, nullptr, static_cast<uint8_t*>(packed), scale, mn, n_elems, log2_L,
-        (uint32_t)key, (uint32_t)(key >> 32), 0, 0.0f, static_cast<uint8_t*>(y), bn);
-    return cudaGetLastError();
+    return launch_overlapped(quant_pack_kernel<DT, BITS, NM, kProBN>, grid, PackCfg<DT>::threads, st,
+                             x, static_cast<const float*>(nullptr), static_cast<uint8_t*>(packed), scale, mn,
+                             n_elems, log2_L, (uint32_t)key, (uint32_t)(key >> 32), 0, 0.0f,
+                             static_cast<uint8_t*>(y), bn);
 }
 
 template <int DT>

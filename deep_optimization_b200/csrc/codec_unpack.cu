@@ -45,6 +45,8 @@ dequant_unpack_kernel(const uint8_t* __restrict__ packed, const float* __restric
     const int64_t n_tiles = (n_elems + kTileElems - 1) / kTileElems;
     const int64_t warp_stride = (int64_t)gridDim.x * kUnpackWarps;
     const f32x2 magic2 = pack2(kMagic, kMagic);
+    grid_dependency_wait();
+    grid_launch_dependents();
     for (int64_t tile = (int64_t)blockIdx.x * kUnpackWarps + (threadIdx.x >> 5); tile < n_tiles;
          tile += warp_stride) {
         // per-tile 64-bit bases; everything inside the tile is 32-bit arithmetic
@@ -116,6 +118,8 @@ dequant_unpack_f32_kernel(const uint32_t* __restrict__ packed, const float* __re
     const int64_t n_tiles = (n_elems + kTileElems - 1) / kTileElems;
     const int64_t warp_stride = (int64_t)gridDim.x * kUnpackWarps;
     const f32x2 magic2 = pack2(kMagic, kMagic);
+    grid_dependency_wait();
+    grid_launch_dependents();
     for (int64_t tile = (int64_t)blockIdx.x * kUnpackWarps + (threadIdx.x >> 5); tile < n_tiles;
          tile += warp_stride) {
         const int64_t tile_e0 = tile * kTileElems;
@@ -264,12 +268,12 @@ static void launch_unpack_one(const uint8_t* p, const float* s, const float* m, 
             per_sm_f32 = n;
         }
         const int grid = stream_grid_for((tiles + kUnpackWarps - 1) / kUnpackWarps, per_sm_f32);
-        dequant_unpack_f32_kernel<BITS><<<grid, kUnpackThreads, 0, st>>>(
-            reinterpret_cast<const uint32_t*>(p), s, m, reinterpret_cast<float*>(y), n_elems, log2_gs);
+        launch_overlapped(dequant_unpack_f32_kernel<BITS>, grid, kUnpackThreads, st,
+                          reinterpret_cast<const uint32_t*>(p), s, m, reinterpret_cast<float*>(y), n_elems, log2_gs);
         return;
     }
     const int grid = stream_grid_for((tiles + kUnpackWarps - 1) / kUnpackWarps, per_sm);
-    dequant_unpack_kernel<DT, BITS><<<grid, kUnpackThreads, 0, st>>>(p, s, m, y, n_elems, log2_gs);
+    launch_overlapped(dequant_unpack_kernel<DT, BITS>, grid, kUnpackThreads, st, p, s, m, y, n_elems, log2_gs);
 }
 
 template <int DT>
