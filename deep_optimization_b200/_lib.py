@@ -24,6 +24,7 @@ ACT_KIND_GELU, ACT_KIND_SILU = 1, 2
 # every symbol include/act_b200.h declares, with its ctypes signature
 _vp, _i32, _i64, _u64, _f32 = (ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_uint64,
                                ctypes.c_float)
+_f64, _sz = ctypes.c_double, ctypes.c_size_t
 SIGNATURES = {
     "act_quant_pack": ([_vp, _i32, _i64, _i32, _i32, _vp, _u64, _u64, _i32, _f32, _vp, _vp, _vp, _vp], _i32),
     "act_dequant_unpack": ([_vp, _vp, _vp, _i64, _i32, _i32, _i32, _vp, _vp], _i32),
@@ -34,6 +35,8 @@ SIGNATURES = {
     "act_relu_bwd_unpack": ([_vp, _vp, _i32, _i64, _vp, _vp], _i32),
     "act_mul_dequant_unpack": ([_vp, _vp, _vp, _vp, _i32, _i64, _i32, _i32, _vp, _vp], _i32),
     "act_bn_fwd_norm_quant_pack": ([_vp, _i32, _i64, _i32, _i64, _vp, _i32, _i32, _u64, _u64, _i32, _vp, _vp, _vp, _vp, _vp], _i32),
+    "act_bn_stats_workspace": ([_i64, _i32], _sz),
+    "act_bn_stats": ([_vp, _i32, _i64, _i32, _i64, _f64, _vp, _vp, _vp, _vp, _f64, _vp, _vp, _sz, _vp], _i32),
     "act_bn_bwd_reduce": ([_vp, _vp, _vp, _vp, _i32, _i64, _i32, _i64, _i32, _i32, _vp, _vp], _i32),
     "act_bn_bwd_dx": ([_vp, _vp, _vp, _vp, _i32, _i64, _i32, _i64, _i32, _i32, _vp, _vp, _vp], _i32),
     "act_minmax": ([_vp, _i32, _i64, _i64, _vp, _vp, _vp], _i32),

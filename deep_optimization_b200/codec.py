@@ -255,19 +255,51 @@ def bn_fused_supported(x: torch.Tensor, group_size: int) -> bool:
             and x.numel() % group_size == 0)
 
 
-def bn_fwd_norm_quant_pack(x: torch.Tensor, mean: torch.Tensor, invstd: torch.Tensor,
+def bn_stats(x: torch.Tensor, eps: float, weight: Optional[torch.Tensor] = None,
+             bias: Optional[torch.Tensor] = None, running_mean: Optional[torch.Tensor] = None,
+             running_var: Optional[torch.Tensor] = None, momentum: float = 0.0) -> torch.Tensor:
+    """Batch statistics of x [N, C, ...]: the fp32 [C, 4] table (mean, 1/sqrt(var+eps), weight,
+    bias) that bn_fwd_norm_quant_pack reads; fp32 running statistics are updated in place."""
+    x = x.contiguous()
+    N, C = x.shape[0], x.shape[1]
+    hw = x.numel() // (N * C)
+
+    def f32(t):
+        if t is None:
+            return None
+        if t.dtype != torch.float32 or not t.is_contiguous():
+            raise ValueError("bn_stats takes contiguous fp32 parameters and running statistics")
+        return t
+
+    weight, bias, running_mean, running_var = f32(weight), f32(bias), f32(running_mean), f32(running_var)
+    lib = _lib.load()
+    params = torch.empty((C, 4), dtype=torch.float32, device=x.device)
+    ws_bytes = int(lib.act_bn_stats_workspace(N, C))
+    ws = torch.empty((max(ws_bytes, 4) // 4,), dtype=torch.float32, device=x.device)
+    ptr = lambda t: None if t is None else t.data_ptr()
+    with torch.cuda.device(x.device):
+        rc = lib.act_bn_stats(x.data_ptr(), _DTYPES[x.dtype], N, C, hw, float(eps), ptr(weight), ptr(bias),
+                              ptr(running_mean), ptr(running_var), float(momentum), params.data_ptr(),
+                              ws.data_ptr(), ws_bytes, _stream_ptr(x))
+    _lib.check(rc, "act_bn_stats")
+    return params
+
+
+def bn_fwd_norm_quant_pack(x: torch.Tensor, mean: Optional[torch.Tensor], invstd: Optional[torch.Tensor],
                            weight: Optional[torch.Tensor], bias: Optional[torch.Tensor], bits: int,
                            group_size: int, seed: Optional[int] = None, offset: Optional[int] = None,
-                           flags: int = 0):
-    """y = (x - mean) * invstd * weight + bias and the packed x_hat: (y, packed, scale, min)."""
+                           flags: int = 0, params: Optional[torch.Tensor] = None):
+    """y = (x - mean) * invstd * weight + bias and the packed x_hat: (y, packed, scale, min).
+    `params` is bn_stats' table; without it the table is built from mean, invstd, weight, bias."""
     global _next_offset
     _, nwords, _ = _bits_consts(bits, group_size)
     x = x.contiguous()
     N, C = x.shape[0], x.shape[1]
     hw = x.numel() // (N * C)
-    ones = torch.ones_like(mean) if weight is None else weight.float()
-    zeros = torch.zeros_like(mean) if bias is None else bias.float()
-    params = torch.stack([mean.float(), invstd.float(), ones, zeros], dim=1).contiguous()
+    if params is None:
+        ones = torch.ones_like(mean) if weight is None else weight.float()
+        zeros = torch.zeros_like(mean) if bias is None else bias.float()
+        params = torch.stack([mean.float(), invstd.float(), ones, zeros], dim=1).contiguous()
     ng = x.numel() // group_size
     y = torch.empty_like(x)
     packed = torch.empty((ng, nwords), dtype=torch.int32, device=x.device)

@@ -1,0 +1,278 @@
+// Per-channel reductions of batch norm over x [N, C, HW], sm_100a.
+//
+//   act_bn_stats:       batch mean and inverse deviation of x (forward), written together with
+//                       the affine parameters as the [C][4] table the fused normalise+codec
+//                       kernel reads; running statistics updated in place
+//   act_bn_bwd_reduce:  sum(dy * x_hat) and sum(dy) per channel, x_hat decoded from the codec
+//
+// Both walk the tensor plane by plane: block (c, s) owns channel c and a slice of the batch,
+// its eight warps take the planes (n, c) of the slice in turn, the lanes stride over the
+// plane four elements at a time, and every lane accumulates in registers until the block's
+// slice is done, so there is one warp reduction per block instead of one per load.  Loads
+// are contiguous inside a plane (256 or 512 bytes per warp instruction).
+// HBM traffic: s_in bytes per element (plus bits/8 in backward); nothing is written but
+// 2 floats per block.
+//
+// Replaces: Activation_Compression/modules/normalization/kernel_implementation.py:13-92
+// (bn_fwd_reduce) and :328-420 (bn_bwd_reduce_dequant_unpack_fused), whose programs
+// accumulate with one atomic per tile.
+#include "act_common.cuh"
+
+namespace act {
+
+constexpr int kRedThreads = 256;
+constexpr int kRedWarps = kRedThreads / 32;
+
+// four consecutive elements starting at element e (a multiple of 4), widened to fp32
+template <int DT> __device__ __forceinline__ void load4(const uint8_t* p, int64_t e, float (&f)[4]) {
+    if (ElemT<DT>::bytes == 4) {
+        const uint4 v = ldg_stream_v4(p + e * 4);
+        f[0] = __uint_as_float(v.x); f[1] = __uint_as_float(v.y);
+        f[2] = __uint_as_float(v.z); f[3] = __uint_as_float(v.w);
+    } else {
+        uint2 v;
+        asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p + e * 2));
+        constexpr int D16 = (DT == ACT_DTYPE_F32) ? ACT_DTYPE_BF16 : DT;
+        f[0] = widen_lo<D16>(v.x); f[1] = widen_hi<D16>(v.x);
+        f[2] = widen_lo<D16>(v.y); f[3] = widen_hi<D16>(v.y);
+    }
+}
+
+template <int DT> __device__ __forceinline__ float load1(const uint8_t* p, int64_t e) {
+    if (ElemT<DT>::bytes == 4) return __ldg(reinterpret_cast<const float*>(p) + e);
+    constexpr int D16 = (DT == ACT_DTYPE_F32) ? ACT_DTYPE_BF16 : DT;
+    return widen_lo<D16>((uint32_t)__ldg(reinterpret_cast<const unsigned short*>(p) + e));
+}
+
+// the four BITS-bit codes of elements e..e+3 (e a multiple of 4)
+template <int BITS> __device__ __forceinline__ uint32_t load_codes4(const uint8_t* packed, int64_t e) {
+    if (BITS == 8) return __ldg(reinterpret_cast<const uint32_t*>(packed + e));
+    if (BITS == 4) return __ldg(reinterpret_cast<const unsigned short*>(packed + (e >> 1)));
+    if (BITS == 2) return __ldg(packed + (e >> 2));
+    return ((uint32_t)__ldg(packed + (e >> 3)) >> (uint32_t)(e & 4)) & 0xFu;
+}
+
+// MODE 0: a = sum(x - pivot), b = sum((x - pivot)^2), pivot = x[0, c, 0], written as the
+//         block's partial pair out[(c * S + s) * 2 + {0, 1}] (no atomics, no zeroing);
+// MODE 1: a = sum(dy * x_hat), b = sum(dy), added to out[c] and out[C + c].
+template <int DT, int MODE, int BITS>
+__global__ void __launch_bounds__(kRedThreads)
+bn_plane_reduce_kernel(const uint8_t* __restrict__ x, const uint8_t* __restrict__ packed,
+                       const float* __restrict__ scale, const float* __restrict__ mn,
+                       float* __restrict__ out, int64_t n_batch, uint32_t C, uint32_t hw, int log2_gs)
+{
+    __shared__ float s_part[kRedWarps][2];
+    const uint32_t c = blockIdx.x, s = blockIdx.y, S = gridDim.y;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int64_t n0 = n_batch * s / S, n1 = n_batch * (s + 1) / S;
+    const uint32_t vpp = hw >> 2;                           // four-element vectors per plane
+    grid_dependency_wait();
+    grid_launch_dependents();
+    const float pivot = (MODE == 0) ? load1<DT>(x, (int64_t)c * hw) : 0.0f;
+    float a = 0.0f, b = 0.0f;
+    for (int64_t n = n0 + warp; n < n1; n += kRedWarps) {
+        const int64_t plane_e0 = (n * C + c) * hw;
+#pragma unroll 4
+        for (uint32_t v = lane; v < vpp; v += 32) {
+            const int64_t e = plane_e0 + 4 * (int64_t)v;
+            float f[4];
+            load4<DT>(x, e, f);
+            if (MODE == 0) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float d = __fsub_rn(f[i], pivot);
+                    a = __fadd_rn(a, d);
+                    b = __fmaf_rn(d, d, b);
+                }
+            } else {
+                constexpr uint32_t MASK = (1u << BITS) - 1u;
+                const uint32_t w = load_codes4<BITS>(packed, e);
+                const int64_t g = e >> log2_gs;
+                const float sc = __ldg(scale + g), m = __ldg(mn + g);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float code = __uint_as_float(kMagicBits | ((w >> (i * BITS)) & MASK)) - kMagic;
+                    a = __fmaf_rn(f[i], __fmaf_rn(code, sc, m), a);
+                    b = __fadd_rn(b, f[i]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        a += __shfl_xor_sync(0xffffffffu, a, off);
+        b += __shfl_xor_sync(0xffffffffu, b, off);
+    }
+    if (lane == 0) { s_part[warp][0] = a; s_part[warp][1] = b; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float ta = 0.0f, tb = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kRedWarps; ++w) { ta += s_part[w][0]; tb += s_part[w][1]; }
+        if (MODE == 0) {
+            out[((int64_t)c * S + s) * 2] = ta;
+            out[((int64_t)c * S + s) * 2 + 1] = tb;
+        } else {
+            atomicAdd(out + c, ta);
+            atomicAdd(out + C + c, tb);
+        }
+    }
+}
+
+// One thread per channel: the block partials summed in a fixed order in double, then
+// mean = pivot + a/M, var = b/M - (a/M)^2 (biased), invstd = 1/sqrt(var + eps).
+template <int DT>
+__global__ void bn_stats_finalize_kernel(const uint8_t* __restrict__ x, const float* __restrict__ part,
+                                         const float* __restrict__ weight, const float* __restrict__ bias,
+                                         float* __restrict__ running_mean, float* __restrict__ running_var,
+                                         float4* __restrict__ params, int64_t n_batch, uint32_t C, uint32_t hw,
+                                         uint32_t S, double eps, double momentum)
+{
+    grid_dependency_wait();
+    grid_launch_dependents();
+    const uint32_t c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    double a = 0.0, b = 0.0;
+    for (uint32_t s = 0; s < S; ++s) {
+        a += (double)part[((int64_t)c * S + s) * 2];
+        b += (double)part[((int64_t)c * S + s) * 2 + 1];
+    }
+    const double M = (double)n_batch * (double)hw;
+    const double dm = a / M;
+    const double mean = (double)load1<DT>(x, (int64_t)c * hw) + dm;
+    double var = b / M - dm * dm;
+    if (!(var > 0.0)) var = 0.0;
+    const double invstd = 1.0 / sqrt(var + eps);
+    params[c] = make_float4((float)mean, (float)invstd, weight ? weight[c] : 1.0f, bias ? bias[c] : 0.0f);
+    if (running_mean) running_mean[c] = (float)((1.0 - momentum) * (double)running_mean[c] + momentum * mean);
+    if (running_var) {
+        const double unbiased = var * (M / (M > 1.0 ? M - 1.0 : 1.0));
+        running_var[c] = (float)((1.0 - momentum) * (double)running_var[c] + momentum * unbiased);
+    }
+}
+
+// batch slices per channel: enough blocks for eight per SM, at least eight planes per block
+static int bn_splits(int64_t n_batch, int channels) {
+    int64_t want = (148 * 8 + channels - 1) / channels;
+    int64_t most = n_batch / kRedWarps;
+    if (most < 1) most = 1;
+    if (want > most) want = most;
+    if (want < 1) want = 1;
+    if (want > 65535) want = 65535;
+    return (int)want;
+}
+
+static bool dtype_ok(int d) { return d == ACT_DTYPE_F32 || d == ACT_DTYPE_BF16 || d == ACT_DTYPE_F16; }
+
+template <int DT>
+static cudaError_t launch_stats(const uint8_t* x, int64_t n_batch, int C, int64_t hw, double eps,
+                                const float* weight, const float* bias, float* rm, float* rv, double momentum,
+                                float* params, float* ws, cudaStream_t st)
+{
+    const int S = bn_splits(n_batch, C);
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.gridDim = dim3((unsigned)C, (unsigned)S, 1);
+    cfg.blockDim = dim3(kRedThreads, 1, 1);
+    cfg.stream = st;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, bn_plane_reduce_kernel<DT, 0, 2>, x, static_cast<const uint8_t*>(nullptr),
+                                       static_cast<const float*>(nullptr), static_cast<const float*>(nullptr),
+                                       ws, n_batch, (uint32_t)C, (uint32_t)hw, 5);
+    if (e != cudaSuccess) return e;
+    return launch_overlapped(bn_stats_finalize_kernel<DT>, (C + 127) / 128, 128, st, x, static_cast<const float*>(ws),
+                             weight, bias, rm, rv, reinterpret_cast<float4*>(params), n_batch, (uint32_t)C,
+                             (uint32_t)hw, (uint32_t)S, eps, momentum);
+}
+
+template <int DT, int BITS>
+static cudaError_t launch_bwd_reduce_one(const uint8_t* dy, const uint8_t* packed, const float* scale, const float* mn,
+                                         float* sums, int64_t n_batch, int C, int64_t hw, int log2_gs, cudaStream_t st)
+{
+    const int S = bn_splits(n_batch, C);
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.gridDim = dim3((unsigned)C, (unsigned)S, 1);
+    cfg.blockDim = dim3(kRedThreads, 1, 1);
+    cfg.stream = st;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, bn_plane_reduce_kernel<DT, 1, BITS>, dy, packed, scale, mn, sums, n_batch,
+                              (uint32_t)C, (uint32_t)hw, log2_gs);
+}
+
+template <int DT>
+static cudaError_t launch_bwd_reduce(int bits, const uint8_t* dy, const uint8_t* packed, const float* scale,
+                                     const float* mn, float* sums, int64_t n_batch, int C, int64_t hw, int log2_gs,
+                                     cudaStream_t st)
+{
+    switch (bits) {
+        case 1: return launch_bwd_reduce_one<DT, 1>(dy, packed, scale, mn, sums, n_batch, C, hw, log2_gs, st);
+        case 2: return launch_bwd_reduce_one<DT, 2>(dy, packed, scale, mn, sums, n_batch, C, hw, log2_gs, st);
+        case 4: return launch_bwd_reduce_one<DT, 4>(dy, packed, scale, mn, sums, n_batch, C, hw, log2_gs, st);
+        default: return launch_bwd_reduce_one<DT, 8>(dy, packed, scale, mn, sums, n_batch, C, hw, log2_gs, st);
+    }
+}
+
+}  // namespace act
+
+extern "C" size_t act_bn_stats_workspace(int64_t n_batch, int channels)
+{
+    if (n_batch <= 0 || channels <= 0) return 0;
+    return (size_t)channels * (size_t)act::bn_splits(n_batch, channels) * 2 * sizeof(float);
+}
+
+extern "C" int act_bn_stats(const void* x, int dtype, int64_t n_batch, int channels, int64_t hw, double eps,
+                            const float* weight, const float* bias, float* running_mean, float* running_var,
+                            double momentum, float* params, void* workspace, size_t ws_bytes, void* stream)
+{
+    using namespace act;
+    if (!dtype_ok(dtype)) return ACT_ERR_DTYPE;
+    if (n_batch <= 0 || channels <= 0 || hw <= 0) return ACT_ERR_SIZE;
+    if ((hw & 3) || hw >= (1ll << 31) || channels > 65535) return ACT_ERR_UNSUPPORTED;
+    if (n_batch * channels > (INT64_MAX >> 4) / hw) return ACT_ERR_SIZE;
+    if (!x || !params || !workspace) return ACT_ERR_NULL;
+    // a plane starts on a multiple of 4 elements: 8 bytes for 16-bit types, 16 for fp32
+    if (((uintptr_t)x | (uintptr_t)params) & 15 || ((uintptr_t)workspace & 3)) return ACT_ERR_ALIGN;
+    if (ws_bytes < act_bn_stats_workspace(n_batch, channels)) return ACT_ERR_WORKSPACE;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const uint8_t* xb = static_cast<const uint8_t*>(x);
+    float* ws = static_cast<float*>(workspace);
+    cudaError_t e;
+    if (dtype == ACT_DTYPE_F32) e = launch_stats<ACT_DTYPE_F32>(xb, n_batch, channels, hw, eps, weight, bias, running_mean, running_var, momentum, params, ws, st);
+    else if (dtype == ACT_DTYPE_BF16) e = launch_stats<ACT_DTYPE_BF16>(xb, n_batch, channels, hw, eps, weight, bias, running_mean, running_var, momentum, params, ws, st);
+    else e = launch_stats<ACT_DTYPE_F16>(xb, n_batch, channels, hw, eps, weight, bias, running_mean, running_var, momentum, params, ws, st);
+    return e == cudaSuccess ? ACT_OK : ACT_ERR_LAUNCH;
+}
+
+extern "C" int act_bn_bwd_reduce(const void* packed, const float* scale, const float* mn, const void* dy,
+                                 int dtype, int64_t n_batch, int channels, int64_t hw, int group_size,
+                                 int bits, float* sums, void* stream)
+{
+    using namespace act;
+    if (!dtype_ok(dtype)) return ACT_ERR_DTYPE;
+    if (bits != 1 && bits != 2 && bits != 4 && bits != 8) return ACT_ERR_BITS;
+    if (group_size < 32 || group_size > 1024 || (group_size & (group_size - 1))) return ACT_ERR_GROUP;
+    if (n_batch < 0 || channels <= 0 || hw <= 0) return ACT_ERR_SIZE;
+    if ((hw & 3) || hw >= (1ll << 31) || channels > 65535) return ACT_ERR_UNSUPPORTED;
+    const int64_t n = n_batch * channels * hw;
+    if (n > (INT64_MAX >> 4) || n % group_size) return ACT_ERR_SIZE;
+    if (n == 0) return ACT_OK;
+    if (!packed || !scale || !mn || !dy || !sums) return ACT_ERR_NULL;
+    if (((uintptr_t)dy & 15) || ((uintptr_t)packed & 7)) return ACT_ERR_ALIGN;
+    int log2_gs = 5;
+    while ((1 << log2_gs) < group_size) ++log2_gs;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const uint8_t* p = static_cast<const uint8_t*>(packed);
+    const uint8_t* g = static_cast<const uint8_t*>(dy);
+    cudaError_t e;
+    if (dtype == ACT_DTYPE_F32) e = launch_bwd_reduce<ACT_DTYPE_F32>(bits, g, p, scale, mn, sums, n_batch, channels, hw, log2_gs, st);
+    else if (dtype == ACT_DTYPE_BF16) e = launch_bwd_reduce<ACT_DTYPE_BF16>(bits, g, p, scale, mn, sums, n_batch, channels, hw, log2_gs, st);
+    else e = launch_bwd_reduce<ACT_DTYPE_F16>(bits, g, p, scale, mn, sums, n_batch, channels, hw, log2_gs, st);
+    return e == cudaSuccess ? ACT_OK : ACT_ERR_LAUNCH;
+}

@@ -289,64 +289,6 @@ template <int BITS> __device__ __forceinline__ float decode_at(uint2 w, int i, f
 
 template <int DT, int BITS>
 __global__ void __launch_bounds__(kFusedThreads)
-bn_bwd_reduce_kernel(const uint8_t* __restrict__ packed, const float* __restrict__ scale,
-                     const float* __restrict__ mn, const uint8_t* __restrict__ dy, float* __restrict__ sums,
-                     int64_t n_elems, int log2_gs, uint32_t hw, uint32_t C)
-{
-    extern __shared__ float s_sum[];                 // [2*C]: dy*x_hat sums, then dy sums
-    for (uint32_t i = threadIdx.x; i < 2 * C; i += kFusedThreads) s_sum[i] = 0.0f;
-    __syncthreads();
-    const int64_t n_pieces = n_elems >> 3;
-    const int64_t stride = (int64_t)gridDim.x * kFusedThreads;
-    int64_t p = (int64_t)blockIdx.x * kFusedThreads + threadIdx.x;
-    PlaneWalk walk;
-    walk.init(p * 8, stride * 8, hw, C);
-    const int64_t n_rounds = (n_pieces + stride - 1) / stride;      // all lanes loop together (shuffles)
-    for (int64_t it = 0; it < n_rounds; ++it, p += stride, walk.advance()) {
-        const bool ok = p < n_pieces;
-        float a[2] = {0.0f, 0.0f}, b[2] = {0.0f, 0.0f};
-        uint32_t ch[2] = {walk.c, walk.c};
-        if (ok) {
-            const Vec8<DT> v = load8<DT>(dy, p * 8);
-            const uint2 w = load_codes8<BITS>(packed, p);
-            const int64_t g = (p * 8) >> log2_gs;
-            const float s = __ldg(scale + g), m = __ldg(mn + g);
-            float f[8];
-            to_float8<DT>(v, f);
-            ch[1] = walk.channel_at(4);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                a[i >> 2] = __fmaf_rn(f[i], decode_at<BITS>(w, i, s, m), a[i >> 2]);
-                b[i >> 2] += f[i];
-            }
-        }
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            // lanes of a warp usually sit in one channel: reduce in registers, one atomic pair
-            const uint32_t c0 = __shfl_sync(0xffffffffu, ch[h], 0);
-            if (__all_sync(0xffffffffu, ch[h] == c0)) {
-                float sa = a[h], sb = b[h];
-#pragma unroll
-                for (int off = 16; off > 0; off >>= 1) {
-                    sa += __shfl_xor_sync(0xffffffffu, sa, off);
-                    sb += __shfl_xor_sync(0xffffffffu, sb, off);
-                }
-                if ((threadIdx.x & 31) == 0) { atomicAdd(&s_sum[c0], sa); atomicAdd(&s_sum[C + c0], sb); }
-            } else if (ok) {
-                atomicAdd(&s_sum[ch[h]], a[h]);
-                atomicAdd(&s_sum[C + ch[h]], b[h]);
-            }
-        }
-    }
-    __syncthreads();
-    for (uint32_t i = threadIdx.x; i < 2 * C; i += kFusedThreads) {
-        const float v = s_sum[i];
-        if (v != 0.0f) atomicAdd(sums + i, v);
-    }
-}
-
-template <int DT, int BITS>
-__global__ void __launch_bounds__(kFusedThreads)
 bn_bwd_dx_kernel(const uint8_t* __restrict__ packed, const float* __restrict__ scale,
                  const float* __restrict__ mn, const uint8_t* __restrict__ dy, const float4* __restrict__ coef,
                  uint8_t* __restrict__ dx, int64_t n_elems, int log2_gs, uint32_t hw, uint32_t C)
@@ -375,39 +317,36 @@ bn_bwd_dx_kernel(const uint8_t* __restrict__ packed, const float* __restrict__ s
 }
 
 template <int DT>
-static cudaError_t launch_bn_bwd(int which, int bits, const uint8_t* p, const float* s, const float* m,
-                                 const uint8_t* dy, float* sums, const float4* coef, uint8_t* dx, int64_t n,
-                                 int log2_gs, uint32_t hw, uint32_t C, cudaStream_t st)
+static cudaError_t launch_bn_bwd_dx(int bits, const uint8_t* p, const float* s, const float* m,
+                                    const uint8_t* dy, const float4* coef, uint8_t* dx, int64_t n,
+                                    int log2_gs, uint32_t hw, uint32_t C, cudaStream_t st)
 {
     const int grid = stream_grid_for(((n >> 3) + kFusedThreads - 1) / kFusedThreads, 6);
-    const size_t smem = (size_t)2 * C * sizeof(float);
-#define ACT_BNB_CASE(B) \
-    if (which == 0) bn_bwd_reduce_kernel<DT, B><<<grid, kFusedThreads, smem, st>>>(p, s, m, dy, sums, n, log2_gs, hw, C); \
-    else bn_bwd_dx_kernel<DT, B><<<grid, kFusedThreads, 0, st>>>(p, s, m, dy, coef, dx, n, log2_gs, hw, C); \
-    break
     switch (bits) {
-        case 1: ACT_BNB_CASE(1);
-        case 2: ACT_BNB_CASE(2);
-        case 4: ACT_BNB_CASE(4);
-        default: ACT_BNB_CASE(8);
+        case 1: bn_bwd_dx_kernel<DT, 1><<<grid, kFusedThreads, 0, st>>>(p, s, m, dy, coef, dx, n, log2_gs, hw, C); break;
+        case 2: bn_bwd_dx_kernel<DT, 2><<<grid, kFusedThreads, 0, st>>>(p, s, m, dy, coef, dx, n, log2_gs, hw, C); break;
+        case 4: bn_bwd_dx_kernel<DT, 4><<<grid, kFusedThreads, 0, st>>>(p, s, m, dy, coef, dx, n, log2_gs, hw, C); break;
+        default: bn_bwd_dx_kernel<DT, 8><<<grid, kFusedThreads, 0, st>>>(p, s, m, dy, coef, dx, n, log2_gs, hw, C); break;
     }
-#undef ACT_BNB_CASE
     return cudaGetLastError();
 }
 
-static int bn_bwd_common(int which, const void* packed, const float* scale, const float* mn, const void* dy,
-                         int dtype, int64_t n_batch, int channels, int64_t hw, int group_size, int bits,
-                         float* sums, const float* coef, void* dx, void* stream)
+}  // namespace act
+
+extern "C" int act_bn_bwd_dx(const void* packed, const float* scale, const float* mn, const void* dy,
+                             int dtype, int64_t n_batch, int channels, int64_t hw, int group_size, int bits,
+                             const float* coef, void* dx, void* stream)
 {
+    using namespace act;
     if (!dtype_ok(dtype)) return ACT_ERR_DTYPE;
     if (bits != 1 && bits != 2 && bits != 4 && bits != 8) return ACT_ERR_BITS;
     if (group_size < 32 || group_size > 1024 || (group_size & (group_size - 1))) return ACT_ERR_GROUP;
     if (n_batch < 0 || channels <= 0 || hw <= 0) return ACT_ERR_SIZE;
-    if ((hw & 3) || hw >= (1ll << 31) || channels > 4096) return ACT_ERR_UNSUPPORTED;
+    if ((hw & 3) || hw >= (1ll << 31)) return ACT_ERR_UNSUPPORTED;
     const int64_t n = n_batch * channels * hw;
     if (n > (INT64_MAX >> 4) || n % group_size) return ACT_ERR_SIZE;
     if (n == 0) return ACT_OK;
-    if (!packed || !scale || !mn || !dy || (which == 0 ? !sums : (!coef || !dx))) return ACT_ERR_NULL;
+    if (!packed || !scale || !mn || !dy || !coef || !dx) return ACT_ERR_NULL;
     if (((uintptr_t)dy | (uintptr_t)dx | (uintptr_t)coef) & 15 || ((uintptr_t)packed & 7)) return ACT_ERR_ALIGN;
     int log2_gs = 5;
     while ((1 << log2_gs) < group_size) ++log2_gs;
@@ -417,26 +356,8 @@ static int bn_bwd_common(int which, const void* packed, const float* scale, cons
     const float4* k = reinterpret_cast<const float4*>(coef);
     uint8_t* o = static_cast<uint8_t*>(dx);
     cudaError_t e;
-    if (dtype == ACT_DTYPE_F32) e = launch_bn_bwd<ACT_DTYPE_F32>(which, bits, p, scale, mn, g, sums, k, o, n, log2_gs, (uint32_t)hw, (uint32_t)channels, st);
-    else if (dtype == ACT_DTYPE_BF16) e = launch_bn_bwd<ACT_DTYPE_BF16>(which, bits, p, scale, mn, g, sums, k, o, n, log2_gs, (uint32_t)hw, (uint32_t)channels, st);
-    else e = launch_bn_bwd<ACT_DTYPE_F16>(which, bits, p, scale, mn, g, sums, k, o, n, log2_gs, (uint32_t)hw, (uint32_t)channels, st);
+    if (dtype == ACT_DTYPE_F32) e = launch_bn_bwd_dx<ACT_DTYPE_F32>(bits, p, scale, mn, g, k, o, n, log2_gs, (uint32_t)hw, (uint32_t)channels, st);
+    else if (dtype == ACT_DTYPE_BF16) e = launch_bn_bwd_dx<ACT_DTYPE_BF16>(bits, p, scale, mn, g, k, o, n, log2_gs, (uint32_t)hw, (uint32_t)channels, st);
+    else e = launch_bn_bwd_dx<ACT_DTYPE_F16>(bits, p, scale, mn, g, k, o, n, log2_gs, (uint32_t)hw, (uint32_t)channels, st);
     return e == cudaSuccess ? ACT_OK : ACT_ERR_LAUNCH;
-}
-
-}  // namespace act
-
-extern "C" int act_bn_bwd_reduce(const void* packed, const float* scale, const float* mn, const void* dy,
-                                 int dtype, int64_t n_batch, int channels, int64_t hw, int group_size,
-                                 int bits, float* sums, void* stream)
-{
-    return act::bn_bwd_common(0, packed, scale, mn, dy, dtype, n_batch, channels, hw, group_size, bits,
-                              sums, nullptr, nullptr, stream);
-}
-
-extern "C" int act_bn_bwd_dx(const void* packed, const float* scale, const float* mn, const void* dy,
-                             int dtype, int64_t n_batch, int channels, int64_t hw, int group_size, int bits,
-                             const float* coef, void* dx, void* stream)
-{
-    return act::bn_bwd_common(1, packed, scale, mn, dy, dtype, n_batch, channels, hw, group_size, bits,
-                              nullptr, coef, dx, stream);
 }

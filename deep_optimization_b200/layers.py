@@ -23,8 +23,8 @@ class DOLinear(nn.Linear):
 
     def forward(self, x):
         if self.training:
-            y = _DOLinear.apply(x, self.weight, self.clamp_alpha, self.target_name, self.meta, self.ema_grad_meta)
-            return y if self.bias is None else y + self.bias.to(y.dtype)
+            return _DOLinear.apply(x, self.weight, self.clamp_alpha, self.target_name, self.meta,
+                                   self.ema_grad_meta, self.bias)
         return super().forward(x)
 
 

@@ -63,19 +63,18 @@ class _DOBatchNorm(Function):
             # fused path: one statistics pass, then normalise + affine + x_hat codec in one kernel
             # (normalization_ops.py:71-98 of the reference: bn_fwd_reduce + bn_fwd_norm_quant_pack_fused)
             x = input.contiguous()
-            mean, invstd = torch.batch_norm_stats(x, eps)
-            if running_mean is not None:
-                var = 1.0 / (invstd * invstd) - eps
-                n = float(count)
-                f = exponential_average_factor
-                running_mean.mul_(1.0 - f).add_(mean, alpha=f)
-                running_var.mul_(1.0 - f).add_(var * (n / max(n - 1.0, 1.0)), alpha=f)
+            f32 = lambda t: None if t is None else (t if t.dtype == torch.float32 else t.float())
+            rm, rv = f32(running_mean), f32(running_var)
+            params = codec.bn_stats(x, eps, f32(weight), f32(bias), rm, rv, exponential_average_factor or 0.0)
+            if rm is not running_mean and running_mean is not None:      # running statistics kept in another type
+                running_mean.copy_(rm)
+                running_var.copy_(rv)
             flags = _lib.ACT_FLAG_ROUND_NEAREST if act_kernels.get_mode() != "baseline" else 0
-            y, packed, scale, mn = codec.bn_fwd_norm_quant_pack(x, mean, invstd, weight, bias, m["bits"],
-                                                                m["group_size"], flags=flags)
+            y, packed, scale, mn = codec.bn_fwd_norm_quant_pack(x, None, None, weight, bias, m["bits"],
+                                                                m["group_size"], flags=flags, params=params)
             ctx.fused = (m["bits"], m["group_size"], count)
             ctx.sync = (process_group, world_size)
-            ctx.save_for_backward(weight, packed, scale, mn, invstd)
+            ctx.save_for_backward(weight, packed, scale, mn, params[:, 1])
             return y
         if world_size == 1:
             # one native kernel: x_hat and the saved statistics (running stats updated in place)

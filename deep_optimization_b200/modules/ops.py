@@ -106,7 +106,10 @@ _DOConv3d = _make_conv(3, F.conv3d, _triple)
 class _DOLinear(Function):
     @staticmethod
     @custom_fwd(device_type="cuda")
-    def forward(ctx, input, weight, clamp_alpha, target_name, meta, ema_grad_meta):
+    def forward(ctx, input, weight, clamp_alpha, target_name, meta, ema_grad_meta, bias=None):
+        # `bias` is an addition to the reference's argument list (Activation_Compression/
+        # modules/ops.py:438-479 computes the product without it): handing it to the GEMM
+        # keeps the add in the GEMM's epilogue instead of a broadcast pass over the output
         weight_master = weight
         if torch.is_autocast_enabled("cuda"):
             dt = torch.get_autocast_dtype("cuda")
@@ -114,6 +117,7 @@ class _DOLinear(Function):
             weight_compute = weight.to(dt)
         else:
             weight_compute = weight_master
+        bias_compute = None if bias is None else bias.to(weight_compute.dtype)
         m = meta[f"{target_name}"]
 
         input_l = None
@@ -126,8 +130,9 @@ class _DOLinear(Function):
         ctx.target_name = target_name
         ctx.q_inputs_meta = q_meta
         ctx.meta = input.shape, ema_grad_meta, clamp_alpha
+        ctx.bias_dtype = None if bias is None else bias.dtype
         ctx.save_for_backward(weight_master, q_tensors[0], q_tensors[1], q_tensors[2], input_l)
-        return F.linear(input, weight_compute, None)
+        return F.linear(input, weight_compute, bias_compute)
 
     @staticmethod
     @custom_bwd(device_type="cuda")
@@ -145,12 +150,14 @@ class _DOLinear(Function):
         dy = dy.to(weight_compute.dtype)
         dy2 = dy.reshape(-1, dy.shape[-1])
         x2 = x.reshape(-1, x.shape[-1])
-        dw = dx = None
+        dw = dx = db = None
         if ctx.needs_input_grad[1]:
             dw = dy2.T.mm(x2).to(weight_master.dtype)
         if ctx.needs_input_grad[0]:
             dx = dy2.mm(weight_compute).view(*input_shape)
-        return dx, dw, None, None, None, None
+        if ctx.bias_dtype is not None and ctx.needs_input_grad[6]:
+            db = dy2.sum(0, dtype=torch.float32).to(ctx.bias_dtype)
+        return dx, dw, None, None, None, None, db
 
 
 class GroupPACTClampFn(Function):

@@ -141,14 +141,26 @@ ACT_API int act_mul_dequant_unpack(const void* packed, const float* scale, const
  *       x_hat = (x - mean) * invstd, y = x_hat * weight + bias (each step rounded to fp32),
  *       y written in `dtype`, x_hat quantised with the default scheme of act_quant_pack.
  *       Needs HW*(HW+1024) < 2^32 and C*(C+260) < 2^32, else ACT_ERR_UNSUPPORTED.
+ *   act_bn_stats: the batch statistics pass in front of it (replaces bn_fwd_reduce,
+ *       AC/modules/normalization/kernel_implementation.py:13-92).  Writes params[c] = (mean,
+ *       1/sqrt(var + eps), weight[c] or 1, bias[c] or 0) with the biased variance, and, when the
+ *       pointers are given, running_mean/var = (1-momentum)*old + momentum*(mean, unbiased
+ *       var).  Sums are shifted by x[0,c,0], accumulated in fp32 per block and combined in
+ *       double in a fixed order: the result does not vary from run to run.  workspace:
+ *       act_bn_stats_workspace(n_batch, channels) bytes, caller-owned.  C <= 65535.
  *   act_bn_bwd_reduce: sums fp32 [2*C], zeroed by the caller; adds sum(dy*x_hat) to sums[c]
- *       and sum(dy) to sums[C+c] (atomic adds: the summation order is not fixed). C <= 4096.
+ *       and sum(dy) to sums[C+c] (one atomic pair per block: the order of the at most
+ *       148*8/C partial sums is not fixed). C <= 65535.
  *   act_bn_bwd_dx: coef = fp32 [C][4] (k1, k2, k3, unused); dx = k1*dy - k2 - k3*x_hat.
  */
 ACT_API int act_bn_fwd_norm_quant_pack(const void* x, int dtype, int64_t n_batch, int channels, int64_t hw,
                                const float* params, int group_size, int bits, uint64_t seed,
                                uint64_t offset, int flags, void* y, void* packed, float* scale,
                                float* min, void* stream);
+ACT_API size_t act_bn_stats_workspace(int64_t n_batch, int channels);
+ACT_API int act_bn_stats(const void* x, int dtype, int64_t n_batch, int channels, int64_t hw, double eps,
+                 const float* weight, const float* bias, float* running_mean, float* running_var,
+                 double momentum, float* params, void* workspace, size_t ws_bytes, void* stream);
 ACT_API int act_bn_bwd_reduce(const void* packed, const float* scale, const float* min, const void* dy,
                       int dtype, int64_t n_batch, int channels, int64_t hw, int group_size, int bits,
                       float* sums, void* stream);

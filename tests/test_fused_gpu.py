@@ -133,3 +133,36 @@ def test_bn_fused_backward(cuda_device, dtype, shape, bits):
     want = k1.view(view) * dy.float() - k2.view(view) - k3.view(view) * dec
     tol = 2.0 ** -7 if dtype == torch.bfloat16 else 1e-5
     assert ((dx.float() - want).abs() <= tol * (1 + want.abs())).all()
+
+
+@pytest.mark.parametrize("dtype", (torch.float32, torch.bfloat16, torch.float16), ids=("f32", "bf16", "f16"))
+@pytest.mark.parametrize("shape", [(8, 16, 32, 32), (6, 24, 14, 14), (8, 5, 2, 2), (64, 64, 56, 56), (3, 130, 4, 4)])
+def test_bn_stats(cuda_device, dtype, shape):
+    """Mean and inverse deviation against float64 statistics of the same tensor (the kernel
+    sums in fp32 per block around a pivot and combines in double: relative 2e-5), a large
+    offset included; identical from run to run; running statistics as nn.BatchNorm2d updates them."""
+    from deep_optimization_b200 import codec
+    g = torch.Generator().manual_seed(8)
+    C = shape[1]
+    offset = torch.linspace(-50, 50, C).view(1, C, 1, 1)
+    x = (torch.randn(shape, generator=g) * 1.5 + offset).to(dtype).to(cuda_device)
+    w = torch.randn(C, generator=g).to(cuda_device)
+    b = torch.randn(C, generator=g).to(cuda_device)
+    rm = torch.randn(C, generator=g).to(cuda_device)
+    rv = (torch.rand(C, generator=g) + 0.5).to(cuda_device)
+    rm0, rv0 = rm.clone(), rv.clone()
+    eps, mom = 1e-5, 0.1
+    params = codec.bn_stats(x, eps, w, b, rm, rv, mom)
+    xd = x.double()
+    mean = xd.mean((0, 2, 3))
+    var = xd.var((0, 2, 3), unbiased=False)
+    M = x.numel() // C
+    assert torch.allclose(params[:, 0].double(), mean, rtol=2e-5, atol=2e-5)
+    assert torch.allclose(params[:, 1].double(), 1.0 / torch.sqrt(var + eps), rtol=2e-5)
+    assert torch.equal(params[:, 2], w) and torch.equal(params[:, 3], b)
+    assert torch.allclose(rm.double(), 0.9 * rm0.double() + 0.1 * mean, rtol=1e-5, atol=1e-5)
+    assert torch.allclose(rv.double(), 0.9 * rv0.double() + 0.1 * var * M / max(M - 1, 1), rtol=1e-4)
+    again = codec.bn_stats(x, eps)
+    assert torch.equal(again[:, :2], codec.bn_stats(x, eps)[:, :2])
+    assert torch.equal(again[:, 0], params[:, 0]) and torch.equal(again[:, 1], params[:, 1])
+    assert (again[:, 2] == 1).all() and (again[:, 3] == 0).all()
