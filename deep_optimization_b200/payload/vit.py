@@ -17,7 +17,8 @@ class Attention(nn.Module):
     def forward(self, x):
         B, T, D = x.shape
         qkv = self.qkv(x).reshape(B, T, 3, self.heads, D // self.heads).permute(2, 0, 3, 1, 4)
-        out = F.scaled_dot_product_attention(qkv[0], qkv[1], qkv[2])
+        parts = qkv.unbind(0)      # one stack in backward instead of three zero-filled selects
+        out = F.scaled_dot_product_attention(parts[0], parts[1], parts[2])
         return self.proj(out.transpose(1, 2).reshape(B, T, D))
 
 
