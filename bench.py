@@ -210,6 +210,24 @@ def run_extras(dev):
         "unpack_GBps": ub / tu / 1e6, "unpack_frac": ub / tu / 1e6 / peak,
         "pack_plus_unpack_frac": (pb + ub) / (tp + tu) / 1e6 / peak}
     del xs, outs, ys
+    # the other rounding modes on the bench workload (bf16 [256,256,28,28], group 128, 2 bits):
+    # caller-supplied fp32 noise (exact-division float formula; its algorithmic bytes include
+    # the 4 bytes of noise read per element) and round-to-nearest
+    n = 1
+    for d in SHAPE:
+        n *= d
+    xs = [torch.relu(torch.randn(SHAPE, device=dev)).to(torch.bfloat16) for _ in range(rot)]
+    us = [torch.rand(SHAPE, device=dev) for _ in range(2)]
+    outs = [(torch.empty((n // GROUP, GROUP * BITS // 32), dtype=torch.int32, device=dev),
+             torch.empty(n // GROUP, device=dev), torch.empty(n // GROUP, device=dev)) for _ in range(rot)]
+    pb, _ = algorithmic_bytes(n, GROUP, BITS, 2)
+    tt = _time_launches(lambda i=0: codec.quant_pack(xs[i % rot], BITS, GROUP, noise=us[i % 2], out=outs[i % rot]), 40)
+    tn = _time_launches(lambda i=0: codec.quant_pack(xs[i % rot], BITS, GROUP, flags=1, out=outs[i % rot]), 40)
+    out["pack_modes_bf16_g128_b2"] = {
+        "noise_tensor": {"GBps_with_noise_bytes": (pb + 4 * n) / tt / 1e6, "frac": (pb + 4 * n) / tt / 1e6 / peak,
+                         "ms_per_launch": tt},
+        "round_to_nearest": {"GBps": pb / tn / 1e6, "frac": pb / tn / 1e6 / peak, "ms_per_launch": tn}}
+    del xs, us, outs
     # FP8 GEMM shapes (M, K, N); peak = nominal dense FP8 of a B200
     gem = {}
     bf16_peak = None
