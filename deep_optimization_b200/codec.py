@@ -288,9 +288,10 @@ def bn_stats(x: torch.Tensor, eps: float, weight: Optional[torch.Tensor] = None,
 def bn_fwd_norm_quant_pack(x: torch.Tensor, mean: Optional[torch.Tensor], invstd: Optional[torch.Tensor],
                            weight: Optional[torch.Tensor], bias: Optional[torch.Tensor], bits: int,
                            group_size: int, seed: Optional[int] = None, offset: Optional[int] = None,
-                           flags: int = 0, params: Optional[torch.Tensor] = None):
+                           flags: int = 0, params: Optional[torch.Tensor] = None, relu: bool = False):
     """y = (x - mean) * invstd * weight + bias and the packed x_hat: (y, packed, scale, min).
-    `params` is bn_stats' table; without it the table is built from mean, invstd, weight, bias."""
+    `params` is bn_stats' table; without it the table is built from mean, invstd, weight, bias.
+    relu=True also applies y = max(y, 0) and returns the 1-bit ReLU mask as a fifth value."""
     global _next_offset
     _, nwords, _ = _bits_consts(bits, group_size)
     x = x.contiguous()
@@ -310,6 +311,15 @@ def bn_fwd_norm_quant_pack(x: torch.Tensor, mean: Optional[torch.Tensor], invstd
     if offset is None:
         offset = _next_offset
         _next_offset += 1
+    if relu:
+        mask = torch.empty((x.numel() // 8,), dtype=torch.uint8, device=x.device)
+        with torch.cuda.device(x.device):
+            rc = _lib.load().act_bn_relu_fwd_norm_quant_pack(
+                x.data_ptr(), _DTYPES[x.dtype], N, C, hw, params.data_ptr(), group_size, bits,
+                seed & 0xFFFFFFFFFFFFFFFF, offset & 0xFFFFFFFFFFFFFFFF, flags, y.data_ptr(), packed.data_ptr(),
+                scale.data_ptr(), mn.data_ptr(), mask.data_ptr(), _stream_ptr(x))
+        _lib.check(rc, "act_bn_relu_fwd_norm_quant_pack")
+        return y, packed, scale, mn, mask
     with torch.cuda.device(x.device):
         rc = _lib.load().act_bn_fwd_norm_quant_pack(
             x.data_ptr(), _DTYPES[x.dtype], N, C, hw, params.data_ptr(), group_size, bits,
@@ -320,31 +330,45 @@ def bn_fwd_norm_quant_pack(x: torch.Tensor, mean: Optional[torch.Tensor], invstd
 
 
 def bn_bwd_reduce(packed: torch.Tensor, scale: torch.Tensor, mn: torch.Tensor, dy: torch.Tensor, bits: int,
-                  group_size: int) -> Tuple[torch.Tensor, torch.Tensor]:
-    """(sum dy * x_hat, sum dy) per channel, from the packed x_hat."""
+                  group_size: int, mask: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """(sum dy * x_hat, sum dy) per channel, from the packed x_hat; with the fused ReLU's `mask`
+    dy counts only where its bit is set."""
     dy = dy.contiguous()
     N, C = dy.shape[0], dy.shape[1]
     hw = dy.numel() // (N * C)
     sums = torch.zeros(2 * C, dtype=torch.float32, device=dy.device)
+    lib = _lib.load()
     with torch.cuda.device(dy.device):
-        rc = _lib.load().act_bn_bwd_reduce(packed.data_ptr(), scale.data_ptr(), mn.data_ptr(), dy.data_ptr(),
-                                           _DTYPES[dy.dtype], N, C, hw, group_size, bits, sums.data_ptr(),
-                                           _stream_ptr(dy))
+        if mask is None:
+            rc = lib.act_bn_bwd_reduce(packed.data_ptr(), scale.data_ptr(), mn.data_ptr(), dy.data_ptr(),
+                                       _DTYPES[dy.dtype], N, C, hw, group_size, bits, sums.data_ptr(),
+                                       _stream_ptr(dy))
+        else:
+            rc = lib.act_bn_relu_bwd_reduce(packed.data_ptr(), scale.data_ptr(), mn.data_ptr(), dy.data_ptr(),
+                                            mask.data_ptr(), _DTYPES[dy.dtype], N, C, hw, group_size, bits,
+                                            sums.data_ptr(), _stream_ptr(dy))
     _lib.check(rc, "act_bn_bwd_reduce")
     return sums[:C], sums[C:]
 
 
 def bn_bwd_dx(packed: torch.Tensor, scale: torch.Tensor, mn: torch.Tensor, dy: torch.Tensor, k1: torch.Tensor,
-              k2: torch.Tensor, k3: torch.Tensor, bits: int, group_size: int) -> torch.Tensor:
-    """dx = k1[c] * dy - k2[c] - k3[c] * x_hat."""
+              k2: torch.Tensor, k3: torch.Tensor, bits: int, group_size: int,
+              mask: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """dx = k1[c] * dy - k2[c] - k3[c] * x_hat (dy zeroed where the fused ReLU's `mask` bit is clear)."""
     dy = dy.contiguous()
     N, C = dy.shape[0], dy.shape[1]
     hw = dy.numel() // (N * C)
     coef = torch.stack([k1.float(), k2.float(), k3.float(), torch.zeros_like(k1, dtype=torch.float32)], dim=1).contiguous()
     dx = torch.empty_like(dy)
+    lib = _lib.load()
     with torch.cuda.device(dy.device):
-        rc = _lib.load().act_bn_bwd_dx(packed.data_ptr(), scale.data_ptr(), mn.data_ptr(), dy.data_ptr(),
-                                       _DTYPES[dy.dtype], N, C, hw, group_size, bits, coef.data_ptr(),
-                                       dx.data_ptr(), _stream_ptr(dy))
+        if mask is None:
+            rc = lib.act_bn_bwd_dx(packed.data_ptr(), scale.data_ptr(), mn.data_ptr(), dy.data_ptr(),
+                                   _DTYPES[dy.dtype], N, C, hw, group_size, bits, coef.data_ptr(),
+                                   dx.data_ptr(), _stream_ptr(dy))
+        else:
+            rc = lib.act_bn_relu_bwd_dx(packed.data_ptr(), scale.data_ptr(), mn.data_ptr(), dy.data_ptr(),
+                                        mask.data_ptr(), _DTYPES[dy.dtype], N, C, hw, group_size, bits,
+                                        coef.data_ptr(), dx.data_ptr(), _stream_ptr(dy))
     _lib.check(rc, "act_bn_bwd_dx")
     return dx

@@ -82,6 +82,7 @@ class Controller:
         self.layer_clamp = 3.0
         self.traced_model = None
         self.target_dict = {}
+        self.fused_bn_relu = []
         if not test:
             self.warp_model(quantizer=True)
 
@@ -192,6 +193,31 @@ class Controller:
                     dst.copy_(src)
         return new
 
+    @staticmethod
+    def _fuse_bn_relu(traced):
+        """BatchNorm whose only consumer is a plain ReLU: the BatchNorm module takes the ReLU
+        over (one forward kernel, no ReLU backward pass; the reference's norm+activation fusion,
+        triton_kernel/norm_act_fusion/bn_act_fusion.py) and the ReLU node leaves the graph.
+        Returns the fused BatchNorm targets."""
+        fused = []
+        for node in list(traced.graph.nodes):
+            if node.op != "call_module" or len(node.users) != 1:
+                continue
+            bn = traced.get_submodule(node.target)
+            if type(bn) is not DOBatchNorm2d:
+                continue
+            user = next(iter(node.users))
+            if user.op != "call_module" or len(user.args) != 1 or user.args[0] is not node:
+                continue
+            relu = traced.get_submodule(user.target)
+            if not (isinstance(relu, DOReLU_Variance) and relu.relu and not relu.relu6):
+                continue
+            bn.fuse_relu = True
+            user.replace_all_uses_with(node)
+            traced.graph.erase_node(user)
+            fused.append(node.target)
+        return fused
+
     # ------------------------------------------------------------------ rewrite
     def warp_model(self, graph_mode=False, quantizer=False):
         traced = FX.symbolic_trace(self.model)
@@ -212,6 +238,8 @@ class Controller:
                     if isinstance(mod, nn.LayerNorm):
                         parent_path, _, child = name.rpartition(".")
                         setattr(traced.get_submodule(parent_path), child, RMSNorm(mod.normalized_shape[-1]))
+            if self.config.get("fuse_bn_relu", True):
+                self.fused_bn_relu = self._fuse_bn_relu(traced)
             traced.graph.eliminate_dead_code()
             traced.graph.lint()
             traced.recompile()

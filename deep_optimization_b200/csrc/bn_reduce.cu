@@ -54,12 +54,14 @@ template <int BITS> __device__ __forceinline__ uint32_t load_codes4(const uint8_
 
 // MODE 0: a = sum(x - pivot), b = sum((x - pivot)^2), pivot = x[0, c, 0], written as the
 //         block's partial pair out[(c * S + s) * 2 + {0, 1}] (no atomics, no zeroing);
-// MODE 1: a = sum(dy * x_hat), b = sum(dy), added to out[c] and out[C + c].
+// MODE 1: a = sum(dy * x_hat), b = sum(dy), added to out[c] and out[C + c]; with `mask`
+//         (one bit per element, the fused ReLU's) dy counts only where its bit is set.
 template <int DT, int MODE, int BITS>
 __global__ void __launch_bounds__(kRedThreads)
 bn_plane_reduce_kernel(const uint8_t* __restrict__ x, const uint8_t* __restrict__ packed,
                        const float* __restrict__ scale, const float* __restrict__ mn,
-                       float* __restrict__ out, int64_t n_batch, uint32_t C, uint32_t hw, int log2_gs)
+                       const uint8_t* __restrict__ mask, float* __restrict__ out, int64_t n_batch,
+                       uint32_t C, uint32_t hw, int log2_gs)
 {
     __shared__ float s_part[kRedWarps][2];
     const uint32_t c = blockIdx.x, s = blockIdx.y, S = gridDim.y;
@@ -89,6 +91,11 @@ bn_plane_reduce_kernel(const uint8_t* __restrict__ x, const uint8_t* __restrict_
                 const uint32_t w = load_codes4<BITS>(packed, e);
                 const int64_t g = e >> log2_gs;
                 const float sc = __ldg(scale + g), m = __ldg(mn + g);
+                if (mask) {
+                    const uint32_t keep = load_codes4<1>(mask, e);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) f[i] = ((keep >> i) & 1u) ? f[i] : 0.0f;
+                }
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const float code = __uint_as_float(kMagicBits | ((w >> (i * BITS)) & MASK)) - kMagic;
@@ -181,7 +188,7 @@ static cudaError_t launch_stats(const uint8_t* x, int64_t n_batch, int C, int64_
     cfg.numAttrs = 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, bn_plane_reduce_kernel<DT, 0, 2>, x, static_cast<const uint8_t*>(nullptr),
                                        static_cast<const float*>(nullptr), static_cast<const float*>(nullptr),
-                                       ws, n_batch, (uint32_t)C, (uint32_t)hw, 5);
+                                       static_cast<const uint8_t*>(nullptr), ws, n_batch, (uint32_t)C, (uint32_t)hw, 5);
     if (e != cudaSuccess) return e;
     return launch_overlapped(bn_stats_finalize_kernel<DT>, (C + 127) / 128, 128, st, x, static_cast<const float*>(ws),
                              weight, bias, rm, rv, reinterpret_cast<float4*>(params), n_batch, (uint32_t)C,
@@ -190,7 +197,7 @@ static cudaError_t launch_stats(const uint8_t* x, int64_t n_batch, int C, int64_
 
 template <int DT, int BITS>
 static cudaError_t launch_bwd_reduce_one(const uint8_t* dy, const uint8_t* packed, const float* scale, const float* mn,
-                                         float* sums, int64_t n_batch, int C, int64_t hw, int log2_gs, cudaStream_t st)
+                                         const uint8_t* mask, float* sums, int64_t n_batch, int C, int64_t hw, int log2_gs, cudaStream_t st)
 {
     const int S = bn_splits(n_batch, C);
     cudaLaunchConfig_t cfg = {};
@@ -202,20 +209,20 @@ static cudaError_t launch_bwd_reduce_one(const uint8_t* dy, const uint8_t* packe
     cfg.stream = st;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, bn_plane_reduce_kernel<DT, 1, BITS>, dy, packed, scale, mn, sums, n_batch,
+    return cudaLaunchKernelEx(&cfg, bn_plane_reduce_kernel<DT, 1, BITS>, dy, packed, scale, mn, mask, sums, n_batch,
                               (uint32_t)C, (uint32_t)hw, log2_gs);
 }
 
 template <int DT>
 static cudaError_t launch_bwd_reduce(int bits, const uint8_t* dy, const uint8_t* packed, const float* scale,
-                                     const float* mn, float* sums, int64_t n_batch, int C, int64_t hw, int log2_gs,
+                                     const float* mn, const uint8_t* mask, float* sums, int64_t n_batch, int C, int64_t hw, int log2_gs,
                                      cudaStream_t st)
 {
     switch (bits) {
-        case 1: return launch_bwd_reduce_one<DT, 1>(dy, packed, scale, mn, sums, n_batch, C, hw, log2_gs, st);
-        case 2: return launch_bwd_reduce_one<DT, 2>(dy, packed, scale, mn, sums, n_batch, C, hw, log2_gs, st);
-        case 4: return launch_bwd_reduce_one<DT, 4>(dy, packed, scale, mn, sums, n_batch, C, hw, log2_gs, st);
-        default: return launch_bwd_reduce_one<DT, 8>(dy, packed, scale, mn, sums, n_batch, C, hw, log2_gs, st);
+        case 1: return launch_bwd_reduce_one<DT, 1>(dy, packed, scale, mn, mask, sums, n_batch, C, hw, log2_gs, st);
+        case 2: return launch_bwd_reduce_one<DT, 2>(dy, packed, scale, mn, mask, sums, n_batch, C, hw, log2_gs, st);
+        case 4: return launch_bwd_reduce_one<DT, 4>(dy, packed, scale, mn, mask, sums, n_batch, C, hw, log2_gs, st);
+        default: return launch_bwd_reduce_one<DT, 8>(dy, packed, scale, mn, mask, sums, n_batch, C, hw, log2_gs, st);
     }
 }
 
@@ -250,9 +257,9 @@ extern "C" int act_bn_stats(const void* x, int dtype, int64_t n_batch, int chann
     return e == cudaSuccess ? ACT_OK : ACT_ERR_LAUNCH;
 }
 
-extern "C" int act_bn_bwd_reduce(const void* packed, const float* scale, const float* mn, const void* dy,
-                                 int dtype, int64_t n_batch, int channels, int64_t hw, int group_size,
-                                 int bits, float* sums, void* stream)
+static int bn_bwd_reduce_common(const void* packed, const float* scale, const float* mn, const void* dy,
+                                const void* mask_bits, int dtype, int64_t n_batch, int channels, int64_t hw,
+                                int group_size, int bits, float* sums, void* stream)
 {
     using namespace act;
     if (!dtype_ok(dtype)) return ACT_ERR_DTYPE;
@@ -270,9 +277,27 @@ extern "C" int act_bn_bwd_reduce(const void* packed, const float* scale, const f
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const uint8_t* p = static_cast<const uint8_t*>(packed);
     const uint8_t* g = static_cast<const uint8_t*>(dy);
+    const uint8_t* mask = static_cast<const uint8_t*>(mask_bits);
     cudaError_t e;
-    if (dtype == ACT_DTYPE_F32) e = launch_bwd_reduce<ACT_DTYPE_F32>(bits, g, p, scale, mn, sums, n_batch, channels, hw, log2_gs, st);
-    else if (dtype == ACT_DTYPE_BF16) e = launch_bwd_reduce<ACT_DTYPE_BF16>(bits, g, p, scale, mn, sums, n_batch, channels, hw, log2_gs, st);
-    else e = launch_bwd_reduce<ACT_DTYPE_F16>(bits, g, p, scale, mn, sums, n_batch, channels, hw, log2_gs, st);
+    if (dtype == ACT_DTYPE_F32) e = launch_bwd_reduce<ACT_DTYPE_F32>(bits, g, p, scale, mn, mask, sums, n_batch, channels, hw, log2_gs, st);
+    else if (dtype == ACT_DTYPE_BF16) e = launch_bwd_reduce<ACT_DTYPE_BF16>(bits, g, p, scale, mn, mask, sums, n_batch, channels, hw, log2_gs, st);
+    else e = launch_bwd_reduce<ACT_DTYPE_F16>(bits, g, p, scale, mn, mask, sums, n_batch, channels, hw, log2_gs, st);
     return e == cudaSuccess ? ACT_OK : ACT_ERR_LAUNCH;
+}
+
+extern "C" int act_bn_bwd_reduce(const void* packed, const float* scale, const float* mn, const void* dy,
+                                 int dtype, int64_t n_batch, int channels, int64_t hw, int group_size,
+                                 int bits, float* sums, void* stream)
+{
+    return bn_bwd_reduce_common(packed, scale, mn, dy, nullptr, dtype, n_batch, channels, hw, group_size, bits,
+                                sums, stream);
+}
+
+extern "C" int act_bn_relu_bwd_reduce(const void* packed, const float* scale, const float* mn, const void* dy,
+                                      const void* mask_bits, int dtype, int64_t n_batch, int channels,
+                                      int64_t hw, int group_size, int bits, float* sums, void* stream)
+{
+    if (!mask_bits) return n_batch * channels * hw == 0 ? ACT_OK : ACT_ERR_NULL;
+    return bn_bwd_reduce_common(packed, scale, mn, dy, mask_bits, dtype, n_batch, channels, hw, group_size, bits,
+                                sums, stream);
 }

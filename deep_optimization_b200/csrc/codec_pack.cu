@@ -76,10 +76,10 @@ extern "C" int act_activation_fwd_quant_pack(const void* x, int dtype, int kind,
     return e == cudaSuccess ? ACT_OK : ACT_ERR_LAUNCH;
 }
 
-extern "C" int act_bn_fwd_norm_quant_pack(const void* x, int dtype, int64_t n_batch, int channels, int64_t hw,
-                                          const float* params, int group_size, int bits, uint64_t seed,
-                                          uint64_t offset, int flags, void* y, void* packed, float* scale,
-                                          float* mn, void* stream)
+static int bn_fwd_common(const void* x, int dtype, int64_t n_batch, int channels, int64_t hw,
+                         const float* params, int group_size, int bits, uint64_t seed, uint64_t offset,
+                         int flags, void* y, void* packed, float* scale, float* mn, void* mask_bits,
+                         void* stream)
 {
     using namespace act;
     if (dtype != ACT_DTYPE_F32 && dtype != ACT_DTYPE_BF16 && dtype != ACT_DTYPE_F16) return ACT_ERR_DTYPE;
@@ -98,7 +98,7 @@ extern "C" int act_bn_fwd_norm_quant_pack(const void* x, int dtype, int64_t n_ba
     int log2_L = 0;
     while ((32 << log2_L) < group_size) ++log2_L;
     BNArgs bn{reinterpret_cast<const float4*>(params), (uint32_t)hw, (uint32_t)channels,
-              magic_for((uint32_t)hw), magic_for((uint32_t)channels)};
+              magic_for((uint32_t)hw), magic_for((uint32_t)channels), static_cast<uint8_t*>(mask_bits)};
     const bool nearest = (flags & ACT_FLAG_ROUND_NEAREST) != 0;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     cudaError_t e;
@@ -106,4 +106,23 @@ extern "C" int act_bn_fwd_norm_quant_pack(const void* x, int dtype, int64_t n_ba
     else if (dtype == ACT_DTYPE_BF16) e = launch_bn<ACT_DTYPE_BF16>(bits, nearest, x, y, packed, scale, mn, n, log2_L, seed, offset, bn, st);
     else e = launch_bn<ACT_DTYPE_F16>(bits, nearest, x, y, packed, scale, mn, n, log2_L, seed, offset, bn, st);
     return e == cudaSuccess ? ACT_OK : ACT_ERR_LAUNCH;
+}
+
+extern "C" int act_bn_fwd_norm_quant_pack(const void* x, int dtype, int64_t n_batch, int channels, int64_t hw,
+                                          const float* params, int group_size, int bits, uint64_t seed,
+                                          uint64_t offset, int flags, void* y, void* packed, float* scale,
+                                          float* mn, void* stream)
+{
+    return bn_fwd_common(x, dtype, n_batch, channels, hw, params, group_size, bits, seed, offset, flags, y,
+                         packed, scale, mn, nullptr, stream);
+}
+
+extern "C" int act_bn_relu_fwd_norm_quant_pack(const void* x, int dtype, int64_t n_batch, int channels,
+                                               int64_t hw, const float* params, int group_size, int bits,
+                                               uint64_t seed, uint64_t offset, int flags, void* y, void* packed,
+                                               float* scale, float* mn, void* mask_bits, void* stream)
+{
+    if (!mask_bits) return n_batch * channels * hw == 0 ? ACT_OK : ACT_ERR_NULL;
+    return bn_fwd_common(x, dtype, n_batch, channels, hw, params, group_size, bits, seed, offset, flags, y,
+                         packed, scale, mn, mask_bits, stream);
 }

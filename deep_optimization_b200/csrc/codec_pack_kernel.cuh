@@ -322,15 +322,18 @@ __device__ __forceinline__ void encode_piece_ref(const float* xf8, float mn, flo
 // kProGelu / kProSilu write y = act(x) to y_out and quantise the activation's derivative
 // (what backward multiplies dy with), replacing the reference's fused forward kernels
 // (Activation_Compression/modules/activations/kernel_implementation.py:184-342, 468-559).
-enum Producer { kProNone = 0, kProGelu = 1, kProSilu = 2, kProBN = 3 };
+enum Producer { kProNone = 0, kProGelu = 1, kProSilu = 2, kProBN = 3, kProBNRelu = 4 };
 
 // Per-channel inputs of the batch-norm producer: x is [N, C, HW] contiguous and
 // params[c] = (mean, invstd, weight, bias).  The channel of element e is (e / HW) % C;
 // inside a lane's group it is found with two exact multiply-high divisions, which the
 // host enables only when HW*(HW+1024) < 2^32 and C*(C+260) < 2^32.
+// kProBNRelu also applies y = max(y, 0) and writes one mask bit per element (bit i of byte
+// e/8 = element e, the layout of relu_fwd_pack) to `mask`.
 struct BNArgs {
     const float4* params;
     uint32_t hw, c, magic_hw, magic_c;
+    uint8_t* mask;
 };
 
 __device__ __forceinline__ float tanh_fast(float v) {
@@ -361,7 +364,7 @@ quant_pack_kernel(const void* __restrict__ x_, const float* __restrict__ noise,
                   uint8_t* __restrict__ packed, float* __restrict__ scale_out,
                   float* __restrict__ min_out, int64_t n_elems, int log2_L,
                   uint32_t key_lo, uint32_t key_hi, int flags, float clamp_alpha,
-                  uint8_t* __restrict__ y_out = nullptr, BNArgs bn = BNArgs{nullptr, 1u, 1u, 0u, 0u})
+                  uint8_t* __restrict__ y_out = nullptr, BNArgs bn = BNArgs{nullptr, 1u, 1u, 0u, 0u, nullptr})
 {
     constexpr int QMAX = (1 << BITS) - 1;
     constexpr int TILE_OUT = kTileElems * BITS / 8;          // packed bytes per tile
@@ -428,8 +431,9 @@ quant_pack_kernel(const void* __restrict__ x_, const float* __restrict__ noise,
         }
 
         // batch norm: plane index and offset inside the plane of the lane's group
+        constexpr bool IS_BN = (PRO == kProBN || PRO == kProBNRelu);
         uint32_t bn_c0 = 0, bn_r0 = 0;
-        if (PRO == kProBN) {
+        if (IS_BN) {
             const uint64_t plane = (uint64_t)group_e0 / bn.hw;
             bn_r0 = (uint32_t)((uint64_t)group_e0 - plane * bn.hw);
             bn_c0 = (uint32_t)(plane % bn.c);
@@ -439,7 +443,7 @@ quant_pack_kernel(const void* __restrict__ x_, const float* __restrict__ noise,
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
                 float yv[8];
-                if (PRO == kProBN) {
+                if (IS_BN) {
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
                         // four consecutive elements share a channel (HW is a multiple of 4)
@@ -458,6 +462,16 @@ quant_pack_kernel(const void* __restrict__ x_, const float* __restrict__ noise,
                 } else {
 #pragma unroll
                     for (int i = 0; i < 8; ++i) act_and_derivative<PRO>(xf[k * 8 + i], yv[i], xf[k * 8 + i]);
+                }
+                if (PRO == kProBNRelu) {
+                    uint32_t bits8 = 0;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const bool on = yv[i] > 0.0f;
+                        bits8 |= (on ? 1u : 0u) << i;
+                        yv[i] = on ? yv[i] : 0.0f;
+                    }
+                    if (valid) bn.mask[(group_e0 >> 3) + ((k << log2_L) + j)] = (uint8_t)bits8;
                 }
                 if (valid) {
                     const int64_t e = group_e0 + (int64_t)((k << log2_L) + j) * 8;
@@ -629,7 +643,7 @@ cudaError_t launch_pack_one(const void* x, const float* noise, void* packed, flo
     return launch_overlapped(quant_pack_kernel<DT, BITS, NM, kProNone>, grid, PackCfg<DT>::threads, st,
                              x, noise, static_cast<uint8_t*>(packed), scale, mn, n_elems, log2_L,
                              (uint32_t)key, (uint32_t)(key >> 32), flags, clamp_alpha,
-                             static_cast<uint8_t*>(nullptr), BNArgs{nullptr, 1u, 1u, 0u, 0u});
+                             static_cast<uint8_t*>(nullptr), BNArgs{nullptr, 1u, 1u, 0u, 0u, nullptr});
 }
 
 template <int DT, int BITS>
@@ -681,7 +695,7 @@ cudaError_t launch_fused_one(const void* x, void* y, void* packed, float* scale,
     return launch_overlapped(quant_pack_kernel<DT, BITS, NM, PRO>, grid, PackCfg<DT>::threads, st,
                              x, static_cast<const float*>(nullptr), static_cast<uint8_t*>(packed), scale, mn,
                              n_elems, log2_L, (uint32_t)key, (uint32_t)(key >> 32), 0, 0.0f,
-                             static_cast<uint8_t*>(y), BNArgs{nullptr, 1u, 1u, 0u, 0u});
+                             static_cast<uint8_t*>(y), BNArgs{nullptr, 1u, 1u, 0u, 0u, nullptr});
 }
 
 template <int DT, int BITS>
@@ -718,7 +732,7 @@ inline uint32_t magic_for(uint32_t d) {
     return (uint32_t)(((1ull << 32) + d - 1) / d);
 }
 
-template <int DT, int BITS, int NM>
+template <int DT, int BITS, int NM, int PRO>
 cudaError_t launch_bn_one(const void* x, void* y, void* packed, float* scale, float* mn,
                                  int64_t n_elems, int log2_L, uint64_t seed, uint64_t offset,
                                  BNArgs bn, cudaStream_t st)
@@ -726,14 +740,14 @@ cudaError_t launch_bn_one(const void* x, void* y, void* packed, float* scale, fl
     static int per_sm = 0;
     if (per_sm == 0) {
         int n = 0;
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, quant_pack_kernel<DT, BITS, NM, kProBN>,
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, quant_pack_kernel<DT, BITS, NM, PRO>,
                                                           PackCfg<DT>::threads, 0) != cudaSuccess || n < 1) n = 1;
         per_sm = n;
     }
     const uint64_t key = hash_key(hash_key(seed) + offset);
     const int64_t n_tiles = (n_elems + kTileElems - 1) / kTileElems;
     const int grid = stream_grid_for((n_tiles + PackCfg<DT>::warps - 1) / PackCfg<DT>::warps, per_sm);
-    return launch_overlapped(quant_pack_kernel<DT, BITS, NM, kProBN>, grid, PackCfg<DT>::threads, st,
+    return launch_overlapped(quant_pack_kernel<DT, BITS, NM, PRO>, grid, PackCfg<DT>::threads, st,
                              x, static_cast<const float*>(nullptr), static_cast<uint8_t*>(packed), scale, mn,
                              n_elems, log2_L, (uint32_t)key, (uint32_t)(key >> 32), 0, 0.0f,
                              static_cast<uint8_t*>(y), bn);
@@ -745,8 +759,11 @@ cudaError_t launch_bn(int bits, bool nearest, const void* x, void* y, void* pack
                              cudaStream_t st)
 {
 #define ACT_BN_CASE(B) \
-    return nearest ? launch_bn_one<DT, B, kNoiseConst>(x, y, packed, scale, mn, n, l2, seed, offset, bn, st) \
-                   : launch_bn_one<DT, B, kNoiseHash>(x, y, packed, scale, mn, n, l2, seed, offset, bn, st)
+    if (bn.mask) \
+        return nearest ? launch_bn_one<DT, B, kNoiseConst, kProBNRelu>(x, y, packed, scale, mn, n, l2, seed, offset, bn, st) \
+                       : launch_bn_one<DT, B, kNoiseHash, kProBNRelu>(x, y, packed, scale, mn, n, l2, seed, offset, bn, st); \
+    return nearest ? launch_bn_one<DT, B, kNoiseConst, kProBN>(x, y, packed, scale, mn, n, l2, seed, offset, bn, st) \
+                   : launch_bn_one<DT, B, kNoiseHash, kProBN>(x, y, packed, scale, mn, n, l2, seed, offset, bn, st)
     switch (bits) {
         case 1: ACT_BN_CASE(1);
         case 2: ACT_BN_CASE(2);

@@ -290,8 +290,8 @@ template <int BITS> __device__ __forceinline__ float decode_at(uint2 w, int i, f
 template <int DT, int BITS>
 __global__ void __launch_bounds__(kFusedThreads)
 bn_bwd_dx_kernel(const uint8_t* __restrict__ packed, const float* __restrict__ scale,
-                 const float* __restrict__ mn, const uint8_t* __restrict__ dy, const float4* __restrict__ coef,
-                 uint8_t* __restrict__ dx, int64_t n_elems, int log2_gs, uint32_t hw, uint32_t C)
+                 const float* __restrict__ mn, const uint8_t* __restrict__ dy, const uint8_t* __restrict__ mask,
+                 const float4* __restrict__ coef, uint8_t* __restrict__ dx, int64_t n_elems, int log2_gs, uint32_t hw, uint32_t C)
 {
     const int64_t n_pieces = n_elems >> 3;
     const int64_t stride = (int64_t)gridDim.x * kFusedThreads;
@@ -307,6 +307,11 @@ bn_bwd_dx_kernel(const uint8_t* __restrict__ packed, const float* __restrict__ s
         const float4 k0 = __ldg(coef + walk.c), k1 = __ldg(coef + walk.channel_at(4));
         float f[8];
         to_float8<DT>(v, f);
+        if (mask) {                                   // fused ReLU: dy counts only where y was positive
+            const uint32_t keep = __ldg(mask + p);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) f[i] = ((keep >> i) & 1u) ? f[i] : 0.0f;
+        }
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             const float4 k = i < 4 ? k0 : k1;
@@ -318,24 +323,24 @@ bn_bwd_dx_kernel(const uint8_t* __restrict__ packed, const float* __restrict__ s
 
 template <int DT>
 static cudaError_t launch_bn_bwd_dx(int bits, const uint8_t* p, const float* s, const float* m,
-                                    const uint8_t* dy, const float4* coef, uint8_t* dx, int64_t n,
+                                    const uint8_t* dy, const uint8_t* mask, const float4* coef, uint8_t* dx, int64_t n,
                                     int log2_gs, uint32_t hw, uint32_t C, cudaStream_t st)
 {
     const int grid = stream_grid_for(((n >> 3) + kFusedThreads - 1) / kFusedThreads, 6);
     switch (bits) {
-        case 1: bn_bwd_dx_kernel<DT, 1><<<grid, kFusedThreads, 0, st>>>(p, s, m, dy, coef, dx, n, log2_gs, hw, C); break;
-        case 2: bn_bwd_dx_kernel<DT, 2><<<grid, kFusedThreads, 0, st>>>(p, s, m, dy, coef, dx, n, log2_gs, hw, C); break;
-        case 4: bn_bwd_dx_kernel<DT, 4><<<grid, kFusedThreads, 0, st>>>(p, s, m, dy, coef, dx, n, log2_gs, hw, C); break;
-        default: bn_bwd_dx_kernel<DT, 8><<<grid, kFusedThreads, 0, st>>>(p, s, m, dy, coef, dx, n, log2_gs, hw, C); break;
+        case 1: bn_bwd_dx_kernel<DT, 1><<<grid, kFusedThreads, 0, st>>>(p, s, m, dy, mask, coef, dx, n, log2_gs, hw, C); break;
+        case 2: bn_bwd_dx_kernel<DT, 2><<<grid, kFusedThreads, 0, st>>>(p, s, m, dy, mask, coef, dx, n, log2_gs, hw, C); break;
+        case 4: bn_bwd_dx_kernel<DT, 4><<<grid, kFusedThreads, 0, st>>>(p, s, m, dy, mask, coef, dx, n, log2_gs, hw, C); break;
+        default: bn_bwd_dx_kernel<DT, 8><<<grid, kFusedThreads, 0, st>>>(p, s, m, dy, mask, coef, dx, n, log2_gs, hw, C); break;
     }
     return cudaGetLastError();
 }
 
 }  // namespace act
 
-extern "C" int act_bn_bwd_dx(const void* packed, const float* scale, const float* mn, const void* dy,
-                             int dtype, int64_t n_batch, int channels, int64_t hw, int group_size, int bits,
-                             const float* coef, void* dx, void* stream)
+static int bn_bwd_dx_common(const void* packed, const float* scale, const float* mn, const void* dy,
+                            const void* mask_bits, int dtype, int64_t n_batch, int channels, int64_t hw,
+                            int group_size, int bits, const float* coef, void* dx, void* stream)
 {
     using namespace act;
     if (!dtype_ok(dtype)) return ACT_ERR_DTYPE;
@@ -355,9 +360,27 @@ extern "C" int act_bn_bwd_dx(const void* packed, const float* scale, const float
     const uint8_t* g = static_cast<const uint8_t*>(dy);
     const float4* k = reinterpret_cast<const float4*>(coef);
     uint8_t* o = static_cast<uint8_t*>(dx);
+    const uint8_t* mk = static_cast<const uint8_t*>(mask_bits);
     cudaError_t e;
-    if (dtype == ACT_DTYPE_F32) e = launch_bn_bwd_dx<ACT_DTYPE_F32>(bits, p, scale, mn, g, k, o, n, log2_gs, (uint32_t)hw, (uint32_t)channels, st);
-    else if (dtype == ACT_DTYPE_BF16) e = launch_bn_bwd_dx<ACT_DTYPE_BF16>(bits, p, scale, mn, g, k, o, n, log2_gs, (uint32_t)hw, (uint32_t)channels, st);
-    else e = launch_bn_bwd_dx<ACT_DTYPE_F16>(bits, p, scale, mn, g, k, o, n, log2_gs, (uint32_t)hw, (uint32_t)channels, st);
+    if (dtype == ACT_DTYPE_F32) e = launch_bn_bwd_dx<ACT_DTYPE_F32>(bits, p, scale, mn, g, mk, k, o, n, log2_gs, (uint32_t)hw, (uint32_t)channels, st);
+    else if (dtype == ACT_DTYPE_BF16) e = launch_bn_bwd_dx<ACT_DTYPE_BF16>(bits, p, scale, mn, g, mk, k, o, n, log2_gs, (uint32_t)hw, (uint32_t)channels, st);
+    else e = launch_bn_bwd_dx<ACT_DTYPE_F16>(bits, p, scale, mn, g, mk, k, o, n, log2_gs, (uint32_t)hw, (uint32_t)channels, st);
     return e == cudaSuccess ? ACT_OK : ACT_ERR_LAUNCH;
+}
+
+extern "C" int act_bn_bwd_dx(const void* packed, const float* scale, const float* mn, const void* dy,
+                             int dtype, int64_t n_batch, int channels, int64_t hw, int group_size, int bits,
+                             const float* coef, void* dx, void* stream)
+{
+    return bn_bwd_dx_common(packed, scale, mn, dy, nullptr, dtype, n_batch, channels, hw, group_size, bits,
+                            coef, dx, stream);
+}
+
+extern "C" int act_bn_relu_bwd_dx(const void* packed, const float* scale, const float* mn, const void* dy,
+                                  const void* mask_bits, int dtype, int64_t n_batch, int channels, int64_t hw,
+                                  int group_size, int bits, const float* coef, void* dx, void* stream)
+{
+    if (!mask_bits) return n_batch * channels * hw == 0 ? ACT_OK : ACT_ERR_NULL;
+    return bn_bwd_dx_common(packed, scale, mn, dy, mask_bits, dtype, n_batch, channels, hw, group_size, bits,
+                            coef, dx, stream);
 }

@@ -20,14 +20,18 @@ class DOBatchNorm2d(nn.BatchNorm2d):
                  group=0, target_name=None, meta={}):
         super().__init__(num_features, eps, momentum, affine, track_running_stats)
         self.target_name, self.meta, self.ema_grad_meta = target_name, meta, None
+        # set by the Controller when the only consumer is a ReLU: the module then returns
+        # relu(batch_norm(x)) and the ReLU node is taken out of the graph
+        self.fuse_relu = False
 
     def forward(self, x):
         if not self.training:
-            return super().forward(x)
+            y = super().forward(x)
+            return nn.functional.relu(y) if self.fuse_relu else y
         self._check_input_dim(x)
         return _DOBatchNorm.apply(x, self.weight, self.bias, self.running_mean, self.running_var,
                                   _ema_factor(self), self.eps, self.target_name, self.meta,
-                                  self.ema_grad_meta)
+                                  self.ema_grad_meta, None, 1, self.fuse_relu)
 
 
 class DOSyncBatchNorm2d(nn.SyncBatchNorm):

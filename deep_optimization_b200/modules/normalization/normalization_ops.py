@@ -51,8 +51,11 @@ class _DOBatchNorm(Function):
     @staticmethod
     @custom_fwd(device_type="cuda")
     def forward(ctx, input, weight, bias, running_mean, running_var, exponential_average_factor,
-                eps, target_name, meta, ema_grad_meta, process_group=None, world_size=1):
+                eps, target_name, meta, ema_grad_meta, process_group=None, world_size=1, fuse_relu=False):
+        # fuse_relu (not in the reference's argument list): the module's output is
+        # relu(batch_norm(x)); on the fused path the same three kernels do it and keep the mask
         ctx.set_materialize_grads(False)
+        ctx.relu_mask = False
         C = input.shape[1]
         shape = _channel_view(input)
         count = input.numel() // C
@@ -70,11 +73,16 @@ class _DOBatchNorm(Function):
                 running_mean.copy_(rm)
                 running_var.copy_(rv)
             flags = _lib.ACT_FLAG_ROUND_NEAREST if act_kernels.get_mode() != "baseline" else 0
-            y, packed, scale, mn = codec.bn_fwd_norm_quant_pack(x, None, None, weight, bias, m["bits"],
-                                                                m["group_size"], flags=flags, params=params)
+            out = codec.bn_fwd_norm_quant_pack(x, None, None, weight, bias, m["bits"], m["group_size"],
+                                               flags=flags, params=params, relu=fuse_relu)
+            y, packed, scale, mn = out[:4]
             ctx.fused = (m["bits"], m["group_size"], count)
             ctx.sync = (process_group, world_size)
-            ctx.save_for_backward(weight, packed, scale, mn, params[:, 1])
+            if fuse_relu:
+                ctx.relu_mask = True
+                ctx.save_for_backward(weight, packed, scale, mn, params[:, 1], out[4])
+            else:
+                ctx.save_for_backward(weight, packed, scale, mn, params[:, 1])
             return y
         if world_size == 1:
             # one native kernel: x_hat and the saved statistics (running stats updated in place)
@@ -99,25 +107,39 @@ class _DOBatchNorm(Function):
         q_tensors, q_meta, _ = unified_quantize(x_hat, None, target_name, meta, clamp=False, clamp_alpha=0.0)
         ctx.q_meta = q_meta
         ctx.sync = (process_group, world_size)
-        ctx.save_for_backward(weight, q_tensors[0], q_tensors[1], q_tensors[2], invstd)
+        if fuse_relu:
+            # unfused shapes: plain ReLU behind the codec path, its mask kept as a bool tensor
+            keep = y > 0
+            y = torch.where(keep, y, torch.zeros_like(y))
+            ctx.relu_mask = True
+            ctx.save_for_backward(weight, q_tensors[0], q_tensors[1], q_tensors[2], invstd, keep)
+        else:
+            ctx.save_for_backward(weight, q_tensors[0], q_tensors[1], q_tensors[2], invstd)
         return y
 
     @staticmethod
     @custom_bwd(device_type="cuda")
     def backward(ctx, dy):
-        weight, q_out, q_scale, q_min, invstd = ctx.saved_tensors
+        mask = None
+        if ctx.relu_mask:
+            weight, q_out, q_scale, q_min, invstd, mask = ctx.saved_tensors
+        else:
+            weight, q_out, q_scale, q_min, invstd = ctx.saved_tensors
         process_group, world_size = ctx.sync
         if ctx.fused is not None:
             # two kernels on the packed x_hat: per-channel sums, then dx (normalization_ops.py:145-163)
             bits, gs, count = ctx.fused
             dyc = dy.contiguous()
-            dgamma, dbeta = codec.bn_bwd_reduce(q_out, q_scale, q_min, dyc, bits, gs)
+            dgamma, dbeta = codec.bn_bwd_reduce(q_out, q_scale, q_min, dyc, bits, gs, mask=mask)
             w = weight.float() if weight is not None else torch.ones_like(invstd)
             k1 = w * invstd
-            dx = codec.bn_bwd_dx(q_out, q_scale, q_min, dyc, k1, k1 * dbeta / count, k1 * dgamma / count, bits, gs)
+            dx = codec.bn_bwd_dx(q_out, q_scale, q_min, dyc, k1, k1 * dbeta / count, k1 * dgamma / count, bits, gs,
+                                 mask=mask)
             dw = dgamma.to(weight.dtype) if weight is not None else None
             db = dbeta.to(weight.dtype) if weight is not None else None
-            return dx, dw, db, None, None, None, None, None, None, None, None, None
+            return dx, dw, db, None, None, None, None, None, None, None, None, None, None
+        if mask is not None:
+            dy = torch.where(mask, dy, torch.zeros_like(dy))
         x_hat = unified_dequantize((q_out, q_scale, q_min), ctx.q_meta, None)
         shape = _channel_view(dy)
         C = dy.shape[1]
@@ -131,7 +153,7 @@ class _DOBatchNorm(Function):
             dx = dx * invstd.to(dx.dtype).view(shape)
             dw = dgamma.to(weight.dtype) if weight is not None else None
             db = dbeta.to(weight.dtype) if weight is not None else None
-            return dx, dw, db, None, None, None, None, None, None, None, None, None
+            return dx, dw, db, None, None, None, None, None, None, None, None, None, None
         g = dy.float()
         x_hat = x_hat.float()
         dims = [0] + list(range(2, g.dim()))
@@ -144,7 +166,7 @@ class _DOBatchNorm(Function):
         dx = (w * invstd / M).view(shape) * (M * g - sum_db.view(shape) - x_hat * sum_dg.view(shape))
         dw = dgamma.to(weight.dtype) if weight is not None else None
         db = dbeta.to(weight.dtype) if weight is not None else None
-        return dx.to(dy.dtype), dw, db, None, None, None, None, None, None, None, None, None
+        return dx.to(dy.dtype), dw, db, None, None, None, None, None, None, None, None, None, None
 
 
 class _DOSyncBatchNorm:

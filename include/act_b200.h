@@ -169,6 +169,25 @@ ACT_API int act_bn_bwd_dx(const void* packed, const float* scale, const float* m
                   const float* coef, void* dx, void* stream);
 
 /*
+ * Batch norm followed by ReLU in the same three kernels (replaces the norm+activation fusion
+ * of AC/triton_kernel/norm_act_fusion/bn_act_fusion.py:7-278).  Forward also applies
+ * y = max(y, 0) and writes the ReLU mask, one bit per element (bit i of byte e/8 = element e,
+ * N*C*HW/8 bytes, the layout of act_relu_fwd_pack); the two backward kernels read dy only
+ * where the mask bit is set, so the ReLU backward pass disappears.  Everything else is as in
+ * the three entry points above.
+ */
+ACT_API int act_bn_relu_fwd_norm_quant_pack(const void* x, int dtype, int64_t n_batch, int channels,
+                                    int64_t hw, const float* params, int group_size, int bits,
+                                    uint64_t seed, uint64_t offset, int flags, void* y, void* packed,
+                                    float* scale, float* min, void* mask_bits, void* stream);
+ACT_API int act_bn_relu_bwd_reduce(const void* packed, const float* scale, const float* min, const void* dy,
+                           const void* mask_bits, int dtype, int64_t n_batch, int channels, int64_t hw,
+                           int group_size, int bits, float* sums, void* stream);
+ACT_API int act_bn_relu_bwd_dx(const void* packed, const float* scale, const float* min, const void* dy,
+                       const void* mask_bits, int dtype, int64_t n_batch, int channels, int64_t hw,
+                       int group_size, int bits, const float* coef, void* dx, void* stream);
+
+/*
  * Per-row min and max of a contiguous [rows, cols] matrix.
  * Replaces cpp_extension.min_max_kernel (AC/cpp_extension/src/min_max_kernel.cu:66-141).
  */

@@ -166,3 +166,62 @@ def test_bn_stats(cuda_device, dtype, shape):
     assert torch.equal(again[:, :2], codec.bn_stats(x, eps)[:, :2])
     assert torch.equal(again[:, 0], params[:, 0]) and torch.equal(again[:, 1], params[:, 1])
     assert (again[:, 2] == 1).all() and (again[:, 3] == 0).all()
+
+
+@pytest.mark.parametrize("dtype", (torch.float32, torch.bfloat16), ids=("f32", "bf16"))
+@pytest.mark.parametrize("shape", [(8, 16, 32, 32), (6, 24, 14, 14), (8, 5, 2, 2)])
+def test_bn_relu_fused(oracle, cuda_device, dtype, shape):
+    """Forward: the packed x_hat is the one of the kernel without ReLU (bit-exact), y is its y
+    clamped at zero and the mask is y > 0.  Backward: sums and dx equal those of the unfused
+    kernels fed with dy * mask."""
+    from deep_optimization_b200 import codec
+    g = torch.Generator().manual_seed(15)
+    x = (torch.randn(shape, generator=g) * 2 + 0.5).to(dtype).to(cuda_device)
+    C = shape[1]
+    mean = torch.randn(C, generator=g).to(cuda_device)
+    invstd = (torch.rand(C, generator=g) + 0.5).to(cuda_device)
+    w = torch.randn(C, generator=g).to(cuda_device)
+    b = torch.randn(C, generator=g).to(cuda_device)
+    gs = 64 if x.numel() % 256 else 256
+    if x.numel() % gs:
+        gs = 32
+    y0, p0, s0, m0 = codec.bn_fwd_norm_quant_pack(x, mean, invstd, w, b, 2, gs, seed=3, offset=2)
+    y1, p1, s1, m1, mask = codec.bn_fwd_norm_quant_pack(x, mean, invstd, w, b, 2, gs, seed=3, offset=2, relu=True)
+    assert torch.equal(p0, p1) and torch.equal(s0, s1) and torch.equal(m0, m1)
+    assert torch.equal(y1, torch.relu(y0))
+    keep = (y0 > 0)
+    bits = np.unpackbits(mask.cpu().numpy(), bitorder="little")[: x.numel()].reshape(shape)
+    assert np.array_equal(bits.astype(bool), keep.cpu().numpy())
+    dy = torch.randn(shape, generator=g).to(dtype).to(cuda_device)
+    dym = torch.where(keep, dy, torch.zeros_like(dy))
+    a1, b1 = codec.bn_bwd_reduce(p1, s1, m1, dy, 2, gs, mask=mask)
+    a0, b0 = codec.bn_bwd_reduce(p1, s1, m1, dym, 2, gs)
+    assert torch.allclose(a1, a0, rtol=1e-5, atol=1e-4) and torch.allclose(b1, b0, rtol=1e-5, atol=1e-4)
+    k1, k2, k3 = (torch.randn(C, generator=g).to(cuda_device) for _ in range(3))
+    d1 = codec.bn_bwd_dx(p1, s1, m1, dy, k1, k2, k3, 2, gs, mask=mask)
+    d0 = codec.bn_bwd_dx(p1, s1, m1, dym, k1, k2, k3, 2, gs)
+    assert torch.equal(d1, d0)
+
+
+def test_bn_relu_module_matches_pytorch(cuda_device):
+    """DOBatchNorm2d with fuse_relu against BatchNorm2d + ReLU: output exact to rounding,
+    gradients within the 8-bit codec's error."""
+    from deep_optimization_b200.modules.normalization.normalization_layers import DOBatchNorm2d
+    torch.manual_seed(2)
+    meta = {"b": {"bits": 8, "pack_only": False, "group_size": 256, "act_padding": False, "N": 8,
+                  "AVG_ALAM": False, "ALAM_BITS": 0, "DIVISION": None}}
+    bn = DOBatchNorm2d(4, target_name="b", meta=meta).to(cuda_device).train()
+    bn.fuse_relu = True
+    rb = torch.nn.BatchNorm2d(4).to(cuda_device).train()
+    with torch.no_grad():
+        bn.weight.copy_(torch.randn(4)); bn.bias.copy_(torch.randn(4))
+        rb.weight.copy_(bn.weight); rb.bias.copy_(bn.bias)
+    x = torch.randn(8, 4, 16, 16, device=cuda_device, requires_grad=True)
+    xr = x.detach().clone().requires_grad_()
+    g = torch.randn_like(x)
+    y, yr = bn(x), torch.relu(rb(xr))
+    assert torch.allclose(y, yr, atol=1e-4)
+    y.backward(g); yr.backward(g)
+    assert (x.grad - xr.grad).abs().max() < 0.05
+    assert (bn.weight.grad - rb.weight.grad).norm() / rb.weight.grad.norm() < 0.03
+    assert torch.allclose(bn.bias.grad, rb.bias.grad, rtol=1e-4, atol=1e-3)

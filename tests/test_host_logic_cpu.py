@@ -61,10 +61,11 @@ def test_controller_plans_and_swaps():
                           nn.Conv2d(64, 64, 3, padding=1, bias=False), nn.Flatten(), nn.Linear(64 * 32 * 32, 10))
     cfg = dict(default_bits=2, auto_precision=None, batch_size=64, min_activation_mib=1)
     w0 = model[0].weight.detach().clone()
-    c = Controller(model, cfg, input_shape=(3, 32, 32), test=False, device="cpu")
+    c = Controller(model, dict(cfg, fuse_bn_relu=False), input_shape=(3, 32, 32), test=False, device="cpu")
     net = c.traced_model
     t = [net.get_submodule(str(i)) for i in range(6)]
     assert isinstance(t[0], DOConv2d) and isinstance(t[1], DOBatchNorm2d)
+    assert not t[1].fuse_relu and c.fused_bn_relu == []
     assert isinstance(t[2], DOReLU_Variance) and isinstance(t[3], DOConv2d)
     assert isinstance(t[5], nn.Linear) and not isinstance(t[5], DOLinear)      # output too small
     assert torch.equal(t[0].weight, w0)
@@ -76,6 +77,40 @@ def test_controller_plans_and_swaps():
     net.eval()
     with torch.no_grad():
         assert net(torch.randn(2, 3, 32, 32)).shape == (2, 10)
+
+
+def test_controller_fuses_bn_relu():
+    """A BatchNorm whose only consumer is a ReLU takes the ReLU over (the default); one with a
+    second consumer, or followed by ReLU6, keeps its ReLU node."""
+    from deep_optimization_b200.controller import Controller
+
+    class Net(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.c1, self.b1, self.r1 = nn.Conv2d(3, 64, 3, padding=1, bias=False), nn.BatchNorm2d(64), nn.ReLU()
+            self.c2, self.b2, self.r2 = nn.Conv2d(64, 64, 3, padding=1, bias=False), nn.BatchNorm2d(64), nn.ReLU()
+            self.c3, self.b3, self.r3 = nn.Conv2d(64, 64, 3, padding=1, bias=False), nn.BatchNorm2d(64), nn.ReLU6()
+
+        def forward(self, x):
+            x = self.r1(self.b1(self.c1(x)))
+            y = self.b2(self.c2(x))
+            x = self.r2(y) + y                      # b2 has two consumers
+            return self.r3(self.b3(self.c3(x)))
+
+    cfg = dict(default_bits=2, auto_precision=None, batch_size=64, min_activation_mib=1)
+    c = Controller(Net(), cfg, input_shape=(3, 32, 32), test=False, device="cpu")
+    net = c.traced_model
+    assert c.fused_bn_relu == ["b1"]
+    assert net.b1.fuse_relu and not net.b2.fuse_relu and not net.b3.fuse_relu
+    targets = [n.target for n in net.graph.nodes if n.op == "call_module"]
+    assert "r1" not in targets and "r2" in targets and "r3" in targets
+    # eval mode: the fused module still applies the ReLU
+    net.eval()
+    ref = Net().eval()
+    ref.load_state_dict({k: v for k, v in net.state_dict().items()})
+    x = torch.randn(2, 3, 32, 32)
+    with torch.no_grad():
+        assert torch.allclose(net(x), ref(x), atol=1e-6)
 
 
 def test_quantizer_policy():
