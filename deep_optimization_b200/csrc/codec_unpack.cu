@@ -73,6 +73,44 @@ dequant_unpack_kernel(const uint8_t* __restrict__ packed, const float* __restric
             const int e = k * 256 + lane * 8;
             if (e >= remain) continue;
             const f32x2 s2 = pack2(s[k], s[k]), m2 = pack2(m[k], m[k]);
+            if (ElemT<DT>::bytes == 2 && BITS <= 2) {
+                // 1- and 2-bit codes to 16-bit outputs: a group has only 2^BITS distinct outputs,
+                // so they are computed once per chunk (same fma, same rounding) and every element
+                // picks its two bytes out of that table with a byte permute.  A code c becomes
+                // the selector nibbles (2c, 2c+1); four codes are spread to four bytes with two
+                // integer multiplies whose partial products never overlap.
+                uint32_t t_lo, t_hi = 0u;
+                {
+                    uint32_t f0, f1, f2, f3;
+                    unpack2u(fma2_rn(pack2(0.0f, 1.0f), s2, m2), f0, f1);
+                    if (DT == ACT_DTYPE_BF16) { const __nv_bfloat162 t = __floats2bfloat162_rn(__uint_as_float(f0), __uint_as_float(f1)); t_lo = *reinterpret_cast<const uint32_t*>(&t); }
+                    else { const __half2 t = __floats2half2_rn(__uint_as_float(f0), __uint_as_float(f1)); t_lo = *reinterpret_cast<const uint32_t*>(&t); }
+                    if (BITS == 2) {
+                        unpack2u(fma2_rn(pack2(2.0f, 3.0f), s2, m2), f2, f3);
+                        if (DT == ACT_DTYPE_BF16) { const __nv_bfloat162 t = __floats2bfloat162_rn(__uint_as_float(f2), __uint_as_float(f3)); t_hi = *reinterpret_cast<const uint32_t*>(&t); }
+                        else { const __half2 t = __floats2half2_rn(__uint_as_float(f2), __uint_as_float(f3)); t_hi = *reinterpret_cast<const uint32_t*>(&t); }
+                    }
+                }
+                uint4 a;
+                uint32_t* ap = &a.x;
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    uint32_t z;
+                    if (BITS == 2) {
+                        const uint32_t x = (w[k].x >> (8 * h)) & 0xFFu;           // four codes
+                        const uint32_t y = (x * 4097u) & 0x000F000Fu;             // two per half
+                        z = (y * 65u) & 0x03030303u;                              // one per byte
+                    } else {
+                        const uint32_t x = (w[k].x >> (4 * h)) & 0xFu;            // four one-bit codes
+                        z = (x * 0x00204081u) & 0x01010101u;                      // one per byte
+                    }
+                    const uint32_t sel = z * 0x22u + 0x10101010u;
+                    ap[2 * h] = __byte_perm(t_lo, t_hi, sel);
+                    ap[2 * h + 1] = __byte_perm(t_lo, t_hi, sel >> 16);
+                }
+                stg_stream_v4(y_tile + e * 2, a);
+                continue;
+            }
             uint32_t o[8];
 #pragma unroll
             for (int p = 0; p < 4; ++p) {
