@@ -358,11 +358,14 @@ __device__ __forceinline__ void act_and_derivative(float x, float& y, float& d) 
     }
 }
 
-template <int DT, int BITS, int NM, int PRO = kProNone>
+// L2 >= 0 fixes log2(lanes per group) at compile time (the common group sizes get their own
+// instantiation: addresses, strides and the shuffle loop then fold to constants); L2 = -1
+// takes it from the argument.
+template <int DT, int BITS, int NM, int PRO = kProNone, int L2 = -1>
 __global__ void __launch_bounds__(PackCfg<DT>::threads, PackCfg<DT>::min_blocks)
 quant_pack_kernel(const void* __restrict__ x_, const float* __restrict__ noise,
                   uint8_t* __restrict__ packed, float* __restrict__ scale_out,
-                  float* __restrict__ min_out, int64_t n_elems, int log2_L,
+                  float* __restrict__ min_out, int64_t n_elems, int log2_L_arg,
                   uint32_t key_lo, uint32_t key_hi, int flags, float clamp_alpha,
                   uint8_t* __restrict__ y_out = nullptr, BNArgs bn = BNArgs{nullptr, 1u, 1u, 0u, 0u, nullptr})
 {
@@ -373,11 +376,11 @@ quant_pack_kernel(const void* __restrict__ x_, const float* __restrict__ noise,
 
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
+    const int log2_L = (L2 >= 0) ? L2 : log2_L_arg;
     const int L = 1 << log2_L;                  // lanes per group
     const int j = lane & (L - 1);               // lane index inside the group
     const int g_local = lane >> log2_L;         // group index inside the tile
     const int lane_e0 = g_local << (log2_L + 5);   // first element of the lane's group inside the tile
-    const int64_t n_tiles = (n_elems + kTileElems - 1) / kTileElems;
     const int64_t warp_stride = (int64_t)gridDim.x * kPackWarps;
     const uint8_t* xb = static_cast<const uint8_t*>(x_);
     uint8_t* my_stage = stage[warp];
@@ -520,14 +523,23 @@ quant_pack_kernel(const void* __restrict__ x_, const float* __restrict__ noise,
 
         // ---- scale ----------------------------------------------------------------
         const float range = __fsub_rn(mx, mn);
-        float s = (BITS == 1) ? range : __fdiv_rn(range, (float)QMAX);
-        if (!(s > 0.0f)) s = 1.0f;
-        const float y = __frcp_rn(s);
         // the fast paths need a finite range well inside the normal numbers (then
         // 2^-58 <= s <= 2^50); a denormal, huge, infinite or NaN range sends the whole
         // tile the slow way
         const bool fast = (range == 0.0f) || (range >= 0x1p-50f && range <= 0x1p50f);     // a regular group
         const bool tile_fast = (NM != kRefCompat) && __all_sync(0xffffffffu, fast);
+        float s;
+        if (BITS == 1) {
+            s = range;
+        } else if (tile_fast) {
+            // range / QMAX by the FMA sequence: equal to the IEEE quotient for every normal
+            // range (checked over all 2^23 mantissas for the divisors 3, 15 and 255)
+            s = div_by_scale(range, (float)QMAX, 1.0f / (float)QMAX);
+        } else {
+            s = __fdiv_rn(range, (float)QMAX);
+        }
+        if (!(s > 0.0f)) s = 1.0f;
+        const float y = __frcp_rn(s);
 
         if (valid && j == 0) {
             const int64_t g = (tile << (5 - log2_L)) + g_local;
@@ -617,12 +629,12 @@ quant_pack_kernel(const void* __restrict__ x_, const float* __restrict__ noise,
 // ------------------------------------------------------------------ launcher
 
 // blocks of one instantiation that fit on an SM (asked once per instantiation)
-template <int DT, int BITS, int NM>
+template <int DT, int BITS, int NM, int L2>
 int pack_blocks_per_sm() {
     static int cached = 0;
     if (cached == 0) {
         int n = 0;
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, quant_pack_kernel<DT, BITS, NM>,
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, quant_pack_kernel<DT, BITS, NM, kProNone, L2>,
                                                           PackCfg<DT>::threads, 0) != cudaSuccess || n < 1) n = 1;
         cached = n;
     }
@@ -631,19 +643,33 @@ int pack_blocks_per_sm() {
 
 int stream_grid_for(int64_t n_blocks_wanted, int blocks_per_sm);   // cabi.cu
 
+template <int DT, int BITS, int NM, int L2>
+cudaError_t launch_pack_fixed(const void* x, const float* noise, void* packed, float* scale,
+                              float* mn, int64_t n_elems, int log2_L, uint64_t seed,
+                              uint64_t offset, int flags, float clamp_alpha, cudaStream_t st)
+{
+    const uint64_t key = hash_key(hash_key(seed) + offset);
+    const int64_t n_tiles = (n_elems + kTileElems - 1) / kTileElems;
+    // persistent grid: exactly the resident blocks of one wave (or fewer for small inputs)
+    const int grid = stream_grid_for((n_tiles + PackCfg<DT>::warps - 1) / PackCfg<DT>::warps,
+                                     pack_blocks_per_sm<DT, BITS, NM, L2>());
+    return launch_overlapped(quant_pack_kernel<DT, BITS, NM, kProNone, L2>, grid, PackCfg<DT>::threads, st,
+                             x, noise, static_cast<uint8_t*>(packed), scale, mn, n_elems, log2_L,
+                             (uint32_t)key, (uint32_t)(key >> 32), flags, clamp_alpha,
+                             static_cast<uint8_t*>(nullptr), BNArgs{nullptr, 1u, 1u, 0u, 0u, nullptr});
+}
+
 template <int DT, int BITS, int NM>
 cudaError_t launch_pack_one(const void* x, const float* noise, void* packed, float* scale,
                                    float* mn, int64_t n_elems, int log2_L, uint64_t seed,
                                    uint64_t offset, int flags, float clamp_alpha, cudaStream_t st)
 {
-    const uint64_t key = hash_key(hash_key(seed) + offset);
-    const int64_t n_tiles = (n_elems + kTileElems - 1) / kTileElems;
-    // persistent grid: exactly the resident blocks of one wave (or fewer for small inputs)
-    const int grid = stream_grid_for((n_tiles + PackCfg<DT>::warps - 1) / PackCfg<DT>::warps, pack_blocks_per_sm<DT, BITS, NM>());
-    return launch_overlapped(quant_pack_kernel<DT, BITS, NM, kProNone>, grid, PackCfg<DT>::threads, st,
-                             x, noise, static_cast<uint8_t*>(packed), scale, mn, n_elems, log2_L,
-                             (uint32_t)key, (uint32_t)(key >> 32), flags, clamp_alpha,
-                             static_cast<uint8_t*>(nullptr), BNArgs{nullptr, 1u, 1u, 0u, 0u, nullptr});
+    // the default mode at group sizes 128 and 256 runs kernels with the group size compiled in
+    if (NM == kNoiseHash && log2_L == 2)
+        return launch_pack_fixed<DT, BITS, NM, (NM == kNoiseHash ? 2 : -1)>(x, noise, packed, scale, mn, n_elems, log2_L, seed, offset, flags, clamp_alpha, st);
+    if (NM == kNoiseHash && log2_L == 3)
+        return launch_pack_fixed<DT, BITS, NM, (NM == kNoiseHash ? 3 : -1)>(x, noise, packed, scale, mn, n_elems, log2_L, seed, offset, flags, clamp_alpha, st);
+    return launch_pack_fixed<DT, BITS, NM, -1>(x, noise, packed, scale, mn, n_elems, log2_L, seed, offset, flags, clamp_alpha, st);
 }
 
 template <int DT, int BITS>
