@@ -146,7 +146,7 @@ __device__ __forceinline__ void load_noise8(float (&u8)[8], const float* noise, 
     }
 }
 
-// ---- fast path of the tensor-noise and round-to-nearest modes: one piece -> BITS bytes
+// ---- fast path of the tensor-noise mode (the float formula): one piece -> BITS bytes
 // Preconditions (checked per tile, warp-uniformly): the group's range is 0 or in
 // [2^-50, 2^50], so the FMA division is exact.  floor is a round-down add of 2^23; the
 // code is then the low mantissa bits and the codes of a piece are summed with shifts,
@@ -163,14 +163,12 @@ __device__ __forceinline__ void encode_piece_fast(const float* xf8, const float*
         const f32x2 a2 = add2_rn(pack2(xf8[2 * p], xf8[2 * p + 1]), nmn2);
         const f32x2 q2 = div_by_scale2(a2, ns2, y2);
         f32x2 t2;
-        if (NM == kNoiseTensor) {
+        {
             // caller-supplied noise may lie outside [0,1) or be NaN: clamp t to [0,QMAX]
             // first (NaN -> 0), after which the round-down add is floor again
             uint32_t l, h; unpack2u(add2_rn(q2, pack2(u8[2 * p], u8[2 * p + 1])), l, h);
             t2 = pack2(fminf(fmaxf(__uint_as_float(l), 0.0f), (float)QMAX),
                        fminf(fmaxf(__uint_as_float(h), 0.0f), (float)QMAX));
-        } else {
-            t2 = add2_rn(q2, pack2(0.5f - 1e-6f, 0.5f - 1e-6f));
         }
         uint32_t tb0, tb1;
         unpack2u(add2_rm(t2, magic2), tb0, tb1);
@@ -186,8 +184,8 @@ __device__ __forceinline__ void encode_piece_fast(const float* xf8, const float*
 }
 
 // ---- fixed-point fast path of the counter-hash mode -----------------------------
-// For a regular group (range 0 or in [2^-50, 2^50]) the hash mode is defined in fixed
-// point: v = fma(a, RN(1/s), 2^15) rounds a/s once onto a grid of 8 fraction bits, so the low
+// For a regular group (range 0 or in [2^-50, 2^50]) the hash mode (and round-to-nearest,
+// whose "noise" is the constant 127) is defined in fixed point: v = fma(a, RN(1/s), 2^15) rounds a/s once onto a grid of 8 fraction bits, so the low
 // 16 mantissa bits of v are Q = RNE(a*y*256) <= qmax*256; the element's noise byte h is added
 // as an integer and code = (Q + h) >> 8 <= qmax: no clamp, no conversion.  Elements 2p and 2p+1
 // of a piece share a register (low and high half) after the FMA; one 64-bit hash output holds
@@ -218,15 +216,15 @@ __device__ __forceinline__ uint32_t mul_lo(uint32_t a, uint32_t b) {
     uint32_t d; asm("mul.lo.u32 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d;
 }
 
-template <int DT, int BITS, bool FROM_RAW>
+template <int DT, int BITS, bool FROM_RAW, int NM>
 __device__ __forceinline__ void encode_piece_fx(const uint4 rv, const float* xf8, float mn, f32x2 nmn2,
                                                 f32x2 y2, uint32_t ctr_lo, uint32_t ctr_hi, uint32_t key_lo,
                                                 uint32_t& acc0, uint32_t& acc1)
 {
     constexpr uint32_t MB = (uint32_t)(127 + 23 - 8) << 23;          // bit pattern of 2^15: 8 fraction bits
     const f32x2 magic2 = pack2u(MB, MB);
-    uint32_t hw[2];
-    hash_2x32_split(ctr_lo, ctr_hi, key_lo, hw[0], hw[1]);           // eight noise bytes, one per element
+    uint32_t hw[2] = {0u, 0u};
+    if (NM == kNoiseHash) hash_2x32_split(ctr_lo, ctr_hi, key_lo, hw[0], hw[1]);   // eight noise bytes, one per element
     const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
     uint32_t sum[4];
 #pragma unroll
@@ -238,7 +236,9 @@ __device__ __forceinline__ void encode_piece_fx(const uint4 rv, const float* xf8
         uint32_t b0, b1;
         unpack2u(fma2_rn(a2, y2, magic2), b0, b1);
         const uint32_t w = shl_add(b1, 16, b0);                       // (Q1 << 16) + Q0 + MB
-        const uint32_t n = __byte_perm(hw[p >> 1], 0u, (p & 1) ? 0x4342 : 0x4140);   // noise bytes under each half
+        // noise bytes under each half; round-to-nearest adds 127/256 to both (the reference's
+        // 0.5 - 1e-6 on this grid: ties go down)
+        const uint32_t n = (NM == kNoiseHash) ? __byte_perm(hw[p >> 1], 0u, (p & 1) ? 0x4342 : 0x4140) : 0x007F007Fu;
         sum[p] = add3(w, n, 0u - MB);
     }
     // byte 1 of each half is the code: gather them, elements 0-3 and 4-7
@@ -279,17 +279,18 @@ __device__ __forceinline__ void encode_piece_slow(const float* xf8, const float*
     for (int i = 0; i < 8; ++i) {
         const float a = __fsub_rn(xf8[i], mn);
         uint32_t c;
-        if (NM == kNoiseHash) {
-            const uint32_t h = (hw[i >> 2] >> ((i & 3) * 8)) & 0xFFu;       // byte i of the hash output
+        if (NM == kNoiseHash || NM == kNoiseConst) {
+            // byte i of the hash output, or the constant 127 of round-to-nearest
+            const uint32_t h = (NM == kNoiseHash) ? ((hw[i >> 2] >> ((i & 3) * 8)) & 0xFFu) : 127u;
             if (regular) {
                 const uint32_t q = __float_as_uint(__fmaf_rn(a, y, 32768.0f)) - 0x47000000u;
                 c = (q + h) >> 8;
             } else {
-                c = code_from_t(__fadd_rn(__fdiv_rn(a, s), __fmul_rn((float)h, 0x1p-8f)), QMAX);
+                const float uu = (NM == kNoiseHash) ? __fmul_rn((float)h, 0x1p-8f) : 0.5f - 1e-6f;
+                c = code_from_t(__fadd_rn(__fdiv_rn(a, s), uu), QMAX);
             }
         } else {
-            const float uu = (NM == kNoiseTensor) ? u8[i] : 0.5f - 1e-6f;
-            c = code_from_t(__fadd_rn(__fdiv_rn(a, s), uu), QMAX);
+            c = code_from_t(__fadd_rn(__fdiv_rn(a, s), u8[i]), QMAX);
         }
         if (BITS == 8 && i >= 4) acc1 |= c << ((i - 4) * 8);
         else acc0 |= c << (i * BITS);
@@ -423,7 +424,8 @@ quant_pack_kernel(const void* __restrict__ x_, const float* __restrict__ noise,
 
         // 16-bit inputs in hash mode are consumed straight from the raw registers by the
         // fixed-point encoder; only the slow path widens them
-        constexpr bool RAW16 = (ElemT<DT>::bytes == 2 && NM == kNoiseHash && PRO == kProNone);
+        constexpr bool FIXED = (NM == kNoiseHash || NM == kNoiseConst);      // the fixed-point modes
+        constexpr bool RAW16 = (ElemT<DT>::bytes == 2 && FIXED && PRO == kProNone);
         float xf[32];
         if (!RAW16) widen_raw<DT>(raw_cur, xf);
 
@@ -564,9 +566,9 @@ quant_pack_kernel(const void* __restrict__ x_, const float* __restrict__ noise,
             for (int k = 0; k < 4; ++k) {
                 uint32_t acc0, acc1;
                 const uint32_t ctr_lo = ctr_lo0 + (uint32_t)(k * (piece_stride >> 3));
-                if (NM == kNoiseHash) {
-                    encode_piece_fx<DT, BITS, RAW16>(raw_cur.v[RAW16 ? k : 0], xf + k * 8, mn, nmn2, y2,
-                                                     ctr_lo, ctr_hi, key_lo, acc0, acc1);
+                if (FIXED) {
+                    encode_piece_fx<DT, BITS, RAW16, NM>(raw_cur.v[RAW16 ? k : 0], xf + k * 8, mn, nmn2, y2,
+                                                         ctr_lo, ctr_hi, key_lo, acc0, acc1);
                 } else {
                     float u8[8];
                     if (NM == kNoiseTensor)
@@ -664,11 +666,12 @@ cudaError_t launch_pack_one(const void* x, const float* noise, void* packed, flo
                                    float* mn, int64_t n_elems, int log2_L, uint64_t seed,
                                    uint64_t offset, int flags, float clamp_alpha, cudaStream_t st)
 {
-    // the default mode at group sizes 128 and 256 runs kernels with the group size compiled in
-    if (NM == kNoiseHash && log2_L == 2)
-        return launch_pack_fixed<DT, BITS, NM, (NM == kNoiseHash ? 2 : -1)>(x, noise, packed, scale, mn, n_elems, log2_L, seed, offset, flags, clamp_alpha, st);
-    if (NM == kNoiseHash && log2_L == 3)
-        return launch_pack_fixed<DT, BITS, NM, (NM == kNoiseHash ? 3 : -1)>(x, noise, packed, scale, mn, n_elems, log2_L, seed, offset, flags, clamp_alpha, st);
+    // the two fixed-point modes at group sizes 128 and 256 run kernels with the group size compiled in
+    constexpr bool kFixedPoint = (NM == kNoiseHash || NM == kNoiseConst);
+    if (kFixedPoint && log2_L == 2)
+        return launch_pack_fixed<DT, BITS, NM, (kFixedPoint ? 2 : -1)>(x, noise, packed, scale, mn, n_elems, log2_L, seed, offset, flags, clamp_alpha, st);
+    if (kFixedPoint && log2_L == 3)
+        return launch_pack_fixed<DT, BITS, NM, (kFixedPoint ? 3 : -1)>(x, noise, packed, scale, mn, n_elems, log2_L, seed, offset, flags, clamp_alpha, st);
     return launch_pack_fixed<DT, BITS, NM, -1>(x, noise, packed, scale, mn, n_elems, log2_L, seed, offset, flags, clamp_alpha, st);
 }
 

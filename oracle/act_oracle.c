@@ -25,17 +25,18 @@
  *     r  = mx - mn
  *     s  = r / qmax ; if !(s > 0) s = 1
  *     a  = x - mn ; q = a / s ; t = q + u ; code = clamp(floor(t), 0, qmax)
- * u is the caller's noise tensor or the constant 0.5f-1e-6f (round to nearest,
- * the reference's constant, act_triton_kernel.py:114).
+ * u is the caller's noise tensor.
  *
- * With neither (the "hash" mode, the product's default) the noise is one byte h
- * per element from the counter hash below, and a regular group -- range 0 or in
+ * Without one (the "hash" mode, the product's default) the noise is one byte h per
+ * element from the counter hash below; with FLAG_ROUND_NEAREST h is the constant 127
+ * (the reference's rounding constant 0.5f-1e-6f, act_triton_kernel.py:114, on a grid
+ * of 1/256: ties go down).  In both a regular group -- range 0 or in
  * [2^-50, 2^50] -- is quantised in fixed point with 8 fraction bits:
  *     y = 1 / s ; Q = RNE(a * y * 256), rounded once (v = fmaf(a, y, 2^15) and
  *     Q = the low mantissa bits of v) ; code = (Q + h) >> 8        (<= qmax, no clamp)
  * i.e. stochastic rounding of Q/256 with 8 noise bits.  An irregular group
  * (denormal, huge, infinite or NaN range) uses the float formula above with
- * u = h / 256.
+ * u = h / 256 (hash) or u = 0.5f-1e-6f (round to nearest).
  *
  * The "reference-compatible" scheme (ACT_FLAG_REF_COMPAT) follows the live
  * Triton kernel instead: optional clamp to +-alpha, optional tanh squash,
@@ -266,20 +267,24 @@ static int quant_pack_from(const void *x, int dtype, int64_t n_groups, int group
                         if (c < 0) c = 0;
                         if (c > qmax) c = qmax;
                     }
-                } else if ((flags & FLAG_ROUND_NEAREST) || noise) {
-                    const float u = (flags & FLAG_ROUND_NEAREST) ? half_c : noise[base + i];
+                } else if (noise && !(flags & FLAG_ROUND_NEAREST)) {
                     const float q = a / s;
-                    const float t = q + u;
+                    const float t = q + noise[base + i];
                     c = code_from_t(t, qmax);
                 } else {
-                    const uint32_t h = hash_byte((uint64_t)(first_group * group_size + base + i), seed, offset);
+                    /* the two fixed-point modes: a hash byte, or 127 for round to nearest
+                     * (0.5f - 1e-6f on the 1/256 grid: a tie goes down)                   */
+                    const int nearest = (flags & FLAG_ROUND_NEAREST) != 0;
+                    const uint32_t h = nearest ? 127u
+                        : hash_byte((uint64_t)(first_group * group_size + base + i), seed, offset);
                     if (regular) {
                         /* one rounding onto the 2^-8 grid; 2^15 <= v < 2^16 for a regular group */
                         const float v = fmaf(a, inv, 32768.0f);
                         const uint32_t Q = f32_bits(v) - f32_bits(32768.0f);
                         c = (int)((Q + h) >> 8);
                     } else {
-                        const float t = a / s + (float)h * (1.0f / 256.0f);
+                        const float u = nearest ? half_c : (float)h * (1.0f / 256.0f);
+                        const float t = a / s + u;
                         c = code_from_t(t, qmax);
                     }
                 }

@@ -299,9 +299,11 @@ def np_quant_pack(x: np.ndarray, group_size: int, bits: int, noise: np.ndarray |
             t = ((a * inv[:, None]).astype(np.float32) + HALF_C).astype(np.float32)
             codes = np.clip(np.trunc(t), 0, qmax).astype(np.uint32)
         else:
-            hashed = not (flags & FLAG_ROUND_NEAREST) and noise is None
-            if flags & FLAG_ROUND_NEAREST:
+            nearest = bool(flags & FLAG_ROUND_NEAREST)
+            hashed = nearest or noise is None                      # the two fixed-point modes
+            if nearest:
                 u = np.full(v.shape, HALF_C, np.float32)
+                h = np.full(v.shape, 127, np.uint32)
             elif noise is not None:
                 u = np.ascontiguousarray(noise, np.float32).reshape(v.shape)
             else:
