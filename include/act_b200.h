@@ -34,7 +34,7 @@ extern "C" {
 #define ACT_DTYPE_F16  2
 
 /* flags of act_quant_pack */
-#define ACT_FLAG_ROUND_NEAREST 1   /* u = 0.5f-1e-6f instead of noise (AC/act_triton_kernel.py:114) */
+#define ACT_FLAG_ROUND_NEAREST 1   /* no noise: round to nearest (constant of AC/act_triton_kernel.py:114) */
 #define ACT_FLAG_REF_COMPAT    2   /* live-Triton arithmetic: a*(1/s)+c, truncate                    */
 #define ACT_FLAG_REF_CLAMP     4   /* with REF_COMPAT: clamp x to +-clamp_alpha first                */
 #define ACT_FLAG_REF_TANH      8   /* with REF_COMPAT: x = tanh(x/0.5)*0.5 before the range          */
@@ -69,15 +69,24 @@ extern "C" {
  *
  *   x       [n_groups, group_size] of `dtype`, contiguous, 16-byte aligned
  *   noise   NULL, or fp32 [n_groups, group_size] of u in [0,1), 16-byte aligned
- *   seed, offset   used when noise == NULL and ACT_FLAG_ROUND_NEAREST is clear:
- *           element e takes u = 16 bits of hash(e >> 2; key(seed, offset)) / 65536;
- *           seed picks a family of streams, offset one stream (advance it per call)
+ *   seed, offset   used when noise == NULL and ACT_FLAG_ROUND_NEAREST is clear: element e
+ *           takes the noise byte h = byte (e & 7) of hash(e >> 3; key(seed, offset)); seed picks
+ *           a family of streams, offset one stream (advance it per call)
  *   packed  n_groups*group_size*bits/8 bytes, 16-byte aligned; 32-bit little-endian
  *           words, code j of a word at bits [j*bits,(j+1)*bits)
  *   scale, min   fp32 [n_groups]
  *
- * Default arithmetic (IEEE binary32, nothing fused): s = (max-min)/(2^bits-1),
- * s = 1 if that is not positive; code = clamp(floor((x-min)/s + u), 0, 2^bits-1).
+ * Per group: min and max (-0 < +0, a NaN makes min NaN, scale 1, codes 0),
+ * s = (max-min)/(2^bits-1) in IEEE binary32, s = 1 if that is not positive.  Codes:
+ *   noise given:  code = clamp(floor((x-min)/s + u), 0, 2^bits-1), every operation IEEE
+ *                 binary32 round-to-nearest, nothing fused;
+ *   noise NULL:   fixed point with 8 fraction bits for a group whose range is 0 or in
+ *                 [2^-50, 2^50]: Q = RNE((x-min) * RN(1/s) * 256) rounded once (the low mantissa
+ *                 bits of fmaf(x-min, RN(1/s), 2^15)), code = (Q + h) >> 8, which cannot exceed
+ *                 2^bits-1; h is the noise byte, or the constant 127 with
+ *                 ACT_FLAG_ROUND_NEAREST (0.5f-1e-6f on the 1/256 grid, a tie going down).
+ *                 Any other group uses the formula of the first case with u = h/256
+ *                 (u = 0.5f-1e-6f for round to nearest).
  */
 ACT_API int act_quant_pack(const void* x, int dtype, int64_t n_groups, int group_size, int bits,
                    const float* noise, uint64_t seed, uint64_t offset, int flags,
