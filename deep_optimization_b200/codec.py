@@ -348,17 +348,35 @@ def bn_bwd_reduce(packed: torch.Tensor, scale: torch.Tensor, mn: torch.Tensor, d
                                             mask.data_ptr(), _DTYPES[dy.dtype], N, C, hw, group_size, bits,
                                             sums.data_ptr(), _stream_ptr(dy))
     _lib.check(rc, "act_bn_bwd_reduce")
-    return sums[:C], sums[C:]
+    return sums[:C], sums[C:]          # two views of one [2C] tensor (bn_bwd_coef takes it whole)
 
 
-def bn_bwd_dx(packed: torch.Tensor, scale: torch.Tensor, mn: torch.Tensor, dy: torch.Tensor, k1: torch.Tensor,
-              k2: torch.Tensor, k3: torch.Tensor, bits: int, group_size: int,
-              mask: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """dx = k1[c] * dy - k2[c] - k3[c] * x_hat (dy zeroed where the fused ReLU's `mask` bit is clear)."""
+def bn_bwd_coef(sums: torch.Tensor, params: torch.Tensor, count: float) -> torch.Tensor:
+    """The [C, 4] table (k1, k2, k3, 0) of bn_bwd_dx from bn_bwd_reduce's sums ([2C], or the
+    pair it returns) and bn_stats' params."""
+    if isinstance(sums, (tuple, list)):
+        sums = torch.cat([sums[0], sums[1]])
+    sums = sums.contiguous()
+    C = params.shape[0]
+    coef = torch.empty((C, 4), dtype=torch.float32, device=params.device)
+    with torch.cuda.device(params.device):
+        rc = _lib.load().act_bn_bwd_coef(sums.data_ptr(), params.data_ptr(), C, float(count), coef.data_ptr(),
+                                         _stream_ptr(params))
+    _lib.check(rc, "act_bn_bwd_coef")
+    return coef
+
+
+def bn_bwd_dx(packed: torch.Tensor, scale: torch.Tensor, mn: torch.Tensor, dy: torch.Tensor,
+              k1: Optional[torch.Tensor], k2: Optional[torch.Tensor], k3: Optional[torch.Tensor], bits: int,
+              group_size: int, mask: Optional[torch.Tensor] = None,
+              coef: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """dx = k1[c] * dy - k2[c] - k3[c] * x_hat (dy zeroed where the fused ReLU's `mask` bit is
+    clear); the constants come as three vectors or as bn_bwd_coef's table."""
     dy = dy.contiguous()
     N, C = dy.shape[0], dy.shape[1]
     hw = dy.numel() // (N * C)
-    coef = torch.stack([k1.float(), k2.float(), k3.float(), torch.zeros_like(k1, dtype=torch.float32)], dim=1).contiguous()
+    if coef is None:
+        coef = torch.stack([k1.float(), k2.float(), k3.float(), torch.zeros_like(k1, dtype=torch.float32)], dim=1).contiguous()
     dx = torch.empty_like(dy)
     lib = _lib.load()
     with torch.cuda.device(dy.device):

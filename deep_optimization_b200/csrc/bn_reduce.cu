@@ -44,6 +44,28 @@ template <int DT> __device__ __forceinline__ float load1(const uint8_t* p, int64
     return widen_lo<D16>((uint32_t)__ldg(reinterpret_cast<const unsigned short*>(p) + e));
 }
 
+// eight consecutive elements starting at element e (a multiple of 8), widened to fp32
+template <int DT> __device__ __forceinline__ void load8f(const uint8_t* p, int64_t e, float (&f)[8]) {
+    if (ElemT<DT>::bytes == 4) {
+        const uint4 a = ldg_stream_v4(p + e * 4), b = ldg_stream_v4(p + e * 4 + 16);
+        f[0] = __uint_as_float(a.x); f[1] = __uint_as_float(a.y); f[2] = __uint_as_float(a.z); f[3] = __uint_as_float(a.w);
+        f[4] = __uint_as_float(b.x); f[5] = __uint_as_float(b.y); f[6] = __uint_as_float(b.z); f[7] = __uint_as_float(b.w);
+    } else {
+        const uint4 v = ldg_stream_v4(p + e * 2);
+        constexpr int D16 = (DT == ACT_DTYPE_F32) ? ACT_DTYPE_BF16 : DT;
+        f[0] = widen_lo<D16>(v.x); f[1] = widen_hi<D16>(v.x); f[2] = widen_lo<D16>(v.y); f[3] = widen_hi<D16>(v.y);
+        f[4] = widen_lo<D16>(v.z); f[5] = widen_hi<D16>(v.z); f[6] = widen_lo<D16>(v.w); f[7] = widen_hi<D16>(v.w);
+    }
+}
+
+// the eight BITS-bit codes of elements e..e+7 (e a multiple of 8), low word first
+template <int BITS> __device__ __forceinline__ uint2 load_codes8v(const uint8_t* packed, int64_t e) {
+    if (BITS == 8) return __ldg(reinterpret_cast<const uint2*>(packed + e));
+    if (BITS == 4) return make_uint2(__ldg(reinterpret_cast<const uint32_t*>(packed + (e >> 1))), 0u);
+    if (BITS == 2) return make_uint2(__ldg(reinterpret_cast<const unsigned short*>(packed + (e >> 2))), 0u);
+    return make_uint2(__ldg(packed + (e >> 3)), 0u);
+}
+
 // the four BITS-bit codes of elements e..e+3 (e a multiple of 4)
 template <int BITS> __device__ __forceinline__ uint32_t load_codes4(const uint8_t* packed, int64_t e) {
     if (BITS == 8) return __ldg(reinterpret_cast<const uint32_t*>(packed + e));
@@ -56,7 +78,8 @@ template <int BITS> __device__ __forceinline__ uint32_t load_codes4(const uint8_
 //         block's partial pair out[(c * S + s) * 2 + {0, 1}] (no atomics, no zeroing);
 // MODE 1: a = sum(dy * x_hat), b = sum(dy), added to out[c] and out[C + c]; with `mask`
 //         (one bit per element, the fused ReLU's) dy counts only where its bit is set.
-template <int DT, int MODE, int BITS>
+// VEC = elements per lane and step: 8 when HW is a multiple of 8 (16-byte loads), else 4.
+template <int DT, int MODE, int BITS, int VEC>
 __global__ void __launch_bounds__(kRedThreads)
 bn_plane_reduce_kernel(const uint8_t* __restrict__ x, const uint8_t* __restrict__ packed,
                        const float* __restrict__ scale, const float* __restrict__ mn,
@@ -67,7 +90,7 @@ bn_plane_reduce_kernel(const uint8_t* __restrict__ x, const uint8_t* __restrict_
     const uint32_t c = blockIdx.x, s = blockIdx.y, S = gridDim.y;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int64_t n0 = n_batch * s / S, n1 = n_batch * (s + 1) / S;
-    const uint32_t vpp = hw >> 2;                           // four-element vectors per plane
+    const uint32_t vpp = hw / VEC;                          // VEC-element vectors per plane
     grid_dependency_wait();
     grid_launch_dependents();
     const float pivot = (MODE == 0) ? load1<DT>(x, (int64_t)c * hw) : 0.0f;
@@ -76,29 +99,34 @@ bn_plane_reduce_kernel(const uint8_t* __restrict__ x, const uint8_t* __restrict_
         const int64_t plane_e0 = (n * C + c) * hw;
 #pragma unroll 4
         for (uint32_t v = lane; v < vpp; v += 32) {
-            const int64_t e = plane_e0 + 4 * (int64_t)v;
-            float f[4];
-            load4<DT>(x, e, f);
+            const int64_t e = plane_e0 + VEC * (int64_t)v;
+            float f[VEC];
+            if (VEC == 8) load8f<DT>(x, e, reinterpret_cast<float (&)[8]>(f));
+            else load4<DT>(x, e, reinterpret_cast<float (&)[4]>(f));
             if (MODE == 0) {
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
+                for (int i = 0; i < VEC; ++i) {
                     const float d = __fsub_rn(f[i], pivot);
                     a = __fadd_rn(a, d);
                     b = __fmaf_rn(d, d, b);
                 }
             } else {
                 constexpr uint32_t MASK = (1u << BITS) - 1u;
-                const uint32_t w = load_codes4<BITS>(packed, e);
+                uint2 w;
+                if (VEC == 8) w = load_codes8v<BITS>(packed, e);
+                else w = make_uint2(load_codes4<BITS>(packed, e), 0u);
                 const int64_t g = e >> log2_gs;
                 const float sc = __ldg(scale + g), m = __ldg(mn + g);
                 if (mask) {
-                    const uint32_t keep = load_codes4<1>(mask, e);
+                    const uint32_t keep = (VEC == 8) ? (uint32_t)__ldg(mask + (e >> 3)) : load_codes4<1>(mask, e);
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) f[i] = ((keep >> i) & 1u) ? f[i] : 0.0f;
+                    for (int i = 0; i < VEC; ++i) f[i] = ((keep >> i) & 1u) ? f[i] : 0.0f;
                 }
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float code = __uint_as_float(kMagicBits | ((w >> (i * BITS)) & MASK)) - kMagic;
+                for (int i = 0; i < VEC; ++i) {
+                    const uint32_t word = (BITS == 8 && i >= 4) ? w.y : w.x;
+                    const int sh = (BITS == 8) ? (i & 3) * 8 : i * BITS;
+                    const float code = __uint_as_float(kMagicBits | ((word >> sh) & MASK)) - kMagic;
                     a = __fmaf_rn(f[i], __fmaf_rn(code, sc, m), a);
                     b = __fadd_rn(b, f[i]);
                 }
@@ -158,6 +186,21 @@ __global__ void bn_stats_finalize_kernel(const uint8_t* __restrict__ x, const fl
     }
 }
 
+// coef[c] = (k1, k1 * sum(dy) / M, k1 * sum(dy * x_hat) / M, 0) with k1 = weight * invstd: the
+// per-channel constants of dx = k1 * dy - k2 - k3 * x_hat
+__global__ void bn_bwd_coef_kernel(const float* __restrict__ sums, const float4* __restrict__ params,
+                                   float4* __restrict__ coef, uint32_t C, float inv_count)
+{
+    grid_dependency_wait();
+    grid_launch_dependents();
+    const uint32_t c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const float4 p = params[c];
+    const float k1 = __fmul_rn(p.z, p.y);
+    coef[c] = make_float4(k1, __fmul_rn(__fmul_rn(k1, sums[C + c]), inv_count),
+                          __fmul_rn(__fmul_rn(k1, sums[c]), inv_count), 0.0f);
+}
+
 // batch slices per channel: enough blocks for eight per SM, at least eight planes per block
 static int bn_splits(int64_t n_batch, int channels) {
     int64_t want = (148 * 8 + channels - 1) / channels;
@@ -186,7 +229,8 @@ static cudaError_t launch_stats(const uint8_t* x, int64_t n_batch, int C, int64_
     cfg.stream = st;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, bn_plane_reduce_kernel<DT, 0, 2>, x, static_cast<const uint8_t*>(nullptr),
+    auto kernel = (hw & 7) ? bn_plane_reduce_kernel<DT, 0, 2, 4> : bn_plane_reduce_kernel<DT, 0, 2, 8>;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, x, static_cast<const uint8_t*>(nullptr),
                                        static_cast<const float*>(nullptr), static_cast<const float*>(nullptr),
                                        static_cast<const uint8_t*>(nullptr), ws, n_batch, (uint32_t)C, (uint32_t)hw, 5);
     if (e != cudaSuccess) return e;
@@ -209,7 +253,8 @@ static cudaError_t launch_bwd_reduce_one(const uint8_t* dy, const uint8_t* packe
     cfg.stream = st;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, bn_plane_reduce_kernel<DT, 1, BITS>, dy, packed, scale, mn, mask, sums, n_batch,
+    auto kernel = (hw & 7) ? bn_plane_reduce_kernel<DT, 1, BITS, 4> : bn_plane_reduce_kernel<DT, 1, BITS, 8>;
+    return cudaLaunchKernelEx(&cfg, kernel, dy, packed, scale, mn, mask, sums, n_batch,
                               (uint32_t)C, (uint32_t)hw, log2_gs);
 }
 
@@ -300,4 +345,17 @@ extern "C" int act_bn_relu_bwd_reduce(const void* packed, const float* scale, co
     if (!mask_bits) return n_batch * channels * hw == 0 ? ACT_OK : ACT_ERR_NULL;
     return bn_bwd_reduce_common(packed, scale, mn, dy, mask_bits, dtype, n_batch, channels, hw, group_size, bits,
                                 sums, stream);
+}
+
+extern "C" int act_bn_bwd_coef(const float* sums, const float* params, int channels, double count,
+                               float* coef, void* stream)
+{
+    using namespace act;
+    if (channels <= 0 || !(count > 0.0)) return ACT_ERR_SIZE;
+    if (!sums || !params || !coef) return ACT_ERR_NULL;
+    if (((uintptr_t)params | (uintptr_t)coef) & 15 || ((uintptr_t)sums & 3)) return ACT_ERR_ALIGN;
+    cudaError_t e = launch_overlapped(bn_bwd_coef_kernel, (channels + 127) / 128, 128, static_cast<cudaStream_t>(stream),
+                                      sums, reinterpret_cast<const float4*>(params), reinterpret_cast<float4*>(coef),
+                                      (uint32_t)channels, (float)(1.0 / count));
+    return e == cudaSuccess ? ACT_OK : ACT_ERR_LAUNCH;
 }

@@ -80,9 +80,9 @@ class _DOBatchNorm(Function):
             ctx.sync = (process_group, world_size)
             if fuse_relu:
                 ctx.relu_mask = True
-                ctx.save_for_backward(weight, packed, scale, mn, params[:, 1], out[4])
+                ctx.save_for_backward(weight, packed, scale, mn, params, out[4])
             else:
-                ctx.save_for_backward(weight, packed, scale, mn, params[:, 1])
+                ctx.save_for_backward(weight, packed, scale, mn, params)
             return y
         if world_size == 1:
             # one native kernel: x_hat and the saved statistics (running stats updated in place)
@@ -131,10 +131,9 @@ class _DOBatchNorm(Function):
             bits, gs, count = ctx.fused
             dyc = dy.contiguous()
             dgamma, dbeta = codec.bn_bwd_reduce(q_out, q_scale, q_min, dyc, bits, gs, mask=mask)
-            w = weight.float() if weight is not None else torch.ones_like(invstd)
-            k1 = w * invstd
-            dx = codec.bn_bwd_dx(q_out, q_scale, q_min, dyc, k1, k1 * dbeta / count, k1 * dgamma / count, bits, gs,
-                                 mask=mask)
+            # `invstd` is the whole [C, 4] parameter table on this path
+            coef = codec.bn_bwd_coef(dgamma._base if dgamma._base is not None else (dgamma, dbeta), invstd, count)
+            dx = codec.bn_bwd_dx(q_out, q_scale, q_min, dyc, None, None, None, bits, gs, mask=mask, coef=coef)
             dw = dgamma.to(weight.dtype) if weight is not None else None
             db = dbeta.to(weight.dtype) if weight is not None else None
             return dx, dw, db, None, None, None, None, None, None, None, None, None, None

@@ -161,6 +161,9 @@ ACT_API int act_mul_dequant_unpack(const void* packed, const float* scale, const
  *       and sum(dy) to sums[C+c] (one atomic pair per block: the order of the at most
  *       148*8/C partial sums is not fixed). C <= 65535.
  *   act_bn_bwd_dx: coef = fp32 [C][4] (k1, k2, k3, unused); dx = k1*dy - k2 - k3*x_hat.
+ *   act_bn_bwd_coef: that table from the sums of act_bn_bwd_reduce and the params of
+ *       act_bn_stats: k1 = weight*invstd, k2 = k1*sum(dy)/count, k3 = k1*sum(dy*x_hat)/count
+ *       (count = N*HW); one small launch instead of a chain of elementwise operators.
  */
 ACT_API int act_bn_fwd_norm_quant_pack(const void* x, int dtype, int64_t n_batch, int channels, int64_t hw,
                                const float* params, int group_size, int bits, uint64_t seed,
@@ -173,6 +176,8 @@ ACT_API int act_bn_stats(const void* x, int dtype, int64_t n_batch, int channels
 ACT_API int act_bn_bwd_reduce(const void* packed, const float* scale, const float* min, const void* dy,
                       int dtype, int64_t n_batch, int channels, int64_t hw, int group_size, int bits,
                       float* sums, void* stream);
+ACT_API int act_bn_bwd_coef(const float* sums, const float* params, int channels, double count,
+                    float* coef, void* stream);
 ACT_API int act_bn_bwd_dx(const void* packed, const float* scale, const float* min, const void* dy,
                   int dtype, int64_t n_batch, int channels, int64_t hw, int group_size, int bits,
                   const float* coef, void* dx, void* stream);

@@ -225,3 +225,19 @@ def test_bn_relu_module_matches_pytorch(cuda_device):
     assert (x.grad - xr.grad).abs().max() < 0.05
     assert (bn.weight.grad - rb.weight.grad).norm() / rb.weight.grad.norm() < 0.03
     assert torch.allclose(bn.bias.grad, rb.bias.grad, rtol=1e-4, atol=1e-3)
+
+
+def test_bn_bwd_coef(cuda_device):
+    """k1 = w * invstd, k2 = k1 * sum(dy) / M, k3 = k1 * sum(dy * x_hat) / M, each product rounded to fp32."""
+    from deep_optimization_b200 import codec
+    g = torch.Generator().manual_seed(21)
+    C, M = 37, 5000.0
+    sums = torch.randn(2 * C, generator=g).to(cuda_device)
+    params = torch.rand(C, 4, generator=g).to(cuda_device) + 0.5
+    coef = codec.bn_bwd_coef(sums, params, M)
+    k1 = params[:, 2] * params[:, 1]
+    inv = torch.tensor(1.0 / M, dtype=torch.float32, device=cuda_device)
+    assert torch.equal(coef[:, 0], k1)
+    assert torch.equal(coef[:, 1], k1 * sums[C:] * inv)
+    assert torch.equal(coef[:, 2], k1 * sums[:C] * inv)
+    assert (coef[:, 3] == 0).all()
