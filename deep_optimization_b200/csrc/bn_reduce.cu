@@ -5,11 +5,11 @@
 //                       kernel reads; running statistics updated in place
 //   act_bn_bwd_reduce:  sum(dy * x_hat) and sum(dy) per channel, x_hat decoded from the codec
 //
-// Both walk the tensor plane by plane: block (c, s) owns channel c and a slice of the batch,
-// its eight warps take the planes (n, c) of the slice in turn, the lanes stride over the
-// plane four elements at a time, and every lane accumulates in registers until the block's
-// slice is done, so there is one warp reduction per block instead of one per load.  Loads
-// are contiguous inside a plane (256 or 512 bytes per warp instruction).
+// Both give block (c, s) channel c and a slice of the batch; the block walks the planes (n, c)
+// of its slice as one list of 4- or 8-element vectors, thread t taking vectors t, t + 256, ...,
+// and every lane accumulates in registers until the slice is done, so there is one warp
+// reduction per block instead of one per load.  Loads are contiguous inside a plane.  The
+// grid is one resident wave: the number of slices per channel follows from the occupancy.
 // HBM traffic: s_in bytes per element (plus bits/8 in backward); nothing is written but
 // 2 floats per block.
 //
@@ -90,46 +90,51 @@ bn_plane_reduce_kernel(const uint8_t* __restrict__ x, const uint8_t* __restrict_
     const uint32_t c = blockIdx.x, s = blockIdx.y, S = gridDim.y;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int64_t n0 = n_batch * s / S, n1 = n_batch * (s + 1) / S;
+    const uint32_t planes = (uint32_t)(n1 - n0);            // the host keeps a slice below 2^31 planes
     const uint32_t vpp = hw / VEC;                          // VEC-element vectors per plane
+    // The slice is walked as one list of (plane, vector) items, thread t taking items
+    // t, t + 256, ...: every lane is busy whatever the plane size, and consecutive lanes read
+    // consecutive vectors.  The position advances without a division.
+    const uint32_t step_n = kRedThreads / vpp, step_v = kRedThreads % vpp;
+    uint32_t n = threadIdx.x / vpp, v = threadIdx.x % vpp;
     grid_dependency_wait();
     grid_launch_dependents();
     const float pivot = (MODE == 0) ? load1<DT>(x, (int64_t)c * hw) : 0.0f;
     float a = 0.0f, b = 0.0f;
-    for (int64_t n = n0 + warp; n < n1; n += kRedWarps) {
-        const int64_t plane_e0 = (n * C + c) * hw;
 #pragma unroll 4
-        for (uint32_t v = lane; v < vpp; v += 32) {
-            const int64_t e = plane_e0 + VEC * (int64_t)v;
-            float f[VEC];
-            if (VEC == 8) load8f<DT>(x, e, reinterpret_cast<float (&)[8]>(f));
-            else load4<DT>(x, e, reinterpret_cast<float (&)[4]>(f));
-            if (MODE == 0) {
+    while (n < planes) {
+        const int64_t e = ((n0 + n) * C + c) * hw + VEC * (int64_t)v;
+        v += step_v; n += step_n;
+        if (v >= vpp) { v -= vpp; ++n; }
+        float f[VEC];
+        if (VEC == 8) load8f<DT>(x, e, reinterpret_cast<float (&)[8]>(f));
+        else load4<DT>(x, e, reinterpret_cast<float (&)[4]>(f));
+        if (MODE == 0) {
 #pragma unroll
-                for (int i = 0; i < VEC; ++i) {
-                    const float d = __fsub_rn(f[i], pivot);
-                    a = __fadd_rn(a, d);
-                    b = __fmaf_rn(d, d, b);
-                }
-            } else {
-                constexpr uint32_t MASK = (1u << BITS) - 1u;
-                uint2 w;
-                if (VEC == 8) w = load_codes8v<BITS>(packed, e);
-                else w = make_uint2(load_codes4<BITS>(packed, e), 0u);
-                const int64_t g = e >> log2_gs;
-                const float sc = __ldg(scale + g), m = __ldg(mn + g);
-                if (mask) {
-                    const uint32_t keep = (VEC == 8) ? (uint32_t)__ldg(mask + (e >> 3)) : load_codes4<1>(mask, e);
+            for (int i = 0; i < VEC; ++i) {
+                const float d = __fsub_rn(f[i], pivot);
+                a = __fadd_rn(a, d);
+                b = __fmaf_rn(d, d, b);
+            }
+        } else {
+            constexpr uint32_t MASK = (1u << BITS) - 1u;
+            uint2 w;
+            if (VEC == 8) w = load_codes8v<BITS>(packed, e);
+            else w = make_uint2(load_codes4<BITS>(packed, e), 0u);
+            const int64_t g = e >> log2_gs;
+            const float sc = __ldg(scale + g), m = __ldg(mn + g);
+            if (mask) {
+                const uint32_t keep = (VEC == 8) ? (uint32_t)__ldg(mask + (e >> 3)) : load_codes4<1>(mask, e);
 #pragma unroll
-                    for (int i = 0; i < VEC; ++i) f[i] = ((keep >> i) & 1u) ? f[i] : 0.0f;
-                }
+                for (int i = 0; i < VEC; ++i) f[i] = ((keep >> i) & 1u) ? f[i] : 0.0f;
+            }
 #pragma unroll
-                for (int i = 0; i < VEC; ++i) {
-                    const uint32_t word = (BITS == 8 && i >= 4) ? w.y : w.x;
-                    const int sh = (BITS == 8) ? (i & 3) * 8 : i * BITS;
-                    const float code = __uint_as_float(kMagicBits | ((word >> sh) & MASK)) - kMagic;
-                    a = __fmaf_rn(f[i], __fmaf_rn(code, sc, m), a);
-                    b = __fadd_rn(b, f[i]);
-                }
+            for (int i = 0; i < VEC; ++i) {
+                const uint32_t word = (BITS == 8 && i >= 4) ? w.y : w.x;
+                const int sh = (BITS == 8) ? (i & 3) * 8 : i * BITS;
+                const float code = __uint_as_float(kMagicBits | ((word >> sh) & MASK)) - kMagic;
+                a = __fmaf_rn(f[i], __fmaf_rn(code, sc, m), a);
+                b = __fadd_rn(b, f[i]);
             }
         }
     }
@@ -201,15 +206,32 @@ __global__ void bn_bwd_coef_kernel(const float* __restrict__ sums, const float4*
                           __fmul_rn(__fmul_rn(k1, sums[c]), inv_count), 0.0f);
 }
 
-// batch slices per channel: enough blocks for eight per SM, at least eight planes per block
-static int bn_splits(int64_t n_batch, int channels) {
-    int64_t want = (148 * 8 + channels - 1) / channels;
-    int64_t most = n_batch / kRedWarps;
-    if (most < 1) most = 1;
-    if (want > most) want = most;
+// Batch slices per channel: as many as keep the whole grid resident at once (`capacity`
+// blocks), at least one plane per slice, and few enough planes per slice for 32-bit counters.
+static int bn_splits(int64_t n_batch, int channels, int capacity) {
+    int64_t want = capacity / channels;
     if (want < 1) want = 1;
+    if (want > n_batch) want = n_batch;
+    const int64_t least = (n_batch + (1ll << 30) - 1) >> 30;
+    if (want < least) want = least;
     if (want > 65535) want = 65535;
     return (int)want;
+}
+
+// resident blocks of a reduce kernel on the current device (SM count x occupancy), asked once
+// per instantiation; the statistics workspace is sized for the largest answer possible
+constexpr int kMaxCapacity = 148 * 8 * 2;
+template <typename K> static int reduce_capacity(K kernel) {
+    static int cached = 0;
+    if (cached == 0) {
+        int per_sm = 0, dev = 0, sms = 148;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kRedThreads, 0) != cudaSuccess || per_sm < 1) per_sm = 4;
+        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        int cap = per_sm * sms;
+        if (cap > kMaxCapacity) cap = kMaxCapacity;
+        cached = cap;
+    }
+    return cached;
 }
 
 static bool dtype_ok(int d) { return d == ACT_DTYPE_F32 || d == ACT_DTYPE_BF16 || d == ACT_DTYPE_F16; }
@@ -219,7 +241,9 @@ static cudaError_t launch_stats(const uint8_t* x, int64_t n_batch, int C, int64_
                                 const float* weight, const float* bias, float* rm, float* rv, double momentum,
                                 float* params, float* ws, cudaStream_t st)
 {
-    const int S = bn_splits(n_batch, C);
+    auto kernel = (hw & 7) ? bn_plane_reduce_kernel<DT, 0, 2, 4> : bn_plane_reduce_kernel<DT, 0, 2, 8>;
+    const int S = bn_splits(n_batch, C, (hw & 7) ? reduce_capacity(bn_plane_reduce_kernel<DT, 0, 2, 4>)
+                                                 : reduce_capacity(bn_plane_reduce_kernel<DT, 0, 2, 8>));
     cudaLaunchConfig_t cfg = {};
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -229,7 +253,6 @@ static cudaError_t launch_stats(const uint8_t* x, int64_t n_batch, int C, int64_
     cfg.stream = st;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    auto kernel = (hw & 7) ? bn_plane_reduce_kernel<DT, 0, 2, 4> : bn_plane_reduce_kernel<DT, 0, 2, 8>;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, x, static_cast<const uint8_t*>(nullptr),
                                        static_cast<const float*>(nullptr), static_cast<const float*>(nullptr),
                                        static_cast<const uint8_t*>(nullptr), ws, n_batch, (uint32_t)C, (uint32_t)hw, 5);
@@ -243,7 +266,9 @@ template <int DT, int BITS>
 static cudaError_t launch_bwd_reduce_one(const uint8_t* dy, const uint8_t* packed, const float* scale, const float* mn,
                                          const uint8_t* mask, float* sums, int64_t n_batch, int C, int64_t hw, int log2_gs, cudaStream_t st)
 {
-    const int S = bn_splits(n_batch, C);
+    auto kernel = (hw & 7) ? bn_plane_reduce_kernel<DT, 1, BITS, 4> : bn_plane_reduce_kernel<DT, 1, BITS, 8>;
+    const int S = bn_splits(n_batch, C, (hw & 7) ? reduce_capacity(bn_plane_reduce_kernel<DT, 1, BITS, 4>)
+                                                 : reduce_capacity(bn_plane_reduce_kernel<DT, 1, BITS, 8>));
     cudaLaunchConfig_t cfg = {};
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -253,7 +278,6 @@ static cudaError_t launch_bwd_reduce_one(const uint8_t* dy, const uint8_t* packe
     cfg.stream = st;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    auto kernel = (hw & 7) ? bn_plane_reduce_kernel<DT, 1, BITS, 4> : bn_plane_reduce_kernel<DT, 1, BITS, 8>;
     return cudaLaunchKernelEx(&cfg, kernel, dy, packed, scale, mn, mask, sums, n_batch,
                               (uint32_t)C, (uint32_t)hw, log2_gs);
 }
@@ -276,7 +300,7 @@ static cudaError_t launch_bwd_reduce(int bits, const uint8_t* dy, const uint8_t*
 extern "C" size_t act_bn_stats_workspace(int64_t n_batch, int channels)
 {
     if (n_batch <= 0 || channels <= 0) return 0;
-    return (size_t)channels * (size_t)act::bn_splits(n_batch, channels) * 2 * sizeof(float);
+    return (size_t)channels * (size_t)act::bn_splits(n_batch, channels, act::kMaxCapacity) * 2 * sizeof(float);
 }
 
 extern "C" int act_bn_stats(const void* x, int dtype, int64_t n_batch, int channels, int64_t hw, double eps,
