@@ -101,11 +101,15 @@ bn_plane_reduce_kernel(const uint8_t* __restrict__ x, const uint8_t* __restrict_
     grid_launch_dependents();
     const float pivot = (MODE == 0) ? load1<DT>(x, (int64_t)c * hw) : 0.0f;
     float a = 0.0f, b = 0.0f;
+    // element index of the thread's item, advanced with the position (no multiplies in the loop)
+    const int64_t plane_stride = (int64_t)C * hw;
+    const int64_t step_e = (int64_t)step_n * plane_stride + (int64_t)step_v * VEC;
+    int64_t e_next = ((n0 + n) * C + c) * hw + VEC * (int64_t)v;
 #pragma unroll 4
     while (n < planes) {
-        const int64_t e = ((n0 + n) * C + c) * hw + VEC * (int64_t)v;
-        v += step_v; n += step_n;
-        if (v >= vpp) { v -= vpp; ++n; }
+        const int64_t e = e_next;
+        v += step_v; n += step_n; e_next += step_e;
+        if (v >= vpp) { v -= vpp; ++n; e_next += plane_stride - hw; }
         float f[VEC];
         if (VEC == 8) load8f<DT>(x, e, reinterpret_cast<float (&)[8]>(f));
         else load4<DT>(x, e, reinterpret_cast<float (&)[4]>(f));

@@ -84,7 +84,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, Smem* 
     return false;
 }
 // Warp-wide bounded wait: lane 0 polls (with a short sleep between polls, so the 256
-// epilogue threads do not flood the shared-memory pipe), the verdict is broadcast.
+// epilogue threads do not flood the shared-memory pipe), the outcome is broadcast.
 __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, Smem* s, uint32_t code) {
     uint32_t ok = 1;
     if ((threadIdx.x & 31) == 0) {
