@@ -23,39 +23,10 @@ namespace act {
 constexpr int kRedThreads = 256;
 constexpr int kRedWarps = kRedThreads / 32;
 
-// four consecutive elements starting at element e (a multiple of 4), widened to fp32
-template <int DT> __device__ __forceinline__ void load4(const uint8_t* p, int64_t e, float (&f)[4]) {
-    if (ElemT<DT>::bytes == 4) {
-        const uint4 v = ldg_stream_v4(p + e * 4);
-        f[0] = __uint_as_float(v.x); f[1] = __uint_as_float(v.y);
-        f[2] = __uint_as_float(v.z); f[3] = __uint_as_float(v.w);
-    } else {
-        uint2 v;
-        asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p + e * 2));
-        constexpr int D16 = (DT == ACT_DTYPE_F32) ? ACT_DTYPE_BF16 : DT;
-        f[0] = widen_lo<D16>(v.x); f[1] = widen_hi<D16>(v.x);
-        f[2] = widen_lo<D16>(v.y); f[3] = widen_hi<D16>(v.y);
-    }
-}
-
 template <int DT> __device__ __forceinline__ float load1(const uint8_t* p, int64_t e) {
     if (ElemT<DT>::bytes == 4) return __ldg(reinterpret_cast<const float*>(p) + e);
     constexpr int D16 = (DT == ACT_DTYPE_F32) ? ACT_DTYPE_BF16 : DT;
     return widen_lo<D16>((uint32_t)__ldg(reinterpret_cast<const unsigned short*>(p) + e));
-}
-
-// eight consecutive elements starting at element e (a multiple of 8), widened to fp32
-template <int DT> __device__ __forceinline__ void load8f(const uint8_t* p, int64_t e, float (&f)[8]) {
-    if (ElemT<DT>::bytes == 4) {
-        const uint4 a = ldg_stream_v4(p + e * 4), b = ldg_stream_v4(p + e * 4 + 16);
-        f[0] = __uint_as_float(a.x); f[1] = __uint_as_float(a.y); f[2] = __uint_as_float(a.z); f[3] = __uint_as_float(a.w);
-        f[4] = __uint_as_float(b.x); f[5] = __uint_as_float(b.y); f[6] = __uint_as_float(b.z); f[7] = __uint_as_float(b.w);
-    } else {
-        const uint4 v = ldg_stream_v4(p + e * 2);
-        constexpr int D16 = (DT == ACT_DTYPE_F32) ? ACT_DTYPE_BF16 : DT;
-        f[0] = widen_lo<D16>(v.x); f[1] = widen_hi<D16>(v.x); f[2] = widen_lo<D16>(v.y); f[3] = widen_hi<D16>(v.y);
-        f[4] = widen_lo<D16>(v.z); f[5] = widen_hi<D16>(v.z); f[6] = widen_lo<D16>(v.w); f[7] = widen_hi<D16>(v.w);
-    }
 }
 
 // the eight BITS-bit codes of elements e..e+7 (e a multiple of 8), low word first
@@ -105,40 +76,105 @@ bn_plane_reduce_kernel(const uint8_t* __restrict__ x, const uint8_t* __restrict_
     const int64_t plane_stride = (int64_t)C * hw;
     const int64_t step_e = (int64_t)step_n * plane_stride + (int64_t)step_v * VEC;
     int64_t e_next = ((n0 + n) * C + c) * hw + VEC * (int64_t)v;
-#pragma unroll 4
+    // U items per trip: all their loads go out before the first one is consumed (a thread has
+    // only a few dozen items, so the loop is bound by load latency, not by instructions)
+#ifndef ACT_BN_U8
+#define ACT_BN_U8 4
+#endif
+#ifndef ACT_BN_U4
+#define ACT_BN_U4 2
+#endif
+    constexpr int U = (MODE == 0) ? 4 : (VEC == 8 ? ACT_BN_U8 : ACT_BN_U4);
+    constexpr int RAW = (ElemT<DT>::bytes == 4) ? VEC / 4 : (VEC == 8 ? 1 : 0);   // uint4 per item (0: one uint2)
     while (n < planes) {
-        const int64_t e = e_next;
-        v += step_v; n += step_n; e_next += step_e;
-        if (v >= vpp) { v -= vpp; ++n; e_next += plane_stride - hw; }
-        float f[VEC];
-        if (VEC == 8) load8f<DT>(x, e, reinterpret_cast<float (&)[8]>(f));
-        else load4<DT>(x, e, reinterpret_cast<float (&)[4]>(f));
-        if (MODE == 0) {
+        int64_t e[U];
+        bool ok[U];
+        uint4 raw[U][RAW > 0 ? RAW : 1];
+        uint2 w[U];
+        uint32_t keep[U];
+        float sc[U], m[U];
 #pragma unroll
-            for (int i = 0; i < VEC; ++i) {
-                const float d = __fsub_rn(f[i], pivot);
-                a = __fadd_rn(a, d);
-                b = __fmaf_rn(d, d, b);
+        for (int u = 0; u < U; ++u) {
+            ok[u] = n < planes;
+            e[u] = e_next;
+            v += step_v; n += step_n; e_next += step_e;
+            if (v >= vpp) { v -= vpp; ++n; e_next += plane_stride - hw; }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+#pragma unroll
+            for (int r = 0; r < (RAW > 0 ? RAW : 1); ++r) raw[u][r] = make_uint4(0u, 0u, 0u, 0u);
+            w[u] = make_uint2(0u, 0u); keep[u] = 0xFFu; sc[u] = 0.0f; m[u] = 0.0f;
+            if (!ok[u]) continue;
+            const uint8_t* px = x + e[u] * ElemT<DT>::bytes;
+            if (RAW == 0) {
+                uint2 t;
+                asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(t.x), "=r"(t.y) : "l"(px));
+                raw[u][0] = make_uint4(t.x, t.y, 0u, 0u);
+            } else {
+#pragma unroll
+                for (int r = 0; r < RAW; ++r) raw[u][r] = ldg_stream_v4(px + 16 * r);
             }
-        } else {
-            constexpr uint32_t MASK = (1u << BITS) - 1u;
-            uint2 w;
-            if (VEC == 8) w = load_codes8v<BITS>(packed, e);
-            else w = make_uint2(load_codes4<BITS>(packed, e), 0u);
-            const int64_t g = e >> log2_gs;
-            const float sc = __ldg(scale + g), m = __ldg(mn + g);
-            if (mask) {
-                const uint32_t keep = (VEC == 8) ? (uint32_t)__ldg(mask + (e >> 3)) : load_codes4<1>(mask, e);
-#pragma unroll
-                for (int i = 0; i < VEC; ++i) f[i] = ((keep >> i) & 1u) ? f[i] : 0.0f;
+            if (MODE == 1) {
+                if (VEC == 8) w[u] = load_codes8v<BITS>(packed, e[u]);
+                else w[u] = make_uint2(load_codes4<BITS>(packed, e[u]), 0u);
+                const int64_t g = e[u] >> log2_gs;
+                sc[u] = __ldg(scale + g); m[u] = __ldg(mn + g);
+                if (mask) keep[u] = (VEC == 8) ? (uint32_t)__ldg(mask + (e[u] >> 3)) : load_codes4<1>(mask, e[u]);
             }
+        }
 #pragma unroll
-            for (int i = 0; i < VEC; ++i) {
-                const uint32_t word = (BITS == 8 && i >= 4) ? w.y : w.x;
-                const int sh = (BITS == 8) ? (i & 3) * 8 : i * BITS;
-                const float code = __uint_as_float(kMagicBits | ((word >> sh) & MASK)) - kMagic;
-                a = __fmaf_rn(f[i], __fmaf_rn(code, sc, m), a);
-                b = __fadd_rn(b, f[i]);
+        for (int u = 0; u < U; ++u) {
+            float f[VEC];
+            if (ElemT<DT>::bytes == 4) {
+#pragma unroll
+                for (int r = 0; r < VEC / 4; ++r) {
+                    f[4 * r] = __uint_as_float(raw[u][r].x); f[4 * r + 1] = __uint_as_float(raw[u][r].y);
+                    f[4 * r + 2] = __uint_as_float(raw[u][r].z); f[4 * r + 3] = __uint_as_float(raw[u][r].w);
+                }
+            } else {
+                constexpr int D16 = (DT == ACT_DTYPE_F32) ? ACT_DTYPE_BF16 : DT;
+                const uint32_t h[4] = {raw[u][0].x, raw[u][0].y, raw[u][0].z, raw[u][0].w};
+#pragma unroll
+                for (int r = 0; r < VEC / 2; ++r) { f[2 * r] = widen_lo<D16>(h[r]); f[2 * r + 1] = widen_hi<D16>(h[r]); }
+            }
+            if (MODE == 0) {
+                if (ok[u]) {
+#pragma unroll
+                    for (int i = 0; i < VEC; ++i) {
+                        const float d = __fsub_rn(f[i], pivot);
+                        a = __fadd_rn(a, d);
+                        b = __fmaf_rn(d, d, b);
+                    }
+                }
+            } else {
+                // an item past the end holds zeros and adds nothing
+                constexpr uint32_t MASK = (1u << BITS) - 1u;
+                if (mask) {
+#pragma unroll
+                    for (int i = 0; i < VEC; ++i) f[i] = ((keep[u] >> i) & 1u) ? f[i] : 0.0f;
+                }
+                // the item lies inside one group: sum(dy * x_hat) = scale * sum(dy * code) + min * sum(dy),
+                // the two inner sums on f32x2 pairs
+                const f32x2 magic2 = pack2(kMagic, kMagic);
+                f32x2 dc2 = pack2(0.0f, 0.0f), d2 = pack2(0.0f, 0.0f);
+#pragma unroll
+                for (int p = 0; p < VEC / 2; ++p) {
+                    const uint32_t word = (BITS == 8 && p >= 2) ? w[u].y : w[u].x;
+                    const int sh0 = (BITS == 8) ? ((2 * p) & 3) * 8 : 2 * p * BITS;
+                    const f32x2 code2 = sub2_rn(pack2u(kMagicBits | ((word >> sh0) & MASK),
+                                                       kMagicBits | ((word >> (sh0 + BITS)) & MASK)), magic2);
+                    const f32x2 dy2 = pack2(f[2 * p], f[2 * p + 1]);
+                    dc2 = fma2_rn(dy2, code2, dc2);
+                    d2 = add2_rn(d2, dy2);
+                }
+                uint32_t u0, u1, v0, v1;
+                unpack2u(dc2, u0, u1);
+                unpack2u(d2, v0, v1);
+                const float dc = __fadd_rn(__uint_as_float(u0), __uint_as_float(u1));
+                const float dsum = __fadd_rn(__uint_as_float(v0), __uint_as_float(v1));
+                a = __fmaf_rn(sc[u], dc, __fmaf_rn(m[u], dsum, a));
+                b = __fadd_rn(b, dsum);
             }
         }
     }
