@@ -210,6 +210,27 @@ def run_extras(dev):
         "unpack_GBps": ub / tu / 1e6, "unpack_frac": ub / tu / 1e6 / peak,
         "pack_plus_unpack_frac": (pb + ub) / (tp + tu) / 1e6 / peak}
     del xs, outs, ys
+    # bit-width and shape sweep of the bf16 configuration: conv [256,256,28,28] = ReLU(N(0,1)) and
+    # ViT [256,197,768] = GELU(N(0,1)), group 128, bits 1/2/4/8
+    sweep = {}
+    for name, shp, fn in (("conv_256x256x28x28", SHAPE, torch.relu),
+                          ("vit_256x197x768", (256, 197, 768), torch.nn.functional.gelu)):
+        n = 1
+        for d in shp:
+            n *= d
+        xs = [fn(torch.randn(shp, device=dev)).to(torch.bfloat16) for _ in range(rot)]
+        ys = [torch.empty((n // GROUP, GROUP), dtype=torch.bfloat16, device=dev) for _ in range(rot)]
+        for b in (1, 2, 4, 8):
+            outs = [(torch.empty((n // GROUP, GROUP * b // 32), dtype=torch.int32, device=dev),
+                     torch.empty(n // GROUP, device=dev), torch.empty(n // GROUP, device=dev)) for _ in range(rot)]
+            pb, ub = algorithmic_bytes(n, GROUP, b, 2)
+            tp = _time_launches(lambda i=0: codec.quant_pack(xs[i % rot], b, GROUP, seed=3, offset=i, out=outs[i % rot]), 40)
+            tu = _time_launches(lambda i=0: codec.dequant_unpack(*outs[i % rot], b, GROUP, out_dtype=torch.bfloat16, out=ys[i % rot]), 40)
+            sweep[f"{name}_b{b}"] = {"pack_frac": pb / tp / 1e6 / peak, "unpack_frac": ub / tu / 1e6 / peak,
+                                     "pack_us": tp * 1e3, "unpack_us": tu * 1e3}
+            del outs
+        del xs, ys
+    out["codec_bf16_g128_sweep"] = sweep
     # the other rounding modes on the bench workload (bf16 [256,256,28,28], group 128, 2 bits):
     # caller-supplied fp32 noise (exact-division float formula; its algorithmic bytes include
     # the 4 bytes of noise read per element) and round-to-nearest
