@@ -28,6 +28,8 @@ _f64, _sz = ctypes.c_double, ctypes.c_size_t
 SIGNATURES = {
     "act_quant_pack": ([_vp, _i32, _i64, _i32, _i32, _vp, _u64, _u64, _i32, _f32, _vp, _vp, _vp, _vp], _i32),
     "act_dequant_unpack": ([_vp, _vp, _vp, _i64, _i32, _i32, _i32, _vp, _vp], _i32),
+    "act_quant_pack_tiles": ([_vp, _i32, _i64, _i32, _i32, _i32, _i32, _u64, _u64, _i32, _vp, _vp, _vp, _vp], _i32),
+    "act_dequant_unpack_tiles": ([_vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _i32, _vp, _vp], _i32),
     "act_pack_bits": ([_vp, _i64, _i32, _i32, _vp, _vp], _i32),
     "act_unpack_bits": ([_vp, _i64, _i32, _i32, _vp, _vp], _i32),
     "act_activation_fwd_quant_pack": ([_vp, _i32, _i32, _i64, _i32, _i32, _u64, _u64, _i32, _vp, _vp, _vp, _vp, _vp], _i32),

@@ -116,6 +116,52 @@ def dequant_unpack(packed: torch.Tensor, scale: torch.Tensor, mn: torch.Tensor, 
     return y
 
 
+def tiles_supported(x: torch.Tensor, group_size: int) -> bool:
+    """4-D contiguous CUDA activations whose group is a square tile of 8, 16 or 32 that divides
+    H and W: the shapes quant_pack_tiles / dequant_unpack_tiles take."""
+    if x.dim() != 4 or not x.is_cuda or x.dtype not in _DTYPES or not x.is_contiguous():
+        return False
+    t = {64: 8, 256: 16, 1024: 32}.get(group_size)
+    return t is not None and x.shape[2] % t == 0 and x.shape[3] % t == 0 and x.numel() > 0
+
+
+def quant_pack_tiles(x: torch.Tensor, bits: int, tile: int, seed: Optional[int] = None,
+                     offset: Optional[int] = None, flags: int = 0):
+    """quant_pack of x [N, C, H, W] grouped into tile x tile spatial blocks, read in place:
+    (packed [groups, tile*tile*bits/32], scale [groups], min [groups])."""
+    global _next_offset
+    gs = tile * tile
+    _, nwords, _ = _bits_consts(bits, gs)
+    N, C, H, W = x.shape
+    groups = N * C * (H // tile) * (W // tile)
+    packed = torch.empty((groups, nwords), dtype=torch.int32, device=x.device)
+    scale = torch.empty((groups,), dtype=torch.float32, device=x.device)
+    mn = torch.empty((groups,), dtype=torch.float32, device=x.device)
+    if seed is None:
+        seed = _default_seed
+    if offset is None:
+        offset = _next_offset
+        _next_offset += 1
+    with torch.cuda.device(x.device):
+        rc = _lib.load().act_quant_pack_tiles(x.data_ptr(), _DTYPES[x.dtype], N * C, H, W, tile, bits,
+                                              seed & 0xFFFFFFFFFFFFFFFF, offset & 0xFFFFFFFFFFFFFFFF, flags,
+                                              packed.data_ptr(), scale.data_ptr(), mn.data_ptr(), _stream_ptr(x))
+    _lib.check(rc, "act_quant_pack_tiles")
+    return packed, scale, mn
+
+
+def dequant_unpack_tiles(packed: torch.Tensor, scale: torch.Tensor, mn: torch.Tensor, bits: int, tile: int,
+                         shape, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """Inverse of quant_pack_tiles: the [N, C, H, W] tensor written in place (no permute back)."""
+    N, C, H, W = shape
+    y = torch.empty((N, C, H, W), dtype=out_dtype, device=packed.device)
+    with torch.cuda.device(packed.device):
+        rc = _lib.load().act_dequant_unpack_tiles(packed.data_ptr(), scale.data_ptr(), mn.data_ptr(), N * C, H, W,
+                                                  tile, bits, _DTYPES[out_dtype], y.data_ptr(), _stream_ptr(packed))
+    _lib.check(rc, "act_dequant_unpack_tiles")
+    return y
+
+
 def pack_bits(x: torch.Tensor, bits: int, group_size: int) -> torch.Tensor:
     """int8 [NG*group_size] -> int32 words (mask / ready-made code packing)."""
     _, nwords, _ = _bits_consts(bits, group_size)

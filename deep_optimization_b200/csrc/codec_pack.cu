@@ -13,6 +13,9 @@ extern template cudaError_t launch_bn<ACT_DTYPE_BF16>(int bits, bool nearest, co
 extern template cudaError_t launch_pack_bits<ACT_DTYPE_F16>(int bits, int mode, const void* x, const float* noise, void* packed, float* scale, float* mn, int64_t n_elems, int log2_L, uint64_t seed, uint64_t offset, int flags, float clamp_alpha, cudaStream_t st);
 extern template cudaError_t launch_fused<ACT_DTYPE_F16>(int bits, int kind, bool nearest, const void* x, void* y, void* packed, float* scale, float* mn, int64_t n, int l2, uint64_t seed, uint64_t offset, cudaStream_t st);
 extern template cudaError_t launch_bn<ACT_DTYPE_F16>(int bits, bool nearest, const void* x, void* y, void* packed, float* scale, float* mn, int64_t n, int l2, uint64_t seed, uint64_t offset, BNArgs bn, cudaStream_t st);
+extern template cudaError_t launch_pack_tiled<ACT_DTYPE_F32>(int bits, bool nearest, const void* x, void* packed, float* scale, float* mn, int64_t n_elems, int log2_L, uint64_t seed, uint64_t offset, TileArgs ta, cudaStream_t st);
+extern template cudaError_t launch_pack_tiled<ACT_DTYPE_BF16>(int bits, bool nearest, const void* x, void* packed, float* scale, float* mn, int64_t n_elems, int log2_L, uint64_t seed, uint64_t offset, TileArgs ta, cudaStream_t st);
+extern template cudaError_t launch_pack_tiled<ACT_DTYPE_F16>(int bits, bool nearest, const void* x, void* packed, float* scale, float* mn, int64_t n_elems, int log2_L, uint64_t seed, uint64_t offset, TileArgs ta, cudaStream_t st);
 }  // namespace act
 
 extern "C" int act_quant_pack(const void* x, int dtype, int64_t n_groups, int group_size, int bits,
@@ -125,4 +128,34 @@ extern "C" int act_bn_relu_fwd_norm_quant_pack(const void* x, int dtype, int64_t
     if (!mask_bits) return n_batch * channels * hw == 0 ? ACT_OK : ACT_ERR_NULL;
     return bn_fwd_common(x, dtype, n_batch, channels, hw, params, group_size, bits, seed, offset, flags, y,
                          packed, scale, mn, mask_bits, stream);
+}
+
+extern "C" int act_quant_pack_tiles(const void* x, int dtype, int64_t n_planes, int height, int width, int tile,
+                                    int bits, uint64_t seed, uint64_t offset, int flags, void* packed,
+                                    float* scale, float* mn, void* stream)
+{
+    using namespace act;
+    if (dtype != ACT_DTYPE_F32 && dtype != ACT_DTYPE_BF16 && dtype != ACT_DTYPE_F16) return ACT_ERR_DTYPE;
+    if (flags & ~ACT_FLAG_ROUND_NEAREST) return ACT_ERR_UNSUPPORTED;
+    if (bits != 1 && bits != 2 && bits != 4 && bits != 8) return ACT_ERR_BITS;
+    if (tile != 8 && tile != 16 && tile != 32) return ACT_ERR_GROUP;
+    if (n_planes < 0 || height <= 0 || width <= 0 || height % tile || width % tile) return ACT_ERR_SIZE;
+    const int64_t groups = n_planes * (height / tile) * (width / tile);
+    if (n_planes > (1ll << 31) || groups >= (1ll << 32)) return ACT_ERR_SIZE;
+    if (groups == 0) return ACT_OK;
+    if (!x || !packed || !scale || !mn) return ACT_ERR_NULL;
+    if (((uintptr_t)x | (uintptr_t)packed) & 15) return ACT_ERR_ALIGN;
+    if (((uintptr_t)scale | (uintptr_t)mn) & 3) return ACT_ERR_ALIGN;
+    int log2_t = 3;
+    while ((1 << log2_t) < tile) ++log2_t;
+    const int log2_L = 2 * log2_t - 5;                       // lanes per group = tile * tile / 32
+    const int64_t n_elems = groups << (2 * log2_t);
+    const TileArgs ta{(uint32_t)height, (uint32_t)width, (uint32_t)(width / tile), (uint32_t)(height / tile), log2_t};
+    const bool nearest = (flags & ACT_FLAG_ROUND_NEAREST) != 0;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaError_t e;
+    if (dtype == ACT_DTYPE_F32) e = launch_pack_tiled<ACT_DTYPE_F32>(bits, nearest, x, packed, scale, mn, n_elems, log2_L, seed, offset, ta, st);
+    else if (dtype == ACT_DTYPE_BF16) e = launch_pack_tiled<ACT_DTYPE_BF16>(bits, nearest, x, packed, scale, mn, n_elems, log2_L, seed, offset, ta, st);
+    else e = launch_pack_tiled<ACT_DTYPE_F16>(bits, nearest, x, packed, scale, mn, n_elems, log2_L, seed, offset, ta, st);
+    return e == cudaSuccess ? ACT_OK : ACT_ERR_LAUNCH;
 }

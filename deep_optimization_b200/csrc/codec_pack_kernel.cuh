@@ -337,6 +337,16 @@ struct BNArgs {
     uint8_t* mask;
 };
 
+// Tiled source addressing (TILED kernels): x is [planes, H, W] and group g is the T x T tile
+// (plane, ty, tx) with g = (plane * tiles_y + ty) * tiles_x + tx, its elements row-major inside
+// the tile, T = 8, 16 or 32 -- the grouping the reference makes with a permute and a copy
+// (Activation_Compression/modules/tensor_act_reshape_utils.py:82-110).  Codes, scale, min and
+// the hash counters are those of the permuted [groups, T*T] tensor.
+struct TileArgs {
+    uint32_t H, W, tiles_x, tiles_y;
+    int log2_t;
+};
+
 __device__ __forceinline__ float tanh_fast(float v) {
     float r; asm("tanh.approx.f32 %0, %1;" : "=f"(r) : "f"(v)); return r;
 }
@@ -362,14 +372,16 @@ __device__ __forceinline__ void act_and_derivative(float x, float& y, float& d) 
 // L2 >= 0 fixes log2(lanes per group) at compile time (the common group sizes get their own
 // instantiation: addresses, strides and the shuffle loop then fold to constants); L2 = -1
 // takes it from the argument.
-template <int DT, int BITS, int NM, int PRO = kProNone, int L2 = -1>
+template <int DT, int BITS, int NM, int PRO = kProNone, int L2 = -1, bool TILED = false>
 __global__ void __launch_bounds__(PackCfg<DT>::threads, PackCfg<DT>::min_blocks)
 quant_pack_kernel(const void* __restrict__ x_, const float* __restrict__ noise,
                   uint8_t* __restrict__ packed, float* __restrict__ scale_out,
                   float* __restrict__ min_out, int64_t n_elems, int log2_L_arg,
                   uint32_t key_lo, uint32_t key_hi, int flags, float clamp_alpha,
-                  uint8_t* __restrict__ y_out = nullptr, BNArgs bn = BNArgs{nullptr, 1u, 1u, 0u, 0u, nullptr})
+                  uint8_t* __restrict__ y_out = nullptr, BNArgs bn = BNArgs{nullptr, 1u, 1u, 0u, 0u, nullptr},
+                  TileArgs ta = TileArgs{0u, 0u, 1u, 1u, 3})
 {
+    static_assert(!TILED || PRO == kProNone, "tiled addressing is built for the plain codec only");
     constexpr int QMAX = (1 << BITS) - 1;
     constexpr int TILE_OUT = kTileElems * BITS / 8;          // packed bytes per tile
     constexpr int kPackWarps = PackCfg<DT>::warps;
@@ -397,6 +409,27 @@ quant_pack_kernel(const void* __restrict__ x_, const float* __restrict__ noise,
     uint8_t* sts_lane = my_stage + ((g_local << (log2_L + 2)) + j) * BITS;   // its staging slot
 
     auto load_tile = [&](RawTile<DT>& r, int64_t t) {
+        if (TILED) {
+            // the lane's group -> (plane, ty, tx); its piece pg -> row pg / (T/8), eight-element
+            // column block pg % (T/8) of the tile
+            const uint32_t g = (uint32_t)t * (32u >> log2_L) + (uint32_t)g_local;
+            const uint32_t q = g / ta.tiles_x, tx = g - q * ta.tiles_x;
+            const uint32_t plane = q / ta.tiles_y, ty = q - plane * ta.tiles_y;
+            const int64_t base = ((int64_t)plane * ta.H + ((int64_t)ty << ta.log2_t)) * ta.W + ((int64_t)tx << ta.log2_t);
+            const int log2_tp = ta.log2_t - 3;                        // pieces per tile row
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int pg = (k << log2_L) + j;
+                const int64_t e = base + (int64_t)(pg >> log2_tp) * ta.W + ((pg & ((1 << log2_tp) - 1)) << 3);
+                if (ElemT<DT>::bytes == 4) {
+                    r.v[2 * k] = ldg_nc_v4(xb + e * 4);
+                    r.v[2 * k + 1] = ldg_nc_v4(xb + e * 4 + 16);
+                } else {
+                    r.v[k] = ldg_nc_v4(xb + e * 2);
+                }
+            }
+            return;
+        }
         const uint8_t* p = xlane + t * (int64_t)(kTileElems * ElemT<DT>::bytes);
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
@@ -658,7 +691,45 @@ cudaError_t launch_pack_fixed(const void* x, const float* noise, void* packed, f
     return launch_overlapped(quant_pack_kernel<DT, BITS, NM, kProNone, L2>, grid, PackCfg<DT>::threads, st,
                              x, noise, static_cast<uint8_t*>(packed), scale, mn, n_elems, log2_L,
                              (uint32_t)key, (uint32_t)(key >> 32), flags, clamp_alpha,
-                             static_cast<uint8_t*>(nullptr), BNArgs{nullptr, 1u, 1u, 0u, 0u, nullptr});
+                             static_cast<uint8_t*>(nullptr), BNArgs{nullptr, 1u, 1u, 0u, 0u, nullptr}, TileArgs{0u, 0u, 1u, 1u, 3});
+}
+
+// tiled source addressing, the two fixed-point modes only
+template <int DT, int BITS, int NM>
+cudaError_t launch_pack_tiled_one(const void* x, void* packed, float* scale, float* mn, int64_t n_elems,
+                                  int log2_L, uint64_t seed, uint64_t offset, TileArgs ta, cudaStream_t st)
+{
+    static int per_sm = 0;
+    if (per_sm == 0) {
+        int n = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, quant_pack_kernel<DT, BITS, NM, kProNone, -1, true>,
+                                                          PackCfg<DT>::threads, 0) != cudaSuccess || n < 1) n = 1;
+        per_sm = n;
+    }
+    const uint64_t key = hash_key(hash_key(seed) + offset);
+    const int64_t n_tiles = (n_elems + kTileElems - 1) / kTileElems;
+    const int grid = stream_grid_for((n_tiles + PackCfg<DT>::warps - 1) / PackCfg<DT>::warps, per_sm);
+    return launch_overlapped(quant_pack_kernel<DT, BITS, NM, kProNone, -1, true>, grid, PackCfg<DT>::threads, st,
+                             x, static_cast<const float*>(nullptr), static_cast<uint8_t*>(packed), scale, mn,
+                             n_elems, log2_L, (uint32_t)key, (uint32_t)(key >> 32), 0, 0.0f,
+                             static_cast<uint8_t*>(nullptr), BNArgs{nullptr, 1u, 1u, 0u, 0u, nullptr}, ta);
+}
+
+template <int DT>
+cudaError_t launch_pack_tiled(int bits, bool nearest, const void* x, void* packed, float* scale, float* mn,
+                              int64_t n_elems, int log2_L, uint64_t seed, uint64_t offset, TileArgs ta,
+                              cudaStream_t st)
+{
+#define ACT_TILED_CASE(B) \
+    return nearest ? launch_pack_tiled_one<DT, B, kNoiseConst>(x, packed, scale, mn, n_elems, log2_L, seed, offset, ta, st) \
+                   : launch_pack_tiled_one<DT, B, kNoiseHash>(x, packed, scale, mn, n_elems, log2_L, seed, offset, ta, st)
+    switch (bits) {
+        case 1: ACT_TILED_CASE(1);
+        case 2: ACT_TILED_CASE(2);
+        case 4: ACT_TILED_CASE(4);
+        default: ACT_TILED_CASE(8);
+    }
+#undef ACT_TILED_CASE
 }
 
 template <int DT, int BITS, int NM>
@@ -724,7 +795,7 @@ cudaError_t launch_fused_one(const void* x, void* y, void* packed, float* scale,
     return launch_overlapped(quant_pack_kernel<DT, BITS, NM, PRO>, grid, PackCfg<DT>::threads, st,
                              x, static_cast<const float*>(nullptr), static_cast<uint8_t*>(packed), scale, mn,
                              n_elems, log2_L, (uint32_t)key, (uint32_t)(key >> 32), 0, 0.0f,
-                             static_cast<uint8_t*>(y), BNArgs{nullptr, 1u, 1u, 0u, 0u, nullptr});
+                             static_cast<uint8_t*>(y), BNArgs{nullptr, 1u, 1u, 0u, 0u, nullptr}, TileArgs{0u, 0u, 1u, 1u, 3});
 }
 
 template <int DT, int BITS>
@@ -779,7 +850,7 @@ cudaError_t launch_bn_one(const void* x, void* y, void* packed, float* scale, fl
     return launch_overlapped(quant_pack_kernel<DT, BITS, NM, PRO>, grid, PackCfg<DT>::threads, st,
                              x, static_cast<const float*>(nullptr), static_cast<uint8_t*>(packed), scale, mn,
                              n_elems, log2_L, (uint32_t)key, (uint32_t)(key >> 32), 0, 0.0f,
-                             static_cast<uint8_t*>(y), bn);
+                             static_cast<uint8_t*>(y), bn, TileArgs{0u, 0u, 1u, 1u, 3});
 }
 
 template <int DT>

@@ -34,11 +34,30 @@ template <int BITS> __device__ __forceinline__ uint32_t code_bits_at(uint2 w, in
     return ((w.x >> (i * BITS)) & MASK) | kMagicBits;
 }
 
-template <int DT, int BITS>
+// Tiled destination addressing (TILED kernels): y is [planes, H, W] and group g is the T x T
+// tile (plane, ty, tx), g = (plane * tiles_y + ty) * tiles_x + tx, elements row-major inside the
+// tile: the inverse of the grouping the reference makes with a permute and a copy
+// (Activation_Compression/modules/tensor_act_reshape_utils.py:113-154).
+struct UnpackTiles {
+    uint32_t H, W, tiles_x, tiles_y;
+    int log2_t;
+};
+// element offset in y of group-ordered element `ge` (a multiple of 4 or 8, so a run of 4 or 8
+// stays inside one tile row)
+__device__ __forceinline__ int64_t tiled_offset(int64_t ge, int log2_gs, const UnpackTiles& ta) {
+    const uint32_t g = (uint32_t)(ge >> log2_gs);
+    const uint32_t pe = (uint32_t)ge & ((1u << log2_gs) - 1u);
+    const uint32_t q = g / ta.tiles_x, tx = g - q * ta.tiles_x;
+    const uint32_t plane = q / ta.tiles_y, ty = q - plane * ta.tiles_y;
+    const uint32_t r = pe >> ta.log2_t, col = pe & ((1u << ta.log2_t) - 1u);
+    return ((int64_t)plane * ta.H + ((int64_t)ty << ta.log2_t) + r) * ta.W + ((int64_t)tx << ta.log2_t) + col;
+}
+
+template <int DT, int BITS, bool TILED = false>
 __global__ void __launch_bounds__(kUnpackThreads)
 dequant_unpack_kernel(const uint8_t* __restrict__ packed, const float* __restrict__ scale,
                       const float* __restrict__ mn, uint8_t* __restrict__ y, int64_t n_elems,
-                      int log2_gs)
+                      int log2_gs, UnpackTiles ta = UnpackTiles{0u, 0u, 1u, 1u, 3})
 {
     constexpr int EB = ElemT<DT>::bytes;
     const int lane = threadIdx.x & 31;
@@ -108,7 +127,7 @@ dequant_unpack_kernel(const uint8_t* __restrict__ packed, const float* __restric
                     ap[2 * h] = __byte_perm(t_lo, t_hi, sel);
                     ap[2 * h + 1] = __byte_perm(t_lo, t_hi, sel >> 16);
                 }
-                stg_stream_v4(y_tile + e * 2, a);
+                stg_stream_v4(TILED ? y + tiled_offset(tile_e0 + e, log2_gs, ta) * 2 : y_tile + e * 2, a);
                 continue;
             }
             uint32_t o[8];
@@ -119,9 +138,10 @@ dequant_unpack_kernel(const uint8_t* __restrict__ packed, const float* __restric
                                                 code_bits_at<BITS>(w[k], 2 * p + 1)), magic2);
                 unpack2u(fma2_rn(c2, s2, m2), o[2 * p], o[2 * p + 1]);
             }
+            uint8_t* dst = TILED ? y + tiled_offset(tile_e0 + e, log2_gs, ta) * EB : y_tile + e * EB;
             if (DT == ACT_DTYPE_F32) {
-                stg_stream_v4(y_tile + e * 4, make_uint4(o[0], o[1], o[2], o[3]));
-                stg_stream_v4(y_tile + e * 4 + 16, make_uint4(o[4], o[5], o[6], o[7]));
+                stg_stream_v4(dst, make_uint4(o[0], o[1], o[2], o[3]));
+                stg_stream_v4(dst + 16, make_uint4(o[4], o[5], o[6], o[7]));
             } else {
                 uint4 a;
                 uint32_t* ap = &a.x;
@@ -136,7 +156,7 @@ dequant_unpack_kernel(const uint8_t* __restrict__ packed, const float* __restric
                         ap[p] = *reinterpret_cast<const uint32_t*>(&t);
                     }
                 }
-                stg_stream_v4(y_tile + e * 2, a);
+                stg_stream_v4(dst, a);
             }
         }
     }
@@ -311,7 +331,8 @@ static void launch_unpack_one(const uint8_t* p, const float* s, const float* m, 
         return;
     }
     const int grid = stream_grid_for((tiles + kUnpackWarps - 1) / kUnpackWarps, per_sm);
-    launch_overlapped(dequant_unpack_kernel<DT, BITS>, grid, kUnpackThreads, st, p, s, m, y, n_elems, log2_gs);
+    launch_overlapped(dequant_unpack_kernel<DT, BITS, false>, grid, kUnpackThreads, st, p, s, m, y, n_elems, log2_gs,
+                      UnpackTiles{0u, 0u, 1u, 1u, 3});
 }
 
 template <int DT>
@@ -326,7 +347,63 @@ static void launch_unpack(int bits, const uint8_t* p, const float* s, const floa
     }
 }
 
+template <int DT, int BITS>
+static void launch_unpack_tiled_one(const uint8_t* p, const float* s, const float* m, uint8_t* y,
+                                    int64_t n_elems, int log2_gs, UnpackTiles ta, cudaStream_t st)
+{
+    static int per_sm = 0;
+    if (per_sm == 0) {
+        int n = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, dequant_unpack_kernel<DT, BITS, true>,
+                                                          kUnpackThreads, 0) != cudaSuccess || n < 1) n = 1;
+        per_sm = n;
+    }
+    const int64_t tiles = (n_elems + kTileElems - 1) / kTileElems;
+    const int grid = stream_grid_for((tiles + kUnpackWarps - 1) / kUnpackWarps, per_sm);
+    launch_overlapped(dequant_unpack_kernel<DT, BITS, true>, grid, kUnpackThreads, st, p, s, m, y, n_elems, log2_gs, ta);
+}
+
+template <int DT>
+static void launch_unpack_tiled(int bits, const uint8_t* p, const float* s, const float* m, uint8_t* y,
+                                int64_t n_elems, int log2_gs, UnpackTiles ta, cudaStream_t st)
+{
+    switch (bits) {
+        case 1: launch_unpack_tiled_one<DT, 1>(p, s, m, y, n_elems, log2_gs, ta, st); break;
+        case 2: launch_unpack_tiled_one<DT, 2>(p, s, m, y, n_elems, log2_gs, ta, st); break;
+        case 4: launch_unpack_tiled_one<DT, 4>(p, s, m, y, n_elems, log2_gs, ta, st); break;
+        default: launch_unpack_tiled_one<DT, 8>(p, s, m, y, n_elems, log2_gs, ta, st); break;
+    }
+}
+
 }  // namespace act
+
+extern "C" int act_dequant_unpack_tiles(const void* packed, const float* scale, const float* mn,
+                                        int64_t n_planes, int height, int width, int tile, int bits,
+                                        int out_dtype, void* y, void* stream)
+{
+    using namespace act;
+    if (out_dtype != ACT_DTYPE_F32 && out_dtype != ACT_DTYPE_BF16 && out_dtype != ACT_DTYPE_F16) return ACT_ERR_DTYPE;
+    if (!bits_ok(bits)) return ACT_ERR_BITS;
+    if (tile != 8 && tile != 16 && tile != 32) return ACT_ERR_GROUP;
+    if (n_planes < 0 || height <= 0 || width <= 0 || height % tile || width % tile) return ACT_ERR_SIZE;
+    const int64_t groups = n_planes * (height / tile) * (width / tile);
+    if (n_planes > (1ll << 31) || groups >= (1ll << 32)) return ACT_ERR_SIZE;
+    if (groups == 0) return ACT_OK;
+    if (!packed || !scale || !mn || !y) return ACT_ERR_NULL;
+    if (((uintptr_t)y & 15) || ((uintptr_t)packed & 7) || (((uintptr_t)scale | (uintptr_t)mn) & 3)) return ACT_ERR_ALIGN;
+    int log2_t = 3;
+    while ((1 << log2_t) < tile) ++log2_t;
+    const int log2_gs = 2 * log2_t;
+    const int64_t n_elems = groups << log2_gs;
+    const UnpackTiles ta{(uint32_t)height, (uint32_t)width, (uint32_t)(width / tile), (uint32_t)(height / tile), log2_t};
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const uint8_t* p = static_cast<const uint8_t*>(packed);
+    uint8_t* out = static_cast<uint8_t*>(y);
+    if (out_dtype == ACT_DTYPE_F32) launch_unpack_tiled<ACT_DTYPE_F32>(bits, p, scale, mn, out, n_elems, log2_gs, ta, st);
+    else if (out_dtype == ACT_DTYPE_BF16) launch_unpack_tiled<ACT_DTYPE_BF16>(bits, p, scale, mn, out, n_elems, log2_gs, ta, st);
+    else launch_unpack_tiled<ACT_DTYPE_F16>(bits, p, scale, mn, out, n_elems, log2_gs, ta, st);
+    return cudaGetLastError() == cudaSuccess ? ACT_OK : ACT_ERR_LAUNCH;
+}
 
 extern "C" int act_dequant_unpack(const void* packed, const float* scale, const float* mn,
                                   int64_t n_groups, int group_size, int bits, int out_dtype,

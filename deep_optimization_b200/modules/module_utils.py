@@ -14,14 +14,35 @@ from __future__ import annotations
 import torch
 import torch.nn.functional as F
 
-from .. import act_kernels  # noqa: F401  (registers torch.ops.act_lib.*)
+from .. import _lib, act_kernels, codec
 from .tensor_act_reshape_utils import (
     spatical_aware_act_tensor_reshape,
     spatical_aware_act_tensor_reshape_back,
+    spatical_aware_act_tensor_reshape_eligibility,
 )
+
+_TILE = {64: 8, 256: 16, 1024: 32}
+
+
+def _tiled_in_place(input, group_size, act_padding, pack_only, avg_alam):
+    """Spatial grouping that the tiled kernels read and write in place (no permute copy): the
+    spatial branch of the reshape helpers, in the two fixed-point modes."""
+    if pack_only or avg_alam or act_kernels.get_mode() == "ref_compat" or not codec.tiles_supported(input, group_size):
+        return False
+    pad_elig, reshape_elig = spatical_aware_act_tensor_reshape_eligibility(input, group_size, act_padding)
+    return reshape_elig and not pad_elig
 
 
 def quantize(input, bits, pack_only, group_size, act_padding, N, avg_alam, alam_bits, clamp, clamp_alpha):
+    if _tiled_in_place(input, group_size, act_padding, pack_only, avg_alam):
+        t = _TILE[group_size]
+        n, C, H, W = input.shape
+        G = C * (H // t) * (W // t)
+        flags = _lib.ACT_FLAG_ROUND_NEAREST if act_kernels.get_mode() == "nearest" else 0
+        out, scaler, ema_min = codec.quant_pack_tiles(input, bits, t, flags=flags)
+        return (out, scaler.view(n, G), ema_min.view(n, G)), (bits, pack_only, group_size, act_padding, n, G, H // t,
+                                                              W // t, False, True, False, avg_alam, alam_bits,
+                                                              input.shape)
     groups, N, G, new_H, new_W, ori_shape, pad_elig, reshape_elig, channel_mean = \
         spatical_aware_act_tensor_reshape(input, Group_Size=group_size, act_padding=act_padding,
                                           pack_only=pack_only)
@@ -48,6 +69,10 @@ def dequantize(quantized_tensor, quantized_meta):
     q_input, q_scale, ema_mn = quantized_tensor
     (q_bits, pack_only, group_size, act_padding, N, G, new_H, new_W, pad_elig, reshape_elig,
      channel_mean, avg_alam, alam_bits, input_shape) = quantized_meta
+    if (not pack_only and reshape_elig and not pad_elig and not avg_alam and group_size in _TILE
+            and q_input.is_cuda and len(input_shape) == 4):
+        return codec.dequant_unpack_tiles(q_input, q_scale.reshape(-1), ema_mn.reshape(-1), q_bits,
+                                          _TILE[group_size], tuple(input_shape))
     if pack_only:
         unpack = torch.ops.act_lib.unpack_triton(q_input, q_bits, N, G, group_size)
     else:

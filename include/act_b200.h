@@ -103,6 +103,23 @@ ACT_API int act_dequant_unpack(const void* packed, const float* scale, const flo
                        void* stream);
 
 /*
+ * The same two kernels on spatial tiles, without the permute-and-copy the reference makes first
+ * (AC/modules/tensor_act_reshape_utils.py:82-154): x and y are [n_planes, height, width]
+ * (n_planes = N*C), a group is one tile x tile block of one plane (tile = 8, 16 or 32, i.e.
+ * group sizes 64, 256, 1024; height and width multiples of tile), group index
+ * (plane * height/tile + ty) * width/tile + tx, elements row-major inside the tile.  packed,
+ * scale and min are exactly those of act_quant_pack applied to the permuted
+ * [groups, tile*tile] tensor (same codes, same hash counters); noise-tensor and
+ * reference-compatible modes are not built here (flags: 0 or ACT_FLAG_ROUND_NEAREST).
+ */
+ACT_API int act_quant_pack_tiles(const void* x, int dtype, int64_t n_planes, int height, int width, int tile,
+                         int bits, uint64_t seed, uint64_t offset, int flags, void* packed,
+                         float* scale, float* min, void* stream);
+ACT_API int act_dequant_unpack_tiles(const void* packed, const float* scale, const float* min,
+                             int64_t n_planes, int height, int width, int tile, int bits,
+                             int out_dtype, void* y, void* stream);
+
+/*
  * Bit-pack int8 values (masks or ready-made codes), low `bits` bits of each.
  * Replaces torch.ops.act_lib.pack_triton / unpack_triton
  * (AC/act_triton_kernel.py:398-433, kernels :246-322).  x, y: int8 [n_groups, group_size].

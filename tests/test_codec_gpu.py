@@ -264,3 +264,46 @@ def test_beyond_32bit_indices(oracle, cuda_device):
     y = c.dequant_unpack(packed[-ng_tail:], scale[-ng_tail:], mn[-ng_tail:], bits, gs, out_dtype=torch.float32)
     err = (y - x[-n_tail:].float().view(-1, gs)).abs()
     assert (err <= scale[-ng_tail:, None] * 1.0001 + 1e-6).all()
+
+
+@pytest.mark.parametrize("dtype", (torch.float32, torch.bfloat16, torch.float16), ids=("f32", "bf16", "f16"))
+@pytest.mark.parametrize("tile", (8, 16, 32))
+@pytest.mark.parametrize("bits", (1, 2, 4, 8))
+def test_tiled_addressing_equals_permute(cuda_device, dtype, tile, bits):
+    """quant_pack_tiles reads sqrt(gs) x sqrt(gs) spatial tiles in place: packed words, scale and
+    min equal those of the flat kernel on the permuted copy (same hash counters); the tiled
+    unpack writes what the flat unpack plus the inverse permute give.  Shapes include a partial
+    last kernel tile and H != W."""
+    from deep_optimization_b200 import codec
+    g = torch.Generator().manual_seed(31 + tile + bits)
+    N, C, H, W = 3, 5, 2 * tile, 3 * tile
+    x = (torch.randn((N, C, H, W), generator=g) * 3).to(dtype).to(cuda_device)
+    gs = tile * tile
+    xp = x.reshape(N, C, H // tile, tile, W // tile, tile).permute(0, 1, 2, 4, 3, 5).reshape(-1, gs).contiguous()
+    for flags in (0, 1):
+        want = codec.quant_pack(xp, bits, gs, seed=5, offset=9, flags=flags)
+        got = codec.quant_pack_tiles(x, bits, tile, seed=5, offset=9, flags=flags)
+        assert torch.equal(got[0], want[0]) and torch.equal(got[1], want[1]) and torch.equal(got[2], want[2])
+    for out_dtype in (torch.bfloat16, torch.float32):
+        flat = codec.dequant_unpack(*want, bits, gs, out_dtype=out_dtype)
+        back = flat.reshape(N, C, H // tile, W // tile, tile, tile).permute(0, 1, 2, 4, 3, 5).reshape(N, C, H, W)
+        y = codec.dequant_unpack_tiles(*got, bits, tile, (N, C, H, W), out_dtype=out_dtype)
+        assert torch.equal(y, back)
+
+
+def test_module_utils_uses_tiles(cuda_device):
+    """The quantise boundary takes the in-place tiled kernels for spatially groupable inputs and
+    returns the same tensors and meta as the permute path."""
+    from deep_optimization_b200 import codec
+    from deep_optimization_b200.modules import module_utils as mu
+    from deep_optimization_b200.modules.tensor_act_reshape_utils import spatical_aware_act_tensor_reshape
+    x = torch.randn(4, 6, 32, 48, device=cuda_device).to(torch.bfloat16)
+    codec.manual_seed(77)
+    (p, s, m), meta = mu.quantize(x, 2, False, 256, False, 4, False, 0, False, 0.0)
+    groups, N, G, nh, nw, shape, pad_e, re_e, cm = spatical_aware_act_tensor_reshape(x, 256, False, False)
+    assert meta == (2, False, 256, False, N, G, nh, nw, pad_e, re_e, cm, False, 0, shape)
+    assert p.shape == (N * G, 16) and s.shape == (N, G) and m.shape == (N, G)
+    y = mu.dequantize((p, s, m), meta)
+    assert y.shape == x.shape and y.dtype == torch.bfloat16
+    step = s.reshape(4, 6, 2, 3, 1, 1).expand(4, 6, 2, 3, 16, 16).permute(0, 1, 2, 4, 3, 5).reshape(4, 6, 32, 48)
+    assert ((y.float() - x.float()).abs() <= step * 1.01 + 0.02 * x.float().abs()).all()
