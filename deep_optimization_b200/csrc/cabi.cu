@@ -51,7 +51,9 @@ extern "C" const char* act_strerror(int code) {
     }
 }
 
-extern "C" int act_abi_version(void) { return 1; }
+// 2: hash and round-to-nearest modes are fixed-point (8 fraction bits, noise bytes); entry
+// points added for batch-norm statistics, BN+ReLU, backward constants and tiled addressing
+extern "C" int act_abi_version(void) { return 2; }
 
 // Greedy bit allocation.  Every layer i starts at b[i] bits and weighs w[i]; the
 // layer whose variance term C*(1/(2^b-1)^2 - 1/(2^(b-1)-1)^2) grows least loses
