@@ -272,6 +272,31 @@ def run_extras(dev):
         k: {"GBps": by[k] / t / 1e6, "frac": by[k] / t / 1e6 / peak, "ms_per_launch": t}
         for k, t in (("stats", t_stats), ("norm_relu_quant_pack", t_fwd), ("bwd_reduce", t_red), ("bwd_dx", t_dx))}
     del xb, dyb, pk, sc, mnn, mask
+    # fused activation kernels on the ViT MLP activation, bf16 [256,197,3072], group 128, 2 bits:
+    # forward writes y and the packed derivative, backward multiplies dy by the decoded derivative;
+    # ReLU on the conv activation keeps one mask bit per element (wrapper time included)
+    shp = (256, 197, 3072)
+    n = shp[0] * shp[1] * shp[2]
+    xa = [torch.randn(shp, device=dev).to(torch.bfloat16) for _ in range(2)]
+    _, pk, sc, mnn = codec.activation_fwd_quant_pack(xa[0], "gelu", BITS, GROUP)
+    t_gf = _time_launches(lambda i=0: codec.activation_fwd_quant_pack(xa[i % 2], "gelu", BITS, GROUP), 20)
+    t_gb = _time_launches(lambda i=0: codec.mul_dequant_unpack(pk, sc, mnn, xa[i % 2], BITS, GROUP), 20)
+    b_gf = 2 * n + 2 * n + n * BITS // 8 + 8 * (n // GROUP)
+    fused = {"gelu_fwd_quant_pack": {"GBps": b_gf / t_gf / 1e6, "frac": b_gf / t_gf / 1e6 / peak, "ms_per_launch": t_gf},
+             "gelu_bwd_dequant_mul": {"GBps": b_gf / t_gb / 1e6, "frac": b_gf / t_gb / 1e6 / peak, "ms_per_launch": t_gb}}
+    del xa, pk, sc, mnn
+    n = 1
+    for d in SHAPE:
+        n *= d
+    xr = [torch.randn(SHAPE, device=dev).to(torch.bfloat16) for _ in range(rot)]
+    _, mbits = codec.relu_fwd_pack(xr[0])
+    t_rf = _time_launches(lambda i=0: codec.relu_fwd_pack(xr[i % rot]), 40)
+    t_rb = _time_launches(lambda i=0: codec.relu_bwd_unpack(mbits, xr[i % rot]), 40)
+    b_r = 2 * n + 2 * n + n // 8
+    fused["relu_fwd_mask_pack"] = {"GBps": b_r / t_rf / 1e6, "frac": b_r / t_rf / 1e6 / peak, "ms_per_launch": t_rf}
+    fused["relu_bwd_mask_unpack"] = {"GBps": b_r / t_rb / 1e6, "frac": b_r / t_rb / 1e6 / peak, "ms_per_launch": t_rb}
+    out["fused_activation_kernels_bf16"] = fused
+    del xr, mbits
     # FP8 GEMM shapes (M, K, N); peak = nominal dense FP8 of a B200
     gem = {}
     bf16_peak = None
