@@ -482,19 +482,34 @@ quant_pack_kernel(const void* __restrict__ x_, const float* __restrict__ noise,
             for (int k = 0; k < 4; ++k) {
                 float yv[8];
                 if (IS_BN) {
+                    // four consecutive elements share a channel (HW is a multiple of 4), all eight
+                    // when HW is a multiple of 8; the four roundings of x_hat and y run on f32x2 pairs
+                    const bool one_channel = (bn.hw & 7u) == 0u;
+                    float4 p = make_float4(0.0f, 1.0f, 1.0f, 0.0f);
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
-                        // four consecutive elements share a channel (HW is a multiple of 4)
-                        const uint32_t t = bn_r0 + (uint32_t)(((k << log2_L) + j) * 8 + h * 4);
-                        const uint32_t q = bn.magic_hw ? __umulhi(t, bn.magic_hw) : t / bn.hw;
-                        uint32_t cc = bn_c0 + q;
-                        cc -= (bn.magic_c ? __umulhi(cc, bn.magic_c) : cc / bn.c) * bn.c;
-                        const float4 p = __ldg(bn.params + cc);
+                        if (h == 0 || !one_channel) {
+                            const uint32_t t = bn_r0 + (uint32_t)(((k << log2_L) + j) * 8 + h * 4);
+                            const uint32_t q = bn.magic_hw ? __umulhi(t, bn.magic_hw) : t / bn.hw;
+                            uint32_t cc = bn_c0 + q;
+                            cc -= (bn.magic_c ? __umulhi(cc, bn.magic_c) : cc / bn.c) * bn.c;
+                            p = __ldg(bn.params + cc);
+                        }
+                        const f32x2 nmean2 = pack2(-p.x, -p.x), inv2 = pack2(p.y, p.y);
+                        const f32x2 w2 = pack2(p.z, p.z);
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const float xh = __fmul_rn(__fsub_rn(xf[k * 8 + h * 4 + i], p.x), p.y);   // x_hat
-                            yv[h * 4 + i] = __fadd_rn(__fmul_rn(xh, p.z), p.w);                       // affine
-                            xf[k * 8 + h * 4 + i] = xh;
+                        for (int i = 0; i < 4; i += 2) {
+                            const int e = k * 8 + h * 4 + i;
+                            const f32x2 xh2 = mul2_rn(add2_rn(pack2(xf[e], xf[e + 1]), nmean2), inv2);   // x_hat
+                            // affine: the product on the pair, the add as two scalar adds (a packed
+                            // multiply followed by a packed add gets fused into one FMA by ptxas,
+                            // which would drop the rounding of the product)
+                            uint32_t a0, a1, c0, c1;
+                            unpack2u(xh2, a0, a1);
+                            unpack2u(mul2_rn(xh2, w2), c0, c1);
+                            xf[e] = __uint_as_float(a0); xf[e + 1] = __uint_as_float(a1);
+                            yv[h * 4 + i] = __fadd_rn(__uint_as_float(c0), p.w);
+                            yv[h * 4 + i + 1] = __fadd_rn(__uint_as_float(c1), p.w);
                         }
                     }
                 } else {
