@@ -323,10 +323,12 @@ def run_extras(dev):
     return out
 
 
-def run_train(name, dev, world, local, steps=8, warmup=3, act=True, batch=256):
+def run_train(name, dev, world, local, steps=8, warmup=3, act=True, batch=256, channels_last=False):
     """One end-to-end configuration: `name` in (resnet50, vit_b16), ACT 2-bit on every
     supported layer whose activation exceeds 10 MiB, bf16 autocast, batch 256 per GPU of
     synthetic N(0,1) images with uniform labels, DDP (NCCL all-reduce) when world > 1.
+    `channels_last` keeps model and images in NHWC memory (cuDNN's native layout for bf16
+    convolutions; the fused batch-norm, ReLU and codec kernels then work channel-minor).
     Returns images/s over all ranks (device-timed, max over ranks) and peak memory."""
     import torch
     import torch.distributed as dist
@@ -341,6 +343,8 @@ def run_train(name, dev, world, local, steps=8, warmup=3, act=True, batch=256):
         net = Controller(model, cfg, input_shape=(3, 224, 224), test=False, device=dev).traced_model
     else:
         net = model.train()
+    if channels_last:
+        net = net.to(memory_format=torch.channels_last)
     if world > 1:
         net = nn.parallel.DistributedDataParallel(net, device_ids=[local], static_graph=True,
                                                   bucket_cap_mb=25, broadcast_buffers=False)
@@ -351,6 +355,8 @@ def run_train(name, dev, world, local, steps=8, warmup=3, act=True, batch=256):
     g = torch.Generator(device=dev).manual_seed(1234 + local)
     x = torch.randn((batch, 3, 224, 224), device=dev, generator=g).to(torch.bfloat16)
     y = torch.randint(0, 1000, (batch,), device=dev, generator=g)
+    if channels_last:
+        x = x.contiguous(memory_format=torch.channels_last)
     codec.manual_seed(99)
     torch.cuda.reset_peak_memory_stats(dev)
 
@@ -522,6 +528,8 @@ def run_ours(args):
         train = {"config": "batch 256 per GPU, bf16 autocast, synthetic images, ACT 2-bit via Controller",
                  "resnet50_act2bit": run_train("resnet50", dev, world, local),
                  "resnet50_no_act": run_train("resnet50", dev, world, local, act=False),
+                 "resnet50_act2bit_channels_last": run_train("resnet50", dev, world, local, channels_last=True),
+                 "resnet50_no_act_channels_last": run_train("resnet50", dev, world, local, act=False, channels_last=True),
                  "vit_b16_act2bit": run_train("vit_b16", dev, world, local),
                  "vit_b16_no_act": run_train("vit_b16", dev, world, local, act=False)}
 

@@ -221,7 +221,9 @@ def calc_precision(b: torch.Tensor, C: torch.Tensor, w: torch.Tensor, target: fl
 def relu_fwd_pack(x: torch.Tensor, relu6: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
     """y = relu(x) (or the ReLU6 window) and the 1-bit mask as int32 words, one pass."""
     _require_cuda(x, "x")
-    x = x.contiguous()
+    # element-wise: a channels-last tensor is processed as it lies in memory (y and the mask
+    # bits follow that order; relu_bwd_unpack must be given dy in the same memory format)
+    x = x if _channels_last(x) else x.contiguous()
     if x.numel() % 32:
         raise ValueError("numel must be a multiple of 32")
     y = torch.empty_like(x)
@@ -233,10 +235,14 @@ def relu_fwd_pack(x: torch.Tensor, relu6: bool = False) -> Tuple[torch.Tensor, t
     return y, bits
 
 
-def relu_bwd_unpack(mask_bits: torch.Tensor, dy: torch.Tensor) -> torch.Tensor:
-    """dx = mask ? dy : 0."""
+def relu_bwd_unpack(mask_bits: torch.Tensor, dy: torch.Tensor, channels_last: bool = False) -> torch.Tensor:
+    """dx = mask ? dy : 0.  `channels_last`: the mask was taken from a channels-last tensor, so
+    dy is walked (after a conversion if it arrives in another format) in that memory order."""
     _require_cuda(dy, "dy")
-    dy = dy.contiguous()
+    if channels_last or _channels_last(dy):
+        dy = dy.contiguous(memory_format=torch.channels_last)
+    else:
+        dy = dy.contiguous()
     dx = torch.empty_like(dy)
     with torch.cuda.device(dy.device):
         rc = _lib.load().act_relu_bwd_unpack(mask_bits.data_ptr(), dy.data_ptr(), _DTYPES[dy.dtype],
@@ -291,11 +297,31 @@ def mul_dequant_unpack(packed: torch.Tensor, scale: torch.Tensor, mn: torch.Tens
 
 # ---------------------------------------------------------------- fused batch-norm kernels
 
+def _channels_last(x: torch.Tensor) -> bool:
+    """True for a 4-D tensor stored channel-minor (NHWC memory) and not also NCHW-contiguous."""
+    return (x.dim() == 4 and not x.is_contiguous()
+            and x.is_contiguous(memory_format=torch.channels_last))
+
+
+def _bn_layout(x: torch.Tensor):
+    """(tensor whose storage the kernels walk, n_batch, C, hw) of a batch-norm operand.  A
+    channels-last tensor is taken as it lies in memory, [N*H*W, C] with hw = 1 (the kernels'
+    channel-minor layout); anything else as contiguous [N, C, HW]."""
+    C = x.shape[1]
+    if _channels_last(x) and C % 8 == 0:
+        return x, x.numel() // C, C, 1
+    x = x.contiguous()
+    return x, x.shape[0], C, x.numel() // (x.shape[0] * C)
+
+
 def bn_fused_supported(x: torch.Tensor, group_size: int) -> bool:
-    """Shapes the fused batch-norm kernels take: [N, C, ...] with HW a multiple of 4."""
+    """Shapes the fused batch-norm kernels take: [N, C, ...] with HW a multiple of 4, or a
+    channels-last [N, C, H, W] with C a multiple of 8 (groups then run over NHWC memory)."""
     if x.dim() < 3 or not x.is_cuda or x.dtype not in _DTYPES:
         return False
     C = x.shape[1]
+    if _channels_last(x) and C % 8 == 0:
+        return C <= 4096 and x.numel() % group_size == 0
     hw = x.numel() // (x.shape[0] * C)
     return (hw % 4 == 0 and hw * (hw + 1024) < 2 ** 32 and C <= 4096
             and x.numel() % group_size == 0)
@@ -306,9 +332,7 @@ def bn_stats(x: torch.Tensor, eps: float, weight: Optional[torch.Tensor] = None,
              running_var: Optional[torch.Tensor] = None, momentum: float = 0.0) -> torch.Tensor:
     """Batch statistics of x [N, C, ...]: the fp32 [C, 4] table (mean, 1/sqrt(var+eps), weight,
     bias) that bn_fwd_norm_quant_pack reads; fp32 running statistics are updated in place."""
-    x = x.contiguous()
-    N, C = x.shape[0], x.shape[1]
-    hw = x.numel() // (N * C)
+    x, N, C, hw = _bn_layout(x)
 
     def f32(t):
         if t is None:
@@ -340,9 +364,7 @@ def bn_fwd_norm_quant_pack(x: torch.Tensor, mean: Optional[torch.Tensor], invstd
     relu=True also applies y = max(y, 0) and returns the 1-bit ReLU mask as a fifth value."""
     global _next_offset
     _, nwords, _ = _bits_consts(bits, group_size)
-    x = x.contiguous()
-    N, C = x.shape[0], x.shape[1]
-    hw = x.numel() // (N * C)
+    x, N, C, hw = _bn_layout(x)
     if params is None:
         ones = torch.ones_like(mean) if weight is None else weight.float()
         zeros = torch.zeros_like(mean) if bias is None else bias.float()
@@ -379,9 +401,7 @@ def bn_bwd_reduce(packed: torch.Tensor, scale: torch.Tensor, mn: torch.Tensor, d
                   group_size: int, mask: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     """(sum dy * x_hat, sum dy) per channel, from the packed x_hat; with the fused ReLU's `mask`
     dy counts only where its bit is set."""
-    dy = dy.contiguous()
-    N, C = dy.shape[0], dy.shape[1]
-    hw = dy.numel() // (N * C)
+    dy, N, C, hw = _bn_layout(dy)
     sums = torch.zeros(2 * C, dtype=torch.float32, device=dy.device)
     lib = _lib.load()
     with torch.cuda.device(dy.device):
@@ -418,9 +438,7 @@ def bn_bwd_dx(packed: torch.Tensor, scale: torch.Tensor, mn: torch.Tensor, dy: t
               coef: Optional[torch.Tensor] = None) -> torch.Tensor:
     """dx = k1[c] * dy - k2[c] - k3[c] * x_hat (dy zeroed where the fused ReLU's `mask` bit is
     clear); the constants come as three vectors or as bn_bwd_coef's table."""
-    dy = dy.contiguous()
-    N, C = dy.shape[0], dy.shape[1]
-    hw = dy.numel() // (N * C)
+    dy, N, C, hw = _bn_layout(dy)
     if coef is None:
         coef = torch.stack([k1.float(), k2.float(), k3.float(), torch.zeros_like(k1, dtype=torch.float32)], dim=1).contiguous()
     dx = torch.empty_like(dy)

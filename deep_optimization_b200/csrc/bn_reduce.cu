@@ -199,24 +199,161 @@ bn_plane_reduce_kernel(const uint8_t* __restrict__ x, const uint8_t* __restrict_
     }
 }
 
-// One thread per channel: the block partials summed in a fixed order in double, then
+// Channel-minor layout (HW = 1: x is [rows, C], C a multiple of 8, a channels-last
+// activation).  A thread owns eight consecutive channels (one 16-byte vector of 16-bit
+// elements per row) and walks the rows of the block's slice; tpr = min(C/8, 256) threads
+// cover one row (or 2048 channels of it, blockIdx.x choosing which) and the block's other
+// threads take the following rows, so a warp reads contiguous memory.  Sixteen accumulators per
+// thread; at the end the threads of a channel vector are summed through shared memory and
+// every channel leaves once per block with coalesced stores (MODE 0: partial pairs
+// out[(s * C + c) * 2 + {0, 1}], slice-major) or coalesced atomics (MODE 1).
+template <int DT, int MODE, int BITS>
+__global__ void __launch_bounds__(kRedThreads)
+bn_rows_reduce_kernel(const uint8_t* __restrict__ x, const uint8_t* __restrict__ packed,
+                      const float* __restrict__ scale, const float* __restrict__ mn,
+                      const uint8_t* __restrict__ mask, float* __restrict__ out, int64_t n_rows,
+                      uint32_t C, uint32_t tpr, int log2_gs)
+{
+    __shared__ float s_acc[16][kRedThreads + 1];
+    const uint32_t s = blockIdx.y, S = gridDim.y;
+    const uint32_t rpi = kRedThreads / tpr;                  // rows per block step
+    const uint32_t q = threadIdx.x % tpr, rl = threadIdx.x / tpr;
+    const uint32_t chunk = blockIdx.x * tpr + q;             // which vector of eight channels
+    const bool active = rl < rpi && chunk * 8u < C;
+    const int64_t r0 = n_rows * s / S, r1 = n_rows * (s + 1) / S;
+    grid_dependency_wait();
+    grid_launch_dependents();
+    float a[8], b[8], pivot[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { a[i] = 0.0f; b[i] = 0.0f; pivot[i] = 0.0f; }
+    if (active) {
+        if (MODE == 0) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) pivot[i] = load1<DT>(x, (int64_t)chunk * 8 + i);
+        }
+        constexpr int U = 4;
+        constexpr int RAW = (ElemT<DT>::bytes == 4) ? 2 : 1;
+        for (int64_t r = r0 + rl; r < r1; r += (int64_t)U * rpi) {
+            uint4 raw[U][RAW];
+            uint2 w[U];
+            uint32_t keep[U];
+            float sc[U], m[U];
+            bool ok[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int64_t row = r + (int64_t)u * rpi;
+                ok[u] = row < r1;
+#pragma unroll
+                for (int k = 0; k < RAW; ++k) raw[u][k] = make_uint4(0u, 0u, 0u, 0u);
+                w[u] = make_uint2(0u, 0u); keep[u] = 0xFFu; sc[u] = 0.0f; m[u] = 0.0f;
+                if (!ok[u]) continue;
+                const int64_t e = row * C + (int64_t)chunk * 8;
+                const uint8_t* px = x + e * ElemT<DT>::bytes;
+#pragma unroll
+                for (int k = 0; k < RAW; ++k) raw[u][k] = ldg_stream_v4(px + 16 * k);
+                if (MODE == 1) {
+                    w[u] = load_codes8v<BITS>(packed, e);
+                    const int64_t g = e >> log2_gs;
+                    sc[u] = __ldg(scale + g); m[u] = __ldg(mn + g);
+                    if (mask) keep[u] = (uint32_t)__ldg(mask + (e >> 3));
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                float f[8];
+                if (ElemT<DT>::bytes == 4) {
+#pragma unroll
+                    for (int k = 0; k < RAW; ++k) {
+                        f[4 * k] = __uint_as_float(raw[u][k].x); f[4 * k + 1] = __uint_as_float(raw[u][k].y);
+                        f[4 * k + 2] = __uint_as_float(raw[u][k].z); f[4 * k + 3] = __uint_as_float(raw[u][k].w);
+                    }
+                } else {
+                    constexpr int D16 = (DT == ACT_DTYPE_F32) ? ACT_DTYPE_BF16 : DT;
+                    const uint32_t h[4] = {raw[u][0].x, raw[u][0].y, raw[u][0].z, raw[u][0].w};
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) { f[2 * k] = widen_lo<D16>(h[k]); f[2 * k + 1] = widen_hi<D16>(h[k]); }
+                }
+                if (MODE == 0) {
+                    if (ok[u]) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const float d = __fsub_rn(f[i], pivot[i]);
+                            a[i] = __fadd_rn(a[i], d);
+                            b[i] = __fmaf_rn(d, d, b[i]);
+                        }
+                    }
+                } else {
+                    // a row past the end holds zeros and adds nothing
+                    constexpr uint32_t MASK = (1u << BITS) - 1u;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const uint32_t word = (BITS == 8 && i >= 4) ? w[u].y : w[u].x;
+                        const int sh = (BITS == 8) ? (i & 3) * 8 : i * BITS;
+                        const float code = __fsub_rn(__uint_as_float(kMagicBits | ((word >> sh) & MASK)), kMagic);
+                        const float xh = __fmaf_rn(code, sc[u], m[u]);
+                        const float d = ((keep[u] >> i) & 1u) ? f[i] : 0.0f;
+                        a[i] = __fmaf_rn(d, xh, a[i]);
+                        b[i] = __fadd_rn(b[i], d);
+                    }
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { s_acc[i][threadIdx.x] = a[i]; s_acc[8 + i][threadIdx.x] = b[i]; }
+    __syncthreads();
+    // channel cl of the block's tile: vector cl / 8, element cl % 8, summed over the row lanes
+    const uint32_t tile_c = tpr * 8u, c_base = blockIdx.x * tile_c;
+    for (uint32_t cl = threadIdx.x; cl < tile_c && c_base + cl < C; cl += kRedThreads) {
+        const uint32_t v = cl >> 3, i = cl & 7u;
+        float ta = 0.0f, tb = 0.0f;
+        for (uint32_t l = 0; l < rpi; ++l) { ta += s_acc[i][l * tpr + v]; tb += s_acc[8 + i][l * tpr + v]; }
+        const uint32_t c = c_base + cl;
+        if (MODE == 0) {
+            *reinterpret_cast<float2*>(out + ((int64_t)s * C + c) * 2) = make_float2(ta, tb);
+        } else {
+            atomicAdd(out + c, ta);
+            atomicAdd(out + C + c, tb);
+        }
+    }
+}
+
+// LPC lanes per channel (1 after the plane walk; 32 after the row walk, which leaves hundreds of
+// partials per channel): the block partials summed in a fixed order in double, then
 // mean = pivot + a/M, var = b/M - (a/M)^2 (biased), invstd = 1/sqrt(var + eps).
-template <int DT>
+template <int DT, int LPC>
 __global__ void bn_stats_finalize_kernel(const uint8_t* __restrict__ x, const float* __restrict__ part,
                                          const float* __restrict__ weight, const float* __restrict__ bias,
                                          float* __restrict__ running_mean, float* __restrict__ running_var,
                                          float4* __restrict__ params, int64_t n_batch, uint32_t C, uint32_t hw,
-                                         uint32_t S, double eps, double momentum)
+                                         uint32_t S, double eps, double momentum, uint32_t stride_c, uint32_t stride_s)
 {
     grid_dependency_wait();
     grid_launch_dependents();
-    const uint32_t c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= C) return;
+    const uint32_t c = (blockIdx.x * blockDim.x + threadIdx.x) / LPC, sub = threadIdx.x % LPC;
     double a = 0.0, b = 0.0;
-    for (uint32_t s = 0; s < S; ++s) {
-        a += (double)part[((int64_t)c * S + s) * 2];
-        b += (double)part[((int64_t)c * S + s) * 2 + 1];
+    // partial pair (c, s) sits at pair index c * stride_c + s * stride_s (channel-major from the
+    // plane walk, slice-major from the row walk)
+    if (c < C) {
+        // four loads in flight per lane; the order of the additions is fixed
+        for (uint32_t s = sub; s < S; s += 4 * LPC) {
+            float2 t[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const uint32_t su = s + u * LPC;
+                t[u] = su < S ? *reinterpret_cast<const float2*>(part + ((int64_t)c * stride_c + (int64_t)su * stride_s) * 2)
+                              : make_float2(0.0f, 0.0f);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) { a += (double)t[u].x; b += (double)t[u].y; }
+        }
     }
+#pragma unroll
+    for (int off = LPC / 2; off > 0; off >>= 1) {
+        a += __shfl_xor_sync(0xffffffffu, a, off);
+        b += __shfl_xor_sync(0xffffffffu, b, off);
+    }
+    if (c >= C || sub != 0) return;
     const double M = (double)n_batch * (double)hw;
     const double dm = a / M;
     const double mean = (double)load1<DT>(x, (int64_t)c * hw) + dm;
@@ -274,6 +411,25 @@ template <typename K> static int reduce_capacity(K kernel) {
     return cached;
 }
 
+// Row walk (channel-minor layout): threads per row, column tiles of 2048 channels and row
+// slices; the grid is col_tiles x slices, at most one resident wave and kMaxRowSlices slices.
+constexpr int kMaxRowSlices = 592;
+struct RowGeom { uint32_t tpr, col_tiles; int S; };
+static RowGeom row_geom(int64_t n_rows, int channels, int capacity) {
+    RowGeom g;
+    const uint32_t cols8 = (uint32_t)channels / 8u;
+    g.tpr = cols8 < (uint32_t)kRedThreads ? cols8 : (uint32_t)kRedThreads;
+    g.col_tiles = (cols8 + g.tpr - 1) / g.tpr;
+    int64_t want = capacity / (int64_t)g.col_tiles;
+    const int64_t rpi = kRedThreads / g.tpr;
+    const int64_t steps = (n_rows + rpi - 1) / rpi;          // a slice gets at least one block step of rows
+    if (want > steps) want = steps;
+    if (want > kMaxRowSlices) want = kMaxRowSlices;
+    if (want < 1) want = 1;
+    g.S = (int)want;
+    return g;
+}
+
 static bool dtype_ok(int d) { return d == ACT_DTYPE_F32 || d == ACT_DTYPE_BF16 || d == ACT_DTYPE_F16; }
 
 template <int DT>
@@ -281,6 +437,26 @@ static cudaError_t launch_stats(const uint8_t* x, int64_t n_batch, int C, int64_
                                 const float* weight, const float* bias, float* rm, float* rv, double momentum,
                                 float* params, float* ws, cudaStream_t st)
 {
+    if (hw == 1) {
+        // channel-minor: row walk, slice-major partials
+        const RowGeom g = row_geom(n_batch, C, reduce_capacity(bn_rows_reduce_kernel<DT, 0, 2>));
+        cudaLaunchConfig_t cfg = {};
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.gridDim = dim3(g.col_tiles, (unsigned)g.S, 1);
+        cfg.blockDim = dim3(kRedThreads, 1, 1);
+        cfg.stream = st;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        cudaError_t e = cudaLaunchKernelEx(&cfg, bn_rows_reduce_kernel<DT, 0, 2>, x, static_cast<const uint8_t*>(nullptr),
+                                           static_cast<const float*>(nullptr), static_cast<const float*>(nullptr),
+                                           static_cast<const uint8_t*>(nullptr), ws, n_batch, (uint32_t)C, g.tpr, 5);
+        if (e != cudaSuccess) return e;
+        return launch_overlapped(bn_stats_finalize_kernel<DT, 32>, (C * 32 + 127) / 128, 128, st, x, static_cast<const float*>(ws),
+                                 weight, bias, rm, rv, reinterpret_cast<float4*>(params), n_batch, (uint32_t)C,
+                                 1u, (uint32_t)g.S, eps, momentum, 1u, (uint32_t)C);
+    }
     auto kernel = (hw & 7) ? bn_plane_reduce_kernel<DT, 0, 2, 4> : bn_plane_reduce_kernel<DT, 0, 2, 8>;
     const int S = bn_splits(n_batch, C, (hw & 7) ? reduce_capacity(bn_plane_reduce_kernel<DT, 0, 2, 4>)
                                                  : reduce_capacity(bn_plane_reduce_kernel<DT, 0, 2, 8>));
@@ -297,15 +473,29 @@ static cudaError_t launch_stats(const uint8_t* x, int64_t n_batch, int C, int64_
                                        static_cast<const float*>(nullptr), static_cast<const float*>(nullptr),
                                        static_cast<const uint8_t*>(nullptr), ws, n_batch, (uint32_t)C, (uint32_t)hw, 5);
     if (e != cudaSuccess) return e;
-    return launch_overlapped(bn_stats_finalize_kernel<DT>, (C + 127) / 128, 128, st, x, static_cast<const float*>(ws),
+    return launch_overlapped(bn_stats_finalize_kernel<DT, 1>, (C + 127) / 128, 128, st, x, static_cast<const float*>(ws),
                              weight, bias, rm, rv, reinterpret_cast<float4*>(params), n_batch, (uint32_t)C,
-                             (uint32_t)hw, (uint32_t)S, eps, momentum);
+                             (uint32_t)hw, (uint32_t)S, eps, momentum, (uint32_t)S, 1u);
 }
 
 template <int DT, int BITS>
 static cudaError_t launch_bwd_reduce_one(const uint8_t* dy, const uint8_t* packed, const float* scale, const float* mn,
                                          const uint8_t* mask, float* sums, int64_t n_batch, int C, int64_t hw, int log2_gs, cudaStream_t st)
 {
+    if (hw == 1) {
+        const RowGeom g = row_geom(n_batch, C, reduce_capacity(bn_rows_reduce_kernel<DT, 1, BITS>));
+        cudaLaunchConfig_t cfg = {};
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.gridDim = dim3(g.col_tiles, (unsigned)g.S, 1);
+        cfg.blockDim = dim3(kRedThreads, 1, 1);
+        cfg.stream = st;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        return cudaLaunchKernelEx(&cfg, bn_rows_reduce_kernel<DT, 1, BITS>, dy, packed, scale, mn, mask, sums, n_batch,
+                                  (uint32_t)C, g.tpr, log2_gs);
+    }
     auto kernel = (hw & 7) ? bn_plane_reduce_kernel<DT, 1, BITS, 4> : bn_plane_reduce_kernel<DT, 1, BITS, 8>;
     const int S = bn_splits(n_batch, C, (hw & 7) ? reduce_capacity(bn_plane_reduce_kernel<DT, 1, BITS, 4>)
                                                  : reduce_capacity(bn_plane_reduce_kernel<DT, 1, BITS, 8>));
@@ -340,7 +530,12 @@ static cudaError_t launch_bwd_reduce(int bits, const uint8_t* dy, const uint8_t*
 extern "C" size_t act_bn_stats_workspace(int64_t n_batch, int channels)
 {
     if (n_batch <= 0 || channels <= 0) return 0;
-    return (size_t)channels * (size_t)act::bn_splits(n_batch, channels, act::kMaxCapacity) * 2 * sizeof(float);
+    // enough for the plane walk's slices and for the row walk's (channel-minor layout, where
+    // n_batch counts rows)
+    size_t slices = (size_t)act::bn_splits(n_batch, channels, act::kMaxCapacity);
+    const size_t row_slices = (size_t)(n_batch < act::kMaxRowSlices ? n_batch : act::kMaxRowSlices);
+    if (row_slices > slices) slices = row_slices;
+    return (size_t)channels * slices * 2 * sizeof(float);
 }
 
 extern "C" int act_bn_stats(const void* x, int dtype, int64_t n_batch, int channels, int64_t hw, double eps,
@@ -350,7 +545,8 @@ extern "C" int act_bn_stats(const void* x, int dtype, int64_t n_batch, int chann
     using namespace act;
     if (!dtype_ok(dtype)) return ACT_ERR_DTYPE;
     if (n_batch <= 0 || channels <= 0 || hw <= 0) return ACT_ERR_SIZE;
-    if ((hw & 3) || hw >= (1ll << 31) || channels > 65535) return ACT_ERR_UNSUPPORTED;
+    // hw == 1: channel-minor layout ([rows, C]), vectors of eight channels
+    if (hw == 1 ? (channels & 7) != 0 : ((hw & 3) || hw >= (1ll << 31) || channels > 65535)) return ACT_ERR_UNSUPPORTED;
     if (n_batch * channels > (INT64_MAX >> 4) / hw) return ACT_ERR_SIZE;
     if (!x || !params || !workspace) return ACT_ERR_NULL;
     // a plane starts on a multiple of 4 elements: 8 bytes for 16-bit types, 16 for fp32
@@ -375,7 +571,7 @@ static int bn_bwd_reduce_common(const void* packed, const float* scale, const fl
     if (bits != 1 && bits != 2 && bits != 4 && bits != 8) return ACT_ERR_BITS;
     if (group_size < 32 || group_size > 1024 || (group_size & (group_size - 1))) return ACT_ERR_GROUP;
     if (n_batch < 0 || channels <= 0 || hw <= 0) return ACT_ERR_SIZE;
-    if ((hw & 3) || hw >= (1ll << 31) || channels > 65535) return ACT_ERR_UNSUPPORTED;
+    if (hw == 1 ? (channels & 7) != 0 : ((hw & 3) || hw >= (1ll << 31) || channels > 65535)) return ACT_ERR_UNSUPPORTED;
     const int64_t n = n_batch * channels * hw;
     if (n > (INT64_MAX >> 4) || n % group_size) return ACT_ERR_SIZE;
     if (n == 0) return ACT_OK;

@@ -7,12 +7,15 @@ namespace act {
 extern template cudaError_t launch_pack_bits<ACT_DTYPE_F32>(int bits, int mode, const void* x, const float* noise, void* packed, float* scale, float* mn, int64_t n_elems, int log2_L, uint64_t seed, uint64_t offset, int flags, float clamp_alpha, cudaStream_t st);
 extern template cudaError_t launch_fused<ACT_DTYPE_F32>(int bits, int kind, bool nearest, const void* x, void* y, void* packed, float* scale, float* mn, int64_t n, int l2, uint64_t seed, uint64_t offset, cudaStream_t st);
 extern template cudaError_t launch_bn<ACT_DTYPE_F32>(int bits, bool nearest, const void* x, void* y, void* packed, float* scale, float* mn, int64_t n, int l2, uint64_t seed, uint64_t offset, BNArgs bn, cudaStream_t st);
+extern template cudaError_t launch_bn_cl<ACT_DTYPE_F32>(int bits, bool nearest, const void* x, void* y, void* packed, float* scale, float* mn, int64_t n, int l2, uint64_t seed, uint64_t offset, BNArgs bn, cudaStream_t st);
 extern template cudaError_t launch_pack_bits<ACT_DTYPE_BF16>(int bits, int mode, const void* x, const float* noise, void* packed, float* scale, float* mn, int64_t n_elems, int log2_L, uint64_t seed, uint64_t offset, int flags, float clamp_alpha, cudaStream_t st);
 extern template cudaError_t launch_fused<ACT_DTYPE_BF16>(int bits, int kind, bool nearest, const void* x, void* y, void* packed, float* scale, float* mn, int64_t n, int l2, uint64_t seed, uint64_t offset, cudaStream_t st);
 extern template cudaError_t launch_bn<ACT_DTYPE_BF16>(int bits, bool nearest, const void* x, void* y, void* packed, float* scale, float* mn, int64_t n, int l2, uint64_t seed, uint64_t offset, BNArgs bn, cudaStream_t st);
+extern template cudaError_t launch_bn_cl<ACT_DTYPE_BF16>(int bits, bool nearest, const void* x, void* y, void* packed, float* scale, float* mn, int64_t n, int l2, uint64_t seed, uint64_t offset, BNArgs bn, cudaStream_t st);
 extern template cudaError_t launch_pack_bits<ACT_DTYPE_F16>(int bits, int mode, const void* x, const float* noise, void* packed, float* scale, float* mn, int64_t n_elems, int log2_L, uint64_t seed, uint64_t offset, int flags, float clamp_alpha, cudaStream_t st);
 extern template cudaError_t launch_fused<ACT_DTYPE_F16>(int bits, int kind, bool nearest, const void* x, void* y, void* packed, float* scale, float* mn, int64_t n, int l2, uint64_t seed, uint64_t offset, cudaStream_t st);
 extern template cudaError_t launch_bn<ACT_DTYPE_F16>(int bits, bool nearest, const void* x, void* y, void* packed, float* scale, float* mn, int64_t n, int l2, uint64_t seed, uint64_t offset, BNArgs bn, cudaStream_t st);
+extern template cudaError_t launch_bn_cl<ACT_DTYPE_F16>(int bits, bool nearest, const void* x, void* y, void* packed, float* scale, float* mn, int64_t n, int l2, uint64_t seed, uint64_t offset, BNArgs bn, cudaStream_t st);
 extern template cudaError_t launch_pack_tiled<ACT_DTYPE_F32>(int bits, bool nearest, const void* x, void* packed, float* scale, float* mn, int64_t n_elems, int log2_L, uint64_t seed, uint64_t offset, TileArgs ta, cudaStream_t st);
 extern template cudaError_t launch_pack_tiled<ACT_DTYPE_BF16>(int bits, bool nearest, const void* x, void* packed, float* scale, float* mn, int64_t n_elems, int log2_L, uint64_t seed, uint64_t offset, TileArgs ta, cudaStream_t st);
 extern template cudaError_t launch_pack_tiled<ACT_DTYPE_F16>(int bits, bool nearest, const void* x, void* packed, float* scale, float* mn, int64_t n_elems, int log2_L, uint64_t seed, uint64_t offset, TileArgs ta, cudaStream_t st);
@@ -90,8 +93,14 @@ static int bn_fwd_common(const void* x, int dtype, int64_t n_batch, int channels
     if (bits != 1 && bits != 2 && bits != 4 && bits != 8) return ACT_ERR_BITS;
     if (group_size < 32 || group_size > 1024 || (group_size & (group_size - 1))) return ACT_ERR_GROUP;
     if (n_batch < 0 || channels <= 0 || hw <= 0) return ACT_ERR_SIZE;
+    // hw == 1 is the channel-minor layout ([rows, C], a channels-last activation): pieces of
+    // eight consecutive channels
+    const bool channel_minor = (hw == 1);
+    if (channel_minor) {
+        if ((channels & 7) || channels > 4096) return ACT_ERR_UNSUPPORTED;     // the table sits in shared memory
+    }
     // exactness of the multiply-high channel lookup, and channel-uniform groups of four
-    if ((hw & 3) || (uint64_t)hw * (uint64_t)(hw + 1024) >= (1ull << 32) ||
+    else if ((hw & 3) || (uint64_t)hw * (uint64_t)(hw + 1024) >= (1ull << 32) ||
         (uint64_t)channels * (uint64_t)(channels + 260) >= (1ull << 32)) return ACT_ERR_UNSUPPORTED;
     const int64_t n = n_batch * channels * hw;
     if (n > (INT64_MAX >> 4) || n % group_size) return ACT_ERR_SIZE;
@@ -105,7 +114,12 @@ static int bn_fwd_common(const void* x, int dtype, int64_t n_batch, int channels
     const bool nearest = (flags & ACT_FLAG_ROUND_NEAREST) != 0;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     cudaError_t e;
-    if (dtype == ACT_DTYPE_F32) e = launch_bn<ACT_DTYPE_F32>(bits, nearest, x, y, packed, scale, mn, n, log2_L, seed, offset, bn, st);
+    if (channel_minor) {
+        if (dtype == ACT_DTYPE_F32) e = launch_bn_cl<ACT_DTYPE_F32>(bits, nearest, x, y, packed, scale, mn, n, log2_L, seed, offset, bn, st);
+        else if (dtype == ACT_DTYPE_BF16) e = launch_bn_cl<ACT_DTYPE_BF16>(bits, nearest, x, y, packed, scale, mn, n, log2_L, seed, offset, bn, st);
+        else e = launch_bn_cl<ACT_DTYPE_F16>(bits, nearest, x, y, packed, scale, mn, n, log2_L, seed, offset, bn, st);
+    }
+    else if (dtype == ACT_DTYPE_F32) e = launch_bn<ACT_DTYPE_F32>(bits, nearest, x, y, packed, scale, mn, n, log2_L, seed, offset, bn, st);
     else if (dtype == ACT_DTYPE_BF16) e = launch_bn<ACT_DTYPE_BF16>(bits, nearest, x, y, packed, scale, mn, n, log2_L, seed, offset, bn, st);
     else e = launch_bn<ACT_DTYPE_F16>(bits, nearest, x, y, packed, scale, mn, n, log2_L, seed, offset, bn, st);
     return e == cudaSuccess ? ACT_OK : ACT_ERR_LAUNCH;

@@ -323,7 +323,7 @@ __device__ __forceinline__ void encode_piece_ref(const float* xf8, float mn, flo
 // kProGelu / kProSilu write y = act(x) to y_out and quantise the activation's derivative
 // (what backward multiplies dy with), replacing the reference's fused forward kernels
 // (Activation_Compression/modules/activations/kernel_implementation.py:184-342, 468-559).
-enum Producer { kProNone = 0, kProGelu = 1, kProSilu = 2, kProBN = 3, kProBNRelu = 4 };
+enum Producer { kProNone = 0, kProGelu = 1, kProSilu = 2, kProBN = 3, kProBNRelu = 4, kProBNcl = 5, kProBNReluCl = 6 };
 
 // Per-channel inputs of the batch-norm producer: x is [N, C, HW] contiguous and
 // params[c] = (mean, invstd, weight, bias).  The channel of element e is (e / HW) % C;
@@ -331,6 +331,11 @@ enum Producer { kProNone = 0, kProGelu = 1, kProSilu = 2, kProBN = 3, kProBNRelu
 // host enables only when HW*(HW+1024) < 2^32 and C*(C+260) < 2^32.
 // kProBNRelu also applies y = max(y, 0) and writes one mask bit per element (bit i of byte
 // e/8 = element e, the layout of relu_fwd_pack) to `mask`.
+// kProBNcl / kProBNReluCl are the same producers for the channel-minor layout (HW = 1, x is
+// [rows, C] with C a multiple of 8, what a channels-last activation is in memory): the
+// channel of element e is e % C, so the eight elements of a piece belong to eight
+// consecutive channels and every element reads its own row of the table (the rows of a
+// warp's loads are contiguous); the kernel keeps the table in shared memory, so C <= 4096.
 struct BNArgs {
     const float4* params;
     uint32_t hw, c, magic_hw, magic_c;
@@ -446,6 +451,17 @@ quant_pack_kernel(const void* __restrict__ x_, const float* __restrict__ noise,
     RawTile<DT> raw_a, raw_b;
     grid_dependency_wait();
     grid_launch_dependents();
+    // Channel-minor batch norm: every element needs its own table row, so the table is copied
+    // to shared memory once per block, the eight rows of a channel vector followed by one row
+    // of padding (144 bytes per vector): the lanes of a quarter warp read consecutive vectors
+    // and then fall on distinct banks.
+    extern __shared__ __align__(16) uint8_t dyn_smem[];
+    float4* const s_table = reinterpret_cast<float4*>(dyn_smem);
+    if (PRO == kProBNcl || PRO == kProBNReluCl) {
+        for (uint32_t c = threadIdx.x; c < bn.c; c += PackCfg<DT>::threads)
+            s_table[(c >> 3) * 9u + (c & 7u)] = __ldg(bn.params + c);
+        __syncthreads();
+    }
     if (tile < n_full) load_tile(raw_a, tile);
 
     // raw_cur holds this tile, raw_next receives the following one while this one is encoded
@@ -469,9 +485,13 @@ quant_pack_kernel(const void* __restrict__ x_, const float* __restrict__ noise,
         }
 
         // batch norm: plane index and offset inside the plane of the lane's group
-        constexpr bool IS_BN = (PRO == kProBN || PRO == kProBNRelu);
+        constexpr bool BN_CL = (PRO == kProBNcl || PRO == kProBNReluCl);
+        constexpr bool BN_RELU = (PRO == kProBNRelu || PRO == kProBNReluCl);
+        constexpr bool IS_BN = (PRO == kProBN || PRO == kProBNRelu || BN_CL);
         uint32_t bn_c0 = 0, bn_r0 = 0;
-        if (IS_BN) {
+        if (BN_CL) {
+            bn_c0 = (uint32_t)((uint64_t)group_e0 % bn.c);               // channel of the group's first element
+        } else if (IS_BN) {
             const uint64_t plane = (uint64_t)group_e0 / bn.hw;
             bn_r0 = (uint32_t)((uint64_t)group_e0 - plane * bn.hw);
             bn_c0 = (uint32_t)(plane % bn.c);
@@ -481,7 +501,27 @@ quant_pack_kernel(const void* __restrict__ x_, const float* __restrict__ noise,
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
                 float yv[8];
-                if (IS_BN) {
+                if (BN_CL) {
+                    // channel-minor: element i of the piece is channel cc + i (no wrap inside a piece)
+                    uint32_t cc = bn_c0 + (uint32_t)(((k << log2_L) + j) * 8);
+                    cc -= (bn.magic_c ? __umulhi(cc, bn.magic_c) : cc / bn.c) * bn.c;
+                    float4 p[8];
+                    const float4* row = s_table + (cc >> 3) * 9u;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) p[i] = row[i];
+#pragma unroll
+                    for (int i = 0; i < 8; i += 2) {
+                        const int e = k * 8 + i;
+                        const f32x2 xh2 = mul2_rn(add2_rn(pack2(xf[e], xf[e + 1]), pack2(-p[i].x, -p[i + 1].x)),
+                                                  pack2(p[i].y, p[i + 1].y));                  // x_hat
+                        uint32_t a0, a1, c0, c1;
+                        unpack2u(xh2, a0, a1);
+                        unpack2u(mul2_rn(xh2, pack2(p[i].z, p[i + 1].z)), c0, c1);
+                        xf[e] = __uint_as_float(a0); xf[e + 1] = __uint_as_float(a1);
+                        yv[i] = __fadd_rn(__uint_as_float(c0), p[i].w);
+                        yv[i + 1] = __fadd_rn(__uint_as_float(c1), p[i + 1].w);
+                    }
+                } else if (IS_BN) {
                     // four consecutive elements share a channel (HW is a multiple of 4), all eight
                     // when HW is a multiple of 8; the four roundings of x_hat and y run on f32x2 pairs
                     const bool one_channel = (bn.hw & 7u) == 0u;
@@ -516,7 +556,7 @@ quant_pack_kernel(const void* __restrict__ x_, const float* __restrict__ noise,
 #pragma unroll
                     for (int i = 0; i < 8; ++i) act_and_derivative<PRO>(xf[k * 8 + i], yv[i], xf[k * 8 + i]);
                 }
-                if (PRO == kProBNRelu) {
+                if (BN_RELU) {
                     uint32_t bits8 = 0;
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
@@ -852,20 +892,33 @@ cudaError_t launch_bn_one(const void* x, void* y, void* packed, float* scale, fl
                                  int64_t n_elems, int log2_L, uint64_t seed, uint64_t offset,
                                  BNArgs bn, cudaStream_t st)
 {
+    constexpr bool CL = (PRO == kProBNcl || PRO == kProBNReluCl);
+    constexpr size_t kMaxTable = (size_t)(4096 / 8) * 144;          // channel-minor table, C <= 4096
     static int per_sm = 0;
     if (per_sm == 0) {
         int n = 0;
+        if (CL) cudaFuncSetAttribute(quant_pack_kernel<DT, BITS, NM, PRO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxTable);
         if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, quant_pack_kernel<DT, BITS, NM, PRO>,
-                                                          PackCfg<DT>::threads, 0) != cudaSuccess || n < 1) n = 1;
+                                                          PackCfg<DT>::threads, CL ? kMaxTable : 0) != cudaSuccess || n < 1) n = 1;
         per_sm = n;
     }
     const uint64_t key = hash_key(hash_key(seed) + offset);
     const int64_t n_tiles = (n_elems + kTileElems - 1) / kTileElems;
     const int grid = stream_grid_for((n_tiles + PackCfg<DT>::warps - 1) / PackCfg<DT>::warps, per_sm);
-    return launch_overlapped(quant_pack_kernel<DT, BITS, NM, PRO>, grid, PackCfg<DT>::threads, st,
-                             x, static_cast<const float*>(nullptr), static_cast<uint8_t*>(packed), scale, mn,
-                             n_elems, log2_L, (uint32_t)key, (uint32_t)(key >> 32), 0, 0.0f,
-                             static_cast<uint8_t*>(y), bn, TileArgs{0u, 0u, 1u, 1u, 3});
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid, 1, 1);
+    cfg.blockDim = dim3((unsigned)PackCfg<DT>::threads, 1, 1);
+    cfg.dynamicSmemBytes = CL ? (size_t)(bn.c / 8u) * 144 : 0;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ACT_NO_PDL ? 0 : 1;
+    return cudaLaunchKernelEx(&cfg, quant_pack_kernel<DT, BITS, NM, PRO>,
+                              x, static_cast<const float*>(nullptr), static_cast<uint8_t*>(packed), scale, mn,
+                              n_elems, log2_L, (uint32_t)key, (uint32_t)(key >> 32), 0, 0.0f,
+                              static_cast<uint8_t*>(y), bn, TileArgs{0u, 0u, 1u, 1u, 3});
 }
 
 template <int DT>
@@ -879,6 +932,27 @@ cudaError_t launch_bn(int bits, bool nearest, const void* x, void* y, void* pack
                        : launch_bn_one<DT, B, kNoiseHash, kProBNRelu>(x, y, packed, scale, mn, n, l2, seed, offset, bn, st); \
     return nearest ? launch_bn_one<DT, B, kNoiseConst, kProBN>(x, y, packed, scale, mn, n, l2, seed, offset, bn, st) \
                    : launch_bn_one<DT, B, kNoiseHash, kProBN>(x, y, packed, scale, mn, n, l2, seed, offset, bn, st)
+    switch (bits) {
+        case 1: ACT_BN_CASE(1);
+        case 2: ACT_BN_CASE(2);
+        case 4: ACT_BN_CASE(4);
+        default: ACT_BN_CASE(8);
+    }
+#undef ACT_BN_CASE
+}
+
+// the same for the channel-minor layout (HW = 1)
+template <int DT>
+cudaError_t launch_bn_cl(int bits, bool nearest, const void* x, void* y, void* packed, float* scale,
+                         float* mn, int64_t n, int l2, uint64_t seed, uint64_t offset, BNArgs bn,
+                         cudaStream_t st)
+{
+#define ACT_BN_CASE(B) \
+    if (bn.mask) \
+        return nearest ? launch_bn_one<DT, B, kNoiseConst, kProBNReluCl>(x, y, packed, scale, mn, n, l2, seed, offset, bn, st) \
+                       : launch_bn_one<DT, B, kNoiseHash, kProBNReluCl>(x, y, packed, scale, mn, n, l2, seed, offset, bn, st); \
+    return nearest ? launch_bn_one<DT, B, kNoiseConst, kProBNcl>(x, y, packed, scale, mn, n, l2, seed, offset, bn, st) \
+                   : launch_bn_one<DT, B, kNoiseHash, kProBNcl>(x, y, packed, scale, mn, n, l2, seed, offset, bn, st)
     switch (bits) {
         case 1: ACT_BN_CASE(1);
         case 2: ACT_BN_CASE(2);

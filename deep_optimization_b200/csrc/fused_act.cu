@@ -321,12 +321,73 @@ bn_bwd_dx_kernel(const uint8_t* __restrict__ packed, const float* __restrict__ s
     }
 }
 
+// The same for the channel-minor layout (HW = 1: dy is [rows, C], C a multiple of 8): the
+// eight elements of a piece belong to channels c..c+7 with c = (8 p) % C.  When the grid
+// stride is a multiple of C (every power-of-two C up to 2048 pieces' worth) a thread meets
+// the same eight channels in every step and keeps their constants in registers.
+template <int DT, int BITS>
+__global__ void __launch_bounds__(kFusedThreads)
+bn_bwd_dx_cl_kernel(const uint8_t* __restrict__ packed, const float* __restrict__ scale,
+                    const float* __restrict__ mn, const uint8_t* __restrict__ dy, const uint8_t* __restrict__ mask,
+                    const float4* __restrict__ coef, uint8_t* __restrict__ dx, int64_t n_elems, int log2_gs, uint32_t C)
+{
+    const int64_t n_pieces = n_elems >> 3;
+    const int64_t stride = (int64_t)gridDim.x * kFusedThreads;
+    int64_t p = (int64_t)blockIdx.x * kFusedThreads + threadIdx.x;
+    if (p >= n_pieces) return;
+    uint32_t c = (uint32_t)((uint64_t)(p * 8) % C);
+    const uint32_t dc = (uint32_t)((uint64_t)(stride * 8) % C);
+    float4 k[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) k[i] = __ldg(coef + c + i);
+    for (; p < n_pieces; p += stride) {
+        const Vec8<DT> v = load8<DT>(dy, p * 8);
+        const uint2 w = load_codes8<BITS>(packed, p);
+        const int64_t g = (p * 8) >> log2_gs;
+        const float s = __ldg(scale + g), m = __ldg(mn + g);
+        float f[8];
+        to_float8<DT>(v, f);
+        if (mask) {
+            const uint32_t keep = __ldg(mask + p);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) f[i] = ((keep >> i) & 1u) ? f[i] : 0.0f;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            f[i] = __fmaf_rn(-k[i].z, decode_at<BITS>(w, i, s, m), __fmaf_rn(k[i].x, f[i], -k[i].y));
+        store8<DT>(dx, p * 8, f);
+        if (dc != 0) {
+            c += dc;
+            if (c >= C) c -= C;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) k[i] = __ldg(coef + c + i);
+        }
+    }
+}
+
 template <int DT>
 static cudaError_t launch_bn_bwd_dx(int bits, const uint8_t* p, const float* s, const float* m,
                                     const uint8_t* dy, const uint8_t* mask, const float4* coef, uint8_t* dx, int64_t n,
                                     int log2_gs, uint32_t hw, uint32_t C, cudaStream_t st)
 {
     const int grid = stream_grid_for(((n >> 3) + kFusedThreads - 1) / kFusedThreads, 6);
+    if (hw == 1) {
+        // the constants held in registers cost occupancy: the grid is what is resident at once
+        static int per_sm = 0;
+        if (per_sm == 0) {
+            int nb = 0;
+            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, bn_bwd_dx_cl_kernel<DT, 2>, kFusedThreads, 0) != cudaSuccess || nb < 1) nb = 4;
+            per_sm = nb;
+        }
+        const int grid = stream_grid_for(((n >> 3) + kFusedThreads - 1) / kFusedThreads, per_sm);
+        switch (bits) {
+            case 1: bn_bwd_dx_cl_kernel<DT, 1><<<grid, kFusedThreads, 0, st>>>(p, s, m, dy, mask, coef, dx, n, log2_gs, C); break;
+            case 2: bn_bwd_dx_cl_kernel<DT, 2><<<grid, kFusedThreads, 0, st>>>(p, s, m, dy, mask, coef, dx, n, log2_gs, C); break;
+            case 4: bn_bwd_dx_cl_kernel<DT, 4><<<grid, kFusedThreads, 0, st>>>(p, s, m, dy, mask, coef, dx, n, log2_gs, C); break;
+            default: bn_bwd_dx_cl_kernel<DT, 8><<<grid, kFusedThreads, 0, st>>>(p, s, m, dy, mask, coef, dx, n, log2_gs, C); break;
+        }
+        return cudaGetLastError();
+    }
     switch (bits) {
         case 1: bn_bwd_dx_kernel<DT, 1><<<grid, kFusedThreads, 0, st>>>(p, s, m, dy, mask, coef, dx, n, log2_gs, hw, C); break;
         case 2: bn_bwd_dx_kernel<DT, 2><<<grid, kFusedThreads, 0, st>>>(p, s, m, dy, mask, coef, dx, n, log2_gs, hw, C); break;
@@ -347,7 +408,8 @@ static int bn_bwd_dx_common(const void* packed, const float* scale, const float*
     if (bits != 1 && bits != 2 && bits != 4 && bits != 8) return ACT_ERR_BITS;
     if (group_size < 32 || group_size > 1024 || (group_size & (group_size - 1))) return ACT_ERR_GROUP;
     if (n_batch < 0 || channels <= 0 || hw <= 0) return ACT_ERR_SIZE;
-    if ((hw & 3) || hw >= (1ll << 31)) return ACT_ERR_UNSUPPORTED;
+    // hw == 1: channel-minor layout, pieces of eight consecutive channels
+    if (hw == 1 ? (channels & 7) != 0 : ((hw & 3) || hw >= (1ll << 31))) return ACT_ERR_UNSUPPORTED;
     const int64_t n = n_batch * channels * hw;
     if (n > (INT64_MAX >> 4) || n % group_size) return ACT_ERR_SIZE;
     if (n == 0) return ACT_OK;

@@ -24,6 +24,12 @@ from .tensor_act_reshape_utils import (
 _TILE = {64: 8, 256: 16, 1024: 32}
 
 
+class ChannelsLastShape(tuple):
+    """The `ori_shape` entry of q_meta for an activation that was stored channels-last: the
+    logical [N, C, H, W] shape, tagged so that `dequantize` rebuilds the same memory format.
+    Such a tensor is grouped flat over its NHWC memory order (no conversion copy either way)."""
+
+
 def _tiled_in_place(input, group_size, act_padding, pack_only, avg_alam):
     """Spatial grouping that the tiled kernels read and write in place (no permute copy): the
     spatial branch of the reshape helpers, in the two fixed-point modes."""
@@ -34,6 +40,12 @@ def _tiled_in_place(input, group_size, act_padding, pack_only, avg_alam):
 
 
 def quantize(input, bits, pack_only, group_size, act_padding, N, avg_alam, alam_bits, clamp, clamp_alpha):
+    if codec._channels_last(input):
+        # [N, H*W*C] view of the memory as it lies; flat groups; the shape entry records the format
+        n = input.shape[0]
+        tensors, q_meta = quantize(input.permute(0, 2, 3, 1).reshape(n, -1), bits, pack_only, group_size,
+                                   act_padding, N, avg_alam, alam_bits, clamp, clamp_alpha)
+        return tensors, q_meta[:-1] + (ChannelsLastShape(input.shape),)
     if _tiled_in_place(input, group_size, act_padding, pack_only, avg_alam):
         t = _TILE[group_size]
         n, C, H, W = input.shape
@@ -69,6 +81,10 @@ def dequantize(quantized_tensor, quantized_meta):
     q_input, q_scale, ema_mn = quantized_tensor
     (q_bits, pack_only, group_size, act_padding, N, G, new_H, new_W, pad_elig, reshape_elig,
      channel_mean, avg_alam, alam_bits, input_shape) = quantized_meta
+    if isinstance(input_shape, ChannelsLastShape):
+        n, C, H, W = input_shape
+        flat = dequantize(quantized_tensor, tuple(quantized_meta[:-1]) + (torch.Size((n, H * W * C)),))
+        return flat.view(n, H, W, C).permute(0, 3, 1, 2)
     if (not pack_only and reshape_elig and not pad_elig and not avg_alam and group_size in _TILE
             and q_input.is_cuda and len(input_shape) == 4):
         return codec.dequant_unpack_tiles(q_input, q_scale.reshape(-1), ema_mn.reshape(-1), q_bits,

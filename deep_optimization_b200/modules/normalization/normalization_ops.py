@@ -65,7 +65,9 @@ class _DOBatchNorm(Function):
                 and codec.bn_fused_supported(input, m["group_size"])):
             # fused path: one statistics pass, then normalise + affine + x_hat codec in one kernel
             # (normalization_ops.py:71-98 of the reference: bn_fwd_reduce + bn_fwd_norm_quant_pack_fused)
-            x = input.contiguous()
+            # a channels-last activation is normalised and grouped as it lies in memory
+            ctx.channels_last = codec._channels_last(input) and C % 8 == 0
+            x = input if ctx.channels_last else input.contiguous()
             f32 = lambda t: None if t is None else (t if t.dtype == torch.float32 else t.float())
             rm, rv = f32(running_mean), f32(running_var)
             params = codec.bn_stats(x, eps, f32(weight), f32(bias), rm, rv, exponential_average_factor or 0.0)
@@ -129,7 +131,7 @@ class _DOBatchNorm(Function):
         if ctx.fused is not None:
             # two kernels on the packed x_hat: per-channel sums, then dx (normalization_ops.py:145-163)
             bits, gs, count = ctx.fused
-            dyc = dy.contiguous()
+            dyc = dy.contiguous(memory_format=torch.channels_last) if ctx.channels_last else dy.contiguous()
             dgamma, dbeta = codec.bn_bwd_reduce(q_out, q_scale, q_min, dyc, bits, gs, mask=mask)
             # `invstd` is the whole [C, 4] parameter table on this path
             coef = codec.bn_bwd_coef(dgamma._base if dgamma._base is not None else (dgamma, dbeta), invstd, count)

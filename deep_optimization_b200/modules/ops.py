@@ -15,14 +15,9 @@ import torch
 import torch.nn.functional as F
 from torch.amp import custom_bwd, custom_fwd
 from torch.autograd import Function
-from torch.nn.grad import (conv1d_input, conv1d_weight, conv2d_input, conv2d_weight,
-                           conv3d_input, conv3d_weight)
 from torch.nn.modules.utils import _pair, _single, _triple
 
 from .module_utils import unified_dequantize, unified_quantize
-
-_CONV_GRADS = {1: (conv1d_input, conv1d_weight), 2: (conv2d_input, conv2d_weight),
-               3: (conv3d_input, conv3d_weight)}
 
 
 class _DOConvnd(Function):
@@ -67,14 +62,21 @@ class _DOConvnd(Function):
         x = unified_dequantize((q_out, q_scale, q_min), q_meta, input_l)
         x = x.to(weight_compute.dtype)
         dy = dy.to(weight_compute.dtype)
-        grad_input, grad_weight = _CONV_GRADS[dim]
+        # one backward call on the real input and weight: the library picks its memory format
+        # from them (the torch.nn.grad helpers hand it a strideless placeholder, which turns a
+        # channels-last gradient back into NCHW with a copy)
+        need_dx, need_dw = bool(ctx.needs_input_grad[0]), bool(ctx.needs_input_grad[1])
         dx = dw = None
-        if ctx.needs_input_grad[0]:
-            dx = grad_input(x.shape, weight_compute, dy, stride=stride, padding=padding,
-                            dilation=dilation, groups=groups)
-        if ctx.needs_input_grad[1]:
-            dw = grad_weight(x, weight_compute.shape, dy, stride=stride, padding=padding,
-                             dilation=dilation, groups=groups).to(weight_master.dtype)
+        if need_dx or need_dw:
+            dx, dw, _ = torch.ops.aten.convolution_backward(
+                dy, x, weight_compute, None, list(stride), list(padding), list(dilation), False,
+                [0] * dim, groups, [need_dx, need_dw, False])
+            if need_dw:
+                dw = dw.to(weight_master.dtype)
+            else:
+                dw = None
+            if not need_dx:
+                dx = None
         return dx, dw, None, None, None, None, None, None, None, None, None
 
 

@@ -181,6 +181,13 @@ ACT_API int act_mul_dequant_unpack(const void* packed, const float* scale, const
  *   act_bn_bwd_coef: that table from the sums of act_bn_bwd_reduce and the params of
  *       act_bn_stats: k1 = weight*invstd, k2 = k1*sum(dy)/count, k3 = k1*sum(dy*x_hat)/count
  *       (count = N*HW); one small launch instead of a chain of elementwise operators.
+ * Channel-minor layout: hw = 1 means x is [n_batch, C] with the channel running fastest, which
+ * is what a channels-last [N, C, H, W] activation is in memory (pass n_batch = N*H*W).  All of
+ * the entry points above and the three BN+ReLU ones below take it, with C a multiple of 8 (and
+ * C <= 4096 in the forward kernel, which keeps the parameter table in shared memory); groups,
+ * mask bits and hash counters then follow that memory order, and the arithmetic per element is
+ * unchanged.  (The reference's kernels address NCHW only; cuDNN's bf16 convolutions work in
+ * NHWC, so this layout removes their layout conversions around every batch norm.)
  */
 ACT_API int act_bn_fwd_norm_quant_pack(const void* x, int dtype, int64_t n_batch, int channels, int64_t hw,
                                const float* params, int group_size, int bits, uint64_t seed,

@@ -241,3 +241,159 @@ def test_bn_bwd_coef(cuda_device):
     assert torch.equal(coef[:, 1], k1 * sums[C:] * inv)
     assert torch.equal(coef[:, 2], k1 * sums[:C] * inv)
     assert (coef[:, 3] == 0).all()
+
+
+# ------------------------------------------------------------------ channels-last (channel-minor) batch norm
+
+_CL_SHAPES = [(8, 16, 32, 32), (6, 24, 14, 14), (4, 64, 56, 56), (3, 136, 4, 4), (2, 2048, 7, 7), (5, 8, 3, 5)]
+
+
+def _cl_group(numel):
+    for gs in (256, 128, 64, 32):
+        if numel % gs == 0:
+            return gs
+    return None
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", (torch.float32, torch.bfloat16), ids=("f32", "bf16"))
+@pytest.mark.parametrize("shape", _CL_SHAPES)
+@pytest.mark.parametrize("relu", (False, True))
+def test_bn_fused_forward_channels_last(oracle, cuda_device, dtype, shape, relu):
+    """A channels-last activation is normalised and grouped as it lies in memory ([N*H*W, C]):
+    codes, scale and min bit-exact with the oracle applied to the fp32 x_hat in NHWC order, y
+    exact, y channels-last, mask = y > 0 in memory order."""
+    from deep_optimization_b200 import codec
+    g = torch.Generator().manual_seed(31)
+    gs = _cl_group(int(np.prod(shape)))
+    if gs is None:
+        pytest.skip("no group size divides this shape")
+    x = (torch.randn(shape, generator=g) * 2 + 0.5).to(dtype).to(cuda_device).contiguous(memory_format=torch.channels_last)
+    C = shape[1]
+    mean = torch.randn(C, generator=g).to(cuda_device)
+    invstd = (torch.rand(C, generator=g) + 0.5).to(cuda_device)
+    w = torch.randn(C, generator=g).to(cuda_device)
+    b = torch.randn(C, generator=g).to(cuda_device)
+    assert codec.bn_fused_supported(x, gs)
+    out = codec.bn_fwd_norm_quant_pack(x, mean, invstd, w, b, 2, gs, seed=3, offset=2, relu=relu)
+    y, packed, scale, mn = out[:4]
+    assert y.is_contiguous(memory_format=torch.channels_last) and y.shape == x.shape
+    view = [1, C, 1, 1]
+    x_hat = (x.float() - mean.view(view)) * invstd.view(view)
+    nhwc = x_hat.permute(0, 2, 3, 1).contiguous()
+    want = oracle.quant_pack(nhwc.cpu().numpy().reshape(-1), gs, 2, seed=3, offset=2)
+    assert np.array_equal(packed.cpu().numpy().view(np.uint32).reshape(-1), np.asarray(want[0]).reshape(-1))
+    assert np.array_equal(scale.cpu().numpy().view(np.uint32), want[1].view(np.uint32).reshape(-1))
+    assert np.array_equal(mn.cpu().numpy().view(np.uint32), want[2].view(np.uint32).reshape(-1))
+    y_ref = (x_hat * w.view(view) + b.view(view))
+    if relu:
+        keep = y_ref > 0
+        y_ref = torch.where(keep, y_ref, torch.zeros_like(y_ref))
+        bits = np.unpackbits(out[4].cpu().numpy(), bitorder="little")[: x.numel()]
+        assert np.array_equal(bits.astype(bool), keep.permute(0, 2, 3, 1).reshape(-1).cpu().numpy())
+    assert torch.equal(y, y_ref.to(dtype))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", (torch.float32, torch.bfloat16, torch.float16), ids=("f32", "bf16", "f16"))
+@pytest.mark.parametrize("shape", _CL_SHAPES + [(64, 64, 56, 56)])
+def test_bn_stats_channels_last(cuda_device, dtype, shape):
+    """Statistics of a channels-last tensor equal those of the same values stored NCHW (to the
+    tolerance of test_bn_stats against float64), run-to-run identical."""
+    from deep_optimization_b200 import codec
+    g = torch.Generator().manual_seed(8)
+    C = shape[1]
+    offset = torch.linspace(-50, 50, C).view(1, C, 1, 1)
+    x = (torch.randn(shape, generator=g) * 1.5 + offset).to(dtype).to(cuda_device).contiguous(memory_format=torch.channels_last)
+    rm = torch.zeros(C, device=cuda_device)
+    rv = torch.ones(C, device=cuda_device)
+    eps = 1e-5
+    params = codec.bn_stats(x, eps, None, None, rm, rv, 0.1)
+    xd = x.double()
+    mean = xd.mean((0, 2, 3))
+    var = xd.var((0, 2, 3), unbiased=False)
+    M = x.numel() // C
+    assert torch.allclose(params[:, 0].double(), mean, rtol=2e-5, atol=2e-5)
+    assert torch.allclose(params[:, 1].double(), 1.0 / torch.sqrt(var + eps), rtol=2e-5)
+    assert torch.allclose(rm.double(), 0.1 * mean, rtol=1e-5, atol=1e-5)
+    assert torch.allclose(rv.double(), 0.9 + 0.1 * var * M / max(M - 1, 1), rtol=1e-4)
+    assert torch.equal(params, codec.bn_stats(x, eps))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", (torch.float32, torch.bfloat16), ids=("f32", "bf16"))
+@pytest.mark.parametrize("shape", _CL_SHAPES)
+@pytest.mark.parametrize("bits", (2, 8))
+@pytest.mark.parametrize("masked", (False, True))
+def test_bn_fused_backward_channels_last(cuda_device, dtype, shape, bits, masked):
+    """Channel-minor sums and dx against the formulas on the decoded tensor (tolerances of
+    test_bn_fused_backward)."""
+    from deep_optimization_b200 import codec
+    g = torch.Generator().manual_seed(6)
+    gs = 32
+    if int(np.prod(shape)) % gs:
+        pytest.skip("numel not a multiple of 32")
+    N, C, H, W = shape
+    xh_nhwc = torch.randn((N, H, W, C), generator=g).to(cuda_device)
+    dy = torch.randn(shape, generator=g).to(dtype).to(cuda_device).contiguous(memory_format=torch.channels_last)
+    packed, scale, mn = codec.quant_pack(xh_nhwc, bits, gs, seed=1, offset=0)
+    dec = codec.dequant_unpack(packed, scale, mn, bits, gs, out_dtype=torch.float32).view(N, H, W, C).permute(0, 3, 1, 2)
+    mask = keep = None
+    dyf = dy.float()
+    if masked:
+        keep = torch.rand(shape, generator=g).to(cuda_device) > 0.4
+        flat = keep.permute(0, 2, 3, 1).reshape(-1).cpu().numpy()
+        mask = torch.from_numpy(np.packbits(flat, bitorder="little")).to(cuda_device)
+        dyf = torch.where(keep, dyf, torch.zeros_like(dyf))
+    s1, s2 = codec.bn_bwd_reduce(packed, scale, mn, dy, bits, gs, mask=mask)
+    dims = [0, 2, 3]
+    r1, r2 = (dyf * dec).sum(dims), dyf.sum(dims)
+    assert torch.allclose(s1, r1, rtol=1e-4, atol=1e-3 * r1.abs().max().item())
+    assert torch.allclose(s2, r2, rtol=1e-4, atol=1e-3 * r2.abs().max().item() + 1e-3)
+    k1, k2, k3 = (torch.randn(C, generator=g).to(cuda_device) for _ in range(3))
+    dx = codec.bn_bwd_dx(packed, scale, mn, dy, k1, k2, k3, bits, gs, mask=mask)
+    assert dx.is_contiguous(memory_format=torch.channels_last)
+    view = [1, C, 1, 1]
+    want = k1.view(view) * dyf - k2.view(view) - k3.view(view) * dec
+    tol = 2.0 ** -7 if dtype == torch.bfloat16 else 1e-5
+    assert ((dx.float() - want).abs() <= tol * (1 + want.abs())).all()
+
+
+@pytest.mark.gpu
+def test_channels_last_modules_match_pytorch(cuda_device):
+    """conv -> BN(+ReLU) -> ReLU on a channels-last input through the DO* modules: outputs stay
+    channels-last, the forward equals PyTorch's to rounding, gradients agree within the 8-bit
+    codec's error, and the saved conv input is rebuilt channels-last."""
+    from deep_optimization_b200.layers import DOConv2d
+    from deep_optimization_b200.modules.activations.act_layers import DOReLU_Variance
+    from deep_optimization_b200.modules.module_utils import unified_dequantize, unified_quantize
+    from deep_optimization_b200.modules.normalization.normalization_layers import DOBatchNorm2d
+    torch.manual_seed(4)
+    entry = {"bits": 8, "pack_only": False, "group_size": 256, "act_padding": False, "N": 8,
+             "AVG_ALAM": False, "ALAM_BITS": 0, "DIVISION": None}
+    meta = {"c": dict(entry), "b": dict(entry), "r": dict(entry, bits=1, pack_only=True)}
+    x = torch.randn(8, 16, 16, 16, device=cuda_device).contiguous(memory_format=torch.channels_last)
+    q, q_meta, _ = unified_quantize(x, None, "c", meta, clamp=False, clamp_alpha=0.0)
+    back = unified_dequantize(q, q_meta, None)
+    assert back.shape == x.shape and back.is_contiguous(memory_format=torch.channels_last)
+    assert (back.float() - x).abs().max() < 0.05
+    bn = DOBatchNorm2d(16, target_name="b", meta=meta).to(cuda_device).train()
+    rb = torch.nn.BatchNorm2d(16).to(cuda_device).train()
+    relu = DOReLU_Variance(target_name="r", meta=meta).train()
+    conv = DOConv2d(16, 16, 3, padding=1, target_name="c", meta=meta).to(cuda_device).train()
+    rc = torch.nn.Conv2d(16, 16, 3, padding=1, bias=False).to(cuda_device)
+    conv = conv.to(memory_format=torch.channels_last)
+    rc = rc.to(memory_format=torch.channels_last)
+    with torch.no_grad():
+        rc.weight.copy_(conv.weight)
+    xr = x.detach().clone().requires_grad_()
+    xq = x.detach().clone().requires_grad_()
+    y = relu(bn(conv(xq)))
+    yr = torch.relu(rb(rc(xr)))
+    assert y.is_contiguous(memory_format=torch.channels_last)
+    assert torch.allclose(y, yr, atol=2e-3)
+    gy = torch.randn_like(y)
+    y.backward(gy); yr.backward(gy)
+    assert xq.grad.is_contiguous(memory_format=torch.channels_last)
+    assert (xq.grad - xr.grad).abs().max() < 0.05
+    assert torch.allclose(bn.bias.grad, rb.bias.grad, rtol=1e-4, atol=1e-3)
