@@ -253,25 +253,26 @@ def run_extras(dev):
     # 2 bits: algorithmic bytes = what each kernel must read and write once
     shp = (256, 64, 56, 56)
     n = shp[0] * shp[1] * shp[2] * shp[3]
-    xb = [torch.randn(shp, device=dev).to(torch.bfloat16) for _ in range(rot)]
-    dyb = [torch.randn(shp, device=dev).to(torch.bfloat16) for _ in range(2)]
-    w = torch.ones(shp[1], device=dev)
-    b = torch.zeros(shp[1], device=dev)
-    params = codec.bn_stats(xb[0], 1e-5, w, b)
-    _, pk, sc, mnn, mask = codec.bn_fwd_norm_quant_pack(xb[0], None, None, w, b, 2, 256, params=params, relu=True)
-    k1 = torch.ones(shp[1], device=dev)
-    t_stats = _time_launches(lambda i=0: codec.bn_stats(xb[i % rot], 1e-5, w, b), 40)
-    t_fwd = _time_launches(lambda i=0: codec.bn_fwd_norm_quant_pack(xb[i % rot], None, None, w, b, 2, 256,
-                                                                     params=params, relu=True), 40)
-    t_red = _time_launches(lambda i=0: codec.bn_bwd_reduce(pk, sc, mnn, dyb[i % 2], 2, 256, mask=mask), 40)
-    t_dx = _time_launches(lambda i=0: codec.bn_bwd_dx(pk, sc, mnn, dyb[i % 2], k1, k1, k1, 2, 256, mask=mask), 40)
-    meta_b = 8 * (n // 256)
-    by = {"stats": 2 * n, "norm_relu_quant_pack": 2 * n + 2 * n + n // 4 + n // 8 + meta_b,
-          "bwd_reduce": 2 * n + n // 4 + n // 8 + meta_b, "bwd_dx": 2 * n + n // 4 + n // 8 + meta_b + 2 * n}
-    out["bn_relu_fused_bf16_256x64x56x56_g256_b2"] = {
-        k: {"GBps": by[k] / t / 1e6, "frac": by[k] / t / 1e6 / peak, "ms_per_launch": t}
-        for k, t in (("stats", t_stats), ("norm_relu_quant_pack", t_fwd), ("bwd_reduce", t_red), ("bwd_dx", t_dx))}
-    del xb, dyb, pk, sc, mnn, mask
+    for tag, fmt in (("", torch.contiguous_format), ("_channels_last", torch.channels_last)):
+        xb = [torch.randn(shp, device=dev).to(torch.bfloat16).contiguous(memory_format=fmt) for _ in range(rot)]
+        dyb = [torch.randn(shp, device=dev).to(torch.bfloat16).contiguous(memory_format=fmt) for _ in range(2)]
+        w = torch.ones(shp[1], device=dev)
+        b = torch.zeros(shp[1], device=dev)
+        params = codec.bn_stats(xb[0], 1e-5, w, b)
+        _, pk, sc, mnn, mask = codec.bn_fwd_norm_quant_pack(xb[0], None, None, w, b, 2, 256, params=params, relu=True)
+        k1 = torch.ones(shp[1], device=dev)
+        t_stats = _time_launches(lambda i=0: codec.bn_stats(xb[i % rot], 1e-5, w, b), 40)
+        t_fwd = _time_launches(lambda i=0: codec.bn_fwd_norm_quant_pack(xb[i % rot], None, None, w, b, 2, 256,
+                                                                         params=params, relu=True), 40)
+        t_red = _time_launches(lambda i=0: codec.bn_bwd_reduce(pk, sc, mnn, dyb[i % 2], 2, 256, mask=mask), 40)
+        t_dx = _time_launches(lambda i=0: codec.bn_bwd_dx(pk, sc, mnn, dyb[i % 2], k1, k1, k1, 2, 256, mask=mask), 40)
+        meta_b = 8 * (n // 256)
+        by = {"stats": 2 * n, "norm_relu_quant_pack": 2 * n + 2 * n + n // 4 + n // 8 + meta_b,
+              "bwd_reduce": 2 * n + n // 4 + n // 8 + meta_b, "bwd_dx": 2 * n + n // 4 + n // 8 + meta_b + 2 * n}
+        out["bn_relu_fused_bf16_256x64x56x56_g256_b2" + tag] = {
+            k: {"GBps": by[k] / t / 1e6, "frac": by[k] / t / 1e6 / peak, "ms_per_launch": t}
+            for k, t in (("stats", t_stats), ("norm_relu_quant_pack", t_fwd), ("bwd_reduce", t_red), ("bwd_dx", t_dx))}
+        del xb, dyb, pk, sc, mnn, mask
     # fused activation kernels on the ViT MLP activation, bf16 [256,197,3072], group 128, 2 bits:
     # forward writes y and the packed derivative, backward multiplies dy by the decoded derivative;
     # ReLU on the conv activation keeps one mask bit per element (wrapper time included)

@@ -1,5 +1,6 @@
 """The kernel sequence of one fused BatchNorm+ReLU layer, forward and backward, on a random
-activation: `python -m deep_optimization_b200.bn_sequence N C H W [reps] [bits] [group]`.
+activation: `python -m deep_optimization_b200.bn_sequence N C H W [reps] [bits] [group] [cl]`
+(`cl`: the activation is stored channels-last and the kernels run channel-minor).
 
 A small driver for profilers (one process, a handful of launches): batch statistics,
 normalise + ReLU + codec, backward sums, backward constants, dx.
@@ -13,11 +14,13 @@ import torch
 from . import codec
 
 
-def run(shape, reps: int = 3, bits: int = 2, group: int = 256, dtype=torch.bfloat16) -> torch.Tensor:
+def run(shape, reps: int = 3, bits: int = 2, group: int = 256, dtype=torch.bfloat16,
+        channels_last: bool = False) -> torch.Tensor:
     dev = torch.device("cuda")
     N, C, H, W = shape
-    xs = [torch.randn(shape, device=dev).to(dtype) for _ in range(reps)]
-    dys = [torch.randn(shape, device=dev).to(dtype) for _ in range(reps)]
+    fmt = torch.channels_last if channels_last else torch.contiguous_format
+    xs = [torch.randn(shape, device=dev).to(dtype).contiguous(memory_format=fmt) for _ in range(reps)]
+    dys = [torch.randn(shape, device=dev).to(dtype).contiguous(memory_format=fmt) for _ in range(reps)]
     w, b = torch.ones(C, device=dev), torch.zeros(C, device=dev)
     dx = None
     for x, dy in zip(xs, dys):
@@ -32,8 +35,9 @@ def run(shape, reps: int = 3, bits: int = 2, group: int = 256, dtype=torch.bfloa
 
 
 if __name__ == "__main__":
-    a = [int(v) for v in sys.argv[1:]]
+    cl = "cl" in sys.argv[1:]
+    a = [int(v) for v in sys.argv[1:] if v != "cl"]
     if len(a) < 4:
         raise SystemExit(__doc__)
-    run(tuple(a[:4]), *(a[4:7]))
+    run(tuple(a[:4]), *(a[4:7]), channels_last=cl)
     print("ok")

@@ -340,28 +340,44 @@ bn_bwd_dx_cl_kernel(const uint8_t* __restrict__ packed, const float* __restrict_
     float4 k[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) k[i] = __ldg(coef + c + i);
-    for (; p < n_pieces; p += stride) {
-        const Vec8<DT> v = load8<DT>(dy, p * 8);
-        const uint2 w = load_codes8<BITS>(packed, p);
-        const int64_t g = (p * 8) >> log2_gs;
-        const float s = __ldg(scale + g), m = __ldg(mn + g);
+    auto finish = [&](int64_t q, const Vec8<DT>& v, uint2 w, float s, float m, uint32_t keep) {
         float f[8];
         to_float8<DT>(v, f);
         if (mask) {
-            const uint32_t keep = __ldg(mask + p);
 #pragma unroll
             for (int i = 0; i < 8; ++i) f[i] = ((keep >> i) & 1u) ? f[i] : 0.0f;
         }
 #pragma unroll
         for (int i = 0; i < 8; ++i)
             f[i] = __fmaf_rn(-k[i].z, decode_at<BITS>(w, i, s, m), __fmaf_rn(k[i].x, f[i], -k[i].y));
-        store8<DT>(dx, p * 8, f);
-        if (dc != 0) {
-            c += dc;
-            if (c >= C) c -= C;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) k[i] = __ldg(coef + c + i);
+        store8<DT>(dx, q * 8, f);
+    };
+    if (dc == 0) {
+        // two pieces per trip, both sets of loads issued before either is used
+        for (; p < n_pieces; p += 2 * stride) {
+            const int64_t p1 = p + stride;
+            const bool two = p1 < n_pieces;
+            const int64_t q1 = two ? p1 : p;
+            const Vec8<DT> v0 = load8<DT>(dy, p * 8), v1 = load8<DT>(dy, q1 * 8);
+            const uint2 w0 = load_codes8<BITS>(packed, p), w1 = load_codes8<BITS>(packed, q1);
+            const int64_t g0 = (p * 8) >> log2_gs, g1 = (q1 * 8) >> log2_gs;
+            const float s0 = __ldg(scale + g0), m0 = __ldg(mn + g0), s1 = __ldg(scale + g1), m1 = __ldg(mn + g1);
+            const uint32_t keep0 = mask ? __ldg(mask + p) : 0xFFu, keep1 = mask ? __ldg(mask + q1) : 0xFFu;
+            finish(p, v0, w0, s0, m0, keep0);
+            if (two) finish(p1, v1, w1, s1, m1, keep1);
         }
+        return;
+    }
+    for (; p < n_pieces; p += stride) {
+        const Vec8<DT> v = load8<DT>(dy, p * 8);
+        const uint2 w = load_codes8<BITS>(packed, p);
+        const int64_t g = (p * 8) >> log2_gs;
+        const float s = __ldg(scale + g), m = __ldg(mn + g);
+        finish(p, v, w, s, m, mask ? __ldg(mask + p) : 0xFFu);
+        c += dc;
+        if (c >= C) c -= C;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) k[i] = __ldg(coef + c + i);
     }
 }
 
