@@ -43,6 +43,7 @@ SIGNATURES = {
     "act_bn_bwd_coef": ([_vp, _vp, _i32, _f64, _vp, _vp], _i32),
     "act_bn_bwd_dx": ([_vp, _vp, _vp, _vp, _i32, _i64, _i32, _i64, _i32, _i32, _vp, _vp, _vp], _i32),
     "act_bn_relu_fwd_norm_quant_pack": ([_vp, _i32, _i64, _i32, _i64, _vp, _i32, _i32, _u64, _u64, _i32, _vp, _vp, _vp, _vp, _vp, _vp], _i32),
+    "act_bn_add_relu_fwd_norm_quant_pack": ([_vp, _vp, _i32, _i64, _i32, _i64, _vp, _i32, _i32, _u64, _u64, _i32, _vp, _vp, _vp, _vp, _vp, _vp], _i32),
     "act_bn_relu_bwd_reduce": ([_vp, _vp, _vp, _vp, _vp, _i32, _i64, _i32, _i64, _i32, _i32, _vp, _vp], _i32),
     "act_bn_relu_bwd_dx": ([_vp, _vp, _vp, _vp, _vp, _i32, _i64, _i32, _i64, _i32, _i32, _vp, _vp, _vp], _i32),
     "act_minmax": ([_vp, _i32, _i64, _i64, _vp, _vp, _vp], _i32),

@@ -52,7 +52,28 @@ def _no_alam(avg_alam: bool) -> None:
         raise NotImplementedError("AVG_ALAM sub-group averaging is not built in this backend")
 
 
-@torch.library.custom_op("act_lib::quant_pack_triton", mutates_args=(), device_types="cuda")
+IMPL = {}
+
+
+def _op(name):
+    """Registers `fn` as torch.ops.act_lib.<name> and keeps the plain function in IMPL."""
+    def deco(fn):
+        IMPL[name] = fn
+        return torch.library.custom_op(f"act_lib::{name}", fn, mutates_args=(), device_types="cuda")
+    return deco
+
+
+def op(name: str):
+    """The callable behind `torch.ops.act_lib.<name>` for this package's own autograd Functions:
+    the plain Python implementation in eager mode (a dispatcher round trip costs about 60 us
+    of host time per call, more than most of these kernels run), the registered operator while
+    torch.compile is tracing."""
+    if torch.compiler.is_compiling():
+        return getattr(torch.ops.act_lib, name)
+    return IMPL[name]
+
+
+@_op("quant_pack_triton")
 def quant_pack_triton(x: torch.Tensor, bits: int, group_size: int, avg_alam: bool, alam_bits: int,
                       clamp: bool, clamp_alpha: float, noise: Optional[torch.Tensor] = None,
                       seed: Optional[int] = None) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
@@ -81,7 +102,7 @@ def _(x, bits, group_size, avg_alam, alam_bits, clamp, clamp_alpha, noise=None, 
             x.new_empty((N, G), dtype=torch.float32), x.new_empty((N, G), dtype=torch.float32))
 
 
-@torch.library.custom_op("act_lib::dequant_unpack_triton", mutates_args=(), device_types="cuda")
+@_op("dequant_unpack_triton")
 def dequant_unpack_triton(packed: torch.Tensor, scale: torch.Tensor, xmin: torch.Tensor, bits: int,
                           group_size: int, avg_alam: bool, alam_bits: int) -> torch.Tensor:
     _no_alam(avg_alam)
@@ -96,7 +117,7 @@ def _(packed, scale, xmin, bits, group_size, avg_alam, alam_bits):
     return packed.new_empty((N, G, group_size), dtype=torch.bfloat16)
 
 
-@torch.library.custom_op("act_lib::pack_triton", mutates_args=(), device_types="cuda")
+@_op("pack_triton")
 def pack_triton(x: torch.Tensor, bits: int, group_size: int) -> torch.Tensor:
     if x.shape[-1] != group_size:
         raise ValueError("last dimension must equal group_size")
@@ -110,7 +131,7 @@ def _(x, bits, group_size):
     return x.new_empty((N * G, nwords), dtype=torch.int32)
 
 
-@torch.library.custom_op("act_lib::unpack_triton", mutates_args=(), device_types="cuda")
+@_op("unpack_triton")
 def unpack_triton(packed: torch.Tensor, bits: int, N: int, G: int, group_size: int) -> torch.Tensor:
     return codec.unpack_bits(packed, bits, N * G, group_size).view(N, G, group_size)
 
@@ -123,7 +144,7 @@ def _(packed, bits, N, G, group_size):
 # ---- fused activation operators (Activation_Compression/modules/activations/
 # kernel_registration.py:43-94, 148-237, 262-319): same names, schemas and return orders ----
 
-@torch.library.custom_op("act_lib::relu_fwd_fused_pack", mutates_args=(), device_types="cuda")
+@_op("relu_fwd_fused_pack")
 def relu_fwd_fused_pack(x: torch.Tensor, relu: bool, relu6: bool, bits: int,
                         group_size: int) -> Tuple[torch.Tensor, torch.Tensor, int, int]:
     if bits != 1:
@@ -141,7 +162,7 @@ def _(x, relu, relu6, bits, group_size):
     return torch.empty_like(x), x.new_empty((N * G, group_size // 32), dtype=torch.int32), N, G
 
 
-@torch.library.custom_op("act_lib::relu_bwd_fused_unpack", mutates_args=(), device_types="cuda")
+@_op("relu_bwd_fused_unpack")
 def relu_bwd_fused_unpack(packed: torch.Tensor, dy: torch.Tensor, bits: int, N: int, G: int,
                           group_size: int) -> torch.Tensor:
     return codec.relu_bwd_unpack(packed, dy)
@@ -168,7 +189,7 @@ def _fused_act_fake(x, bits, group_size):
             x.new_empty((N, G), dtype=torch.float32), x.new_empty((N, G), dtype=torch.float32), N, G)
 
 
-@torch.library.custom_op("act_lib::gelu_fwd_fused_quan_pack", mutates_args=(), device_types="cuda")
+@_op("gelu_fwd_fused_quan_pack")
 def gelu_fwd_fused_quan_pack(x: torch.Tensor, bits: int, group_size: int
                              ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, int, int]:
     return _fused_act_fwd(x, "gelu", bits, group_size)
@@ -179,7 +200,7 @@ def _(x, bits, group_size):
     return _fused_act_fake(x, bits, group_size)
 
 
-@torch.library.custom_op("act_lib::gelu_bwd_fused_dequan_unpack", mutates_args=(), device_types="cuda")
+@_op("gelu_bwd_fused_dequan_unpack")
 def gelu_bwd_fused_dequan_unpack(packed: torch.Tensor, dy: torch.Tensor, scale: torch.Tensor,
                                  min: torch.Tensor, bits: int, N: int, G: int, group_size: int) -> torch.Tensor:
     return codec.mul_dequant_unpack(packed, scale.reshape(-1), min.reshape(-1), dy, bits, group_size)
@@ -190,7 +211,7 @@ def _(packed, dy, scale, min, bits, N, G, group_size):
     return torch.empty_like(dy)
 
 
-@torch.library.custom_op("act_lib::silu_fwd_quan_pack", mutates_args=(), device_types="cuda")
+@_op("silu_fwd_quan_pack")
 def silu_fwd_quan_pack(input: torch.Tensor, bits: int, group_size: int, pack_only: bool, avg_alam: bool,
                        alam_bits: int) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, int,
                                                 int, int, int, bool, bool]:
@@ -204,7 +225,7 @@ def _(input, bits, group_size, pack_only, avg_alam, alam_bits):
     return _fused_act_fake(input, bits, group_size) + (0, 0, False, False)
 
 
-@torch.library.custom_op("act_lib::silu_bwd_fused_dequan_unpack", mutates_args=(), device_types="cuda")
+@_op("silu_bwd_fused_dequan_unpack")
 def silu_bwd_fused_dequan_unpack(act_packed: torch.Tensor, dy: torch.Tensor, scale: torch.Tensor,
                                  min: torch.Tensor, bits: int, N: int, G: int, group_size: int,
                                  pack_only: bool, new_H: int, new_W: int, spatical_padding_eligibility: bool,

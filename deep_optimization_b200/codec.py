@@ -7,6 +7,7 @@ Activation_Compression/act_triton_kernel.py:336-433 with the grouped layout
 """
 from __future__ import annotations
 
+import contextlib
 from typing import Optional, Tuple
 
 import torch
@@ -42,7 +43,18 @@ def _require_cuda(t: torch.Tensor, name: str) -> None:
 
 
 def _stream_ptr(t: torch.Tensor) -> int:
-    return torch.cuda.current_stream(t.device).cuda_stream
+    """Raw handle of PyTorch's current stream on t's device (no Stream object is built)."""
+    return torch._C._cuda_getCurrentRawStream(t.device.index)
+
+
+_NO_SWITCH = contextlib.nullcontext()
+
+
+def _device_of(t: torch.Tensor):
+    """Context that makes t's device current for the launch; free when it already is."""
+    if t.device.index == torch.cuda.current_device():
+        return _NO_SWITCH
+    return torch.cuda.device(t.device)
 
 
 def quant_pack(x: torch.Tensor, bits: int, group_size: int, noise: Optional[torch.Tensor] = None,
@@ -82,7 +94,7 @@ def quant_pack(x: torch.Tensor, bits: int, group_size: int, noise: Optional[torc
     if offset is None:
         offset = _next_offset
         _next_offset += 1
-    with torch.cuda.device(x.device):
+    with _device_of(x):
         rc = _lib.load().act_quant_pack(
             x.data_ptr(), _DTYPES[x.dtype], ng, group_size, bits,
             noise.data_ptr() if noise is not None else None,
@@ -108,7 +120,7 @@ def dequant_unpack(packed: torch.Tensor, scale: torch.Tensor, mn: torch.Tensor, 
         y = out
     else:
         y = torch.empty((ng, group_size), dtype=out_dtype, device=packed.device)
-    with torch.cuda.device(packed.device):
+    with _device_of(packed):
         rc = _lib.load().act_dequant_unpack(packed.data_ptr(), scale.data_ptr(), mn.data_ptr(), ng,
                                             group_size, bits, _DTYPES[out_dtype], y.data_ptr(),
                                             _stream_ptr(packed))
@@ -142,7 +154,7 @@ def quant_pack_tiles(x: torch.Tensor, bits: int, tile: int, seed: Optional[int] 
     if offset is None:
         offset = _next_offset
         _next_offset += 1
-    with torch.cuda.device(x.device):
+    with _device_of(x):
         rc = _lib.load().act_quant_pack_tiles(x.data_ptr(), _DTYPES[x.dtype], N * C, H, W, tile, bits,
                                               seed & 0xFFFFFFFFFFFFFFFF, offset & 0xFFFFFFFFFFFFFFFF, flags,
                                               packed.data_ptr(), scale.data_ptr(), mn.data_ptr(), _stream_ptr(x))
@@ -155,7 +167,7 @@ def dequant_unpack_tiles(packed: torch.Tensor, scale: torch.Tensor, mn: torch.Te
     """Inverse of quant_pack_tiles: the [N, C, H, W] tensor written in place (no permute back)."""
     N, C, H, W = shape
     y = torch.empty((N, C, H, W), dtype=out_dtype, device=packed.device)
-    with torch.cuda.device(packed.device):
+    with _device_of(packed):
         rc = _lib.load().act_dequant_unpack_tiles(packed.data_ptr(), scale.data_ptr(), mn.data_ptr(), N * C, H, W,
                                                   tile, bits, _DTYPES[out_dtype], y.data_ptr(), _stream_ptr(packed))
     _lib.check(rc, "act_dequant_unpack_tiles")
@@ -169,7 +181,7 @@ def pack_bits(x: torch.Tensor, bits: int, group_size: int) -> torch.Tensor:
     x = x.to(torch.int8).contiguous()
     ng = x.numel() // group_size
     packed = torch.empty((ng, nwords), dtype=torch.int32, device=x.device)
-    with torch.cuda.device(x.device):
+    with _device_of(x):
         rc = _lib.load().act_pack_bits(x.data_ptr(), ng, group_size, bits, packed.data_ptr(),
                                        _stream_ptr(x))
     _lib.check(rc, "act_pack_bits")
@@ -181,7 +193,7 @@ def unpack_bits(packed: torch.Tensor, bits: int, n_groups: int, group_size: int)
     _require_cuda(packed, "packed")
     packed = packed.contiguous()
     y = torch.empty((n_groups, group_size), dtype=torch.int8, device=packed.device)
-    with torch.cuda.device(packed.device):
+    with _device_of(packed):
         rc = _lib.load().act_unpack_bits(packed.data_ptr(), n_groups, group_size, bits,
                                          y.data_ptr(), _stream_ptr(packed))
     _lib.check(rc, "act_unpack_bits")
@@ -197,7 +209,7 @@ def minmax(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     rows = x.numel() // cols
     mn = torch.empty(x.shape[:-1], dtype=torch.float32, device=x.device)
     mx = torch.empty(x.shape[:-1], dtype=torch.float32, device=x.device)
-    with torch.cuda.device(x.device):
+    with _device_of(x):
         rc = _lib.load().act_minmax(x.data_ptr(), _DTYPES[x.dtype], rows, cols, mn.data_ptr(),
                                     mx.data_ptr(), _stream_ptr(x))
     _lib.check(rc, "act_minmax")
@@ -228,7 +240,7 @@ def relu_fwd_pack(x: torch.Tensor, relu6: bool = False) -> Tuple[torch.Tensor, t
         raise ValueError("numel must be a multiple of 32")
     y = torch.empty_like(x)
     bits = torch.empty((x.numel() // 32,), dtype=torch.int32, device=x.device)
-    with torch.cuda.device(x.device):
+    with _device_of(x):
         rc = _lib.load().act_relu_fwd_pack(x.data_ptr(), _DTYPES[x.dtype], x.numel(), int(relu6),
                                            y.data_ptr(), bits.data_ptr(), _stream_ptr(x))
     _lib.check(rc, "act_relu_fwd_pack")
@@ -244,7 +256,7 @@ def relu_bwd_unpack(mask_bits: torch.Tensor, dy: torch.Tensor, channels_last: bo
     else:
         dy = dy.contiguous()
     dx = torch.empty_like(dy)
-    with torch.cuda.device(dy.device):
+    with _device_of(dy):
         rc = _lib.load().act_relu_bwd_unpack(mask_bits.data_ptr(), dy.data_ptr(), _DTYPES[dy.dtype],
                                              dy.numel(), dx.data_ptr(), _stream_ptr(dy))
     _lib.check(rc, "act_relu_bwd_unpack")
@@ -271,7 +283,7 @@ def activation_fwd_quant_pack(x: torch.Tensor, kind: str, bits: int, group_size:
         offset = _next_offset
         _next_offset += 1
     k = {"gelu": _lib.ACT_KIND_GELU, "silu": _lib.ACT_KIND_SILU}[kind]
-    with torch.cuda.device(x.device):
+    with _device_of(x):
         rc = _lib.load().act_activation_fwd_quant_pack(
             x.data_ptr(), _DTYPES[x.dtype], k, ng, group_size, bits, seed & 0xFFFFFFFFFFFFFFFF,
             offset & 0xFFFFFFFFFFFFFFFF, flags, y.data_ptr(), packed.data_ptr(), scale.data_ptr(),
@@ -287,7 +299,7 @@ def mul_dequant_unpack(packed: torch.Tensor, scale: torch.Tensor, mn: torch.Tens
     _require_cuda(dy, "dy")
     dy = dy.contiguous()
     dx = torch.empty_like(dy)
-    with torch.cuda.device(dy.device):
+    with _device_of(dy):
         rc = _lib.load().act_mul_dequant_unpack(packed.data_ptr(), scale.data_ptr(), mn.data_ptr(),
                                                 dy.data_ptr(), _DTYPES[dy.dtype], dy.numel() // group_size,
                                                 group_size, bits, dx.data_ptr(), _stream_ptr(dy))
@@ -347,7 +359,7 @@ def bn_stats(x: torch.Tensor, eps: float, weight: Optional[torch.Tensor] = None,
     ws_bytes = int(lib.act_bn_stats_workspace(N, C))
     ws = torch.empty((max(ws_bytes, 4) // 4,), dtype=torch.float32, device=x.device)
     ptr = lambda t: None if t is None else t.data_ptr()
-    with torch.cuda.device(x.device):
+    with _device_of(x):
         rc = lib.act_bn_stats(x.data_ptr(), _DTYPES[x.dtype], N, C, hw, float(eps), ptr(weight), ptr(bias),
                               ptr(running_mean), ptr(running_var), float(momentum), params.data_ptr(),
                               ws.data_ptr(), ws_bytes, _stream_ptr(x))
@@ -358,10 +370,12 @@ def bn_stats(x: torch.Tensor, eps: float, weight: Optional[torch.Tensor] = None,
 def bn_fwd_norm_quant_pack(x: torch.Tensor, mean: Optional[torch.Tensor], invstd: Optional[torch.Tensor],
                            weight: Optional[torch.Tensor], bias: Optional[torch.Tensor], bits: int,
                            group_size: int, seed: Optional[int] = None, offset: Optional[int] = None,
-                           flags: int = 0, params: Optional[torch.Tensor] = None, relu: bool = False):
+                           flags: int = 0, params: Optional[torch.Tensor] = None, relu: bool = False,
+                           residual: Optional[torch.Tensor] = None):
     """y = (x - mean) * invstd * weight + bias and the packed x_hat: (y, packed, scale, min).
     `params` is bn_stats' table; without it the table is built from mean, invstd, weight, bias.
-    relu=True also applies y = max(y, 0) and returns the 1-bit ReLU mask as a fifth value."""
+    relu=True also applies y = max(y, 0) and returns the 1-bit ReLU mask as a fifth value;
+    with `residual` (x's shape, type and memory format) y = max(y + residual, 0)."""
     global _next_offset
     _, nwords, _ = _bits_consts(bits, group_size)
     x, N, C, hw = _bn_layout(x)
@@ -379,16 +393,31 @@ def bn_fwd_norm_quant_pack(x: torch.Tensor, mean: Optional[torch.Tensor], invstd
     if offset is None:
         offset = _next_offset
         _next_offset += 1
+    if residual is not None:
+        if not relu:
+            raise ValueError("the residual add is fused together with the ReLU only")
+        if residual.shape != x.shape or residual.dtype != x.dtype:
+            raise ValueError("residual must have x's shape and type")
+        residual = residual.contiguous(memory_format=torch.channels_last) if hw == 1 and _channels_last(x) \
+            else residual.contiguous()
+        mask = torch.empty((x.numel() // 8,), dtype=torch.uint8, device=x.device)
+        with _device_of(x):
+            rc = _lib.load().act_bn_add_relu_fwd_norm_quant_pack(
+                x.data_ptr(), residual.data_ptr(), _DTYPES[x.dtype], N, C, hw, params.data_ptr(), group_size, bits,
+                seed & 0xFFFFFFFFFFFFFFFF, offset & 0xFFFFFFFFFFFFFFFF, flags, y.data_ptr(), packed.data_ptr(),
+                scale.data_ptr(), mn.data_ptr(), mask.data_ptr(), _stream_ptr(x))
+        _lib.check(rc, "act_bn_add_relu_fwd_norm_quant_pack")
+        return y, packed, scale, mn, mask
     if relu:
         mask = torch.empty((x.numel() // 8,), dtype=torch.uint8, device=x.device)
-        with torch.cuda.device(x.device):
+        with _device_of(x):
             rc = _lib.load().act_bn_relu_fwd_norm_quant_pack(
                 x.data_ptr(), _DTYPES[x.dtype], N, C, hw, params.data_ptr(), group_size, bits,
                 seed & 0xFFFFFFFFFFFFFFFF, offset & 0xFFFFFFFFFFFFFFFF, flags, y.data_ptr(), packed.data_ptr(),
                 scale.data_ptr(), mn.data_ptr(), mask.data_ptr(), _stream_ptr(x))
         _lib.check(rc, "act_bn_relu_fwd_norm_quant_pack")
         return y, packed, scale, mn, mask
-    with torch.cuda.device(x.device):
+    with _device_of(x):
         rc = _lib.load().act_bn_fwd_norm_quant_pack(
             x.data_ptr(), _DTYPES[x.dtype], N, C, hw, params.data_ptr(), group_size, bits,
             seed & 0xFFFFFFFFFFFFFFFF, offset & 0xFFFFFFFFFFFFFFFF, flags, y.data_ptr(), packed.data_ptr(),
@@ -404,7 +433,7 @@ def bn_bwd_reduce(packed: torch.Tensor, scale: torch.Tensor, mn: torch.Tensor, d
     dy, N, C, hw = _bn_layout(dy)
     sums = torch.zeros(2 * C, dtype=torch.float32, device=dy.device)
     lib = _lib.load()
-    with torch.cuda.device(dy.device):
+    with _device_of(dy):
         if mask is None:
             rc = lib.act_bn_bwd_reduce(packed.data_ptr(), scale.data_ptr(), mn.data_ptr(), dy.data_ptr(),
                                        _DTYPES[dy.dtype], N, C, hw, group_size, bits, sums.data_ptr(),
@@ -425,7 +454,7 @@ def bn_bwd_coef(sums: torch.Tensor, params: torch.Tensor, count: float) -> torch
     sums = sums.contiguous()
     C = params.shape[0]
     coef = torch.empty((C, 4), dtype=torch.float32, device=params.device)
-    with torch.cuda.device(params.device):
+    with _device_of(params):
         rc = _lib.load().act_bn_bwd_coef(sums.data_ptr(), params.data_ptr(), C, float(count), coef.data_ptr(),
                                          _stream_ptr(params))
     _lib.check(rc, "act_bn_bwd_coef")
@@ -443,7 +472,7 @@ def bn_bwd_dx(packed: torch.Tensor, scale: torch.Tensor, mn: torch.Tensor, dy: t
         coef = torch.stack([k1.float(), k2.float(), k3.float(), torch.zeros_like(k1, dtype=torch.float32)], dim=1).contiguous()
     dx = torch.empty_like(dy)
     lib = _lib.load()
-    with torch.cuda.device(dy.device):
+    with _device_of(dy):
         if mask is None:
             rc = lib.act_bn_bwd_dx(packed.data_ptr(), scale.data_ptr(), mn.data_ptr(), dy.data_ptr(),
                                    _DTYPES[dy.dtype], N, C, hw, group_size, bits, coef.data_ptr(),

@@ -218,6 +218,45 @@ class Controller:
             fused.append(node.target)
         return fused
 
+    @staticmethod
+    def _fuse_bn_add_relu(traced):
+        """relu(batch_norm(x) + skip), the end of a residual block (Model/CNN/ResNetV1.py:48-49 of
+        the reference): the BatchNorm module takes the add and the ReLU over.  The pattern is a
+        BatchNorm whose only consumer is an add whose only consumer is a plain ReLU; the BatchNorm
+        call moves to the add's place (the skip operand may be computed after it) with the skip
+        as its second argument.  Returns the fused BatchNorm targets."""
+        import operator
+        adds = (operator.add, operator.iadd, torch.add)
+        fused = []
+        for node in list(traced.graph.nodes):
+            if node.op != "call_module" or len(node.users) != 1 or len(node.args) != 1:
+                continue
+            bn = traced.get_submodule(node.target)
+            if type(bn) is not DOBatchNorm2d or bn.fuse_relu:
+                continue
+            add = next(iter(node.users))
+            if (add.op != "call_function" or add.target not in adds or len(add.args) != 2 or add.kwargs
+                    or len(add.users) != 1):
+                continue
+            other = add.args[1] if add.args[0] is node else add.args[0]
+            if other is node or not isinstance(other, FX.Node):
+                continue
+            user = next(iter(add.users))
+            if user.op != "call_module" or len(user.args) != 1:
+                continue
+            relu = traced.get_submodule(user.target)
+            if not (isinstance(relu, DOReLU_Variance) and relu.relu and not relu.relu6):
+                continue
+            with traced.graph.inserting_before(add):
+                new = traced.graph.call_module(node.target, args=(node.args[0], other))
+            bn.fuse_relu = True
+            user.replace_all_uses_with(new)
+            traced.graph.erase_node(user)
+            traced.graph.erase_node(add)
+            traced.graph.erase_node(node)
+            fused.append(new.target)
+        return fused
+
     # ------------------------------------------------------------------ rewrite
     def warp_model(self, graph_mode=False, quantizer=False):
         traced = FX.symbolic_trace(self.model)
@@ -238,7 +277,10 @@ class Controller:
                     if isinstance(mod, nn.LayerNorm):
                         parent_path, _, child = name.rpartition(".")
                         setattr(traced.get_submodule(parent_path), child, RMSNorm(mod.normalized_shape[-1]))
+            self.fused_bn_add_relu = []
             if self.config.get("fuse_bn_relu", True):
+                if self.config.get("fuse_bn_add_relu", True):
+                    self.fused_bn_add_relu = self._fuse_bn_add_relu(traced)
                 self.fused_bn_relu = self._fuse_bn_relu(traced)
             traced.graph.eliminate_dead_code()
             traced.graph.lint()

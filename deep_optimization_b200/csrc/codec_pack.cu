@@ -8,14 +8,17 @@ extern template cudaError_t launch_pack_bits<ACT_DTYPE_F32>(int bits, int mode, 
 extern template cudaError_t launch_fused<ACT_DTYPE_F32>(int bits, int kind, bool nearest, const void* x, void* y, void* packed, float* scale, float* mn, int64_t n, int l2, uint64_t seed, uint64_t offset, cudaStream_t st);
 extern template cudaError_t launch_bn<ACT_DTYPE_F32>(int bits, bool nearest, const void* x, void* y, void* packed, float* scale, float* mn, int64_t n, int l2, uint64_t seed, uint64_t offset, BNArgs bn, cudaStream_t st);
 extern template cudaError_t launch_bn_cl<ACT_DTYPE_F32>(int bits, bool nearest, const void* x, void* y, void* packed, float* scale, float* mn, int64_t n, int l2, uint64_t seed, uint64_t offset, BNArgs bn, cudaStream_t st);
+extern template cudaError_t launch_bn_add<ACT_DTYPE_F32>(int bits, bool nearest, bool channel_minor, const void* x, void* y, void* packed, float* scale, float* mn, int64_t n, int l2, uint64_t seed, uint64_t offset, BNArgs bn, cudaStream_t st);
 extern template cudaError_t launch_pack_bits<ACT_DTYPE_BF16>(int bits, int mode, const void* x, const float* noise, void* packed, float* scale, float* mn, int64_t n_elems, int log2_L, uint64_t seed, uint64_t offset, int flags, float clamp_alpha, cudaStream_t st);
 extern template cudaError_t launch_fused<ACT_DTYPE_BF16>(int bits, int kind, bool nearest, const void* x, void* y, void* packed, float* scale, float* mn, int64_t n, int l2, uint64_t seed, uint64_t offset, cudaStream_t st);
 extern template cudaError_t launch_bn<ACT_DTYPE_BF16>(int bits, bool nearest, const void* x, void* y, void* packed, float* scale, float* mn, int64_t n, int l2, uint64_t seed, uint64_t offset, BNArgs bn, cudaStream_t st);
 extern template cudaError_t launch_bn_cl<ACT_DTYPE_BF16>(int bits, bool nearest, const void* x, void* y, void* packed, float* scale, float* mn, int64_t n, int l2, uint64_t seed, uint64_t offset, BNArgs bn, cudaStream_t st);
+extern template cudaError_t launch_bn_add<ACT_DTYPE_BF16>(int bits, bool nearest, bool channel_minor, const void* x, void* y, void* packed, float* scale, float* mn, int64_t n, int l2, uint64_t seed, uint64_t offset, BNArgs bn, cudaStream_t st);
 extern template cudaError_t launch_pack_bits<ACT_DTYPE_F16>(int bits, int mode, const void* x, const float* noise, void* packed, float* scale, float* mn, int64_t n_elems, int log2_L, uint64_t seed, uint64_t offset, int flags, float clamp_alpha, cudaStream_t st);
 extern template cudaError_t launch_fused<ACT_DTYPE_F16>(int bits, int kind, bool nearest, const void* x, void* y, void* packed, float* scale, float* mn, int64_t n, int l2, uint64_t seed, uint64_t offset, cudaStream_t st);
 extern template cudaError_t launch_bn<ACT_DTYPE_F16>(int bits, bool nearest, const void* x, void* y, void* packed, float* scale, float* mn, int64_t n, int l2, uint64_t seed, uint64_t offset, BNArgs bn, cudaStream_t st);
 extern template cudaError_t launch_bn_cl<ACT_DTYPE_F16>(int bits, bool nearest, const void* x, void* y, void* packed, float* scale, float* mn, int64_t n, int l2, uint64_t seed, uint64_t offset, BNArgs bn, cudaStream_t st);
+extern template cudaError_t launch_bn_add<ACT_DTYPE_F16>(int bits, bool nearest, bool channel_minor, const void* x, void* y, void* packed, float* scale, float* mn, int64_t n, int l2, uint64_t seed, uint64_t offset, BNArgs bn, cudaStream_t st);
 extern template cudaError_t launch_pack_tiled<ACT_DTYPE_F32>(int bits, bool nearest, const void* x, void* packed, float* scale, float* mn, int64_t n_elems, int log2_L, uint64_t seed, uint64_t offset, TileArgs ta, cudaStream_t st);
 extern template cudaError_t launch_pack_tiled<ACT_DTYPE_BF16>(int bits, bool nearest, const void* x, void* packed, float* scale, float* mn, int64_t n_elems, int log2_L, uint64_t seed, uint64_t offset, TileArgs ta, cudaStream_t st);
 extern template cudaError_t launch_pack_tiled<ACT_DTYPE_F16>(int bits, bool nearest, const void* x, void* packed, float* scale, float* mn, int64_t n_elems, int log2_L, uint64_t seed, uint64_t offset, TileArgs ta, cudaStream_t st);
@@ -85,7 +88,7 @@ extern "C" int act_activation_fwd_quant_pack(const void* x, int dtype, int kind,
 static int bn_fwd_common(const void* x, int dtype, int64_t n_batch, int channels, int64_t hw,
                          const float* params, int group_size, int bits, uint64_t seed, uint64_t offset,
                          int flags, void* y, void* packed, float* scale, float* mn, void* mask_bits,
-                         void* stream)
+                         void* stream, const void* residual = nullptr)
 {
     using namespace act;
     if (dtype != ACT_DTYPE_F32 && dtype != ACT_DTYPE_BF16 && dtype != ACT_DTYPE_F16) return ACT_ERR_DTYPE;
@@ -106,15 +109,21 @@ static int bn_fwd_common(const void* x, int dtype, int64_t n_batch, int channels
     if (n > (INT64_MAX >> 4) || n % group_size) return ACT_ERR_SIZE;
     if (n == 0) return ACT_OK;
     if (!x || !y || !packed || !scale || !mn || !params) return ACT_ERR_NULL;
-    if (((uintptr_t)x | (uintptr_t)y | (uintptr_t)packed | (uintptr_t)params) & 15) return ACT_ERR_ALIGN;
+    if (((uintptr_t)x | (uintptr_t)y | (uintptr_t)packed | (uintptr_t)params | (uintptr_t)residual) & 15) return ACT_ERR_ALIGN;
     int log2_L = 0;
     while ((32 << log2_L) < group_size) ++log2_L;
     BNArgs bn{reinterpret_cast<const float4*>(params), (uint32_t)hw, (uint32_t)channels,
-              magic_for((uint32_t)hw), magic_for((uint32_t)channels), static_cast<uint8_t*>(mask_bits)};
+              magic_for((uint32_t)hw), magic_for((uint32_t)channels), static_cast<uint8_t*>(mask_bits),
+              static_cast<const uint8_t*>(residual)};
     const bool nearest = (flags & ACT_FLAG_ROUND_NEAREST) != 0;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     cudaError_t e;
-    if (channel_minor) {
+    if (residual) {
+        if (dtype == ACT_DTYPE_F32) e = launch_bn_add<ACT_DTYPE_F32>(bits, nearest, channel_minor, x, y, packed, scale, mn, n, log2_L, seed, offset, bn, st);
+        else if (dtype == ACT_DTYPE_BF16) e = launch_bn_add<ACT_DTYPE_BF16>(bits, nearest, channel_minor, x, y, packed, scale, mn, n, log2_L, seed, offset, bn, st);
+        else e = launch_bn_add<ACT_DTYPE_F16>(bits, nearest, channel_minor, x, y, packed, scale, mn, n, log2_L, seed, offset, bn, st);
+    }
+    else if (channel_minor) {
         if (dtype == ACT_DTYPE_F32) e = launch_bn_cl<ACT_DTYPE_F32>(bits, nearest, x, y, packed, scale, mn, n, log2_L, seed, offset, bn, st);
         else if (dtype == ACT_DTYPE_BF16) e = launch_bn_cl<ACT_DTYPE_BF16>(bits, nearest, x, y, packed, scale, mn, n, log2_L, seed, offset, bn, st);
         else e = launch_bn_cl<ACT_DTYPE_F16>(bits, nearest, x, y, packed, scale, mn, n, log2_L, seed, offset, bn, st);
@@ -142,6 +151,17 @@ extern "C" int act_bn_relu_fwd_norm_quant_pack(const void* x, int dtype, int64_t
     if (!mask_bits) return n_batch * channels * hw == 0 ? ACT_OK : ACT_ERR_NULL;
     return bn_fwd_common(x, dtype, n_batch, channels, hw, params, group_size, bits, seed, offset, flags, y,
                          packed, scale, mn, mask_bits, stream);
+}
+
+extern "C" int act_bn_add_relu_fwd_norm_quant_pack(const void* x, const void* residual, int dtype, int64_t n_batch,
+                                                   int channels, int64_t hw, const float* params, int group_size,
+                                                   int bits, uint64_t seed, uint64_t offset, int flags, void* y,
+                                                   void* packed, float* scale, float* mn, void* mask_bits,
+                                                   void* stream)
+{
+    if (!mask_bits || !residual) return n_batch * channels * hw == 0 ? ACT_OK : ACT_ERR_NULL;
+    return bn_fwd_common(x, dtype, n_batch, channels, hw, params, group_size, bits, seed, offset, flags, y,
+                         packed, scale, mn, mask_bits, stream, residual);
 }
 
 extern "C" int act_quant_pack_tiles(const void* x, int dtype, int64_t n_planes, int height, int width, int tile,

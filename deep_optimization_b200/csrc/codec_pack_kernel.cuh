@@ -323,7 +323,8 @@ __device__ __forceinline__ void encode_piece_ref(const float* xf8, float mn, flo
 // kProGelu / kProSilu write y = act(x) to y_out and quantise the activation's derivative
 // (what backward multiplies dy with), replacing the reference's fused forward kernels
 // (Activation_Compression/modules/activations/kernel_implementation.py:184-342, 468-559).
-enum Producer { kProNone = 0, kProGelu = 1, kProSilu = 2, kProBN = 3, kProBNRelu = 4, kProBNcl = 5, kProBNReluCl = 6 };
+enum Producer { kProNone = 0, kProGelu = 1, kProSilu = 2, kProBN = 3, kProBNRelu = 4, kProBNcl = 5, kProBNReluCl = 6,
+                kProBNAddRelu = 7, kProBNAddReluCl = 8 };
 
 // Per-channel inputs of the batch-norm producer: x is [N, C, HW] contiguous and
 // params[c] = (mean, invstd, weight, bias).  The channel of element e is (e / HW) % C;
@@ -336,10 +337,15 @@ enum Producer { kProNone = 0, kProGelu = 1, kProSilu = 2, kProBN = 3, kProBNRelu
 // channel of element e is e % C, so the eight elements of a piece belong to eight
 // consecutive channels and every element reads its own row of the table (the rows of a
 // warp's loads are contiguous); the kernel keeps the table in shared memory, so C <= 4096.
+// kProBNAddRelu / kProBNAddReluCl: y = max(x_hat * weight + bias + residual, 0) with `residual`
+// a tensor of x's type and layout (the skip connection of a residual block: the add and the
+// ReLU behind the block's last batch norm cost no pass of their own); the sum is rounded to
+// fp32 before the ReLU and the mask is that of the sum.
 struct BNArgs {
     const float4* params;
     uint32_t hw, c, magic_hw, magic_c;
     uint8_t* mask;
+    const uint8_t* residual;
 };
 
 // Tiled source addressing (TILED kernels): x is [planes, H, W] and group g is the T x T tile
@@ -383,7 +389,7 @@ quant_pack_kernel(const void* __restrict__ x_, const float* __restrict__ noise,
                   uint8_t* __restrict__ packed, float* __restrict__ scale_out,
                   float* __restrict__ min_out, int64_t n_elems, int log2_L_arg,
                   uint32_t key_lo, uint32_t key_hi, int flags, float clamp_alpha,
-                  uint8_t* __restrict__ y_out = nullptr, BNArgs bn = BNArgs{nullptr, 1u, 1u, 0u, 0u, nullptr},
+                  uint8_t* __restrict__ y_out = nullptr, BNArgs bn = BNArgs{nullptr, 1u, 1u, 0u, 0u, nullptr, nullptr},
                   TileArgs ta = TileArgs{0u, 0u, 1u, 1u, 3})
 {
     static_assert(!TILED || PRO == kProNone, "tiled addressing is built for the plain codec only");
@@ -457,7 +463,7 @@ quant_pack_kernel(const void* __restrict__ x_, const float* __restrict__ noise,
     // and then fall on distinct banks.
     extern __shared__ __align__(16) uint8_t dyn_smem[];
     float4* const s_table = reinterpret_cast<float4*>(dyn_smem);
-    if (PRO == kProBNcl || PRO == kProBNReluCl) {
+    if (PRO == kProBNcl || PRO == kProBNReluCl || PRO == kProBNAddReluCl) {
         for (uint32_t c = threadIdx.x; c < bn.c; c += PackCfg<DT>::threads)
             s_table[(c >> 3) * 9u + (c & 7u)] = __ldg(bn.params + c);
         __syncthreads();
@@ -485,9 +491,28 @@ quant_pack_kernel(const void* __restrict__ x_, const float* __restrict__ noise,
         }
 
         // batch norm: plane index and offset inside the plane of the lane's group
-        constexpr bool BN_CL = (PRO == kProBNcl || PRO == kProBNReluCl);
-        constexpr bool BN_RELU = (PRO == kProBNRelu || PRO == kProBNReluCl);
-        constexpr bool IS_BN = (PRO == kProBN || PRO == kProBNRelu || BN_CL);
+        constexpr bool BN_CL = (PRO == kProBNcl || PRO == kProBNReluCl || PRO == kProBNAddReluCl);
+        constexpr bool BN_ADD = (PRO == kProBNAddRelu || PRO == kProBNAddReluCl);
+        constexpr bool BN_RELU = (PRO == kProBNRelu || PRO == kProBNReluCl || BN_ADD);
+        constexpr bool IS_BN = (PRO == kProBN || PRO == kProBNRelu || BN_CL || BN_ADD);
+        // the residual's pieces, at the addresses of the x pieces they are added to
+        RawTile<DT> res;
+        if (BN_ADD) {
+            if (valid) {
+                const uint8_t* p = bn.residual + (group_e0 + j * 8) * ElemT<DT>::bytes;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    if (ElemT<DT>::bytes == 4) {
+                        res.v[2 * k] = ldg_nc_v4(p + (int64_t)(k * piece_stride) * 4);
+                        res.v[2 * k + 1] = ldg_nc_v4(p + (int64_t)(k * piece_stride) * 4 + 16);
+                    } else {
+                        res.v[k] = ldg_nc_v4(p + (int64_t)(k * piece_stride) * 2);
+                    }
+                }
+            } else {
+                zero_raw<DT>(res);
+            }
+        }
         uint32_t bn_c0 = 0, bn_r0 = 0;
         if (BN_CL) {
             bn_c0 = (uint32_t)((uint64_t)group_e0 % bn.c);               // channel of the group's first element
@@ -555,6 +580,21 @@ quant_pack_kernel(const void* __restrict__ x_, const float* __restrict__ noise,
                 } else {
 #pragma unroll
                     for (int i = 0; i < 8; ++i) act_and_derivative<PRO>(xf[k * 8 + i], yv[i], xf[k * 8 + i]);
+                }
+                if (BN_ADD) {
+                    float rf[8];
+                    if (ElemT<DT>::bytes == 4) {
+                        const uint4 a = res.v[(2 * k) & 7], b = res.v[(2 * k + 1) & 7];
+                        rf[0] = __uint_as_float(a.x); rf[1] = __uint_as_float(a.y); rf[2] = __uint_as_float(a.z); rf[3] = __uint_as_float(a.w);
+                        rf[4] = __uint_as_float(b.x); rf[5] = __uint_as_float(b.y); rf[6] = __uint_as_float(b.z); rf[7] = __uint_as_float(b.w);
+                    } else {
+                        constexpr int D16 = (DT == ACT_DTYPE_F32) ? ACT_DTYPE_BF16 : DT;
+                        const uint4 a = res.v[k & 3];
+                        rf[0] = widen_lo<D16>(a.x); rf[1] = widen_hi<D16>(a.x); rf[2] = widen_lo<D16>(a.y); rf[3] = widen_hi<D16>(a.y);
+                        rf[4] = widen_lo<D16>(a.z); rf[5] = widen_hi<D16>(a.z); rf[6] = widen_lo<D16>(a.w); rf[7] = widen_hi<D16>(a.w);
+                    }
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) yv[i] = __fadd_rn(yv[i], rf[i]);
                 }
                 if (BN_RELU) {
                     uint32_t bits8 = 0;
@@ -746,7 +786,7 @@ cudaError_t launch_pack_fixed(const void* x, const float* noise, void* packed, f
     return launch_overlapped(quant_pack_kernel<DT, BITS, NM, kProNone, L2>, grid, PackCfg<DT>::threads, st,
                              x, noise, static_cast<uint8_t*>(packed), scale, mn, n_elems, log2_L,
                              (uint32_t)key, (uint32_t)(key >> 32), flags, clamp_alpha,
-                             static_cast<uint8_t*>(nullptr), BNArgs{nullptr, 1u, 1u, 0u, 0u, nullptr}, TileArgs{0u, 0u, 1u, 1u, 3});
+                             static_cast<uint8_t*>(nullptr), BNArgs{nullptr, 1u, 1u, 0u, 0u, nullptr, nullptr}, TileArgs{0u, 0u, 1u, 1u, 3});
 }
 
 // tiled source addressing, the two fixed-point modes only
@@ -767,7 +807,7 @@ cudaError_t launch_pack_tiled_one(const void* x, void* packed, float* scale, flo
     return launch_overlapped(quant_pack_kernel<DT, BITS, NM, kProNone, -1, true>, grid, PackCfg<DT>::threads, st,
                              x, static_cast<const float*>(nullptr), static_cast<uint8_t*>(packed), scale, mn,
                              n_elems, log2_L, (uint32_t)key, (uint32_t)(key >> 32), 0, 0.0f,
-                             static_cast<uint8_t*>(nullptr), BNArgs{nullptr, 1u, 1u, 0u, 0u, nullptr}, ta);
+                             static_cast<uint8_t*>(nullptr), BNArgs{nullptr, 1u, 1u, 0u, 0u, nullptr, nullptr}, ta);
 }
 
 template <int DT>
@@ -850,7 +890,7 @@ cudaError_t launch_fused_one(const void* x, void* y, void* packed, float* scale,
     return launch_overlapped(quant_pack_kernel<DT, BITS, NM, PRO>, grid, PackCfg<DT>::threads, st,
                              x, static_cast<const float*>(nullptr), static_cast<uint8_t*>(packed), scale, mn,
                              n_elems, log2_L, (uint32_t)key, (uint32_t)(key >> 32), 0, 0.0f,
-                             static_cast<uint8_t*>(y), BNArgs{nullptr, 1u, 1u, 0u, 0u, nullptr}, TileArgs{0u, 0u, 1u, 1u, 3});
+                             static_cast<uint8_t*>(y), BNArgs{nullptr, 1u, 1u, 0u, 0u, nullptr, nullptr}, TileArgs{0u, 0u, 1u, 1u, 3});
 }
 
 template <int DT, int BITS>
@@ -892,7 +932,7 @@ cudaError_t launch_bn_one(const void* x, void* y, void* packed, float* scale, fl
                                  int64_t n_elems, int log2_L, uint64_t seed, uint64_t offset,
                                  BNArgs bn, cudaStream_t st)
 {
-    constexpr bool CL = (PRO == kProBNcl || PRO == kProBNReluCl);
+    constexpr bool CL = (PRO == kProBNcl || PRO == kProBNReluCl || PRO == kProBNAddReluCl);
     constexpr size_t kMaxTable = (size_t)(4096 / 8) * 144;          // channel-minor table, C <= 4096
     static int per_sm = 0;
     if (per_sm == 0) {
@@ -953,6 +993,27 @@ cudaError_t launch_bn_cl(int bits, bool nearest, const void* x, void* y, void* p
                        : launch_bn_one<DT, B, kNoiseHash, kProBNReluCl>(x, y, packed, scale, mn, n, l2, seed, offset, bn, st); \
     return nearest ? launch_bn_one<DT, B, kNoiseConst, kProBNcl>(x, y, packed, scale, mn, n, l2, seed, offset, bn, st) \
                    : launch_bn_one<DT, B, kNoiseHash, kProBNcl>(x, y, packed, scale, mn, n, l2, seed, offset, bn, st)
+    switch (bits) {
+        case 1: ACT_BN_CASE(1);
+        case 2: ACT_BN_CASE(2);
+        case 4: ACT_BN_CASE(4);
+        default: ACT_BN_CASE(8);
+    }
+#undef ACT_BN_CASE
+}
+
+// batch norm + residual add + ReLU, both layouts (bn.residual and bn.mask set)
+template <int DT>
+cudaError_t launch_bn_add(int bits, bool nearest, bool channel_minor, const void* x, void* y, void* packed,
+                          float* scale, float* mn, int64_t n, int l2, uint64_t seed, uint64_t offset, BNArgs bn,
+                          cudaStream_t st)
+{
+#define ACT_BN_CASE(B) \
+    if (channel_minor) \
+        return nearest ? launch_bn_one<DT, B, kNoiseConst, kProBNAddReluCl>(x, y, packed, scale, mn, n, l2, seed, offset, bn, st) \
+                       : launch_bn_one<DT, B, kNoiseHash, kProBNAddReluCl>(x, y, packed, scale, mn, n, l2, seed, offset, bn, st); \
+    return nearest ? launch_bn_one<DT, B, kNoiseConst, kProBNAddRelu>(x, y, packed, scale, mn, n, l2, seed, offset, bn, st) \
+                   : launch_bn_one<DT, B, kNoiseHash, kProBNAddRelu>(x, y, packed, scale, mn, n, l2, seed, offset, bn, st)
     switch (bits) {
         case 1: ACT_BN_CASE(1);
         case 2: ACT_BN_CASE(2);

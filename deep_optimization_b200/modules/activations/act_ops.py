@@ -13,7 +13,7 @@ import torch
 from torch.amp import custom_bwd, custom_fwd
 from torch.autograd import Function
 
-from ... import codec
+from ... import act_kernels, codec
 from ..module_utils import unified_dequantize, unified_quantize
 
 
@@ -25,7 +25,7 @@ class _DOReLU(Function):
         ctx.fused = not m["act_padding"] and input.numel() % max(m["group_size"], 32) == 0
         if ctx.fused:
             # one pass: y and the 1-bit mask (act_ops.py:31-38 of the reference)
-            y, packed, N, G = torch.ops.act_lib.relu_fwd_fused_pack(input, relu, relu6, 1, m["group_size"])
+            y, packed, N, G = act_kernels.op("relu_fwd_fused_pack")(input, relu, relu6, 1, m["group_size"])
             ctx.meta_ngs = (N, G, m["group_size"])
             ctx.channels_last = codec._channels_last(input)      # the mask follows the input's memory order
             ctx.save_for_backward(packed)
@@ -53,7 +53,7 @@ class _DOReLU(Function):
                 dy = dy.contiguous(memory_format=torch.channels_last)
             elif codec._channels_last(dy):
                 dy = dy.contiguous()
-            return torch.ops.act_lib.relu_bwd_fused_unpack(packed, dy, 1, N, G, gs), None, None, None, None
+            return act_kernels.op("relu_bwd_fused_unpack")(packed, dy, 1, N, G, gs), None, None, None, None
         mask = unified_dequantize((packed, None, None), ctx.q_meta, None)
         return dy * mask.to(dy.dtype), None, None, None, None
 
@@ -72,9 +72,9 @@ def _fused_ok(input, m):
 def _fused_forward(ctx, input, kind, m):
     """activation + derivative codec in one kernel (flat grouping)."""
     if kind == "gelu":
-        y, packed, scale, mn, N, G = torch.ops.act_lib.gelu_fwd_fused_quan_pack(input, m["bits"], m["group_size"])
+        y, packed, scale, mn, N, G = act_kernels.op("gelu_fwd_fused_quan_pack")(input, m["bits"], m["group_size"])
     else:
-        y, packed, scale, mn, N, G = torch.ops.act_lib.silu_fwd_quan_pack(input, m["bits"], m["group_size"],
+        y, packed, scale, mn, N, G = act_kernels.op("silu_fwd_quan_pack")(input, m["bits"], m["group_size"],
                                                                           False, False, 0)[:6]
     ctx.fused_meta = (N, G, m["bits"], m["group_size"])
     ctx.save_for_backward(packed, scale, mn)
@@ -85,7 +85,7 @@ def _apply_derivative(ctx, dy):
     packed, scale, mn = ctx.saved_tensors
     if getattr(ctx, "fused_meta", None) is not None:
         N, G, bits, gs = ctx.fused_meta
-        return torch.ops.act_lib.gelu_bwd_fused_dequan_unpack(packed, dy, scale, mn, bits, N, G, gs)
+        return act_kernels.op("gelu_bwd_fused_dequan_unpack")(packed, dy, scale, mn, bits, N, G, gs)
     deriv = unified_dequantize((packed, scale, mn), ctx.q_meta, None)
     return dy * deriv.to(dy.dtype)
 

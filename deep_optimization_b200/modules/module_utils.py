@@ -3,7 +3,8 @@
 `quantize / dequantize / unified_quantize / unified_dequantize` keep the
 signatures, the `(tensors, 14-tuple meta)` return layout and the DIVISION
 residual of Activation_Compression/modules/module_utils.py:28-102; the kernels
-behind `torch.ops.act_lib.*` are the CUDA ones registered by `act_kernels`.
+behind `torch.ops.act_lib.*` are the CUDA ones registered by `act_kernels` (reached through
+`act_kernels.op`, which skips the dispatcher in eager mode).
 
 q_meta order (module_utils.py:37,68):
   (bits, pack_only, group_size, act_padding, N, G, new_H, new_W,
@@ -59,12 +60,12 @@ def quantize(input, bits, pack_only, group_size, act_padding, N, avg_alam, alam_
         spatical_aware_act_tensor_reshape(input, Group_Size=group_size, act_padding=act_padding,
                                           pack_only=pack_only)
     if pack_only:
-        out = torch.ops.act_lib.pack_triton(groups, bits, group_size)
+        out = act_kernels.op("pack_triton")(groups, bits, group_size)
         # the reference records (0, 0, False, False) here although it grouped spatially,
         # which scrambles masks on the way back; the real grouping is recorded instead
         return (out, None, None), (bits, pack_only, group_size, act_padding, N, G, new_H, new_W, pad_elig,
                                    reshape_elig, channel_mean, None, None, ori_shape)
-    out, scaler, ema_min = torch.ops.act_lib.quant_pack_triton(groups, bits, group_size, avg_alam,
+    out, scaler, ema_min = act_kernels.op("quant_pack_triton")(groups, bits, group_size, avg_alam,
                                                                alam_bits, clamp, clamp_alpha)
     return (out, scaler, ema_min), (bits, pack_only, group_size, act_padding, N, G, new_H, new_W,
                                     pad_elig, reshape_elig, channel_mean, avg_alam, alam_bits, ori_shape)
@@ -90,9 +91,9 @@ def dequantize(quantized_tensor, quantized_meta):
         return codec.dequant_unpack_tiles(q_input, q_scale.reshape(-1), ema_mn.reshape(-1), q_bits,
                                           _TILE[group_size], tuple(input_shape))
     if pack_only:
-        unpack = torch.ops.act_lib.unpack_triton(q_input, q_bits, N, G, group_size)
+        unpack = act_kernels.op("unpack_triton")(q_input, q_bits, N, G, group_size)
     else:
-        unpack = torch.ops.act_lib.dequant_unpack_triton(q_input, q_scale, ema_mn, q_bits, group_size,
+        unpack = act_kernels.op("dequant_unpack_triton")(q_input, q_scale, ema_mn, q_bits, group_size,
                                                          avg_alam, alam_bits)
     return spatical_aware_act_tensor_reshape_back(unpack, input_shape, group_size, new_H, new_W,
                                                   act_padding, pad_elig, reshape_elig, channel_mean)

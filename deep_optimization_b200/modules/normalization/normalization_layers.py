@@ -24,14 +24,17 @@ class DOBatchNorm2d(nn.BatchNorm2d):
         # relu(batch_norm(x)) and the ReLU node is taken out of the graph
         self.fuse_relu = False
 
-    def forward(self, x):
+    def forward(self, x, residual=None):
+        # residual: set by the Controller where the graph had relu(batch_norm(x) + residual)
         if not self.training:
             y = super().forward(x)
+            if residual is not None:
+                y = y + residual
             return nn.functional.relu(y) if self.fuse_relu else y
         self._check_input_dim(x)
         return _DOBatchNorm.apply(x, self.weight, self.bias, self.running_mean, self.running_var,
                                   _ema_factor(self), self.eps, self.target_name, self.meta,
-                                  self.ema_grad_meta, None, 1, self.fuse_relu)
+                                  self.ema_grad_meta, None, 1, self.fuse_relu, residual)
 
 
 class DOSyncBatchNorm2d(nn.SyncBatchNorm):

@@ -51,11 +51,17 @@ class _DOBatchNorm(Function):
     @staticmethod
     @custom_fwd(device_type="cuda")
     def forward(ctx, input, weight, bias, running_mean, running_var, exponential_average_factor,
-                eps, target_name, meta, ema_grad_meta, process_group=None, world_size=1, fuse_relu=False):
+                eps, target_name, meta, ema_grad_meta, process_group=None, world_size=1, fuse_relu=False,
+                residual=None):
         # fuse_relu (not in the reference's argument list): the module's output is
-        # relu(batch_norm(x)); on the fused path the same three kernels do it and keep the mask
+        # relu(batch_norm(x)); on the fused path the same three kernels do it and keep the mask.
+        # residual (with fuse_relu): the output is relu(batch_norm(x) + residual), the end of a
+        # residual block; its gradient is dy under the ReLU mask.
         ctx.set_materialize_grads(False)
         ctx.relu_mask = False
+        ctx.has_residual = residual is not None
+        if residual is not None and not fuse_relu:
+            raise ValueError("a residual is fused only together with the ReLU")
         C = input.shape[1]
         shape = _channel_view(input)
         count = input.numel() // C
@@ -76,7 +82,8 @@ class _DOBatchNorm(Function):
                 running_var.copy_(rv)
             flags = _lib.ACT_FLAG_ROUND_NEAREST if act_kernels.get_mode() != "baseline" else 0
             out = codec.bn_fwd_norm_quant_pack(x, None, None, weight, bias, m["bits"], m["group_size"],
-                                               flags=flags, params=params, relu=fuse_relu)
+                                               flags=flags, params=params, relu=fuse_relu,
+                                               residual=None if residual is None else residual.to(x.dtype))
             y, packed, scale, mn = out[:4]
             ctx.fused = (m["bits"], m["group_size"], count)
             ctx.sync = (process_group, world_size)
@@ -109,6 +116,8 @@ class _DOBatchNorm(Function):
         q_tensors, q_meta, _ = unified_quantize(x_hat, None, target_name, meta, clamp=False, clamp_alpha=0.0)
         ctx.q_meta = q_meta
         ctx.sync = (process_group, world_size)
+        if residual is not None:
+            y = y + residual.to(y.dtype)
         if fuse_relu:
             # unfused shapes: plain ReLU behind the codec path, its mask kept as a bool tensor
             keep = y > 0
@@ -132,15 +141,21 @@ class _DOBatchNorm(Function):
             # two kernels on the packed x_hat: per-channel sums, then dx (normalization_ops.py:145-163)
             bits, gs, count = ctx.fused
             dyc = dy.contiguous(memory_format=torch.channels_last) if ctx.channels_last else dy.contiguous()
+            dres = None
+            if ctx.has_residual:
+                # dy under the mask is the residual's gradient and the batch norm's dy
+                dyc = codec.relu_bwd_unpack(mask, dyc, channels_last=ctx.channels_last)
+                dres, mask = dyc, None
             dgamma, dbeta = codec.bn_bwd_reduce(q_out, q_scale, q_min, dyc, bits, gs, mask=mask)
             # `invstd` is the whole [C, 4] parameter table on this path
             coef = codec.bn_bwd_coef(dgamma._base if dgamma._base is not None else (dgamma, dbeta), invstd, count)
             dx = codec.bn_bwd_dx(q_out, q_scale, q_min, dyc, None, None, None, bits, gs, mask=mask, coef=coef)
             dw = dgamma.to(weight.dtype) if weight is not None else None
             db = dbeta.to(weight.dtype) if weight is not None else None
-            return dx, dw, db, None, None, None, None, None, None, None, None, None, None
+            return dx, dw, db, None, None, None, None, None, None, None, None, None, None, dres
         if mask is not None:
             dy = torch.where(mask, dy, torch.zeros_like(dy))
+        dres = dy if ctx.has_residual else None
         x_hat = unified_dequantize((q_out, q_scale, q_min), ctx.q_meta, None)
         shape = _channel_view(dy)
         C = dy.shape[1]
@@ -154,7 +169,7 @@ class _DOBatchNorm(Function):
             dx = dx * invstd.to(dx.dtype).view(shape)
             dw = dgamma.to(weight.dtype) if weight is not None else None
             db = dbeta.to(weight.dtype) if weight is not None else None
-            return dx, dw, db, None, None, None, None, None, None, None, None, None, None
+            return dx, dw, db, None, None, None, None, None, None, None, None, None, None, dres
         g = dy.float()
         x_hat = x_hat.float()
         dims = [0] + list(range(2, g.dim()))
@@ -167,7 +182,7 @@ class _DOBatchNorm(Function):
         dx = (w * invstd / M).view(shape) * (M * g - sum_db.view(shape) - x_hat * sum_dg.view(shape))
         dw = dgamma.to(weight.dtype) if weight is not None else None
         db = dbeta.to(weight.dtype) if weight is not None else None
-        return dx.to(dy.dtype), dw, db, None, None, None, None, None, None, None, None, None, None
+        return dx.to(dy.dtype), dw, db, None, None, None, None, None, None, None, None, None, None, dres
 
 
 class _DOSyncBatchNorm:

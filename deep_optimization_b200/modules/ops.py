@@ -42,6 +42,8 @@ class _DOConvnd(Function):
         q_tensors, q_meta, input_l = unified_quantize(input.to(torch.bfloat16), input_l, target_name, meta,
                                                       clamp=True, clamp_alpha=clamp_alpha)
         ctx.meta = stride, padding, dilation, groups, ema_grad_meta, clamp_alpha
+        # the weight in its compute type is what backward multiplies with: kept, not re-cast
+        ctx.weight_compute = weight_compute if weight_compute is not weight_master else None
         ctx.save_for_backward(weight_master, q_tensors[0], q_tensors[1], q_tensors[2], input_l, learnable_scale)
         ctx.q_inputs_meta = q_meta
         return forward_op(input, weight_compute, bias=None, stride=stride, padding=padding,
@@ -52,7 +54,10 @@ class _DOConvnd(Function):
         q_meta = ctx.q_inputs_meta
         stride, padding, dilation, groups, _, _ = ctx.meta
         weight_master, q_out, q_scale, q_min, input_l, _ = ctx.saved_tensors
-        if torch.is_autocast_enabled("cuda"):
+        if ctx.weight_compute is not None:
+            weight_compute = ctx.weight_compute
+            dy = dy.to(weight_compute.dtype)
+        elif torch.is_autocast_enabled("cuda"):
             dy = dy.to(torch.get_autocast_dtype("cuda"))
             weight_compute = weight_master.to(torch.bfloat16)
         else:

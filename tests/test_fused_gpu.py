@@ -397,3 +397,67 @@ def test_channels_last_modules_match_pytorch(cuda_device):
     assert xq.grad.is_contiguous(memory_format=torch.channels_last)
     assert (xq.grad - xr.grad).abs().max() < 0.05
     assert torch.allclose(bn.bias.grad, rb.bias.grad, rtol=1e-4, atol=1e-3)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", (torch.float32, torch.bfloat16), ids=("f32", "bf16"))
+@pytest.mark.parametrize("shape", [(8, 16, 32, 32), (6, 24, 14, 14), (4, 64, 56, 56)])
+@pytest.mark.parametrize("channels_last", (False, True))
+def test_bn_add_relu_fused_forward(cuda_device, dtype, shape, channels_last):
+    """y = max(x_hat * w + b + residual, 0): the packed x_hat is the one of the kernel without
+    the add (bit-exact), y equals the fp32 chain rounded once to the output type, the mask is
+    that of the sum, in both layouts."""
+    from deep_optimization_b200 import codec
+    fmt = torch.channels_last if channels_last else torch.contiguous_format
+    g = torch.Generator().manual_seed(41)
+    x = (torch.randn(shape, generator=g) * 2 + 0.5).to(dtype).to(cuda_device).contiguous(memory_format=fmt)
+    r = torch.randn(shape, generator=g).to(dtype).to(cuda_device).contiguous(memory_format=fmt)
+    C = shape[1]
+    mean = torch.randn(C, generator=g).to(cuda_device)
+    invstd = (torch.rand(C, generator=g) + 0.5).to(cuda_device)
+    w = torch.randn(C, generator=g).to(cuda_device)
+    b = torch.randn(C, generator=g).to(cuda_device)
+    gs = _cl_group(x.numel())
+    y0, p0, s0, m0 = codec.bn_fwd_norm_quant_pack(x, mean, invstd, w, b, 2, gs, seed=3, offset=2)
+    y1, p1, s1, m1, mask = codec.bn_fwd_norm_quant_pack(x, mean, invstd, w, b, 2, gs, seed=3, offset=2,
+                                                        relu=True, residual=r)
+    assert torch.equal(p0, p1) and torch.equal(s0, s1) and torch.equal(m0, m1)
+    view = [1, C, 1, 1]
+    x_hat = (x.float() - mean.view(view)) * invstd.view(view)
+    total = (x_hat * w.view(view) + b.view(view)) + r.float()
+    keep = total > 0
+    assert torch.equal(y1, torch.where(keep, total, torch.zeros_like(total)).to(dtype))
+    assert y1.is_contiguous(memory_format=fmt)
+    order = keep.permute(0, 2, 3, 1) if channels_last else keep
+    bits = np.unpackbits(mask.cpu().numpy(), bitorder="little")[: x.numel()]
+    assert np.array_equal(bits.astype(bool), order.reshape(-1).cpu().numpy())
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("channels_last", (False, True))
+def test_bn_add_relu_module_matches_pytorch(cuda_device, channels_last):
+    """DOBatchNorm2d(x, residual) with fuse_relu against relu(BatchNorm2d(x) + residual): output
+    exact to rounding, gradients of x, the residual and the affine parameters within the 8-bit
+    codec's error."""
+    from deep_optimization_b200.modules.normalization.normalization_layers import DOBatchNorm2d
+    torch.manual_seed(3)
+    fmt = torch.channels_last if channels_last else torch.contiguous_format
+    meta = {"b": {"bits": 8, "pack_only": False, "group_size": 256, "act_padding": False, "N": 8,
+                  "AVG_ALAM": False, "ALAM_BITS": 0, "DIVISION": None}}
+    bn = DOBatchNorm2d(16, target_name="b", meta=meta).to(cuda_device).train()
+    bn.fuse_relu = True
+    rb = torch.nn.BatchNorm2d(16).to(cuda_device).train()
+    with torch.no_grad():
+        bn.weight.copy_(torch.randn(16)); bn.bias.copy_(torch.randn(16))
+        rb.weight.copy_(bn.weight); rb.bias.copy_(bn.bias)
+    x = torch.randn(8, 16, 16, 16, device=cuda_device).contiguous(memory_format=fmt).requires_grad_()
+    s = torch.randn(8, 16, 16, 16, device=cuda_device).contiguous(memory_format=fmt).requires_grad_()
+    xr, sr = x.detach().clone().requires_grad_(), s.detach().clone().requires_grad_()
+    g = torch.randn_like(x)
+    y, yr = bn(x, s), torch.relu(rb(xr) + sr)
+    assert torch.allclose(y, yr, atol=1e-4)
+    y.backward(g); yr.backward(g)
+    assert torch.equal(s.grad, sr.grad)
+    assert (x.grad - xr.grad).abs().max() < 0.05
+    assert (bn.weight.grad - rb.weight.grad).norm() / rb.weight.grad.norm() < 0.03
+    assert torch.allclose(bn.bias.grad, rb.bias.grad, rtol=1e-4, atol=1e-3)

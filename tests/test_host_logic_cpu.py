@@ -1,6 +1,8 @@
 """CPU tests of the host-side mirror of the reference interface: grouping helpers,
 operator registration (fake kernels), controller planning, bit-allocation policy."""
 import pytest
+import copy
+
 import torch
 from torch import nn
 
@@ -77,6 +79,45 @@ def test_controller_plans_and_swaps():
     net.eval()
     with torch.no_grad():
         assert net(torch.randn(2, 3, 32, 32)).shape == (2, 10)
+
+
+def test_controller_fuses_bn_add_relu():
+    """relu(bn(x) + skip), the end of a residual block, becomes one BatchNorm call taking the
+    skip as its second argument, also when the skip is computed after the BatchNorm; the
+    eval-mode output is unchanged."""
+    from deep_optimization_b200.controller import Controller
+    from deep_optimization_b200.payload.resnet import Bottleneck
+
+    class Net(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.stem = nn.Conv2d(3, 64, 3, padding=1, bias=False)
+            self.a = Bottleneck(64, 16, project=False)
+            self.b = Bottleneck(64, 32, project=True)
+
+        def forward(self, x):
+            return self.b(self.a(self.stem(x)))
+
+    torch.manual_seed(0)
+    model = Net()
+    ref = copy.deepcopy(model).eval()
+    cfg = dict(default_bits=2, auto_precision=None, batch_size=64, min_activation_mib=0.1)
+    c = Controller(model, cfg, input_shape=(3, 32, 32), test=False, device="cpu")
+    net = c.traced_model
+    assert sorted(c.fused_bn_add_relu) == ["a.bn3", "b.bn3"]
+    targets = [n.target for n in net.graph.nodes if n.op == "call_module"]
+    assert "a.relu3" not in targets and "b.relu3" not in targets
+    assert net.a.bn3.fuse_relu and net.b.bn3.fuse_relu and not net.get_submodule("b.shortcut.1").fuse_relu
+    for n in net.graph.nodes:
+        if n.op == "call_module" and n.target in ("a.bn3", "b.bn3"):
+            assert len(n.args) == 2
+    net.eval()
+    x = torch.randn(2, 3, 32, 32)
+    with torch.no_grad():
+        assert torch.allclose(net(x), ref(x), atol=1e-6)
+    off = Controller(copy.deepcopy(ref).train(), dict(cfg, fuse_bn_add_relu=False), input_shape=(3, 32, 32),
+                     test=False, device="cpu")
+    assert off.fused_bn_add_relu == []
 
 
 def test_controller_fuses_bn_relu():
