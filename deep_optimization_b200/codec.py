@@ -37,6 +37,15 @@ def _bits_consts(bits: int, group_size: int):
     return vpw, group_size // vpw, (1 << bits) - 1
 
 
+def _packed_words(bits: int, group_size: int, planes3: bool) -> int:
+    """32-bit words per group.  bits = 3 (stored as bit planes, three words per 32 elements) is
+    accepted only from callers that ask for it: the act_lib operators keep the reference's
+    bits-in-(1,2,4,8) contract."""
+    if bits == 3 and planes3:
+        return group_size * 3 // 32
+    return _bits_consts(bits, group_size)[1]
+
+
 def _require_cuda(t: torch.Tensor, name: str) -> None:
     if not t.is_cuda:
         raise RuntimeError(f"{name} must be a CUDA tensor: the codec has no CPU path")
@@ -60,13 +69,14 @@ def _device_of(t: torch.Tensor):
 def quant_pack(x: torch.Tensor, bits: int, group_size: int, noise: Optional[torch.Tensor] = None,
                seed: Optional[int] = None, offset: Optional[int] = None, flags: int = 0,
                clamp_alpha: float = 0.0,
-               out: Optional[Tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = None
-               ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+               out: Optional[Tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = None,
+               planes3: bool = False) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """x: [..., group_size]-groupable tensor (numel % group_size == 0), fp32/bf16/fp16.
     Returns (packed int32 [NG, group_size*bits/32], scale fp32 [NG], min fp32 [NG]);
-    `out` supplies those three buffers instead of allocating them."""
+    `out` supplies those three buffers instead of allocating them.  planes3=True admits
+    bits = 3 (bit-plane layout, the cpp_extension pack3 path)."""
     global _next_offset
-    _, nwords, _ = _bits_consts(bits, group_size)
+    nwords = _packed_words(bits, group_size, planes3)
     _require_cuda(x, "x")
     if x.dtype not in _DTYPES:
         raise TypeError(f"unsupported activation dtype {x.dtype}")
@@ -106,9 +116,9 @@ def quant_pack(x: torch.Tensor, bits: int, group_size: int, noise: Optional[torc
 
 def dequant_unpack(packed: torch.Tensor, scale: torch.Tensor, mn: torch.Tensor, bits: int,
                    group_size: int, out_dtype: torch.dtype = torch.bfloat16,
-                   out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                   out: Optional[torch.Tensor] = None, planes3: bool = False) -> torch.Tensor:
     """Inverse of quant_pack; returns [NG, group_size] of out_dtype (written into `out` if given)."""
-    _bits_consts(bits, group_size)
+    _packed_words(bits, group_size, planes3)
     _require_cuda(packed, "packed")
     packed = packed.contiguous()
     scale = scale.to(torch.float32).contiguous()

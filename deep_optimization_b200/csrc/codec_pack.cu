@@ -22,6 +22,9 @@ extern template cudaError_t launch_bn_add<ACT_DTYPE_F16>(int bits, bool nearest,
 extern template cudaError_t launch_pack_tiled<ACT_DTYPE_F32>(int bits, bool nearest, const void* x, void* packed, float* scale, float* mn, int64_t n_elems, int log2_L, uint64_t seed, uint64_t offset, TileArgs ta, cudaStream_t st);
 extern template cudaError_t launch_pack_tiled<ACT_DTYPE_BF16>(int bits, bool nearest, const void* x, void* packed, float* scale, float* mn, int64_t n_elems, int log2_L, uint64_t seed, uint64_t offset, TileArgs ta, cudaStream_t st);
 extern template cudaError_t launch_pack_tiled<ACT_DTYPE_F16>(int bits, bool nearest, const void* x, void* packed, float* scale, float* mn, int64_t n_elems, int log2_L, uint64_t seed, uint64_t offset, TileArgs ta, cudaStream_t st);
+// codec_bits3.cu
+cudaError_t quant_pack3(const void* x, int dtype, const float* noise, int mode, uint64_t seed, uint64_t offset,
+                        void* packed, float* scale, float* mn, int64_t n_elems, int log2_gs, cudaStream_t st);
 }  // namespace act
 
 extern "C" int act_quant_pack(const void* x, int dtype, int64_t n_groups, int group_size, int bits,
@@ -30,13 +33,22 @@ extern "C" int act_quant_pack(const void* x, int dtype, int64_t n_groups, int gr
 {
     using namespace act;
     if (dtype != ACT_DTYPE_F32 && dtype != ACT_DTYPE_BF16 && dtype != ACT_DTYPE_F16) return ACT_ERR_DTYPE;
-    if (bits != 1 && bits != 2 && bits != 4 && bits != 8) return ACT_ERR_BITS;
+    if (bits != 1 && bits != 2 && bits != 3 && bits != 4 && bits != 8) return ACT_ERR_BITS;
     if (group_size < 32 || group_size > 1024 || (group_size & (group_size - 1))) return ACT_ERR_GROUP;
     if (n_groups < 0 || n_groups > (INT64_MAX >> 12)) return ACT_ERR_SIZE;
+    if (bits == 3 && (flags & ACT_FLAG_REF_COMPAT)) return ACT_ERR_UNSUPPORTED;
     if (n_groups == 0) return ACT_OK;
     if (!x || !packed || !scale || !mn) return ACT_ERR_NULL;
     if (((uintptr_t)x | (uintptr_t)packed | (uintptr_t)noise) & 15) return ACT_ERR_ALIGN;
     if (((uintptr_t)scale | (uintptr_t)mn) & 3) return ACT_ERR_ALIGN;
+    if (bits == 3) {
+        // bit-plane layout, kernels of their own (codec_bits3.cu)
+        int log2_gs = 5;
+        while ((1 << log2_gs) < group_size) ++log2_gs;
+        const int m3 = (flags & ACT_FLAG_ROUND_NEAREST) ? 2 : (noise ? 1 : 0);
+        return quant_pack3(x, dtype, noise, m3, seed, offset, packed, scale, mn, n_groups * group_size, log2_gs,
+                           static_cast<cudaStream_t>(stream)) == cudaSuccess ? ACT_OK : ACT_ERR_LAUNCH;
+    }
 
     int mode;
     if (flags & ACT_FLAG_REF_COMPAT) mode = kRefCompat;

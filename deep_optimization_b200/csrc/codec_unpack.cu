@@ -405,13 +405,19 @@ extern "C" int act_dequant_unpack_tiles(const void* packed, const float* scale, 
     return cudaGetLastError() == cudaSuccess ? ACT_OK : ACT_ERR_LAUNCH;
 }
 
+namespace act {
+// codec_bits3.cu
+cudaError_t dequant_unpack3(const void* packed, const float* scale, const float* mn, int out_dtype, void* y,
+                            int64_t n_elems, int log2_gs, cudaStream_t st);
+}  // namespace act
+
 extern "C" int act_dequant_unpack(const void* packed, const float* scale, const float* mn,
                                   int64_t n_groups, int group_size, int bits, int out_dtype,
                                   void* y, void* stream)
 {
     using namespace act;
     if (out_dtype != ACT_DTYPE_F32 && out_dtype != ACT_DTYPE_BF16 && out_dtype != ACT_DTYPE_F16) return ACT_ERR_DTYPE;
-    if (!bits_ok(bits)) return ACT_ERR_BITS;
+    if (!bits_ok(bits) && bits != 3) return ACT_ERR_BITS;
     if (!group_ok(group_size)) return ACT_ERR_GROUP;
     if (n_groups < 0 || n_groups > (INT64_MAX >> 12)) return ACT_ERR_SIZE;
     if (n_groups == 0) return ACT_OK;
@@ -421,6 +427,8 @@ extern "C" int act_dequant_unpack(const void* packed, const float* scale, const 
     while ((1 << log2_gs) < group_size) ++log2_gs;
     const int64_t n_elems = n_groups * group_size;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (bits == 3)          // bit-plane layout (codec_bits3.cu)
+        return dequant_unpack3(packed, scale, mn, out_dtype, y, n_elems, log2_gs, st) == cudaSuccess ? ACT_OK : ACT_ERR_LAUNCH;
     const uint8_t* p = static_cast<const uint8_t*>(packed);
     uint8_t* out = static_cast<uint8_t*>(y);
     if (out_dtype == ACT_DTYPE_F32) launch_unpack<ACT_DTYPE_F32>(bits, p, scale, mn, out, n_elems, log2_gs, st);

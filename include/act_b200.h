@@ -65,7 +65,7 @@ extern "C" {
 /*
  * Per-group quantise-and-pack of a saved activation.
  * Replaces torch.ops.act_lib.quant_pack_triton (AC/act_triton_kernel.py:336-368,
- * kernel :23-171) and cpp_extension.pack{1,2,4,8} (AC/cpp_extension/bind.cpp:10-14).
+ * kernel :23-171) and cpp_extension.pack{1,2,3,4,8} (AC/cpp_extension/bind.cpp:10-14).
  *
  *   x       [n_groups, group_size] of `dtype`, contiguous, 16-byte aligned
  *   noise   NULL, or fp32 [n_groups, group_size] of u in [0,1), 16-byte aligned
@@ -87,6 +87,11 @@ extern "C" {
  *                 ACT_FLAG_ROUND_NEAREST (0.5f-1e-6f on the 1/256 grid, a tie going down).
  *                 Any other group uses the formula of the first case with u = h/256
  *                 (u = 0.5f-1e-6f for round to nearest).
+ * bits = 3 (cpp_extension.pack3 / unpack3, AC/cpp_extension/bind.cpp:12,18) is taken too, with
+ * the same arithmetic (eight levels) and a bit-plane layout, since 3-bit codes do not fill a
+ * word: every 32 consecutive elements take three consecutive words, bit l of word p = bit p of
+ * the code of element l (the reference's kernel stores planes too, in its ballot order).  Not
+ * with ACT_FLAG_REF_COMPAT.  act_dequant_unpack reads the same layout.
  */
 ACT_API int act_quant_pack(const void* x, int dtype, int64_t n_groups, int group_size, int bits,
                    const float* noise, uint64_t seed, uint64_t offset, int flags,
@@ -95,7 +100,7 @@ ACT_API int act_quant_pack(const void* x, int dtype, int64_t n_groups, int group
 /*
  * Unpack-and-dequantise: y = fma(code, scale, min) rounded to `out_dtype`.
  * Replaces torch.ops.act_lib.dequant_unpack_triton (AC/act_triton_kernel.py:372-395,
- * kernel :174-241) and cpp_extension.unpack{1,2,4,8} (AC/cpp_extension/bind.cpp:16-20).
+ * kernel :174-241) and cpp_extension.unpack{1,2,3,4,8} (AC/cpp_extension/bind.cpp:16-20).
  *   y  [n_groups, group_size] of out_dtype, 16-byte aligned.
  */
 ACT_API int act_dequant_unpack(const void* packed, const float* scale, const float* min,

@@ -212,10 +212,11 @@ static int quant_pack_from(const void *x, int dtype, int64_t n_groups, int group
                            int bits, const float *noise, uint64_t seed, uint64_t offset,
                            int flags, float clamp_alpha, uint32_t *packed, float *scale,
                            float *mn_out, int64_t first_group) {
-    if (!valid_bits(bits) || !valid_group(group_size, bits) || dtype < 0 || dtype > 2) return 1;
+    if (!(valid_bits(bits) || bits == 3) || !valid_group(group_size, bits) || dtype < 0 || dtype > 2) return 1;
+    if (bits == 3 && (flags & FLAG_REF_COMPAT)) return 1;
     const int qmax = (1 << bits) - 1;
-    const int vpw = 32 / bits;
-    const int nwords = group_size / vpw;
+    const int vpw = 32 / bits;                         /* unused for the 3-bit planes */
+    const int nwords = group_size * bits / 32;
     const float half_c = 0.5f - 1e-6f;
     const int ref = (flags & FLAG_REF_COMPAT) != 0;
 
@@ -248,49 +249,62 @@ static int quant_pack_from(const void *x, int dtype, int64_t n_groups, int group
         uint32_t *pw = packed + g * (int64_t)nwords;
         const float inv = 1.0f / s;
         const int regular = (r == 0.0f) || (r >= 0x1p-50f && r <= 0x1p50f);
-        for (int w = 0; w < nwords; ++w) {
-            uint32_t word = 0;
-            for (int j = 0; j < vpw; ++j) {
-                const int i = w * vpw + j;
-                const float a = v[i] - mn;
-                int c;
-                if (ref) {
-                    /* act_triton_kernel.py:71,114,151-153: multiply by the reciprocal,
-                     * add the rounding constant, truncate, clamp                       */
-                    float prod = a * inv;
-                    float t = prod + half_c;
-                    if (!(t == t)) c = 0;
-                    else {
-                        if (t > 1.0e9f) t = 1.0e9f;
-                        if (t < -1.0e9f) t = -1.0e9f;
-                        c = (int)t;                 /* toward zero */
-                        if (c < 0) c = 0;
-                        if (c > qmax) c = qmax;
-                    }
-                } else if (noise && !(flags & FLAG_ROUND_NEAREST)) {
-                    const float q = a / s;
-                    const float t = q + noise[base + i];
-                    c = code_from_t(t, qmax);
-                } else {
-                    /* the two fixed-point modes: a hash byte, or 127 for round to nearest
-                     * (0.5f - 1e-6f on the 1/256 grid: a tie goes down)                   */
-                    const int nearest = (flags & FLAG_ROUND_NEAREST) != 0;
-                    const uint32_t h = nearest ? 127u
-                        : hash_byte((uint64_t)(first_group * group_size + base + i), seed, offset);
-                    if (regular) {
-                        /* one rounding onto the 2^-8 grid; 2^15 <= v < 2^16 for a regular group */
-                        const float v = fmaf(a, inv, 32768.0f);
-                        const uint32_t Q = f32_bits(v) - f32_bits(32768.0f);
-                        c = (int)((Q + h) >> 8);
-                    } else {
-                        const float u = nearest ? half_c : (float)h * (1.0f / 256.0f);
-                        const float t = a / s + u;
-                        c = code_from_t(t, qmax);
-                    }
+        uint8_t code[1024];
+        for (int i = 0; i < group_size; ++i) {
+            const float a = v[i] - mn;
+            int c;
+            if (ref) {
+                /* act_triton_kernel.py:71,114,151-153: multiply by the reciprocal,
+                 * add the rounding constant, truncate, clamp                       */
+                float prod = a * inv;
+                float t = prod + half_c;
+                if (!(t == t)) c = 0;
+                else {
+                    if (t > 1.0e9f) t = 1.0e9f;
+                    if (t < -1.0e9f) t = -1.0e9f;
+                    c = (int)t;                 /* toward zero */
+                    if (c < 0) c = 0;
+                    if (c > qmax) c = qmax;
                 }
-                word |= (uint32_t)c << (j * bits);
+            } else if (noise && !(flags & FLAG_ROUND_NEAREST)) {
+                const float q = a / s;
+                const float t = q + noise[base + i];
+                c = code_from_t(t, qmax);
+            } else {
+                /* the two fixed-point modes: a hash byte, or 127 for round to nearest
+                 * (0.5f - 1e-6f on the 1/256 grid: a tie goes down)                   */
+                const int nearest = (flags & FLAG_ROUND_NEAREST) != 0;
+                const uint32_t h = nearest ? 127u
+                    : hash_byte((uint64_t)(first_group * group_size + base + i), seed, offset);
+                if (regular) {
+                    /* one rounding onto the 2^-8 grid; 2^15 <= v < 2^16 for a regular group */
+                    const float vv = fmaf(a, inv, 32768.0f);
+                    const uint32_t Q = f32_bits(vv) - f32_bits(32768.0f);
+                    c = (int)((Q + h) >> 8);
+                } else {
+                    const float u = nearest ? half_c : (float)h * (1.0f / 256.0f);
+                    const float t = a / s + u;
+                    c = code_from_t(t, qmax);
+                }
             }
-            pw[w] = word;
+            code[i] = (uint8_t)c;
+        }
+        if (bits == 3) {
+            /* bit planes: 32 elements -> 3 words, bit l of word p = bit p of the code of element l
+             * (the cpp_extension kernels store planes too, in their ballot order:
+             * cpp_extension/include/quant_pack_1bit_sm90.cuh:140-175)                              */
+            for (int ch = 0; ch < group_size / 32; ++ch)
+                for (int p = 0; p < 3; ++p) {
+                    uint32_t word = 0;
+                    for (int l = 0; l < 32; ++l) word |= (uint32_t)((code[ch * 32 + l] >> p) & 1) << l;
+                    pw[ch * 3 + p] = word;
+                }
+        } else {
+            for (int w = 0; w < nwords; ++w) {
+                uint32_t word = 0;
+                for (int j = 0; j < vpw; ++j) word |= (uint32_t)code[w * vpw + j] << (j * bits);
+                pw[w] = word;
+            }
         }
     }
     return 0;
@@ -303,18 +317,23 @@ static int quant_pack_from(const void *x, int dtype, int64_t n_groups, int group
 ORACLE_EXPORT int oracle_dequant_unpack(const uint32_t *packed, const float *scale,
                                         const float *mn, int64_t n_groups, int group_size,
                                         int bits, int out_dtype, void *y) {
-    if (!valid_bits(bits) || !valid_group(group_size, bits) || out_dtype < 0 || out_dtype > 2) return 1;
-    const int vpw = 32 / bits;
-    const int nwords = group_size / vpw;
+    if (!(valid_bits(bits) || bits == 3) || !valid_group(group_size, bits) || out_dtype < 0 || out_dtype > 2) return 1;
+    const int vpw = (bits == 3) ? 32 : 32 / bits;      /* elements per word, or per 3-word chunk */
+    const int nwords = group_size / vpw;               /* words, or chunks */
     const uint32_t mask = (1u << bits) - 1u;
 #pragma omp parallel for schedule(static)
     for (int64_t g = 0; g < n_groups; ++g) {
         const float s = scale[g], m = mn[g];
-        const uint32_t *pw = packed + g * (int64_t)nwords;
+        const uint32_t *pw = packed + g * (int64_t)(group_size * bits / 32);
         for (int w = 0; w < nwords; ++w) {
-            const uint32_t word = pw[w];
+            const uint32_t word = (bits == 3) ? 0u : pw[w];
             for (int j = 0; j < vpw; ++j) {
-                const float c = (float)((word >> (j * bits)) & mask);
+                uint32_t code;
+                if (bits == 3)
+                    code = ((pw[w * 3] >> j) & 1u) | (((pw[w * 3 + 1] >> j) & 1u) << 1) | (((pw[w * 3 + 2] >> j) & 1u) << 2);
+                else
+                    code = (word >> (j * bits)) & mask;
+                const float c = (float)code;
                 const float val = fmaf(c, s, m);
                 const int64_t i = g * (int64_t)group_size + w * vpw + j;
                 if (out_dtype == DT_F32) ((float *)y)[i] = val;

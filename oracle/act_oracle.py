@@ -323,9 +323,16 @@ def np_quant_pack(x: np.ndarray, group_size: int, bits: int, noise: np.ndarray |
                 fx = ((Q.astype(np.int64) + h.astype(np.int64)) >> 8).astype(np.uint32)
                 regular = (r == 0) | ((r >= np.float32(2.0 ** -50)) & (r <= np.float32(2.0 ** 50)))
                 codes = np.where(regular[:, None], fx, codes)
-    shifts = (np.arange(vpw, dtype=np.uint32) * np.uint32(bits))
-    words = (codes.reshape(ng, group_size // vpw, vpw) << shifts).sum(axis=2, dtype=np.uint64)
-    packed = words.astype(np.uint32)
+    if bits == 3:
+        # bit planes: word p of a 32-element chunk holds bit p of its 32 codes, element l at bit l
+        ch = codes.reshape(ng, group_size // 32, 1, 32)
+        planes = (ch >> np.arange(3, dtype=np.uint32).reshape(1, 1, 3, 1)) & np.uint32(1)
+        words = (planes.astype(np.uint64) << np.arange(32, dtype=np.uint64)).sum(axis=3, dtype=np.uint64)
+        packed = words.reshape(ng, group_size * 3 // 32).astype(np.uint32)
+    else:
+        shifts = (np.arange(vpw, dtype=np.uint32) * np.uint32(bits))
+        words = (codes.reshape(ng, group_size // vpw, vpw) << shifts).sum(axis=2, dtype=np.uint64)
+        packed = words.astype(np.uint32)
     if flags & FLAG_META_BF16:
         s = bf16_bits_to_f32(f32_to_bf16_bits(s))
         mn = bf16_bits_to_f32(f32_to_bf16_bits(mn))
@@ -333,6 +340,11 @@ def np_quant_pack(x: np.ndarray, group_size: int, bits: int, noise: np.ndarray |
 
 
 def np_unpack_codes(packed: np.ndarray, group_size: int, bits: int) -> np.ndarray:
+    if bits == 3:
+        w = np.ascontiguousarray(packed, np.uint32).reshape(-1, group_size // 32, 3, 1)
+        b = (w >> np.arange(32, dtype=np.uint32)) & np.uint32(1)              # [NG, chunks, 3, 32]
+        c = b[:, :, 0] | (b[:, :, 1] << np.uint32(1)) | (b[:, :, 2] << np.uint32(2))
+        return c.reshape(c.shape[0], group_size)
     vpw = 32 // bits
     packed = np.ascontiguousarray(packed, np.uint32).reshape(-1, group_size // vpw)
     shifts = (np.arange(vpw, dtype=np.uint32) * np.uint32(bits))

@@ -38,7 +38,7 @@ def test_argument_errors_need_no_gpu(lib):
     bad = ctypes.c_void_p(16)
     qp = lib.act_quant_pack
     assert qp(bad, 7, 1, 128, 2, None, 0, 0, 0, 0.0, bad, bad, bad, None) == 1      # dtype
-    assert qp(bad, 0, 1, 128, 3, None, 0, 0, 0, 0.0, bad, bad, bad, None) == 2      # bits
+    assert qp(bad, 0, 1, 128, 5, None, 0, 0, 0, 0.0, bad, bad, bad, None) == 2      # bits
     assert qp(bad, 0, 1, 96, 2, None, 0, 0, 0, 0.0, bad, bad, bad, None) == 3       # group
     assert qp(bad, 0, -1, 128, 2, None, 0, 0, 0, 0.0, bad, bad, bad, None) == 5     # size
     assert qp(None, 0, 1, 128, 2, None, 0, 0, 0, 0.0, bad, bad, bad, None) == 6     # null

@@ -307,3 +307,30 @@ def test_module_utils_uses_tiles(cuda_device):
     assert y.shape == x.shape and y.dtype == torch.bfloat16
     step = s.reshape(4, 6, 2, 3, 1, 1).expand(4, 6, 2, 3, 16, 16).permute(0, 1, 2, 4, 3, 5).reshape(4, 6, 32, 48)
     assert ((y.float() - x.float()).abs() <= step * 1.01 + 0.02 * x.float().abs()).all()
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=("f32", "bf16", "f16"))
+@pytest.mark.parametrize("gs", GROUPS)
+def test_three_bit_planes(oracle, cuda_device, dtype, gs):
+    """3-bit codes in the bit-plane layout (cpp_extension pack3 / unpack3): packed words, scale
+    and min bit-exact with the oracle in the noise-tensor, hash and nearest modes on an odd
+    number of groups; decoded values bit-exact; adversarial groups included."""
+    c = _codec()
+    x = torch.cat([relu_normal((75, gs), seed=3 + gs, dtype=dtype), adversarial_groups(gs).to(dtype)])
+    u = uniform_noise(x.shape, seed=2)
+    arr, tag = to_numpy(x)
+    xd, ud = x.to(cuda_device), u.to(cuda_device)
+    F = oracle
+    for name, gkw, okw in (("noise tensor", dict(noise=ud), dict(noise=u.numpy())),
+                           ("hash noise", dict(seed=1234, offset=77), dict(seed=1234, offset=77)),
+                           ("round nearest", dict(flags=F.FLAG_ROUND_NEAREST), dict(flags=F.FLAG_ROUND_NEAREST))):
+        got = c.quant_pack(xd, 3, gs, planes3=True, **gkw)
+        want = oracle.quant_pack(arr, gs, 3, dtype=tag, **okw)
+        _cmp_pack(oracle, got, want, f"3-bit {name} {tag} g{gs}")
+    ok = np.isfinite(want[2]) & np.isfinite(want[1])         # NaN payloads are not compared
+    y = c.dequant_unpack(got[0], got[1], got[2], 3, gs, out_dtype=dtype, planes3=True)
+    yw = oracle.dequant_unpack(want[0], want[1], want[2], gs, 3, out=tag)
+    g, _ = to_numpy(y)
+    assert np.array_equal(g.view(np.uint8).reshape(len(ok), -1)[ok], yw.view(np.uint8).reshape(len(ok), -1)[ok])
+    with pytest.raises(ValueError):
+        c.quant_pack(xd, 3, gs)                      # the act_lib contract: bits in (1,2,4,8)

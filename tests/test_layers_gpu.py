@@ -113,7 +113,7 @@ def test_controller_end_to_end_step(cuda_device):
 def test_cpp_extension_mirror(cuda_device):
     from deep_optimization_b200 import cpp_extension as cx
     x = torch.relu(torch.randn(4, 6, 256, device=cuda_device)).to(torch.bfloat16)
-    for bits, pack, unpack in ((2, cx.pack2, cx.unpack2), (8, cx.pack8, cx.unpack8)):
+    for bits, pack, unpack in ((2, cx.pack2, cx.unpack2), (3, cx.pack3, cx.unpack3), (8, cx.pack8, cx.unpack8)):
         out = torch.zeros(4 * 6 * 8 * bits, dtype=torch.int32, device=cuda_device)
         scaler = torch.empty(4, 6, dtype=torch.bfloat16, device=cuda_device)
         mn = torch.empty(24, dtype=torch.bfloat16, device=cuda_device)
@@ -125,4 +125,4 @@ def test_cpp_extension_mirror(cuda_device):
     lo, hi = cx.min_max_kernel(x)
     assert torch.equal(lo, x.float().amin(-1)) and torch.equal(hi, x.float().amax(-1))
     with pytest.raises(NotImplementedError):
-        cx.pack3(x, None, None, None, 0.0)
+        cx.pack_mixed_precision_cuda(x, None, None, None, 0.0)

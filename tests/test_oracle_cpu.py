@@ -187,3 +187,32 @@ def test_fp8_gemm_small(oracle):
     ref = (A8.double() @ B8.double()).float() * sa[:, None] * sb[None, :]
     assert np.array_equal(Cf, ref.numpy())
     assert np.allclose(Cf, (A @ B).numpy(), rtol=0.2, atol=0.5)
+
+
+@pytest.mark.parametrize("gs", GROUPS)
+def test_three_bit_planes(oracle, gs):
+    """3-bit codes (the cpp_extension pack3 / unpack3 width): C against numpy in the three
+    non-reference modes, codes <= 7, round trip within one step, and the bit-plane layout on a
+    hand-made case: element l of a 32-element chunk with code c sets bit l of word p for every
+    set bit p of c."""
+    x = relu_normal((20, gs), seed=300 + gs).numpy()
+    u = uniform_noise(x.shape, seed=3).numpy()
+    for kw in (dict(noise=u), dict(seed=11, offset=5), dict(flags=oracle.FLAG_ROUND_NEAREST)):
+        a = oracle.quant_pack(x, gs, 3, **kw)
+        b = oracle.np_quant_pack(x, gs, 3, **kw)
+        for p, q in zip(a, b):
+            assert np.array_equal(p.view(np.uint32), q.view(np.uint32)), kw.keys()
+        assert a[0].shape == (20, gs * 3 // 32)
+        codes = oracle.np_unpack_codes(a[0], gs, 3)
+        assert codes.max() <= 7
+        y = oracle.dequant_unpack(*a, gs, 3)
+        assert np.array_equal(y, oracle.np_dequant(*a, gs, 3))
+        assert (np.abs(y - x) <= a[1][:, None] * (1 + 1e-6)).all()
+    with pytest.raises(ValueError):
+        oracle.quant_pack(x, gs, 3, flags=oracle.FLAG_REF_COMPAT)
+    # values on the code points, no noise: code of element i is i % 8
+    ramp = np.tile(np.arange(8, dtype=np.float32), gs // 8)[None, :]
+    packed, scale, mn = oracle.quant_pack(ramp, gs, 3, noise=np.zeros_like(ramp))
+    assert scale[0] == 1.0 and mn[0] == 0.0
+    want = [sum(((l % 8) >> p & 1) << l for l in range(32)) for p in range(3)]
+    assert packed[0, :3].tolist() == want and packed[0, -3:].tolist() == want
