@@ -47,11 +47,6 @@ def get_mode() -> str:
     return _MODE
 
 
-def _no_alam(avg_alam: bool) -> None:
-    if avg_alam:
-        raise NotImplementedError("AVG_ALAM sub-group averaging is not built in this backend")
-
-
 IMPL = {}
 
 
@@ -77,7 +72,6 @@ def op(name: str):
 def quant_pack_triton(x: torch.Tensor, bits: int, group_size: int, avg_alam: bool, alam_bits: int,
                       clamp: bool, clamp_alpha: float, noise: Optional[torch.Tensor] = None,
                       seed: Optional[int] = None) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-    _no_alam(avg_alam)
     N, G, gs = x.shape
     if gs != group_size:
         raise ValueError(f"last dimension {gs} != group_size {group_size}")
@@ -89,8 +83,13 @@ def quant_pack_triton(x: torch.Tensor, bits: int, group_size: int, avg_alam: boo
         if clamp:
             flags |= _lib.ACT_FLAG_REF_CLAMP
             alpha = clamp_alpha
-    packed, scale, mn = codec.quant_pack(x, bits, group_size, noise=noise, seed=seed, flags=flags,
-                                         clamp_alpha=alpha)
+    if avg_alam:
+        # one code per alam_bits consecutive elements (act_triton_kernel.py:116-118, 344-347)
+        packed, scale, mn = codec.quant_pack_avg(x, bits, group_size, alam_bits, noise=noise, seed=seed,
+                                                 flags=flags, clamp_alpha=alpha)
+    else:
+        packed, scale, mn = codec.quant_pack(x, bits, group_size, noise=noise, seed=seed, flags=flags,
+                                             clamp_alpha=alpha)
     return packed, scale.view(N, G), mn.view(N, G)
 
 
@@ -98,6 +97,8 @@ def quant_pack_triton(x: torch.Tensor, bits: int, group_size: int, avg_alam: boo
 def _(x, bits, group_size, avg_alam, alam_bits, clamp, clamp_alpha, noise=None, seed=None):
     N, G = x.shape[:2]
     _, nwords, _ = _bits_consts(bits, group_size)
+    if avg_alam:
+        nwords = -(-nwords // alam_bits)
     return (x.new_empty((N * G, nwords), dtype=torch.int32),
             x.new_empty((N, G), dtype=torch.float32), x.new_empty((N, G), dtype=torch.float32))
 
@@ -105,9 +106,11 @@ def _(x, bits, group_size, avg_alam, alam_bits, clamp, clamp_alpha, noise=None, 
 @_op("dequant_unpack_triton")
 def dequant_unpack_triton(packed: torch.Tensor, scale: torch.Tensor, xmin: torch.Tensor, bits: int,
                           group_size: int, avg_alam: bool, alam_bits: int) -> torch.Tensor:
-    _no_alam(avg_alam)
     N, G = scale.shape
-    y = codec.dequant_unpack(packed, scale, xmin, bits, group_size, out_dtype=torch.bfloat16)
+    if avg_alam:
+        y = codec.dequant_unpack_avg(packed, scale, xmin, bits, group_size, alam_bits, out_dtype=torch.bfloat16)
+    else:
+        y = codec.dequant_unpack(packed, scale, xmin, bits, group_size, out_dtype=torch.bfloat16)
     return y.view(N, G, group_size)
 
 

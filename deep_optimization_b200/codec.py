@@ -138,6 +138,64 @@ def dequant_unpack(packed: torch.Tensor, scale: torch.Tensor, mn: torch.Tensor, 
     return y
 
 
+def quant_pack_avg(x: torch.Tensor, bits: int, group_size: int, avg: int,
+                   noise: Optional[torch.Tensor] = None, seed: Optional[int] = None,
+                   offset: Optional[int] = None, flags: int = 0, clamp_alpha: float = 0.0
+                   ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Sub-group averaging (the reference's AVG_ALAM): one code per `avg` consecutive elements.
+    Returns (packed int32 [NG, group_size*bits/(32*avg)], scale fp32 [NG], min fp32 [NG])."""
+    global _next_offset
+    _, nwords, _ = _bits_consts(bits, group_size)
+    if avg not in (2, 4, 8) or nwords % avg:
+        raise ValueError(f"avg must be 2, 4 or 8 and divide the {nwords} words of a group, got {avg}")
+    _require_cuda(x, "x")
+    if x.dtype not in _DTYPES:
+        raise TypeError(f"unsupported activation dtype {x.dtype}")
+    x = x.contiguous()
+    if x.numel() % group_size:
+        raise ValueError("numel must be a multiple of group_size")
+    ng = x.numel() // group_size
+    packed = torch.empty((ng, nwords // avg), dtype=torch.int32, device=x.device)
+    scale = torch.empty((ng,), dtype=torch.float32, device=x.device)
+    mn = torch.empty((ng,), dtype=torch.float32, device=x.device)
+    if noise is not None:
+        _require_cuda(noise, "noise")
+        noise = noise.to(torch.float32).contiguous()
+        if noise.numel() != x.numel():
+            raise ValueError("noise must have as many elements as x")
+    if seed is None:
+        seed = _default_seed
+    if offset is None:
+        offset = _next_offset
+        _next_offset += 1
+    with _device_of(x):
+        rc = _lib.load().act_quant_pack_avg(
+            x.data_ptr(), _DTYPES[x.dtype], ng, group_size, bits, avg,
+            noise.data_ptr() if noise is not None else None,
+            seed & 0xFFFFFFFFFFFFFFFF, offset & 0xFFFFFFFFFFFFFFFF, flags, float(clamp_alpha),
+            packed.data_ptr(), scale.data_ptr(), mn.data_ptr(), _stream_ptr(x))
+    _lib.check(rc, "act_quant_pack_avg")
+    return packed, scale, mn
+
+
+def dequant_unpack_avg(packed: torch.Tensor, scale: torch.Tensor, mn: torch.Tensor, bits: int,
+                       group_size: int, avg: int, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """Inverse of quant_pack_avg: every code repeated `avg` times, [NG, group_size] of out_dtype."""
+    _bits_consts(bits, group_size)
+    _require_cuda(packed, "packed")
+    packed = packed.contiguous()
+    scale = scale.to(torch.float32).contiguous()
+    mn = mn.to(torch.float32).contiguous()
+    ng = scale.numel()
+    y = torch.empty((ng, group_size), dtype=out_dtype, device=packed.device)
+    with _device_of(packed):
+        rc = _lib.load().act_dequant_unpack_avg(packed.data_ptr(), scale.data_ptr(), mn.data_ptr(), ng,
+                                                group_size, bits, avg, _DTYPES[out_dtype], y.data_ptr(),
+                                                _stream_ptr(packed))
+    _lib.check(rc, "act_dequant_unpack_avg")
+    return y
+
+
 def tiles_supported(x: torch.Tensor, group_size: int) -> bool:
     """4-D contiguous CUDA activations whose group is a square tile of 8, 16 or 32 that divides
     H and W: the shapes quant_pack_tiles / dequant_unpack_tiles take."""

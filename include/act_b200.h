@@ -108,6 +108,25 @@ ACT_API int act_dequant_unpack(const void* packed, const float* scale, const flo
                        void* stream);
 
 /*
+ * Sub-group averaging, the AVG_ALAM switch of the reference's live kernels
+ * (AC/act_triton_kernel.py:116-118 and :212-215): `avg` (2, 4 or 8) consecutive elements of a
+ * group share one code, so packed holds group_size*bits/(32*avg) words per group (a whole
+ * number, else ACT_ERR_GROUP) and decoding repeats every code avg times.  min, max and scale as
+ * in act_quant_pack.  With ACT_FLAG_REF_COMPAT: qf_i = RN(RN((x_i-min) * RN(1/s)) + (0.5f-1e-6f)),
+ * m = (qf_0 + ... + qf_{avg-1}) / avg summed left to right in fp32, code = clamp(trunc(m))
+ * (clamp, tanh and bf16-meta flags as in act_quant_pack).  Otherwise q_i = RN((x_i-min) / s),
+ * m likewise, code = clamp(floor(RN(m + u))) with u the noise of the sub-group's first
+ * element: its noise-tensor value, its hash byte / 256, or 0.5f-1e-6f for round to nearest.
+ * The reference sums in a tree and its decoder adds Gaussian noise to the codes; neither is
+ * reproduced.
+ */
+ACT_API int act_quant_pack_avg(const void* x, int dtype, int64_t n_groups, int group_size, int bits, int avg,
+                       const float* noise, uint64_t seed, uint64_t offset, int flags,
+                       float clamp_alpha, void* packed, float* scale, float* min, void* stream);
+ACT_API int act_dequant_unpack_avg(const void* packed, const float* scale, const float* min, int64_t n_groups,
+                           int group_size, int bits, int avg, int out_dtype, void* y, void* stream);
+
+/*
  * The same two kernels on spatial tiles, without the permute-and-copy the reference makes first
  * (AC/modules/tensor_act_reshape_utils.py:82-154): x and y are [n_planes, height, width]
  * (n_planes = N*C), a group is one tile x tile block of one plane (tile = 8, 16 or 32, i.e.

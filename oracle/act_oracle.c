@@ -310,6 +310,107 @@ static int quant_pack_from(const void *x, int dtype, int64_t n_groups, int group
     return 0;
 }
 
+/* ------------------------------------------------- sub-group averaging (AVG_ALAM)
+ * act_triton_kernel.py:116-118 (quant_pack_kernel) and :212-215 (dequant_unpack_kernel):
+ * the quotients of `avg` consecutive elements are averaged before rounding, so a group
+ * stores group_size/avg codes, and decoding repeats each code `avg` times.  Sums run left
+ * to right in fp32 (Triton reduces in a tree); the noise of a sub-group is that of its
+ * first element; no fixed-point path; the reference's decoder noise is not reproduced.  */
+ORACLE_EXPORT int oracle_quant_pack_avg(const void *x, int dtype, int64_t n_groups, int group_size,
+                                        int bits, int avg, const float *noise, uint64_t seed,
+                                        uint64_t offset, int flags, float clamp_alpha,
+                                        uint32_t *packed, float *scale, float *mn_out) {
+    if (!valid_bits(bits) || !valid_group(group_size, bits) || dtype < 0 || dtype > 2) return 1;
+    if ((avg != 2 && avg != 4 && avg != 8) || (group_size * bits) % (32 * avg)) return 1;
+    const int qmax = (1 << bits) - 1;
+    const int vpw = 32 / bits;
+    const int ncodes = group_size / avg;
+    const int nwords = ncodes / vpw;
+    const float half_c = 0.5f - 1e-6f;
+    const int ref = (flags & FLAG_REF_COMPAT) != 0;
+#pragma omp parallel for schedule(static)
+    for (int64_t g = 0; g < n_groups; ++g) {
+        float v[1024];
+        const int64_t base = g * group_size;
+        for (int i = 0; i < group_size; ++i) {
+            float f = load_as_f32(x, dtype, base + i);
+            if (ref && (flags & FLAG_REF_CLAMP)) {
+                if (f < -clamp_alpha) f = -clamp_alpha;
+                if (f > clamp_alpha) f = clamp_alpha;
+            }
+            if (ref && (flags & FLAG_REF_TANH)) f = tanhf(f / 0.5f) * 0.5f;
+            v[i] = f;
+        }
+        float mn = v[0], mx = v[0];
+        for (int i = 1; i < group_size; ++i) { mn = min_ord(mn, v[i]); mx = max_ord(mx, v[i]); }
+        const float r = mx - mn;
+        float s = r / (float)qmax;
+        if (!(s > 0.0f)) s = 1.0f;
+        scale[g] = (flags & FLAG_META_BF16) ? bf16_to_f32(f32_to_bf16(s)) : s;
+        mn_out[g] = (flags & FLAG_META_BF16) ? bf16_to_f32(f32_to_bf16(mn)) : mn;
+        const float inv = 1.0f / s;
+        uint32_t *pw = packed + g * (int64_t)nwords;
+        for (int w = 0; w < nwords; ++w) pw[w] = 0;
+        for (int c = 0; c < ncodes; ++c) {
+            float sum = 0.0f;
+            for (int k = 0; k < avg; ++k) {
+                const float a = v[c * avg + k] - mn;
+                float q;
+                if (ref) { const float prod = a * inv; q = prod + half_c; }
+                else q = a / s;
+                sum = (k == 0) ? q : sum + q;
+            }
+            const float m = sum * (1.0f / (float)avg);
+            int code;
+            if (ref) {
+                if (!(m == m)) code = 0;
+                else {
+                    float t = m;
+                    if (t > 1.0e9f) t = 1.0e9f;
+                    if (t < -1.0e9f) t = -1.0e9f;
+                    code = (int)t;
+                    if (code < 0) code = 0;
+                    if (code > qmax) code = qmax;
+                }
+            } else {
+                float u;
+                if (flags & FLAG_ROUND_NEAREST) u = half_c;
+                else if (noise) u = noise[base + c * avg];
+                else u = (float)hash_byte((uint64_t)(base + c * avg), seed, offset) * (1.0f / 256.0f);
+                const float t = m + u;
+                code = code_from_t(t, qmax);
+            }
+            pw[c / vpw] |= (uint32_t)code << ((c % vpw) * bits);
+        }
+    }
+    return 0;
+}
+
+ORACLE_EXPORT int oracle_dequant_unpack_avg(const uint32_t *packed, const float *scale, const float *mn,
+                                            int64_t n_groups, int group_size, int bits, int avg,
+                                            int out_dtype, void *y) {
+    if (!valid_bits(bits) || !valid_group(group_size, bits) || out_dtype < 0 || out_dtype > 2) return 1;
+    if ((avg != 2 && avg != 4 && avg != 8) || (group_size * bits) % (32 * avg)) return 1;
+    const int vpw = 32 / bits;
+    const int nwords = group_size / avg / vpw;
+    const uint32_t mask = (1u << bits) - 1u;
+#pragma omp parallel for schedule(static)
+    for (int64_t g = 0; g < n_groups; ++g) {
+        const float s = scale[g], m = mn[g];
+        const uint32_t *pw = packed + g * (int64_t)nwords;
+        for (int i = 0; i < group_size; ++i) {
+            const int c = i / avg;
+            const float code = (float)((pw[c / vpw] >> ((c % vpw) * bits)) & mask);
+            const float val = fmaf(code, s, m);
+            const int64_t e = g * (int64_t)group_size + i;
+            if (out_dtype == DT_F32) ((float *)y)[e] = val;
+            else if (out_dtype == DT_BF16) ((uint16_t *)y)[e] = f32_to_bf16(val);
+            else ((uint16_t *)y)[e] = f32_to_f16(val);
+        }
+    }
+    return 0;
+}
+
 /* ---------------------------------------------------------- dequant-unpack
  * y = fma(code, scale, min) rounded once to fp32, then to the output type
  * (the Triton kernel's q*scale+min is contracted to one FMA when compiled for

@@ -59,6 +59,8 @@ def lib() -> ctypes.CDLL:
         L.oracle_quant_pack.argtypes = [vp, i32, i64, i32, i32, vp, u64, u64, i32, f32, vp, vp, vp]
         L.oracle_quant_pack_slice.argtypes = [vp, i32, i64, i32, i32, vp, u64, u64, i32, f32, vp, vp, vp, i64]
         L.oracle_dequant_unpack.argtypes = [vp, vp, vp, i64, i32, i32, i32, vp]
+        L.oracle_quant_pack_avg.argtypes = [vp, i32, i64, i32, i32, i32, vp, u64, u64, i32, f32, vp, vp, vp]
+        L.oracle_dequant_unpack_avg.argtypes = [vp, vp, vp, i64, i32, i32, i32, i32, vp]
         L.oracle_pack_bits.argtypes = [vp, i64, i32, i32, vp]
         L.oracle_unpack_bits.argtypes = [vp, i64, i32, i32, vp]
         L.oracle_minmax.argtypes = [vp, i32, i64, i64, vp, vp]
@@ -138,6 +140,81 @@ def dequant_unpack(packed: np.ndarray, scale: np.ndarray, mn: np.ndarray, group_
     if rc:
         raise ValueError("oracle_dequant_unpack rejected its arguments")
     return y
+
+
+def quant_pack_avg(x: np.ndarray, group_size: int, bits: int, avg: int, noise: np.ndarray | None = None,
+                   seed: int = 0, offset: int = 0, flags: int = 0, clamp_alpha: float = 0.0,
+                   dtype: str | None = None):
+    """Sub-group averaging: one code per `avg` consecutive elements.  Returns (packed uint32
+    [NG, group_size*bits/(32*avg)], scale f32 [NG], min f32 [NG])."""
+    x = np.ascontiguousarray(x)
+    code = _dtype_code(x, dtype)
+    ng, rem = divmod(x.size, group_size)
+    assert rem == 0
+    packed = np.empty((ng, group_size * bits // (32 * avg)), np.uint32)
+    scale = np.empty(ng, np.float32)
+    mn = np.empty(ng, np.float32)
+    if noise is not None:
+        noise = np.ascontiguousarray(noise, np.float32)
+    rc = lib().oracle_quant_pack_avg(_ptr(x), code, ng, group_size, bits, avg, _ptr(noise), seed, offset,
+                                     flags, clamp_alpha, _ptr(packed), _ptr(scale), _ptr(mn))
+    if rc:
+        raise ValueError(f"oracle_quant_pack_avg rejected bits={bits} group_size={group_size} avg={avg}")
+    return packed, scale, mn
+
+
+def dequant_unpack_avg(packed: np.ndarray, scale: np.ndarray, mn: np.ndarray, group_size: int,
+                       bits: int, avg: int, out: str = "f32") -> np.ndarray:
+    packed = np.ascontiguousarray(packed, np.uint32)
+    scale = np.ascontiguousarray(scale, np.float32)
+    mn = np.ascontiguousarray(mn, np.float32)
+    ng = scale.size
+    code = {"f32": DT_F32, "bf16": DT_BF16, "f16": DT_F16}[out]
+    y = np.empty((ng, group_size), {DT_F32: np.float32, DT_BF16: np.uint16, DT_F16: np.float16}[code])
+    rc = lib().oracle_dequant_unpack_avg(_ptr(packed), _ptr(scale), _ptr(mn), ng, group_size, bits, avg,
+                                         code, _ptr(y))
+    if rc:
+        raise ValueError("oracle_dequant_unpack_avg rejected its arguments")
+    return y
+
+
+def np_quant_pack_avg(x: np.ndarray, group_size: int, bits: int, avg: int, noise: np.ndarray | None = None,
+                      seed: int = 0, offset: int = 0, flags: int = 0):
+    """numpy restatement of oracle_quant_pack_avg (finite fp32 inputs; no clamp/tanh, fp32 meta)."""
+    qmax = (1 << bits) - 1
+    vpw = 32 // bits
+    v = np.ascontiguousarray(x, np.float32).reshape(-1, group_size)
+    ng = v.shape[0]
+    mn, mx = np_group_minmax(v)
+    r = (mx - mn).astype(np.float32)
+    s = (r / np.float32(qmax)).astype(np.float32)
+    s = np.where(s > 0, s, np.float32(1.0)).astype(np.float32)
+    a = (v - mn[:, None]).astype(np.float32)
+    if flags & FLAG_REF_COMPAT:
+        inv = (np.float32(1.0) / s).astype(np.float32)
+        q = ((a * inv[:, None]).astype(np.float32) + HALF_C).astype(np.float32)
+    else:
+        q = (a / s[:, None]).astype(np.float32)
+    q = q.reshape(ng, group_size // avg, avg)
+    total = q[:, :, 0].copy()
+    for k in range(1, avg):
+        total = (total + q[:, :, k]).astype(np.float32)
+    m = (total * np.float32(1.0 / avg)).astype(np.float32)
+    if flags & FLAG_REF_COMPAT:
+        codes = np.clip(np.trunc(m), 0, qmax).astype(np.uint32)
+    else:
+        if flags & FLAG_ROUND_NEAREST:
+            u = np.full(m.shape, HALF_C, np.float32)
+        elif noise is not None:
+            u = np.ascontiguousarray(noise, np.float32).reshape(ng, group_size // avg, avg)[:, :, 0]
+        else:
+            h = np_hash_bytes(seed, offset, 0, v.size).reshape(ng, group_size // avg, avg)[:, :, 0]
+            u = h.astype(np.float32) * np.float32(1.0 / 256.0)
+        t = (m + u).astype(np.float32)
+        codes = np.where(t >= 0, np.minimum(np.floor(t), qmax), 0).astype(np.uint32)
+    shifts = (np.arange(vpw, dtype=np.uint32) * np.uint32(bits))
+    words = (codes.reshape(ng, -1, vpw) << shifts).sum(axis=2, dtype=np.uint64).astype(np.uint32)
+    return words, s, mn.astype(np.float32)
 
 
 def pack_bits(x: np.ndarray, group_size: int, bits: int) -> np.ndarray:

@@ -334,3 +334,52 @@ def test_three_bit_planes(oracle, cuda_device, dtype, gs):
     assert np.array_equal(g.view(np.uint8).reshape(len(ok), -1)[ok], yw.view(np.uint8).reshape(len(ok), -1)[ok])
     with pytest.raises(ValueError):
         c.quant_pack(xd, 3, gs)                      # the act_lib contract: bits in (1,2,4,8)
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=("f32", "bf16", "f16"))
+@pytest.mark.parametrize("bits", BITS)
+@pytest.mark.parametrize("avg", (2, 4, 8))
+def test_sub_group_averaging(oracle, cuda_device, dtype, bits, avg):
+    """AVG_ALAM (one code per `avg` neighbours): packed words, scale and min bit-exact with the
+    oracle in the four modes, decoded values bit-exact, odd group counts, all group sizes that
+    give whole words."""
+    c = _codec()
+    F = oracle
+    for gs in GROUPS:
+        if (gs * bits) % (32 * avg):
+            with pytest.raises(ValueError):
+                c.quant_pack_avg(torch.zeros(gs, device=cuda_device), bits, gs, avg)
+            continue
+        x = relu_normal((37, gs), seed=bits + gs + avg, dtype=dtype)
+        u = uniform_noise(x.shape, seed=2)
+        arr, tag = to_numpy(x)
+        xd, ud = x.to(cuda_device), u.to(cuda_device)
+        ref = F.FLAG_REF_COMPAT | F.FLAG_META_BF16 | F.FLAG_REF_CLAMP
+        for name, gkw, okw in (("noise tensor", dict(noise=ud), dict(noise=u.numpy())),
+                               ("hash noise", dict(seed=1234, offset=77), dict(seed=1234, offset=77)),
+                               ("round nearest", dict(flags=F.FLAG_ROUND_NEAREST), dict(flags=F.FLAG_ROUND_NEAREST)),
+                               ("ref compat", dict(flags=ref, clamp_alpha=1.5), dict(flags=ref, clamp_alpha=1.5))):
+            got = c.quant_pack_avg(xd, bits, gs, avg, **gkw)
+            want = oracle.quant_pack_avg(arr, gs, bits, avg, dtype=tag, **okw)
+            _cmp_pack(oracle, got, want, f"avg{avg} {name} {tag} b{bits} g{gs}")
+        y = c.dequant_unpack_avg(got[0], got[1], got[2], bits, gs, avg, out_dtype=dtype)
+        yw = oracle.dequant_unpack_avg(want[0], want[1], want[2], gs, bits, avg, out=tag)
+        g, _ = to_numpy(y)
+        assert np.array_equal(g.view(np.uint8), yw.view(np.uint8))
+
+
+def test_avg_alam_through_the_operators(cuda_device):
+    """quantize / dequantize with AVG_ALAM set: the packed tensor shrinks by alam_bits and the
+    decoded activation is piecewise constant over alam_bits neighbours, near the input's local mean."""
+    from deep_optimization_b200.modules.module_utils import unified_dequantize, unified_quantize
+    meta = {"t": {"bits": 2, "pack_only": False, "group_size": 256, "act_padding": False, "N": 4,
+                  "AVG_ALAM": True, "ALAM_BITS": 4, "DIVISION": None}}
+    x = torch.relu(torch.randn(4, 8, 10, 32, device=cuda_device)).to(torch.bfloat16)   # flat grouping (H % 16 != 0)
+    q, q_meta, _ = unified_quantize(x, None, "t", meta, clamp=False, clamp_alpha=0.0)
+    assert q[0].shape == (x.numel() // 256, 256 * 2 // 32 // 4)
+    y = unified_dequantize(q, q_meta, None)
+    assert y.shape == x.shape
+    yg = y.float().reshape(-1, 4)
+    assert (yg == yg[:, :1]).all()
+    step = q[1].float().reshape(-1, 1).repeat_interleave(64, 0)
+    assert ((yg[:, :1] - x.float().reshape(-1, 4).mean(1, keepdim=True)).abs() <= step * 1.05 + 0.02).all()

@@ -216,3 +216,28 @@ def test_three_bit_planes(oracle, gs):
     assert scale[0] == 1.0 and mn[0] == 0.0
     want = [sum(((l % 8) >> p & 1) << l for l in range(32)) for p in range(3)]
     assert packed[0, :3].tolist() == want and packed[0, -3:].tolist() == want
+
+
+@pytest.mark.parametrize("bits", BITS)
+@pytest.mark.parametrize("avg", (2, 4, 8))
+def test_sub_group_averaging(oracle, bits, avg):
+    """AVG_ALAM: one code per `avg` neighbours.  C against numpy in all four modes; the decoded
+    value of a sub-group is one number, within one step of the sub-group's mean."""
+    for gs in (64, 256, 1024):
+        if (gs * bits) % (32 * avg):
+            with pytest.raises(ValueError):
+                oracle.quant_pack_avg(np.zeros(gs, np.float32), gs, bits, avg)
+            continue
+        x = relu_normal((24, gs), seed=bits * 10 + avg + gs).numpy()
+        u = uniform_noise(x.shape, seed=3).numpy()
+        for kw in (dict(noise=u), dict(seed=11, offset=5), dict(flags=oracle.FLAG_ROUND_NEAREST),
+                   dict(flags=oracle.FLAG_REF_COMPAT)):
+            a = oracle.quant_pack_avg(x, gs, bits, avg, **kw)
+            b = oracle.np_quant_pack_avg(x, gs, bits, avg, **kw)
+            for p, q in zip(a, b):
+                assert np.array_equal(p.view(np.uint32), q.view(np.uint32)), (gs, kw.keys())
+            assert a[0].shape == (24, gs * bits // (32 * avg))
+            y = oracle.dequant_unpack_avg(*a, gs, bits, avg).reshape(24, gs // avg, avg)
+            assert (y == y[:, :, :1]).all()
+            mean = x.reshape(24, gs // avg, avg).mean(2)
+            assert (np.abs(y[:, :, 0] - mean) <= a[1][:, None] * 1.001 + 1e-6).all()
