@@ -214,6 +214,12 @@ def _(packed, dy, scale, min, bits, N, G, group_size):
     return torch.empty_like(dy)
 
 
+def _no_alam(avg_alam: bool) -> None:
+    if avg_alam:
+        raise NotImplementedError("the fused activation operators do not average sub-groups; "
+                                  "layers with AVG_ALAM take the unfused path (quant_pack_triton)")
+
+
 @_op("silu_fwd_quan_pack")
 def silu_fwd_quan_pack(input: torch.Tensor, bits: int, group_size: int, pack_only: bool, avg_alam: bool,
                        alam_bits: int) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, int,
