@@ -303,7 +303,7 @@ def relu_fwd_pack(x: torch.Tensor, relu6: bool = False) -> Tuple[torch.Tensor, t
     _require_cuda(x, "x")
     # element-wise: a channels-last tensor is processed as it lies in memory (y and the mask
     # bits follow that order; relu_bwd_unpack must be given dy in the same memory format)
-    x = x if _channels_last(x) else x.contiguous()
+    x = x if is_channels_last(x) else x.contiguous()
     if x.numel() % 32:
         raise ValueError("numel must be a multiple of 32")
     y = torch.empty_like(x)
@@ -319,7 +319,7 @@ def relu_bwd_unpack(mask_bits: torch.Tensor, dy: torch.Tensor, channels_last: bo
     """dx = mask ? dy : 0.  `channels_last`: the mask was taken from a channels-last tensor, so
     dy is walked (after a conversion if it arrives in another format) in that memory order."""
     _require_cuda(dy, "dy")
-    if channels_last or _channels_last(dy):
+    if channels_last or is_channels_last(dy):
         dy = dy.contiguous(memory_format=torch.channels_last)
     else:
         dy = dy.contiguous()
@@ -377,7 +377,7 @@ def mul_dequant_unpack(packed: torch.Tensor, scale: torch.Tensor, mn: torch.Tens
 
 # ---------------------------------------------------------------- fused batch-norm kernels
 
-def _channels_last(x: torch.Tensor) -> bool:
+def is_channels_last(x: torch.Tensor) -> bool:
     """True for a 4-D tensor stored channel-minor (NHWC memory) and not also NCHW-contiguous."""
     return (x.dim() == 4 and not x.is_contiguous()
             and x.is_contiguous(memory_format=torch.channels_last))
@@ -388,7 +388,7 @@ def _bn_layout(x: torch.Tensor):
     channels-last tensor is taken as it lies in memory, [N*H*W, C] with hw = 1 (the kernels'
     channel-minor layout); anything else as contiguous [N, C, HW]."""
     C = x.shape[1]
-    if _channels_last(x) and C % 8 == 0:
+    if is_channels_last(x) and C % 8 == 0:
         return x, x.numel() // C, C, 1
     x = x.contiguous()
     return x, x.shape[0], C, x.numel() // (x.shape[0] * C)
@@ -400,7 +400,7 @@ def bn_fused_supported(x: torch.Tensor, group_size: int) -> bool:
     if x.dim() < 3 or not x.is_cuda or x.dtype not in _DTYPES:
         return False
     C = x.shape[1]
-    if _channels_last(x) and C % 8 == 0:
+    if is_channels_last(x) and C % 8 == 0:
         return C <= 4096 and x.numel() % group_size == 0
     hw = x.numel() // (x.shape[0] * C)
     return (hw % 4 == 0 and hw * (hw + 1024) < 2 ** 32 and C <= 4096
@@ -466,7 +466,7 @@ def bn_fwd_norm_quant_pack(x: torch.Tensor, mean: Optional[torch.Tensor], invstd
             raise ValueError("the residual add is fused together with the ReLU only")
         if residual.shape != x.shape or residual.dtype != x.dtype:
             raise ValueError("residual must have x's shape and type")
-        residual = residual.contiguous(memory_format=torch.channels_last) if hw == 1 and _channels_last(x) \
+        residual = residual.contiguous(memory_format=torch.channels_last) if hw == 1 and is_channels_last(x) \
             else residual.contiguous()
         mask = torch.empty((x.numel() // 8,), dtype=torch.uint8, device=x.device)
         with _device_of(x):

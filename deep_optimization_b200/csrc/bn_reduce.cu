@@ -13,6 +13,9 @@
 // HBM traffic: s_in bytes per element (plus bits/8 in backward); nothing is written but
 // 2 floats per block.
 //
+// A channels-last activation ([rows, C] in memory, "channel-minor", passed as HW = 1) is walked
+// by rows instead: bn_rows_reduce_kernel below, a thread owning eight channels.
+//
 // Replaces: Activation_Compression/modules/normalization/kernel_implementation.py:13-92
 // (bn_fwd_reduce) and :328-420 (bn_bwd_reduce_dequant_unpack_fused), whose programs
 // accumulate with one atomic per tile.

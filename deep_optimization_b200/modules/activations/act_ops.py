@@ -27,7 +27,7 @@ class _DOReLU(Function):
             # one pass: y and the 1-bit mask (act_ops.py:31-38 of the reference)
             y, packed, N, G = act_kernels.op("relu_fwd_fused_pack")(input, relu, relu6, 1, m["group_size"])
             ctx.meta_ngs = (N, G, m["group_size"])
-            ctx.channels_last = codec._channels_last(input)      # the mask follows the input's memory order
+            ctx.channels_last = codec.is_channels_last(input)      # the mask follows the input's memory order
             ctx.save_for_backward(packed)
             return y
         if relu6 and not relu:
@@ -51,7 +51,7 @@ class _DOReLU(Function):
             N, G, gs = ctx.meta_ngs
             if ctx.channels_last:
                 dy = dy.contiguous(memory_format=torch.channels_last)
-            elif codec._channels_last(dy):
+            elif codec.is_channels_last(dy):
                 dy = dy.contiguous()
             return act_kernels.op("relu_bwd_fused_unpack")(packed, dy, 1, N, G, gs), None, None, None, None
         mask = unified_dequantize((packed, None, None), ctx.q_meta, None)

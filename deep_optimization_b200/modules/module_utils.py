@@ -41,7 +41,7 @@ def _tiled_in_place(input, group_size, act_padding, pack_only, avg_alam):
 
 
 def quantize(input, bits, pack_only, group_size, act_padding, N, avg_alam, alam_bits, clamp, clamp_alpha):
-    if codec._channels_last(input):
+    if codec.is_channels_last(input):
         # [N, H*W*C] view of the memory as it lies; flat groups; the shape entry records the format
         n = input.shape[0]
         tensors, q_meta = quantize(input.permute(0, 2, 3, 1).reshape(n, -1), bits, pack_only, group_size,

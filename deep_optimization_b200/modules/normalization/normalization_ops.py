@@ -72,7 +72,7 @@ class _DOBatchNorm(Function):
             # fused path: one statistics pass, then normalise + affine + x_hat codec in one kernel
             # (normalization_ops.py:71-98 of the reference: bn_fwd_reduce + bn_fwd_norm_quant_pack_fused)
             # a channels-last activation is normalised and grouped as it lies in memory
-            ctx.channels_last = codec._channels_last(input) and C % 8 == 0
+            ctx.channels_last = codec.is_channels_last(input) and C % 8 == 0
             x = input if ctx.channels_last else input.contiguous()
             f32 = lambda t: None if t is None else (t if t.dtype == torch.float32 else t.float())
             rm, rv = f32(running_mean), f32(running_var)
