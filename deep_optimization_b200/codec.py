@@ -551,3 +551,39 @@ def bn_bwd_dx(packed: torch.Tensor, scale: torch.Tensor, mn: torch.Tensor, dy: t
                                         coef.data_ptr(), dx.data_ptr(), _stream_ptr(dy))
     _lib.check(rc, "act_bn_bwd_dx")
     return dx
+
+
+# ---------------------------------------------------------------- max pooling, channels-last
+
+def maxpool_supported(x: torch.Tensor, k: int, s: int, pad: int) -> bool:
+    """Channels-last 4-D CUDA activations with C a multiple of 8, window k <= 4, pad <= k/2."""
+    return (x.dim() == 4 and x.is_cuda and x.dtype in _DTYPES and is_channels_last(x) and x.shape[1] % 8 == 0
+            and 1 <= k <= 4 and s >= 1 and 0 <= 2 * pad <= k and x.shape[2] + 2 * pad >= k and x.shape[3] + 2 * pad >= k)
+
+
+def maxpool_fwd(x: torch.Tensor, k: int, s: int, pad: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """max_pool2d of a channels-last x: (y channels-last, idx int32 [N*OH*OW*C/8] holding the
+    4-bit window position of every maximum)."""
+    if not maxpool_supported(x, k, s, pad):
+        raise ValueError("maxpool_fwd takes a channels-last CUDA tensor with C % 8 == 0, k <= 4, pad <= k/2")
+    N, C, H, W = x.shape
+    OH, OW = (H + 2 * pad - k) // s + 1, (W + 2 * pad - k) // s + 1
+    y = torch.empty((N, C, OH, OW), dtype=x.dtype, device=x.device, memory_format=torch.channels_last)
+    idx = torch.empty((N * OH * OW * C // 8,), dtype=torch.int32, device=x.device)
+    with _device_of(x):
+        rc = _lib.load().act_maxpool_fwd_cl(x.data_ptr(), _DTYPES[x.dtype], N, H, W, C, k, s, pad, y.data_ptr(),
+                                            idx.data_ptr(), _stream_ptr(x))
+    _lib.check(rc, "act_maxpool_fwd_cl")
+    return y, idx
+
+
+def maxpool_bwd(idx: torch.Tensor, dy: torch.Tensor, input_shape, k: int, s: int, pad: int) -> torch.Tensor:
+    """Gradient of maxpool_fwd's input (channels-last) from its idx and dy."""
+    N, C, H, W = input_shape
+    dy = dy.contiguous(memory_format=torch.channels_last)
+    dx = torch.empty((N, C, H, W), dtype=dy.dtype, device=dy.device, memory_format=torch.channels_last)
+    with _device_of(dy):
+        rc = _lib.load().act_maxpool_bwd_cl(idx.data_ptr(), dy.data_ptr(), _DTYPES[dy.dtype], N, H, W, C, k, s, pad,
+                                            dx.data_ptr(), _stream_ptr(dy))
+    _lib.check(rc, "act_maxpool_bwd_cl")
+    return dx

@@ -23,7 +23,7 @@ from torch import nn
 from torch.fx.passes.shape_prop import ShapeProp
 
 from .layers import DOConv1d, DOConv2d, DOConv3d, DODepthPointConv2d, DOLinear, RMSNorm
-from .modules.activations.act_layers import DOGELU, DOReLU_Variance, DOSiLU
+from .modules.activations.act_layers import DOGELU, DOMaxPool2d, DOReLU_Variance, DOSiLU
 from .modules.normalization.normalization_layers import DOBatchNorm2d, DOSyncBatchNorm2d
 from .quantizer import Quantizer
 
@@ -277,6 +277,15 @@ class Controller:
                     if isinstance(mod, nn.LayerNorm):
                         parent_path, _, child = name.rpartition(".")
                         setattr(traced.get_submodule(parent_path), child, RMSNorm(mod.normalized_shape[-1]))
+            if self.config.get("compress_maxpool", True):
+                # not in the reference's swap list (controller.py:87): max-pool layers keep a 4-bit
+                # argmax for backward when their input is channels-last
+                for name, mod in list(traced.named_modules()):
+                    if type(mod) is nn.MaxPool2d:
+                        parent_path, _, child = name.rpartition(".")
+                        setattr(traced.get_submodule(parent_path), child,
+                                DOMaxPool2d(mod.kernel_size, mod.stride, mod.padding, mod.dilation,
+                                            mod.return_indices, mod.ceil_mode))
             self.fused_bn_add_relu = []
             if self.config.get("fuse_bn_relu", True):
                 if self.config.get("fuse_bn_add_relu", True):

@@ -4,7 +4,8 @@ In eval mode they are the stock modules; in training they save compressed state.
 its eval mode compute SiLU)."""
 from torch import nn
 
-from .act_ops import _DOGELU, _DOReLU, _DOSiLU
+from ... import codec
+from .act_ops import _DOMaxPool2d, _DOGELU, _DOReLU, _DOSiLU
 
 
 class DOReLU_Variance(nn.ReLU):
@@ -39,4 +40,25 @@ class DOGELU(nn.GELU):
     def forward(self, x):
         if self.training:
             return _DOGELU.apply(x, self.target_name, self.meta)
+        return super().forward(x)
+
+
+def _square(v):
+    if isinstance(v, (tuple, list)):
+        return v[0] if len(set(v)) == 1 else None
+    return v
+
+
+class DOMaxPool2d(nn.MaxPool2d):
+    """nn.MaxPool2d that, in training on a channels-last activation, saves a 4-bit argmax per
+    output instead of PyTorch's int64 index (an extension: the reference leaves pooling to
+    PyTorch).  Any other case (NCHW memory, dilation, ceil_mode, return_indices, windows above
+    4 x 4, channel counts that are not multiples of 8) is the stock operator."""
+
+    def forward(self, x):
+        k, s, p = _square(self.kernel_size), _square(self.stride if self.stride is not None else self.kernel_size), \
+            _square(self.padding)
+        if (self.training and x.requires_grad and not self.ceil_mode and not self.return_indices
+                and _square(self.dilation) == 1 and None not in (k, s, p) and codec.maxpool_supported(x, k, s, p)):
+            return _DOMaxPool2d.apply(x, k, s, p)
         return super().forward(x)

@@ -132,3 +132,23 @@ class _DOGELU(Function):
     @custom_bwd(device_type="cuda")
     def backward(ctx, dy):
         return _apply_derivative(ctx, dy), None, None
+
+
+class _DOMaxPool2d(Function):
+    """max_pool2d of a channels-last activation whose saved state is a 4-bit argmax per output
+    (PyTorch keeps an int64 index per output).  The caller checks `codec.maxpool_supported`."""
+
+    @staticmethod
+    @custom_fwd(device_type="cuda")
+    def forward(ctx, input, kernel_size, stride, padding):
+        y, idx = codec.maxpool_fwd(input, kernel_size, stride, padding)
+        ctx.geom = (tuple(input.shape), kernel_size, stride, padding)
+        ctx.save_for_backward(idx)
+        return y
+
+    @staticmethod
+    @custom_bwd(device_type="cuda")
+    def backward(ctx, dy):
+        (idx,) = ctx.saved_tensors
+        shape, k, s, pad = ctx.geom
+        return codec.maxpool_bwd(idx, dy, shape, k, s, pad), None, None, None

@@ -263,6 +263,21 @@ ACT_API int act_bn_relu_bwd_dx(const void* packed, const float* scale, const flo
                        int group_size, int bits, const float* coef, void* dx, void* stream);
 
 /*
+ * Max pooling on a channels-last activation with a 4-bit argmax saved for backward instead of
+ * PyTorch's int64 index per output (no counterpart in the reference, which leaves the pooling
+ * layer of its ResNet payload, Model/CNN/ResNetV1.py:63,99, to PyTorch): x [N, H, W, C] with C a
+ * multiple of 8, square window k <= 4, stride s, zero padding pad <= k/2, no dilation, floor
+ * output size OH = (H + 2*pad - k)/s + 1.  idx: uint32 [N*OH*OW*C/8], nibble j of a word = window
+ * position kh*k + kw of the maximum for channel 8q+j (ties: first position; a NaN wins).
+ * Backward gathers: dx[n,ih,iw,c] = sum of dy over the windows whose saved position is (ih,iw),
+ * accumulated in fp32 and rounded once.
+ */
+ACT_API int act_maxpool_fwd_cl(const void* x, int dtype, int64_t n, int h, int w, int c, int k, int s, int pad,
+                       void* y, void* idx, void* stream);
+ACT_API int act_maxpool_bwd_cl(const void* idx, const void* dy, int dtype, int64_t n, int h, int w, int c, int k,
+                       int s, int pad, void* dx, void* stream);
+
+/*
  * Per-row min and max of a contiguous [rows, cols] matrix.
  * Replaces cpp_extension.min_max_kernel (AC/cpp_extension/src/min_max_kernel.cu:66-141).
  */

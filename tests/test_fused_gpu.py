@@ -461,3 +461,50 @@ def test_bn_add_relu_module_matches_pytorch(cuda_device, channels_last):
     assert (x.grad - xr.grad).abs().max() < 0.05
     assert (bn.weight.grad - rb.weight.grad).norm() / rb.weight.grad.norm() < 0.03
     assert torch.allclose(bn.bias.grad, rb.bias.grad, rtol=1e-4, atol=1e-3)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", (torch.float32, torch.bfloat16), ids=("f32", "bf16"))
+@pytest.mark.parametrize("geom", [(3, 2, 1), (2, 2, 0), (3, 1, 1), (4, 2, 2), (3, 2, 0)])
+@pytest.mark.parametrize("shape", [(4, 64, 112, 112), (3, 8, 7, 9), (2, 16, 4, 4)])
+def test_maxpool_channels_last(cuda_device, dtype, geom, shape):
+    """Forward equals F.max_pool2d exactly (ties and repeated values included); backward equals
+    PyTorch's on fp32 exactly and on bf16 to one rounding of the sum; the saved state is 4 bits
+    per output."""
+    from deep_optimization_b200 import codec
+    k, s, p = geom
+    g = torch.Generator().manual_seed(51)
+    # few distinct values: many ties inside a window
+    x = torch.randint(-3, 4, shape, generator=g).to(dtype).to(cuda_device).contiguous(memory_format=torch.channels_last)
+    assert codec.maxpool_supported(x, k, s, p)
+    y, idx = codec.maxpool_fwd(x, k, s, p)
+    xr = x.detach().clone().requires_grad_()
+    yr = torch.nn.functional.max_pool2d(xr, k, s, p)
+    assert torch.equal(y, yr) and y.is_contiguous(memory_format=torch.channels_last)
+    assert idx.numel() * 32 == y.numel() * 4
+    dy = torch.randn(yr.shape, generator=g).to(dtype).to(cuda_device).contiguous(memory_format=torch.channels_last)
+    yr.backward(dy)
+    dx = codec.maxpool_bwd(idx, dy, x.shape, k, s, p)
+    if dtype == torch.float32:
+        assert torch.allclose(dx, xr.grad, rtol=1e-6, atol=1e-6)
+    else:
+        assert ((dx.float() - xr.grad.float()).abs() <= 2.0 ** -6 * (1 + xr.grad.float().abs())).all()
+
+
+@pytest.mark.gpu
+def test_maxpool_module_and_nan(cuda_device):
+    """DOMaxPool2d: channels-last training input takes the 4-bit path, an NCHW input or eval mode
+    the stock operator; a NaN in a window is that window's maximum."""
+    from deep_optimization_b200.modules.activations.act_layers import DOMaxPool2d
+    pool = DOMaxPool2d(3, 2, 1).train()
+    x = torch.randn(2, 16, 12, 12, device=cuda_device)
+    x[0, 3, 5, 5] = float("nan")
+    xc = x.contiguous(memory_format=torch.channels_last).requires_grad_()
+    xn = x.clone().requires_grad_()
+    yc, yn = pool(xc), pool(xn)
+    assert type(yc.grad_fn).__name__ == "_DOMaxPool2dBackward" and type(yn.grad_fn).__name__ != "_DOMaxPool2dBackward"
+    assert torch.equal(torch.nan_to_num(yc, nan=7.0), torch.nan_to_num(yn, nan=7.0)) and torch.isnan(yc).sum() == 4
+    g = torch.randn_like(yn)
+    yc.backward(g); yn.backward(g)
+    assert torch.allclose(xc.grad, xn.grad, rtol=1e-6, atol=1e-6)
+    assert pool.eval()(xc).grad_fn is None or type(pool(xc).grad_fn).__name__ != "_DOMaxPool2dBackward"
