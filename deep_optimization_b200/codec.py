@@ -553,6 +553,82 @@ def bn_bwd_dx(packed: torch.Tensor, scale: torch.Tensor, mn: torch.Tensor, dy: t
     return dx
 
 
+# ---------------------------------------------------------------- one call per batch-norm layer
+
+_bn_ws_bytes = {}
+
+
+def bn_forward(x: torch.Tensor, eps: float, weight: Optional[torch.Tensor], bias: Optional[torch.Tensor],
+               running_mean: Optional[torch.Tensor], running_var: Optional[torch.Tensor], momentum: float,
+               bits: int, group_size: int, flags: int = 0, relu: bool = False,
+               residual: Optional[torch.Tensor] = None, seed: Optional[int] = None,
+               offset: Optional[int] = None):
+    """bn_stats followed by bn_fwd_norm_quant_pack in one library call (act_bn_forward).
+    weight, bias and the running statistics are fp32 (or None).  Returns (y, packed, scale, min,
+    params, mask) with mask None unless relu."""
+    global _next_offset
+    _, nwords, _ = _bits_consts(bits, group_size)
+    x, N, C, hw = _bn_layout(x)
+    for t in (weight, bias, running_mean, running_var):
+        if t is not None and (t.dtype != torch.float32 or not t.is_contiguous()):
+            raise ValueError("bn_forward takes contiguous fp32 parameters and running statistics")
+    if residual is not None:
+        if not relu:
+            raise ValueError("the residual add is fused together with the ReLU only")
+        if residual.shape != x.shape or residual.dtype != x.dtype:
+            raise ValueError("residual must have x's shape and type")
+        residual = residual.contiguous(memory_format=torch.channels_last) if hw == 1 and is_channels_last(x) \
+            else residual.contiguous()
+    lib = _lib.load()
+    key = (N, C)
+    ws_bytes = _bn_ws_bytes.get(key)
+    if ws_bytes is None:
+        ws_bytes = _bn_ws_bytes[key] = int(lib.act_bn_stats_workspace(N, C))
+    dev = x.device
+    ng = x.numel() // group_size
+    params = torch.empty((C, 4), dtype=torch.float32, device=dev)
+    ws = torch.empty((max(ws_bytes, 4) // 4,), dtype=torch.float32, device=dev)
+    y = torch.empty_like(x)
+    packed = torch.empty((ng, nwords), dtype=torch.int32, device=dev)
+    meta = torch.empty((2, ng), dtype=torch.float32, device=dev)
+    mask = torch.empty((x.numel() // 8,), dtype=torch.uint8, device=dev) if relu else None
+    if seed is None:
+        seed = _default_seed
+    if offset is None:
+        offset = _next_offset
+        _next_offset += 1
+    ptr = lambda t: None if t is None else t.data_ptr()
+    with _device_of(x):
+        rc = lib.act_bn_forward(x.data_ptr(), ptr(residual), _DTYPES[x.dtype], N, C, hw, float(eps), ptr(weight),
+                                ptr(bias), ptr(running_mean), ptr(running_var), float(momentum), params.data_ptr(),
+                                ws.data_ptr(), ws_bytes, group_size, bits, seed & 0xFFFFFFFFFFFFFFFF,
+                                offset & 0xFFFFFFFFFFFFFFFF, flags, y.data_ptr(), packed.data_ptr(),
+                                meta[0].data_ptr(), meta[1].data_ptr(), ptr(mask), _stream_ptr(x))
+    _lib.check(rc, "act_bn_forward")
+    return y, packed, meta[0], meta[1], params, mask
+
+
+def bn_backward(packed: torch.Tensor, scale: torch.Tensor, mn: torch.Tensor, dy: torch.Tensor,
+                mask: Optional[torch.Tensor], has_residual: bool, bits: int, group_size: int,
+                params: torch.Tensor, count: float):
+    """bn_bwd_reduce, bn_bwd_coef and bn_bwd_dx in one library call (act_bn_backward), dy being
+    in the memory format of the forward input.  Returns (dx, dgamma, dbeta, dy_masked): with
+    has_residual, dy under the ReLU mask (the residual's gradient), else None."""
+    dy, N, C, hw = _bn_layout(dy)
+    dev = dy.device
+    work = torch.empty((6 * C,), dtype=torch.float32, device=dev)      # sums [2C] and coef [C][4]
+    dx = torch.empty_like(dy)
+    dym = torch.empty_like(dy) if has_residual else None
+    with _device_of(dy):
+        rc = _lib.load().act_bn_backward(packed.data_ptr(), scale.data_ptr(), mn.data_ptr(), dy.data_ptr(),
+                                         None if mask is None else mask.data_ptr(), _DTYPES[dy.dtype], N, C, hw,
+                                         group_size, bits, params.data_ptr(), float(count), work.data_ptr(),
+                                         work[2 * C:].data_ptr(), None if dym is None else dym.data_ptr(),
+                                         dx.data_ptr(), _stream_ptr(dy))
+    _lib.check(rc, "act_bn_backward")
+    return dx, work[:C], work[C:2 * C], dym
+
+
 # ---------------------------------------------------------------- max pooling, channels-last
 
 def maxpool_supported(x: torch.Tensor, k: int, s: int, pad: int) -> bool:

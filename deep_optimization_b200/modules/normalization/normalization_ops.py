@@ -76,15 +76,15 @@ class _DOBatchNorm(Function):
             x = input if ctx.channels_last else input.contiguous()
             f32 = lambda t: None if t is None else (t if t.dtype == torch.float32 else t.float())
             rm, rv = f32(running_mean), f32(running_var)
-            params = codec.bn_stats(x, eps, f32(weight), f32(bias), rm, rv, exponential_average_factor or 0.0)
+            flags = _lib.ACT_FLAG_ROUND_NEAREST if act_kernels.get_mode() != "baseline" else 0
+            y, packed, scale, mn, params, relu_mask = codec.bn_forward(
+                x, eps, f32(weight), f32(bias), rm, rv, exponential_average_factor or 0.0, m["bits"],
+                m["group_size"], flags=flags, relu=fuse_relu,
+                residual=None if residual is None else residual.to(x.dtype))
             if rm is not running_mean and running_mean is not None:      # running statistics kept in another type
                 running_mean.copy_(rm)
                 running_var.copy_(rv)
-            flags = _lib.ACT_FLAG_ROUND_NEAREST if act_kernels.get_mode() != "baseline" else 0
-            out = codec.bn_fwd_norm_quant_pack(x, None, None, weight, bias, m["bits"], m["group_size"],
-                                               flags=flags, params=params, relu=fuse_relu,
-                                               residual=None if residual is None else residual.to(x.dtype))
-            y, packed, scale, mn = out[:4]
+            out = (y, packed, scale, mn, relu_mask)
             ctx.fused = (m["bits"], m["group_size"], count)
             ctx.sync = (process_group, world_size)
             if fuse_relu:
@@ -141,15 +141,10 @@ class _DOBatchNorm(Function):
             # two kernels on the packed x_hat: per-channel sums, then dx (normalization_ops.py:145-163)
             bits, gs, count = ctx.fused
             dyc = dy.contiguous(memory_format=torch.channels_last) if ctx.channels_last else dy.contiguous()
-            dres = None
-            if ctx.has_residual:
-                # dy under the mask is the residual's gradient and the batch norm's dy
-                dyc = codec.relu_bwd_unpack(mask, dyc, channels_last=ctx.channels_last)
-                dres, mask = dyc, None
-            dgamma, dbeta = codec.bn_bwd_reduce(q_out, q_scale, q_min, dyc, bits, gs, mask=mask)
-            # `invstd` is the whole [C, 4] parameter table on this path
-            coef = codec.bn_bwd_coef(dgamma._base if dgamma._base is not None else (dgamma, dbeta), invstd, count)
-            dx = codec.bn_bwd_dx(q_out, q_scale, q_min, dyc, None, None, None, bits, gs, mask=mask, coef=coef)
+            # `invstd` is the whole [C, 4] parameter table on this path; with a residual, dy under
+            # the mask is the residual's gradient and the batch norm's dy
+            dx, dgamma, dbeta, dres = codec.bn_backward(q_out, q_scale, q_min, dyc, mask, ctx.has_residual,
+                                                        bits, gs, invstd, count)
             dw = dgamma.to(weight.dtype) if weight is not None else None
             db = dbeta.to(weight.dtype) if weight is not None else None
             return dx, dw, db, None, None, None, None, None, None, None, None, None, None, dres

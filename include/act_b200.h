@@ -263,6 +263,26 @@ ACT_API int act_bn_relu_bwd_dx(const void* packed, const float* scale, const flo
                        int group_size, int bits, const float* coef, void* dx, void* stream);
 
 /*
+ * One call per layer and direction: the launches of the entry points above in sequence, for
+ * hosts where the round trip per launch matters (53 layers per ResNet-50 step).
+ *   act_bn_forward: act_bn_stats, then the forward kernel that the arguments select
+ *       (residual != NULL: + residual + ReLU; else mask_bits != NULL: + ReLU; else plain).
+ *   act_bn_backward: zeroes sums [2C], then act_bn_bwd_reduce, act_bn_bwd_coef (writes coef
+ *       [C][4]) and act_bn_bwd_dx.  mask_bits NULL: plain; mask_bits and dy_masked NULL: the
+ *       ReLU variants; mask_bits and dy_masked given: dy under the mask goes to dy_masked
+ *       first (act_relu_bwd_unpack; the residual's gradient) and the plain kernels read that.
+ */
+ACT_API int act_bn_forward(const void* x, const void* residual, int dtype, int64_t n_batch, int channels,
+                   int64_t hw, double eps, const float* weight, const float* bias, float* running_mean,
+                   float* running_var, double momentum, float* params, void* workspace, size_t ws_bytes,
+                   int group_size, int bits, uint64_t seed, uint64_t offset, int flags, void* y,
+                   void* packed, float* scale, float* min, void* mask_bits, void* stream);
+ACT_API int act_bn_backward(const void* packed, const float* scale, const float* min, const void* dy,
+                    const void* mask_bits, int dtype, int64_t n_batch, int channels, int64_t hw,
+                    int group_size, int bits, const float* params, double count, float* sums, float* coef,
+                    void* dy_masked, void* dx, void* stream);
+
+/*
  * Max pooling on a channels-last activation with a 4-bit argmax saved for backward instead of
  * PyTorch's int64 index per output (no counterpart in the reference, which leaves the pooling
  * layer of its ResNet payload, Model/CNN/ResNetV1.py:63,99, to PyTorch): x [N, H, W, C] with C a
