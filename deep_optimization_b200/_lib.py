@@ -48,6 +48,7 @@ SIGNATURES = {
                         _u64, _u64, _i32, _vp, _vp, _vp, _vp, _vp, _vp], _i32),
     "act_bn_backward": ([_vp, _vp, _vp, _vp, _vp, _i32, _i64, _i32, _i64, _i32, _i32, _vp, _f64, _vp, _vp, _vp, _vp,
                          _vp], _i32),
+    "act_bn_add_relu_bwd_reduce": ([_vp, _vp, _vp, _vp, _vp, _i32, _i64, _i32, _i64, _i32, _i32, _vp, _vp, _vp], _i32),
     "act_quant_pack_avg": ([_vp, _i32, _i64, _i32, _i32, _i32, _vp, _u64, _u64, _i32, _f32, _vp, _vp, _vp, _vp], _i32),
     "act_dequant_unpack_avg": ([_vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _vp, _vp], _i32),
     "act_bn_relu_fwd_norm_quant_pack": ([_vp, _i32, _i64, _i32, _i64, _vp, _i32, _i32, _u64, _u64, _i32, _vp, _vp, _vp, _vp, _vp, _vp], _i32),

@@ -30,7 +30,8 @@ extern "C" int act_bn_forward(const void* x, const void* residual, int dtype, in
 // Backward: sums = (sum dy*x_hat, sum dy) per channel [2C] (zeroed here), coef [C][4], dx.
 // mask_bits NULL: plain batch norm.  mask_bits with dy_masked NULL: BN + ReLU, the two kernels
 // read dy through the mask.  mask_bits with dy_masked: BN + residual + ReLU; dy under the mask
-// is written to dy_masked first (the residual's gradient) and is what the two kernels read.
+// is written to dy_masked first (act_bn_add_relu_bwd_reduce; the residual's gradient) and is
+// what the dx kernel reads.
 extern "C" int act_bn_backward(const void* packed, const float* scale, const float* mn, const void* dy,
                                const void* mask_bits, int dtype, int64_t n_batch, int channels, int64_t hw,
                                int group_size, int bits, const float* params, double count, float* sums,
@@ -41,10 +42,12 @@ extern "C" int act_bn_backward(const void* packed, const float* scale, const flo
     if (cudaMemsetAsync(sums, 0, (size_t)channels * 2 * sizeof(float), st) != cudaSuccess) return ACT_ERR_LAUNCH;
     int rc;
     if (mask_bits && dy_masked) {
-        rc = act_relu_bwd_unpack(mask_bits, dy, dtype, n_batch * channels * hw, dy_masked, stream);
+        rc = act_bn_add_relu_bwd_reduce(packed, scale, mn, dy, mask_bits, dtype, n_batch, channels, hw, group_size,
+                                        bits, sums, dy_masked, stream);
         if (rc != ACT_OK) return rc;
-        dy = dy_masked;
-        mask_bits = nullptr;
+        rc = act_bn_bwd_coef(sums, params, channels, count, coef, stream);
+        if (rc != ACT_OK) return rc;
+        return act_bn_bwd_dx(packed, scale, mn, dy_masked, dtype, n_batch, channels, hw, group_size, bits, coef, dx, stream);
     }
     if (mask_bits) rc = act_bn_relu_bwd_reduce(packed, scale, mn, dy, mask_bits, dtype, n_batch, channels, hw, group_size, bits, sums, stream);
     else rc = act_bn_bwd_reduce(packed, scale, mn, dy, dtype, n_batch, channels, hw, group_size, bits, sums, stream);

@@ -247,14 +247,18 @@ ACT_API int act_bn_relu_fwd_norm_quant_pack(const void* x, int dtype, int64_t n_
  * (the reference's bottleneck ends `x += identity; return relu3(x)`, Model/CNN/ResNetV1.py:48-49,
  * as an add and a ReLU pass of their own): y = max(x_hat * weight + bias + residual, 0), the
  * sum rounded to fp32 before the ReLU, `residual` of x's type, shape and layout; the mask is
- * that of the sum.  Backward: dy * mask (act_relu_bwd_unpack on mask_bits) is the gradient of
- * the residual and the dy of act_bn_bwd_reduce / act_bn_bwd_dx.
+ * that of the sum.  Backward: dy * mask is the gradient of the residual and the dy of the
+ * batch norm; act_bn_add_relu_bwd_reduce writes it to dy_masked (act_relu_bwd_unpack) and
+ * computes the sums of act_bn_bwd_reduce on it; act_bn_bwd_dx then reads dy_masked.
  */
 ACT_API int act_bn_add_relu_fwd_norm_quant_pack(const void* x, const void* residual, int dtype, int64_t n_batch,
                                         int channels, int64_t hw, const float* params, int group_size,
                                         int bits, uint64_t seed, uint64_t offset, int flags, void* y,
                                         void* packed, float* scale, float* min, void* mask_bits,
                                         void* stream);
+ACT_API int act_bn_add_relu_bwd_reduce(const void* packed, const float* scale, const float* min, const void* dy,
+                               const void* mask_bits, int dtype, int64_t n_batch, int channels, int64_t hw,
+                               int group_size, int bits, float* sums, void* dy_masked, void* stream);
 ACT_API int act_bn_relu_bwd_reduce(const void* packed, const float* scale, const float* min, const void* dy,
                            const void* mask_bits, int dtype, int64_t n_batch, int channels, int64_t hw,
                            int group_size, int bits, float* sums, void* stream);

@@ -508,3 +508,37 @@ def test_maxpool_module_and_nan(cuda_device):
     yc.backward(g); yn.backward(g)
     assert torch.allclose(xc.grad, xn.grad, rtol=1e-6, atol=1e-6)
     assert pool.eval()(xc).grad_fn is None or type(pool(xc).grad_fn).__name__ != "_DOMaxPool2dBackward"
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("channels_last", (False, True))
+@pytest.mark.parametrize("mode", ("plain", "relu", "residual"))
+def test_bn_backward_one_call(cuda_device, channels_last, mode):
+    """act_bn_backward (sums zeroed inside, reduction, constants, dx, and for a residual block
+    dy under the mask as a by-product of the reduction) against the separate entry points."""
+    from deep_optimization_b200 import codec
+    fmt = torch.channels_last if channels_last else torch.contiguous_format
+    g = torch.Generator().manual_seed(61)
+    shape, gs, bits = (6, 32, 14, 14), 64, 2
+    x = torch.randn(shape, generator=g).to(torch.bfloat16).to(cuda_device).contiguous(memory_format=fmt)
+    dy = torch.randn(shape, generator=g).to(torch.bfloat16).to(cuda_device).contiguous(memory_format=fmt)
+    C = shape[1]
+    w = torch.randn(C, generator=g).to(cuda_device)
+    b = torch.randn(C, generator=g).to(cuda_device)
+    y, packed, scale, mn, params, mask = codec.bn_forward(x, 1e-5, w, b, None, None, 0.0, bits, gs,
+                                                          relu=(mode != "plain"), seed=5, offset=1)
+    count = x.numel() // C
+    dx, dg, db, dym = codec.bn_backward(packed, scale, mn, dy, mask, mode == "residual", bits, gs, params, count)
+    if mode == "residual":
+        want_dym = codec.relu_bwd_unpack(mask, dy, channels_last=channels_last)
+        assert torch.equal(dym, want_dym)
+        s1, s2 = codec.bn_bwd_reduce(packed, scale, mn, want_dym, bits, gs)
+        coef = codec.bn_bwd_coef((s1, s2), params, count)
+        want_dx = codec.bn_bwd_dx(packed, scale, mn, want_dym, None, None, None, bits, gs, coef=coef)
+    else:
+        assert dym is None
+        s1, s2 = codec.bn_bwd_reduce(packed, scale, mn, dy, bits, gs, mask=mask)
+        coef = codec.bn_bwd_coef((s1, s2), params, count)
+        want_dx = codec.bn_bwd_dx(packed, scale, mn, dy, None, None, None, bits, gs, mask=mask, coef=coef)
+    assert torch.allclose(dg, s1, rtol=1e-4, atol=1e-3) and torch.allclose(db, s2, rtol=1e-4, atol=1e-3)
+    assert ((dx.float() - want_dx.float()).abs() <= 2.0 ** -6 * (1 + want_dx.float().abs())).all()
