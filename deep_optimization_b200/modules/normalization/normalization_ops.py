@@ -1,14 +1,15 @@
 """BatchNorm Function that saves the normalised activation compressed.
 
 Forward: per-channel batch statistics (fp32), x_hat = (x - mean) * invstd,
-y = x_hat * weight + bias; x_hat is stored through the codec.  Backward:
-dgamma = sum(dy * x_hat), dbeta = sum(dy),
+y = x_hat * weight + bias (optionally + residual, optionally ReLU); x_hat is stored through
+the codec.  Backward: dgamma = sum(dy * x_hat), dbeta = sum(dy),
 dx = weight * invstd / M * (M * dy - dbeta - x_hat * dgamma).
 Argument order and saved tensors follow
-Activation_Compression/modules/normalization/normalization_ops.py:10-171; the
-statistics and the element-wise maths are plain PyTorch here, the compressed
-state goes through the CUDA codec.  The SyncBN variant all-gathers
-(mean, invstd, count) per rank as normalization_ops.py:181-195 does.
+Activation_Compression/modules/normalization/normalization_ops.py:10-171.  Single-GPU batches
+of supported shapes (NCHW with HW a multiple of 4, or channels-last with C a multiple of 8) run
+on the library's fused kernels, one call per direction (`codec.bn_forward`, `codec.bn_backward`);
+other shapes use PyTorch's native batch-norm kernels around the stand-alone codec, and the SyncBN
+variant all-gathers (mean, invstd, count) per rank as normalization_ops.py:181-195 does.
 """
 from __future__ import annotations
 
