@@ -33,6 +33,7 @@ SHAPE = (256, 256, 28, 28)
 GROUP = 128
 BITS = 2
 ROTATE = 4                      # distinct buffer sets cycled through: working set >> 126 MB L2
+REGIONS = 25                    # timed regions of K steps each; the median region is reported
 METRIC = "act_quant_pack_unpack_GBps"
 UNIT = "GB/s"
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the pack kernel on this
@@ -50,6 +51,14 @@ def algorithmic_bytes(n_elems: int, group: int, bits: int, elem_bytes: int):
 def workload_name():
     return (f"bf16 conv activation {list(SHAPE)} ReLU(N(0,1)), group {GROUP}, {BITS}-bit, "
             f"quant-pack + dequant-unpack")
+
+
+def config_dict(world: int):
+    """The `config` object of the JSON line; both arms print the same one."""
+    return {"workload": workload_name(), "input_dtype": "bf16", "group_size": GROUP, "bits": BITS,
+            "noise": "in-kernel counter hash, 8 noise bits, fixed-point mode",
+            "cache": f"{ROTATE} rotating buffer sets (0.9 GB working set, larger than L2)",
+            "parallelism": f"replicas x{world} (no data-path collective)"}
 
 
 class ClockSampler:
@@ -163,7 +172,8 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-        "data": "synthetic", "config": {"workload": workload_name()},
+        "data": "synthetic", "config": config_dict(int(os.environ.get("WORLD_SIZE", "1"))),
+        "baseline_kind": "CPU port of the reference codec (oracle/), not the reference's GPU path",
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
                          "sample": f"each step: {sample}"},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -186,6 +196,65 @@ def _time_launches(fn, reps):
     return e0.elapsed_time(e1) / reps
 
 
+def _median_launch_ms(fn, reps=20, regions=7):
+    """Median over `regions` of the mean of `reps` back-to-back launches (CUDA events)."""
+    import torch
+    for i in range(3):
+        fn(i)
+    vals = []
+    for r in range(regions):
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(reps):
+            fn(r * reps + i)
+        e1.record()
+        torch.cuda.synchronize()
+        vals.append(e0.elapsed_time(e1) / reps)
+    vals.sort()
+    return vals[len(vals) // 2]
+
+
+def run_contract_modes(dev):
+    """The arithmetic the evaluation configuration states word for word (fp32 min and scale, true
+    division, code = clamp(floor((x-min)/scale + u)) with a caller-supplied fp32 noise tensor u)
+    beside the in-kernel hash mode the headline uses, on configuration 1 (fp32 [128,64,56,56],
+    group 256, 2 bits) and on the headline workload.  The noise tensor adds 4 bytes of reads per
+    element; fractions are given with those bytes counted (what the kernel moves) and without
+    (the codec's own algorithmic bytes)."""
+    import torch
+    from deep_optimization_b200 import codec
+    peak, _ = load_peaks()
+    out = {}
+    rot = 3
+    for name, shape, gs, dtype, sbytes in (("config1_fp32_128x64x56x56_g256_b2", (128, 64, 56, 56), 256, torch.float32, 4),
+                                           ("headline_bf16_256x256x28x28_g128_b2", SHAPE, GROUP, torch.bfloat16, 2)):
+        n = 1
+        for d in shape:
+            n *= d
+        ng = n // gs
+        xs = [torch.relu(torch.randn(shape, device=dev)).to(dtype) for _ in range(rot)]
+        us = [torch.rand(shape, device=dev) for _ in range(2)]
+        outs = [(torch.empty((ng, gs * BITS // 32), dtype=torch.int32, device=dev),
+                 torch.empty(ng, device=dev), torch.empty(ng, device=dev)) for _ in range(rot)]
+        ys = [torch.empty((ng, gs), dtype=dtype, device=dev) for _ in range(rot)]
+        pb, ub = algorithmic_bytes(n, gs, BITS, sbytes)
+        t_noise = _median_launch_ms(lambda i: codec.quant_pack(xs[i % rot], BITS, gs, noise=us[i % 2], out=outs[i % rot]))
+        t_hash = _median_launch_ms(lambda i: codec.quant_pack(xs[i % rot], BITS, gs, seed=3, offset=i, out=outs[i % rot]))
+        t_un = _median_launch_ms(lambda i: codec.dequant_unpack(*outs[i % rot], BITS, gs, out_dtype=dtype, out=ys[i % rot]))
+        fr = lambda b, t: b / t / 1e6 / peak
+        out[name] = {
+            "pack_noise_tensor": {"ms_per_launch": t_noise, "frac_with_noise_bytes": fr(pb + 4 * n, t_noise),
+                                  "frac_codec_bytes_only": fr(pb, t_noise)},
+            "pack_hash": {"ms_per_launch": t_hash, "frac": fr(pb, t_hash)},
+            "unpack": {"ms_per_launch": t_un, "frac": fr(ub, t_un)},
+            "pack_plus_unpack_frac_noise_tensor": fr(pb + 4 * n + ub, t_noise + t_un),
+            "pack_plus_unpack_frac_hash": fr(pb + ub, t_hash + t_un)}
+        del xs, us, outs, ys
+    torch.cuda.empty_cache()
+    return out
+
+
 def run_extras(dev):
     """Untimed-region extras on rank 0: the fp32 configuration of the codec and the three
     FP8 GEMM shapes.  Each number is the mean of back-to-back launches between two CUDA
@@ -195,21 +264,7 @@ def run_extras(dev):
     from deep_optimization_b200.gemm import fp8_gemm, quantize_e4m3
     peak, _ = load_peaks()
     out = {}
-    # fp32 [128,64,56,56], group 256, 2 bits
-    shape, gs, bits, rot = (128, 64, 56, 56), 256, 2, 4
-    n = 128 * 64 * 56 * 56
-    xs = [torch.relu(torch.randn(shape, device=dev)) for _ in range(rot)]
-    outs = [(torch.empty((n // gs, gs * bits // 32), dtype=torch.int32, device=dev),
-             torch.empty(n // gs, device=dev), torch.empty(n // gs, device=dev)) for _ in range(rot)]
-    ys = [torch.empty((n // gs, gs), device=dev) for _ in range(rot)]
-    pb, ub = algorithmic_bytes(n, gs, bits, 4)
-    tp = _time_launches(lambda i=0: codec.quant_pack(xs[i % rot], bits, gs, seed=3, offset=i, out=outs[i % rot]), 40)
-    tu = _time_launches(lambda i=0: codec.dequant_unpack(*outs[i % rot], bits, gs, out_dtype=torch.float32, out=ys[i % rot]), 40)
-    out["codec_fp32_128x64x56x56_g256_b2"] = {
-        "pack_GBps": pb / tp / 1e6, "pack_frac": pb / tp / 1e6 / peak,
-        "unpack_GBps": ub / tu / 1e6, "unpack_frac": ub / tu / 1e6 / peak,
-        "pack_plus_unpack_frac": (pb + ub) / (tp + tu) / 1e6 / peak}
-    del xs, outs, ys
+    rot = 4
     # bit-width and shape sweep of the bf16 configuration: conv [256,256,28,28] = ReLU(N(0,1)) and
     # ViT [256,197,768] = GELU(N(0,1)), group 128, bits 1/2/4/8
     sweep = {}
@@ -231,24 +286,6 @@ def run_extras(dev):
             del outs
         del xs, ys
     out["codec_bf16_g128_sweep"] = sweep
-    # the other rounding modes on the bench workload (bf16 [256,256,28,28], group 128, 2 bits):
-    # caller-supplied fp32 noise (exact-division float formula; its algorithmic bytes include
-    # the 4 bytes of noise read per element) and round-to-nearest
-    n = 1
-    for d in SHAPE:
-        n *= d
-    xs = [torch.relu(torch.randn(SHAPE, device=dev)).to(torch.bfloat16) for _ in range(rot)]
-    us = [torch.rand(SHAPE, device=dev) for _ in range(2)]
-    outs = [(torch.empty((n // GROUP, GROUP * BITS // 32), dtype=torch.int32, device=dev),
-             torch.empty(n // GROUP, device=dev), torch.empty(n // GROUP, device=dev)) for _ in range(rot)]
-    pb, _ = algorithmic_bytes(n, GROUP, BITS, 2)
-    tt = _time_launches(lambda i=0: codec.quant_pack(xs[i % rot], BITS, GROUP, noise=us[i % 2], out=outs[i % rot]), 40)
-    tn = _time_launches(lambda i=0: codec.quant_pack(xs[i % rot], BITS, GROUP, flags=1, out=outs[i % rot]), 40)
-    out["pack_modes_bf16_g128_b2"] = {
-        "noise_tensor": {"GBps_with_noise_bytes": (pb + 4 * n) / tt / 1e6, "frac": (pb + 4 * n) / tt / 1e6 / peak,
-                         "ms_per_launch": tt},
-        "round_to_nearest": {"GBps": pb / tn / 1e6, "frac": pb / tn / 1e6 / peak, "ms_per_launch": tn}}
-    del xs, us, outs
     # fused batch-norm kernels on a ResNet-50 stage-1 activation, bf16 [256,64,56,56], group 256,
     # 2 bits: algorithmic bytes = what each kernel must read and write once
     shp = (256, 64, 56, 56)
@@ -298,33 +335,109 @@ def run_extras(dev):
     fused["relu_bwd_mask_unpack"] = {"GBps": b_r / t_rb / 1e6, "frac": b_r / t_rb / 1e6 / peak, "ms_per_launch": t_rb}
     out["fused_activation_kernels_bf16"] = fused
     del xr, mbits
-    # FP8 GEMM shapes (M, K, N); peak = nominal dense FP8 of a B200
-    gem = {}
+    out["fp8_gemm"] = run_gemm_shapes(dev)
+    out["write_stream"] = run_write_stream(dev)
+    out["reference_triton"] = run_reference_triton()
+    return out
+
+
+GEMM_SHAPES = ((8192, 4096, 4096), (50432, 768, 3072), (50432, 3072, 768))      # (M, K, N)
+
+
+def run_gemm_shapes(dev, shapes=GEMM_SHAPES, reps=20):
+    """The FP8 GEMM on the evaluation shapes, B in both layouts, beside cuBLASLt's scaled matmul
+    on the same operands.  Before a time is reported the kernel's abort word must be clear and 64
+    sampled rows of C must match the float64 product.  Fractions: of the nominal dense FP8 peak
+    of a B200 (4.5 PFLOP/s) and of twice the measured bf16 cuBLAS burst (no FP8 figure is
+    measured on this pool)."""
+    import torch
+    from deep_optimization_b200.gemm import fp8_gemm, gemm_status, quantize_e4m3
     bf16_peak = None
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         with open(path) as f:
             bf16_peak = float(json.load(f).get("bf16_tflops", 0)) or None
-    for (M, K, N) in ((8192, 4096, 4096), (50432, 768, 3072), (50432, 3072, 768)):
+    gem = {}
+    for (M, K, N) in shapes:
         A8, sa = quantize_e4m3(torch.randn(M, K, device=dev), 1)
         B8, sb = quantize_e4m3(torch.randn(K, N, device=dev), 0)
+        Bt = B8.t().contiguous()
         C = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
         ws = torch.empty(N * K, dtype=torch.uint8, device=dev)
-        t = _time_launches(lambda i=0: fp8_gemm(A8, B8, sa, sb, out=C, workspace=ws), 20)
-        Bt = B8.t().contiguous()
-        t_nk = _time_launches(lambda i=0: fp8_gemm(A8, Bt, sa, sb, b_is_nk=True, out=C), 20)
-        fl = 2.0 * M * N * K
-        gem[f"M{M}_K{K}_N{N}"] = {"TFLOPs_B_kn": fl / t / 1e9, "TFLOPs_B_nk": fl / t_nk / 1e9,
-                                   "frac_of_nominal_fp8_4500": fl / t_nk / 1e9 / 4500.0}
+        rows = torch.linspace(0, M - 1, 64, device=dev).long()
+        ref = (A8[rows].double() @ B8.double()) * sa[rows].double()[:, None] * sb.double()[None, :]
+        entry = {}
+        for tag, fn in (("B_nk", lambda i=0: fp8_gemm(A8, Bt, sa, sb, b_is_nk=True, out=C)),
+                        ("B_kn", lambda i=0: fp8_gemm(A8, B8, sa, sb, out=C, workspace=ws))):
+            C.fill_(float("nan"))
+            fn()
+            status = gemm_status()
+            got = C[rows].double()
+            tol = ref.abs() * 2.0 ** -8 + ref.abs().max() * 2.0 ** -12 + 1e-6
+            if status != 0 or torch.isnan(C).any() or not bool(((got - ref).abs() <= tol).all()):
+                raise SystemExit(f"fp8_gemm {tag} M={M} K={K} N={N}: wrong result (abort word {status})")
+            t = _median_launch_ms(fn, reps=reps, regions=5)
+            if gemm_status() != 0:
+                raise SystemExit(f"fp8_gemm {tag} M={M} K={K} N={N}: aborted inside the timing loop")
+            entry["TFLOPs_" + tag] = 2.0 * M * N * K / t / 1e9
+            entry["ms_" + tag] = t
+        entry["checked"] = "abort word 0; 64 sampled rows within 2^-8 |ref| + 2^-12 max|ref| of the float64 product"
+        entry["frac_of_nominal_fp8_4500"] = entry["TFLOPs_B_nk"] / 4500.0
+        entry["frac_of_nominal_fp8_4500_B_kn"] = entry["TFLOPs_B_kn"] / 4500.0
         if bf16_peak:
-            # no FP8 figure is measured on this pool; twice the measured bf16 cuBLAS burst stands in
-            gem[f"M{M}_K{K}_N{N}"]["frac_of_2x_measured_bf16"] = fl / t_nk / 1e9 / (2.0 * bf16_peak)
-        del A8, B8, C, ws, Bt
-    out["fp8_gemm"] = gem
+            entry["frac_of_2x_measured_bf16"] = entry["TFLOPs_B_nk"] / (2.0 * bf16_peak)
+        try:
+            sa2, sb2 = sa.view(M, 1).contiguous(), sb.view(1, N).contiguous()
+            t2 = _median_launch_ms(lambda i=0: torch._scaled_mm(A8, Bt.t(), scale_a=sa2, scale_b=sb2,
+                                                                out_dtype=torch.bfloat16), reps=reps, regions=5)
+            entry["cublaslt_scaled_mm_TFLOPs"] = 2.0 * M * N * K / t2 / 1e9
+            entry["vs_cublaslt"] = t2 / entry["ms_B_nk"]
+        except Exception as ex:        # noqa: BLE001 - a library yardstick only
+            entry["cublaslt_scaled_mm_TFLOPs"] = f"unavailable: {str(ex)[:80]}"
+        gem[f"M{M}_K{K}_N{N}"] = entry
+        del A8, B8, C, ws, Bt, ref
+    torch.cuda.empty_cache()
+    return gem
+
+
+def run_write_stream(dev):
+    """What a pure write stream reaches on this GPU: torch's fill kernel on outputs of the size
+    the unpack kernel (102.8 MB) and the K = 768 GEMM (309.9 MB) write, rotating buffers."""
+    import torch
+    peak, _ = load_peaks()
+    out = {}
+    for name, nbytes in (("unpack_output_102.8MB", 102_760_448), ("gemm_output_309.9MB", 309_854_208)):
+        bufs = [torch.empty(nbytes, dtype=torch.uint8, device=dev) for _ in range(3)]
+        t = _median_launch_ms(lambda i: bufs[i % 3].zero_())
+        out[name] = {"ms": t, "GBps": nbytes / t / 1e6, "frac_of_copy_peak": nbytes / t / 1e6 / peak}
+        del bufs
+    torch.cuda.empty_cache()
     return out
 
 
-def run_train(name, dev, world, local, steps=8, warmup=3, act=True, batch=256, channels_last=False):
+def run_reference_triton(steps=20, warmup=3):
+    """The reference's own Triton operators on this GPU, in a child process (they register the
+    same operator names as this package): baseline/reference_triton.py, which needs the
+    reference's two Triton modules under baseline/_ref (baseline/install_reference.py)."""
+    runner = os.path.join(ROOT, "baseline", "reference_triton.py")
+    if not os.path.exists(os.path.join(ROOT, "baseline", "_ref", "act_triton_kernel.py")):
+        return {"unavailable": "reference Triton path unavailable on this box: baseline/_ref not installed"}
+    try:
+        r = subprocess.run([sys.executable, runner, "time", "--steps", str(steps), "--warmup", str(warmup)],
+                           capture_output=True, text=True, timeout=900)
+    except subprocess.TimeoutExpired:
+        return {"unavailable": "reference Triton path unavailable on this box: timed out after 900 s"}
+    lines = [ln for ln in r.stdout.strip().splitlines() if ln.startswith("{")]
+    if not lines:
+        return {"unavailable": "reference Triton path unavailable on this box: " + (r.stderr.strip().splitlines() or ["no output"])[-1][:200]}
+    res = json.loads(lines[-1])
+    if "unavailable" in res:
+        res["unavailable"] = "reference Triton path unavailable on this box: " + res["unavailable"]
+    return res
+
+
+def run_train(name, dev, world, local, steps=8, warmup=3, act=True, batch=256, channels_last=False,
+              profiler=None):
     """One end-to-end configuration: `name` in (resnet50, vit_b16), ACT 2-bit on every
     supported layer whose activation exceeds 10 MiB, bf16 autocast, batch 256 per GPU of
     synthetic N(0,1) images with uniform labels, DDP (NCCL all-reduce) when world > 1.
@@ -375,11 +488,13 @@ def run_train(name, dev, world, local, steps=8, warmup=3, act=True, batch=256, c
         dist.barrier()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(steps):
-        loss = one_step()
-    e1.record()
-    torch.cuda.synchronize()
+    import contextlib
+    with (profiler if profiler is not None else contextlib.nullcontext()):
+        e0.record()
+        for _ in range(steps):
+            loss = one_step()
+        e1.record()
+        torch.cuda.synchronize()
     ms = torch.tensor([e0.elapsed_time(e1) / steps], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
@@ -435,47 +550,55 @@ def run_ours(args):
         step(i)
     barrier()
 
-    # ---- device-resident timing: K steps between two events on the launch stream ----
+    # ---- device-resident timing ---------------------------------------------------
+    # REGIONS timed regions of K steps each, every one bracketed by barrier + synchronize and
+    # two CUDA events on the launch stream; per region the max over ranks, then the median
+    # over regions is the value (a single region of K = 20 steps lasts about a millisecond,
+    # and one such sample moved by +-5 % from box to box and run to run).
     K = args.steps
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-        time.sleep(0.3)
-    barrier()
-    e_begin, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e_begin.record()
-    for i in range(K):
-        step(i)
-    e_end.record()
-    barrier()
-    total_ms = e_begin.elapsed_time(e_end)
+    # the same load, untimed, while the sampler starts: the GPU must not idle (and drop its
+    # clocks) right before the timed regions
+    t_end = time.perf_counter() + 0.3
+    i = 0
+    while time.perf_counter() < t_end:
+        for _ in range(50):
+            step(i)
+            i += 1
+        torch.cuda.synchronize()
+
+    def regions_of(fn, regions, sync_ranks):
+        out = []
+        for r in range(regions):
+            if sync_ranks:
+                barrier()
+            else:
+                torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for i in range(K):
+                fn(r * K + i)
+            b.record()
+            if sync_ranks:
+                barrier()
+            else:
+                torch.cuda.synchronize()
+            out.append(a.elapsed_time(b))
+        return out
+
+    region_ms = regions_of(step, REGIONS, True)
 
     # ---- per-kernel durations for the roofline: K launches of one kernel back to back on the
-    # rotating buffer sets, between two events on the same stream (an event between every two
-    # launches would add the launch gap, about 4 us, to each of them)
-    def kernel_loop(fn):
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for i in range(K):
-            fn(i)
-        b.record()
-        torch.cuda.synchronize()
-        return a.elapsed_time(b) / K
-
-    pack_ms = kernel_loop(lambda i: codec.quant_pack(xs[i % ROTATE], BITS, GROUP, seed=17,
-                                                     offset=i * (n_elems // 4), out=outs[i % ROTATE]))
-    unpack_ms = kernel_loop(lambda i: codec.dequant_unpack(*outs[i % ROTATE], BITS, GROUP,
-                                                           out_dtype=torch.bfloat16, out=ys[i % ROTATE]))
-    if rank == 0:
-        # the timed region is short; keep the same load running (untimed) until the
-        # sampler has at least half a second of samples under load
-        t_end = time.perf_counter() + 0.5
-        i = K
-        while time.perf_counter() < t_end:
-            for _ in range(50):
-                step(i)
-                i += 1
-            torch.cuda.synchronize()
+    # rotating buffer sets between two events on the same stream (an event between every two
+    # launches would add the launch gap, about 4 us, to each of them), REGIONS times over
+    pack_region_ms = regions_of(lambda i: codec.quant_pack(xs[i % ROTATE], BITS, GROUP, seed=17,
+                                                           offset=i * (n_elems // 4), out=outs[i % ROTATE]),
+                                REGIONS, False)
+    unpack_region_ms = regions_of(lambda i: codec.dequant_unpack(*outs[i % ROTATE], BITS, GROUP,
+                                                                 out_dtype=torch.bfloat16, out=ys[i % ROTATE]),
+                                  REGIONS, False)
     clocks = sampler.stop() if rank == 0 else None
 
     # ---- end to end: pinned host input -> H2D -> pack -> unpack -> D2H ----------
@@ -520,6 +643,7 @@ def run_ours(args):
     barrier()
     e2e_ms = e0.elapsed_time(e1) / KE
 
+    contract = run_contract_modes(dev) if rank == 0 else None
     extras = None
     if rank == 0 and not args.no_extras:
         extras = run_extras(dev)
@@ -534,15 +658,20 @@ def run_ours(args):
                  "vit_b16_act2bit": run_train("vit_b16", dev, world, local),
                  "vit_b16_no_act": run_train("vit_b16", dev, world, local, act=False)}
 
-    # ---- max over ranks ----------------------------------------------------------
-    t = torch.tensor([total_ms, e2e_ms, pack_ms, unpack_ms], device=dev, dtype=torch.float64)
+    # ---- max over ranks (per region), then the median over regions -------------------
+    t = torch.tensor([region_ms, pack_region_ms, unpack_region_ms, [e2e_ms] * REGIONS], device=dev,
+                     dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    total_ms, e2e_ms, pack_ms, unpack_ms = t.tolist()
+    region_ms, pack_region_ms, unpack_region_ms = (sorted(v) for v in t[:3].tolist())
+    e2e_ms = float(t[3][0])
+    med = lambda v: v[len(v) // 2]
+    total_ms, pack_ms, unpack_ms = med(region_ms), med(pack_region_ms) / K, med(unpack_region_ms) / K
 
     if rank == 0:
         step_bytes = pack_bytes + unpack_bytes
-        value = world * step_bytes * K / (total_ms * 1e-3) / 1e9
+        gbps = lambda ms: world * step_bytes * K / (ms * 1e-3) / 1e9
+        value = gbps(total_ms)
         e2e_value = world * step_bytes / (e2e_ms * 1e-3) / 1e9
         peak, peak_kind = load_peaks()
         achieved = pack_bytes / (pack_ms * 1e-3) / 1e9
@@ -550,25 +679,35 @@ def run_ours(args):
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K,
             "warmup": max(args.warmup, 3), "ms_per_step": total_ms / K, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": workload_name(), "input_dtype": "bf16", "group_size": GROUP,
-                       "bits": BITS, "noise": "in-kernel counter hash, 8 noise bits, fixed-point mode",
-                       "cache": f"{ROTATE} rotating buffer sets (0.9 GB working set, larger than L2)",
-                       "parallelism": f"replicas x{world} (no data-path collective)"},
+            "config": config_dict(world),
+            "regions": {"count": REGIONS, "steps_each": K, "value": "median region",
+                        "value_min": gbps(region_ms[-1]), "value_max": gbps(region_ms[0]),
+                        "spread": (region_ms[-1] - region_ms[0]) / total_ms,
+                        "frac_of_hbm_peak": value / world / peak},
             "roofline": {"bound": "hbm", "kernel": "quant_pack_kernel<bf16,2,hash>",
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": f"{peak_kind} (copy bandwidth)", "traffic": NCU_PACK_TRAFFIC_BYTES,
+                         "traffic_source": "one ncu capture of this kernel on this workload (profiles/quant_pack_bf16_g128_b2_ncu.md)",
                          "algorithmic_bytes_per_launch": pack_bytes, "ms_per_launch": pack_ms,
-                         "timing": "mean of K back-to-back launches on rotating buffers, CUDA events on the launch stream",
+                         "ms_per_launch_min_max": [pack_region_ms[0] / K, pack_region_ms[-1] / K],
+                         "timing": f"median of {REGIONS} regions of K back-to-back launches on rotating buffers, "
+                                   "CUDA events on the launch stream",
                          "unpack": {"kernel": "dequant_unpack_kernel<bf16,2>",
                                     "achieved": unpack_bytes / (unpack_ms * 1e-3) / 1e9,
                                     "frac": unpack_bytes / (unpack_ms * 1e-3) / 1e9 / peak,
-                                    "ms_per_launch": unpack_ms},
+                                    "ms_per_launch": unpack_ms,
+                                    "ms_per_launch_min_max": [unpack_region_ms[0] / K, unpack_region_ms[-1] / K]},
                          "pack_plus_unpack_frac": step_bytes / ((pack_ms + unpack_ms) * 1e-3) / 1e9 / peak},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": n_elems * 2,
-                    "d2h_bytes_per_step": n_elems * 2, "ms_per_step": e2e_ms},
-            "gpu_launches": 2 * K,        # inside the timed steps; the two kernel loops launch 2K more
+                    "d2h_bytes_per_step": n_elems * 2, "ms_per_step": e2e_ms,
+                    "per_rank_h2d_GBps": n_elems * 2 / (e2e_ms * 1e-3) / 1e9,
+                    "per_rank_d2h_GBps": n_elems * 2 / (e2e_ms * 1e-3) / 1e9,
+                    "bound": "host memory and PCIe: the two copies of a step run concurrently with the kernels"},
+            "gpu_launches": 2 * K,        # per timed region of K steps; there are REGIONS of them
             "clocks": clocks,
         }
+        if contract is not None:
+            line["roofline"]["contract_modes"] = contract
         if extras is not None:
             line["other_configs"] = extras
         if train is not None:
@@ -584,6 +723,58 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_only(args):
+    """Small single-purpose runs for profilers (`--only`): a handful of launches of one part of
+    the benchmark, so that a capture of them ends by itself.
+
+    --only gemm --shape M K N [--reps R]          the FP8 GEMM on one shape (checked, then timed)
+    --only bn --shape N C H W [--channels-last]   the five kernels of one fused BatchNorm+ReLU layer
+    --only train-profile --model resnet50|vit_b16 [--channels-last] [--no-act] [--rows R]
+                                                  two training steps under torch.profiler; under
+                                                  torchrun every rank runs them (DDP), rank 0 prints
+    """
+    import torch
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if args.only == "gemm":
+        M, K, N = args.shape
+        print(json.dumps(run_gemm_shapes(dev, ((M, K, N),), reps=args.reps)), flush=True)
+    elif args.only == "bn":
+        from deep_optimization_b200 import codec
+        N, C, H, W = args.shape
+        fmt = torch.channels_last if args.channels_last else torch.contiguous_format
+        mk = lambda: torch.randn((N, C, H, W), device=dev).to(torch.bfloat16).contiguous(memory_format=fmt)
+        w, b = torch.ones(C, device=dev), torch.zeros(C, device=dev)
+        for _ in range(args.reps):
+            x, dy = mk(), mk()
+            params = codec.bn_stats(x, 1e-5, w, b)
+            y, packed, scale, mn, mask = codec.bn_fwd_norm_quant_pack(x, None, None, w, b, BITS, 256,
+                                                                      params=params, relu=True)
+            s1, s2 = codec.bn_bwd_reduce(packed, scale, mn, dy, BITS, 256, mask=mask)
+            coef = codec.bn_bwd_coef(s1._base, params, N * H * W)
+            codec.bn_bwd_dx(packed, scale, mn, dy, None, None, None, BITS, 256, mask=mask, coef=coef)
+        torch.cuda.synchronize()
+        print("ok", flush=True)
+    elif args.only == "train-profile":
+        import torch.distributed as dist
+        from torch.profiler import ProfilerActivity, profile
+        if world > 1:
+            dist.init_process_group("nccl", device_id=dev)
+        prof = profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA])
+        res = run_train(args.model, dev, world, local, steps=2, warmup=3, act=not args.no_act,
+                        channels_last=args.channels_last, profiler=prof)
+        if rank == 0:
+            print(json.dumps(res))
+            print(prof.key_averages().table(sort_by="self_cuda_time_total", row_limit=args.rows,
+                                            max_name_column_width=70), flush=True)
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -593,7 +784,19 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the fp32 codec and GEMM side measurements")
     ap.add_argument("--no-train", action="store_true", help="skip the ResNet-50 / ViT-B/16 training steps")
+    ap.add_argument("--only", choices=("codec", "gemm", "bn", "train-profile"),
+                    help="codec: the headline alone; the others: small runs for profilers (see run_only)")
+    ap.add_argument("--shape", type=int, nargs="+", help="--only gemm: M K N; --only bn: N C H W")
+    ap.add_argument("--reps", type=int, default=5)
+    ap.add_argument("--model", default="resnet50", choices=("resnet50", "vit_b16"))
+    ap.add_argument("--channels-last", action="store_true")
+    ap.add_argument("--no-act", action="store_true")
+    ap.add_argument("--rows", type=int, default=45)
     args = ap.parse_args()
+    if args.only == "codec":
+        args.no_extras = args.no_train = True
+    elif args.only:
+        return run_only(args)
     if args.impl == "reference":
         run_reference(args)
     else:

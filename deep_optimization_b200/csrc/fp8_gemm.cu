@@ -404,6 +404,8 @@ bool make_map(CUtensorMap* map, const void* base, int rows, int cols, int ld, in
 
 int round_up(int v, int m) { return (v + m - 1) / m * m; }
 
+constexpr int kMaxDevices = 64;                      // per-device host state below is indexed by ordinal
+
 }  // namespace
 
 extern "C" size_t act_fp8_gemm_workspace(int M, int N, int K, int flags) {
@@ -447,15 +449,19 @@ extern "C" int act_fp8_gemm(const void* A, const void* B, const float* sa, const
     if (!make_map(&map_a, A, M, K, lda, BM) || !make_map(&map_bt, bt, N, K, ldbt, BN) ||
         !make_map_c(&map_c, C, M, N, ldc)) return ACT_ERR_DEVICE;
 
-    static bool attr_set = false;
+    // the shared-memory opt-in is a per-device attribute of the kernel: remember it per device,
+    // so that a process driving several GPUs sets it on each of them
+    static int sms_of_device[kMaxDevices];           // 0 = attribute not yet set on that device
     const int smem_bytes = (int)sizeof(Smem) + 1024;
-    if (!attr_set) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return ACT_ERR_DEVICE;
+    int sms = sms_of_device[dev];
+    if (!sms) {
         if (cudaFuncSetAttribute(fp8_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess)
             return ACT_ERR_DEVICE;
-        attr_set = true;
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) return ACT_ERR_DEVICE;
+        sms_of_device[dev] = sms;
     }
-    int dev = 0, sms = 148;
-    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
     const int grid = tiles < sms ? tiles : sms;
     fp8_gemm_kernel<<<grid, THREADS, smem_bytes, st>>>(map_a, map_bt, map_c, sa, sb, M, N, K);
@@ -487,7 +493,7 @@ static __device__ __align__(256) uint8_t g_static_bt_scratch[kStaticScratchBytes
 
 // Device address of the array on each device, looked up on first use.  In host code
 // the array's name is only a handle for this lookup, never a pointer to pass along.
-static uint8_t* g_static_scratch_ptr[64];
+static uint8_t* g_static_scratch_ptr[kMaxDevices];
 
 extern "C" size_t act_fp8_gemm_static_limit(void) { return kStaticScratchBytes; }
 
@@ -497,7 +503,7 @@ extern "C" int act_fp8_gemm_static(const void* A, const void* B, const float* sa
     if (M < 0 || N < 0 || K < 0) return ACT_ERR_SIZE;
     if ((size_t)N * (size_t)round_up(K > 0 ? K : 1, 16) > kStaticScratchBytes) return ACT_ERR_STATIC_LIMIT;
     int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return ACT_ERR_DEVICE;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return ACT_ERR_DEVICE;
     uint8_t* scratch = g_static_scratch_ptr[dev];
     if (!scratch) {
         // once per device, with that device current (it is: cudaGetDevice just said so)

@@ -67,42 +67,3 @@ def gemm_status(clear: bool = True) -> int:
     v = ctypes.c_uint(0)
     _lib.check(_lib.load().act_fp8_gemm_status(ctypes.byref(v), 1 if clear else 0), "act_fp8_gemm_status")
     return int(v.value)
-
-
-def _main(argv) -> None:
-    """`python -m deep_optimization_b200.gemm M K N [reps]`: time the GEMM on random e4m3
-    operands (B given as [N,K]) and print TFLOP/s beside cuBLASLt's scaled matmul."""
-    M, K, N = (int(a) for a in argv[:3])
-    reps = int(argv[3]) if len(argv) > 3 else 20
-    d = torch.device("cuda")
-    A8, sa = quantize_e4m3(torch.randn(M, K, device=d), 1)
-    B8, sb = quantize_e4m3(torch.randn(K, N, device=d), 0)
-    Bt = B8.t().contiguous()
-    C = torch.empty((M, N), dtype=torch.bfloat16, device=d)
-
-    def timed(fn):
-        for _ in range(3):
-            fn()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(reps):
-            fn()
-        e1.record()
-        torch.cuda.synchronize()
-        return e0.elapsed_time(e1) / reps
-
-    flops = 2.0 * M * N * K
-    t = timed(lambda: fp8_gemm(A8, Bt, sa, sb, b_is_nk=True, out=C))
-    print(f"fp8_gemm M={M} K={K} N={N}: {t * 1e3:.1f} us, {flops / t / 1e9:.0f} TFLOP/s, status {gemm_status()}")
-    try:
-        sa2, sb2 = sa.view(M, 1).contiguous(), sb.view(1, N).contiguous()
-        t2 = timed(lambda: torch._scaled_mm(A8, Bt.t(), scale_a=sa2, scale_b=sb2, out_dtype=torch.bfloat16))
-        print(f"cuBLASLt scaled_mm: {t2 * 1e3:.1f} us, {flops / t2 / 1e9:.0f} TFLOP/s")
-    except Exception as ex:      # library yardstick only
-        print(f"cuBLASLt scaled_mm unavailable: {str(ex)[:80]}")
-
-
-if __name__ == "__main__":
-    import sys
-    _main(sys.argv[1:])

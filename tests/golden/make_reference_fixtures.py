@@ -1,10 +1,13 @@
 """Generates tests/golden/reference_triton_codec.npz by running the REFERENCE's own Triton
 kernels (Activation_Compression/act_triton_kernel.py: quant_pack_kernel,
-dequant_unpack_kernel, pack_kernel, unpack_kernel) under Triton's CPU interpreter.
+dequant_unpack_kernel, pack_kernel, unpack_kernel) under Triton's CPU interpreter, and
+tests/golden/reference_triton_linear.npz by running its GEMM kernel
+(Activation_Compression/triton_kernel/linear.py:43-95, Triton_Linear) the same way on
+e4m3 operands.
 
 Run where the reference checkout is available:
 
-    TRITON_INTERPRET=1 python tests/golden/make_reference_fixtures.py /path/to/Deep_Optimization
+    TRITON_INTERPRET=1 python tests/golden/make_reference_fixtures.py /path/to/Deep_Optimization [codec|linear|all]
 
 The kernels are called directly (their torch.library wrappers refuse interpreted
 functions).  `libdevice.tanh`, which the interpreter cannot evaluate, is replaced for
@@ -104,5 +107,56 @@ def main():
     print("wrote", path, len(out), "arrays")
 
 
+def run_linear(A8, B8, block):
+    """C = A8 @ B8 by the reference's Triton_Linear (the jitted function under its autotuner,
+    one of its own tile shapes given explicitly), fp32 accumulator stored as fp32."""
+    import triton
+    import triton.language as tl
+    sys.path.insert(0, os.path.join(ref_root, "Activation_Compression", "triton_kernel"))
+    import linear as ref_linear
+    M, K = A8.shape
+    N = B8.shape[1]
+    bm, bn, bk = block
+    C = torch.zeros((M, N), dtype=torch.float32)
+    grid = (triton.cdiv(M, bm) * triton.cdiv(N, bn),)
+    ref_linear.Triton_Linear.fn[grid](A8, B8, C, M, N, K, A8.stride(0), A8.stride(1), B8.stride(0), B8.stride(1),
+                                      C.stride(0), C.stride(1), BLOCK_SIZE_M=bm, BLOCK_SIZE_N=bn,
+                                      BLOCK_SIZE_K=bk, GROUP_SIZE_M=8, OUT_DTYPE=tl.float32)
+    return C
+
+
+def main_linear():
+    """Two kinds of case.  `int`: small-integer operands (every product and partial sum is exact in
+    fp32, so any correct GEMM returns the same bits whatever its summation order).  `rand`: N(0,1)
+    operands scaled to the e4m3 range as the evaluation configuration describes; the fp32 sums then
+    depend on the order, which the test bounds."""
+    out = {}
+    g = torch.Generator().manual_seed(0)
+    cases = (("int", 96, 136, 160, (32, 64, 32)), ("int", 130, 72, 272, (64, 32, 32)),
+             ("rand", 64, 128, 256, (32, 64, 32)), ("rand", 100, 264, 144, (64, 128, 64)))
+    for i, (kind, M, N, K, block) in enumerate(cases):
+        if kind == "int":
+            A = torch.randint(-8, 9, (M, K), generator=g).float()
+            B = torch.randint(-8, 9, (K, N), generator=g).float()
+        else:
+            A = torch.randn(M, K, generator=g)
+            B = torch.randn(K, N, generator=g)
+            A = A / (A.abs().amax(1, keepdim=True) / 448.0)
+            B = B / (B.abs().amax(0, keepdim=True) / 448.0)
+        A8, B8 = A.to(torch.float8_e4m3fn), B.to(torch.float8_e4m3fn)
+        C = run_linear(A8, B8, block)
+        out[f"case{i}_kind"] = np.array(kind)
+        out[f"case{i}_A8"] = A8.view(torch.uint8).numpy()
+        out[f"case{i}_B8"] = B8.view(torch.uint8).numpy()
+        out[f"case{i}_C"] = C.numpy()
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference_triton_linear.npz")
+    np.savez_compressed(path, **out)
+    print("wrote", path, len(out), "arrays")
+
+
 if __name__ == "__main__":
-    main()
+    what = sys.argv[2] if len(sys.argv) > 2 else "all"
+    if what in ("codec", "all"):
+        main()
+    if what in ("linear", "all"):
+        main_linear()

@@ -55,6 +55,77 @@ def test_against_float64_product(cuda_device, shape):
     _check(got, ref, K)
 
 
+def _full_check(cuda_device, oracle, M, N, K, seed, layouts=(False, True), oracle_rows=48):
+    """Whole output against the float64 product on the GPU, a row sample against the C oracle
+    (double accumulation, bf16 bits compared as values), abort word clear, both B layouts."""
+    from deep_optimization_b200.gemm import fp8_gemm, gemm_status
+    d = cuda_device
+    g = torch.Generator(device=d).manual_seed(seed)
+    from deep_optimization_b200.gemm import quantize_e4m3
+    A8, sa = quantize_e4m3(torch.randn(M, K, device=d, generator=g), 1)
+    B8, sb = quantize_e4m3(torch.randn(K, N, device=d, generator=g), 0)
+    ref = (A8.double() @ B8.double()) * sa.double()[:, None] * sb.double()[None, :]
+    rows = torch.linspace(0, M - 1, min(M, oracle_rows), device=d).long().unique()
+    _, want_rows = oracle.fp8_gemm(A8[rows].cpu().view(torch.uint8).numpy(), B8.cpu().view(torch.uint8).numpy(),
+                                   sa[rows].cpu().numpy(), sb.cpu().numpy())
+    first = None
+    for b_is_nk in layouts:
+        Bop = B8.t().contiguous() if b_is_nk else B8
+        C = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=d)
+        fp8_gemm(A8, Bop, sa, sb, b_is_nk=b_is_nk, out=C)
+        assert gemm_status() == 0
+        assert not torch.isnan(C).any(), "part of C was never written"
+        _check(C, ref, K)
+        _check(C[rows], torch.from_numpy(want_rows), K)
+        if first is None:
+            first = C
+        else:
+            assert torch.equal(first, C)       # same kernel and operands: the layouts agree bit for bit
+    del ref
+
+
+# More tiles than the 148 CTAs of the persistent grid, odd and uneven tile counts per CTA, ragged
+# edges: the second accumulator buffer, every mbarrier phase flip and the ring carried from one
+# tile to the next all run here.  (M, N, K): tiles = ceil(M/128) * ceil(N/256).
+@pytest.mark.parametrize("shape", [(5000, 1024, 256),        # 40 x 4 = 160 tiles: 12 CTAs take two
+                                   (128 * 151, 768, 384),    # 453 tiles: 3 per CTA and 9 take a fourth
+                                   (4096, 4096, 256),        # 512 tiles, two k-blocks each
+                                   (4096, 2304, 384),        # 288 tiles, three k-blocks: the ring phase drifts
+                                   (4100, 2312, 400),        # ragged M, N and K (K % 128 != 0)
+                                   (19000, 520, 144),        # 447 tiles with a 8-column last tile, 2 k-blocks
+                                   (12800, 256, 2048)])      # 100 tiles of 16 k-blocks on 100 CTAs, then ...
+def test_persistent_multi_tile(oracle, cuda_device, shape):
+    M, N, K = shape
+    _full_check(cuda_device, oracle, M, N, K, seed=M + N + K)
+
+
+# The three shapes of the evaluation configuration (M, K, N) = (8192,4096,4096), (50432,768,3072),
+# (50432,3072,768): 1024 / 4728 / 1182 tiles.
+@pytest.mark.parametrize("shape", [(8192, 4096, 4096), (50432, 3072, 768), (50432, 768, 3072)])
+def test_evaluation_shapes(oracle, cuda_device, shape):
+    M, N, K = shape
+    _full_check(cuda_device, oracle, M, N, K, seed=5)
+    torch.cuda.empty_cache()
+
+
+def test_two_calls_back_to_back_keep_their_results(cuda_device):
+    """Two GEMMs in flight on one stream with different operands and outputs: the second must not
+    disturb the first (nothing but the abort word is shared between launches)."""
+    from deep_optimization_b200.gemm import fp8_gemm, gemm_status, quantize_e4m3
+    d = cuda_device
+    g = torch.Generator(device=d).manual_seed(3)
+    ops = []
+    for (M, N, K) in ((6000, 1536, 512), (3000, 2048, 640)):
+        A8, sa = quantize_e4m3(torch.randn(M, K, device=d, generator=g), 1)
+        B8, sb = quantize_e4m3(torch.randn(N, K, device=d, generator=g), 1)
+        ops.append((A8, B8, sa, sb))
+    outs = [fp8_gemm(A8, B8, sa, sb, b_is_nk=True) for (A8, B8, sa, sb) in ops]
+    assert gemm_status() == 0
+    for (A8, B8, sa, sb), C in zip(ops, outs):
+        ref = (A8.double() @ B8.double().t()) * sa.double()[:, None] * sb.double()[None, :]
+        _check(C, ref, A8.shape[1])
+
+
 def test_linearity_and_identity(cuda_device):
     """Size-independent properties: an identity B returns A scaled, and doubling sa doubles C."""
     from deep_optimization_b200.gemm import fp8_gemm
@@ -77,3 +148,27 @@ def test_argument_errors(cuda_device):
     B = torch.zeros(24, 16, device=d).to(torch.float8_e4m3fn)
     with pytest.raises(_lib.ActLibraryError):
         fp8_gemm(A, B, torch.ones(16, device=d), torch.ones(16, device=d))
+
+
+@pytest.mark.parametrize("case", range(4))
+def test_against_reference_kernel_fixture(cuda_device, case):
+    """The CUDA kernel against outputs of the reference's own Triton GEMM kernel
+    (tests/golden/reference_triton_linear.npz, made by tests/golden/make_reference_fixtures.py):
+    scales of one.  Integer-operand cases: every product and partial sum is exact in fp32, so the
+    only rounding is the final one to bf16 and the comparison is exact.  Random cases: within the
+    GEMM tolerance."""
+    import os
+    from deep_optimization_b200.gemm import fp8_gemm, gemm_status
+    fx = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "reference_triton_linear.npz"))
+    A8 = torch.from_numpy(fx[f"case{case}_A8"]).view(torch.float8_e4m3fn)
+    B8 = torch.from_numpy(fx[f"case{case}_B8"]).view(torch.float8_e4m3fn)
+    want = torch.from_numpy(fx[f"case{case}_C"])
+    M, K = A8.shape
+    N = B8.shape[1]
+    d = cuda_device
+    got = fp8_gemm(A8.to(d), B8.to(d), torch.ones(M, device=d), torch.ones(N, device=d))
+    assert gemm_status() == 0
+    if str(fx[f"case{case}_kind"]) == "int":
+        assert torch.equal(got.cpu(), want.to(torch.bfloat16))       # exact sums, one rounding to bf16
+    else:
+        _check(got, want, K)

@@ -82,3 +82,31 @@ def test_dequant_and_masks(oracle, fix, bits, gs):
     mask = fix[key + "_mask"]
     assert np.array_equal(oracle.pack_bits(mask, gs, bits), fix[key + "_mask_packed"])
     assert np.array_equal(oracle.unpack_bits(fix[key + "_mask_packed"], gs, bits), fix[key + "_mask_unpacked"])
+
+
+# ---------------------------------------------------------------- FP8 GEMM
+# tests/golden/reference_triton_linear.npz: outputs of the reference's own GEMM kernel
+# (Activation_Compression/triton_kernel/linear.py:43-95) run under Triton's CPU interpreter on
+# e4m3 operands, fp32 accumulator stored as fp32.  With scales of one the oracle's product must
+# reproduce them: exactly where every partial sum is exact (small-integer operands), and within
+# the fp32 summation-order bound K * 2^-24 * sum|a*b| otherwise (the oracle sums in double).
+LIN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "reference_triton_linear.npz")
+
+
+@pytest.mark.parametrize("case", range(4))
+def test_gemm_oracle_against_reference_kernel(oracle, case):
+    fx = np.load(LIN)
+    A8, B8, want = fx[f"case{case}_A8"], fx[f"case{case}_B8"], fx[f"case{case}_C"]
+    M, K = A8.shape
+    N = B8.shape[1]
+    _, got = oracle.fp8_gemm(A8, B8, np.ones(M, np.float32), np.ones(N, np.float32))
+    if str(fx[f"case{case}_kind"]) == "int":
+        assert np.array_equal(got, want)
+    else:
+        a = np.abs(oracle.e4m3_decode(A8).astype(np.float64))
+        b = np.abs(oracle.e4m3_decode(B8).astype(np.float64))
+        bound = (a @ b) * K * 2.0 ** -24 + 1e-30
+        assert (np.abs(got.astype(np.float64) - want.astype(np.float64)) <= bound).all()
+        # and the double-accumulated value is the closer one to the exact product
+        exact = oracle.e4m3_decode(A8).astype(np.float64) @ oracle.e4m3_decode(B8).astype(np.float64)
+        assert np.abs(got - exact).max() <= np.abs(exact).max() * 2.0 ** -23
