@@ -19,6 +19,7 @@ ACT_FLAG_REF_CLAMP = 4
 ACT_FLAG_REF_TANH = 8
 ACT_FLAG_META_BF16 = 16
 ACT_GEMM_B_IS_NK = 1
+ACT_GEMM_SINGLE_CTA = 2
 ACT_KIND_GELU, ACT_KIND_SILU = 1, 2
 
 # every symbol include/act_b200.h declares, with its ctypes signature

@@ -325,6 +325,370 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     }
 }
 
+// ===================================================================== CTA-pair kernel
+// Two CTAs on the two SMs of one TPC (a cluster of two) compute one 256 x 256 tile with
+// tcgen05.mma.cta_group::2: each CTA stages its own 128 rows of A and its own 128 rows of
+// B^T (32 KB per k-block instead of the 48 KB a lone CTA needs for 128 x 256), the tensor
+// cores of the pair exchange the B halves over the SM-to-SM link, and each CTA keeps the
+// 128 x 256 accumulator of its own rows in its own tensor memory.  L2-to-SM traffic per
+// flop drops by a third, which is what bounds the lone-CTA kernel on short-K shapes.
+//
+// Roles per CTA (320 threads): warp 0 = TMA producer (both CTAs load; the loads carry
+// .cta_group::2 so that their bytes are counted on the leader's mbarrier; no multicast),
+// warp 1 = MMA issuer (rank 0 of the pair only; its commits arrive on the barriers of both
+// CTAs), warps 2..9 = epilogue (each CTA drains its own accumulator; 32 x 64 bf16 pieces go
+// through two swizzled staging buffers per warp into bulk tensor stores of full 128-byte
+// rows).  Every wait is bounded as in the lone-CTA kernel.
+namespace pair {
+
+constexpr int BM_CTA = 128;                     // rows of A (and of B^T) staged per CTA
+constexpr int BN = 256, BK = 128;
+constexpr int TILE_M = 2 * BM_CTA;              // rows of C per pair
+#ifndef ACT_GEMM_PAIR_STAGES
+#define ACT_GEMM_PAIR_STAGES 5
+#endif
+#ifndef ACT_GEMM_EPI_BUFS
+#define ACT_GEMM_EPI_BUFS 2
+#endif
+#ifndef ACT_GEMM_PREFETCH
+#define ACT_GEMM_PREFETCH 0                      // 1: every cluster requests its next A rows into L2; 2: one per row group
+#endif
+#ifndef ACT_GEMM_EPI_TEST
+#define ACT_GEMM_EPI_TEST 0                      // 1, 2: timing experiments with wrong results, never shipped
+#endif
+constexpr int STAGES = ACT_GEMM_PAIR_STAGES;
+constexpr int EPI_BUFS = ACT_GEMM_EPI_BUFS;     // staging buffers per epilogue warp
+constexpr int A_STAGE = BM_CTA * BK, B_STAGE = BM_CTA * BK;
+constexpr int PIECE_BYTES = 32 * 128;           // 32 rows x 64 bf16
+
+struct __align__(1024) Smem {
+    uint8_t a[STAGES][A_STAGE];
+    uint8_t b[STAGES][B_STAGE];
+    uint8_t cstage[EPI_WARPS][EPI_BUFS][PIECE_BYTES];   // 128-byte rows, 16-byte pieces xor-swizzled by row & 7
+    float sb[2][BN];
+    uint64_t full[STAGES], empty[STAGES], acc_full[2], acc_empty[2];
+    uint32_t tmem_base;
+    volatile uint32_t abort;
+};
+static_assert(sizeof(Smem) <= 227 * 1024, "shared memory of the pair kernel exceeds one SM");
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r;
+}
+__device__ __forceinline__ uint32_t cluster_id() {
+    uint32_t r; asm volatile("mov.u32 %0, %%clusterid.x;" : "=r"(r)); return r;
+}
+__device__ __forceinline__ uint32_t n_clusters() {
+    uint32_t r; asm volatile("mov.u32 %0, %%nclusterid.x;" : "=r"(r)); return r;
+}
+// address of the same shared-memory location in CTA `rank` of this cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+    uint32_t r; asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank)); return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+#ifndef ACT_GEMM_ARRIVE_MODE
+#define ACT_GEMM_ARRIVE_MODE 1
+#endif
+// Arrival on an mbarrier of (possibly) the other CTA of the pair.  It orders nothing but the
+// tensor-memory loads before it, which tcgen05.wait::ld and the tcgen05 fence already did, so it
+// carries the default CTA-scope release: a cluster-scope release made every accumulator hand-back
+// wait about 3000 cycles for the thread's earlier stores.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+#if ACT_GEMM_ARRIVE_MODE == 0
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" :: "r"(cluster_addr) : "memory");
+#elif ACT_GEMM_ARRIVE_MODE == 2
+    asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" :: "r"(cluster_addr) : "memory");
+#else
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" :: "r"(cluster_addr) : "memory");
+#endif
+}
+__device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v) {
+    asm volatile("st.shared::cluster.u32 [%0], %1;" :: "r"(cluster_addr), "r"(v) : "memory");
+}
+// tile load whose completion bytes are counted on an mbarrier of the pair's leader
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint32_t leader_bar, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+                 " [%0], [%1, {%3, %4}], [%2];"
+                 :: "r"(smem_u32(dst)), "l"(map), "r"(leader_bar), "r"(c0), "r"(c1) : "memory");
+}
+// requests a tile into L2 only (no shared-memory destination, nothing to wait for)
+__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* map, int c0, int c1) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
+                 :: "l"(map), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void umma_f8_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+                 :: "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// arrives, once the pair's MMAs issued so far are done, on the barrier at this offset in both CTAs
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+    const uint16_t both = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 :: "r"(smem_u32(bar)), "h"(both) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                 :: "r"(smem_u32(dst_smem)), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" :: "r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tma_store_wait_read_keep(int keep) {
+    if (keep == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+    else           asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+}
+// fp32 accumulate, A and B e4m3, both K-major, N = 256, M = 256 (both CTAs together)
+__host__ __device__ constexpr uint32_t make_idesc_pair() {
+    return (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TILE_M >> 4) << 24);
+}
+
+#ifdef ACT_GEMM_TRACE
+// timing experiment: cycle stamps of the first tiles of CTA 0, [tile][slot]
+constexpr int TRACE_TILES = 24, TRACE_SLOTS = 16;
+__device__ long long g_trace[TRACE_TILES * TRACE_SLOTS];
+#define TRACE(tile, slot, val) do { if (blockIdx.x == 0 && (tile) < TRACE_TILES) g_trace[(tile) * TRACE_SLOTS + (slot)] = (val); } while (0)
+#else
+#define TRACE(tile, slot, val) do {} while (0)
+#endif
+
+template <typename S>
+__device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, S* s, uint32_t code, uint32_t peer_abort_addr) {
+    for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (s->abort) return false;
+    }
+    s->abort = 1;
+    st_cluster_u32(peer_abort_addr, 1u);            // the other CTA of the pair gives up too
+    atomicExch(&g_gemm_error, code);
+    return false;
+}
+template <typename S>
+__device__ __forceinline__ bool wait_bar_warp(uint64_t* bar, uint32_t parity, S* s, uint32_t code, uint32_t peer_abort_addr) {
+    uint32_t ok = 1;
+    if ((threadIdx.x & 31) == 0) {
+        ok = 0;
+        for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+            if (mbar_try_wait(bar, parity)) { ok = 1; break; }
+            if (s->abort) break;
+            __nanosleep(32);
+        }
+        if (!ok && !s->abort) { s->abort = 1; st_cluster_u32(peer_abort_addr, 1u); atomicExch(&g_gemm_error, code); }
+    }
+    return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_bt,
+                     const __grid_constant__ CUtensorMap map_c,
+                     const float* __restrict__ sa, const float* __restrict__ sb, int M, int N, int K)
+{
+    extern __shared__ __align__(1024) uint8_t smem_raw_pair[];
+    Smem* s = reinterpret_cast<Smem*>(smem_raw_pair);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();                  // 0 = leader of the pair
+    const int m_tiles = (M + TILE_M - 1) / TILE_M, n_tiles = (N + BN - 1) / BN;
+    const int n_work = m_tiles * n_tiles;
+    const int k_blocks = (K + BK - 1) / BK;
+    const int first = (int)cluster_id(), stride = (int)n_clusters();
+    const uint32_t peer_abort = map_to_cta(smem_u32((const void*)&s->abort), rank ^ 1u);
+
+    if (smem_u32(s) & 1023u) {                                // the swizzled tiles need this alignment
+        if (threadIdx.x == 0) atomicExch(&g_gemm_error, 5u);
+        return;                                               // uniform over the grid: nobody waits for anybody
+    }
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < STAGES; ++i) { mbar_init(&s->full[i], 1); mbar_init(&s->empty[i], 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(&s->acc_full[i], 1); mbar_init(&s->acc_empty[i], 2 * EPI_WARPS); }
+        s->abort = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) tmem_alloc_pair(&s->tmem_base, TMEM_COLS);   // the same warp of both CTAs
+    tc_fence_before();
+    cluster_sync_all();                                       // barriers of both CTAs exist from here on
+    tc_fence_after();
+    const uint32_t tmem_base = s->tmem_base;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer (both CTAs)
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (int w = first; ok && w < n_work; w += stride) {
+                const int m0 = (w / n_tiles) * TILE_M + (int)rank * BM_CTA;
+                const int n0 = (w % n_tiles) * BN + (int)rank * BM_CTA;
+#if ACT_GEMM_PREFETCH
+                // A is read from HBM exactly once (the clusters that share its rows run side by side),
+                // so every first touch of an A block would pay the HBM latency inside the ring.  The
+                // rows of this cluster's NEXT tile are therefore requested into L2 one tile ahead, by
+                // one cluster per group of clusters that will share them.
+                const int w_next = w + stride;
+                const bool prefetch = w_next < n_work &&
+                                      (ACT_GEMM_PREFETCH == 1 || (w_next % n_tiles) == 0 || first == 0);
+                const int m0_next = (w_next / n_tiles) * TILE_M + (int)rank * BM_CTA;
+#endif
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!(ok = wait_bar(&s->empty[stage], phase ^ 1, s, 1, peer_abort))) break;
+                    // the leader's barrier counts the bytes of all four loads of the pair
+                    if (rank == 0) mbar_expect_tx(&s->full[stage], 2 * (A_STAGE + B_STAGE));
+                    const uint32_t bar = map_to_cta(smem_u32(&s->full[stage]), 0);
+                    tma_load_2d_pair(s->a[stage], &map_a, bar, kb * BK, m0);
+                    tma_load_2d_pair(s->b[stage], &map_bt, bar, kb * BK, n0);
+#if ACT_GEMM_PREFETCH
+                    if (prefetch) tma_prefetch_l2_2d(&map_a, kb * BK, m0_next);
+#endif
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+            // tail: every slot handed out has come back, i.e. no arrival from the leader's
+            // commits is still on its way to this CTA's barriers when the CTA leaves
+            for (int i = 0; ok && i < STAGES; ++i) {
+                ok = wait_bar(&s->empty[stage], phase ^ 1, s, 6, peer_abort);
+                if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            }
+        }
+    } else if (warp == 1) {
+        // -------------------------------------------------------------- MMA issuer (leader only)
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t idesc = make_idesc_pair();
+            uint32_t stage = 0, phase = 0, acc_phase[2] = {0, 0};
+            bool ok = true;
+            int t = 0;
+            for (int w = first; ok && w < n_work; w += stride, ++t) {
+                const int buf = t & 1;
+                TRACE(t, 0, clock64());
+                if (!(ok = wait_bar(&s->acc_empty[buf], acc_phase[buf] ^ 1, s, 2, peer_abort))) break;
+                TRACE(t, 1, clock64());
+                tc_fence_after();
+                const uint32_t d = tmem_base + (uint32_t)(buf * BN);
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!(ok = wait_bar(&s->full[stage], phase, s, 3, peer_abort))) break;
+                    if (kb == 0) TRACE(t, 2, clock64());
+                    tc_fence_after();
+                    const uint64_t adesc = make_kmajor_desc(s->a[stage]);
+                    const uint64_t bdesc = make_kmajor_desc(s->b[stage]);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        umma_f8_pair(d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) ? 1u : 0u);
+                    umma_commit_pair(&s->empty[stage]);        // frees the slot in both CTAs
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+                umma_commit_pair(&s->acc_full[buf]);           // both CTAs' accumulators are complete
+                TRACE(t, 3, clock64());
+                acc_phase[buf] ^= 1;
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------- epilogue (both CTAs)
+        const int q = warp & 3;                                // TMEM lane quarter this warp may read
+        const int half = (warp - 2) >> 2;                      // which 128 columns of the tile
+        const int etid = threadIdx.x - 64;
+        uint8_t* my_stage = &s->cstage[warp - 2][0][0];
+        uint32_t full_phase[2] = {0, 0};
+        // a tile is two 32 x 64 pieces per warp, piece p staged in buffer p % EPI_BUFS
+        uint32_t groups = 0, last_group[EPI_BUFS] = {};        // lane 0: store groups committed, and which one last read a buffer
+        bool ok = true;
+        int t = 0;
+        for (int w = first; w < n_work; w += stride, ++t) {
+            const int buf = t & 1;
+            const int m0 = (w / n_tiles) * TILE_M + (int)rank * BM_CTA, n0 = (w % n_tiles) * BN;
+            s->sb[buf][etid] = (n0 + etid < N) ? __ldg(sb + n0 + etid) : 0.0f;
+            asm volatile("bar.sync 1, %0;" :: "n"(EPI_WARPS * 32) : "memory");
+            if (threadIdx.x == 64) TRACE(t, 4, clock64());
+            const int row = m0 + q * 32 + lane;
+            const float sa_row = row < M ? __ldg(sa + row) : 0.0f;
+            const f32x2 sa2 = pack2(sa_row, sa_row);
+            if (ok) ok = wait_bar_warp(&s->acc_full[buf], full_phase[buf], s, 4, peer_abort);
+            if (!ok) continue;
+            if (threadIdx.x == 64) TRACE(t, 5, clock64());
+            full_phase[buf] ^= 1;
+            tc_fence_after();
+            const uint32_t t_base = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + half * 128);
+            const float* sb_s = s->sb[buf] + half * 128;
+            uint32_t r[2][32];
+            tmem_ld32(t_base, r[0]);
+#pragma unroll
+            for (int chunk = 0; chunk < 4; ++chunk) {
+                tmem_ld_wait();
+                if (chunk + 1 < 4) tmem_ld32(t_base + (uint32_t)((chunk + 1) * 32), r[(chunk + 1) & 1]);
+                else {
+                    // the accumulator now lives in registers: hand the buffer back to the leader
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&s->acc_empty[buf]), 0));
+                }
+                const uint32_t* rc = r[chunk & 1];
+                constexpr int kBufOfPiece[2] = {0, 1 % EPI_BUFS};
+                const int pb = kBufOfPiece[chunk >> 1];
+                uint8_t* stage_buf = my_stage + pb * PIECE_BYTES;
+                if ((chunk & 1) == 0) {
+                    // the store that last read this staging buffer must be done with it: it is if at
+                    // most (groups committed after it) groups are still reading (a skipped store, at a
+                    // ragged edge, commits no group, so the count is kept rather than assumed)
+                    if (lane == 0) tma_store_wait_read_keep(groups - last_group[pb] >= 1u ? 1 : 0);
+                    __syncwarp();
+                }
+#pragma unroll
+                for (int v = 0; v < 4; ++v) {
+                    const float4 s0 = *reinterpret_cast<const float4*>(sb_s + chunk * 32 + v * 8);
+                    const float4 s1 = *reinterpret_cast<const float4*>(sb_s + chunk * 32 + v * 8 + 4);
+                    const f32x2 sc[4] = {pack2(s0.x, s0.y), pack2(s0.z, s0.w), pack2(s1.x, s1.y), pack2(s1.z, s1.w)};
+                    uint32_t o[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        uint32_t lo, hi;
+                        unpack2u(mul2_rn(mul2_rn(pack2u(rc[v * 8 + 2 * i], rc[v * 8 + 2 * i + 1]), sa2), sc[i]), lo, hi);
+                        const __nv_bfloat162 p = __floats2bfloat162_rn(__uint_as_float(lo), __uint_as_float(hi));
+                        o[i] = *reinterpret_cast<const uint32_t*>(&p);
+                    }
+                    // row `lane`, 16-byte piece (chunk & 1) * 4 + v of its 128 bytes, xor-swizzled by the row
+                    const int pc = ((chunk & 1) * 4 + v) ^ (lane & 7);
+                    *reinterpret_cast<uint4*>(stage_buf + lane * 128 + (pc << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                }
+                if (threadIdx.x == 64) TRACE(t, 6 + chunk, clock64());
+                if (chunk & 1) {
+                    // 32 rows x 64 columns leave as one bulk tensor store of full 128-byte rows
+                    fence_proxy_async();
+                    __syncwarp();
+                    const int col0 = n0 + half * 128 + (chunk >> 1) * 64;
+#if ACT_GEMM_EPI_TEST == 1
+                    (void)col0;                              // experiment: everything but the store
+#elif ACT_GEMM_EPI_TEST == 2
+                    if (lane == 0 && col0 < N && m0 + q * 32 < M) {   // experiment: all stores land in one 256 x 256 corner
+                        tma_store_2d(&map_c, stage_buf, col0 % 256, (m0 + q * 32) % 256);
+                        last_group[pb] = ++groups;
+                    }
+#else
+                    if (lane == 0 && col0 < N && m0 + q * 32 < M) {
+                        tma_store_2d(&map_c, stage_buf, col0, m0 + q * 32);
+                        last_group[pb] = ++groups;
+                    }
+#endif
+                }
+            }
+        }
+        if (lane == 0) tma_store_wait_all();
+    }
+
+    __syncwarp();                                             // lanes that had no role wait for the one that had
+    // ---------------------------------------------------------------- teardown
+    if (s->abort) {
+        for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+    }
+    tc_fence_before();
+    cluster_sync_all();                                       // neither CTA's memory is needed by the other any more
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    }
+}
+
+}  // namespace pair
+
 // ---------------------------------------------------------- [K,N] -> [N,K] bytes
 // 64x64 byte tiles through shared memory; both global sides move 4-byte words.
 __global__ void __launch_bounds__(256)
@@ -390,6 +754,19 @@ bool make_map_c(CUtensorMap* map, void* base, int rows, int cols, int ld) {
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// C for the pair kernel: box 64 x 32 elements (full 128-byte rows), 128-byte swizzle
+bool make_map_c_wide(CUtensorMap* map, void* base, int rows, int cols, int ld) {
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    const cuuint32_t box[2] = {64, 32};
+    const cuuint32_t estr[2] = {1, 1};
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 bool make_map(CUtensorMap* map, const void* base, int rows, int cols, int ld, int box_rows) {
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) return false;
@@ -445,27 +822,68 @@ extern "C" int act_fp8_gemm(const void* A, const void* B, const float* sa, const
         bt = static_cast<const uint8_t*>(workspace);
     }
 
-    CUtensorMap map_a, map_bt, map_c;
-    if (!make_map(&map_a, A, M, K, lda, BM) || !make_map(&map_bt, bt, N, K, ldbt, BN) ||
-        !make_map_c(&map_c, C, M, N, ldc)) return ACT_ERR_DEVICE;
-
-    // the shared-memory opt-in is a per-device attribute of the kernel: remember it per device,
-    // so that a process driving several GPUs sets it on each of them
-    static int sms_of_device[kMaxDevices];           // 0 = attribute not yet set on that device
-    const int smem_bytes = (int)sizeof(Smem) + 1024;
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return ACT_ERR_DEVICE;
-    int sms = sms_of_device[dev];
-    if (!sms) {
-        if (cudaFuncSetAttribute(fp8_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess)
+    // Per-device state, set up on the first call on that device: the shared-memory opt-in is a
+    // per-device attribute of each kernel, so a process driving several GPUs sets it on each.
+    struct DeviceState { int sms; int clusters; };
+    static DeviceState state[kMaxDevices];                  // sms == 0: not yet set up
+    const int smem_one = (int)sizeof(Smem) + 1024;
+    const int smem_pair = (int)sizeof(pair::Smem);
+    DeviceState& ds = state[dev];
+    if (!ds.sms) {
+        int sms = 0;
+        if (cudaFuncSetAttribute(fp8_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_one) != cudaSuccess ||
+            cudaFuncSetAttribute(pair::fp8_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_pair) != cudaSuccess)
             return ACT_ERR_DEVICE;
         if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) return ACT_ERR_DEVICE;
-        sms_of_device[dev] = sms;
+        // how many CTA pairs the device holds at once (one CTA per SM, both SMs of a TPC)
+        cudaLaunchConfig_t q = {};
+        q.gridDim = dim3(2u * (unsigned)sms, 1, 1);
+        q.blockDim = dim3(THREADS, 1, 1);
+        q.dynamicSmemBytes = (size_t)smem_pair;
+        cudaLaunchAttribute qa[1];
+        qa[0].id = cudaLaunchAttributeClusterDimension;
+        qa[0].val.clusterDim.x = 2; qa[0].val.clusterDim.y = 1; qa[0].val.clusterDim.z = 1;
+        q.attrs = qa; q.numAttrs = 1;
+        int clusters = 0;
+        if (cudaOccupancyMaxActiveClusters(&clusters, pair::fp8_gemm_pair_kernel, &q) != cudaSuccess || clusters <= 0) {
+            (void)cudaGetLastError();
+            clusters = sms / 2;
+        }
+        ds.clusters = clusters < sms / 2 ? clusters : sms / 2;
+        ds.sms = sms;
     }
-    const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-    const int grid = tiles < sms ? tiles : sms;
-    fp8_gemm_kernel<<<grid, THREADS, smem_bytes, st>>>(map_a, map_bt, map_c, sa, sb, M, N, K);
-    return cudaGetLastError() == cudaSuccess ? ACT_OK : ACT_ERR_LAUNCH;
+
+    CUtensorMap map_a, map_bt, map_c;
+    // A lone CTA per 128 x 256 tile when asked for, or when the problem has a single row block
+    // (the second CTA of a pair would stage rows that do not exist); otherwise CTA pairs.
+    if ((flags & ACT_GEMM_SINGLE_CTA) || M <= BM) {
+        if (!make_map(&map_a, A, M, K, lda, BM) || !make_map(&map_bt, bt, N, K, ldbt, BN) ||
+            !make_map_c(&map_c, C, M, N, ldc)) return ACT_ERR_DEVICE;
+        const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+        const int grid = tiles < ds.sms ? tiles : ds.sms;
+        fp8_gemm_kernel<<<grid, THREADS, smem_one, st>>>(map_a, map_bt, map_c, sa, sb, M, N, K);
+        return cudaGetLastError() == cudaSuccess ? ACT_OK : ACT_ERR_LAUNCH;
+    }
+    if (!make_map(&map_a, A, M, K, lda, pair::BM_CTA) || !make_map(&map_bt, bt, N, K, ldbt, pair::BM_CTA) ||
+        !make_map_c_wide(&map_c, C, M, N, ldc)) return ACT_ERR_DEVICE;
+    const int work = ((M + pair::TILE_M - 1) / pair::TILE_M) * ((N + pair::BN - 1) / pair::BN);
+    const int clusters = work < ds.clusters ? work : ds.clusters;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2u * (unsigned)clusters, 1, 1);
+    cfg.blockDim = dim3(THREADS, 1, 1);
+    cfg.dynamicSmemBytes = (size_t)smem_pair;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, pair::fp8_gemm_pair_kernel, map_a, map_bt, map_c, sa, sb, M, N, K) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return ACT_ERR_LAUNCH;
+    }
+    return ACT_OK;
 }
 
 // Reads (and optionally clears) the abort reason of the last GEMM on the current
@@ -494,6 +912,12 @@ static __device__ __align__(256) uint8_t g_static_bt_scratch[kStaticScratchBytes
 // Device address of the array on each device, looked up on first use.  In host code
 // the array's name is only a handle for this lookup, never a pointer to pass along.
 static uint8_t* g_static_scratch_ptr[kMaxDevices];
+
+#ifdef ACT_GEMM_TRACE
+extern "C" int act_fp8_gemm_trace(long long* out) {
+    return cudaMemcpyFromSymbol(out, act::gemm::pair::g_trace, sizeof(long long) * 24 * 16) == cudaSuccess ? 0 : 1;
+}
+#endif
 
 extern "C" size_t act_fp8_gemm_static_limit(void) { return kStaticScratchBytes; }
 

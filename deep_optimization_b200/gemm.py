@@ -31,7 +31,7 @@ def workspace_bytes(M: int, N: int, K: int, b_is_nk: bool) -> int:
 
 def fp8_gemm(A8: torch.Tensor, B8: torch.Tensor, sa: torch.Tensor, sb: torch.Tensor,
              b_is_nk: bool = False, out: Optional[torch.Tensor] = None,
-             workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+             workspace: Optional[torch.Tensor] = None, single_cta: bool = False) -> torch.Tensor:
     if not A8.is_cuda:
         raise RuntimeError("fp8_gemm needs CUDA tensors: there is no CPU path")
     if A8.dtype != torch.float8_e4m3fn or B8.dtype != torch.float8_e4m3fn:
@@ -46,7 +46,7 @@ def fp8_gemm(A8: torch.Tensor, B8: torch.Tensor, sa: torch.Tensor, sb: torch.Ten
     if sa.numel() != M or sb.numel() != N:
         raise ValueError("sa must have M entries and sb N entries")
     C = out if out is not None else torch.empty((M, N), dtype=torch.bfloat16, device=A8.device)
-    flags = _lib.ACT_GEMM_B_IS_NK if b_is_nk else 0
+    flags = (_lib.ACT_GEMM_B_IS_NK if b_is_nk else 0) | (_lib.ACT_GEMM_SINGLE_CTA if single_cta else 0)
     need = workspace_bytes(M, N, K, b_is_nk)
     ws_ptr, ws_len = None, 0
     if need:

@@ -46,6 +46,7 @@ extern "C" {
 
 /* flags of act_fp8_gemm */
 #define ACT_GEMM_B_IS_NK 1         /* B is stored [N,K] (K contiguous, like nn.Linear weights)        */
+#define ACT_GEMM_SINGLE_CTA 2      /* one CTA per 128x256 tile instead of CTA pairs on 256x256 tiles  */
 
 /* return codes */
 #define ACT_OK             0
