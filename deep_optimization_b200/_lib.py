@@ -20,7 +20,7 @@ ACT_FLAG_REF_TANH = 8
 ACT_FLAG_META_BF16 = 16
 ACT_GEMM_B_IS_NK = 1
 ACT_GEMM_SINGLE_CTA = 2
-ACT_KIND_GELU, ACT_KIND_SILU = 1, 2
+ACT_KIND_GELU, ACT_KIND_SILU, ACT_KIND_GELU_ERF = 1, 2, 3
 
 # every symbol include/act_b200.h declares, with its ctypes signature
 _vp, _i32, _i64, _u64, _f32 = (ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_uint64,

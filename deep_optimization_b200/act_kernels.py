@@ -193,13 +193,15 @@ def _fused_act_fake(x, bits, group_size):
 
 
 @_op("gelu_fwd_fused_quan_pack")
-def gelu_fwd_fused_quan_pack(x: torch.Tensor, bits: int, group_size: int
+def gelu_fwd_fused_quan_pack(x: torch.Tensor, bits: int, group_size: int, exact: bool = False
                              ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, int, int]:
-    return _fused_act_fwd(x, "gelu", bits, group_size)
+    """`exact` (an addition to the reference's schema) selects x * Phi(x) instead of the tanh
+    approximation, for modules built from nn.GELU(approximate="none")."""
+    return _fused_act_fwd(x, "gelu_erf" if exact else "gelu", bits, group_size)
 
 
 @gelu_fwd_fused_quan_pack.register_fake
-def _(x, bits, group_size):
+def _(x, bits, group_size, exact=False):
     return _fused_act_fake(x, bits, group_size)
 
 

@@ -23,10 +23,39 @@ _next_offset = 0
 
 
 def manual_seed(seed: int) -> None:
-    """Seed of the in-kernel counter hash used when no noise tensor is passed."""
-    global _default_seed, _next_offset
+    """Seed of the in-kernel counter hash used when no noise tensor is passed.  In a
+    torch.distributed job every rank may pass the same value: the rank is mixed in when
+    the seed is used (see `_stream_seed`)."""
+    global _default_seed, _next_offset, _seed_for_rank
     _default_seed = int(seed) & 0xFFFFFFFFFFFFFFFF
     _next_offset = 0
+    _seed_for_rank = None
+
+
+_seed_for_rank = None        # (rank, seed mixed with it), computed on first use
+
+
+def _mix64(z: int) -> int:
+    """splitmix64 finaliser (the same mixing function the kernels key their hash with)."""
+    z = (z + 0x9E3779B97F4A7C15) & 0xFFFFFFFFFFFFFFFF
+    z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & 0xFFFFFFFFFFFFFFFF
+    z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & 0xFFFFFFFFFFFFFFFF
+    return z ^ (z >> 31)
+
+
+def _stream_seed() -> int:
+    """The default seed of this process.  Data-parallel ranks start from the same Python state,
+    so with one shared seed they would all draw the same rounding noise per element index and
+    their rounding errors would add up across the gradient all-reduce instead of averaging out:
+    once a process group exists, the rank is mixed into the seed (rank 0 keeps the plain seed,
+    so single-process results do not change)."""
+    global _seed_for_rank
+    rank = 0
+    if torch.distributed.is_available() and torch.distributed.is_initialized():
+        rank = torch.distributed.get_rank()
+    if _seed_for_rank is None or _seed_for_rank[0] != rank:
+        _seed_for_rank = (rank, _default_seed if rank == 0 else _default_seed ^ _mix64(rank))
+    return _seed_for_rank[1]
 
 
 def _bits_consts(bits: int, group_size: int):
@@ -100,7 +129,7 @@ def quant_pack(x: torch.Tensor, bits: int, group_size: int, noise: Optional[torc
         if noise.numel() != x.numel():
             raise ValueError("noise must have as many elements as x")
     if seed is None:
-        seed = _default_seed
+        seed = _stream_seed()
     if offset is None:
         offset = _next_offset
         _next_offset += 1
@@ -164,7 +193,7 @@ def quant_pack_avg(x: torch.Tensor, bits: int, group_size: int, avg: int,
         if noise.numel() != x.numel():
             raise ValueError("noise must have as many elements as x")
     if seed is None:
-        seed = _default_seed
+        seed = _stream_seed()
     if offset is None:
         offset = _next_offset
         _next_offset += 1
@@ -218,7 +247,7 @@ def quant_pack_tiles(x: torch.Tensor, bits: int, tile: int, seed: Optional[int] 
     scale = torch.empty((groups,), dtype=torch.float32, device=x.device)
     mn = torch.empty((groups,), dtype=torch.float32, device=x.device)
     if seed is None:
-        seed = _default_seed
+        seed = _stream_seed()
     if offset is None:
         offset = _next_offset
         _next_offset += 1
@@ -333,7 +362,8 @@ def relu_bwd_unpack(mask_bits: torch.Tensor, dy: torch.Tensor, channels_last: bo
 
 def activation_fwd_quant_pack(x: torch.Tensor, kind: str, bits: int, group_size: int,
                               seed: Optional[int] = None, offset: Optional[int] = None, flags: int = 0):
-    """y = gelu/silu(x) and the packed derivative: (y, packed, scale, min)."""
+    """y = act(x) and the packed derivative: (y, packed, scale, min).  kind: "gelu" (tanh
+    approximation), "gelu_erf" (exact) or "silu"."""
     global _next_offset
     _, nwords, _ = _bits_consts(bits, group_size)
     _require_cuda(x, "x")
@@ -346,11 +376,11 @@ def activation_fwd_quant_pack(x: torch.Tensor, kind: str, bits: int, group_size:
     scale = torch.empty((ng,), dtype=torch.float32, device=x.device)
     mn = torch.empty((ng,), dtype=torch.float32, device=x.device)
     if seed is None:
-        seed = _default_seed
+        seed = _stream_seed()
     if offset is None:
         offset = _next_offset
         _next_offset += 1
-    k = {"gelu": _lib.ACT_KIND_GELU, "silu": _lib.ACT_KIND_SILU}[kind]
+    k = {"gelu": _lib.ACT_KIND_GELU, "silu": _lib.ACT_KIND_SILU, "gelu_erf": _lib.ACT_KIND_GELU_ERF}[kind]
     with _device_of(x):
         rc = _lib.load().act_activation_fwd_quant_pack(
             x.data_ptr(), _DTYPES[x.dtype], k, ng, group_size, bits, seed & 0xFFFFFFFFFFFFFFFF,
@@ -457,7 +487,7 @@ def bn_fwd_norm_quant_pack(x: torch.Tensor, mean: Optional[torch.Tensor], invstd
     scale = torch.empty((ng,), dtype=torch.float32, device=x.device)
     mn = torch.empty((ng,), dtype=torch.float32, device=x.device)
     if seed is None:
-        seed = _default_seed
+        seed = _stream_seed()
     if offset is None:
         offset = _next_offset
         _next_offset += 1
@@ -593,7 +623,7 @@ def bn_forward(x: torch.Tensor, eps: float, weight: Optional[torch.Tensor], bias
     meta = torch.empty((2, ng), dtype=torch.float32, device=dev)
     mask = torch.empty((x.numel() // 8,), dtype=torch.uint8, device=dev) if relu else None
     if seed is None:
-        seed = _default_seed
+        seed = _stream_seed()
     if offset is None:
         offset = _next_offset
         _next_offset += 1

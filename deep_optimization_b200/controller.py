@@ -24,11 +24,14 @@ from torch.fx.passes.shape_prop import ShapeProp
 
 from .layers import DOConv1d, DOConv2d, DOConv3d, DODepthPointConv2d, DOLinear, RMSNorm
 from .modules.activations.act_layers import DOGELU, DOMaxPool2d, DOReLU_Variance, DOSiLU
-from .modules.normalization.normalization_layers import DOBatchNorm2d, DOSyncBatchNorm2d
+from .modules.normalization.normalization_layers import DOBatchNorm2d, DOLayerNorm, DOSyncBatchNorm2d
 from .quantizer import Quantizer
 
 _SUPPORTED = (nn.Linear, nn.Conv1d, nn.Conv2d, nn.Conv3d, nn.BatchNorm2d, nn.SyncBatchNorm,
               nn.ReLU, nn.ReLU6, nn.SiLU, nn.GELU)
+# not in the reference's swap list (controller.py:87); on unless the config says
+# compress_layernorm=False
+_EXTENSIONS = (nn.LayerNorm,)
 
 
 def assign_tensor_meta(node):
@@ -103,7 +106,9 @@ class Controller:
             if node.op != "call_module":
                 continue
             mod = named[node.target]
-            if not isinstance(mod, _SUPPORTED):
+            if not isinstance(mod, _SUPPORTED) and not (
+                    isinstance(mod, _EXTENSIONS) and self.config.get("compress_layernorm", True)
+                    and not self.config.get("rms_norm", False)):
                 continue
             if compute_activation_size_in_bytes(node) <= threshold:
                 continue
@@ -159,23 +164,28 @@ class Controller:
                 new.bias = None
         elif isinstance(mod, nn.Conv1d):
             new = DOConv1d(mod.in_channels, mod.out_channels, mod.kernel_size, mod.stride, mod.padding,
-                           mod.dilation, mod.groups, mod.padding_mode, clamp_alpha=self.layer_clamp, **kw)
+                           mod.dilation, mod.groups, mod.padding_mode, clamp_alpha=self.layer_clamp,
+                           bias=mod.bias is not None, **kw)
         elif isinstance(mod, nn.Conv2d):
             if self.config.get("depth_point_conv", False):
                 return DODepthPointConv2d(mod.in_channels, mod.out_channels, mod.kernel_size, mod.stride,
                                           mod.padding, mod.dilation, mod.groups, mod.padding_mode,
                                           acc_var=self.layer_clamp, **kw)
             new = DOConv2d(mod.in_channels, mod.out_channels, mod.kernel_size, mod.stride, mod.padding,
-                           mod.dilation, mod.groups, mod.padding_mode, clamp_alpha=self.layer_clamp, **kw)
+                           mod.dilation, mod.groups, mod.padding_mode, clamp_alpha=self.layer_clamp,
+                           bias=mod.bias is not None, **kw)
         elif isinstance(mod, nn.Conv3d):
             new = DOConv3d(mod.in_channels, mod.out_channels, mod.kernel_size, mod.stride, mod.padding,
-                           mod.dilation, mod.groups, mod.padding_mode, clamp_alpha=self.layer_clamp, **kw)
+                           mod.dilation, mod.groups, mod.padding_mode, clamp_alpha=self.layer_clamp,
+                           bias=mod.bias is not None, **kw)
         elif isinstance(mod, nn.SyncBatchNorm):
             new = DOSyncBatchNorm2d(mod.num_features, mod.eps, mod.momentum, mod.affine,
                                     mod.track_running_stats, mod.process_group, **kw)
         elif isinstance(mod, nn.BatchNorm2d):
             new = DOBatchNorm2d(mod.num_features, mod.eps, mod.momentum, mod.affine,
                                 mod.track_running_stats, **kw)
+        elif isinstance(mod, nn.LayerNorm):
+            new = DOLayerNorm(mod.normalized_shape, mod.eps, mod.elementwise_affine, mod.bias is not None, **kw)
         elif isinstance(mod, nn.ReLU6):
             return DOReLU_Variance(inplace=False, relu=False, relu6=True, **kw)
         elif isinstance(mod, nn.ReLU):
@@ -183,7 +193,7 @@ class Controller:
         elif isinstance(mod, nn.SiLU):
             return DOSiLU(inplace=False, **kw)
         elif isinstance(mod, nn.GELU):
-            return DOGELU(inplace=False, **kw)
+            return DOGELU(inplace=False, approximate=mod.approximate, **kw)
         else:
             raise TypeError(type(mod))
         with torch.no_grad():

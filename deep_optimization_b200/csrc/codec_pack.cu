@@ -77,7 +77,7 @@ extern "C" int act_activation_fwd_quant_pack(const void* x, int dtype, int kind,
 {
     using namespace act;
     if (dtype != ACT_DTYPE_F32 && dtype != ACT_DTYPE_BF16 && dtype != ACT_DTYPE_F16) return ACT_ERR_DTYPE;
-    if (kind != ACT_KIND_GELU && kind != ACT_KIND_SILU) return ACT_ERR_UNSUPPORTED;
+    if (kind != ACT_KIND_GELU && kind != ACT_KIND_SILU && kind != ACT_KIND_GELU_ERF) return ACT_ERR_UNSUPPORTED;
     if (flags & ~ACT_FLAG_ROUND_NEAREST) return ACT_ERR_UNSUPPORTED;
     if (bits != 1 && bits != 2 && bits != 4 && bits != 8) return ACT_ERR_BITS;
     if (group_size < 32 || group_size > 1024 || (group_size & (group_size - 1))) return ACT_ERR_GROUP;

@@ -324,7 +324,7 @@ __device__ __forceinline__ void encode_piece_ref(const float* xf8, float mn, flo
 // (what backward multiplies dy with), replacing the reference's fused forward kernels
 // (Activation_Compression/modules/activations/kernel_implementation.py:184-342, 468-559).
 enum Producer { kProNone = 0, kProGelu = 1, kProSilu = 2, kProBN = 3, kProBNRelu = 4, kProBNcl = 5, kProBNReluCl = 6,
-                kProBNAddRelu = 7, kProBNAddReluCl = 8 };
+                kProBNAddRelu = 7, kProBNAddReluCl = 8, kProGeluErf = 9 };
 
 // Per-channel inputs of the batch-norm producer: x is [N, C, HW] contiguous and
 // params[c] = (mean, invstd, weight, bias).  The channel of element e is (e / HW) % C;
@@ -371,6 +371,11 @@ __device__ __forceinline__ void act_and_derivative(float x, float& y, float& d) 
         const float th = tanh_fast(k * (x + c * x2 * x));
         y = 0.5f * x * (1.0f + th);
         d = 0.5f * (1.0f + th) + 0.5f * x * (1.0f - th * th) * k * (1.0f + 3.0f * c * x2);
+    } else if (PRO == kProGeluErf) {
+        // exact GELU: x * Phi(x); derivative Phi(x) + x * phi(x)
+        const float cdf = 0.5f * (1.0f + erff(x * 0.7071067811865476f));
+        y = x * cdf;
+        d = cdf + x * (0.3989422804014327f * __expf(-0.5f * x * x));
     } else if (PRO == kProSilu) {
         const float sig = __fdividef(1.0f, 1.0f + __expf(-x));
         y = x * sig;
@@ -901,6 +906,9 @@ cudaError_t launch_fused_bits(int kind, bool nearest, const void* x, void* y, vo
     if (kind == ACT_KIND_GELU)
         return nearest ? launch_fused_one<DT, BITS, kNoiseConst, kProGelu>(x, y, packed, scale, mn, n, l2, seed, offset, st)
                        : launch_fused_one<DT, BITS, kNoiseHash, kProGelu>(x, y, packed, scale, mn, n, l2, seed, offset, st);
+    if (kind == ACT_KIND_GELU_ERF)
+        return nearest ? launch_fused_one<DT, BITS, kNoiseConst, kProGeluErf>(x, y, packed, scale, mn, n, l2, seed, offset, st)
+                       : launch_fused_one<DT, BITS, kNoiseHash, kProGeluErf>(x, y, packed, scale, mn, n, l2, seed, offset, st);
     return nearest ? launch_fused_one<DT, BITS, kNoiseConst, kProSilu>(x, y, packed, scale, mn, n, l2, seed, offset, st)
                    : launch_fused_one<DT, BITS, kNoiseHash, kProSilu>(x, y, packed, scale, mn, n, l2, seed, offset, st);
 }

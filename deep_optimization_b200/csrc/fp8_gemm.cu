@@ -353,6 +353,9 @@ constexpr int TILE_M = 2 * BM_CTA;              // rows of C per pair
 #ifndef ACT_GEMM_PREFETCH
 #define ACT_GEMM_PREFETCH 0                      // 1: every cluster requests its next A rows into L2; 2: one per row group
 #endif
+#ifndef ACT_GEMM_RASTER
+#define ACT_GEMM_RASTER 0                        // 0: tiles dealt out round-robin; 1: one contiguous run per cluster
+#endif
 #ifndef ACT_GEMM_EPI_TEST
 #define ACT_GEMM_EPI_TEST 0                      // 1, 2: timing experiments with wrong results, never shipped
 #endif
@@ -493,7 +496,19 @@ fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     const int m_tiles = (M + TILE_M - 1) / TILE_M, n_tiles = (N + BN - 1) / BN;
     const int n_work = m_tiles * n_tiles;
     const int k_blocks = (K + BK - 1) / BK;
+#if ACT_GEMM_RASTER == 1
+    // Each cluster takes one contiguous run of tiles (row-major over the tile grid): consecutive
+    // tiles of a cluster then share their rows of A, which come out of L2 after the first of them,
+    // and a row block of C is written by one cluster over a short time.
+    const int n_cl = (int)n_clusters(), cid = (int)cluster_id();
+    const int per = n_work / n_cl, extra = n_work % n_cl;
+    const int first = cid * per + (cid < extra ? cid : extra);
+    const int w_end = first + per + (cid < extra ? 1 : 0);
+    constexpr int stride = 1;
+#else
     const int first = (int)cluster_id(), stride = (int)n_clusters();
+    const int w_end = n_work;
+#endif
     const uint32_t peer_abort = map_to_cta(smem_u32((const void*)&s->abort), rank ^ 1u);
 
     if (smem_u32(s) & 1023u) {                                // the swizzled tiles need this alignment
@@ -517,7 +532,7 @@ fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
             bool ok = true;
-            for (int w = first; ok && w < n_work; w += stride) {
+            for (int w = first; ok && w < w_end; w += stride) {
                 const int m0 = (w / n_tiles) * TILE_M + (int)rank * BM_CTA;
                 const int n0 = (w % n_tiles) * BN + (int)rank * BM_CTA;
 #if ACT_GEMM_PREFETCH
@@ -526,7 +541,7 @@ fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                 // rows of this cluster's NEXT tile are therefore requested into L2 one tile ahead, by
                 // one cluster per group of clusters that will share them.
                 const int w_next = w + stride;
-                const bool prefetch = w_next < n_work &&
+                const bool prefetch = w_next < w_end &&
                                       (ACT_GEMM_PREFETCH == 1 || (w_next % n_tiles) == 0 || first == 0);
                 const int m0_next = (w_next / n_tiles) * TILE_M + (int)rank * BM_CTA;
 #endif
@@ -557,7 +572,7 @@ fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
             uint32_t stage = 0, phase = 0, acc_phase[2] = {0, 0};
             bool ok = true;
             int t = 0;
-            for (int w = first; ok && w < n_work; w += stride, ++t) {
+            for (int w = first; ok && w < w_end; w += stride, ++t) {
                 const int buf = t & 1;
                 TRACE(t, 0, clock64());
                 if (!(ok = wait_bar(&s->acc_empty[buf], acc_phase[buf] ^ 1, s, 2, peer_abort))) break;
@@ -593,7 +608,7 @@ fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         uint32_t groups = 0, last_group[EPI_BUFS] = {};        // lane 0: store groups committed, and which one last read a buffer
         bool ok = true;
         int t = 0;
-        for (int w = first; w < n_work; w += stride, ++t) {
+        for (int w = first; w < w_end; w += stride, ++t) {
             const int buf = t & 1;
             const int m0 = (w / n_tiles) * TILE_M + (int)rank * BM_CTA, n0 = (w % n_tiles) * BN;
             s->sb[buf][etid] = (n0 + etid < N) ? __ldg(sb + n0 + etid) : 0.0f;

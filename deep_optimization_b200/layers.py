@@ -4,7 +4,9 @@ Constructor signatures match the reference (including its `out_channesl` and
 `in_chanels` spellings being positional).  In eval mode they are the stock
 modules; in training they call the save-for-backward Functions.  Conv1d/3d use
 `clamp_alpha` for the PACT clamp (the reference reads an undefined `pact_alpha`
-and forgets `.apply`).
+and forgets `.apply`).  The conv modules take a trailing `bias` keyword (default
+False, the reference's fixed choice) so that a biased convolution can be swapped
+without losing its bias.
 """
 from __future__ import annotations
 
@@ -48,16 +50,17 @@ class _DOConvMixin:
             x = F.pad(x, self._reversed_padding_repeated_twice, mode=self.padding_mode)
             padding = 0
         return self._fn.apply(x, self.weight, self.learnable_scale, self.stride, padding, self.dilation,
-                              self.groups, self.clamp_alpha, self.target_name, self.meta, self.ema_grad_meta)
+                              self.groups, self.clamp_alpha, self.target_name, self.meta, self.ema_grad_meta,
+                              self.bias)
 
 
 class DOConv1d(_DOConvMixin, nn.Conv1d):
     _fn, _pact = _DOConv1d, True
 
     def __init__(self, in_channels, out_channels, kernel_size, stride=1, padding=0, dilation=1, groups=1,
-                 padding_mode="zeros", clamp_alpha=3.0, target_name=None, meta={}):
+                 padding_mode="zeros", clamp_alpha=3.0, target_name=None, meta={}, bias=False):
         nn.Conv1d.__init__(self, in_channels, out_channels, kernel_size, stride, padding, dilation, groups,
-                           bias=False, padding_mode=padding_mode)
+                           bias=bias, padding_mode=padding_mode)
         self._init_do(clamp_alpha, target_name, meta)
 
 
@@ -65,9 +68,9 @@ class DOConv2d(_DOConvMixin, nn.Conv2d):
     _fn = _DOConv2d
 
     def __init__(self, in_channels, out_channesl, kernel_size, stride=1, padding=0, dilation=1, groups=1,
-                 padding_mode="zeros", clamp_alpha=3.0, target_name=None, meta={}):
+                 padding_mode="zeros", clamp_alpha=3.0, target_name=None, meta={}, bias=False):
         nn.Conv2d.__init__(self, in_channels, out_channesl, kernel_size, stride, padding, dilation, groups,
-                           bias=False, padding_mode=padding_mode)
+                           bias=bias, padding_mode=padding_mode)
         self._init_do(clamp_alpha, target_name, meta)
 
 
@@ -75,9 +78,9 @@ class DOConv3d(_DOConvMixin, nn.Conv3d):
     _fn, _pact = _DOConv3d, True
 
     def __init__(self, in_chanels, out_channels, kernel_size, stride=1, padding=0, dilation=1, groups=1,
-                 padding_mode="zeros", clamp_alpha=3.0, target_name=None, meta={}):
+                 padding_mode="zeros", clamp_alpha=3.0, target_name=None, meta={}, bias=False):
         nn.Conv3d.__init__(self, in_chanels, out_channels, kernel_size, stride, padding, dilation, groups,
-                           bias=False, padding_mode=padding_mode)
+                           bias=bias, padding_mode=padding_mode)
         self._init_do(clamp_alpha, target_name, meta)
 
 

@@ -33,13 +33,17 @@ class DOSiLU(nn.SiLU):
 
 
 class DOGELU(nn.GELU):
-    def __init__(self, inplace=False, target_name=None, meta={}):
-        super().__init__(approximate="tanh")
+    """`approximate` ("tanh", the reference's only form and the default here, or "none") is an
+    addition to the reference's constructor: the Controller passes the replaced module's own
+    setting, so swapping an nn.GELU() does not change the function the model computes."""
+
+    def __init__(self, inplace=False, target_name=None, meta={}, approximate="tanh"):
+        super().__init__(approximate=approximate)
         self.target_name, self.meta = target_name, meta
 
     def forward(self, x):
         if self.training:
-            return _DOGELU.apply(x, self.target_name, self.meta)
+            return _DOGELU.apply(x, self.target_name, self.meta, self.approximate == "none")
         return super().forward(x)
 
 

@@ -71,8 +71,9 @@ def _fused_ok(input, m):
 
 def _fused_forward(ctx, input, kind, m):
     """activation + derivative codec in one kernel (flat grouping)."""
-    if kind == "gelu":
-        y, packed, scale, mn, N, G = act_kernels.op("gelu_fwd_fused_quan_pack")(input, m["bits"], m["group_size"])
+    if kind in ("gelu", "gelu_erf"):
+        y, packed, scale, mn, N, G = act_kernels.op("gelu_fwd_fused_quan_pack")(input, m["bits"], m["group_size"],
+                                                                                kind == "gelu_erf")
     else:
         y, packed, scale, mn, N, G = act_kernels.op("silu_fwd_quan_pack")(input, m["bits"], m["group_size"],
                                                                           False, False, 0)[:6]
@@ -110,28 +111,34 @@ class _DOSiLU(Function):
 
 
 class _DOGELU(Function):
-    """tanh-approximated GELU, as the reference's kernel
-    (Activation_Compression/modules/activations/kernel_implementation.py:433-465)."""
+    """GELU: the tanh approximation of the reference's kernel
+    (Activation_Compression/modules/activations/kernel_implementation.py:433-465) or, with
+    `exact`, x * Phi(x), so that a module built from nn.GELU() keeps its function."""
 
     @staticmethod
     @custom_fwd(device_type="cuda")
-    def forward(ctx, input, target_name, meta):
+    def forward(ctx, input, target_name, meta, exact=False):
         ctx.fused_meta = None
         if _fused_ok(input, meta[f"{target_name}"]):
-            return _fused_forward(ctx, input, "gelu", meta[f"{target_name}"])
+            return _fused_forward(ctx, input, "gelu_erf" if exact else "gelu", meta[f"{target_name}"])
         x = input.float()
-        k = math.sqrt(2.0 / math.pi)
-        inner = k * (x + 0.044715 * x * x * x)
-        th = torch.tanh(inner)
-        y = (0.5 * x * (1.0 + th)).to(input.dtype)
-        deriv = 0.5 * (1.0 + th) + 0.5 * x * (1.0 - th * th) * k * (1.0 + 3 * 0.044715 * x * x)
+        if exact:
+            cdf = 0.5 * (1.0 + torch.erf(x * math.sqrt(0.5)))
+            y = (x * cdf).to(input.dtype)
+            deriv = cdf + x * torch.exp(-0.5 * x * x) * (1.0 / math.sqrt(2.0 * math.pi))
+        else:
+            k = math.sqrt(2.0 / math.pi)
+            inner = k * (x + 0.044715 * x * x * x)
+            th = torch.tanh(inner)
+            y = (0.5 * x * (1.0 + th)).to(input.dtype)
+            deriv = 0.5 * (1.0 + th) + 0.5 * x * (1.0 - th * th) * k * (1.0 + 3 * 0.044715 * x * x)
         _save_derivative(ctx, deriv, target_name, meta)
         return y
 
     @staticmethod
     @custom_bwd(device_type="cuda")
     def backward(ctx, dy):
-        return _apply_derivative(ctx, dy), None, None
+        return _apply_derivative(ctx, dy), None, None, None
 
 
 class _DOMaxPool2d(Function):

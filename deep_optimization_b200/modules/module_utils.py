@@ -99,17 +99,23 @@ def dequantize(quantized_tensor, quantized_meta):
                                                   act_padding, pad_elig, reshape_elig, channel_mean)
 
 
-def unified_dequantize(ori_quantized_tensor, ori_quantized_meta, input_l):
-    input_shape = ori_quantized_meta[-1]
-    x = dequantize(ori_quantized_tensor, ori_quantized_meta)
-    if input_l is None:
-        return x
-    # DIVISION: add back the nearest-upsampled low-pass part (module_utils.py:91-102)
+def low_pass_upsampled(input_l, input_shape):
+    """The stored low-pass part of a DIVISION layer, nearest-upsampled to the layer input's
+    shape (module_utils.py:91-102).  Forward subtracts exactly this tensor before the codec
+    and backward adds it back, so the pair cancels whatever the e4m3 storage lost."""
     if len(input_shape) == 4:
         size = (input_shape[-2], input_shape[-1])
     elif len(input_shape) == 3:
         size = input_shape[2]
     else:
         size = input_shape[0]
-    low = F.interpolate(input_l.to(torch.bfloat16), size=size, mode="nearest")
-    return x + low.to(torch.bfloat16)
+    return F.interpolate(input_l.to(torch.bfloat16), size=size, mode="nearest")
+
+
+def unified_dequantize(ori_quantized_tensor, ori_quantized_meta, input_l):
+    input_shape = ori_quantized_meta[-1]
+    x = dequantize(ori_quantized_tensor, ori_quantized_meta)
+    if input_l is None:
+        return x
+    # DIVISION: residual + low-pass part
+    return x + low_pass_upsampled(input_l, input_shape).to(x.dtype)

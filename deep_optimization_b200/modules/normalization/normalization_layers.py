@@ -3,7 +3,7 @@
 import torch.distributed as dist
 from torch import nn
 
-from .normalization_ops import _DOBatchNorm, _DOSyncBatchNorm
+from .normalization_ops import _DOBatchNorm, _DOLayerNorm, _DOSyncBatchNorm
 
 
 def _ema_factor(mod):
@@ -60,3 +60,18 @@ class DOSyncBatchNorm2d(nn.SyncBatchNorm):
         return _DOSyncBatchNorm.apply(x, self.weight, self.bias, self.running_mean, self.running_var,
                                       self.eps, factor, group, world_size, self.target_name, self.meta,
                                       self.ema_grad_meta)
+
+
+class DOLayerNorm(nn.LayerNorm):
+    """nn.LayerNorm whose input is saved compressed in training (an extension: the reference
+    leaves LayerNorm alone).  Eval mode is the stock module."""
+
+    def __init__(self, normalized_shape, eps=1e-5, elementwise_affine=True, bias=True, target_name=None, meta={}):
+        super().__init__(normalized_shape, eps, elementwise_affine, bias)
+        self.target_name, self.meta = target_name, meta
+
+    def forward(self, x):
+        if not self.training:
+            return super().forward(x)
+        return _DOLayerNorm.apply(x, self.normalized_shape, self.weight, self.bias, self.eps,
+                                  self.target_name, self.meta)

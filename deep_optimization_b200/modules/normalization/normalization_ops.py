@@ -190,3 +190,40 @@ class _DOSyncBatchNorm:
               world_size, target_name, meta, ema_grad_meta):
         return _DOBatchNorm.apply(input, weight, bias, running_mean, running_var, momentum, eps,
                                   target_name, meta, ema_grad_meta, process_group, world_size)
+
+
+class _DOLayerNorm(Function):
+    """LayerNorm that keeps its input compressed.  The reference's swap list has no LayerNorm
+    (Activation_Compression/controller.py:87); the evaluation configuration for ViT-B/16 names
+    LayerNorm inputs among the compressed activations, so the input goes through the same
+    `unified_quantize` boundary as a Linear input.  Forward is PyTorch's native kernel (which
+    also returns the per-row mean and inverse deviation, kept in fp32: 8 bytes per row); backward
+    decodes the input and calls the native backward with those statistics."""
+
+    @staticmethod
+    @custom_fwd(device_type="cuda")
+    def forward(ctx, input, normalized_shape, weight, bias, eps, target_name, meta):
+        w = None if weight is None else weight.to(input.dtype)
+        b = None if bias is None else bias.to(input.dtype)
+        y, mean, rstd = torch.ops.aten.native_layer_norm(input, list(normalized_shape), w, b, eps)
+        q_tensors, q_meta, _ = unified_quantize(input, None, target_name, meta, clamp=False, clamp_alpha=0.0)
+        ctx.q_meta = q_meta
+        ctx.normalized_shape = list(normalized_shape)
+        ctx.param_dtypes = (None if weight is None else weight.dtype, None if bias is None else bias.dtype)
+        ctx.save_for_backward(q_tensors[0], q_tensors[1], q_tensors[2], mean, rstd, weight, bias)
+        return y
+
+    @staticmethod
+    @custom_bwd(device_type="cuda")
+    def backward(ctx, dy):
+        packed, scale, mn, mean, rstd, weight, bias = ctx.saved_tensors
+        x = unified_dequantize((packed, scale, mn), ctx.q_meta, None).to(dy.dtype)
+        w = None if weight is None else weight.to(dy.dtype)
+        b = None if bias is None else bias.to(dy.dtype)
+        mask = [bool(ctx.needs_input_grad[0]), weight is not None and bool(ctx.needs_input_grad[2]),
+                bias is not None and bool(ctx.needs_input_grad[3])]
+        dx, dw, db = torch.ops.aten.native_layer_norm_backward(dy.contiguous(), x.contiguous(), ctx.normalized_shape,
+                                                               mean, rstd, w, b, mask)
+        wd, bd = ctx.param_dtypes
+        return (dx if mask[0] else None, None, dw.to(wd) if mask[1] else None, db.to(bd) if mask[2] else None,
+                None, None, None)

@@ -17,13 +17,17 @@ from torch.amp import custom_bwd, custom_fwd
 from torch.autograd import Function
 from torch.nn.modules.utils import _pair, _single, _triple
 
-from .module_utils import unified_dequantize, unified_quantize
+from .module_utils import low_pass_upsampled, unified_dequantize, unified_quantize
 
 
 class _DOConvnd(Function):
     @staticmethod
     def run_forward(ctx, forward_op, input, weight, learnable_scale, stride=1, padding=0, dilation=1,
-                    groups=1, clamp_alpha=3.0, target_name=None, meta=None, ema_grad_meta=None):
+                    groups=1, clamp_alpha=3.0, target_name=None, meta=None, ema_grad_meta=None, bias=None):
+        # `bias` is an addition to the reference's argument list (its conv Functions call the
+        # forward op with bias=None, Activation_Compression/modules/ops.py:271-272, so a biased
+        # convolution silently loses its bias when swapped): it rides in the convolution itself
+        # and its gradient is the sum of dy over everything but the channel axis
         weight_master = weight
         if torch.is_autocast_enabled("cuda"):
             dt = torch.get_autocast_dtype("cuda")
@@ -33,20 +37,28 @@ class _DOConvnd(Function):
             weight_compute = weight_master
         m = meta[f"{target_name}"]
 
-        # DIVISION: keep a low-pass copy (average pool) beside the compressed input
+        # DIVISION: the input is split into a low-pass part (average pool, kept in e4m3) and the
+        # residual above it, and only the residual goes through the codec: its range, hence its
+        # quantisation step, is smaller.  Backward adds the two back together.  (The reference
+        # quantises the whole input and still adds the low-pass part back, modules/ops.py:253-256
+        # with the subtraction commented out, which doubles the low frequencies in dW.)
         input_l = None
-        if m["DIVISION"] is not None and not m["pack_only"]:
+        to_save = input.to(torch.bfloat16)
+        if m["DIVISION"] is not None and not m["pack_only"] and input.dim() == 4:
             k = min(input.shape[-2], input.shape[-1], m["DIVISION"]["pool_kernel_size"])
-            input_l = F.avg_pool2d(input.to(torch.bfloat16), k, stride=k, padding=0).to(torch.float8_e4m3fn)
+            input_l = F.avg_pool2d(to_save, k, stride=k, padding=0).to(torch.float8_e4m3fn)
+            to_save = to_save - low_pass_upsampled(input_l, input.shape)
 
-        q_tensors, q_meta, input_l = unified_quantize(input.to(torch.bfloat16), input_l, target_name, meta,
+        q_tensors, q_meta, input_l = unified_quantize(to_save, input_l, target_name, meta,
                                                       clamp=True, clamp_alpha=clamp_alpha)
         ctx.meta = stride, padding, dilation, groups, ema_grad_meta, clamp_alpha
         # the weight in its compute type is what backward multiplies with: kept, not re-cast
         ctx.weight_compute = weight_compute if weight_compute is not weight_master else None
+        ctx.bias_meta = None if bias is None else (bias.dtype, bias.shape[0])
         ctx.save_for_backward(weight_master, q_tensors[0], q_tensors[1], q_tensors[2], input_l, learnable_scale)
         ctx.q_inputs_meta = q_meta
-        return forward_op(input, weight_compute, bias=None, stride=stride, padding=padding,
+        bias_compute = None if bias is None else bias.to(weight_compute.dtype)
+        return forward_op(input, weight_compute, bias=bias_compute, stride=stride, padding=padding,
                           dilation=dilation, groups=groups)
 
     @staticmethod
@@ -71,18 +83,17 @@ class _DOConvnd(Function):
         # from them (the torch.nn.grad helpers hand it a strideless placeholder, which turns a
         # channels-last gradient back into NCHW with a copy)
         need_dx, need_dw = bool(ctx.needs_input_grad[0]), bool(ctx.needs_input_grad[1])
-        dx = dw = None
-        if need_dx or need_dw:
-            dx, dw, _ = torch.ops.aten.convolution_backward(
-                dy, x, weight_compute, None, list(stride), list(padding), list(dilation), False,
-                [0] * dim, groups, [need_dx, need_dw, False])
-            if need_dw:
-                dw = dw.to(weight_master.dtype)
-            else:
-                dw = None
+        need_db = ctx.bias_meta is not None and bool(ctx.needs_input_grad[11])
+        dx = dw = db = None
+        if need_dx or need_dw or need_db:
+            dx, dw, db = torch.ops.aten.convolution_backward(
+                dy, x, weight_compute, [ctx.bias_meta[1]] if need_db else None, list(stride), list(padding),
+                list(dilation), False, [0] * dim, groups, [need_dx, need_dw, need_db])
+            dw = dw.to(weight_master.dtype) if need_dw else None
+            db = db.to(ctx.bias_meta[0]) if need_db else None
             if not need_dx:
                 dx = None
-        return dx, dw, None, None, None, None, None, None, None, None, None
+        return dx, dw, None, None, None, None, None, None, None, None, None, db
 
 
 def _make_conv(dim, fwd_op, pad_fn):
@@ -90,11 +101,11 @@ def _make_conv(dim, fwd_op, pad_fn):
         @staticmethod
         @custom_fwd(device_type="cuda")
         def forward(ctx, input, weight, learnable_scale, stride=1, padding=0, dilation=1, groups=1,
-                    clamp_alpha=3.0, target_name=None, meta=None, ema_grad_meta=None):
+                    clamp_alpha=3.0, target_name=None, meta=None, ema_grad_meta=None, bias=None):
             return _DOConvnd.run_forward(ctx, fwd_op, input, weight, learnable_scale, stride=stride,
                                          padding=padding, dilation=dilation, groups=groups,
                                          clamp_alpha=clamp_alpha, target_name=target_name, meta=meta,
-                                         ema_grad_meta=ema_grad_meta)
+                                         ema_grad_meta=ema_grad_meta, bias=bias)
 
         @staticmethod
         @custom_bwd(device_type="cuda")
@@ -127,12 +138,15 @@ class _DOLinear(Function):
         bias_compute = None if bias is None else bias.to(weight_compute.dtype)
         m = meta[f"{target_name}"]
 
+        # DIVISION as in the conv Functions: low-pass part beside the compressed residual
         input_l = None
-        if m["DIVISION"] is not None and input.ndim > 2 and not m["pack_only"]:
+        to_save = input
+        if m["DIVISION"] is not None and input.ndim == 3 and not m["pack_only"]:
             k = min(input.shape[2], m["DIVISION"]["pool_kernel_size"])
             input_l = F.avg_pool1d(input.to(torch.bfloat16), k, stride=k, padding=0)
+            to_save = (input.to(torch.bfloat16) - low_pass_upsampled(input_l, input.shape)).to(input.dtype)
 
-        q_tensors, q_meta, input_l = unified_quantize(input, input_l, target_name, meta, clamp=True,
+        q_tensors, q_meta, input_l = unified_quantize(to_save, input_l, target_name, meta, clamp=True,
                                                       clamp_alpha=clamp_alpha)
         ctx.target_name = target_name
         ctx.q_inputs_meta = q_meta

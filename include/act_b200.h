@@ -43,6 +43,7 @@ extern "C" {
 /* activation kinds of act_activation_fwd_quant_pack */
 #define ACT_KIND_GELU 1            /* tanh-approximated GELU */
 #define ACT_KIND_SILU 2
+#define ACT_KIND_GELU_ERF 3        /* exact GELU, x * Phi(x) */
 
 /* flags of act_fp8_gemm */
 #define ACT_GEMM_B_IS_NK 1         /* B is stored [N,K] (K contiguous, like nn.Linear weights)        */

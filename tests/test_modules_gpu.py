@@ -1,0 +1,246 @@
+"""GPU tests of the modules and options the layer tests do not reach: DOConv1d / DOConv3d (with
+their PACT clamp), DODepthPointConv2d, a biased convolution, the exact-GELU module, DOLayerNorm,
+the DIVISION split, the reference-compatible codec mode through a layer, DOSyncBatchNorm2d on one
+rank, and whole models: every parameter gradient of a Controller-wrapped ResNet-50 and ViT-B/16 at
+8 bits against the stock model's."""
+import pytest
+import torch
+from torch import nn
+
+pytestmark = pytest.mark.gpu
+
+
+def _meta(target, bits, gs, N, pack_only=False, pad=False, division=None):
+    return {target: {"bits": bits, "pack_only": pack_only, "group_size": gs, "act_padding": pad, "N": N,
+                     "AVG_ALAM": False, "ALAM_BITS": 0, "DIVISION": division}}
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-12)).item()
+
+
+@pytest.mark.parametrize("dim", (1, 3))
+def test_conv1d_conv3d_with_pact_clamp(cuda_device, dim):
+    from deep_optimization_b200.layers import DOConv1d, DOConv3d
+    torch.manual_seed(dim)
+    alpha = 1.5
+    if dim == 1:
+        conv = DOConv1d(16, 24, 3, padding=1, clamp_alpha=alpha, target_name="c", meta=_meta("c", 8, 256, 4))
+        ref = nn.Conv1d(16, 24, 3, padding=1, bias=False)
+        x = torch.randn(4, 16, 128, device=cuda_device)
+    else:
+        conv = DOConv3d(8, 12, 3, padding=1, clamp_alpha=alpha, target_name="c", meta=_meta("c", 8, 256, 4))
+        ref = nn.Conv3d(8, 12, 3, padding=1, bias=False)
+        x = torch.randn(4, 8, 8, 8, 8, device=cuda_device)
+    conv, ref = conv.to(cuda_device).train(), ref.to(cuda_device)
+    ref.weight.data.copy_(conv.weight.data)
+    x.requires_grad_()
+    xr = x.detach().clone().requires_grad_()
+    y = conv(x)
+    yr = ref(xr.clamp(-alpha, alpha))                 # the module clamps its input first (PACT)
+    assert torch.allclose(y.float(), yr, atol=2e-2, rtol=2e-2)     # the clamp hands on bf16
+    g = torch.randn_like(yr)
+    y.backward(g.to(y.dtype)); yr.backward(g)
+    # dx: exact mask of the clamp (1 bit per element) times the convolution's dx
+    assert _rel(x.grad, xr.grad) < 0.02
+    assert ((x.grad == 0) == (xr.grad == 0)).float().mean() > 0.999
+    assert _rel(conv.weight.grad, ref.weight.grad) < 0.03
+
+
+def test_depth_point_conv(cuda_device):
+    from deep_optimization_b200.layers import DODepthPointConv2d
+    torch.manual_seed(0)
+    mod = DODepthPointConv2d(16, 32, 3, padding=1, target_name="d", meta=_meta("d", 8, 256, 4)).to(cuda_device).train()
+    x = torch.randn(4, 16, 16, 16, device=cuda_device, requires_grad=True)
+    xr = x.detach().clone().requires_grad_()
+    y = mod(x)
+    yr = nn.functional.conv2d(nn.functional.conv2d(xr, mod.depth_quanconv2d.weight.detach(), padding=1, groups=16),
+                              mod.point_quanconv2d.weight.detach())
+    assert torch.allclose(y, yr, atol=1e-4)
+    g = torch.randn_like(y)
+    y.backward(g); yr.backward(g)
+    assert _rel(x.grad, xr.grad) < 1e-3
+    assert mod.depth_quanconv2d.weight.grad is not None and mod.point_quanconv2d.weight.grad is not None
+
+
+def test_biased_conv_keeps_its_bias(cuda_device):
+    """A convolution with a bias, swapped by the Controller, computes the same function and gets
+    the same bias gradient (the reference's conv Functions drop the bias)."""
+    from deep_optimization_b200.controller import Controller
+    from deep_optimization_b200.layers import DOConv2d
+    torch.manual_seed(0)
+    model = nn.Sequential(nn.Conv2d(8, 16, 3, padding=1, bias=True), nn.GELU(), nn.Conv2d(16, 8, 1, bias=True))
+    stock = nn.Sequential(nn.Conv2d(8, 16, 3, padding=1, bias=True), nn.GELU(), nn.Conv2d(16, 8, 1, bias=True)).to(cuda_device)
+    stock.load_state_dict(model.state_dict())
+    cfg = dict(default_bits=8, auto_precision=None, batch_size=16, min_activation_mib=0.01)
+    net = Controller(model, cfg, input_shape=(8, 32, 32), test=False, device=cuda_device).traced_model
+    convs = [m for m in net.modules() if isinstance(m, DOConv2d)]
+    assert len(convs) == 2 and all(c.bias is not None for c in convs)
+    gelu = [m for m in net.modules() if type(m).__name__ == "DOGELU"]
+    assert len(gelu) == 1 and gelu[0].approximate == "none"          # erf GELU stays erf GELU
+    x = torch.randn(16, 8, 32, 32, device=cuda_device)
+    y, yr = net(x), stock(x)
+    assert torch.allclose(y, yr, atol=1e-4)
+    g = torch.randn_like(y)
+    y.backward(g); yr.backward(g)
+    for (n1, p1), (n2, p2) in zip(sorted(net.named_parameters()), sorted(stock.named_parameters())):
+        assert p1.grad is not None, n1
+        assert _rel(p1.grad, p2.grad) < (1e-4 if n1.endswith("bias") and n1.startswith("2") else 0.03), n1
+    net.eval()
+    assert torch.allclose(net(x), stock(x), atol=1e-5)
+
+
+def test_exact_gelu_module(cuda_device):
+    from deep_optimization_b200.modules.activations.act_layers import DOGELU
+    torch.manual_seed(0)
+    for n_elem_shape in ((8, 4, 16, 16), (3, 5, 7)):                  # fused kernel path / unfused fallback
+        numel = 1
+        for d in n_elem_shape:
+            numel *= d
+        meta = _meta("g", 8, 256, n_elem_shape[0], pad=(numel % 256 != 0))
+        mod = DOGELU(target_name="g", meta=meta, approximate="none").to(cuda_device).train()
+        x = (torch.randn(n_elem_shape, device=cuda_device) * 2).requires_grad_()
+        xr = x.detach().double().requires_grad_()
+        y, yr = mod(x), nn.functional.gelu(xr)
+        assert torch.allclose(y.double(), yr, atol=2e-6)
+        g = torch.randn_like(y)
+        y.backward(g); yr.backward(g.double())
+        assert (x.grad.double() - xr.grad).abs().max() < 0.01 * g.abs().max()     # 8-bit derivative
+        mod.eval()
+        assert torch.allclose(mod(x), nn.functional.gelu(x))
+
+
+def test_layer_norm_module(cuda_device):
+    from deep_optimization_b200.modules.normalization.normalization_layers import DOLayerNorm
+    torch.manual_seed(0)
+    ln = DOLayerNorm(256, target_name="n", meta=_meta("n", 8, 256, 8)).to(cuda_device).train()
+    ref = nn.LayerNorm(256).to(cuda_device)
+    with torch.no_grad():
+        ln.weight.uniform_(0.5, 1.5); ln.bias.uniform_(-0.5, 0.5)
+    ref.load_state_dict(ln.state_dict())
+    x = torch.randn(8, 50, 256, device=cuda_device, requires_grad=True)
+    xr = x.detach().clone().requires_grad_()
+    y, yr = ln(x), ref(xr)
+    assert torch.allclose(y, yr, atol=1e-5)
+    g = torch.randn_like(y)
+    y.backward(g); yr.backward(g)
+    assert _rel(x.grad, xr.grad) < 0.02 and _rel(ln.weight.grad, ref.weight.grad) < 0.02
+    assert torch.allclose(ln.bias.grad, ref.bias.grad, atol=1e-4)
+    # the saved state is the packed input plus 8 bytes per row
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        yb = ln(x.detach().to(torch.bfloat16).requires_grad_())
+    assert yb.dtype == torch.bfloat16
+    ln.eval()
+    assert torch.allclose(ln(x), ref(x), atol=1e-6)
+
+
+def test_division_split(cuda_device):
+    """DIVISION: low-pass part + compressed residual reconstruct the input, so the weight
+    gradients stay those of the stock layer (within the quantisation error), for the conv and
+    the linear Function, and the residual's quantisation step is smaller than the input's."""
+    from deep_optimization_b200.layers import DOConv2d, DOLinear
+    torch.manual_seed(0)
+    div = {"pool_kernel_size": 4}
+    # smooth input + small detail: the case the split is for
+    base = torch.randn(4, 8, 8, 8, device=cuda_device)
+    x = nn.functional.interpolate(base, scale_factor=4, mode="nearest") * 3 + 0.1 * torch.randn(4, 8, 32, 32, device=cuda_device)
+    errs = {}
+    for name, d in (("plain", None), ("division", div)):
+        conv = DOConv2d(8, 16, 3, padding=1, target_name="c", meta=_meta("c", 4, 256, 4, division=d)).to(cuda_device).train()
+        torch.manual_seed(1)
+        with torch.no_grad():
+            conv.weight.normal_(0, 0.1)
+        ref = nn.Conv2d(8, 16, 3, padding=1, bias=False).to(cuda_device)
+        ref.weight.data.copy_(conv.weight.data)
+        y, yr = conv(x), ref(x)
+        g = torch.randn_like(y)
+        y.backward(g); yr.backward(g)
+        errs[name] = _rel(conv.weight.grad, ref.weight.grad)
+    assert errs["division"] < 0.05 and errs["division"] < errs["plain"]
+    lin = DOLinear(256, 32, target_name="l", meta=_meta("l", 4, 256, 4, division=div)).to(cuda_device).train()
+    ref = nn.Linear(256, 32).to(cuda_device); ref.load_state_dict(lin.state_dict())
+    xl = torch.randn(4, 10, 64, device=cuda_device).repeat_interleave(4, dim=2) * 3 + 0.1 * torch.randn(4, 10, 256, device=cuda_device)
+    y, yr = lin(xl), ref(xl)
+    g = torch.randn_like(y)
+    y.backward(g); yr.backward(g)
+    assert _rel(lin.weight.grad, ref.weight.grad) < 0.05
+
+
+def test_ref_compat_mode_through_a_layer(cuda_device):
+    """set_mode("ref_compat"): the layer's saved tensors are those of the reference's live
+    arithmetic (bf16-rounded scale and minimum of the tanh-squashed input)."""
+    from deep_optimization_b200 import act_kernels
+    from deep_optimization_b200.layers import DOLinear
+    torch.manual_seed(0)
+    lin = DOLinear(256, 32, target_name="l", meta=_meta("l", 8, 256, 8)).to(cuda_device).train()
+    x = torch.randn(8, 20, 256, device=cuda_device) * 0.2
+    act_kernels.set_mode("ref_compat")
+    try:
+        y = lin(x)
+        saved = y.grad_fn.saved_tensors
+        scale, mn = saved[2], saved[3]
+        assert torch.equal(scale.to(torch.bfloat16).float(), scale) and torch.equal(mn.to(torch.bfloat16).float(), mn)
+        squashed = torch.tanh(x.clamp(-3, 3) / 0.5) * 0.5
+        assert torch.allclose(mn.view(-1), squashed.view(-1, 256).amin(1).to(torch.bfloat16).float(), atol=1e-2)
+        y.sum().backward()
+        assert torch.isfinite(lin.weight.grad).all()
+    finally:
+        act_kernels.set_mode("baseline")
+
+
+def test_sync_batch_norm_single_rank(cuda_device):
+    from deep_optimization_b200.modules.normalization.normalization_layers import DOSyncBatchNorm2d
+    torch.manual_seed(0)
+    bn = DOSyncBatchNorm2d(8, target_name="b", meta=_meta("b", 8, 256, 8)).to(cuda_device).train()
+    ref = nn.BatchNorm2d(8).to(cuda_device).train()
+    x = (torch.randn(8, 8, 16, 16, device=cuda_device) * 2 + 1).requires_grad_()
+    xr = x.detach().clone().requires_grad_()
+    y, yr = bn(x), ref(xr)
+    assert torch.allclose(y, yr, atol=1e-4)
+    assert torch.allclose(bn.running_mean, ref.running_mean, atol=1e-5)
+    assert torch.allclose(bn.running_var, ref.running_var, atol=1e-4)
+    g = torch.randn_like(y)
+    y.backward(g); yr.backward(g)
+    assert _rel(x.grad, xr.grad) < 0.03 and _rel(bn.weight.grad, ref.weight.grad) < 0.03
+    assert torch.allclose(bn.bias.grad, ref.bias.grad, atol=1e-3)
+    bn.eval()
+    assert torch.allclose(bn(x), ref.eval()(x), atol=1e-5)
+
+
+@pytest.mark.parametrize("name", ("resnet50", "vit_b16"))
+@pytest.mark.parametrize("channels_last", (False, True))
+def test_whole_model_gradients_at_8_bits(cuda_device, name, channels_last):
+    """One step of the Controller-wrapped model at 8 bits against the stock model: same loss and
+    every parameter gradient within 5 % relative L2 (fp32, no autocast, batch 8)."""
+    import copy
+    from deep_optimization_b200 import codec
+    from deep_optimization_b200.controller import Controller
+    from deep_optimization_b200.payload import resnet50, vit_b16
+    if name == "vit_b16" and channels_last:
+        pytest.skip("channels-last is a convolutional layout")
+    torch.manual_seed(0)
+    model = (resnet50() if name == "resnet50" else vit_b16()).to(cuda_device)
+    stock = copy.deepcopy(model).train()
+    cfg = dict(default_bits=8, auto_precision=None, batch_size=8, min_activation_mib=0.05)
+    net = Controller(model, cfg, input_shape=(3, 224, 224), test=False, device=cuda_device).traced_model
+    x = torch.randn(8, 3, 224, 224, device=cuda_device)
+    t = torch.randint(0, 1000, (8,), device=cuda_device)
+    if channels_last:
+        net, stock = net.to(memory_format=torch.channels_last), stock.to(memory_format=torch.channels_last)
+        x = x.contiguous(memory_format=torch.channels_last)
+    codec.manual_seed(5)
+    loss = nn.functional.cross_entropy(net(x), t)
+    loss_ref = nn.functional.cross_entropy(stock(x), t)
+    assert abs(loss.item() - loss_ref.item()) < 1e-3 * max(1.0, abs(loss_ref.item()))
+    loss.backward(); loss_ref.backward()
+    ref_grads = dict(stock.named_parameters())
+    worst = ("", 0.0)
+    n = 0
+    for pname, p in net.named_parameters():
+        assert p.grad is not None, pname
+        r = _rel(p.grad, ref_grads[pname].grad)
+        n += 1
+        if r > worst[1]:
+            worst = (pname, r)
+    print(f"{name} channels_last={channels_last}: {n} parameters, worst relative gradient error {worst[1]:.4f} at {worst[0]}")
+    assert worst[1] < 0.05, worst
