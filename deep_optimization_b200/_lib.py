@@ -18,6 +18,7 @@ ACT_FLAG_REF_COMPAT = 2
 ACT_FLAG_REF_CLAMP = 4
 ACT_FLAG_REF_TANH = 8
 ACT_FLAG_META_BF16 = 16
+ACT_FLAG_BALLOT_REF_BIAS = 32
 ACT_GEMM_B_IS_NK = 1
 ACT_GEMM_SINGLE_CTA = 2
 ACT_KIND_GELU, ACT_KIND_SILU, ACT_KIND_GELU_ERF = 1, 2, 3
@@ -57,6 +58,9 @@ SIGNATURES = {
     "act_bn_relu_bwd_reduce": ([_vp, _vp, _vp, _vp, _vp, _i32, _i64, _i32, _i64, _i32, _i32, _vp, _vp], _i32),
     "act_bn_relu_bwd_dx": ([_vp, _vp, _vp, _vp, _vp, _i32, _i64, _i32, _i64, _i32, _i32, _vp, _vp, _vp], _i32),
     "act_minmax": ([_vp, _i32, _i64, _i64, _vp, _vp, _vp], _i32),
+    "act_pack_ballot": ([_vp, _i32, _i64, _i32, _i32, _vp, _vp, _u64, _i32, _vp, _vp, _vp], _i32),
+    "act_unpack_ballot": ([_vp, _vp, _vp, _i32, _i64, _i32, _i32, _vp, _vp], _i32),
+    "act_copy": ([_vp, _vp, _sz, _sz, _sz, _vp], _i32),
     "act_calc_precision": ([_vp, _vp, _vp, _i64, ctypes.c_double], _i32),
     "act_fp8_gemm_workspace": ([_i32, _i32, _i32, _i32], ctypes.c_size_t),
     "act_fp8_gemm": ([_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _vp, ctypes.c_size_t, _vp], _i32),

@@ -1,7 +1,10 @@
 // FP8 (e4m3) GEMM with per-row / per-column fp32 scales and bf16 output, sm_100a:
 //     C[m,n] = bf16( (sum_k A[m,k] * B[k,n]) * sa[m] * sb[n] )
 //
-// One persistent CTA per SM, 320 threads in three roles:
+// Two kernels.  Problems with more than one 128-row block run on CTA pairs (namespace pair
+// below: tcgen05.mma.cta_group::2 on 256 x 256 tiles); single-row-block problems, and callers
+// that pass ACT_GEMM_SINGLE_CTA, run the kernel described here:
+// one persistent CTA per SM, 320 threads in three roles:
 //   warp 0      TMA producer: one lane issues cp.async.bulk.tensor loads of the
 //               128x128 A tile and the 256x128 B^T tile of a k-block into a
 //               4-stage shared-memory ring (128-byte swizzle), mbarrier-tracked;
@@ -337,30 +340,19 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 // .cta_group::2 so that their bytes are counted on the leader's mbarrier; no multicast),
 // warp 1 = MMA issuer (rank 0 of the pair only; its commits arrive on the barriers of both
 // CTAs), warps 2..9 = epilogue (each CTA drains its own accumulator; 32 x 64 bf16 pieces go
-// through two swizzled staging buffers per warp into bulk tensor stores of full 128-byte
-// rows).  Every wait is bounded as in the lone-CTA kernel.
+// through a swizzled staging buffer per warp into bulk tensor stores of full 128-byte rows).
+// Every wait is bounded as in the lone-CTA kernel.
 namespace pair {
 
 constexpr int BM_CTA = 128;                     // rows of A (and of B^T) staged per CTA
 constexpr int BN = 256, BK = 128;
 constexpr int TILE_M = 2 * BM_CTA;              // rows of C per pair
-#ifndef ACT_GEMM_PAIR_STAGES
-#define ACT_GEMM_PAIR_STAGES 5
-#endif
-#ifndef ACT_GEMM_EPI_BUFS
-#define ACT_GEMM_EPI_BUFS 2
-#endif
-#ifndef ACT_GEMM_PREFETCH
-#define ACT_GEMM_PREFETCH 0                      // 1: every cluster requests its next A rows into L2; 2: one per row group
-#endif
-#ifndef ACT_GEMM_RASTER
-#define ACT_GEMM_RASTER 0                        // 0: tiles dealt out round-robin; 1: one contiguous run per cluster
-#endif
-#ifndef ACT_GEMM_EPI_TEST
-#define ACT_GEMM_EPI_TEST 0                      // 1, 2: timing experiments with wrong results, never shipped
-#endif
-constexpr int STAGES = ACT_GEMM_PAIR_STAGES;
-constexpr int EPI_BUFS = ACT_GEMM_EPI_BUFS;     // staging buffers per epilogue warp
+// Six ring slots of 32 KB and one 4 KB staging buffer per epilogue warp fill the SM's 227 KB.
+// Measured on the three evaluation shapes: five slots with two staging buffers per warp ran
+// 1-2 % slower (the ring hides L2 latency, the second staging buffer hid nothing), and handing
+// each cluster one contiguous run of tiles instead of dealing them out round-robin 1-3 % slower.
+constexpr int STAGES = 6;
+constexpr int EPI_BUFS = 1;                     // staging buffers per epilogue warp
 constexpr int A_STAGE = BM_CTA * BK, B_STAGE = BM_CTA * BK;
 constexpr int PIECE_BYTES = 32 * 128;           // 32 rows x 64 bf16
 
@@ -391,21 +383,12 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-#ifndef ACT_GEMM_ARRIVE_MODE
-#define ACT_GEMM_ARRIVE_MODE 1
-#endif
 // Arrival on an mbarrier of (possibly) the other CTA of the pair.  It orders nothing but the
 // tensor-memory loads before it, which tcgen05.wait::ld and the tcgen05 fence already did, so it
 // carries the default CTA-scope release: a cluster-scope release made every accumulator hand-back
 // wait about 3000 cycles for the thread's earlier stores.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-#if ACT_GEMM_ARRIVE_MODE == 0
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" :: "r"(cluster_addr) : "memory");
-#elif ACT_GEMM_ARRIVE_MODE == 2
-    asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" :: "r"(cluster_addr) : "memory");
-#else
     asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" :: "r"(cluster_addr) : "memory");
-#endif
 }
 __device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v) {
     asm volatile("st.shared::cluster.u32 [%0], %1;" :: "r"(cluster_addr), "r"(v) : "memory");
@@ -415,11 +398,6 @@ __device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* m
     asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
                  " [%0], [%1, {%3, %4}], [%2];"
                  :: "r"(smem_u32(dst)), "l"(map), "r"(leader_bar), "r"(c0), "r"(c1) : "memory");
-}
-// requests a tile into L2 only (no shared-memory destination, nothing to wait for)
-__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* map, int c0, int c1) {
-    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
-                 :: "l"(map), "r"(c0), "r"(c1) : "memory");
 }
 __device__ __forceinline__ void umma_f8_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
@@ -448,15 +426,6 @@ __device__ __forceinline__ void tma_store_wait_read_keep(int keep) {
 __host__ __device__ constexpr uint32_t make_idesc_pair() {
     return (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TILE_M >> 4) << 24);
 }
-
-#ifdef ACT_GEMM_TRACE
-// timing experiment: cycle stamps of the first tiles of CTA 0, [tile][slot]
-constexpr int TRACE_TILES = 24, TRACE_SLOTS = 16;
-__device__ long long g_trace[TRACE_TILES * TRACE_SLOTS];
-#define TRACE(tile, slot, val) do { if (blockIdx.x == 0 && (tile) < TRACE_TILES) g_trace[(tile) * TRACE_SLOTS + (slot)] = (val); } while (0)
-#else
-#define TRACE(tile, slot, val) do {} while (0)
-#endif
 
 template <typename S>
 __device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, S* s, uint32_t code, uint32_t peer_abort_addr) {
@@ -496,19 +465,7 @@ fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     const int m_tiles = (M + TILE_M - 1) / TILE_M, n_tiles = (N + BN - 1) / BN;
     const int n_work = m_tiles * n_tiles;
     const int k_blocks = (K + BK - 1) / BK;
-#if ACT_GEMM_RASTER == 1
-    // Each cluster takes one contiguous run of tiles (row-major over the tile grid): consecutive
-    // tiles of a cluster then share their rows of A, which come out of L2 after the first of them,
-    // and a row block of C is written by one cluster over a short time.
-    const int n_cl = (int)n_clusters(), cid = (int)cluster_id();
-    const int per = n_work / n_cl, extra = n_work % n_cl;
-    const int first = cid * per + (cid < extra ? cid : extra);
-    const int w_end = first + per + (cid < extra ? 1 : 0);
-    constexpr int stride = 1;
-#else
     const int first = (int)cluster_id(), stride = (int)n_clusters();
-    const int w_end = n_work;
-#endif
     const uint32_t peer_abort = map_to_cta(smem_u32((const void*)&s->abort), rank ^ 1u);
 
     if (smem_u32(s) & 1023u) {                                // the swizzled tiles need this alignment
@@ -532,19 +489,9 @@ fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
             bool ok = true;
-            for (int w = first; ok && w < w_end; w += stride) {
+            for (int w = first; ok && w < n_work; w += stride) {
                 const int m0 = (w / n_tiles) * TILE_M + (int)rank * BM_CTA;
                 const int n0 = (w % n_tiles) * BN + (int)rank * BM_CTA;
-#if ACT_GEMM_PREFETCH
-                // A is read from HBM exactly once (the clusters that share its rows run side by side),
-                // so every first touch of an A block would pay the HBM latency inside the ring.  The
-                // rows of this cluster's NEXT tile are therefore requested into L2 one tile ahead, by
-                // one cluster per group of clusters that will share them.
-                const int w_next = w + stride;
-                const bool prefetch = w_next < w_end &&
-                                      (ACT_GEMM_PREFETCH == 1 || (w_next % n_tiles) == 0 || first == 0);
-                const int m0_next = (w_next / n_tiles) * TILE_M + (int)rank * BM_CTA;
-#endif
                 for (int kb = 0; kb < k_blocks; ++kb) {
                     if (!(ok = wait_bar(&s->empty[stage], phase ^ 1, s, 1, peer_abort))) break;
                     // the leader's barrier counts the bytes of all four loads of the pair
@@ -552,9 +499,6 @@ fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                     const uint32_t bar = map_to_cta(smem_u32(&s->full[stage]), 0);
                     tma_load_2d_pair(s->a[stage], &map_a, bar, kb * BK, m0);
                     tma_load_2d_pair(s->b[stage], &map_bt, bar, kb * BK, n0);
-#if ACT_GEMM_PREFETCH
-                    if (prefetch) tma_prefetch_l2_2d(&map_a, kb * BK, m0_next);
-#endif
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
             }
@@ -572,16 +516,13 @@ fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
             uint32_t stage = 0, phase = 0, acc_phase[2] = {0, 0};
             bool ok = true;
             int t = 0;
-            for (int w = first; ok && w < w_end; w += stride, ++t) {
+            for (int w = first; ok && w < n_work; w += stride, ++t) {
                 const int buf = t & 1;
-                TRACE(t, 0, clock64());
                 if (!(ok = wait_bar(&s->acc_empty[buf], acc_phase[buf] ^ 1, s, 2, peer_abort))) break;
-                TRACE(t, 1, clock64());
                 tc_fence_after();
                 const uint32_t d = tmem_base + (uint32_t)(buf * BN);
                 for (int kb = 0; kb < k_blocks; ++kb) {
                     if (!(ok = wait_bar(&s->full[stage], phase, s, 3, peer_abort))) break;
-                    if (kb == 0) TRACE(t, 2, clock64());
                     tc_fence_after();
                     const uint64_t adesc = make_kmajor_desc(s->a[stage]);
                     const uint64_t bdesc = make_kmajor_desc(s->b[stage]);
@@ -593,7 +534,6 @@ fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                 }
                 if (!ok) break;
                 umma_commit_pair(&s->acc_full[buf]);           // both CTAs' accumulators are complete
-                TRACE(t, 3, clock64());
                 acc_phase[buf] ^= 1;
             }
         }
@@ -608,18 +548,16 @@ fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         uint32_t groups = 0, last_group[EPI_BUFS] = {};        // lane 0: store groups committed, and which one last read a buffer
         bool ok = true;
         int t = 0;
-        for (int w = first; w < w_end; w += stride, ++t) {
+        for (int w = first; w < n_work; w += stride, ++t) {
             const int buf = t & 1;
             const int m0 = (w / n_tiles) * TILE_M + (int)rank * BM_CTA, n0 = (w % n_tiles) * BN;
             s->sb[buf][etid] = (n0 + etid < N) ? __ldg(sb + n0 + etid) : 0.0f;
             asm volatile("bar.sync 1, %0;" :: "n"(EPI_WARPS * 32) : "memory");
-            if (threadIdx.x == 64) TRACE(t, 4, clock64());
             const int row = m0 + q * 32 + lane;
             const float sa_row = row < M ? __ldg(sa + row) : 0.0f;
             const f32x2 sa2 = pack2(sa_row, sa_row);
             if (ok) ok = wait_bar_warp(&s->acc_full[buf], full_phase[buf], s, 4, peer_abort);
             if (!ok) continue;
-            if (threadIdx.x == 64) TRACE(t, 5, clock64());
             full_phase[buf] ^= 1;
             tc_fence_after();
             const uint32_t t_base = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + half * 128);
@@ -664,25 +602,15 @@ fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                     const int pc = ((chunk & 1) * 4 + v) ^ (lane & 7);
                     *reinterpret_cast<uint4*>(stage_buf + lane * 128 + (pc << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
                 }
-                if (threadIdx.x == 64) TRACE(t, 6 + chunk, clock64());
                 if (chunk & 1) {
                     // 32 rows x 64 columns leave as one bulk tensor store of full 128-byte rows
                     fence_proxy_async();
                     __syncwarp();
                     const int col0 = n0 + half * 128 + (chunk >> 1) * 64;
-#if ACT_GEMM_EPI_TEST == 1
-                    (void)col0;                              // experiment: everything but the store
-#elif ACT_GEMM_EPI_TEST == 2
-                    if (lane == 0 && col0 < N && m0 + q * 32 < M) {   // experiment: all stores land in one 256 x 256 corner
-                        tma_store_2d(&map_c, stage_buf, col0 % 256, (m0 + q * 32) % 256);
-                        last_group[pb] = ++groups;
-                    }
-#else
                     if (lane == 0 && col0 < N && m0 + q * 32 < M) {
                         tma_store_2d(&map_c, stage_buf, col0, m0 + q * 32);
                         last_group[pb] = ++groups;
                     }
-#endif
                 }
             }
         }
@@ -927,12 +855,6 @@ static __device__ __align__(256) uint8_t g_static_bt_scratch[kStaticScratchBytes
 // Device address of the array on each device, looked up on first use.  In host code
 // the array's name is only a handle for this lookup, never a pointer to pass along.
 static uint8_t* g_static_scratch_ptr[kMaxDevices];
-
-#ifdef ACT_GEMM_TRACE
-extern "C" int act_fp8_gemm_trace(long long* out) {
-    return cudaMemcpyFromSymbol(out, act::gemm::pair::g_trace, sizeof(long long) * 24 * 16) == cudaSuccess ? 0 : 1;
-}
-#endif
 
 extern "C" size_t act_fp8_gemm_static_limit(void) { return kStaticScratchBytes; }
 

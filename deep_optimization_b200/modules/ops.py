@@ -35,6 +35,7 @@ class _DOConvnd(Function):
             weight_compute = weight.to(dt)
         else:
             weight_compute = weight_master
+            input = input.to(weight_master.dtype)      # e.g. the bf16 output of the PACT clamp in an fp32 model
         m = meta[f"{target_name}"]
 
         # DIVISION: the input is split into a low-pass part (average pool, kept in e4m3) and the

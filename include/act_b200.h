@@ -39,6 +39,7 @@ extern "C" {
 #define ACT_FLAG_REF_CLAMP     4   /* with REF_COMPAT: clamp x to +-clamp_alpha first                */
 #define ACT_FLAG_REF_TANH      8   /* with REF_COMPAT: x = tanh(x/0.5)*0.5 before the range          */
 #define ACT_FLAG_META_BF16     16  /* round scale and min to bf16 precision (still stored as fp32)   */
+#define ACT_FLAG_BALLOT_REF_BIAS 32 /* act_pack_ballot: keep the reference's extra -0.5 in the rounding */
 
 /* activation kinds of act_activation_fwd_quant_pack */
 #define ACT_KIND_GELU 1            /* tanh-approximated GELU */
@@ -309,6 +310,35 @@ ACT_API int act_maxpool_bwd_cl(const void* idx, const void* dy, int dtype, int64
  */
 ACT_API int act_minmax(const void* x, int dtype, int64_t rows, int64_t cols, float* mn, float* mx,
                void* stream);
+
+/*
+ * The reference's second codec: caller-supplied per-group min and max (in x's own type),
+ * scale = (2^bits - 1) / (max - min + 2e-6), stochastic rounding with its index hash
+ * sgd_noise keyed by (element index << 32) ^ seed, codes stored as bit planes in warp-ballot
+ * order (32 consecutive elements = one chunk of `bits` consecutive words; bit i of word p =
+ * bit p of the code of the chunk's element i).  group_size: a multiple of 32; bits: 1..8.
+ *   packed: uint32 [n_groups * group_size/32 * bits]; scale: [n_groups] in x's type (output).
+ *   flags: 0 rounds without bias, rint((x-min)*scale + noise) with noise in [-0.5, 0.5);
+ *          ACT_FLAG_BALLOT_REF_BIAS subtracts the further 0.5 the reference subtracts.
+ * act_unpack_ballot: y = code / scale + min, in the type of scale and min.
+ * Replaces cpp_extension.pack_mixed_precision_cuda / unpack_mixed_precision_cuda
+ * (AC/cpp_extension/src/quantization_cuda_kernels.cu:15-195, 200-298; hash:
+ * AC/cpp_extension/include/quant_common.h:32-43).
+ */
+ACT_API int act_pack_ballot(const void* x, int dtype, int64_t n_groups, int group_size, int bits,
+                    const void* mn, const void* mx, uint64_t seed, int flags,
+                    void* packed, void* scale, void* stream);
+ACT_API int act_unpack_ballot(const void* packed, const void* scale, const void* mn, int dtype,
+                      int64_t n_groups, int group_size, int bits, void* y, void* stream);
+
+/*
+ * Identity copy of nbytes from src to dst (both 16-byte aligned), refused with ACT_ERR_SIZE
+ * when nbytes exceeds either buffer's stated capacity.
+ * Replaces cpp_extension.copy_launch (AC/cpp_extension/src/copy.cu:50-102), a debugging
+ * aid of the reference that copies [N*G, 256] elements without any bounds check.
+ */
+ACT_API int act_copy(const void* src, void* dst, size_t nbytes, size_t src_capacity, size_t dst_capacity,
+             void* stream);
 
 /*
  * Greedy bit allocation on the host (no GPU work).

@@ -614,6 +614,100 @@ ORACLE_EXPORT int oracle_fp8_gemm(const uint8_t *A, const uint8_t *B, const floa
     return 0;
 }
 
+/* ------------------------------------------------ ballot-plane codec (legacy)
+ * The reference's second codec, cpp_extension/src/quantization_cuda_kernels.cu:
+ *   scale = (2^b - 1) / (max - min + 2e-6)  in the data's own type (:15-28);
+ *   q = rint(max((x - min) * scale + noise - 0.5, 0)) with noise = sgd_noise(key),
+ *   key = (linear element index << 32) ^ seed (:76-87);
+ *   layout: 32 consecutive elements of a group form one chunk; the chunk's b words
+ *   follow one another and bit `lane` of word p is bit p of the code of the
+ *   chunk's element `lane` (the __ballot_sync order, :94-104);
+ *   decode: code / scale + min (:241-242).
+ * sgd_noise is cpp_extension/include/quant_common.h:32-43: one multiply-xorshift
+ * step, the top 24 bits as u in [0,1), returned as u - 0.5.  Because the noise is
+ * already centred, the reference's extra "- 0.5" biases every code down by half a
+ * step; FLAG_BALLOT_REF_BIAS keeps that arithmetic, without it the rounding is
+ * the unbiased rint((x-min)*scale + noise) = floor((x-min)*scale + u).
+ * Every operation is rounded separately (the reference is built with fast-math,
+ * so its own last bits are not reproducible); 16-bit types round the scale
+ * arithmetic to their own type after every operation as c10's scalar types do. */
+enum { FLAG_BALLOT_REF_BIAS = 32 };
+
+static inline float sgd_noise_ref(uint64_t x) {
+    x ^= x >> 32;
+    x *= 0xD6E8FEB86659FD93ull;
+    x ^= x >> 32;
+    const float u = (float)(x >> 40) * (1.0f / 16777216.0f);
+    return u - 0.5f;
+}
+
+ORACLE_EXPORT void oracle_sgd_noise(const uint64_t *keys, int64_t n, float *out) {
+    for (int64_t i = 0; i < n; ++i) out[i] = sgd_noise_ref(keys[i]);
+}
+
+static inline float round_to(float v, int dtype) {
+    if (dtype == DT_BF16) return bf16_to_f32(f32_to_bf16(v));
+    if (dtype == DT_F16) return f16_to_f32(f32_to_f16(v));
+    return v;
+}
+static inline void store_from_f32(void *y, int dtype, int64_t i, float v) {
+    if (dtype == DT_F32) ((float *)y)[i] = v;
+    else if (dtype == DT_BF16) ((uint16_t *)y)[i] = f32_to_bf16(v);
+    else ((uint16_t *)y)[i] = f32_to_f16(v);
+}
+
+ORACLE_EXPORT int oracle_pack_ballot(const void *x, int dtype, int64_t n_groups, int group_size, int bits,
+                                     const void *mn, const void *mx, uint64_t seed, int flags,
+                                     uint32_t *packed, void *scale) {
+    if (bits < 1 || bits > 8 || group_size < 32 || (group_size & 31)) return 1;
+    const int chunks = group_size / 32;
+    const float qmax = (float)((1 << bits) - 1);
+#pragma omp parallel for schedule(static)
+    for (int64_t g = 0; g < n_groups; ++g) {
+        const float m = load_as_f32(mn, dtype, g);
+        volatile float denom = round_to(load_as_f32(mx, dtype, g) - m, dtype);
+        denom = round_to(denom + round_to(2e-6f, dtype), dtype);
+        const float sc = round_to(qmax / denom, dtype);
+        store_from_f32(scale, dtype, g, sc);
+        for (int c = 0; c < chunks; ++c) {
+            uint32_t words[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            for (int lane = 0; lane < 32; ++lane) {
+                const int64_t id = g * group_size + c * 32 + lane;
+                const float noise = sgd_noise_ref(((uint64_t)id << 32) ^ seed);
+                volatile float t = load_as_f32(x, dtype, id) - m;
+                t = t * sc;
+                t = t + noise;
+                if (flags & FLAG_BALLOT_REF_BIAS) t = t - 0.5f;
+                float q = nearbyintf(t > 0.0f ? t : 0.0f);       /* NaN -> 0 like fmaxf */
+                if (!(q <= qmax)) q = qmax;
+                const uint32_t code = (uint32_t)q;
+                for (int p = 0; p < bits; ++p) words[p] |= ((code >> p) & 1u) << lane;
+            }
+            for (int p = 0; p < bits; ++p) packed[(g * chunks + c) * bits + p] = words[p];
+        }
+    }
+    return 0;
+}
+
+ORACLE_EXPORT int oracle_unpack_ballot(const uint32_t *packed, const void *scale, const void *mn, int dtype,
+                                       int64_t n_groups, int group_size, int bits, void *y) {
+    if (bits < 1 || bits > 8 || group_size < 32 || (group_size & 31)) return 1;
+    const int chunks = group_size / 32;
+#pragma omp parallel for schedule(static)
+    for (int64_t g = 0; g < n_groups; ++g) {
+        const float sc = load_as_f32(scale, dtype, g), m = load_as_f32(mn, dtype, g);
+        for (int c = 0; c < chunks; ++c)
+            for (int lane = 0; lane < 32; ++lane) {
+                uint32_t code = 0;
+                for (int p = 0; p < bits; ++p) code |= ((packed[(g * chunks + c) * bits + p] >> lane) & 1u) << p;
+                volatile float v = (float)code / sc;
+                v = v + m;
+                store_from_f32(y, dtype, g * group_size + c * 32 + lane, v);
+            }
+    }
+    return 0;
+}
+
 /* ------------------------------------------------- division-sequence check
  * The CUDA kernels divide by a per-group scale with a five-operation FMA
  * sequence around the correctly rounded reciprocal instead of a division

@@ -33,6 +33,7 @@ FLAG_REF_COMPAT = 2
 FLAG_REF_CLAMP = 4
 FLAG_REF_TANH = 8
 FLAG_META_BF16 = 16
+FLAG_BALLOT_REF_BIAS = 32
 
 HALF_C = np.float32(0.5) - np.float32(1e-6)
 
@@ -74,6 +75,10 @@ def lib() -> ctypes.CDLL:
         L.oracle_num_threads.restype = i32
         L.oracle_set_threads.argtypes = [i32]
         L.oracle_set_threads.restype = None
+        L.oracle_sgd_noise.argtypes = [vp, i64, vp]
+        L.oracle_sgd_noise.restype = None
+        L.oracle_pack_ballot.argtypes = [vp, i32, i64, i32, i32, vp, vp, u64, i32, vp, vp]
+        L.oracle_unpack_ballot.argtypes = [vp, vp, vp, i32, i64, i32, i32, vp]
         _lib = L
     return _lib
 
@@ -268,6 +273,51 @@ def fp8_gemm(A8: np.ndarray, B8: np.ndarray, sa: np.ndarray, sb: np.ndarray):
     Cf = np.empty((M, N), np.float32)
     lib().oracle_fp8_gemm(_ptr(A8), _ptr(B8), _ptr(sa), _ptr(sb), _ptr(C), _ptr(Cf), M, N, K, K, N, N)
     return C, Cf
+
+
+def sgd_noise(keys: np.ndarray) -> np.ndarray:
+    """The reference's index hash (cpp_extension/include/quant_common.h:32-43) on uint64 keys."""
+    keys = np.ascontiguousarray(keys, np.uint64)
+    out = np.empty(keys.shape, np.float32)
+    lib().oracle_sgd_noise(_ptr(keys), keys.size, _ptr(out))
+    return out
+
+
+def py_sgd_noise(key: int) -> float:
+    """The same hash in Python integers (an independent restatement for known-answer tests)."""
+    x = key & 0xFFFFFFFFFFFFFFFF
+    x ^= x >> 32
+    x = (x * 0xD6E8FEB86659FD93) & 0xFFFFFFFFFFFFFFFF
+    x ^= x >> 32
+    return float(np.float32(np.float32(x >> 40) * np.float32(1.0 / 16777216.0)) - np.float32(0.5))
+
+
+def pack_ballot(x: np.ndarray, mn: np.ndarray, mx: np.ndarray, group_size: int, bits: int, seed: int = 0,
+                flags: int = 0, dtype: str | None = None):
+    """Ballot-plane codec of the reference's cpp extension.  x, mn, mx in one dtype (bf16 as
+    uint16 bits).  Returns (packed uint32 [NG * group_size/32 * bits], scale in that dtype)."""
+    code = _dtype_code(x, dtype)
+    x = np.ascontiguousarray(x)
+    mn, mx = np.ascontiguousarray(mn), np.ascontiguousarray(mx)
+    ng = x.size // group_size
+    packed = np.empty(ng * (group_size // 32) * bits, np.uint32)
+    scale = np.empty(ng, mn.dtype)
+    rc = lib().oracle_pack_ballot(_ptr(x), code, ng, group_size, bits, _ptr(mn), _ptr(mx), seed & 0xFFFFFFFFFFFFFFFF,
+                                  flags, _ptr(packed), _ptr(scale))
+    assert rc == 0
+    return packed, scale
+
+
+def unpack_ballot(packed: np.ndarray, scale: np.ndarray, mn: np.ndarray, group_size: int, bits: int,
+                  dtype: str | None = None) -> np.ndarray:
+    code = _dtype_code(scale, dtype)
+    packed = np.ascontiguousarray(packed, np.uint32)
+    ng = scale.size
+    y = np.empty((ng, group_size), scale.dtype)
+    rc = lib().oracle_unpack_ballot(_ptr(packed), _ptr(np.ascontiguousarray(scale)), _ptr(np.ascontiguousarray(mn)),
+                                    code, ng, group_size, bits, _ptr(y))
+    assert rc == 0
+    return y
 
 
 def e4m3_decode(a: np.ndarray) -> np.ndarray:

@@ -124,5 +124,3 @@ def test_cpp_extension_mirror(cuda_device):
         assert ((y.float() - x.float()).abs() <= step * 1.05 + 0.02).all()
     lo, hi = cx.min_max_kernel(x)
     assert torch.equal(lo, x.float().amin(-1)) and torch.equal(hi, x.float().amax(-1))
-    with pytest.raises(NotImplementedError):
-        cx.pack_mixed_precision_cuda(x, None, None, None, 0.0)

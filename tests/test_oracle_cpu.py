@@ -241,3 +241,48 @@ def test_sub_group_averaging(oracle, bits, avg):
             assert (y == y[:, :, :1]).all()
             mean = x.reshape(24, gs // avg, avg).mean(2)
             assert (np.abs(y[:, :, 0] - mean) <= a[1][:, None] * 1.001 + 1e-6).all()
+
+
+# ------------------------------------------------------------- ballot-plane codec (legacy)
+def test_sgd_noise_known_answers(oracle):
+    """The reference's index hash (cpp_extension/include/quant_common.h:32-43): the C oracle
+    against a restatement in Python integers, on fixed keys with their values written out (worked
+    by hand from the three steps: x ^= x >> 32; x *= 0xD6E8FEB86659FD93; x ^= x >> 32; top 24
+    bits / 2^24 - 0.5) and on random keys."""
+    keys = np.array([0, 1, (5 << 32) ^ 42, (123456789 << 32) ^ 0xDEADBEEF, 2 ** 64 - 1], np.uint64)
+    want = np.array([-0.5, 0.33949267864227295, -0.044788897037506104, -0.2671549320220947, 0.10018932819366455],
+                    np.float32)
+    assert np.array_equal(oracle.sgd_noise(keys), want)
+    # key 1 by hand: 1 ^ 0 = 1; 1 * M = 0xD6E8FEB86659FD93; ^= >> 32 leaves the top 32 bits, 0xD6E8FEB8;
+    # top 24 bits 0xD6E8FE = 14084350; 14084350 / 2^24 - 0.5
+    assert want[1] == np.float32(np.float32(14084350) * np.float32(2.0 ** -24) - np.float32(0.5))
+    rng = np.random.default_rng(0)
+    rk = rng.integers(0, 2 ** 63, size=2000, dtype=np.uint64) * np.uint64(2) + rng.integers(0, 2, size=2000, dtype=np.uint64)
+    got = oracle.sgd_noise(rk)
+    assert all(got[i] == np.float32(oracle.py_sgd_noise(int(rk[i]))) for i in range(rk.size))
+    assert got.min() >= -0.5 and got.max() < 0.5 and abs(float(got.mean())) < 0.02
+
+
+@pytest.mark.parametrize("bits", (1, 2, 3, 4, 8))
+def test_ballot_layout_and_round_trip(oracle, bits):
+    """Bit p of a code sits at bit `lane` of word p of its 32-element chunk; decode inverts it;
+    the unbiased rounding stays within one step and is unbiased, the reference's variant sits
+    half a step lower."""
+    rng = np.random.default_rng(bits)
+    gs, ng = 64, 40
+    x = rng.random((ng, gs), dtype=np.float32) * 4 - 1
+    mn, mx = x.min(1), x.max(1)
+    packed, scale = oracle.pack_ballot(x, mn, mx, gs, bits, seed=11)
+    words = packed.reshape(ng, gs // 32, bits)
+    codes = np.zeros((ng, gs), np.int64)
+    for p in range(bits):
+        codes += (((words[:, :, p, None] >> np.arange(32, dtype=np.uint32)) & 1).reshape(ng, gs).astype(np.int64)) << p
+    y = oracle.unpack_ballot(packed, scale, mn, gs, bits)
+    assert np.array_equal(y, (codes.astype(np.float32) / scale[:, None] + mn[:, None]).astype(np.float32))
+    step = 1.0 / scale[:, None]
+    assert (np.abs(y - x) <= step * 1.0001).all()
+    assert abs(float(((y - x) / step).mean())) < 0.03
+    pb, _ = oracle.pack_ballot(x, mn, mx, gs, bits, seed=11, flags=oracle.FLAG_BALLOT_REF_BIAS)
+    yb = oracle.unpack_ballot(pb, scale, mn, gs, bits)
+    bias = float(((yb - x) / step).mean())
+    assert -0.56 < bias < (-0.2 if bits == 1 else -0.44)      # clipped at code 0, hence above -0.5
