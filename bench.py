@@ -336,6 +336,7 @@ def run_extras(dev):
     out["fused_activation_kernels_bf16"] = fused
     del xr, mbits
     out["fp8_gemm"] = run_gemm_shapes(dev)
+    out["dw_from_packed"] = run_dw_shapes(dev)
     out["write_stream"] = run_write_stream(dev)
     out["reference_triton"] = run_reference_triton()
     return out
@@ -398,6 +399,47 @@ def run_gemm_shapes(dev, shapes=GEMM_SHAPES, reps=20):
         del A8, B8, C, ws, Bt, ref
     torch.cuda.empty_cache()
     return gem
+
+
+def run_dw_shapes(dev, shapes=((50432, 3072, 768), (50432, 768, 3072)), reps=10):
+    """The weight gradient of a linear layer from its 2-bit packed input (group 128), decoded
+    inside the GEMM, beside the unfused sequence it replaces: dequant_unpack to bf16, then
+    cuBLAS dy^T @ x.  (M, N, K) are the two MLP layers of ViT-B/16 at batch 256.  Checked first:
+    abort word clear and the result within 2^-10 of the float64 product on 64 sampled rows."""
+    import torch
+    from deep_optimization_b200 import codec
+    from deep_optimization_b200.gemm import dw_from_packed, dw_status
+    out = {}
+    for (M, N, K) in shapes:
+        x = torch.nn.functional.gelu(torch.randn(M, K, device=dev)).to(torch.bfloat16)
+        dy = (torch.randn(M, N, device=dev) * 0.1).to(torch.bfloat16)
+        packed, scale, mn = codec.quant_pack(x, BITS, GROUP, seed=3, offset=1)
+        xq = torch.empty((M, K), dtype=torch.bfloat16, device=dev)
+        dw = torch.empty((N, K), dtype=torch.float32, device=dev)
+        dw_from_packed(dy, packed, scale, mn, BITS, GROUP, K, out=dw)
+        status = dw_status()
+        codec.dequant_unpack(packed, scale, mn, BITS, GROUP, out_dtype=torch.bfloat16, out=xq.view(-1, GROUP))
+        rows = torch.linspace(0, N - 1, 64, device=dev).long()
+        ref = dy[:, rows].double().t() @ xq.double()
+        tol = ref.abs() * 2.0 ** -10 + ref.abs().max() * 2.0 ** -13 + 1e-6
+        if status != 0 or not bool(((dw[rows].double() - ref).abs() <= tol).all()):
+            raise SystemExit(f"dw_from_packed M={M} N={N} K={K}: wrong result (abort word {status})")
+        del ref
+        t_fused = _median_launch_ms(lambda i=0: dw_from_packed(dy, packed, scale, mn, BITS, GROUP, K, out=dw), reps=reps, regions=5)
+
+        def unfused(i=0):
+            codec.dequant_unpack(packed, scale, mn, BITS, GROUP, out_dtype=torch.bfloat16, out=xq.view(-1, GROUP))
+            return dy.t().mm(xq)
+        t_unfused = _median_launch_ms(unfused, reps=reps, regions=5)
+        t_mm = _median_launch_ms(lambda i=0: dy.t().mm(xq), reps=reps, regions=5)
+        fl = 2.0 * M * N * K
+        out[f"M{M}_N{N}_K{K}"] = {"fused_ms": t_fused, "fused_TFLOPs": fl / t_fused / 1e9,
+                                   "dequant_plus_cublas_ms": t_unfused, "cublas_mm_alone_ms": t_mm,
+                                   "speedup_vs_unfused": t_unfused / t_fused,
+                                   "checked": "abort word 0; 64 sampled rows within 2^-10 |ref| + 2^-13 max|ref|"}
+        del x, dy, packed, scale, mn, xq, dw
+    torch.cuda.empty_cache()
+    return out
 
 
 def run_write_stream(dev):
@@ -728,6 +770,7 @@ def run_only(args):
     the benchmark, so that a capture of them ends by itself.
 
     --only gemm --shape M K N [--reps R]          the FP8 GEMM on one shape (checked, then timed)
+    --only dw --shape M N K [--reps R]            the weight gradient from the packed input on one shape
     --only bn --shape N C H W [--channels-last]   the five kernels of one fused BatchNorm+ReLU layer
     --only train-profile --model resnet50|vit_b16 [--channels-last] [--no-act] [--rows R]
                                                   two training steps under torch.profiler; under
@@ -742,6 +785,9 @@ def run_only(args):
     if args.only == "gemm":
         M, K, N = args.shape
         print(json.dumps(run_gemm_shapes(dev, ((M, K, N),), reps=args.reps)), flush=True)
+    elif args.only == "dw":
+        M, N, K = args.shape
+        print(json.dumps(run_dw_shapes(dev, ((M, N, K),), reps=args.reps)), flush=True)
     elif args.only == "bn":
         from deep_optimization_b200 import codec
         N, C, H, W = args.shape
@@ -784,7 +830,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the fp32 codec and GEMM side measurements")
     ap.add_argument("--no-train", action="store_true", help="skip the ResNet-50 / ViT-B/16 training steps")
-    ap.add_argument("--only", choices=("codec", "gemm", "bn", "train-profile"),
+    ap.add_argument("--only", choices=("codec", "gemm", "dw", "bn", "train-profile"),
                     help="codec: the headline alone; the others: small runs for profilers (see run_only)")
     ap.add_argument("--shape", type=int, nargs="+", help="--only gemm: M K N; --only bn: N C H W")
     ap.add_argument("--reps", type=int, default=5)

@@ -65,6 +65,8 @@ SIGNATURES = {
     "act_fp8_gemm_workspace": ([_i32, _i32, _i32, _i32], ctypes.c_size_t),
     "act_fp8_gemm": ([_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _vp, ctypes.c_size_t, _vp], _i32),
     "act_fp8_gemm_status": ([_vp, _i32], _i32),
+    "act_dw_from_packed": ([_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _i32, _vp], _i32),
+    "act_dw_from_packed_status": ([_vp, _i32], _i32),
     "act_fp8_gemm_static_limit": ([], ctypes.c_size_t),
     "act_fp8_gemm_static": ([_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp], _i32),
     "act_strerror": ([_i32], ctypes.c_char_p),

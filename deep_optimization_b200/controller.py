@@ -304,6 +304,9 @@ class Controller:
             traced.graph.eliminate_dead_code()
             traced.graph.lint()
             traced.recompile()
+        if "fused_dw" in self.config:
+            from .modules import ops as _ops
+            _ops.set_fused_dw(self.config["fused_dw"])
         if graph_mode:
             torch.backends.cuda.matmul.allow_tf32 = True
             torch.backends.cudnn.allow_tf32 = True

@@ -67,3 +67,41 @@ def gemm_status(clear: bool = True) -> int:
     v = ctypes.c_uint(0)
     _lib.check(_lib.load().act_fp8_gemm_status(ctypes.byref(v), 1 if clear else 0), "act_fp8_gemm_status")
     return int(v.value)
+
+
+def dw_from_packed(dy: torch.Tensor, packed: torch.Tensor, scale: torch.Tensor, mn: torch.Tensor, bits: int,
+                   group_size: int, K: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """dW [N, K] (fp32) = dy[M, N]^T @ X~[M, K] with X~ decoded from `packed / scale / mn` (the
+    output of codec.quant_pack on the row-major [M, K] layer input, flat groups) inside the
+    GEMM: the step `dequant_unpack` + `dy.T.mm(x)` of a linear layer's backward
+    (Activation_Compression/modules/ops.py:496-526) without the dequantised copy."""
+    if not dy.is_cuda:
+        raise RuntimeError("dw_from_packed needs CUDA tensors: there is no CPU path")
+    if dy.dtype != torch.bfloat16:
+        raise TypeError("dy must be bfloat16")
+    dy = dy.reshape(-1, dy.shape[-1])
+    if dy.stride(1) != 1:
+        dy = dy.contiguous()
+    M, N = dy.shape
+    packed = packed.contiguous()
+    scale = scale.reshape(-1).to(torch.float32).contiguous()
+    mn = mn.reshape(-1).to(torch.float32).contiguous()
+    if scale.numel() * group_size != M * K:
+        raise ValueError("scale does not have one entry per group of the [M, K] input")
+    dw = out if out is not None else torch.empty((N, K), dtype=torch.float32, device=dy.device)
+    if dw.dtype != torch.float32 or dw.shape != (N, K) or dw.stride(1) != 1:
+        raise ValueError("out must be a float32 [N, K] tensor with unit column stride")
+    with torch.cuda.device(dy.device):
+        rc = _lib.load().act_dw_from_packed(dy.data_ptr(), packed.data_ptr(), scale.data_ptr(), mn.data_ptr(), bits,
+                                            group_size, M, N, K, dy.stride(0), dw.data_ptr(), dw.stride(0),
+                                            torch.cuda.current_stream(dy.device).cuda_stream)
+    _lib.check(rc, "act_dw_from_packed")
+    return dw
+
+
+def dw_status(clear: bool = True) -> int:
+    """Abort reason of the last dw_from_packed (0 = none).  Synchronises the device."""
+    import ctypes
+    v = ctypes.c_uint(0)
+    _lib.check(_lib.load().act_dw_from_packed_status(ctypes.byref(v), 1 if clear else 0), "act_dw_from_packed_status")
+    return int(v.value)

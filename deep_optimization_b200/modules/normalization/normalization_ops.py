@@ -205,7 +205,11 @@ class _DOLayerNorm(Function):
     def forward(ctx, input, normalized_shape, weight, bias, eps, target_name, meta):
         w = None if weight is None else weight.to(input.dtype)
         b = None if bias is None else bias.to(input.dtype)
-        y, mean, rstd = torch.ops.aten.native_layer_norm(input, list(normalized_shape), w, b, eps)
+        # in the input's own type (statistics are fp32 inside the kernel): under autocast the stock
+        # module would first copy a bf16 input to fp32 and return fp32, two passes the next
+        # layer's cast back to bf16 undoes
+        with torch.autocast("cuda", enabled=False):
+            y, mean, rstd = torch.ops.aten.native_layer_norm(input, list(normalized_shape), w, b, eps)
         q_tensors, q_meta, _ = unified_quantize(input, None, target_name, meta, clamp=False, clamp_alpha=0.0)
         ctx.q_meta = q_meta
         ctx.normalized_shape = list(normalized_shape)
@@ -222,8 +226,9 @@ class _DOLayerNorm(Function):
         b = None if bias is None else bias.to(dy.dtype)
         mask = [bool(ctx.needs_input_grad[0]), weight is not None and bool(ctx.needs_input_grad[2]),
                 bias is not None and bool(ctx.needs_input_grad[3])]
-        dx, dw, db = torch.ops.aten.native_layer_norm_backward(dy.contiguous(), x.contiguous(), ctx.normalized_shape,
-                                                               mean, rstd, w, b, mask)
+        with torch.autocast("cuda", enabled=False):
+            dx, dw, db = torch.ops.aten.native_layer_norm_backward(dy.contiguous(), x.contiguous(),
+                                                                   ctx.normalized_shape, mean, rstd, w, b, mask)
         wd, bd = ctx.param_dtypes
         return (dx if mask[0] else None, None, dw.to(wd) if mask[1] else None, db.to(bd) if mask[2] else None,
                 None, None, None)

@@ -122,6 +122,27 @@ _DOConv2d = _make_conv(2, F.conv2d, _pair)
 _DOConv3d = _make_conv(3, F.conv3d, _triple)
 
 
+# When set, _DOLinear.backward computes dW with the GEMM that decodes the packed input in its
+# operand pipeline (gemm.dw_from_packed) wherever the saved state allows it, instead of writing
+# the dequantised input out and multiplying.  `set_fused_dw(True)` / config key `fused_dw`.
+FUSED_DW = False
+
+
+def set_fused_dw(on: bool) -> None:
+    global FUSED_DW
+    FUSED_DW = bool(on)
+
+
+def _fused_dw_applies(q_meta, input_l, dy2, K) -> bool:
+    """The packed tensor is the plain flat grouping of a row-major [M, K] input with fp32 scale
+    and minimum: no low-pass residual, no padding, no spatial tiling, no sub-group averaging."""
+    (bits, pack_only, group_size, act_padding, _N, _G, _h, _w, pad_elig, reshape_elig, _cm, avg_alam,
+     _ab, ori_shape) = q_meta
+    return (input_l is None and not pack_only and not act_padding and not pad_elig and not reshape_elig
+            and not avg_alam and bits in (1, 2, 4, 8) and K % group_size == 0 and K % 8 == 0
+            and dy2.dtype == torch.bfloat16 and dy2.shape[1] % 8 == 0 and ori_shape[-1] == K)
+
+
 class _DOLinear(Function):
     @staticmethod
     @custom_fwd(device_type="cuda")
@@ -168,12 +189,17 @@ class _DOLinear(Function):
             dy = dy.to(dt)
         else:
             weight_compute = weight_master
-        x = unified_dequantize((q_out, q_scale, q_min), q_meta, input_l).to(weight_compute.dtype)
         dy = dy.to(weight_compute.dtype)
         dy2 = dy.reshape(-1, dy.shape[-1])
-        x2 = x.reshape(-1, x.shape[-1])
         dw = dx = db = None
-        if ctx.needs_input_grad[1]:
+        K = weight_master.shape[1]
+        if ctx.needs_input_grad[1] and FUSED_DW and q_scale is not None and q_scale.dtype == torch.float32 \
+                and _fused_dw_applies(q_meta, input_l, dy2, K):
+            from ..gemm import dw_from_packed
+            dw = dw_from_packed(dy2, q_out, q_scale, q_min, q_meta[0], q_meta[2], K).to(weight_master.dtype)
+        elif ctx.needs_input_grad[1]:
+            x = unified_dequantize((q_out, q_scale, q_min), q_meta, input_l).to(weight_compute.dtype)
+            x2 = x.reshape(-1, x.shape[-1])
             dw = dy2.T.mm(x2).to(weight_master.dtype)
         if ctx.needs_input_grad[0]:
             dx = dy2.mm(weight_compute).view(*input_shape)

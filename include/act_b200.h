@@ -378,6 +378,26 @@ ACT_API size_t act_fp8_gemm_static_limit(void);
 ACT_API int act_fp8_gemm_static(const void* A, const void* B, const float* sa, const float* sb, void* C,
                         int M, int N, int K, int lda, int ldb, int ldc, void* stream);
 
+/*
+ * Weight gradient of a linear layer computed from its compressed input, with the codes decoded
+ * inside the GEMM's operand pipeline instead of through a dequantised copy in memory:
+ *     dW[n, k] = sum_m dY[m, n] * bf16(code[m, k] * scale[g] + min[g])        (fp32 output)
+ *   dy: bf16 [M, N], row pitch ld_dy elements (multiple of 8), 16-byte aligned;
+ *   packed / scale / min: what act_quant_pack wrote for the row-major [M, K] input with flat groups
+ *       of group_size (a power of two in 32..1024 that divides K); bits in {1,2,4,8};
+ *   dw: fp32 [N, K], row pitch ld_dw elements (multiple of 4), 16-byte aligned; overwritten.
+ * N and K must be multiples of 8.  No workspace: slices of M owned by different CTAs are summed
+ * into dw with vector reductions after the entry has zeroed it on the same stream.
+ * Replaces the sequence dequant_unpack_triton + dy.T.mm(x) of _DOLinear.backward
+ * (AC/modules/ops.py:496-526); the reference's own attempt at this fusion is
+ * AC/test2.ipynb:14-19, 478-491.
+ */
+ACT_API int act_dw_from_packed(const void* dy, const void* packed, const float* scale, const float* min,
+                       int bits, int group_size, int M, int N, int K, int ld_dy,
+                       float* dw, int ld_dw, void* stream);
+/* Abort reason of the last act_dw_from_packed on the current device (0 = none); synchronises. */
+ACT_API int act_dw_from_packed_status(unsigned int* out, int clear);
+
 /* Abort reason of the last GEMM on the current device (0 = none); synchronises. */
 ACT_API int act_fp8_gemm_status(unsigned int* out, int clear);
 

@@ -172,3 +172,49 @@ def test_against_reference_kernel_fixture(cuda_device, case):
         assert torch.equal(got.cpu(), want.to(torch.bfloat16))       # exact sums, one rounding to bf16
     else:
         _check(got, want, K)
+
+
+# ------------------------------------------------- weight gradient from the packed input
+def _dw_case(cuda_device, M, N, K, bits, gs, seed=0):
+    """dW from the packed input against (a) the float64 product of dy with the dequantised input
+    and (b) the unfused path, dequant_unpack + matmul in bf16 with fp32 accumulation."""
+    from deep_optimization_b200 import codec
+    from deep_optimization_b200.gemm import dw_from_packed, dw_status
+    g = torch.Generator(device=cuda_device).manual_seed(seed)
+    x = torch.nn.functional.gelu(torch.randn(M, K, device=cuda_device, generator=g)).to(torch.bfloat16)
+    dy = (torch.randn(M, N, device=cuda_device, generator=g) * 0.1).to(torch.bfloat16)
+    packed, scale, mn = codec.quant_pack(x, bits, gs, seed=3, offset=1)
+    xq = codec.dequant_unpack(packed, scale, mn, bits, gs, out_dtype=torch.bfloat16).view(M, K)
+    dw = torch.full((N, K), float("nan"), device=cuda_device)
+    dw_from_packed(dy, packed, scale, mn, bits, gs, K, out=dw)
+    assert dw_status() == 0
+    assert not torch.isnan(dw).any()
+    ref = dy.double().t() @ xq.double()
+    # fp32 accumulation of M products of bf16 values, summed in slices: well inside 2^-10 of the
+    # row's scale; the decoded operand is bit-identical to the unfused path's
+    tol = ref.abs() * 2.0 ** -10 + ref.abs().max() * 2.0 ** -13 + 1e-6
+    err = (dw.double() - ref).abs()
+    assert (err <= tol).all(), f"max err {err.max().item()} vs tol {tol.min().item()}"
+    return dw, ref
+
+
+# (M, N, K, group): one stage; a single 8-row tile; ragged M, N and K with 32-element groups (K = 160);
+# several slices of M; more tiles than SMs would need N*K > 148 tiles, covered by (3000, 2048, 5120)
+@pytest.mark.parametrize("shape", [(64, 256, 256, 128), (128, 8, 128, 128), (1000, 264, 160, 32), (4096, 768, 256, 256),
+                                   (50432 // 8, 512, 768, 128), (3000, 2048, 5120, 512)])
+def test_dw_from_packed_two_bits(cuda_device, shape):
+    M, N, K, gs = shape
+    _dw_case(cuda_device, M, N, K, 2, gs)
+
+
+@pytest.mark.parametrize("bits", (1, 4, 8))
+@pytest.mark.parametrize("gs", (32, 256))
+def test_dw_from_packed_other_widths(cuda_device, bits, gs):
+    _dw_case(cuda_device, 1500, 384, 512, bits, gs, seed=bits)
+
+
+@pytest.mark.parametrize("shape", [(50432, 3072, 768), (50432, 768, 3072)])
+def test_dw_from_packed_vit_shapes(cuda_device, shape):
+    """The two MLP weight gradients of ViT-B/16 at batch 256 (M = 256 * 197)."""
+    M, N, K = shape
+    _dw_case(cuda_device, M, N, K, 2, 128)
