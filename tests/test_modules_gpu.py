@@ -210,8 +210,9 @@ def test_sync_batch_norm_single_rank(cuda_device):
 @pytest.mark.parametrize("name", ("resnet50", "vit_b16"))
 @pytest.mark.parametrize("channels_last", (False, True))
 def test_whole_model_gradients_at_8_bits(cuda_device, name, channels_last):
-    """One step of the Controller-wrapped model at 8 bits against the stock model: same loss and
-    every parameter gradient within 5 % relative L2 (fp32, no autocast, batch 8)."""
+    """One step of the Controller-wrapped model at 8 bits against the stock model: same loss, the
+    whole gradient within 2 % and every parameter gradient within 5 % relative L2 (fp32, no
+    autocast, batch 8)."""
     import copy
     from deep_optimization_b200 import codec
     from deep_optimization_b200.controller import Controller
@@ -234,13 +235,25 @@ def test_whole_model_gradients_at_8_bits(cuda_device, name, channels_last):
     assert abs(loss.item() - loss_ref.item()) < 1e-3 * max(1.0, abs(loss_ref.item()))
     loss.backward(); loss_ref.backward()
     ref_grads = dict(stock.named_parameters())
+    # A parameter whose exact gradient nearly cancels (a bias in front of another batch norm: the
+    # next normalisation removes a constant shift, so its gradient is a sum of terms that cancel to
+    # almost nothing) has no meaningful relative error; such entries are held to an absolute bound
+    # of 0.2 % of the whole gradient's norm instead, and the whole gradient to 2 %.
+    total = torch.sqrt(sum((q.grad.float() ** 2).sum() for q in ref_grads.values())).item()
+    err2 = 0.0
     worst = ("", 0.0)
     n = 0
     for pname, p in net.named_parameters():
         assert p.grad is not None, pname
-        r = _rel(p.grad, ref_grads[pname].grad)
+        g, r = p.grad.float(), ref_grads[pname].grad.float()
+        d = (g - r).norm().item()
+        err2 += d * d
         n += 1
-        if r > worst[1]:
-            worst = (pname, r)
-    print(f"{name} channels_last={channels_last}: {n} parameters, worst relative gradient error {worst[1]:.4f} at {worst[0]}")
+        if d > 2e-3 * total:
+            rel = d / r.norm().item()
+            if rel > worst[1]:
+                worst = (pname, rel)
+    print(f"{name} channels_last={channels_last}: {n} parameters, whole-gradient relative error {err2 ** 0.5 / total:.4f}, "
+          f"worst per-parameter relative error {worst[1]:.4f} at {worst[0] or '-'}")
+    assert err2 ** 0.5 / total < 0.02
     assert worst[1] < 0.05, worst
