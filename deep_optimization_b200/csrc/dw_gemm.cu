@@ -38,6 +38,10 @@ constexpr int TN = 256;                   // output columns (k) per tile
 constexpr int KB = 64;                    // rows of the reduction dimension m per stage
 constexpr int UMMA_K = 16;                // K of one tcgen05.mma for 16-bit operands
 constexpr int STAGES = 3;
+#ifndef ACT_DW_PREFETCH_BLOCKS
+#define ACT_DW_PREFETCH_BLOCKS 8
+#endif
+constexpr int PREFETCH_BLOCKS = ACT_DW_PREFETCH_BLOCKS;   // distance of the L2 prefetch of dY, in 64-row blocks (0: off)
 constexpr int A_STAGE = KB * TM * 2, B_STAGE = KB * TN * 2;      // 32 KB each
 constexpr int CHUNK = KB * 128;           // one 64-column chunk of a stage: 64 rows x 128 bytes
 constexpr int DEC_WARPS = 8;
@@ -93,6 +97,10 @@ __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
                  :: "r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+// requests a tile into L2 only (no shared-memory destination, nothing to wait for)
+__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* map, int c0, int c1) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" :: "l"(map), "r"(c0), "r"(c1) : "memory");
 }
 __device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(smem_u32(dst_smem)), "r"(cols) : "memory");
@@ -254,6 +262,13 @@ dw_gemm_kernel(const __grid_constant__ CUtensorMap map_dy, const uint8_t* __rest
 #pragma unroll
                     for (int j = 0; j < TM / 64; ++j)
                         tma_load_2d(s->a[stage] + j * CHUNK, &map_dy, &s->full_a[stage], n0 + j * 64, mb * KB);
+                    // dY streams out of HBM and the ring is only three blocks deep: ask for the block
+                    // PREFETCH_BLOCKS ahead to be brought into L2 now
+                    if (PREFETCH_BLOCKS > 0 && mb + PREFETCH_BLOCKS < b_hi) {
+#pragma unroll
+                        for (int j = 0; j < TM / 64; ++j)
+                            tma_prefetch_l2_2d(&map_dy, n0 + j * 64, (mb + PREFETCH_BLOCKS) * KB);
+                    }
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
             }
@@ -303,22 +318,29 @@ dw_gemm_kernel(const __grid_constant__ CUtensorMap map_dy, const uint8_t* __rest
             const int n0 = (tile / k_tiles) * TM, k0 = (tile % k_tiles) * TN;
             int b_lo, b_hi;
             slice_range(w % slices, b_lo, b_hi);
-            for (int mb = b_lo; ok && mb < b_hi; ++mb) {
-                // loads of this warp's eight (row quad, chunk) pairs first, then the arithmetic
-                uint64_t codes[8];
-                float sc[8], mnv[8];
+            // The codes, scales and minima of a stage are fetched one stage ahead of their use: the
+            // loads of block mb + 1 are in flight while block mb is decoded.
+            uint64_t codes[8], codes_next[8];
+            float sc[8], mnv[8], sc_next[8], mn_next[8];
+            auto fetch = [&](int mb, uint64_t (&cd)[8], float (&sv)[8], float (&mv)[8]) {
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     const int qd = dwarp * 8 + i, chunk = qd & 3, row = (qd >> 2) * 4 + rsub;
                     const int m = mb * KB + row, col = k0 + chunk * 64 + piece * 8;
-                    codes[i] = 0; sc[i] = 0.0f; mnv[i] = 0.0f;
-                    if (m < M && col < K) {
+                    cd[i] = 0; sv[i] = 0.0f; mv[i] = 0.0f;
+                    if (mb < b_hi && m < M && col < K) {
                         const int64_t e = (int64_t)m * K + col;
-                        codes[i] = CodePiece<BITS>::ld(packed + (e >> 3) * BITS);
-                        sc[i] = __ldg(scale + (e >> log2_gs));
-                        mnv[i] = __ldg(mn + (e >> log2_gs));
+                        cd[i] = CodePiece<BITS>::ld(packed + (e >> 3) * BITS);
+                        sv[i] = __ldg(scale + (e >> log2_gs));
+                        mv[i] = __ldg(mn + (e >> log2_gs));
                     }
                 }
+            };
+            fetch(b_lo, codes_next, sc_next, mn_next);
+            for (int mb = b_lo; ok && mb < b_hi; ++mb) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) { codes[i] = codes_next[i]; sc[i] = sc_next[i]; mnv[i] = mn_next[i]; }
+                fetch(mb + 1, codes_next, sc_next, mn_next);
                 if (ok) ok = mbar_wait_warp(&s->empty[stage], phase ^ 1, s, 2);
                 if (!ok) break;
 #pragma unroll

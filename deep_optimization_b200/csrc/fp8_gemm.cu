@@ -20,10 +20,11 @@
 // limit the kernel raises an abort flag, records an error word, drains, frees
 // its tensor memory and returns.
 //
-// B is consumed K-major ([N,K], the layout of nn.Linear weights).  A [K,N]
-// operand, the layout of the reference's Triton_Linear
-// (Activation_Compression/triton_kernel/linear.py:43-95), is transposed into the
-// caller's workspace first.
+// B may be [N,K] (K contiguous, the layout of nn.Linear weights) or [K,N], the layout of
+// the reference's Triton_Linear (Activation_Compression/triton_kernel/linear.py:43-95).
+// The CTA-pair kernel reads either in place ([K,N] as an MN-major tensor-core operand);
+// the lone-CTA kernel takes [N,K] and has a [K,N] operand transposed into the caller's
+// workspace first.
 //
 // Bound: FP8 tensor throughput; flops = 2*M*N*K.
 #include <cuda.h>
@@ -153,10 +154,11 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-// Shared-memory matrix descriptor of a K-major operand tile stored as rows of 128
-// bytes with the 128-byte swizzle (what the TMA box writes): start address >> 4,
-// stride between 8-row groups 1024 bytes, descriptor version 1, layout type 2
-// (128-byte swizzle).  The leading-dimension offset is unused for this layout.
+// Shared-memory matrix descriptor of an operand tile stored as rows of 128 bytes with the
+// 128-byte swizzle (what the TMA box writes): start address >> 4, stride between 8-row groups
+// 1024 bytes, descriptor version 1, layout type 2 (128-byte swizzle).  For a K-major tile the
+// rows are the M/N index and the leading-dimension offset is unused; the same bits describe an
+// MN-major tile of one 128-byte chunk (rows = K index), which is how a [K,N] B tile is read.
 __device__ __forceinline__ uint64_t make_kmajor_desc(const void* tile) {
     uint64_t d = 0;
     d |= (uint64_t)((smem_u32(tile) & 0x3FFFF) >> 4);
@@ -456,7 +458,7 @@ __device__ __forceinline__ bool wait_bar_warp(uint64_t* bar, uint32_t parity, S*
 __global__ void __launch_bounds__(THREADS, 1)
 fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_bt,
                      const __grid_constant__ CUtensorMap map_c,
-                     const float* __restrict__ sa, const float* __restrict__ sb, int M, int N, int K)
+                     const float* __restrict__ sa, const float* __restrict__ sb, int M, int N, int K, int b_kn)
 {
     extern __shared__ __align__(1024) uint8_t smem_raw_pair[];
     Smem* s = reinterpret_cast<Smem*>(smem_raw_pair);
@@ -498,7 +500,10 @@ fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                     if (rank == 0) mbar_expect_tx(&s->full[stage], 2 * (A_STAGE + B_STAGE));
                     const uint32_t bar = map_to_cta(smem_u32(&s->full[stage]), 0);
                     tma_load_2d_pair(s->a[stage], &map_a, bar, kb * BK, m0);
-                    tma_load_2d_pair(s->b[stage], &map_bt, bar, kb * BK, n0);
+                    // B as [N,K]: 128 rows of n, k contiguous.  B as [K,N]: 128 rows of k, n contiguous,
+                    // the same 16 KB with the roles of rows and bytes exchanged (no transposed copy)
+                    if (b_kn) tma_load_2d_pair(s->b[stage], &map_bt, bar, n0, kb * BK);
+                    else      tma_load_2d_pair(s->b[stage], &map_bt, bar, kb * BK, n0);
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
             }
@@ -512,7 +517,10 @@ fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     } else if (warp == 1) {
         // -------------------------------------------------------------- MMA issuer (leader only)
         if (lane == 0 && rank == 0) {
-            constexpr uint32_t idesc = make_idesc_pair();
+            // a [K,N] tile is an "MN-major" operand: bit 16 of the instruction descriptor, and one
+            // K step of 32 rows is 32 * 128 bytes further on instead of 32 bytes
+            const uint32_t idesc = make_idesc_pair() | (b_kn ? (1u << 16) : 0u);
+            const uint64_t b_step = b_kn ? (uint64_t)((UMMA_K * 128) >> 4) : 2ull;
             uint32_t stage = 0, phase = 0, acc_phase[2] = {0, 0};
             bool ok = true;
             int t = 0;
@@ -528,7 +536,7 @@ fp8_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                     const uint64_t bdesc = make_kmajor_desc(s->b[stage]);
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k)
-                        umma_f8_pair(d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) ? 1u : 0u);
+                        umma_f8_pair(d, adesc + 2 * k, bdesc + b_step * k, idesc, (kb | k) ? 1u : 0u);
                     umma_commit_pair(&s->empty[stage]);        // frees the slot in both CTAs
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
@@ -725,13 +733,16 @@ bool make_map(CUtensorMap* map, const void* base, int rows, int cols, int ld, in
 int round_up(int v, int m) { return (v + m - 1) / m * m; }
 
 constexpr int kMaxDevices = 64;                      // per-device host state below is indexed by ordinal
+constexpr int kForceTranspose = 1 << 30;             // internal flag: always stage a [K,N] operand through the workspace
 
 }  // namespace
 
 extern "C" size_t act_fp8_gemm_workspace(int M, int N, int K, int flags) {
-    (void)M;
     if (flags & ACT_GEMM_B_IS_NK) return 0;
     if (N <= 0 || K <= 0) return 0;
+    // more than one 128-row block: CTA pairs read a [K,N] operand in place, provided its pitch is a
+    // multiple of 16 (assumed here: ldb = N) and its base 16-byte aligned
+    if (M > act::gemm::BM && !(flags & ACT_GEMM_SINGLE_CTA) && (N & 15) == 0) return 0;
     return (size_t)N * (size_t)round_up(K, 16);
 }
 
@@ -753,7 +764,11 @@ extern "C" int act_fp8_gemm(const void* A, const void* B, const float* sa, const
 
     const uint8_t* bt = static_cast<const uint8_t*>(B);
     int ldbt = ldb;
-    if (!b_is_nk) {
+    // CTA pairs read a [K,N] operand in place when a tensor map can describe it (16-byte base and
+    // pitch); otherwise, and for the lone-CTA kernel, it is transposed into the workspace first
+    const bool pairs = !(flags & ACT_GEMM_SINGLE_CTA) && M > BM;
+    const bool b_in_place = !b_is_nk && pairs && !(flags & kForceTranspose) && !(ldb & 15) && !((uintptr_t)B & 15);
+    if (!b_is_nk && !b_in_place) {
         const size_t need = act_fp8_gemm_workspace(M, N, K, flags);
         if (!workspace || ws_bytes < need) return ACT_ERR_WORKSPACE;
         if ((uintptr_t)workspace & 15) return ACT_ERR_ALIGN;
@@ -801,7 +816,7 @@ extern "C" int act_fp8_gemm(const void* A, const void* B, const float* sa, const
     CUtensorMap map_a, map_bt, map_c;
     // A lone CTA per 128 x 256 tile when asked for, or when the problem has a single row block
     // (the second CTA of a pair would stage rows that do not exist); otherwise CTA pairs.
-    if ((flags & ACT_GEMM_SINGLE_CTA) || M <= BM) {
+    if (!pairs) {
         if (!make_map(&map_a, A, M, K, lda, BM) || !make_map(&map_bt, bt, N, K, ldbt, BN) ||
             !make_map_c(&map_c, C, M, N, ldc)) return ACT_ERR_DEVICE;
         const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
@@ -809,7 +824,8 @@ extern "C" int act_fp8_gemm(const void* A, const void* B, const float* sa, const
         fp8_gemm_kernel<<<grid, THREADS, smem_one, st>>>(map_a, map_bt, map_c, sa, sb, M, N, K);
         return cudaGetLastError() == cudaSuccess ? ACT_OK : ACT_ERR_LAUNCH;
     }
-    if (!make_map(&map_a, A, M, K, lda, pair::BM_CTA) || !make_map(&map_bt, bt, N, K, ldbt, pair::BM_CTA) ||
+    if (!make_map(&map_a, A, M, K, lda, pair::BM_CTA) ||
+        !(b_in_place ? make_map(&map_bt, B, K, N, ldb, pair::BK) : make_map(&map_bt, bt, N, K, ldbt, pair::BM_CTA)) ||
         !make_map_c_wide(&map_c, C, M, N, ldc)) return ACT_ERR_DEVICE;
     const int work = ((M + pair::TILE_M - 1) / pair::TILE_M) * ((N + pair::BN - 1) / pair::BN);
     const int clusters = work < ds.clusters ? work : ds.clusters;
@@ -822,7 +838,8 @@ extern "C" int act_fp8_gemm(const void* A, const void* B, const float* sa, const
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
-    if (cudaLaunchKernelEx(&cfg, pair::fp8_gemm_pair_kernel, map_a, map_bt, map_c, sa, sb, M, N, K) != cudaSuccess) {
+    if (cudaLaunchKernelEx(&cfg, pair::fp8_gemm_pair_kernel, map_a, map_bt, map_c, sa, sb, M, N, K,
+                           b_in_place ? 1 : 0) != cudaSuccess) {
         (void)cudaGetLastError();
         return ACT_ERR_LAUNCH;
     }
@@ -873,6 +890,7 @@ extern "C" int act_fp8_gemm_static(const void* A, const void* B, const float* sa
         scratch = static_cast<uint8_t*>(p);
         g_static_scratch_ptr[dev] = scratch;
     }
-    // B in the [K,N] layout; the shared array is the workspace of the ordinary entry point
-    return act_fp8_gemm(A, B, sa, sb, C, M, N, K, lda, ldb, ldc, 0, scratch, kStaticScratchBytes, stream);
+    // B in the [K,N] layout, always staged through the transposed copy (this entry point exists
+    // for that copy's buffer); the shared array is the workspace of the ordinary entry point
+    return act_fp8_gemm(A, B, sa, sb, C, M, N, K, lda, ldb, ldc, kForceTranspose, scratch, kStaticScratchBytes, stream);
 }

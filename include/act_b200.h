@@ -353,8 +353,10 @@ ACT_API int act_calc_precision(int32_t* b, const int32_t* C, const int32_t* w, i
  * Replaces Triton_Linear (AC/triton_kernel/linear.py:5-95), the reference's FP8-tuned
  * tiled GEMM, and adds the per-row / per-column dequantisation scales.
  *   A   [M,K] row-major, lda bytes per row (multiple of 16), 16-byte aligned
- *   B   [K,N] row-major with ldb (default, the reference's layout; needs the workspace,
- *       where it is transposed), or [N,K] with ACT_GEMM_B_IS_NK (ldb multiple of 16)
+ *   B   [K,N] row-major with ldb (default, the reference's layout), or [N,K] with
+ *       ACT_GEMM_B_IS_NK (ldb multiple of 16).  A [K,N] operand is read in place when M > 128,
+ *       ldb is a multiple of 16 and B is 16-byte aligned; otherwise it is first transposed into
+ *       the workspace (act_fp8_gemm_workspace says how much that takes for ldb = N)
  *   sa  fp32 [M], sb fp32 [N] (16-byte aligned), C bf16 [M,N] with ldc elements per row
  *   K and lda multiples of 16; N and ldc multiples of 8.
  *   workspace: act_fp8_gemm_workspace(M,N,K,flags) bytes, 16-byte aligned (may be NULL if 0).
