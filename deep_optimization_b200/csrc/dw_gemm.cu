@@ -156,48 +156,62 @@ __host__ __device__ constexpr uint32_t make_idesc() {
 }
 
 // ---------------------------------------------------------------- decoding
+// The 2^BITS possible bf16 outputs of a group, BITS <= 2: (code * scale + min) rounded once to
+// fp32 and once to bf16, as dequant_unpack_kernel does.
+template <int BITS>
+__device__ __forceinline__ void group_table(float s, float m, uint32_t& t_lo, uint32_t& t_hi) {
+    const f32x2 s2 = pack2(s, s), m2 = pack2(m, m);
+    uint32_t f0, f1, f2, f3;
+    unpack2u(fma2_rn(pack2(0.0f, 1.0f), s2, m2), f0, f1);
+    { const __nv_bfloat162 t = __floats2bfloat162_rn(__uint_as_float(f0), __uint_as_float(f1)); t_lo = *reinterpret_cast<const uint32_t*>(&t); }
+    t_hi = 0u;
+    if (BITS == 2) {
+        unpack2u(fma2_rn(pack2(2.0f, 3.0f), s2, m2), f2, f3);
+        const __nv_bfloat162 t = __floats2bfloat162_rn(__uint_as_float(f2), __uint_as_float(f3)); t_hi = *reinterpret_cast<const uint32_t*>(&t);
+    }
+}
+// eight 1- or 2-bit codes -> eight bf16 values picked out of the table, two bytes each, by byte permute
+template <int BITS>
+__device__ __forceinline__ uint4 decode8_table(uint32_t w32, uint32_t t_lo, uint32_t t_hi) {
+    uint4 out;
+    uint32_t* o = &out.x;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        uint32_t z;
+        if (BITS == 2) {
+            const uint32_t x = (w32 >> (8 * h)) & 0xFFu;
+            const uint32_t y = (x * 4097u) & 0x000F000Fu;
+            z = (y * 65u) & 0x03030303u;
+        } else {
+            const uint32_t x = (w32 >> (4 * h)) & 0xFu;
+            z = (x * 0x00204081u) & 0x01010101u;
+        }
+        const uint32_t sel = z * 0x22u + 0x10101010u;
+        o[2 * h] = __byte_perm(t_lo, t_hi, sel);
+        o[2 * h + 1] = __byte_perm(t_lo, t_hi, sel >> 16);
+    }
+    return out;
+}
 // eight b-bit codes (the low 8*BITS bits of w) of one group -> eight bf16 values = one 16-byte piece
 template <int BITS>
 __device__ __forceinline__ uint4 decode8(uint64_t w, float s, float m) {
+    if (BITS <= 2) {
+        uint32_t t_lo, t_hi;
+        group_table<BITS>(s, m, t_lo, t_hi);
+        return decode8_table<BITS>((uint32_t)w, t_lo, t_hi);
+    }
     const f32x2 s2 = pack2(s, s), m2 = pack2(m, m);
     uint4 out;
     uint32_t* o = &out.x;
-    if (BITS <= 2) {
-        // the group's table of 2^BITS outputs, then two bytes per element by byte permute
-        uint32_t f0, f1, f2, f3, t_lo, t_hi = 0u;
-        unpack2u(fma2_rn(pack2(0.0f, 1.0f), s2, m2), f0, f1);
-        { const __nv_bfloat162 t = __floats2bfloat162_rn(__uint_as_float(f0), __uint_as_float(f1)); t_lo = *reinterpret_cast<const uint32_t*>(&t); }
-        if (BITS == 2) {
-            unpack2u(fma2_rn(pack2(2.0f, 3.0f), s2, m2), f2, f3);
-            const __nv_bfloat162 t = __floats2bfloat162_rn(__uint_as_float(f2), __uint_as_float(f3)); t_hi = *reinterpret_cast<const uint32_t*>(&t);
-        }
-        const uint32_t w32 = (uint32_t)w;
+    constexpr uint64_t MASK = (1ull << BITS) - 1ull;
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            uint32_t z;
-            if (BITS == 2) {
-                const uint32_t x = (w32 >> (8 * h)) & 0xFFu;
-                const uint32_t y = (x * 4097u) & 0x000F000Fu;
-                z = (y * 65u) & 0x03030303u;
-            } else {
-                const uint32_t x = (w32 >> (4 * h)) & 0xFu;
-                z = (x * 0x00204081u) & 0x01010101u;
-            }
-            const uint32_t sel = z * 0x22u + 0x10101010u;
-            o[2 * h] = __byte_perm(t_lo, t_hi, sel);
-            o[2 * h + 1] = __byte_perm(t_lo, t_hi, sel >> 16);
-        }
-    } else {
-        constexpr uint64_t MASK = (1ull << BITS) - 1ull;
-#pragma unroll
-        for (int p = 0; p < 4; ++p) {
-            const float c0 = (float)(uint32_t)((w >> (2 * p * BITS)) & MASK);
-            const float c1 = (float)(uint32_t)((w >> ((2 * p + 1) * BITS)) & MASK);
-            uint32_t lo, hi;
-            unpack2u(fma2_rn(pack2(c0, c1), s2, m2), lo, hi);
-            const __nv_bfloat162 t = __floats2bfloat162_rn(__uint_as_float(lo), __uint_as_float(hi));
-            o[p] = *reinterpret_cast<const uint32_t*>(&t);
-        }
+    for (int p = 0; p < 4; ++p) {
+        const float c0 = (float)(uint32_t)((w >> (2 * p * BITS)) & MASK);
+        const float c1 = (float)(uint32_t)((w >> ((2 * p + 1) * BITS)) & MASK);
+        uint32_t lo, hi;
+        unpack2u(fma2_rn(pack2(c0, c1), s2, m2), lo, hi);
+        const __nv_bfloat162 t = __floats2bfloat162_rn(__uint_as_float(lo), __uint_as_float(hi));
+        o[p] = *reinterpret_cast<const uint32_t*>(&t);
     }
     return out;
 }
@@ -318,43 +332,85 @@ dw_gemm_kernel(const __grid_constant__ CUtensorMap map_dy, const uint8_t* __rest
             const int n0 = (tile / k_tiles) * TM, k0 = (tile % k_tiles) * TN;
             int b_lo, b_hi;
             slice_range(w % slices, b_lo, b_hi);
-            // The codes, scales and minima of a stage are fetched one stage ahead of their use: the
-            // loads of block mb + 1 are in flight while block mb is decoded.
-            uint64_t codes[8], codes_next[8];
-            float sc[8], mnv[8], sc_next[8], mn_next[8];
-            auto fetch = [&](int mb, uint64_t (&cd)[8], float (&sv)[8], float (&mv)[8]) {
+            // Per piece i of this thread (eight per stage: two row quads x four 64-column chunks): where
+            // its codes and its group's scale and minimum lie for the first block, advanced by a constant
+            // per block; where it goes in the stage (fixed).  Nothing in the stage loop multiplies.
+            const uint8_t* pcode[8];
+            int gidx[8];
+            uint32_t soff[8], rowi[8];
+            bool colok[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int qd = dwarp * 8 + i, chunk = qd & 3, row = (qd >> 2) * 4 + rsub;
+                const int col = k0 + chunk * 64 + piece * 8;
+                const int64_t e0 = ((int64_t)b_lo * KB + row) * K + col;
+                pcode[i] = packed + (e0 >> 3) * BITS;
+                gidx[i] = (int)(e0 >> log2_gs);
+                soff[i] = (uint32_t)(chunk * CHUNK + row * 128 + ((piece ^ (row & 7)) << 4));
+                rowi[i] = (uint32_t)row;
+                colok[i] = col < K;
+            }
+            const int code_step = KB * (K >> 3) * BITS;            // bytes of codes per 64-row block
+            const int group_step = (KB * K) >> log2_gs;            // groups per 64-row block (group_size divides K)
+            // The codes, scales and minima of a block are fetched one block ahead of their use, into
+            // two register sets that swap roles (the loop body is written out twice).
+            uint64_t cd[2][8];
+            float sv[2][8], mv[2][8];
+            auto fetch = [&](int mb, int set) {
+                const uint32_t rows_left = mb < b_hi ? (uint32_t)(M - mb * KB) : 0u;   // > 63 except in the last block of M
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
-                    const int qd = dwarp * 8 + i, chunk = qd & 3, row = (qd >> 2) * 4 + rsub;
-                    const int m = mb * KB + row, col = k0 + chunk * 64 + piece * 8;
-                    cd[i] = 0; sv[i] = 0.0f; mv[i] = 0.0f;
-                    if (mb < b_hi && m < M && col < K) {
-                        const int64_t e = (int64_t)m * K + col;
-                        cd[i] = CodePiece<BITS>::ld(packed + (e >> 3) * BITS);
-                        sv[i] = __ldg(scale + (e >> log2_gs));
-                        mv[i] = __ldg(mn + (e >> log2_gs));
+                    cd[set][i] = 0; sv[set][i] = 0.0f; mv[set][i] = 0.0f;
+                    if (colok[i] && rowi[i] < rows_left) {
+                        cd[set][i] = CodePiece<BITS>::ld(pcode[i]);
+                        sv[set][i] = __ldg(scale + gidx[i]);
+                        mv[set][i] = __ldg(mn + gidx[i]);
                     }
+                    pcode[i] += code_step;
+                    gidx[i] += group_step;
                 }
             };
-            fetch(b_lo, codes_next, sc_next, mn_next);
-            for (int mb = b_lo; ok && mb < b_hi; ++mb) {
+            auto produce = [&](int mb, int set) {
+                const uint32_t rows_left = (uint32_t)(M - mb * KB);
+                uint8_t* base = s->b[stage];
+                if (BITS <= 2 && log2_gs >= 7) {
+                    // pieces 2j and 2j+1 lie in chunks 2c and 2c+1 of one row, i.e. in one group of
+                    // 128 or more columns: one table serves both
 #pragma unroll
-                for (int i = 0; i < 8; ++i) { codes[i] = codes_next[i]; sc[i] = sc_next[i]; mnv[i] = mn_next[i]; }
-                fetch(mb + 1, codes_next, sc_next, mn_next);
-                if (ok) ok = mbar_wait_warp(&s->empty[stage], phase ^ 1, s, 2);
-                if (!ok) break;
+                    for (int i = 0; i < 8; i += 2) {
+                        uint32_t t_lo, t_hi;
+                        group_table<BITS>(sv[set][i], mv[set][i], t_lo, t_hi);
+                        const bool rows_ok = rowi[i] < rows_left;
+                        uint4 v0 = make_uint4(0u, 0u, 0u, 0u), v1 = v0;
+                        if (colok[i] && rows_ok) v0 = decode8_table<BITS>((uint32_t)cd[set][i], t_lo, t_hi);
+                        if (colok[i + 1] && rows_ok) v1 = decode8_table<BITS>((uint32_t)cd[set][i + 1], t_lo, t_hi);
+                        *reinterpret_cast<uint4*>(base + soff[i]) = v0;
+                        *reinterpret_cast<uint4*>(base + soff[i + 1]) = v1;
+                    }
+                } else {
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const int qd = dwarp * 8 + i, chunk = qd & 3, row = (qd >> 2) * 4 + rsub;
-                    const int m = mb * KB + row, col = k0 + chunk * 64 + piece * 8;
-                    uint4 v = make_uint4(0u, 0u, 0u, 0u);      // rows past M and columns past K contribute nothing
-                    if (m < M && col < K) v = decode8<BITS>(codes[i], sc[i], mnv[i]);
-                    *reinterpret_cast<uint4*>(s->b[stage] + chunk * CHUNK + row * 128 + ((piece ^ (row & 7)) << 4)) = v;
+                    for (int i = 0; i < 8; ++i) {
+                        uint4 v = make_uint4(0u, 0u, 0u, 0u);  // rows past M and columns past K contribute nothing
+                        if (colok[i] && rowi[i] < rows_left) v = decode8<BITS>(cd[set][i], sv[set][i], mv[set][i]);
+                        *reinterpret_cast<uint4*>(base + soff[i]) = v;
+                    }
                 }
                 fence_proxy_async();                           // generic-proxy stores -> visible to the tensor core's reads
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&s->full_b[stage]);
                 if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            };
+            fetch(b_lo, 0);
+            for (int mb = b_lo; ok && mb < b_hi; mb += 2) {
+                fetch(mb + 1, 1);
+                if (ok) ok = mbar_wait_warp(&s->empty[stage], phase ^ 1, s, 2);
+                if (!ok) break;
+                produce(mb, 0);
+                if (mb + 1 >= b_hi) break;
+                fetch(mb + 2, 0);
+                if (ok) ok = mbar_wait_warp(&s->empty[stage], phase ^ 1, s, 2);
+                if (!ok) break;
+                produce(mb + 1, 1);
             }
             // ---- epilogue of this work item: accumulators -> dW (fp32, summed over slices)
             if (ok) ok = mbar_wait_warp(&s->acc_full, acc_phase, s, 6);
