@@ -478,6 +478,45 @@ def run_reference_triton(steps=20, warmup=3):
     return res
 
 
+DDP_BUCKET_MB = 25
+DP_MODE = "flat"         # how the training legs average gradients over ranks; see run_train
+
+
+class FlatGradientAllReduce:
+    """Data-parallel gradient averaging with one NCCL all-reduce per step: every gradient is copied
+    into one flat fp32 buffer by a multi-tensor copy, the buffer is all-reduced (average) and
+    copied back the same way.  The views into the buffer carry each parameter's own strides, so a
+    channels-last weight gradient is copied as it lies.  Against DistributedDataParallel this
+    trades the overlap of communication with backward for two things that matter more on a step
+    of 28 ms that the host thread barely keeps ahead of: no per-parameter hook, copy and scale
+    launches on the backward path (322 small launches per ResNet-50 step), and no collective
+    holding SM slots while the codec's one-wave kernels run."""
+
+    def __init__(self, params, world):
+        import torch
+        self.params = [p for p in params if p.requires_grad]
+        self.world = world
+        n = sum(p.numel() for p in self.params)
+        self.flat = torch.zeros(n, dtype=torch.float32, device=self.params[0].device)
+        self.views, off = [], 0
+        for p in self.params:
+            # a dense parameter (contiguous in some dimension order, as a channels-last weight is)
+            # gets a view with its own strides; anything else a plain contiguous one
+            dense = p.is_contiguous() or (p.dim() == 4 and p.is_contiguous(memory_format=torch.channels_last))
+            self.views.append(self.flat.as_strided(p.size(), p.stride(), off) if dense
+                              else self.flat[off:off + p.numel()].view(p.shape))
+            off += p.numel()
+
+    def __call__(self):
+        import torch
+        import torch.distributed as dist
+        grads = [p.grad for p in self.params]
+        torch._foreach_copy_(self.views, grads)
+        dist.all_reduce(self.flat)
+        self.flat.mul_(1.0 / self.world)
+        torch._foreach_copy_(grads, self.views)
+
+
 def run_train(name, dev, world, local, steps=8, warmup=3, act=True, batch=256, channels_last=False,
               profiler=None):
     """One end-to-end configuration: `name` in (resnet50, vit_b16), ACT 2-bit on every
@@ -501,9 +540,13 @@ def run_train(name, dev, world, local, steps=8, warmup=3, act=True, batch=256, c
         net = model.train()
     if channels_last:
         net = net.to(memory_format=torch.channels_last)
-    if world > 1:
+    reduce_grads = None
+    if world > 1 and DP_MODE == "flat":
+        reduce_grads = FlatGradientAllReduce(net.parameters(), world)
+    elif world > 1:
         net = nn.parallel.DistributedDataParallel(net, device_ids=[local], static_graph=True,
-                                                  bucket_cap_mb=25, broadcast_buffers=False)
+                                                  bucket_cap_mb=DDP_BUCKET_MB, broadcast_buffers=False,
+                                                  gradient_as_bucket_view=(DP_MODE == "ddp-view"))
     if name == "resnet50":
         opt = torch.optim.SGD(net.parameters(), lr=0.1, momentum=0.9)
     else:
@@ -519,8 +562,10 @@ def run_train(name, dev, world, local, steps=8, warmup=3, act=True, batch=256, c
     def one_step():
         with torch.autocast("cuda", dtype=torch.bfloat16):
             loss = nn.functional.cross_entropy(net(x), y)
-        opt.zero_grad(set_to_none=True)
+        opt.zero_grad(set_to_none=(DP_MODE != "ddp-view"))
         loss.backward()
+        if reduce_grads is not None:
+            reduce_grads()
         opt.step()
         return loss
 
@@ -692,13 +737,20 @@ def run_ours(args):
     train = None
     if not args.no_train:
         # every rank takes part: these are the data-parallel end-to-end configurations
-        train = {"config": "batch 256 per GPU, bf16 autocast, synthetic images, ACT 2-bit via Controller",
-                 "resnet50_act2bit": run_train("resnet50", dev, world, local),
-                 "resnet50_no_act": run_train("resnet50", dev, world, local, act=False),
-                 "resnet50_act2bit_channels_last": run_train("resnet50", dev, world, local, channels_last=True),
-                 "resnet50_no_act_channels_last": run_train("resnet50", dev, world, local, act=False, channels_last=True),
-                 "vit_b16_act2bit": run_train("vit_b16", dev, world, local),
-                 "vit_b16_no_act": run_train("vit_b16", dev, world, local, act=False)}
+        legs = {"resnet50_act2bit": dict(name="resnet50"),
+                "resnet50_no_act": dict(name="resnet50", act=False),
+                "resnet50_act2bit_channels_last": dict(name="resnet50", channels_last=True),
+                "resnet50_no_act_channels_last": dict(name="resnet50", act=False, channels_last=True),
+                "vit_b16_act2bit": dict(name="vit_b16"),
+                "vit_b16_no_act": dict(name="vit_b16", act=False)}
+        train = {"config": "batch 256 per GPU, bf16 autocast, synthetic images, ACT 2-bit via Controller; "
+                           + ("one rank" if world == 1 else
+                              {"flat": "gradients averaged by one NCCL all-reduce of a flat buffer per step",
+                               "ddp": f"DistributedDataParallel, {DDP_BUCKET_MB} MB buckets",
+                               "ddp-view": f"DistributedDataParallel, {DDP_BUCKET_MB} MB buckets, gradients as bucket views"}[DP_MODE])}
+        for leg, kw in legs.items():
+            if args.legs is None or leg in args.legs:
+                train[leg] = run_train(kw.pop("name"), dev, world, local, **kw)
 
     # ---- max over ranks (per region), then the median over regions -------------------
     t = torch.tensor([region_ms, pack_region_ms, unpack_region_ms, [e2e_ms] * REGIONS], device=dev,
@@ -838,7 +890,17 @@ def main():
     ap.add_argument("--channels-last", action="store_true")
     ap.add_argument("--no-act", action="store_true")
     ap.add_argument("--rows", type=int, default=45)
+    ap.add_argument("--ddp-bucket-mb", type=int, default=None, help="gradient bucket size of the DDP training legs")
+    ap.add_argument("--dp-mode", choices=("flat", "ddp", "ddp-view"), default=None,
+                    help="gradient averaging of the training legs: one flat all-reduce per step (default), "
+                         "DistributedDataParallel, or DDP with gradients as bucket views")
+    ap.add_argument("--legs", nargs="+", default=None, help="training legs to run (default: all six)")
     args = ap.parse_args()
+    global DDP_BUCKET_MB, DP_MODE
+    if args.ddp_bucket_mb:
+        DDP_BUCKET_MB = args.ddp_bucket_mb
+    if args.dp_mode:
+        DP_MODE = args.dp_mode
     if args.only == "codec":
         args.no_extras = args.no_train = True
     elif args.only:

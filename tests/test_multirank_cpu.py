@@ -128,3 +128,41 @@ def test_sync_batch_norm_function_two_ranks_gloo():
         p.join(180)
         assert p.exitcode == 0
     assert ret.get(0) is True and ret.get(1) is True
+
+
+# ---------------------------------------------------------------- the bench's gradient averaging
+def _flat_worker(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import bench
+        torch.manual_seed(0)
+        net = torch.nn.Sequential(torch.nn.Conv2d(3, 8, 3), torch.nn.Conv2d(8, 4, 1), torch.nn.Flatten(),
+                                  torch.nn.Linear(4 * 6 * 6, 5)).to(memory_format=torch.channels_last)
+        reduce = bench.FlatGradientAllReduce(net.parameters(), world)
+        x = torch.randn(4, 3, 8, 8, generator=torch.Generator().manual_seed(10 + rank))
+        net(x).square().sum().backward()
+        mine = [p.grad.clone() for p in net.parameters()]
+        reduce()
+        ok = True
+        for p, g in zip(net.parameters(), mine):
+            both = [torch.zeros_like(g) for _ in range(world)]
+            dist.all_gather(both, g.contiguous())
+            ok = ok and torch.allclose(p.grad, sum(both) / world, atol=1e-6) and p.grad.stride() == g.stride()
+        ret[rank] = bool(ok)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_flat_gradient_all_reduce_two_ranks_gloo():
+    world = 2
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    port = 33500 + (os.getpid() % 2000)
+    procs = [ctx.Process(target=_flat_worker, args=(r, world, port, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(180)
+        assert p.exitcode == 0
+    assert ret.get(0) is True and ret.get(1) is True
