@@ -498,19 +498,28 @@ class FlatGradientAllReduce:
         self.world = world
         n = sum(p.numel() for p in self.params)
         self.flat = torch.zeros(n, dtype=torch.float32, device=self.params[0].device)
-        self.views, off = [], 0
-        for p in self.params:
-            # a dense parameter (contiguous in some dimension order, as a channels-last weight is)
-            # gets a view with its own strides; anything else a plain contiguous one
-            dense = p.is_contiguous() or (p.dim() == 4 and p.is_contiguous(memory_format=torch.channels_last))
-            self.views.append(self.flat.as_strided(p.size(), p.stride(), off) if dense
-                              else self.flat[off:off + p.numel()].view(p.shape))
-            off += p.numel()
+        self.views = None
+
+    def _make_views(self, grads):
+        # Each view has exactly the strides of the gradient it mirrors (a dense gradient is
+        # contiguous in some dimension order, as a channels-last weight gradient is; the order of
+        # size-1 dimensions differs between a 1x1 convolution's weight and its gradient): only
+        # then do the two multi-tensor copies run as one kernel each instead of one per tensor.
+        import torch
+        views, off = [], 0
+        for g in grads:
+            dense = g.is_contiguous() or (g.dim() == 4 and g.is_contiguous(memory_format=torch.channels_last))
+            views.append(self.flat.as_strided(g.size(), g.stride(), off) if dense
+                         else self.flat[off:off + g.numel()].view(g.shape))
+            off += g.numel()
+        return views
 
     def __call__(self):
         import torch
         import torch.distributed as dist
         grads = [p.grad for p in self.params]
+        if self.views is None or any(v.stride() != g.stride() for v, g in zip(self.views, grads)):
+            self.views = self._make_views(grads)
         torch._foreach_copy_(self.views, grads)
         dist.all_reduce(self.flat)
         self.flat.mul_(1.0 / self.world)
@@ -587,6 +596,21 @@ def run_train(name, dev, world, local, steps=8, warmup=3, act=True, batch=256, c
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     out = {"img_per_s": batch * world / (ms.item() * 1e-3), "ms_per_step": ms.item(),
            "peak_mem_GB": torch.cuda.max_memory_allocated(dev) / 2 ** 30, "final_loss": float(loss.detach())}
+    if reduce_grads is not None:
+        # what the step pays for the gradient exchange: the all-reduce of the flat buffer alone,
+        # and the whole exchange with its two multi-tensor copies, each timed over 5 repetitions
+        def timed(fn):
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(5):
+                fn()
+            b.record()
+            torch.cuda.synchronize()
+            return a.elapsed_time(b) / 5
+        out["gradient_bytes"] = reduce_grads.flat.numel() * 4
+        out["allreduce_ms"] = timed(lambda: dist.all_reduce(reduce_grads.flat))
+        out["gradient_exchange_ms"] = timed(reduce_grads)
     del net, opt, model
     torch.cuda.empty_cache()
     return out
