@@ -443,15 +443,22 @@ def run_dw_shapes(dev, shapes=((50432, 3072, 768), (50432, 768, 3072)), reps=10)
 
 
 def run_write_stream(dev):
-    """What a pure write stream reaches on this GPU: torch's fill kernel on outputs of the size
-    the unpack kernel (102.8 MB) and the K = 768 GEMM (309.9 MB) write, rotating buffers."""
+    """What a pure write stream reaches on this GPU: the runtime's memset (through the library's
+    act_fill_zero) on outputs of the size the unpack kernel (102.8 MB) and the K = 768 GEMM
+    (309.9 MB) write, rotating buffers; torch's fill kernel beside it (it is much slower and was
+    once mistaken here for the pace of the memory system)."""
     import torch
+    from deep_optimization_b200 import _lib
+    lib = _lib.load()
     peak, _ = load_peaks()
     out = {}
+    st = torch.cuda.current_stream(dev).cuda_stream
     for name, nbytes in (("unpack_output_102.8MB", 102_760_448), ("gemm_output_309.9MB", 309_854_208)):
-        bufs = [torch.empty(nbytes, dtype=torch.uint8, device=dev) for _ in range(3)]
-        t = _median_launch_ms(lambda i: bufs[i % 3].zero_())
-        out[name] = {"ms": t, "GBps": nbytes / t / 1e6, "frac_of_copy_peak": nbytes / t / 1e6 / peak}
+        bufs = [torch.empty(nbytes, dtype=torch.uint8, device=dev) for _ in range(4)]
+        t = _median_launch_ms(lambda i: lib.act_fill_zero(bufs[i % 4].data_ptr(), nbytes, st))
+        t_torch = _median_launch_ms(lambda i: bufs[i % 4].zero_())
+        out[name] = {"ms": t, "GBps": nbytes / t / 1e6, "frac_of_copy_peak": nbytes / t / 1e6 / peak,
+                     "torch_fill_ms": t_torch, "torch_fill_GBps": nbytes / t_torch / 1e6}
         del bufs
     torch.cuda.empty_cache()
     return out

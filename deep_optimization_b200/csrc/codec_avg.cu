@@ -185,7 +185,7 @@ dequant_unpack_avg_kernel(const uint32_t* __restrict__ packed, const float* __re
     }
 }
 
-int stream_grid_for(int64_t n_blocks_wanted, int blocks_per_sm);   // cabi.cu
+int stream_grid_for(int64_t n_blocks_wanted, int blocks_per_sm, int waves = 1);   // cabi.cu
 
 template <int DT, int MODE>
 static cudaError_t launch_pack_avg_u(const uint8_t* x, const float* noise, uint32_t* packed, float* scale, float* mn,

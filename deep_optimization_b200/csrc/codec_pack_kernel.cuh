@@ -776,7 +776,7 @@ int pack_blocks_per_sm() {
     return cached;
 }
 
-int stream_grid_for(int64_t n_blocks_wanted, int blocks_per_sm);   // cabi.cu
+int stream_grid_for(int64_t n_blocks_wanted, int blocks_per_sm, int waves = 1);   // cabi.cu
 
 template <int DT, int BITS, int NM, int L2>
 cudaError_t launch_pack_fixed(const void* x, const float* noise, void* packed, float* scale,

@@ -19,6 +19,7 @@ namespace act {
 
 constexpr int kUnpackThreads = 256;
 constexpr int kUnpackWarps = kUnpackThreads / 32;
+constexpr int kDecoderWaves = 4;          // see stream_grid_for
 
 template <int BITS> struct CodeLoad;   // the BITS bytes holding 8 consecutive codes
 template <> struct CodeLoad<1> { static __device__ __forceinline__ uint2 ld(const uint8_t* p) { return make_uint2(__ldg(p), 0u); } };
@@ -299,7 +300,7 @@ minmax_kernel(const void* __restrict__ x_, float* __restrict__ mn_out, float* __
     }
 }
 
-int stream_grid_for(int64_t n_blocks_wanted, int blocks_per_sm);   // cabi.cu
+int stream_grid_for(int64_t n_blocks_wanted, int blocks_per_sm, int waves = 1);   // cabi.cu
 
 static bool bits_ok(int bits) { return bits == 1 || bits == 2 || bits == 4 || bits == 8; }
 static bool group_ok(int gs) { return gs >= 32 && gs <= 1024 && !(gs & (gs - 1)); }
@@ -325,12 +326,12 @@ static void launch_unpack_one(const uint8_t* p, const float* s, const float* m, 
                                                               kUnpackThreads, 0) != cudaSuccess || n < 1) n = 1;
             per_sm_f32 = n;
         }
-        const int grid = stream_grid_for((tiles + kUnpackWarps - 1) / kUnpackWarps, per_sm_f32);
+        const int grid = stream_grid_for((tiles + kUnpackWarps - 1) / kUnpackWarps, per_sm_f32, kDecoderWaves);
         launch_overlapped(dequant_unpack_f32_kernel<BITS>, grid, kUnpackThreads, st,
                           reinterpret_cast<const uint32_t*>(p), s, m, reinterpret_cast<float*>(y), n_elems, log2_gs);
         return;
     }
-    const int grid = stream_grid_for((tiles + kUnpackWarps - 1) / kUnpackWarps, per_sm);
+    const int grid = stream_grid_for((tiles + kUnpackWarps - 1) / kUnpackWarps, per_sm, kDecoderWaves);
     launch_overlapped(dequant_unpack_kernel<DT, BITS, false>, grid, kUnpackThreads, st, p, s, m, y, n_elems, log2_gs,
                       UnpackTiles{0u, 0u, 1u, 1u, 3});
 }
@@ -359,7 +360,7 @@ static void launch_unpack_tiled_one(const uint8_t* p, const float* s, const floa
         per_sm = n;
     }
     const int64_t tiles = (n_elems + kTileElems - 1) / kTileElems;
-    const int grid = stream_grid_for((tiles + kUnpackWarps - 1) / kUnpackWarps, per_sm);
+    const int grid = stream_grid_for((tiles + kUnpackWarps - 1) / kUnpackWarps, per_sm, kDecoderWaves);
     launch_overlapped(dequant_unpack_kernel<DT, BITS, true>, grid, kUnpackThreads, st, p, s, m, y, n_elems, log2_gs, ta);
 }
 

@@ -149,7 +149,7 @@ act_bwd_dequant_kernel(const uint8_t* __restrict__ packed, const float* __restri
     }
 }
 
-int stream_grid_for(int64_t n_blocks_wanted, int blocks_per_sm);   // cabi.cu
+int stream_grid_for(int64_t n_blocks_wanted, int blocks_per_sm, int waves = 1);   // cabi.cu
 
 static bool dtype_ok(int d) { return d == ACT_DTYPE_F32 || d == ACT_DTYPE_BF16 || d == ACT_DTYPE_F16; }
 
@@ -164,7 +164,7 @@ extern "C" int act_relu_fwd_pack(const void* x, int dtype, int64_t n_elems, int 
     if (n_elems == 0) return ACT_OK;
     if (!x || !y || !mask_bits) return ACT_ERR_NULL;
     if (((uintptr_t)x | (uintptr_t)y) & 15 || ((uintptr_t)mask_bits & 3)) return ACT_ERR_ALIGN;
-    const int grid = stream_grid_for(((n_elems >> 3) + kFusedThreads * 4 - 1) / (kFusedThreads * 4), 6);
+    const int grid = stream_grid_for(((n_elems >> 3) + kFusedThreads * 4 - 1) / (kFusedThreads * 4), 6, 4);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const uint8_t* xi = static_cast<const uint8_t*>(x);
     uint8_t* yo = static_cast<uint8_t*>(y);
@@ -184,7 +184,7 @@ extern "C" int act_relu_bwd_unpack(const void* mask_bits, const void* dy, int dt
     if (n_elems == 0) return ACT_OK;
     if (!dy || !dx || !mask_bits) return ACT_ERR_NULL;
     if (((uintptr_t)dy | (uintptr_t)dx) & 15) return ACT_ERR_ALIGN;
-    const int grid = stream_grid_for(((n_elems >> 3) + kFusedThreads * 4 - 1) / (kFusedThreads * 4), 6);
+    const int grid = stream_grid_for(((n_elems >> 3) + kFusedThreads * 4 - 1) / (kFusedThreads * 4), 6, 4);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const uint8_t* b = static_cast<const uint8_t*>(mask_bits);
     const uint8_t* g = static_cast<const uint8_t*>(dy);
@@ -224,7 +224,7 @@ extern "C" int act_mul_dequant_unpack(const void* packed, const float* scale, co
     int log2_gs = 5;
     while ((1 << log2_gs) < group_size) ++log2_gs;
     const int64_t n = n_groups * group_size;
-    const int grid = stream_grid_for(((n >> 3) + kFusedThreads * 2 - 1) / (kFusedThreads * 2), 6);
+    const int grid = stream_grid_for(((n >> 3) + kFusedThreads * 2 - 1) / (kFusedThreads * 2), 6, 4);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const uint8_t* p = static_cast<const uint8_t*>(packed);
     const uint8_t* g = static_cast<const uint8_t*>(dy);

@@ -142,7 +142,7 @@ maxpool_bwd_cl_kernel(const uint32_t* __restrict__ idx, const uint8_t* __restric
     }
 }
 
-int stream_grid_for(int64_t n_blocks_wanted, int blocks_per_sm);   // cabi.cu
+int stream_grid_for(int64_t n_blocks_wanted, int blocks_per_sm, int waves = 1);   // cabi.cu
 
 static int pool_check(int dtype, int64_t n, int h, int w, int c, int k, int s, int pad, PoolGeom* g) {
     if (dtype != ACT_DTYPE_F32 && dtype != ACT_DTYPE_BF16 && dtype != ACT_DTYPE_F16) return ACT_ERR_DTYPE;

@@ -341,6 +341,12 @@ ACT_API int act_copy(const void* src, void* dst, size_t nbytes, size_t src_capac
              void* stream);
 
 /*
+ * Clears nbytes at p on the given stream (cudaMemsetAsync).  No counterpart in the reference:
+ * a convenience for hosts that bind this library but not the CUDA runtime.
+ */
+ACT_API int act_fill_zero(void* p, size_t nbytes, void* stream);
+
+/*
  * Greedy bit allocation on the host (no GPU work).
  * Replaces cpp_extension.calc_precision (AC/cpp_extension/src/calc_precision.cc:10-53):
  * b, C, w are int32 arrays of length n; b is updated in place until sum(b*w) <= target.
