@@ -15,6 +15,11 @@
 namespace act {
 
 constexpr int kWarp = 32;
+#ifndef ACT_DECODER_WAVES
+#define ACT_DECODER_WAVES 4
+#endif
+// Waves of resident blocks the decoding kernels are launched with (see stream_grid_for in cabi.cu).
+constexpr int kDecoderWaves = ACT_DECODER_WAVES;
 constexpr int kTileElems = 1024;          // elements one warp handles per iteration
 constexpr uint32_t kMagicBits = 0x4B000000u;   // bit pattern of 2^23
 constexpr float kMagic = 8388608.0f;           // 2^23

@@ -19,7 +19,6 @@ namespace act {
 
 constexpr int kUnpackThreads = 256;
 constexpr int kUnpackWarps = kUnpackThreads / 32;
-constexpr int kDecoderWaves = 4;          // see stream_grid_for
 
 template <int BITS> struct CodeLoad;   // the BITS bytes holding 8 consecutive codes
 template <> struct CodeLoad<1> { static __device__ __forceinline__ uint2 ld(const uint8_t* p) { return make_uint2(__ldg(p), 0u); } };

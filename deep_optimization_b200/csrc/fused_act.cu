@@ -164,7 +164,7 @@ extern "C" int act_relu_fwd_pack(const void* x, int dtype, int64_t n_elems, int 
     if (n_elems == 0) return ACT_OK;
     if (!x || !y || !mask_bits) return ACT_ERR_NULL;
     if (((uintptr_t)x | (uintptr_t)y) & 15 || ((uintptr_t)mask_bits & 3)) return ACT_ERR_ALIGN;
-    const int grid = stream_grid_for(((n_elems >> 3) + kFusedThreads * 4 - 1) / (kFusedThreads * 4), 6, 4);
+    const int grid = stream_grid_for(((n_elems >> 3) + kFusedThreads * 4 - 1) / (kFusedThreads * 4), 6, kDecoderWaves);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const uint8_t* xi = static_cast<const uint8_t*>(x);
     uint8_t* yo = static_cast<uint8_t*>(y);
@@ -184,7 +184,7 @@ extern "C" int act_relu_bwd_unpack(const void* mask_bits, const void* dy, int dt
     if (n_elems == 0) return ACT_OK;
     if (!dy || !dx || !mask_bits) return ACT_ERR_NULL;
     if (((uintptr_t)dy | (uintptr_t)dx) & 15) return ACT_ERR_ALIGN;
-    const int grid = stream_grid_for(((n_elems >> 3) + kFusedThreads * 4 - 1) / (kFusedThreads * 4), 6, 4);
+    const int grid = stream_grid_for(((n_elems >> 3) + kFusedThreads * 4 - 1) / (kFusedThreads * 4), 6, kDecoderWaves);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const uint8_t* b = static_cast<const uint8_t*>(mask_bits);
     const uint8_t* g = static_cast<const uint8_t*>(dy);
@@ -224,7 +224,7 @@ extern "C" int act_mul_dequant_unpack(const void* packed, const float* scale, co
     int log2_gs = 5;
     while ((1 << log2_gs) < group_size) ++log2_gs;
     const int64_t n = n_groups * group_size;
-    const int grid = stream_grid_for(((n >> 3) + kFusedThreads * 2 - 1) / (kFusedThreads * 2), 6, 4);
+    const int grid = stream_grid_for(((n >> 3) + kFusedThreads * 2 - 1) / (kFusedThreads * 2), 6, kDecoderWaves);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const uint8_t* p = static_cast<const uint8_t*>(packed);
     const uint8_t* g = static_cast<const uint8_t*>(dy);
@@ -297,18 +297,16 @@ bn_bwd_dx_kernel(const uint8_t* __restrict__ packed, const float* __restrict__ s
     const int64_t stride = (int64_t)gridDim.x * kFusedThreads;
     int64_t p = (int64_t)blockIdx.x * kFusedThreads + threadIdx.x;
     if (p >= n_pieces) return;
-    PlaneWalk walk;
-    walk.init(p * 8, stride * 8, hw, C);
-    for (; p < n_pieces; p += stride, walk.advance()) {
-        const Vec8<DT> v = load8<DT>(dy, p * 8);
-        const uint2 w = load_codes8<BITS>(packed, p);
-        const int64_t g = (p * 8) >> log2_gs;
-        const float s = __ldg(scale + g), m = __ldg(mn + g);
-        const float4 k0 = __ldg(coef + walk.c), k1 = __ldg(coef + walk.channel_at(4));
+    // two pieces per trip (p and p + stride), the loads of both issued before either is used:
+    // with one piece per trip the kernel waited on its loads (13 stall cycles per issue on the
+    // long scoreboard); each piece has its own walker, stepping two strides at a time
+    PlaneWalk walk0, walk1;
+    walk0.init(p * 8, stride * 16, hw, C);
+    walk1.init((p + stride) * 8, stride * 16, hw, C);
+    auto finish = [&](int64_t q, const Vec8<DT>& v, uint2 w, float s, float m, uint32_t keep, float4 k0, float4 k1) {
         float f[8];
         to_float8<DT>(v, f);
         if (mask) {                                   // fused ReLU: dy counts only where y was positive
-            const uint32_t keep = __ldg(mask + p);
 #pragma unroll
             for (int i = 0; i < 8; ++i) f[i] = ((keep >> i) & 1u) ? f[i] : 0.0f;
         }
@@ -317,7 +315,21 @@ bn_bwd_dx_kernel(const uint8_t* __restrict__ packed, const float* __restrict__ s
             const float4 k = i < 4 ? k0 : k1;
             f[i] = __fmaf_rn(-k.z, decode_at<BITS>(w, i, s, m), __fmaf_rn(k.x, f[i], -k.y));
         }
-        store8<DT>(dx, p * 8, f);
+        store8<DT>(dx, q * 8, f);
+    };
+    for (; p < n_pieces; p += 2 * stride, walk0.advance(), walk1.advance()) {
+        const int64_t p1 = p + stride;
+        const bool two = p1 < n_pieces;
+        const int64_t q1 = two ? p1 : p;
+        const Vec8<DT> v0 = load8<DT>(dy, p * 8), v1 = load8<DT>(dy, q1 * 8);
+        const uint2 w0 = load_codes8<BITS>(packed, p), w1 = load_codes8<BITS>(packed, q1);
+        const int64_t g0 = (p * 8) >> log2_gs, g1 = (q1 * 8) >> log2_gs;
+        const float s0 = __ldg(scale + g0), m0 = __ldg(mn + g0), s1 = __ldg(scale + g1), m1 = __ldg(mn + g1);
+        const float4 a0 = __ldg(coef + walk0.c), a1 = __ldg(coef + walk0.channel_at(4));
+        const float4 b0 = __ldg(coef + (two ? walk1.c : walk0.c)), b1 = __ldg(coef + (two ? walk1.channel_at(4) : walk0.c));
+        const uint32_t keep0 = mask ? __ldg(mask + p) : 0xFFu, keep1 = mask ? __ldg(mask + q1) : 0xFFu;
+        finish(p, v0, w0, s0, m0, keep0, a0, a1);
+        if (two) finish(p1, v1, w1, s1, m1, keep1, b0, b1);
     }
 }
 
