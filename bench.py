@@ -866,8 +866,8 @@ def run_only(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if args.only == "gemm":
-        M, K, N = args.shape
-        print(json.dumps(run_gemm_shapes(dev, ((M, K, N),), reps=args.reps)), flush=True)
+        shapes = (tuple(args.shape),) if args.shape else GEMM_SHAPES      # M K N; default: all evaluation shapes
+        print(json.dumps(run_gemm_shapes(dev, shapes, reps=args.reps)), flush=True)
     elif args.only == "dw":
         M, N, K = args.shape
         print(json.dumps(run_dw_shapes(dev, ((M, N, K),), reps=args.reps)), flush=True)
