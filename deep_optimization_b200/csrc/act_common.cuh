@@ -78,6 +78,13 @@ __device__ __forceinline__ float fmin_nan(float a, float b) {
 __device__ __forceinline__ float fmax_nan(float a, float b) {
     float d; asm("max.NaN.f32 %0, %1, %2;" : "=f"(d) : "f"(a), "f"(b)); return d;
 }
+// three inputs in one instruction (sm_100)
+__device__ __forceinline__ float fmin3_nan(float a, float b, float c) {
+    float d; asm("min.NaN.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c)); return d;
+}
+__device__ __forceinline__ float fmax3_nan(float a, float b, float c) {
+    float d; asm("max.NaN.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c)); return d;
+}
 
 // Host side: splitmix64 finaliser; the hash key is hash_key(hash_key(seed) + offset).
 __host__ __device__ inline uint64_t hash_key(uint64_t seed) {

@@ -487,7 +487,10 @@ quant_pack_kernel(const void* __restrict__ x_, const float* __restrict__ noise,
         constexpr bool FIXED = (NM == kNoiseHash || NM == kNoiseConst);      // the fixed-point modes
         constexpr bool RAW16 = (ElemT<DT>::bytes == 2 && FIXED && PRO == kProNone);
         float xf[32];
-        if (!RAW16) widen_raw<DT>(raw_cur, xf);
+        // the batch-norm producers subtract the mean straight from the 16-bit halves (one
+        // mixed-precision subtraction, the same single rounding as widening first)
+        constexpr bool BN_RAW16 = (ElemT<DT>::bytes == 2) && (PRO == kProBN || PRO == kProBNRelu || PRO == kProBNcl || PRO == kProBNReluCl || PRO == kProBNAddRelu || PRO == kProBNAddReluCl);
+        if (!RAW16 && !BN_RAW16) widen_raw<DT>(raw_cur, xf);
 
         // next tile's loads go out before this tile's arithmetic
         if (!TAIL) {
@@ -542,8 +545,10 @@ quant_pack_kernel(const void* __restrict__ x_, const float* __restrict__ noise,
 #pragma unroll
                     for (int i = 0; i < 8; i += 2) {
                         const int e = k * 8 + i;
-                        const f32x2 xh2 = mul2_rn(add2_rn(pack2(xf[e], xf[e + 1]), pack2(-p[i].x, -p[i + 1].x)),
-                                                  pack2(p[i].y, p[i + 1].y));                  // x_hat
+                        const uint32_t rw = BN_RAW16 ? (i < 4 ? (i < 2 ? raw_cur.v[k & 3].x : raw_cur.v[k & 3].y) : (i < 6 ? raw_cur.v[k & 3].z : raw_cur.v[k & 3].w)) : 0u;
+                        const f32x2 d2 = BN_RAW16 ? pack2(sub_from_half<DT>(rw, 0, p[i].x), sub_from_half<DT>(rw, 1, p[i + 1].x))
+                                                  : add2_rn(pack2(xf[e], xf[e + 1]), pack2(-p[i].x, -p[i + 1].x));
+                        const f32x2 xh2 = mul2_rn(d2, pack2(p[i].y, p[i + 1].y));                  // x_hat
                         uint32_t a0, a1, c0, c1;
                         unpack2u(xh2, a0, a1);
                         unpack2u(mul2_rn(xh2, pack2(p[i].z, p[i + 1].z)), c0, c1);
@@ -570,7 +575,11 @@ quant_pack_kernel(const void* __restrict__ x_, const float* __restrict__ noise,
 #pragma unroll
                         for (int i = 0; i < 4; i += 2) {
                             const int e = k * 8 + h * 4 + i;
-                            const f32x2 xh2 = mul2_rn(add2_rn(pack2(xf[e], xf[e + 1]), nmean2), inv2);   // x_hat
+                            const int ii = h * 4 + i;
+                            const uint32_t rw = BN_RAW16 ? (ii < 4 ? (ii < 2 ? raw_cur.v[k & 3].x : raw_cur.v[k & 3].y) : (ii < 6 ? raw_cur.v[k & 3].z : raw_cur.v[k & 3].w)) : 0u;
+                            const f32x2 d2 = BN_RAW16 ? pack2(sub_from_half<DT>(rw, 0, p.x), sub_from_half<DT>(rw, 1, p.x))
+                                                      : add2_rn(pack2(xf[e], xf[e + 1]), nmean2);
+                            const f32x2 xh2 = mul2_rn(d2, inv2);   // x_hat
                             // affine: the product on the pair, the add as two scalar adds (a packed
                             // multiply followed by a packed add gets fused into one FMA by ptxas,
                             // which would drop the rounding of the product)
@@ -604,10 +613,11 @@ quant_pack_kernel(const void* __restrict__ x_, const float* __restrict__ noise,
                 if (BN_RELU) {
                     uint32_t bits8 = 0;
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const bool on = yv[i] > 0.0f;
-                        bits8 |= (on ? 1u : 0u) << i;
-                        yv[i] = on ? yv[i] : 0.0f;
+                    for (int i = 7; i >= 0; --i) {
+                        // max(y, +0) is +0 for y <= 0, -0 and NaN; any other result carries into bit 31
+                        // of the sum, which the funnel shift moves into the mask (element 0 ends at bit 0)
+                        yv[i] = fmaxf(yv[i], 0.0f);
+                        bits8 = __funnelshift_l(__float_as_uint(yv[i]) + 0x7FFFFFFFu, bits8, 1);
                     }
                     if (valid) bn.mask[(group_e0 >> 3) + ((k << log2_L) + j)] = (uint8_t)bits8;
                 }
@@ -649,7 +659,8 @@ quant_pack_kernel(const void* __restrict__ x_, const float* __restrict__ noise,
         } else {
             mn = xf[0]; mx = xf[0];
 #pragma unroll
-            for (int i = 1; i < 32; ++i) { mn = fmin_nan(mn, xf[i]); mx = fmax_nan(mx, xf[i]); }
+            for (int i = 1; i < 31; i += 2) { mn = fmin3_nan(mn, xf[i], xf[i + 1]); mx = fmax3_nan(mx, xf[i], xf[i + 1]); }
+            mn = fmin_nan(mn, xf[31]); mx = fmax_nan(mx, xf[31]);
         }
         for (int off = L >> 1; off > 0; off >>= 1) {
             mn = fmin_nan(mn, __shfl_xor_sync(0xffffffffu, mn, off));
