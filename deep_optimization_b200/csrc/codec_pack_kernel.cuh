@@ -43,8 +43,14 @@ enum NoiseMode { kNoiseHash = 0, kNoiseTensor = 1, kNoiseConst = 2, kRefCompat =
 #ifndef ACT_PACK_MIN_BLOCKS
 #define ACT_PACK_MIN_BLOCKS 2
 #endif
-template <int DT> struct PackCfg {
-    static constexpr int threads = (ElemT<DT>::bytes == 4) ? 256 : ACT_PACK_THREADS;
+// The batch-norm producers (PRO 3..8 of enum Producer below) hold more live state than the plain
+// codec: at 384 threads x 2 blocks (80 registers) they spill.  256 threads x 2 blocks (128
+// registers, 16 warps per SM) runs BN+ReLU on bf16 [256,64,56,56] in 50 us against 57.7; the
+// channel-minor producer with the residual add, which has two input streams to keep in flight,
+// is fastest at 320 x 2 (68 us against 72 at 256 and 75 at 384).
+template <int DT, int PRO = 0> struct PackCfg {
+    static constexpr bool bn = (PRO >= 3 && PRO <= 8);
+    static constexpr int threads = (ElemT<DT>::bytes == 4) ? 256 : (bn ? (PRO == 8 ? 320 : 256) : ACT_PACK_THREADS);
     static constexpr int min_blocks = (ElemT<DT>::bytes == 4) ? 2 : ACT_PACK_MIN_BLOCKS;
     static constexpr int warps = threads / 32;
 };
@@ -328,8 +334,9 @@ enum Producer { kProNone = 0, kProGelu = 1, kProSilu = 2, kProBN = 3, kProBNRelu
 
 // Per-channel inputs of the batch-norm producer: x is [N, C, HW] contiguous and
 // params[c] = (mean, invstd, weight, bias).  The channel of element e is (e / HW) % C;
-// inside a lane's group it is found with two exact multiply-high divisions, which the
-// host enables only when HW*(HW+1024) < 2^32 and C*(C+260) < 2^32.
+// inside a lane's group it is found with two exact multiply-high divisions (magic = 0 stands
+// for a divisor of 1: the quotient is the dividend), which the host enables only when
+// HW*(HW+1024) < 2^32 and C*(C+260) < 2^32.
 // kProBNRelu also applies y = max(y, 0) and writes one mask bit per element (bit i of byte
 // e/8 = element e, the layout of relu_fwd_pack) to `mask`.
 // kProBNcl / kProBNReluCl are the same producers for the channel-minor layout (HW = 1, x is
@@ -389,7 +396,7 @@ __device__ __forceinline__ void act_and_derivative(float x, float& y, float& d) 
 // instantiation: addresses, strides and the shuffle loop then fold to constants); L2 = -1
 // takes it from the argument.
 template <int DT, int BITS, int NM, int PRO = kProNone, int L2 = -1, bool TILED = false>
-__global__ void __launch_bounds__(PackCfg<DT>::threads, PackCfg<DT>::min_blocks)
+__global__ void __launch_bounds__(PackCfg<DT, PRO>::threads, PackCfg<DT, PRO>::min_blocks)
 quant_pack_kernel(const void* __restrict__ x_, const float* __restrict__ noise,
                   uint8_t* __restrict__ packed, float* __restrict__ scale_out,
                   float* __restrict__ min_out, int64_t n_elems, int log2_L_arg,
@@ -400,7 +407,7 @@ quant_pack_kernel(const void* __restrict__ x_, const float* __restrict__ noise,
     static_assert(!TILED || PRO == kProNone, "tiled addressing is built for the plain codec only");
     constexpr int QMAX = (1 << BITS) - 1;
     constexpr int TILE_OUT = kTileElems * BITS / 8;          // packed bytes per tile
-    constexpr int kPackWarps = PackCfg<DT>::warps;
+    constexpr int kPackWarps = PackCfg<DT, PRO>::warps;
     __shared__ __align__(16) uint8_t stage[kPackWarps][TILE_OUT];
 
     const int lane = threadIdx.x & 31;
@@ -469,11 +476,44 @@ quant_pack_kernel(const void* __restrict__ x_, const float* __restrict__ noise,
     extern __shared__ __align__(16) uint8_t dyn_smem[];
     float4* const s_table = reinterpret_cast<float4*>(dyn_smem);
     if (PRO == kProBNcl || PRO == kProBNReluCl || PRO == kProBNAddReluCl) {
-        for (uint32_t c = threadIdx.x; c < bn.c; c += PackCfg<DT>::threads)
+        for (uint32_t c = threadIdx.x; c < bn.c; c += PackCfg<DT, PRO>::threads)
             s_table[(c >> 3) * 9u + (c & 7u)] = __ldg(bn.params + c);
         __syncthreads();
     }
     if (tile < n_full) load_tile(raw_a, tile);
+
+    // batch norm: where the lane's group starts, as (offset inside its plane, channel) for the
+    // plane layout or as its channel alone for the channel-minor layout.  Found with 64-bit
+    // divisions once per thread and then advanced tile by tile with additions: a tile step is
+    // the same number of elements every time.
+    constexpr bool BN_CL = (PRO == kProBNcl || PRO == kProBNReluCl || PRO == kProBNAddReluCl);
+    constexpr bool BN_ADD = (PRO == kProBNAddRelu || PRO == kProBNAddReluCl);
+    constexpr bool BN_RELU = (PRO == kProBNRelu || PRO == kProBNReluCl || BN_ADD);
+    constexpr bool IS_BN = (PRO == kProBN || PRO == kProBNRelu || BN_CL || BN_ADD);
+    uint32_t bn_c0 = 0, bn_r0 = 0, bn_dc = 0, bn_dr = 0;
+    if (IS_BN) {
+        const uint64_t e0 = (uint64_t)tile * kTileElems + (uint64_t)lane_e0;
+        const uint64_t step = (uint64_t)warp_stride * kTileElems;
+        if (BN_CL) {
+            bn_c0 = (uint32_t)(e0 % bn.c);
+            bn_dc = (uint32_t)(step % bn.c);
+        } else {
+            const uint64_t plane = e0 / bn.hw, step_planes = step / bn.hw;
+            bn_r0 = (uint32_t)(e0 - plane * bn.hw);
+            bn_c0 = (uint32_t)(plane % bn.c);
+            bn_dr = (uint32_t)(step - step_planes * bn.hw);
+            bn_dc = (uint32_t)(step_planes % bn.c);
+        }
+    }
+    auto bn_advance = [&]() {
+        if (!IS_BN) return;
+        bn_c0 += bn_dc;
+        if (!BN_CL) {
+            bn_r0 += bn_dr;
+            if (bn_r0 >= bn.hw) { bn_r0 -= bn.hw; ++bn_c0; }
+        }
+        if (bn_c0 >= bn.c) bn_c0 -= bn.c;
+    };
 
     // raw_cur holds this tile, raw_next receives the following one while this one is encoded
     auto run_tile = [&](auto tail_tag, const RawTile<DT>& raw_cur, RawTile<DT>& raw_next) {
@@ -489,7 +529,7 @@ quant_pack_kernel(const void* __restrict__ x_, const float* __restrict__ noise,
         float xf[32];
         // the batch-norm producers subtract the mean straight from the 16-bit halves (one
         // mixed-precision subtraction, the same single rounding as widening first)
-        constexpr bool BN_RAW16 = (ElemT<DT>::bytes == 2) && (PRO == kProBN || PRO == kProBNRelu || PRO == kProBNcl || PRO == kProBNReluCl || PRO == kProBNAddRelu || PRO == kProBNAddReluCl);
+        constexpr bool BN_RAW16 = (ElemT<DT>::bytes == 2) && IS_BN;
         if (!RAW16 && !BN_RAW16) widen_raw<DT>(raw_cur, xf);
 
         // next tile's loads go out before this tile's arithmetic
@@ -498,11 +538,6 @@ quant_pack_kernel(const void* __restrict__ x_, const float* __restrict__ noise,
             if (next_tile < n_full) load_tile(raw_next, next_tile);
         }
 
-        // batch norm: plane index and offset inside the plane of the lane's group
-        constexpr bool BN_CL = (PRO == kProBNcl || PRO == kProBNReluCl || PRO == kProBNAddReluCl);
-        constexpr bool BN_ADD = (PRO == kProBNAddRelu || PRO == kProBNAddReluCl);
-        constexpr bool BN_RELU = (PRO == kProBNRelu || PRO == kProBNReluCl || BN_ADD);
-        constexpr bool IS_BN = (PRO == kProBN || PRO == kProBNRelu || BN_CL || BN_ADD);
         // the residual's pieces, at the addresses of the x pieces they are added to
         RawTile<DT> res;
         if (BN_ADD) {
@@ -521,14 +556,6 @@ quant_pack_kernel(const void* __restrict__ x_, const float* __restrict__ noise,
                 zero_raw<DT>(res);
             }
         }
-        uint32_t bn_c0 = 0, bn_r0 = 0;
-        if (BN_CL) {
-            bn_c0 = (uint32_t)((uint64_t)group_e0 % bn.c);               // channel of the group's first element
-        } else if (IS_BN) {
-            const uint64_t plane = (uint64_t)group_e0 / bn.hw;
-            bn_r0 = (uint32_t)((uint64_t)group_e0 - plane * bn.hw);
-            bn_c0 = (uint32_t)(plane % bn.c);
-        }
         if (PRO != kProNone) {
             // fused producer: emit y, keep what backward needs (derivative or x_hat) for the codec
 #pragma unroll
@@ -537,7 +564,7 @@ quant_pack_kernel(const void* __restrict__ x_, const float* __restrict__ noise,
                 if (BN_CL) {
                     // channel-minor: element i of the piece is channel cc + i (no wrap inside a piece)
                     uint32_t cc = bn_c0 + (uint32_t)(((k << log2_L) + j) * 8);
-                    cc -= (bn.magic_c ? __umulhi(cc, bn.magic_c) : cc / bn.c) * bn.c;
+                    cc -= (bn.magic_c ? __umulhi(cc, bn.magic_c) : cc) * bn.c;
                     float4 p[8];
                     const float4* row = s_table + (cc >> 3) * 9u;
 #pragma unroll
@@ -565,9 +592,9 @@ quant_pack_kernel(const void* __restrict__ x_, const float* __restrict__ noise,
                     for (int h = 0; h < 2; ++h) {
                         if (h == 0 || !one_channel) {
                             const uint32_t t = bn_r0 + (uint32_t)(((k << log2_L) + j) * 8 + h * 4);
-                            const uint32_t q = bn.magic_hw ? __umulhi(t, bn.magic_hw) : t / bn.hw;
+                            const uint32_t q = bn.magic_hw ? __umulhi(t, bn.magic_hw) : t;
                             uint32_t cc = bn_c0 + q;
-                            cc -= (bn.magic_c ? __umulhi(cc, bn.magic_c) : cc / bn.c) * bn.c;
+                            cc -= (bn.magic_c ? __umulhi(cc, bn.magic_c) : cc) * bn.c;
                             p = __ldg(bn.params + cc);
                         }
                         const f32x2 nmean2 = pack2(-p.x, -p.x), inv2 = pack2(p.y, p.y);
@@ -762,10 +789,10 @@ quant_pack_kernel(const void* __restrict__ x_, const float* __restrict__ noise,
     // two tiles per trip, the raw buffers swapping roles, so that no register copies are needed
     while (tile < n_full) {
         run_tile(std::false_type{}, raw_a, raw_b);
-        tile += warp_stride;
+        tile += warp_stride; bn_advance();
         if (tile >= n_full) break;
         run_tile(std::false_type{}, raw_b, raw_a);
-        tile += warp_stride;
+        tile += warp_stride; bn_advance();
     }
     if (has_tail && tile == n_full) {
         if (tile * kTileElems + lane_e0 < n_elems) load_tile(raw_a, tile); else zero_raw<DT>(raw_a);
@@ -897,13 +924,13 @@ cudaError_t launch_fused_one(const void* x, void* y, void* packed, float* scale,
     if (per_sm == 0) {
         int n = 0;
         if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, quant_pack_kernel<DT, BITS, NM, PRO>,
-                                                          PackCfg<DT>::threads, 0) != cudaSuccess || n < 1) n = 1;
+                                                          PackCfg<DT, PRO>::threads, 0) != cudaSuccess || n < 1) n = 1;
         per_sm = n;
     }
     const uint64_t key = hash_key(hash_key(seed) + offset);
     const int64_t n_tiles = (n_elems + kTileElems - 1) / kTileElems;
-    const int grid = stream_grid_for((n_tiles + PackCfg<DT>::warps - 1) / PackCfg<DT>::warps, per_sm);
-    return launch_overlapped(quant_pack_kernel<DT, BITS, NM, PRO>, grid, PackCfg<DT>::threads, st,
+    const int grid = stream_grid_for((n_tiles + PackCfg<DT, PRO>::warps - 1) / PackCfg<DT, PRO>::warps, per_sm);
+    return launch_overlapped(quant_pack_kernel<DT, BITS, NM, PRO>, grid, PackCfg<DT, PRO>::threads, st,
                              x, static_cast<const float*>(nullptr), static_cast<uint8_t*>(packed), scale, mn,
                              n_elems, log2_L, (uint32_t)key, (uint32_t)(key >> 32), 0, 0.0f,
                              static_cast<uint8_t*>(y), BNArgs{nullptr, 1u, 1u, 0u, 0u, nullptr, nullptr}, TileArgs{0u, 0u, 1u, 1u, 3});
@@ -958,15 +985,15 @@ cudaError_t launch_bn_one(const void* x, void* y, void* packed, float* scale, fl
         int n = 0;
         if (CL) cudaFuncSetAttribute(quant_pack_kernel<DT, BITS, NM, PRO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxTable);
         if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, quant_pack_kernel<DT, BITS, NM, PRO>,
-                                                          PackCfg<DT>::threads, CL ? kMaxTable : 0) != cudaSuccess || n < 1) n = 1;
+                                                          PackCfg<DT, PRO>::threads, CL ? kMaxTable : 0) != cudaSuccess || n < 1) n = 1;
         per_sm = n;
     }
     const uint64_t key = hash_key(hash_key(seed) + offset);
     const int64_t n_tiles = (n_elems + kTileElems - 1) / kTileElems;
-    const int grid = stream_grid_for((n_tiles + PackCfg<DT>::warps - 1) / PackCfg<DT>::warps, per_sm);
+    const int grid = stream_grid_for((n_tiles + PackCfg<DT, PRO>::warps - 1) / PackCfg<DT, PRO>::warps, per_sm);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid, 1, 1);
-    cfg.blockDim = dim3((unsigned)PackCfg<DT>::threads, 1, 1);
+    cfg.blockDim = dim3((unsigned)PackCfg<DT, PRO>::threads, 1, 1);
     cfg.dynamicSmemBytes = CL ? (size_t)(bn.c / 8u) * 144 : 0;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
