@@ -7,14 +7,15 @@
 // Reference: the author's Triton attempt at the same fusion ran at 0.06-0.17x of
 // dequantise + cuBLAS (Activation_Compression/test2.ipynb:14-19, 478-491).
 //
-// One CTA per (256 x 256 output tile, slice of M); 320 threads:
+// One CTA per (256 x 256 output tile, slice of M); 576 threads:
 //   warp 0       TMA producer: 64 rows of dY x 256 columns per stage, as four 64 x 64 boxes with
 //                the 128-byte swizzle.  dY is row-major [M, N], so the tile lands with the
 //                output dimension n contiguous: the "MN-major" operand form of tcgen05.mma.
 //   warp 1       MMA issuer: per stage 2 x 4 tcgen05.mma.kind::f16 (bf16, M = 128, N = 256,
 //                K = 16), both operands MN-major, two 128 x 256 fp32 accumulators = all 512
 //                columns of tensor memory.
-//   warps 2..9   decoders: read the codes of 64 rows x 256 columns (2 bytes per 8 two-bit
+//   warps 2..17  decoders (four per scheduler: with eight, 244 us instead of 208 on the ViT MLP
+//                shapes): read the codes of 64 rows x 256 columns (2 bytes per 8 two-bit
 //                codes), look the two bytes of every bf16 value up in the group's table of 2^b
 //                outputs with a byte permute (the arithmetic of dequant_unpack_kernel), and
 //                store 16-byte pieces into the same swizzled MN-major layout a bulk tensor copy
@@ -44,8 +45,14 @@ constexpr int STAGES = 3;
 constexpr int PREFETCH_BLOCKS = ACT_DW_PREFETCH_BLOCKS;   // distance of the L2 prefetch of dY, in 64-row blocks (0: off)
 constexpr int A_STAGE = KB * TM * 2, B_STAGE = KB * TN * 2;      // 32 KB each
 constexpr int CHUNK = KB * 128;           // one 64-column chunk of a stage: 64 rows x 128 bytes
-constexpr int DEC_WARPS = 8;
+#ifndef ACT_DW_DEC_WARPS
+#define ACT_DW_DEC_WARPS 16
+#endif
+constexpr int DEC_WARPS = ACT_DW_DEC_WARPS;                // 8 or 16 (a multiple of four: the epilogue's TMEM lane quarters)
+constexpr int PIECES = (KB * TN / 8) / (DEC_WARPS * 32);  // 16-byte pieces of a stage per decoder thread
+constexpr int EPI_COLS = TN / (DEC_WARPS / 4);            // accumulator columns per warp in the epilogue
 constexpr int THREADS = 64 + DEC_WARPS * 32;
+static_assert(DEC_WARPS % 4 == 0 && PIECES >= 2 && PIECES % 2 == 0 && EPI_COLS % 32 == 0, "decoder split");
 constexpr int TMEM_COLS = 512;
 constexpr uint32_t SPIN_LIMIT = 1u << 24;
 
@@ -324,7 +331,7 @@ dw_gemm_kernel(const __grid_constant__ CUtensorMap map_dy, const uint8_t* __rest
         const int dwarp = warp - 2;
         const int piece = lane & 7, rsub = lane >> 3;          // 8 lanes = one 128-byte row of a chunk; 4 rows per warp
         const int q = warp & 3;                                // TMEM lane quarter for the epilogue
-        const int half_cols = dwarp >> 2;                      // which 128 columns of a tile in the epilogue
+        const int col_part = dwarp >> 2;                       // which EPI_COLS columns of a tile in the epilogue
         uint32_t stage = 0, phase = 0, acc_phase = 0;
         bool ok = true;
         for (int w = blockIdx.x; w < n_work; w += gridDim.x) {
@@ -335,13 +342,13 @@ dw_gemm_kernel(const __grid_constant__ CUtensorMap map_dy, const uint8_t* __rest
             // Per piece i of this thread (eight per stage: two row quads x four 64-column chunks): where
             // its codes and its group's scale and minimum lie for the first block, advanced by a constant
             // per block; where it goes in the stage (fixed).  Nothing in the stage loop multiplies.
-            const uint8_t* pcode[8];
-            int gidx[8];
-            uint32_t soff[8], rowi[8];
-            bool colok[8];
+            const uint8_t* pcode[PIECES];
+            int gidx[PIECES];
+            uint32_t soff[PIECES], rowi[PIECES];
+            bool colok[PIECES];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const int qd = dwarp * 8 + i, chunk = qd & 3, row = (qd >> 2) * 4 + rsub;
+            for (int i = 0; i < PIECES; ++i) {
+                const int qd = dwarp * PIECES + i, chunk = qd & 3, row = (qd >> 2) * 4 + rsub;
                 const int col = k0 + chunk * 64 + piece * 8;
                 const int64_t e0 = ((int64_t)b_lo * KB + row) * K + col;
                 pcode[i] = packed + (e0 >> 3) * BITS;
@@ -354,12 +361,12 @@ dw_gemm_kernel(const __grid_constant__ CUtensorMap map_dy, const uint8_t* __rest
             const int group_step = (KB * K) >> log2_gs;            // groups per 64-row block (group_size divides K)
             // The codes, scales and minima of a block are fetched one block ahead of their use, into
             // two register sets that swap roles (the loop body is written out twice).
-            uint64_t cd[2][8];
-            float sv[2][8], mv[2][8];
+            uint64_t cd[2][PIECES];
+            float sv[2][PIECES], mv[2][PIECES];
             auto fetch = [&](int mb, int set) {
                 const uint32_t rows_left = mb < b_hi ? (uint32_t)(M - mb * KB) : 0u;   // > 63 except in the last block of M
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
+                for (int i = 0; i < PIECES; ++i) {
                     cd[set][i] = 0; sv[set][i] = 0.0f; mv[set][i] = 0.0f;
                     if (colok[i] && rowi[i] < rows_left) {
                         cd[set][i] = CodePiece<BITS>::ld(pcode[i]);
@@ -377,7 +384,7 @@ dw_gemm_kernel(const __grid_constant__ CUtensorMap map_dy, const uint8_t* __rest
                     // pieces 2j and 2j+1 lie in chunks 2c and 2c+1 of one row, i.e. in one group of
                     // 128 or more columns: one table serves both
 #pragma unroll
-                    for (int i = 0; i < 8; i += 2) {
+                    for (int i = 0; i < PIECES; i += 2) {
                         uint32_t t_lo, t_hi;
                         group_table<BITS>(sv[set][i], mv[set][i], t_lo, t_hi);
                         const bool rows_ok = rowi[i] < rows_left;
@@ -389,7 +396,7 @@ dw_gemm_kernel(const __grid_constant__ CUtensorMap map_dy, const uint8_t* __rest
                     }
                 } else {
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
+                    for (int i = 0; i < PIECES; ++i) {
                         uint4 v = make_uint4(0u, 0u, 0u, 0u);  // rows past M and columns past K contribute nothing
                         if (colok[i] && rowi[i] < rows_left) v = decode8<BITS>(cd[set][i], sv[set][i], mv[set][i]);
                         *reinterpret_cast<uint4*>(base + soff[i]) = v;
@@ -420,13 +427,13 @@ dw_gemm_kernel(const __grid_constant__ CUtensorMap map_dy, const uint8_t* __rest
 #pragma unroll 1
             for (int h = 0; h < 2; ++h) {
                 const int row = n0 + h * 128 + q * 32 + lane;
-                const uint32_t t_base = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(h * TN + half_cols * 128);
+                const uint32_t t_base = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(h * TN + col_part * EPI_COLS);
 #pragma unroll 1
-                for (int c = 0; c < 4; ++c) {
+                for (int c = 0; c < EPI_COLS / 32; ++c) {
                     uint32_t r[32];
                     tmem_ld32(t_base + (uint32_t)(c * 32), r);
                     tmem_ld_wait();
-                    const int col0 = k0 + half_cols * 128 + c * 32;
+                    const int col0 = k0 + col_part * EPI_COLS + c * 32;
                     if (row < N) {
                         float* dst = dw + (int64_t)row * ld_dw + col0;
 #pragma unroll
