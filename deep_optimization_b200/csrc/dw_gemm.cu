@@ -7,26 +7,35 @@
 // Reference: the author's Triton attempt at the same fusion ran at 0.06-0.17x of
 // dequantise + cuBLAS (Activation_Compression/test2.ipynb:14-19, 478-491).
 //
-// One CTA per (256 x 256 output tile, slice of M); 576 threads:
-//   warp 0       TMA producer: 64 rows of dY x 256 columns per stage, as four 64 x 64 boxes with
-//                the 128-byte swizzle.  dY is row-major [M, N], so the tile lands with the
-//                output dimension n contiguous: the "MN-major" operand form of tcgen05.mma.
-//   warp 1       MMA issuer: per stage 2 x 4 tcgen05.mma.kind::f16 (bf16, M = 128, N = 256,
-//                K = 16), both operands MN-major, two 128 x 256 fp32 accumulators = all 512
-//                columns of tensor memory.
-//   warps 2..17  decoders (four per scheduler: with eight, 244 us instead of 208 on the ViT MLP
-//                shapes): read the codes of 64 rows x 256 columns (2 bytes per 8 two-bit
-//                codes), look the two bytes of every bf16 value up in the group's table of 2^b
-//                outputs with a byte permute (the arithmetic of dequant_unpack_kernel), and
-//                store 16-byte pieces into the same swizzled MN-major layout a bulk tensor copy
-//                of a dense bf16 X would have produced; 8 lanes cover one 128-byte row, so the
-//                stores are conflict-free.  After the last stage the same warps drain the
-//                accumulators and add them to dW with vector reductions (red.global.add.v4.f32):
-//                slices of M owned by different CTAs sum into the same fp32 tile, which the host
-//                zeroes first.
-// Every mbarrier wait is bounded; on a timeout the kernel records a reason and leaves.
-// Bound: bf16 tensor throughput, flops = 2*M*N*K; the decoders need about 2.5 issue slots per
-// element and an element is used by 256 output rows, which keeps them under the MMA time.
+// One CTA pair (a cluster of two, tcgen05 cta_group::2) per (output tile, slice of M); 576 threads
+// per CTA.  A tile is 256 columns of dW (k, the side that has to be decoded: 128 per CTA) by 256,
+// 384 or 512 rows (n, the dY side, which TMA delivers).  The decoded operand is the M side of the
+// MMA (M = 256 over the pair), dY the N side, so the accumulators hold the tile transposed
+// (tensor-memory lane = k, column = n), and each CTA stages only its half of every dY block: the
+// pair's tensor cores read both halves.  Against one CTA per 256 x 256 tile this halves the
+// decoding per flop at the same dY traffic out of L2 (one CTA per 128 x 512 tile halves the
+// decoding too, but doubles that traffic and then waits for L2: 238 us against 208).
+//   warp 0       TMA producer (both CTAs): 96 rows of dY x this CTA's half of the tile's columns
+//                per stage, as 64 x 96 boxes with the 128-byte swizzle, completion counted on the
+//                leader's barrier.  dY is row-major [M, N], so a box lands with the output
+//                dimension n contiguous: the "MN-major" operand form of tcgen05.mma.
+//   warp 1       MMA issuer (leader CTA only): per stage and K step of 16 rows one
+//                tcgen05.mma.cta_group::2.kind::f16 (bf16, M = 256, N = 256) and, for tiles wider
+//                than 256, a second one (N = 128 or 256) on the next 256 columns of tensor memory;
+//                both operands MN-major.  Its commits free the stage in both CTAs.
+//   warps 2..17  (both CTAs) twelve of them decode, the four on the MMA issuer's warp scheduler
+//                only drain: read the codes of 96 rows x 128 columns (2 bytes per 8 two-bit
+//                codes), look the two bytes of every bf16 value up in the group's table of
+//                2^b outputs with a byte permute (the arithmetic of dequant_unpack_kernel), and
+//                store 16-byte pieces into the same swizzled MN-major layout a bulk tensor copy of
+//                a dense bf16 X would have produced; 8 lanes cover one 128-byte row, so the stores
+//                are conflict-free; then arrive on the leader's barrier.  After the last stage the
+//                same warps drain their CTA's accumulators and add them to dW with
+//                red.global.add.f32 (the 32 lanes of a warp hold 32 consecutive k of one row n:
+//                one 128-byte line per instruction): slices of M owned by different pairs sum into
+//                the same fp32 tile, which the host zeroes first.
+// Every mbarrier wait is bounded; on a timeout the kernel records a reason, tells the other CTA of
+// the pair, and leaves.  Bound: bf16 tensor throughput, flops = 2*M*N*K.
 #include <cuda.h>
 
 #include "act_common.cuh"
@@ -34,32 +43,38 @@
 namespace act {
 namespace dw {
 
-constexpr int TM = 256;                   // output rows (n) per tile: two M = 128 accumulators
-constexpr int TN = 256;                   // output columns (k) per tile
-constexpr int KB = 64;                    // rows of the reduction dimension m per stage
+constexpr int TK = 128;                   // output columns (k) per CTA: the decoded operand, half of the MMA's M = 256
+constexpr int TN_MAX = 512;               // output rows (n) per tile at most: two MMAs of N = 256
+constexpr int KB = 96;                    // rows of the reduction dimension m per stage
 constexpr int UMMA_K = 16;                // K of one tcgen05.mma for 16-bit operands
 constexpr int STAGES = 3;
 #ifndef ACT_DW_PREFETCH_BLOCKS
-#define ACT_DW_PREFETCH_BLOCKS 8
+#define ACT_DW_PREFETCH_BLOCKS 0
 #endif
-constexpr int PREFETCH_BLOCKS = ACT_DW_PREFETCH_BLOCKS;   // distance of the L2 prefetch of dY, in 64-row blocks (0: off)
-constexpr int A_STAGE = KB * TM * 2, B_STAGE = KB * TN * 2;      // 32 KB each
-constexpr int CHUNK = KB * 128;           // one 64-column chunk of a stage: 64 rows x 128 bytes
-#ifndef ACT_DW_DEC_WARPS
-#define ACT_DW_DEC_WARPS 16
+constexpr int PREFETCH_BLOCKS = ACT_DW_PREFETCH_BLOCKS;   // distance of the L2 prefetch of dY, in 96-row blocks (0: off)
+constexpr int CHUNK = KB * 128;           // one 64-column chunk of a stage: KB rows x 128 bytes
+constexpr int DY_STAGE = KB * (TN_MAX / 2) * 2;   // 32 KB: this CTA's half of the tile's columns
+constexpr int X_STAGE = KB * TK * 2;      // 16 KB
+// Warps 2..17 drain the accumulators; twelve of them decode.  The four whose index is 1 modulo 4
+// sit on the warp scheduler of the MMA issuer (warp 1) and stay out of the main loop: with decoders
+// on its scheduler the issuing thread needed 100 cycles per MMA instead of 70 and the tensor pipe
+// ran dry (1250 cycles per 1024 of work).
+constexpr int EPI_WARPS = 16;
+constexpr int DEC_WARPS = 12;
+constexpr int PIECES = (KB * TK / 8) / (DEC_WARPS * 32);  // 16-byte pieces of a stage per decoder thread
+constexpr int THREADS = 64 + EPI_WARPS * 32;
+static_assert((KB * TK / 8) % (DEC_WARPS * 32) == 0 && PIECES >= 2 && PIECES % 2 == 0, "decoder split");
+#ifndef ACT_DW_DEPTH
+#define ACT_DW_DEPTH 2
 #endif
-constexpr int DEC_WARPS = ACT_DW_DEC_WARPS;                // 8 or 16 (a multiple of four: the epilogue's TMEM lane quarters)
-constexpr int PIECES = (KB * TN / 8) / (DEC_WARPS * 32);  // 16-byte pieces of a stage per decoder thread
-constexpr int EPI_COLS = TN / (DEC_WARPS / 4);            // accumulator columns per warp in the epilogue
-constexpr int THREADS = 64 + DEC_WARPS * 32;
-static_assert(DEC_WARPS % 4 == 0 && PIECES >= 2 && PIECES % 2 == 0 && EPI_COLS % 32 == 0, "decoder split");
+constexpr int DEPTH = ACT_DW_DEPTH;                       // register sets of fetched codes: blocks in flight + 1
 constexpr int TMEM_COLS = 512;
 constexpr uint32_t SPIN_LIMIT = 1u << 24;
 
 struct __align__(1024) Smem {
-    uint8_t a[STAGES][A_STAGE];
-    uint8_t b[STAGES][B_STAGE];
-    uint64_t full_a[STAGES], full_b[STAGES], empty[STAGES], acc_full;
+    uint8_t dy[STAGES][DY_STAGE];            // B operand: dY boxes
+    uint8_t x[STAGES][X_STAGE];              // A operand: decoded X~
+    uint64_t full[STAGES], empty[STAGES], acc_full, acc_free;
     uint32_t tmem_base;
     volatile uint32_t abort;
 };
@@ -84,47 +99,83 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
                  : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, Smem* s, uint32_t code) {
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r;
+}
+__device__ __forceinline__ uint32_t cluster_id() {
+    uint32_t r; asm volatile("mov.u32 %0, %%clusterid.x;" : "=r"(r)); return r;
+}
+__device__ __forceinline__ uint32_t n_clusters() {
+    uint32_t r; asm volatile("mov.u32 %0, %%nclusterid.x;" : "=r"(r)); return r;
+}
+// address of the same shared-memory location in CTA `rank` of this cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+    uint32_t r; asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank)); return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" :: "r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v) {
+    asm volatile("st.shared::cluster.u32 [%0], %1;" :: "r"(cluster_addr), "r"(v) : "memory");
+}
+// A wait that runs out records why, raises this CTA's abort flag and the other CTA's (peer_abort:
+// its cluster address), so that every role of the pair leaves.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, Smem* s, uint32_t code, uint32_t peer_abort) {
     for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if (s->abort) return false;
     }
     s->abort = 1;
+    st_cluster_u32(peer_abort, 1u);
     atomicExch(&g_dw_error, code);
     return false;
 }
 // warp-wide: lane 0 polls, everybody learns the outcome
-__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, Smem* s, uint32_t code) {
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, Smem* s, uint32_t code, uint32_t peer_abort) {
     uint32_t ok = 1;
-    if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, s, code) ? 1u : 0u;
+    if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, s, code, peer_abort) ? 1u : 0u;
     return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-                 :: "r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+// tile load whose completion bytes are counted on an mbarrier of the pair's leader
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint32_t leader_bar, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+                 " [%0], [%1, {%3, %4}], [%2];"
+                 :: "r"(smem_u32(dst)), "l"(map), "r"(leader_bar), "r"(c0), "r"(c1) : "memory");
 }
 // requests a tile into L2 only (no shared-memory destination, nothing to wait for)
 __device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* map, int c0, int c1) {
     asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" :: "l"(map), "r"(c0), "r"(c1) : "memory");
 }
-__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(smem_u32(dst_smem)), "r"(cols) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(smem_u32(dst_smem)), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
 }
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(taddr), "r"(cols) : "memory");
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" :: "r"(taddr), "r"(cols) : "memory");
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
                  :: "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(smem_u32(bar)) : "memory");
+// the same with the accumulate predicate fixed to true (no predicate to compute per instruction)
+__device__ __forceinline__ void umma_bf16_pair_acc(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.eq.u32 p, 1, 1;\n\t"
+                 "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 :: "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc) : "memory");
+}
+// arrives, once the pair's MMAs issued so far are done, on the barrier at this offset in both CTAs
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+    const uint16_t both = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 :: "r"(smem_u32(bar)), "h"(both) : "memory");
 }
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -137,9 +188,8 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
                  : "r"(taddr) : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void red_add_v4(float* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};"
-                 :: "l"(p), "f"(__uint_as_float(a)), "f"(__uint_as_float(b)), "f"(__uint_as_float(c)), "f"(__uint_as_float(d)) : "memory");
+__device__ __forceinline__ void red_add(float* p, uint32_t a) {
+    asm volatile("red.global.add.f32 [%0], %1;" :: "l"(p), "f"(__uint_as_float(a)) : "memory");
 }
 
 // Shared-memory descriptor of an MN-major operand held as 64-element (128-byte) chunks of the
@@ -156,10 +206,10 @@ __device__ __forceinline__ uint64_t make_mn_major_desc(const void* start) {
     d |= (uint64_t)2 << 61;
     return d;
 }
-// fp32 accumulate, A and B bf16, both MN-major, N = 256, M = 128
-__host__ __device__ constexpr uint32_t make_idesc() {
+// fp32 accumulate, A and B bf16, both MN-major, M = 256 (both CTAs together), N = n
+__host__ __device__ constexpr uint32_t make_idesc(int n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) | (1u << 16) |
-           ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+           ((uint32_t)(n >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
 }
 
 // ---------------------------------------------------------------- decoding
@@ -224,25 +274,31 @@ __device__ __forceinline__ uint4 decode8(uint64_t w, float s, float m) {
 }
 
 template <int BITS> struct CodePiece;       // the BITS bytes that hold eight codes
-template <> struct CodePiece<1> { static __device__ __forceinline__ uint64_t ld(const uint8_t* p) { return __ldg(p); } };
-template <> struct CodePiece<2> { static __device__ __forceinline__ uint64_t ld(const uint8_t* p) { return __ldg(reinterpret_cast<const uint16_t*>(p)); } };
-template <> struct CodePiece<4> { static __device__ __forceinline__ uint64_t ld(const uint8_t* p) { return __ldg(reinterpret_cast<const uint32_t*>(p)); } };
-template <> struct CodePiece<8> { static __device__ __forceinline__ uint64_t ld(const uint8_t* p) { return __ldg(reinterpret_cast<const unsigned long long*>(p)); } };
+template <> struct CodePiece<1> { typedef uint32_t reg_t; static __device__ __forceinline__ reg_t ld(const uint8_t* p) { return __ldg(p); } };
+template <> struct CodePiece<2> { typedef uint32_t reg_t; static __device__ __forceinline__ reg_t ld(const uint8_t* p) { return __ldg(reinterpret_cast<const uint16_t*>(p)); } };
+template <> struct CodePiece<4> { typedef uint32_t reg_t; static __device__ __forceinline__ reg_t ld(const uint8_t* p) { return __ldg(reinterpret_cast<const uint32_t*>(p)); } };
+template <> struct CodePiece<8> { typedef uint64_t reg_t; static __device__ __forceinline__ reg_t ld(const uint8_t* p) { return __ldg(reinterpret_cast<const unsigned long long*>(p)); } };
 
 // ------------------------------------------------------------------ the kernel
-// Work item w = (tile, slice): tile = w / slices walks the output tiles row-major, slice =
-// w % slices is a contiguous run of 64-row blocks of M.
+// Work item w = (tile, slice), taken by pair w % pairs: tile = w / slices = nt * k_tiles + kt, so
+// the pairs that run together share their columns of dY (L2 serves all but the first read of a
+// block); slice = w % slices is a contiguous run of 96-row blocks of M.  nj = width of a tile in
+// 128-row units of n; a tile is 256 columns of k wide, 128 per CTA.
 template <int BITS>
 __global__ void __launch_bounds__(THREADS, 1)
 dw_gemm_kernel(const __grid_constant__ CUtensorMap map_dy, const uint8_t* __restrict__ packed,
                const float* __restrict__ scale, const float* __restrict__ mn, float* __restrict__ dw,
-               int M, int N, int K, int log2_gs, int ld_dw, int slices)
+               int M, int N, int K, int log2_gs, int ld_dw, int slices, int nj)
 {
     extern __shared__ __align__(1024) uint8_t smem_raw_dw[];
     Smem* s = reinterpret_cast<Smem*>(smem_raw_dw);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n_tiles = (N + TM - 1) / TM, k_tiles = (K + TN - 1) / TN;
+    const int tile_n = 128 * nj;
+    const int n_tiles = (N + tile_n - 1) / tile_n, k_tiles = (K + 2 * TK - 1) / (2 * TK);
     const int n_work = n_tiles * k_tiles * slices;
+    const uint32_t rank = cluster_ctarank();                  // 0 = leader of the pair
+    const int first = (int)cluster_id(), stride = (int)n_clusters();
+    const uint32_t peer_abort = map_to_cta(smem_u32((const void*)&s->abort), rank ^ 1u);
     const int m_blocks = (M + KB - 1) / KB;
 
     if (smem_u32(s) & 1023u) {                                // the swizzled tiles need this alignment
@@ -250,18 +306,22 @@ dw_gemm_kernel(const __grid_constant__ CUtensorMap map_dy, const uint8_t* __rest
         return;
     }
     if (threadIdx.x == 0) {
-        for (int i = 0; i < STAGES; ++i) { mbar_init(&s->full_a[i], 1); mbar_init(&s->full_b[i], DEC_WARPS); mbar_init(&s->empty[i], 1); }
+        // `full` of the leader collects, per stage, the producer's arrival (with the byte count of both
+        // CTAs' dY boxes) and the decoder warps of both CTAs: the MMA issuer then waits once per stage
+        // (a wait that is already satisfied still costs it about 230 cycles)
+        for (int i = 0; i < STAGES; ++i) { mbar_init(&s->full[i], 1 + 2 * DEC_WARPS); mbar_init(&s->empty[i], 1); }
         mbar_init(&s->acc_full, 1);
+        mbar_init(&s->acc_free, 2 * EPI_WARPS);             // leader's: every draining warp of the pair has read its part
         s->abort = 0;
         fence_barrier_init();
     }
-    if (warp == 1) tmem_alloc(&s->tmem_base, TMEM_COLS);
+    if (warp == 1) tmem_alloc_pair(&s->tmem_base, TMEM_COLS);  // the same warp of both CTAs
     tc_fence_before();
-    __syncthreads();
+    cluster_sync_all();                                       // barriers of both CTAs exist from here on
     tc_fence_after();
     const uint32_t tmem_base = s->tmem_base;
 
-    // blocks [b_lo, b_hi) of 64 rows belong to slice sl: as even a split as whole blocks allow
+    // blocks [b_lo, b_hi) of 96 rows belong to slice sl: as even a split as whole blocks allow
     auto slice_range = [&](int sl, int& b_lo, int& b_hi) {
         const int per = m_blocks / slices, extra = m_blocks % slices;
         b_lo = sl * per + (sl < extra ? sl : extra);
@@ -269,86 +329,129 @@ dw_gemm_kernel(const __grid_constant__ CUtensorMap map_dy, const uint8_t* __rest
     };
 
     if (warp == 0) {
-        // ------------------------------------------------------------ TMA producer (dY)
+        // ------------------------------------------------------------ TMA producer (dY, both CTAs)
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
             bool ok = true;
-            for (int w = blockIdx.x; ok && w < n_work; w += gridDim.x) {
-                const int tile = w / slices, n0 = (tile / k_tiles) * TM;
+            // This CTA's columns of the tile: its half of the first 256 (two boxes of 64), and its
+            // half of what lies beyond them (nj = 3: one box; nj = 4: two).
+            const int boxes_hi = nj - 2;
+            for (int w = first; ok && w < n_work; w += stride) {
+                const int tile = w / slices, n0 = (tile / k_tiles) * tile_n;
+                const int n_lo = n0 + (int)rank * 128, n_hi = n0 + 256 + (int)rank * 64 * boxes_hi;
                 int b_lo, b_hi;
                 slice_range(w % slices, b_lo, b_hi);
                 for (int mb = b_lo; mb < b_hi; ++mb) {
-                    if (!(ok = mbar_wait(&s->empty[stage], phase ^ 1, s, 1))) break;
-                    mbar_expect_tx(&s->full_a[stage], A_STAGE);       // rows and columns past the edges arrive as zeros
-#pragma unroll
-                    for (int j = 0; j < TM / 64; ++j)
-                        tma_load_2d(s->a[stage] + j * CHUNK, &map_dy, &s->full_a[stage], n0 + j * 64, mb * KB);
-                    // dY streams out of HBM and the ring is only three blocks deep: ask for the block
-                    // PREFETCH_BLOCKS ahead to be brought into L2 now
+                    if (!(ok = mbar_wait(&s->empty[stage], phase ^ 1, s, 1, peer_abort))) break;
+                    // the leader's barrier counts the bytes of both CTAs' boxes (rows and columns past
+                    // the edges arrive as zeros)
+                    if (rank == 0) mbar_expect_tx(&s->full[stage], (uint32_t)(2 * nj * CHUNK));
+                    const uint32_t bar = map_to_cta(smem_u32(&s->full[stage]), 0);
+                    tma_load_2d_pair(s->dy[stage], &map_dy, bar, n_lo, mb * KB);
+                    tma_load_2d_pair(s->dy[stage] + CHUNK, &map_dy, bar, n_lo + 64, mb * KB);
+                    for (int j = 0; j < boxes_hi; ++j)
+                        tma_load_2d_pair(s->dy[stage] + (2 + j) * CHUNK, &map_dy, bar, n_hi + j * 64, mb * KB);
+                    // ask for the block PREFETCH_BLOCKS ahead to be brought into L2 now (off by default:
+                    // with several pairs reading the same columns it only added requests)
                     if (PREFETCH_BLOCKS > 0 && mb + PREFETCH_BLOCKS < b_hi) {
-#pragma unroll
-                        for (int j = 0; j < TM / 64; ++j)
-                            tma_prefetch_l2_2d(&map_dy, n0 + j * 64, (mb + PREFETCH_BLOCKS) * KB);
+                        tma_prefetch_l2_2d(&map_dy, n_lo, (mb + PREFETCH_BLOCKS) * KB);
+                        tma_prefetch_l2_2d(&map_dy, n_lo + 64, (mb + PREFETCH_BLOCKS) * KB);
+                        for (int j = 0; j < boxes_hi; ++j)
+                            tma_prefetch_l2_2d(&map_dy, n_hi + j * 64, (mb + PREFETCH_BLOCKS) * KB);
                     }
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
             }
+            // tail: every slot handed out has come back, i.e. no arrival from the leader's commits
+            // is still on its way to this CTA's barriers when the CTA leaves
+            for (int i = 0; ok && i < STAGES; ++i) {
+                ok = mbar_wait(&s->empty[stage], phase ^ 1, s, 7, peer_abort);
+                if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            }
         }
     } else if (warp == 1) {
-        // -------------------------------------------------------------- MMA issuer
-        if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc();
+        // -------------------------------------------------------------- MMA issuer (leader only)
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t idesc256 = make_idesc(256), idesc128 = make_idesc(128);
+            const uint32_t idesc_hi = (nj == 4) ? idesc256 : idesc128;     // the MMA on columns 256.. of a tile wider than 256
             uint32_t stage = 0, phase = 0;
             bool ok = true;
-            for (int w = blockIdx.x; ok && w < n_work; w += gridDim.x) {
+            const uint64_t adesc0 = make_mn_major_desc(s->x[0]), bdesc0 = make_mn_major_desc(s->dy[0]);
+            int items_done = 0;
+            for (int w = first; ok && w < n_work; w += stride) {
                 int b_lo, b_hi;
                 slice_range(w % slices, b_lo, b_hi);
-                // A second work item overwrites the accumulators with its first MMA.  That MMA waits
-                // for full_b of its stage, on which every decoder warp arrives only after it has read
-                // the previous item's accumulators out of tensor memory (program order in the warp).
+                // A later work item overwrites the accumulators with its first MMA: every warp of the
+                // pair that drains them has arrived on acc_free once it was done with the previous item.
+                if (items_done > 0 && !(ok = mbar_wait(&s->acc_free, (uint32_t)((items_done - 1) & 1), s, 8, peer_abort))) break;
+                ++items_done;
+                // The issuing thread is the narrowest part of the kernel.  Measured with cycle stamps: an
+                // MMA costs it about 70 cycles to issue (100 with decoder warps on its scheduler), a
+                // wait that is already satisfied 250-300, a commit 80, against 128 cycles of tensor
+                // work per MMA; the tensor pipe holds only two or three MMAs beyond the one it
+                // executes.  Hence twelve MMAs per wait (96-row stages), the wait for the NEXT stage
+                // between the two halves of this stage's MMAs, the commit after the second half, and
+                // the stage's descriptors (start address field in 16-byte units) computed before the wait.
+                bool have = false;                               // the current stage's wait is already done
                 for (int mb = b_lo; mb < b_hi; ++mb) {
-                    if (!(ok = mbar_wait(&s->full_a[stage], phase, s, 3))) break;
-                    if (!(ok = mbar_wait(&s->full_b[stage], phase, s, 4))) break;
+                    const uint64_t adesc = adesc0 + (uint64_t)(stage * (X_STAGE >> 4));
+                    const uint64_t bdesc = bdesc0 + (uint64_t)(stage * (DY_STAGE >> 4));
+                    const uint64_t bdesc_hi = bdesc + (uint64_t)((2 * CHUNK) >> 4);
+                    const uint32_t acc0 = mb > b_lo ? 1u : 0u;
+                    const uint32_t next_stage = stage + 1 == STAGES ? 0u : stage + 1;
+                    const uint32_t next_phase = stage + 1 == STAGES ? phase ^ 1u : phase;
+                    if (!have && !(ok = mbar_wait(&s->full[stage], phase, s, 3, peer_abort))) break;
+                    tc_fence_after();
+                    constexpr uint64_t KSTEP = (uint64_t)((UMMA_K * 128) >> 4);
+                    constexpr int KS = KB / UMMA_K;
+                    umma_bf16_pair(tmem_base, adesc, bdesc, idesc256, acc0);
+                    if (nj > 2) umma_bf16_pair(tmem_base + 256u, adesc, bdesc_hi, idesc_hi, acc0);
+#pragma unroll
+                    for (int k = 1; k < KS / 2; ++k) {
+                        umma_bf16_pair_acc(tmem_base, adesc + k * KSTEP, bdesc + k * KSTEP, idesc256);
+                        if (nj > 2) umma_bf16_pair_acc(tmem_base + 256u, adesc + k * KSTEP, bdesc_hi + k * KSTEP, idesc_hi);
+                    }
+                    have = mb + 1 < b_hi;
+                    if (have && !(ok = mbar_wait(&s->full[next_stage], next_phase, s, 4, peer_abort))) break;
                     tc_fence_after();
 #pragma unroll
-                    for (int k = 0; k < KB / UMMA_K; ++k) {
-                        const uint64_t bdesc = make_mn_major_desc(s->b[stage] + k * (UMMA_K * 128));
-#pragma unroll
-                        for (int h = 0; h < 2; ++h) {
-                            const uint64_t adesc = make_mn_major_desc(s->a[stage] + h * 2 * CHUNK + k * (UMMA_K * 128));
-                            umma_bf16(tmem_base + (uint32_t)(h * TN), adesc, bdesc, idesc, (mb > b_lo || k > 0) ? 1u : 0u);
-                        }
+                    for (int k = KS / 2; k < KS; ++k) {
+                        umma_bf16_pair_acc(tmem_base, adesc + k * KSTEP, bdesc + k * KSTEP, idesc256);
+                        if (nj > 2) umma_bf16_pair_acc(tmem_base + 256u, adesc + k * KSTEP, bdesc_hi + k * KSTEP, idesc_hi);
                     }
-                    umma_commit(&s->empty[stage]);
-                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                    umma_commit_pair(&s->empty[stage]);        // frees the slot in both CTAs
+                    stage = next_stage; phase = next_phase;
                 }
                 if (!ok) break;
-                umma_commit(&s->acc_full);
+                umma_commit_pair(&s->acc_full);                // both CTAs' accumulators are complete
             }
         }
     } else {
         // ------------------------------------------- decoders (X~ into shared memory), then epilogue
-        const int dwarp = warp - 2;
+        const int ew = warp - 2;                               // 0..15
+        const bool decodes = (ew & 3) != 3;                    // warps 5, 9, 13, 17 only drain
+        const int dwarp = (ew >> 2) * 3 + (ew & 3);            // 0..11 among the decoders
         const int piece = lane & 7, rsub = lane >> 3;          // 8 lanes = one 128-byte row of a chunk; 4 rows per warp
         const int q = warp & 3;                                // TMEM lane quarter for the epilogue
-        const int col_part = dwarp >> 2;                       // which EPI_COLS columns of a tile in the epilogue
+        const int col_part = ew >> 2;                          // which 32-column blocks of the accumulators in the epilogue
         uint32_t stage = 0, phase = 0, acc_phase = 0;
         bool ok = true;
-        for (int w = blockIdx.x; w < n_work; w += gridDim.x) {
+        const uint32_t leader_full = map_to_cta(smem_u32(&s->full[0]), 0);
+        for (int w = first; w < n_work; w += stride) {
             const int tile = w / slices;
-            const int n0 = (tile / k_tiles) * TM, k0 = (tile % k_tiles) * TN;
+            const int n0 = (tile / k_tiles) * tile_n, k0 = (tile % k_tiles) * (2 * TK) + (int)rank * TK;
             int b_lo, b_hi;
             slice_range(w % slices, b_lo, b_hi);
-            // Per piece i of this thread (eight per stage: two row quads x four 64-column chunks): where
-            // its codes and its group's scale and minimum lie for the first block, advanced by a constant
-            // per block; where it goes in the stage (fixed).  Nothing in the stage loop multiplies.
+            // Per piece i of this thread (PIECES per stage, two neighbouring chunks of one row each pair): where its codes and its
+            // group's scale and minimum lie for the first block, advanced by a constant per block;
+            // where it goes in the stage (fixed).  Nothing in the stage loop multiplies.
             const uint8_t* pcode[PIECES];
             int gidx[PIECES];
             uint32_t soff[PIECES], rowi[PIECES];
             bool colok[PIECES];
 #pragma unroll
             for (int i = 0; i < PIECES; ++i) {
-                const int qd = dwarp * PIECES + i, chunk = qd & 3, row = (qd >> 2) * 4 + rsub;
+                const int qd = dwarp * PIECES + i, chunk = qd & 1, row = (qd >> 1) * 4 + rsub;
                 const int col = k0 + chunk * 64 + piece * 8;
                 const int64_t e0 = ((int64_t)b_lo * KB + row) * K + col;
                 pcode[i] = packed + (e0 >> 3) * BITS;
@@ -357,14 +460,16 @@ dw_gemm_kernel(const __grid_constant__ CUtensorMap map_dy, const uint8_t* __rest
                 rowi[i] = (uint32_t)row;
                 colok[i] = col < K;
             }
-            const int code_step = KB * (K >> 3) * BITS;            // bytes of codes per 64-row block
-            const int group_step = (KB * K) >> log2_gs;            // groups per 64-row block (group_size divides K)
-            // The codes, scales and minima of a block are fetched one block ahead of their use, into
-            // two register sets that swap roles (the loop body is written out twice).
-            uint64_t cd[2][PIECES];
-            float sv[2][PIECES], mv[2][PIECES];
+            const int code_step = KB * (K >> 3) * BITS;            // bytes of codes per 96-row block
+            const int group_step = (KB * K) >> log2_gs;            // groups per 96-row block (group_size divides K)
+            // The codes, scales and minima of a block are fetched DEPTH - 1 blocks ahead of their use
+            // (a block of 96 rows is 1536 cycles of MMA), into
+            // register sets that take turns (the loop body is unrolled over them).
+            typedef typename CodePiece<BITS>::reg_t code_t;       // 32 bits hold eight codes of up to four bits
+            code_t cd[DEPTH][PIECES];
+            float sv[DEPTH][PIECES], mv[DEPTH][PIECES];
             auto fetch = [&](int mb, int set) {
-                const uint32_t rows_left = mb < b_hi ? (uint32_t)(M - mb * KB) : 0u;   // > 63 except in the last block of M
+                const uint32_t rows_left = mb < b_hi ? (uint32_t)(M - mb * KB) : 0u;   // > 31 except in the last block of M
 #pragma unroll
                 for (int i = 0; i < PIECES; ++i) {
                     cd[set][i] = 0; sv[set][i] = 0.0f; mv[set][i] = 0.0f;
@@ -379,9 +484,9 @@ dw_gemm_kernel(const __grid_constant__ CUtensorMap map_dy, const uint8_t* __rest
             };
             auto produce = [&](int mb, int set) {
                 const uint32_t rows_left = (uint32_t)(M - mb * KB);
-                uint8_t* base = s->b[stage];
+                uint8_t* base = s->x[stage];
                 if (BITS <= 2 && log2_gs >= 7) {
-                    // pieces 2j and 2j+1 lie in chunks 2c and 2c+1 of one row, i.e. in one group of
+                    // pieces 2j and 2j+1 lie in chunks 0 and 1 of one row, i.e. in one group of
                     // 128 or more columns: one table serves both
 #pragma unroll
                     for (int i = 0; i < PIECES; i += 2) {
@@ -404,61 +509,60 @@ dw_gemm_kernel(const __grid_constant__ CUtensorMap map_dy, const uint8_t* __rest
                 }
                 fence_proxy_async();                           // generic-proxy stores -> visible to the tensor core's reads
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&s->full_b[stage]);
+                if (lane == 0) mbar_arrive_cluster(leader_full + stage * (uint32_t)sizeof(uint64_t));
                 if (++stage == STAGES) { stage = 0; phase ^= 1; }
             };
-            fetch(b_lo, 0);
-            for (int mb = b_lo; ok && mb < b_hi; mb += 2) {
-                fetch(mb + 1, 1);
-                if (ok) ok = mbar_wait_warp(&s->empty[stage], phase ^ 1, s, 2);
-                if (!ok) break;
-                produce(mb, 0);
-                if (mb + 1 >= b_hi) break;
-                fetch(mb + 2, 0);
-                if (ok) ok = mbar_wait_warp(&s->empty[stage], phase ^ 1, s, 2);
-                if (!ok) break;
-                produce(mb + 1, 1);
+            if (decodes) {
+#pragma unroll
+            for (int d = 0; d < DEPTH - 1; ++d) fetch(b_lo + d, d);
+            for (int mb = b_lo; ok && mb < b_hi; mb += DEPTH) {
+#pragma unroll
+                for (int d = 0; d < DEPTH; ++d) {
+                    if (!ok || mb + d >= b_hi) break;
+                    fetch(mb + d + DEPTH - 1, (d + DEPTH - 1) % DEPTH);
+                    ok = mbar_wait_warp(&s->empty[stage], phase ^ 1, s, 2, peer_abort);
+                    if (ok) produce(mb + d, d);
+                }
             }
-            // ---- epilogue of this work item: accumulators -> dW (fp32, summed over slices)
-            if (ok) ok = mbar_wait_warp(&s->acc_full, acc_phase, s, 6);
+            }
+            // ---- epilogue of this work item: accumulators (lane = k, column = n) -> dW[n, k], fp32,
+            // summed over slices.  A warp owns the 32 lanes of its quarter and every other 32-column
+            // block; for one column its lanes add to 32 consecutive floats of one row of dW.
+            if (ok) ok = mbar_wait_warp(&s->acc_full, acc_phase, s, 6, peer_abort);
             if (!ok) continue;
             acc_phase ^= 1;
             tc_fence_after();
+            const int kk = k0 + q * 32 + lane;
 #pragma unroll 1
-            for (int h = 0; h < 2; ++h) {
-                const int row = n0 + h * 128 + q * 32 + lane;
-                const uint32_t t_base = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(h * TN + col_part * EPI_COLS);
-#pragma unroll 1
-                for (int c = 0; c < EPI_COLS / 32; ++c) {
-                    uint32_t r[32];
-                    tmem_ld32(t_base + (uint32_t)(c * 32), r);
-                    tmem_ld_wait();
-                    const int col0 = k0 + col_part * EPI_COLS + c * 32;
-                    if (row < N) {
-                        float* dst = dw + (int64_t)row * ld_dw + col0;
+            for (int cb = col_part; cb < 4 * nj; cb += EPI_WARPS / 4) {
+                uint32_t r[32];
+                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(cb * 32), r);
+                tmem_ld_wait();
+                const int nn = n0 + cb * 32;
+                if (kk < K) {
+                    float* dst = dw + (int64_t)nn * ld_dw + kk;
 #pragma unroll
-                        for (int v = 0; v < 8; ++v)
-                            if (col0 + v * 4 < K) red_add_v4(dst + v * 4, r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
-                    }
+                    for (int v = 0; v < 32; ++v)
+                        if (nn + v < N) red_add(dst + (int64_t)v * ld_dw, r[v]);
                 }
             }
-            // the accumulators may be overwritten once every decoder warp is past this point: the
-            // next item's first MMA waits for full_b of its first stage, on which each warp arrives
-            // only after its reads above (tcgen05.wait::ld) and this fence
+            // this warp is done with the item's accumulators (tcgen05.wait::ld above): tell the issuer
             tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&s->acc_free), 0));
         }
     }
 
     // ---------------------------------------------------------------- teardown
-    __syncwarp();
+    __syncwarp();                                             // lanes that had no role wait for the one that had
     if (s->abort) {
         for (int i = 0; i < 1000; ++i) __nanosleep(1000);
     }
     tc_fence_before();
-    __syncthreads();
+    cluster_sync_all();                                       // neither CTA's memory is needed by the other any more
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, TMEM_COLS);
+        tmem_dealloc_pair(tmem_base, TMEM_COLS);
     }
 }
 
@@ -487,21 +591,68 @@ EncodeTiledFn encode_tiled_fn() {
 
 constexpr int kMaxDevices = 64;
 
+// Per-device state of one instantiation: the shared-memory opt-in (a per-device attribute of the
+// kernel) and how many CTA pairs the device holds at once.
 template <int BITS>
-int launch(const CUtensorMap& map, const uint8_t* packed, const float* scale, const float* mn, float* dw,
-           int M, int N, int K, int log2_gs, int ld_dw, int slices, int grid, cudaStream_t st)
-{
+int pairs_resident(int* out) {
     using namespace act::dw;
-    static bool attr_set[kMaxDevices];                       // the shared-memory opt-in is per device
+    static int pairs[kMaxDevices];                           // 0: not yet set up on that device
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return ACT_ERR_DEVICE;
-    if (!attr_set[dev]) {
+    if (!pairs[dev]) {
+        int sms = 0;
         if (cudaFuncSetAttribute(dw_gemm_kernel<BITS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Smem)) != cudaSuccess)
             return ACT_ERR_DEVICE;
-        attr_set[dev] = true;
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 2) return ACT_ERR_DEVICE;
+        cudaLaunchConfig_t q = {};
+        q.gridDim = dim3(2u * (unsigned)(sms / 2), 1, 1);
+        q.blockDim = dim3(THREADS, 1, 1);
+        q.dynamicSmemBytes = sizeof(Smem);
+        cudaLaunchAttribute qa[1];
+        qa[0].id = cudaLaunchAttributeClusterDimension;
+        qa[0].val.clusterDim.x = 2; qa[0].val.clusterDim.y = 1; qa[0].val.clusterDim.z = 1;
+        q.attrs = qa; q.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, dw_gemm_kernel<BITS>, &q) != cudaSuccess || n <= 0) {
+            (void)cudaGetLastError();
+            n = sms / 2;
+        }
+        pairs[dev] = n < sms / 2 ? n : sms / 2;
     }
-    dw_gemm_kernel<BITS><<<grid, THREADS, sizeof(Smem), st>>>(map, packed, scale, mn, dw, M, N, K, log2_gs, ld_dw, slices);
-    return cudaGetLastError() == cudaSuccess ? ACT_OK : ACT_ERR_LAUNCH;
+    *out = pairs[dev];
+    return ACT_OK;
+}
+
+template <int BITS>
+int launch(const CUtensorMap& map, const uint8_t* packed, const float* scale, const float* mn, float* dw,
+           int M, int N, int K, int log2_gs, int ld_dw, int nj, cudaStream_t st)
+{
+    using namespace act::dw;
+    int resident = 0;
+    const int rc = pairs_resident<BITS>(&resident);
+    if (rc != ACT_OK) return rc;
+    const int tiles = ((N + 128 * nj - 1) / (128 * nj)) * ((K + 2 * TK - 1) / (2 * TK));
+    const int m_blocks = (M + KB - 1) / KB;
+    // slices of M: enough work items to occupy every pair once, never more slices than blocks
+    int slices = tiles >= resident ? 1 : resident / tiles;
+    if (slices > m_blocks) slices = m_blocks;
+    if (slices < 1) slices = 1;
+    const int work = tiles * slices;
+    const int clusters = work < resident ? work : resident;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2u * (unsigned)clusters, 1, 1);
+    cfg.blockDim = dim3(THREADS, 1, 1);
+    cfg.dynamicSmemBytes = sizeof(Smem);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, dw_gemm_kernel<BITS>, map, packed, scale, mn, dw, M, N, K, log2_gs, ld_dw, slices, nj) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return ACT_ERR_LAUNCH;
+    }
+    return ACT_OK;
 }
 
 }  // namespace
@@ -516,7 +667,7 @@ extern "C" int act_dw_from_packed(const void* dy, const void* packed, const floa
     if (group_size < 32 || group_size > 1024 || (group_size & (group_size - 1))) return ACT_ERR_GROUP;
     if (N == 0 || K == 0) return ACT_OK;
     if (!dw) return ACT_ERR_NULL;
-    // whole groups per row; 16-byte rows of dY for the tensor map; 16-byte pieces of dW for the vector adds
+    // whole groups per row; 16-byte rows of dY for the tensor map
     if ((K % group_size) || (N & 7) || (ld_dy & 7) || ld_dy < N || (ld_dw & 3) || ld_dw < K || (K & 7)) return ACT_ERR_SIZE;
     if ((uintptr_t)dw & 15) return ACT_ERR_ALIGN;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -536,24 +687,18 @@ extern "C" int act_dw_from_packed(const void* dy, const void* packed, const floa
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) return ACT_ERR_DEVICE;
 
-    int dev = 0, sms = 148;
-    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    const int tiles = ((N + TM - 1) / TM) * ((K + TN - 1) / TN);
-    const int m_blocks = (M + KB - 1) / KB;
-    // slices of M: enough work items to occupy every SM once, never more slices than blocks
-    int slices = tiles >= sms ? 1 : sms / tiles;
-    if (slices > m_blocks) slices = m_blocks;
-    if (slices < 1) slices = 1;
-    const int work = tiles * slices;
-    const int grid = work < sms ? work : sms;
+    // width of a tile in 128-row units of n: the least padded of 512, 384 and 256, the widest on a tie
+    int nj = 4;
+    for (int c = 3; c >= 2; --c)
+        if (((N + 128 * c - 1) / (128 * c)) * c < ((N + 128 * nj - 1) / (128 * nj)) * nj) nj = c;
     int log2_gs = 0;
     while ((1 << log2_gs) < group_size) ++log2_gs;
     const uint8_t* pk = static_cast<const uint8_t*>(packed);
     switch (bits) {
-        case 1: return launch<1>(map, pk, scale, mn, dw, M, N, K, log2_gs, ld_dw, slices, grid, st);
-        case 2: return launch<2>(map, pk, scale, mn, dw, M, N, K, log2_gs, ld_dw, slices, grid, st);
-        case 4: return launch<4>(map, pk, scale, mn, dw, M, N, K, log2_gs, ld_dw, slices, grid, st);
-        default: return launch<8>(map, pk, scale, mn, dw, M, N, K, log2_gs, ld_dw, slices, grid, st);
+        case 1: return launch<1>(map, pk, scale, mn, dw, M, N, K, log2_gs, ld_dw, nj, st);
+        case 2: return launch<2>(map, pk, scale, mn, dw, M, N, K, log2_gs, ld_dw, nj, st);
+        case 4: return launch<4>(map, pk, scale, mn, dw, M, N, K, log2_gs, ld_dw, nj, st);
+        default: return launch<8>(map, pk, scale, mn, dw, M, N, K, log2_gs, ld_dw, nj, st);
     }
 }
 
