@@ -488,6 +488,7 @@ def run_reference_triton(steps=20, warmup=3):
 
 
 DDP_BUCKET_MB = 25
+FUSED_DW = True         # Linear weight gradients straight from the packed input (--no-fused-dw: dequantise + cuBLAS)
 DP_MODE = "flat"         # how the training legs average gradients over ranks; see run_train
 
 
@@ -552,7 +553,7 @@ def run_train(name, dev, world, local, steps=8, warmup=3, act=True, batch=256, c
     torch.manual_seed(0)
     model = (resnet50() if name == "resnet50" else vit_b16()).to(dev)
     if act:
-        cfg = dict(default_bits=2, auto_precision=None, batch_size=batch)
+        cfg = dict(default_bits=2, auto_precision=None, batch_size=batch, fused_dw=FUSED_DW)
         net = Controller(model, cfg, input_shape=(3, 224, 224), test=False, device=dev).traced_model
     else:
         net = model.train()
@@ -927,9 +928,12 @@ def main():
     ap.add_argument("--dp-mode", choices=("flat", "ddp", "ddp-view"), default=None,
                     help="gradient averaging of the training legs: one flat all-reduce per step (default), "
                          "DistributedDataParallel, or DDP with gradients as bucket views")
+    ap.add_argument("--no-fused-dw", action="store_true",
+                    help="training legs: Linear layers dequantise and call cuBLAS for dW instead of act_dw_from_packed")
     ap.add_argument("--legs", nargs="+", default=None, help="training legs to run (default: all six)")
     args = ap.parse_args()
-    global DDP_BUCKET_MB, DP_MODE
+    global DDP_BUCKET_MB, DP_MODE, FUSED_DW
+    FUSED_DW = not args.no_fused_dw
     if args.ddp_bucket_mb:
         DDP_BUCKET_MB = args.ddp_bucket_mb
     if args.dp_mode:

@@ -134,6 +134,47 @@ def test_layer_norm_module(cuda_device):
     assert torch.allclose(ln(x), ref(x), atol=1e-6)
 
 
+@pytest.mark.parametrize("bits", [2, 8])
+def test_linear_weight_gradient_from_packed_input(cuda_device, bits):
+    """_DOLinear.backward with the fused weight-gradient GEMM (the default) against the same layer
+    dequantising and calling cuBLAS: both multiply dy by the same decoded bf16 input, so the two
+    gradients differ only in accumulation order and in the bf16 rounding of the cuBLAS result;
+    dx and the bias gradient do not depend on the switch.  Below the row threshold the fused path
+    must stand aside."""
+    from deep_optimization_b200.layers import DOLinear
+    from deep_optimization_b200.modules import ops
+    from deep_optimization_b200.gemm import dw_status
+    torch.manual_seed(5)
+    meta = _meta("l", bits, 128, 16)
+    lin = DOLinear(768, 384, target_name="l", meta=meta).to(cuda_device).train()
+    x = torch.randn(16, 197, 768, device=cuda_device)
+    g = torch.randn(16, 197, 384, device=cuda_device)
+    grads = {}
+    try:
+        for fused in (True, False):
+            ops.set_fused_dw(fused)
+            from deep_optimization_b200 import codec
+            codec.manual_seed(11)                 # the same stochastic codes in both passes
+            lin.zero_grad()
+            xi = x.clone().requires_grad_()
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                lin(xi).backward(g.to(torch.bfloat16))
+            grads[fused] = (lin.weight.grad.clone(), lin.bias.grad.clone(), xi.grad.clone())
+        assert dw_status() == 0
+        ops.set_fused_dw(True)
+        assert not ops._fused_dw_applies((bits, False, 128, False, 0, 0, 0, 0, False, False, None, False, 0, (8, 768)),
+                                         None, torch.empty(8, 384, dtype=torch.bfloat16, device=cuda_device), 768)
+    finally:
+        ops.set_fused_dw(True)
+    wf, bf, xf = grads[True]
+    wu, bu, xu = grads[False]
+    assert torch.equal(bf, bu) and torch.equal(xf, xu)
+    assert (wf - wu).norm() / wu.norm() < 4e-3                     # bf16 rounding of the unfused product
+    # and against the exact gradient: the codes' quantisation error only
+    exact = g.reshape(-1, 384).t() @ x.reshape(-1, 768)
+    assert (wf - exact).norm() / exact.norm() < (0.02 if bits == 8 else 1.5)
+
+
 def test_division_split(cuda_device):
     """DIVISION: low-pass part + compressed residual reconstruct the input, so the weight
     gradients stay those of the stock layer (within the quantisation error), for the conv and
