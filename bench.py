@@ -595,16 +595,30 @@ def run_train(name, dev, world, local, steps=8, warmup=3, act=True, batch=256, c
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     import contextlib
-    with (profiler if profiler is not None else contextlib.nullcontext()):
-        e0.record()
-        for _ in range(steps):
-            loss = one_step()
-        e1.record()
-        torch.cuda.synchronize()
-    ms = torch.tensor([e0.elapsed_time(e1) / steps], device=dev, dtype=torch.float64)
+    # The interpreter's cyclic garbage collector is held off during the timed steps (collected
+    # before, re-enabled after), as a training loop that cares about step-time jitter does: one
+    # collection in a 20-step region otherwise shows up as a 40-70 ms step.  An event after every
+    # step gives the median and the slowest step beside the mean.
+    import gc
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    gc.collect()
+    gc.disable()
+    try:
+        with (profiler if profiler is not None else contextlib.nullcontext()):
+            e0.record()
+            for i in range(steps):
+                loss = one_step()
+                marks[i].record()
+            e1.record()
+            torch.cuda.synchronize()
+    finally:
+        gc.enable()
+    per_step = sorted((marks[i - 1] if i else e0).elapsed_time(marks[i]) for i in range(steps))
+    ms = torch.tensor([e0.elapsed_time(e1) / steps, per_step[steps // 2], per_step[-1]], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    out = {"img_per_s": batch * world / (ms.item() * 1e-3), "ms_per_step": ms.item(),
+    out = {"img_per_s": batch * world / (ms[0].item() * 1e-3), "ms_per_step": ms[0].item(),
+           "ms_per_step_median": ms[1].item(), "ms_per_step_max": ms[2].item(),
            "peak_mem_GB": torch.cuda.max_memory_allocated(dev) / 2 ** 30, "final_loss": float(loss.detach())}
     if reduce_grads is not None:
         # what the step pays for the gradient exchange: the all-reduce of the flat buffer alone,
