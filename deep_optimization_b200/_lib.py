@@ -62,6 +62,8 @@ SIGNATURES = {
     "act_unpack_ballot": ([_vp, _vp, _vp, _i32, _i64, _i32, _i32, _vp, _vp], _i32),
     "act_copy": ([_vp, _vp, _sz, _sz, _sz, _vp], _i32),
     "act_fill_zero": ([_vp, _sz, _vp], _i32),
+    "act_col_sum": ([_vp, _i32, _i64, _i32, _vp, _vp], _i32),
+    "act_ln_bwd_params": ([_vp, _vp, _vp, _vp, _i32, _i64, _i32, _vp, _vp, _vp], _i32),
     "act_calc_precision": ([_vp, _vp, _vp, _i64, ctypes.c_double], _i32),
     "act_fp8_gemm_workspace": ([_i32, _i32, _i32, _i32], ctypes.c_size_t),
     "act_fp8_gemm": ([_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _vp, ctypes.c_size_t, _vp], _i32),

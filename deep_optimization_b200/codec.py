@@ -693,3 +693,52 @@ def maxpool_bwd(idx: torch.Tensor, dy: torch.Tensor, input_shape, k: int, s: int
                                             dx.data_ptr(), _stream_ptr(dy))
     _lib.check(rc, "act_maxpool_bwd_cl")
     return dx
+
+
+# ---------------------------------------------------------------- column reductions
+
+def col_sum_applies(t: torch.Tensor) -> bool:
+    """act_col_sum / act_ln_bwd_params take a CUDA tensor of a codec dtype whose rows (last
+    dimension, a multiple of 8) are contiguous and packed and whose base is 16-byte aligned."""
+    return (t.is_cuda and t.dtype in _DTYPES and t.dim() >= 1 and t.shape[-1] % 8 == 0 and t.shape[-1] > 0
+            and t.is_contiguous() and t.data_ptr() % 16 == 0)
+
+
+def col_sum(a: torch.Tensor) -> torch.Tensor:
+    """fp32 [C] = a.reshape(-1, C).sum(0): the bias gradient of a linear layer from its output
+    gradient (Activation_Compression/modules/ops.py:496-526), one pass at HBM pace."""
+    if not a.is_cuda:
+        raise RuntimeError("col_sum needs a CUDA tensor: there is no CPU path")
+    C = a.shape[-1]
+    a2 = a.reshape(-1, C)
+    if not col_sum_applies(a2):
+        raise ValueError("col_sum: rows must be contiguous, a multiple of 8 long and 16-byte aligned")
+    out = torch.empty(C, dtype=torch.float32, device=a.device)
+    with _device_of(a):
+        rc = _lib.load().act_col_sum(a2.data_ptr(), _DTYPES[a2.dtype], a2.shape[0], C, out.data_ptr(), _stream_ptr(a))
+    _lib.check(rc, "act_col_sum")
+    return out
+
+
+def ln_bwd_params(dy: torch.Tensor, x: torch.Tensor, mean: torch.Tensor, rstd: torch.Tensor):
+    """(dgamma, dbeta), fp32 [C]: sum over rows of dy * (x - mean) * rstd and of dy, for a
+    LayerNorm over the last dimension; mean and rstd are the fp32 per-row statistics of the
+    forward pass."""
+    if not dy.is_cuda:
+        raise RuntimeError("ln_bwd_params needs CUDA tensors: there is no CPU path")
+    C = dy.shape[-1]
+    dy2, x2 = dy.reshape(-1, C), x.reshape(-1, C)
+    if dy2.dtype != x2.dtype or dy2.shape != x2.shape or not col_sum_applies(dy2) or not col_sum_applies(x2):
+        raise ValueError("ln_bwd_params: dy and x must share type and shape, with contiguous aligned rows of a multiple of 8")
+    mean = mean.reshape(-1).to(torch.float32).contiguous()
+    rstd = rstd.reshape(-1).to(torch.float32).contiguous()
+    if mean.numel() != dy2.shape[0] or rstd.numel() != dy2.shape[0]:
+        raise ValueError("ln_bwd_params: one mean and one rstd per row")
+    dgamma = torch.empty(C, dtype=torch.float32, device=dy.device)
+    dbeta = torch.empty(C, dtype=torch.float32, device=dy.device)
+    with _device_of(dy):
+        rc = _lib.load().act_ln_bwd_params(dy2.data_ptr(), x2.data_ptr(), mean.data_ptr(), rstd.data_ptr(),
+                                           _DTYPES[dy2.dtype], dy2.shape[0], C, dgamma.data_ptr(), dbeta.data_ptr(),
+                                           _stream_ptr(dy))
+    _lib.check(rc, "act_ln_bwd_params")
+    return dgamma, dbeta

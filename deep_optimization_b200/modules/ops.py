@@ -17,6 +17,7 @@ from torch.amp import custom_bwd, custom_fwd
 from torch.autograd import Function
 from torch.nn.modules.utils import _pair, _single, _triple
 
+from .. import codec
 from .module_utils import low_pass_upsampled, unified_dequantize, unified_quantize
 
 
@@ -208,7 +209,12 @@ class _DOLinear(Function):
         if ctx.needs_input_grad[0]:
             dx = dy2.mm(weight_compute).view(*input_shape)
         if ctx.bias_dtype is not None and ctx.needs_input_grad[6]:
-            db = dy2.sum(0, dtype=torch.float32).to(ctx.bias_dtype)
+            # the bias gradient: column sums of dy in one pass (codec.col_sum) where its layout allows
+            dyc = dy2 if dy2.is_contiguous() else None
+            if dyc is not None and codec.col_sum_applies(dyc):
+                db = codec.col_sum(dyc).to(ctx.bias_dtype)
+            else:
+                db = dy2.sum(0, dtype=torch.float32).to(ctx.bias_dtype)
         return dx, dw, None, None, None, None, db
 
 

@@ -347,6 +347,22 @@ ACT_API int act_copy(const void* src, void* dst, size_t nbytes, size_t src_capac
 ACT_API int act_fill_zero(void* p, size_t nbytes, void* stream);
 
 /*
+ * Column reductions over a row-major [rows, cols] tensor (cols a multiple of 8, 16-byte aligned
+ * base; dtype ACT_DTYPE_*), results fp32 [cols], overwritten (zeroed, then summed with one atomic
+ * per block and column: the order of the partial sums is not fixed).
+ *   act_col_sum: out[c] = sum_r a[r, c].  Replaces `dy.sum(0)` for the bias gradient in
+ *       _DOLinear.backward (AC/modules/ops.py:496-526).
+ *   act_ln_bwd_params: dgamma[c] = sum_r dy[r, c] * (x[r, c] - mean[r]) * rstd[r] and
+ *       dbeta[c] = sum_r dy[r, c], with mean and rstd fp32 [rows] as the forward pass returned
+ *       them: the parameter gradients of a LayerNorm over the last dimension (the reference leaves
+ *       LayerNorm to PyTorch, AC/controller.py:87; ATen's kernel for these two sums takes 430 us
+ *       on bf16 [50432, 768], a fifth of the ViT-B/16 step).
+ */
+ACT_API int act_col_sum(const void* a, int dtype, int64_t rows, int cols, float* out, void* stream);
+ACT_API int act_ln_bwd_params(const void* dy, const void* x, const float* mean, const float* rstd, int dtype,
+                              int64_t rows, int cols, float* dgamma, float* dbeta, void* stream);
+
+/*
  * Greedy bit allocation on the host (no GPU work).
  * Replaces cpp_extension.calc_precision (AC/cpp_extension/src/calc_precision.cc:10-53):
  * b, C, w are int32 arrays of length n; b is updated in place until sum(b*w) <= target.

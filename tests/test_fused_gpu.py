@@ -542,3 +542,38 @@ def test_bn_backward_one_call(cuda_device, channels_last, mode):
         want_dx = codec.bn_bwd_dx(packed, scale, mn, dy, None, None, None, bits, gs, mask=mask, coef=coef)
     assert torch.allclose(dg, s1, rtol=1e-4, atol=1e-3) and torch.allclose(db, s2, rtol=1e-4, atol=1e-3)
     assert ((dx.float() - want_dx.float()).abs() <= 2.0 ** -6 * (1 + want_dx.float().abs())).all()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("shape", [(50432, 768), (1000, 3072), (197, 8), (3, 2056), (1, 64)])
+def test_column_reductions(cuda_device, dtype, shape):
+    """act_col_sum and act_ln_bwd_params against float64 sums of the same (rounded) inputs."""
+    from deep_optimization_b200 import codec
+    torch.manual_seed(shape[0] + shape[1])
+    R, C = shape
+    dy = torch.randn(R, C, device=cuda_device).to(dtype)
+    x = (torch.randn(R, C, device=cuda_device) * 2 + 0.5).to(dtype)
+    s = codec.col_sum(dy)
+    ref = dy.double().sum(0)
+    tol = dy.double().abs().sum(0) * 2e-6 + 1e-6
+    assert s.dtype == torch.float32 and ((s.double() - ref).abs() <= tol).all()
+    y, mean, rstd = torch.ops.aten.native_layer_norm(x, [C], None, None, 1e-5)
+    dg, db = codec.ln_bwd_params(dy, x, mean, rstd)
+    xh = (x.double() - mean.double().view(-1, 1)) * rstd.double().view(-1, 1)
+    ref_g = (dy.double() * xh).sum(0)
+    tol_g = (dy.double() * xh).abs().sum(0) * 4e-6 + 1e-5
+    assert ((dg.double() - ref_g).abs() <= tol_g).all() and ((db.double() - ref).abs() <= tol).all()
+    # and what ATen computes for the same call
+    if dtype != torch.float16:
+        _, tg, tb = torch.ops.aten.native_layer_norm_backward(dy, x, [C], mean, rstd, torch.ones(C, device=cuda_device, dtype=dtype),
+                                                              torch.zeros(C, device=cuda_device, dtype=dtype), [False, True, True])
+        assert ((dg.double() - tg.double()).abs() <= tol_g + tg.double().abs() * 2.0 ** -7).all()
+
+
+def test_column_reductions_reject_bad_layouts(cuda_device):
+    from deep_optimization_b200 import codec
+    with pytest.raises(ValueError):
+        codec.col_sum(torch.randn(16, 12, device=cuda_device))          # 12 columns: not a multiple of 8
+    with pytest.raises(ValueError):
+        codec.col_sum(torch.randn(16, 32, device=cuda_device)[:, ::2])  # rows not contiguous
+    assert codec.col_sum(torch.empty(0, 16, device=cuda_device)).abs().sum() == 0

@@ -168,7 +168,8 @@ def test_linear_weight_gradient_from_packed_input(cuda_device, bits):
         ops.set_fused_dw(True)
     wf, bf, xf = grads[True]
     wu, bu, xu = grads[False]
-    assert torch.equal(bf, bu) and torch.equal(xf, xu)
+    # the bias gradient is a sum of atomics (order not fixed), dx a cuBLAS product of the same operands
+    assert torch.allclose(bf, bu, rtol=1e-5, atol=1e-3) and torch.equal(xf, xu)
     assert (wf - wu).norm() / wu.norm() < 4e-3                     # bf16 rounding of the unfused product
     # and against the exact gradient: the codes' quantisation error only
     exact = g.reshape(-1, 384).t() @ x.reshape(-1, 768)
