@@ -179,3 +179,77 @@ extern "C" int act_ln_bwd_params(const void* dy, const void* x, const float* mea
         default: return launch_col_reduce<ACT_DTYPE_F16, true>(dy, x, mean, rstd, dgamma, dbeta, rows, cols, st);
     }
 }
+
+// ------------------------------------------------------------------ gradient of the q/k/v split
+// act_merge_heads: dst[b, t, s, h, :] = src_s[b, h, t, :] for s = 0..parts-1, dst contiguous
+// [B, T, parts, H, Dh], the sources given by their element strides for b, h and t (last dimension
+// contiguous).  This is the backward of
+//     q, k, v = qkv.view(B, T, 3, H, Dh).permute(2, 0, 3, 1, 4).unbind(0)
+// (Model/ViT/ViT.py:39-42 of the reference): the three gradients an attention kernel returns
+// become the gradient of the qkv projection's output in one pass (232 MB each way for ViT-B/16 at
+// batch 256), where autograd runs a stack of the three and a strided copy of the result (557 +
+// 292 us).  A block takes whole rows (b, t); a thread keeps its (s, h, 16-byte piece) and walks
+// the block's rows, so eight lanes read one 128-byte run of a source and a warp writes 512
+// contiguous bytes.
+namespace act {
+
+struct MergeSrc {
+    const uint8_t* p[4];
+    int64_t sb[4], sh[4], st[4];          // byte strides
+};
+
+__global__ void __launch_bounds__(1024)
+merge_heads_kernel(MergeSrc src, uint8_t* __restrict__ dst, int B, int T, int H, int parts, int pieces_per_head,
+                   int rows_per_block)
+{
+    const int per_row = parts * H * pieces_per_head;         // 16-byte pieces of one (b, t) row of dst
+    const int64_t rows = (int64_t)B * T;
+    const int64_t row0 = (int64_t)blockIdx.x * rows_per_block;
+    for (int piece = threadIdx.x; piece < per_row; piece += blockDim.x) {
+        const int s = piece / (H * pieces_per_head);
+        const int rem = piece - s * (H * pieces_per_head);
+        const int h = rem / pieces_per_head, pp = rem - h * pieces_per_head;
+        const uint8_t* base = src.p[s] + (int64_t)h * src.sh[s] + (int64_t)pp * 16;
+        for (int r = 0; r < rows_per_block; ++r) {
+            const int64_t row = row0 + r;
+            if (row >= rows) break;
+            const int64_t b = row / T, t = row - b * T;
+            const uint4 v = ldg_stream_v4(base + b * src.sb[s] + t * src.st[s]);
+            stg_stream_v4(dst + (row * per_row + piece) * 16, v);
+        }
+    }
+}
+
+}  // namespace act
+
+extern "C" int act_merge_heads(const void* const* srcs, const int64_t* strides, int parts, int B, int H, int T,
+                               int Dh, int elem_bytes, void* dst, void* stream)
+{
+    using namespace act;
+    if (parts < 1 || parts > 4 || B < 0 || H < 0 || T < 0 || Dh < 0) return ACT_ERR_SIZE;
+    if (elem_bytes != 2 && elem_bytes != 4) return ACT_ERR_DTYPE;
+    if (B == 0 || H == 0 || T == 0 || Dh == 0) return ACT_OK;
+    if (!srcs || !strides || !dst) return ACT_ERR_NULL;
+    if (((int64_t)Dh * elem_bytes) & 15) return ACT_ERR_SIZE;              // whole 16-byte pieces per head
+    if ((uintptr_t)dst & 15) return ACT_ERR_ALIGN;
+    MergeSrc ms;
+    for (int s = 0; s < 4; ++s) { ms.p[s] = nullptr; ms.sb[s] = ms.sh[s] = ms.st[s] = 0; }
+    for (int s = 0; s < parts; ++s) {
+        if (!srcs[s]) return ACT_ERR_NULL;
+        ms.p[s] = static_cast<const uint8_t*>(srcs[s]);
+        ms.sb[s] = strides[3 * s] * elem_bytes; ms.sh[s] = strides[3 * s + 1] * elem_bytes; ms.st[s] = strides[3 * s + 2] * elem_bytes;
+        if (((uintptr_t)ms.p[s] | (uint64_t)ms.sb[s] | (uint64_t)ms.sh[s] | (uint64_t)ms.st[s]) & 15) return ACT_ERR_ALIGN;
+    }
+    const int64_t rows = (int64_t)B * T;
+    const int pieces_per_head = Dh * elem_bytes / 16;
+    // about eight resident waves of blocks: a block's rows are contiguous in dst
+    int64_t blocks = stream_grid_for(rows, 8, 8);
+    const int rows_per_block = (int)((rows + blocks - 1) / blocks);
+    blocks = (rows + rows_per_block - 1) / rows_per_block;
+    // one thread per 16-byte piece of a row where a block can hold that many
+    const int per_row = parts * H * pieces_per_head;
+    const int threads = per_row <= 1024 ? ((per_row + 31) & ~31) : 256;
+    merge_heads_kernel<<<(unsigned)blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(
+        ms, static_cast<uint8_t*>(dst), B, T, H, parts, pieces_per_head, rows_per_block);
+    return cudaGetLastError() == cudaSuccess ? ACT_OK : ACT_ERR_LAUNCH;
+}

@@ -3,8 +3,13 @@
 from __future__ import annotations
 
 import torch
+import torch.fx
 import torch.nn.functional as F
 from torch import nn
+
+from ..modules.attention import split_heads
+
+torch.fx.wrap("split_heads")      # a leaf for torch.fx: the Controller's trace keeps the call, not its branches
 
 
 class Attention(nn.Module):
@@ -16,9 +21,10 @@ class Attention(nn.Module):
 
     def forward(self, x):
         B, T, D = x.shape
-        qkv = self.qkv(x).reshape(B, T, 3, self.heads, D // self.heads).permute(2, 0, 3, 1, 4)
-        parts = qkv.unbind(0)      # one stack in backward instead of three zero-filled selects
-        out = F.scaled_dot_product_attention(parts[0], parts[1], parts[2])
+        # the reference's view / permute / index (Model/ViT/ViT.py:39-42) as three strided views,
+        # with a one-pass backward (modules/attention.py)
+        q, k, v = split_heads(self.qkv(x), self.heads)
+        out = F.scaled_dot_product_attention(q, k, v)
         return self.proj(out.transpose(1, 2).reshape(B, T, D))
 
 

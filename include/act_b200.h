@@ -363,6 +363,17 @@ ACT_API int act_ln_bwd_params(const void* dy, const void* x, const float* mean, 
                               int64_t rows, int cols, float* dgamma, float* dbeta, void* stream);
 
 /*
+ * act_merge_heads: dst[b, t, s, h, :] = srcs[s][b, h, t, :] for s < parts (1..4); dst is contiguous
+ * [B, T, parts, H, Dh]; strides = parts x (element stride of b, of h, of t) of the sources, whose
+ * last dimension is contiguous.  Dh * elem_bytes, the sources' byte strides and all bases are
+ * multiples of 16.  The backward of the q/k/v split of a fused qkv projection
+ * (Model/ViT/ViT.py:39-42 of the reference: view, permute, index): the three gradients of the
+ * attention become the gradient of the projection's output in one pass.
+ */
+ACT_API int act_merge_heads(const void* const* srcs, const int64_t* strides, int parts, int B, int H, int T,
+                            int Dh, int elem_bytes, void* dst, void* stream);
+
+/*
  * Greedy bit allocation on the host (no GPU work).
  * Replaces cpp_extension.calc_precision (AC/cpp_extension/src/calc_precision.cc:10-53):
  * b, C, w are int32 arrays of length n; b is updated in place until sum(b*w) <= target.

@@ -316,3 +316,39 @@ def test_whole_model_gradients_at_8_bits(cuda_device, name, channels_last):
     for k in last:
         g = dict(net.named_parameters())[k].grad.float()
         assert ((g - ref_grads[k]).norm() / ref_grads[k].norm()).item() < 0.02, k
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("dims", [(4, 197, 12, 64), (2, 5, 3, 8), (1, 1, 1, 16)])
+def test_split_heads_backward_is_one_gather(cuda_device, dtype, dims):
+    """split_heads returns the views the plain view / permute / unbind gives and its backward
+    (act_merge_heads) equals autograd's stack-and-copy bit for bit, for contiguous and for strided
+    gradients, with one of the three gradients missing, and through attention."""
+    from deep_optimization_b200.modules.attention import split_heads
+    B, T, H, Dh = dims
+    torch.manual_seed(B * T + H)
+    qkv = torch.randn(B, T, 3 * H * Dh, device=cuda_device).to(dtype)
+    a = qkv.clone().requires_grad_()
+    b = qkv.clone().requires_grad_()
+    qa, ka, va = split_heads(a, H)
+    qb, kb, vb = b.view(B, T, 3, H, Dh).permute(2, 0, 3, 1, 4).unbind(0)
+    assert torch.equal(qa, qb) and torch.equal(ka, kb) and torch.equal(va, vb)
+    assert qa.data_ptr() == a.data_ptr()                               # views, not copies
+    g = [torch.randn(B, H, T, Dh, device=cuda_device).to(dtype) for _ in range(3)]
+    g[1] = torch.randn(B, T, H, Dh, device=cuda_device).to(dtype).transpose(1, 2)     # a strided gradient
+    torch.autograd.backward([qa, ka, va], g)
+    torch.autograd.backward([qb, kb, vb], g)
+    assert torch.equal(a.grad, b.grad)
+    # v unused: its gradient is zero
+    a.grad = None; b.grad = None
+    qa, ka, _ = split_heads(a, H)
+    qb, kb, _ = b.view(B, T, 3, H, Dh).permute(2, 0, 3, 1, 4).unbind(0)
+    (qa * 2 + ka).sum().backward(); (qb * 2 + kb).sum().backward()
+    assert torch.equal(a.grad, b.grad)
+    if dtype == torch.bfloat16 and Dh >= 8:
+        a.grad = None; b.grad = None
+        oa = nn.functional.scaled_dot_product_attention(*split_heads(a, H))
+        ob = nn.functional.scaled_dot_product_attention(*b.view(B, T, 3, H, Dh).permute(2, 0, 3, 1, 4).unbind(0))
+        go = torch.randn_like(oa)
+        oa.backward(go); ob.backward(go)
+        assert torch.equal(oa, ob) and torch.equal(a.grad, b.grad)
