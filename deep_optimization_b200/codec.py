@@ -742,3 +742,76 @@ def ln_bwd_params(dy: torch.Tensor, x: torch.Tensor, mean: torch.Tensor, rstd: t
                                            _stream_ptr(dy))
     _lib.check(rc, "act_ln_bwd_params")
     return dgamma, dbeta
+
+
+# ---------------------------------------------------------------- LayerNorm fused with the codec
+
+def ln_fused_applies(x: torch.Tensor, group_size: int, bits: int) -> bool:
+    """act_ln_fwd_quant_pack / act_ln_bwd_from_packed take a contiguous CUDA tensor of a codec
+    dtype whose last dimension is a multiple of group_size (32..256) and at most 1024."""
+    C = x.shape[-1] if x.dim() else 0
+    return (x.is_cuda and x.dtype in _DTYPES and x.dim() >= 2 and x.is_contiguous() and x.data_ptr() % 16 == 0
+            and bits in (1, 2, 4, 8) and group_size in (32, 64, 128, 256) and 0 < C <= 1024 and C % group_size == 0)
+
+
+def ln_fwd_quant_pack(x: torch.Tensor, weight: Optional[torch.Tensor], bias: Optional[torch.Tensor], eps: float,
+                      bits: int, group_size: int, seed: Optional[int] = None, offset: Optional[int] = None,
+                      flags: int = 0):
+    """(y, mean, rstd, packed, scale, min): LayerNorm over the last dimension and the packed input,
+    the latter identical to quant_pack(x, bits, group_size, seed=seed, offset=offset, flags=flags)."""
+    global _next_offset
+    if not x.is_cuda:
+        raise RuntimeError("ln_fwd_quant_pack needs a CUDA tensor: there is no CPU path")
+    if not ln_fused_applies(x, group_size, bits):
+        raise ValueError("ln_fwd_quant_pack: unsupported shape, type or group size")
+    C = x.shape[-1]
+    rows = x.numel() // C
+    ng = x.numel() // group_size
+    nwords = _packed_words(bits, group_size, False)
+    y = torch.empty_like(x)
+    mean = torch.empty(rows, dtype=torch.float32, device=x.device)
+    rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+    packed = torch.empty((ng, nwords), dtype=torch.int32, device=x.device)
+    scale = torch.empty(ng, dtype=torch.float32, device=x.device)
+    mn = torch.empty(ng, dtype=torch.float32, device=x.device)
+    w = None if weight is None else weight.to(torch.float32).contiguous()
+    b = None if bias is None else bias.to(torch.float32).contiguous()
+    if seed is None:
+        seed = _stream_seed()
+    if offset is None:
+        offset = _next_offset
+        _next_offset += 1
+    with _device_of(x):
+        rc = _lib.load().act_ln_fwd_quant_pack(
+            x.data_ptr(), _DTYPES[x.dtype], rows, C, None if w is None else w.data_ptr(),
+            None if b is None else b.data_ptr(), float(eps), group_size, bits, seed & 0xFFFFFFFFFFFFFFFF,
+            offset & 0xFFFFFFFFFFFFFFFF, flags, y.data_ptr(), mean.data_ptr(), rstd.data_ptr(), packed.data_ptr(),
+            scale.data_ptr(), mn.data_ptr(), _stream_ptr(x))
+    _lib.check(rc, "act_ln_fwd_quant_pack")
+    return y, mean, rstd, packed, scale, mn
+
+
+def ln_bwd_from_packed(dy: torch.Tensor, packed: torch.Tensor, scale: torch.Tensor, mn: torch.Tensor, bits: int,
+                       group_size: int, mean: torch.Tensor, rstd: torch.Tensor, weight: Optional[torch.Tensor]):
+    """(dx, dgamma, dbeta) of a LayerNorm over the last dimension whose input is given packed."""
+    if not dy.is_cuda:
+        raise RuntimeError("ln_bwd_from_packed needs CUDA tensors: there is no CPU path")
+    if not ln_fused_applies(dy, group_size, bits):
+        raise ValueError("ln_bwd_from_packed: unsupported shape, type or group size")
+    C = dy.shape[-1]
+    rows = dy.numel() // C
+    if scale.numel() * group_size != dy.numel() or mean.numel() != rows or rstd.numel() != rows:
+        raise ValueError("ln_bwd_from_packed: packed input and statistics do not match dy")
+    dx = torch.empty_like(dy)
+    dgamma = torch.empty(C, dtype=torch.float32, device=dy.device)
+    dbeta = torch.empty(C, dtype=torch.float32, device=dy.device)
+    w = None if weight is None else weight.to(torch.float32).contiguous()
+    scale = scale.reshape(-1).contiguous()
+    mn = mn.reshape(-1).contiguous()
+    with _device_of(dy):
+        rc = _lib.load().act_ln_bwd_from_packed(
+            dy.data_ptr(), _DTYPES[dy.dtype], rows, C, packed.data_ptr(), scale.data_ptr(), mn.data_ptr(), group_size,
+            bits, mean.data_ptr(), rstd.data_ptr(), None if w is None else w.data_ptr(), dx.data_ptr(),
+            dgamma.data_ptr(), dbeta.data_ptr(), _stream_ptr(dy))
+    _lib.check(rc, "act_ln_bwd_from_packed")
+    return dx, dgamma, dbeta

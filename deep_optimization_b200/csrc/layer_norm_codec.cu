@@ -1,0 +1,404 @@
+// LayerNorm over the last dimension fused with the codec of its INPUT, sm_100a.
+//
+//   act_ln_fwd_quant_pack:  y = (x - mean) * rstd * weight + bias, mean and rstd per row (fp32), and
+//                           the packed x (codes, scale, min) exactly as act_quant_pack would write
+//                           them for the same seed and offset: x is read once instead of twice, and
+//                           ATen's forward kernel (120 us on bf16 [50432, 768]) is not needed.
+//   act_ln_bwd_from_packed: dx, dgamma, dbeta from dy, the packed x, mean, rstd and weight: x is
+//                           decoded in registers (the arithmetic of act_dequant_unpack with a bf16
+//                           result, i.e. the tensor the unfused path hands to ATen), so the [rows, C]
+//                           dequantised copy, ATen's dx kernel and the parameter-gradient pass
+//                           collapse into one read of dy and the codes and one write of dx.
+//
+// One warp per row, rows dealt out round-robin to a persistent grid.  Lane l holds the 8-element
+// vectors l, l + 32, ... of its row (at most kMaxVecs: C <= 1024), so a warp's loads are 512
+// contiguous bytes; a group of G <= 256 elements is G/8 neighbouring lanes of one such step, its
+// minimum and maximum come from xor shuffles.  The hash counter of a piece is its index in the flat
+// tensor, as in quant_pack_kernel; regular groups use the fixed-point encoder, a warp with an
+// irregular group (denormal, huge or non-finite range) the general one, which gives the same codes
+// for the regular groups.
+//
+// The reference has no such operator (it leaves LayerNorm to PyTorch,
+// Activation_Compression/controller.py:87); the evaluation configuration for ViT-B/16 counts
+// LayerNorm inputs among the compressed activations.
+#include "codec_pack_kernel.cuh"
+
+namespace act {
+
+constexpr int kLnThreads = 256;
+constexpr int kLnWarps = kLnThreads / 32;
+constexpr int kMaxVecs = 4;                // 8-element vectors per lane: C <= 32 * 8 * 4 = 1024
+
+template <int DT> __device__ __forceinline__ void ln_load8(const uint8_t* p, float (&f)[8]) {
+    if (ElemT<DT>::bytes == 4) {
+        const uint4 a = ldg_stream_v4(p), b = ldg_stream_v4(p + 16);
+        f[0] = __uint_as_float(a.x); f[1] = __uint_as_float(a.y); f[2] = __uint_as_float(a.z); f[3] = __uint_as_float(a.w);
+        f[4] = __uint_as_float(b.x); f[5] = __uint_as_float(b.y); f[6] = __uint_as_float(b.z); f[7] = __uint_as_float(b.w);
+    } else {
+        constexpr int D16 = (DT == ACT_DTYPE_F32) ? ACT_DTYPE_BF16 : DT;
+        const uint4 a = ldg_stream_v4(p);
+        const uint32_t h[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) { f[2 * k] = widen_lo<D16>(h[k]); f[2 * k + 1] = widen_hi<D16>(h[k]); }
+    }
+}
+
+template <int DT> __device__ __forceinline__ void ln_store8(uint8_t* p, const float (&f)[8]) {
+    if (DT == ACT_DTYPE_F32) {
+        stg_stream_v4(p, make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3])));
+        stg_stream_v4(p + 16, make_uint4(__float_as_uint(f[4]), __float_as_uint(f[5]), __float_as_uint(f[6]), __float_as_uint(f[7])));
+    } else {
+        uint32_t o[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            if (DT == ACT_DTYPE_BF16) { const __nv_bfloat162 t = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]); o[i] = *reinterpret_cast<const uint32_t*>(&t); }
+            else { const __half2 t = __floats2half2_rn(f[2 * i], f[2 * i + 1]); o[i] = *reinterpret_cast<const uint32_t*>(&t); }
+        }
+        stg_stream_v4(p, make_uint4(o[0], o[1], o[2], o[3]));
+    }
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    return v;
+}
+
+template <int BITS> __device__ __forceinline__ void store_codes(uint8_t* p, uint32_t a0, uint32_t a1) {
+    if (BITS == 1) *p = (uint8_t)a0;
+    else if (BITS == 2) *reinterpret_cast<uint16_t*>(p) = (uint16_t)a0;
+    else if (BITS == 4) *reinterpret_cast<uint32_t*>(p) = a0;
+    else *reinterpret_cast<uint2*>(p) = make_uint2(a0, a1);
+}
+
+// ------------------------------------------------------------------------------ forward
+template <int DT, int BITS, int NM>
+__global__ void __launch_bounds__(kLnThreads)
+ln_fwd_pack_kernel(const uint8_t* __restrict__ x, const float* __restrict__ weight, const float* __restrict__ bias,
+                   uint8_t* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out,
+                   uint8_t* __restrict__ packed, float* __restrict__ scale_out, float* __restrict__ min_out,
+                   int64_t rows, int C, float eps, int log2_L, uint32_t key_lo, uint32_t key_hi)
+{
+    constexpr int QMAX = (1 << BITS) - 1;
+    constexpr int EB = ElemT<DT>::bytes;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nvec = C >> 3;
+    const int steps = (nvec + 31) >> 5;
+    const int L = 1 << log2_L;                               // lanes per group
+    const float inv_c = 1.0f / (float)C;
+    // weight and bias of the lane's columns stay in registers for all its rows
+    float w[kMaxVecs][8], b[kMaxVecs][8];
+#pragma unroll
+    for (int k = 0; k < kMaxVecs; ++k) {
+        const int v = k * 32 + lane;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const bool on = k < steps && v < nvec;
+            w[k][i] = (on && weight) ? __ldg(weight + v * 8 + i) : 1.0f;
+            b[k][i] = (on && bias) ? __ldg(bias + v * 8 + i) : 0.0f;
+        }
+    }
+    const int64_t warp_stride = (int64_t)gridDim.x * kLnWarps;
+    for (int64_t row = (int64_t)blockIdx.x * kLnWarps + warp; row < rows; row += warp_stride) {
+        const uint8_t* xr = x + row * C * EB;
+        float xf[kMaxVecs][8];
+        float sum = 0.0f;
+#pragma unroll
+        for (int k = 0; k < kMaxVecs; ++k) {
+            const int v = k * 32 + lane;
+            if (k < steps && v < nvec) {
+                ln_load8<DT>(xr + (int64_t)v * 8 * EB, xf[k]);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) sum += xf[k][i];
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) xf[k][i] = 0.0f;
+            }
+        }
+        const float mean = warp_sum(sum) * inv_c;
+        float sq = 0.0f;
+#pragma unroll
+        for (int k = 0; k < kMaxVecs; ++k) {
+            const int v = k * 32 + lane;
+            if (k < steps && v < nvec) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) { const float d = xf[k][i] - mean; sq = fmaf(d, d, sq); }
+            }
+        }
+        const float rstd = 1.0f / sqrtf(warp_sum(sq) * inv_c + eps);
+        if (lane == 0) { mean_out[row] = mean; rstd_out[row] = rstd; }
+
+        uint8_t* yr = y + row * C * EB;
+        const int64_t piece0 = row * nvec;                   // index of the row's first 8-element piece
+#pragma unroll
+        for (int k = 0; k < kMaxVecs; ++k) {
+            if (k >= steps) break;                           // warp-uniform
+            const int v = k * 32 + lane;
+            const bool on = v < nvec;
+            if (on) {
+                float yv[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) yv[i] = fmaf((xf[k][i] - mean) * rstd, w[k][i], b[k][i]);
+                ln_store8<DT>(yr + (int64_t)v * 8 * EB, yv);
+            }
+            // ---- the codec of x: one group = L neighbouring lanes of this step
+            float mn = xf[k][0], mx = xf[k][0];
+#pragma unroll
+            for (int i = 1; i < 7; i += 2) { mn = fmin3_nan(mn, xf[k][i], xf[k][i + 1]); mx = fmax3_nan(mx, xf[k][i], xf[k][i + 1]); }
+            mn = fmin_nan(mn, xf[k][7]); mx = fmax_nan(mx, xf[k][7]);
+            for (int off = L >> 1; off > 0; off >>= 1) {
+                mn = fmin_nan(mn, __shfl_xor_sync(0xffffffffu, mn, off));
+                mx = fmax_nan(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+            }
+            const float range = __fsub_rn(mx, mn);
+            const bool fast = !on || (range == 0.0f) || (range >= 0x1p-50f && range <= 0x1p50f);
+            const bool all_fast = __all_sync(0xffffffffu, fast);
+            float s;
+            if (BITS == 1) s = range;
+            else if (all_fast) s = div_by_scale(range, (float)QMAX, 1.0f / (float)QMAX);
+            else s = __fdiv_rn(range, (float)QMAX);
+            if (!(s > 0.0f)) s = 1.0f;
+            const float rs = __frcp_rn(s);
+            const int64_t piece = piece0 + v;
+            if (on && (lane & (L - 1)) == 0) {
+                const int64_t g = piece >> log2_L;
+                scale_out[g] = s;
+                min_out[g] = mn;
+            }
+            const uint32_t ctr_lo = (uint32_t)piece, ctr_hi = (uint32_t)((uint64_t)piece >> 32) ^ key_hi;
+            uint32_t a0, a1;
+            if (all_fast) {
+                encode_piece_fx<DT, BITS, false, NM>(make_uint4(0u, 0u, 0u, 0u), xf[k], mn, pack2(-mn, -mn), pack2(rs, rs),
+                                                     ctr_lo, ctr_hi, key_lo, a0, a1);
+            } else {
+                float u8[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+                encode_piece_slow<BITS, NM>(xf[k], u8, mn, s, rs, fast, ctr_lo, ctr_hi, key_lo, a0, a1);
+            }
+            if (on) store_codes<BITS>(packed + piece * BITS, a0, a1);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------ backward
+// eight codes -> eight values of the input as act_dequant_unpack writes them with a bf16 result:
+// fp32 fma(code, scale, min), rounded to bf16
+template <int BITS>
+__device__ __forceinline__ void ln_decode8(const uint8_t* p, float s, float m, float (&xv)[8]) {
+    uint64_t wbits;
+    if (BITS == 1) wbits = __ldg(p);
+    else if (BITS == 2) wbits = __ldg(reinterpret_cast<const uint16_t*>(p));
+    else if (BITS == 4) wbits = __ldg(reinterpret_cast<const uint32_t*>(p));
+    else wbits = __ldg(reinterpret_cast<const unsigned long long*>(p));
+    constexpr uint64_t MASK = (1ull << BITS) - 1ull;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const float c = (float)(uint32_t)((wbits >> (i * BITS)) & MASK);
+        xv[i] = __bfloat162float(__float2bfloat16_rn(__fmaf_rn(c, s, m)));
+    }
+}
+
+template <int DT, int BITS>
+__global__ void __launch_bounds__(kLnThreads)
+ln_bwd_packed_kernel(const uint8_t* __restrict__ dy, const uint8_t* __restrict__ packed, const float* __restrict__ scale,
+                     const float* __restrict__ mn, const float* __restrict__ mean, const float* __restrict__ rstd,
+                     const float* __restrict__ weight, uint8_t* __restrict__ dx, float* __restrict__ dgamma,
+                     float* __restrict__ dbeta, int64_t rows, int C, int log2_L)
+{
+    constexpr int EB = ElemT<DT>::bytes;
+    __shared__ float s_acc[kLnWarps][2][32 * 8 + 8];         // one step's partial sums per warp
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nvec = C >> 3;
+    const int steps = (nvec + 31) >> 5;
+    const float inv_c = 1.0f / (float)C;
+    float w[kMaxVecs][8], ag[kMaxVecs][8], ab[kMaxVecs][8];
+#pragma unroll
+    for (int k = 0; k < kMaxVecs; ++k) {
+        const int v = k * 32 + lane;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            w[k][i] = (k < steps && v < nvec && weight) ? __ldg(weight + v * 8 + i) : 1.0f;
+            ag[k][i] = 0.0f; ab[k][i] = 0.0f;
+        }
+    }
+    const int64_t warp_stride = (int64_t)gridDim.x * kLnWarps;
+    for (int64_t row = (int64_t)blockIdx.x * kLnWarps + warp; row < rows; row += warp_stride) {
+        const float mu = __ldg(mean + row), rs = __ldg(rstd + row);
+        const uint8_t* dyr = dy + row * C * EB;
+        const int64_t piece0 = row * nvec;
+        float xh[kMaxVecs][8], g[kMaxVecs][8];
+        float s1 = 0.0f, s2 = 0.0f;
+#pragma unroll
+        for (int k = 0; k < kMaxVecs; ++k) {
+            const int v = k * 32 + lane;
+            if (k < steps && v < nvec) {
+                const int64_t piece = piece0 + v;
+                const int64_t gi = piece >> log2_L;
+                float xv[8], dv[8];
+                ln_decode8<BITS>(packed + piece * BITS, __ldg(scale + gi), __ldg(mn + gi), xv);
+                ln_load8<DT>(dyr + (int64_t)v * 8 * EB, dv);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    xh[k][i] = (xv[i] - mu) * rs;
+                    g[k][i] = dv[i] * w[k][i];
+                    s1 = fmaf(g[k][i], xh[k][i], s1);
+                    s2 += g[k][i];
+                    ag[k][i] = fmaf(dv[i], xh[k][i], ag[k][i]);
+                    ab[k][i] += dv[i];
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) { xh[k][i] = 0.0f; g[k][i] = 0.0f; }
+            }
+        }
+        const float c1 = warp_sum(s1) * inv_c, c2 = warp_sum(s2) * inv_c;
+        uint8_t* dxr = dx + row * C * EB;
+#pragma unroll
+        for (int k = 0; k < kMaxVecs; ++k) {
+            const int v = k * 32 + lane;
+            if (k < steps && v < nvec) {
+                float o[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) o[i] = rs * (g[k][i] - c2 - xh[k][i] * c1);
+                ln_store8<DT>(dxr + (int64_t)v * 8 * EB, o);
+            }
+        }
+    }
+    // the block's warps own the same columns: combine them step by step in shared memory, then
+    // one atomic per block and column
+#pragma unroll
+    for (int k = 0; k < kMaxVecs; ++k) {
+        if (k >= steps) break;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { s_acc[warp][0][lane * 8 + i] = ag[k][i]; s_acc[warp][1][lane * 8 + i] = ab[k][i]; }
+        __syncthreads();
+        for (int c = threadIdx.x; c < 256; c += kLnThreads) {
+            const int col = k * 256 + c;
+            if (col < C) {
+                float tg = 0.0f, tb = 0.0f;
+#pragma unroll
+                for (int ww = 0; ww < kLnWarps; ++ww) { tg += s_acc[ww][0][c]; tb += s_acc[ww][1][c]; }
+                atomicAdd(dgamma + col, tg);
+                atomicAdd(dbeta + col, tb);
+            }
+        }
+        __syncthreads();
+    }
+}
+
+template <typename K>
+static int ln_grid(K kernel, int64_t rows) {
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kLnThreads, 0) != cudaSuccess || per_sm < 1) per_sm = 1;
+    return stream_grid_for((rows + kLnWarps - 1) / kLnWarps, per_sm);
+}
+
+static int ln_check(int dtype, int64_t rows, int C, int group_size, int bits) {
+    if (rows < 0 || C < 0) return ACT_ERR_SIZE;
+    if (dtype != ACT_DTYPE_F32 && dtype != ACT_DTYPE_BF16 && dtype != ACT_DTYPE_F16) return ACT_ERR_DTYPE;
+    if (bits != 1 && bits != 2 && bits != 4 && bits != 8) return ACT_ERR_BITS;
+    if (group_size < 32 || group_size > 256 || (group_size & (group_size - 1))) return ACT_ERR_GROUP;
+    if (C == 0 || (C % group_size) || C > 32 * 8 * kMaxVecs) return ACT_ERR_SIZE;   // whole groups per row, C <= 1024
+    return ACT_OK;
+}
+
+template <int DT, int BITS>
+int ln_fwd_launch(bool nearest, const void* x, const float* weight, const float* bias, void* y, float* mean, float* rstd,
+                  void* packed, float* scale, float* mn, int64_t rows, int C, float eps, int log2_L, uint64_t seed,
+                  uint64_t offset, cudaStream_t st)
+{
+    const uint64_t key = hash_key(hash_key(seed) + offset);
+#define ACT_LN_FWD(NM) \
+    ln_fwd_pack_kernel<DT, BITS, NM><<<ln_grid(ln_fwd_pack_kernel<DT, BITS, NM>, rows), kLnThreads, 0, st>>>( \
+        static_cast<const uint8_t*>(x), weight, bias, static_cast<uint8_t*>(y), mean, rstd, static_cast<uint8_t*>(packed), \
+        scale, mn, rows, C, eps, log2_L, (uint32_t)key, (uint32_t)(key >> 32))
+    if (nearest) ACT_LN_FWD(kNoiseConst); else ACT_LN_FWD(kNoiseHash);
+#undef ACT_LN_FWD
+    return cudaGetLastError() == cudaSuccess ? ACT_OK : ACT_ERR_LAUNCH;
+}
+
+template <int DT>
+int ln_fwd_bits(int bits, bool nearest, const void* x, const float* weight, const float* bias, void* y, float* mean,
+                float* rstd, void* packed, float* scale, float* mn, int64_t rows, int C, float eps, int log2_L,
+                uint64_t seed, uint64_t offset, cudaStream_t st)
+{
+    switch (bits) {
+        case 1: return ln_fwd_launch<DT, 1>(nearest, x, weight, bias, y, mean, rstd, packed, scale, mn, rows, C, eps, log2_L, seed, offset, st);
+        case 2: return ln_fwd_launch<DT, 2>(nearest, x, weight, bias, y, mean, rstd, packed, scale, mn, rows, C, eps, log2_L, seed, offset, st);
+        case 4: return ln_fwd_launch<DT, 4>(nearest, x, weight, bias, y, mean, rstd, packed, scale, mn, rows, C, eps, log2_L, seed, offset, st);
+        default: return ln_fwd_launch<DT, 8>(nearest, x, weight, bias, y, mean, rstd, packed, scale, mn, rows, C, eps, log2_L, seed, offset, st);
+    }
+}
+
+template <int DT, int BITS>
+int ln_bwd_launch(const void* dy, const void* packed, const float* scale, const float* mn, const float* mean,
+                  const float* rstd, const float* weight, void* dx, float* dgamma, float* dbeta, int64_t rows, int C,
+                  int log2_L, cudaStream_t st)
+{
+    ln_bwd_packed_kernel<DT, BITS><<<ln_grid(ln_bwd_packed_kernel<DT, BITS>, rows), kLnThreads, 0, st>>>(
+        static_cast<const uint8_t*>(dy), static_cast<const uint8_t*>(packed), scale, mn, mean, rstd, weight,
+        static_cast<uint8_t*>(dx), dgamma, dbeta, rows, C, log2_L);
+    return cudaGetLastError() == cudaSuccess ? ACT_OK : ACT_ERR_LAUNCH;
+}
+
+template <int DT>
+int ln_bwd_bits(int bits, const void* dy, const void* packed, const float* scale, const float* mn, const float* mean,
+                const float* rstd, const float* weight, void* dx, float* dgamma, float* dbeta, int64_t rows, int C,
+                int log2_L, cudaStream_t st)
+{
+    switch (bits) {
+        case 1: return ln_bwd_launch<DT, 1>(dy, packed, scale, mn, mean, rstd, weight, dx, dgamma, dbeta, rows, C, log2_L, st);
+        case 2: return ln_bwd_launch<DT, 2>(dy, packed, scale, mn, mean, rstd, weight, dx, dgamma, dbeta, rows, C, log2_L, st);
+        case 4: return ln_bwd_launch<DT, 4>(dy, packed, scale, mn, mean, rstd, weight, dx, dgamma, dbeta, rows, C, log2_L, st);
+        default: return ln_bwd_launch<DT, 8>(dy, packed, scale, mn, mean, rstd, weight, dx, dgamma, dbeta, rows, C, log2_L, st);
+    }
+}
+
+}  // namespace act
+
+extern "C" int act_ln_fwd_quant_pack(const void* x, int dtype, int64_t rows, int cols, const float* weight,
+                                     const float* bias, double eps, int group_size, int bits, uint64_t seed,
+                                     uint64_t offset, int flags, void* y, float* mean, float* rstd, void* packed,
+                                     float* scale, float* min, void* stream)
+{
+    using namespace act;
+    const int rc = ln_check(dtype, rows, cols, group_size, bits);
+    if (rc != ACT_OK) return rc;
+    if (flags & ~ACT_FLAG_ROUND_NEAREST) return ACT_ERR_UNSUPPORTED;
+    if (rows == 0) return ACT_OK;
+    if (!x || !y || !mean || !rstd || !packed || !scale || !min) return ACT_ERR_NULL;
+    if (((uintptr_t)x | (uintptr_t)y | (uintptr_t)packed) & 15) return ACT_ERR_ALIGN;
+    int log2_L = 0;
+    while ((8 << log2_L) < group_size) ++log2_L;
+    const bool nearest = (flags & ACT_FLAG_ROUND_NEAREST) != 0;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    switch (dtype) {
+        case ACT_DTYPE_F32: return ln_fwd_bits<ACT_DTYPE_F32>(bits, nearest, x, weight, bias, y, mean, rstd, packed, scale, min, rows, cols, (float)eps, log2_L, seed, offset, st);
+        case ACT_DTYPE_BF16: return ln_fwd_bits<ACT_DTYPE_BF16>(bits, nearest, x, weight, bias, y, mean, rstd, packed, scale, min, rows, cols, (float)eps, log2_L, seed, offset, st);
+        default: return ln_fwd_bits<ACT_DTYPE_F16>(bits, nearest, x, weight, bias, y, mean, rstd, packed, scale, min, rows, cols, (float)eps, log2_L, seed, offset, st);
+    }
+}
+
+extern "C" int act_ln_bwd_from_packed(const void* dy, int dtype, int64_t rows, int cols, const void* packed,
+                                      const float* scale, const float* min, int group_size, int bits,
+                                      const float* mean, const float* rstd, const float* weight, void* dx,
+                                      float* dgamma, float* dbeta, void* stream)
+{
+    using namespace act;
+    const int rc = ln_check(dtype, rows, cols, group_size, bits);
+    if (rc != ACT_OK) return rc;
+    if (!dgamma || !dbeta) return ACT_ERR_NULL;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (cudaMemsetAsync(dgamma, 0, (size_t)cols * sizeof(float), st) != cudaSuccess ||
+        cudaMemsetAsync(dbeta, 0, (size_t)cols * sizeof(float), st) != cudaSuccess) return ACT_ERR_LAUNCH;
+    if (rows == 0) return ACT_OK;
+    if (!dy || !packed || !scale || !min || !mean || !rstd || !dx) return ACT_ERR_NULL;
+    if (((uintptr_t)dy | (uintptr_t)dx) & 15) return ACT_ERR_ALIGN;
+    if ((uintptr_t)packed & 7) return ACT_ERR_ALIGN;
+    int log2_L = 0;
+    while ((8 << log2_L) < group_size) ++log2_L;
+    switch (dtype) {
+        case ACT_DTYPE_F32: return ln_bwd_bits<ACT_DTYPE_F32>(bits, dy, packed, scale, min, mean, rstd, weight, dx, dgamma, dbeta, rows, cols, log2_L, st);
+        case ACT_DTYPE_BF16: return ln_bwd_bits<ACT_DTYPE_BF16>(bits, dy, packed, scale, min, mean, rstd, weight, dx, dgamma, dbeta, rows, cols, log2_L, st);
+        default: return ln_bwd_bits<ACT_DTYPE_F16>(bits, dy, packed, scale, min, mean, rstd, weight, dx, dgamma, dbeta, rows, cols, log2_L, st);
+    }
+}

@@ -196,13 +196,39 @@ class _DOLayerNorm(Function):
     """LayerNorm that keeps its input compressed.  The reference's swap list has no LayerNorm
     (Activation_Compression/controller.py:87); the evaluation configuration for ViT-B/16 names
     LayerNorm inputs among the compressed activations, so the input goes through the same
-    `unified_quantize` boundary as a Linear input.  Forward is PyTorch's native kernel (which
-    also returns the per-row mean and inverse deviation, kept in fp32: 8 bytes per row); backward
-    decodes the input and calls the native backward with those statistics."""
+    quantise boundary as a Linear input.  Where the layout allows (last dimension a multiple of
+    the group size, at most 1024, flat grouping, one of the two fixed-point modes) forward is one
+    kernel that normalises and packs the input it has just read, and backward one kernel that
+    decodes it in registers; otherwise forward is ATen's kernel followed by `unified_quantize`,
+    backward `unified_dequantize`, ATen's dx and this library's parameter gradients.  The per-row
+    mean and inverse deviation are kept in fp32 (8 bytes per row)."""
+
+    @staticmethod
+    def _fused(input, normalized_shape, m):
+        return (len(normalized_shape) == 1 and normalized_shape[0] == input.shape[-1] and input.dim() in (2, 3)
+                and not m["pack_only"] and not m["AVG_ALAM"] and act_kernels.get_mode() in ("baseline", "nearest")
+                and input.numel() // input.shape[0] % m["group_size"] == 0
+                and codec.ln_fused_applies(input, m["group_size"], m["bits"]))
 
     @staticmethod
     @custom_fwd(device_type="cuda")
     def forward(ctx, input, normalized_shape, weight, bias, eps, target_name, meta):
+        m = meta[f"{target_name}"]
+        ctx.normalized_shape = list(normalized_shape)
+        ctx.param_dtypes = (None if weight is None else weight.dtype, None if bias is None else bias.dtype)
+        input = input.contiguous()
+        if _DOLayerNorm._fused(input, ctx.normalized_shape, m):
+            flags = _lib.ACT_FLAG_ROUND_NEAREST if act_kernels.get_mode() == "nearest" else 0
+            y, mean, rstd, packed, scale, mn = codec.ln_fwd_quant_pack(input, weight, bias, eps, m["bits"],
+                                                                       m["group_size"], flags=flags)
+            # the tensors and the 14-entry meta `quantize` returns for a flat grouping of this input
+            n = input.shape[0]
+            G = input.numel() // n // m["group_size"]
+            ctx.q_meta = (m["bits"], False, m["group_size"], m["act_padding"], n, G, 0, 0, False, False, False,
+                          m["AVG_ALAM"], m["ALAM_BITS"], input.shape)
+            ctx.fused = True
+            ctx.save_for_backward(packed, scale.view(n, G), mn.view(n, G), mean, rstd, weight, bias)
+            return y
         w = None if weight is None else weight.to(input.dtype)
         b = None if bias is None else bias.to(input.dtype)
         # in the input's own type (statistics are fp32 inside the kernel): under autocast the stock
@@ -212,8 +238,7 @@ class _DOLayerNorm(Function):
             y, mean, rstd = torch.ops.aten.native_layer_norm(input, list(normalized_shape), w, b, eps)
         q_tensors, q_meta, _ = unified_quantize(input, None, target_name, meta, clamp=False, clamp_alpha=0.0)
         ctx.q_meta = q_meta
-        ctx.normalized_shape = list(normalized_shape)
-        ctx.param_dtypes = (None if weight is None else weight.dtype, None if bias is None else bias.dtype)
+        ctx.fused = False
         ctx.save_for_backward(q_tensors[0], q_tensors[1], q_tensors[2], mean, rstd, weight, bias)
         return y
 
@@ -221,12 +246,17 @@ class _DOLayerNorm(Function):
     @custom_bwd(device_type="cuda")
     def backward(ctx, dy):
         packed, scale, mn, mean, rstd, weight, bias = ctx.saved_tensors
-        x = unified_dequantize((packed, scale, mn), ctx.q_meta, None).to(dy.dtype)
-        w = None if weight is None else weight.to(dy.dtype)
-        b = None if bias is None else bias.to(dy.dtype)
         mask = [bool(ctx.needs_input_grad[0]), weight is not None and bool(ctx.needs_input_grad[2]),
                 bias is not None and bool(ctx.needs_input_grad[3])]
-        dy, x = dy.contiguous(), x.contiguous()
+        dy = dy.contiguous()
+        if ctx.fused and codec.ln_fused_applies(dy, ctx.q_meta[2], ctx.q_meta[0]):
+            dx, dw, db = codec.ln_bwd_from_packed(dy, packed, scale, mn, ctx.q_meta[0], ctx.q_meta[2], mean, rstd, weight)
+            wd, bd = ctx.param_dtypes
+            return (dx if mask[0] else None, None, dw.to(wd) if mask[1] else None, db.to(bd) if mask[2] else None,
+                    None, None, None)
+        x = unified_dequantize((packed, scale, mn), ctx.q_meta, None).to(dy.dtype).contiguous()
+        w = None if weight is None else weight.to(dy.dtype)
+        b = None if bias is None else bias.to(dy.dtype)
         # the two parameter gradients are column sums over all rows: this library's one-pass
         # reduction (ATen's kernel for them takes 430 us on bf16 [50432, 768], this one about 30);
         # dx stays ATen's

@@ -363,6 +363,29 @@ ACT_API int act_ln_bwd_params(const void* dy, const void* x, const float* mean, 
                               int64_t rows, int cols, float* dgamma, float* dbeta, void* stream);
 
 /*
+ * LayerNorm over the last dimension of a row-major [rows, cols] tensor, fused with the codec of
+ * its input (cols a multiple of group_size, group_size in 32..256, cols <= 1024; weight and bias
+ * fp32 [cols] or NULL; flags 0 or ACT_FLAG_ROUND_NEAREST).
+ *   act_ln_fwd_quant_pack: y = (x - mean) * rstd * weight + bias in x's type, mean and rstd fp32
+ *       [rows] (biased variance, 1/sqrt(var + eps)), and packed / scale / min of x bit for bit what
+ *       act_quant_pack writes for the same (seed, offset, flags): x is read once.
+ *   act_ln_bwd_from_packed: dx (dy's type), dgamma and dbeta (fp32 [cols], overwritten; atomics, so
+ *       their summation order is not fixed) from dy, the packed x, mean, rstd and weight; x is
+ *       decoded as act_dequant_unpack decodes it to bf16.
+ * The reference leaves LayerNorm to PyTorch (AC/controller.py:87); these stand where
+ * `unified_quantize` + ATen's native_layer_norm (forward) and `unified_dequantize` +
+ * native_layer_norm_backward (backward) stand in a LayerNorm that saves its input compressed.
+ */
+ACT_API int act_ln_fwd_quant_pack(const void* x, int dtype, int64_t rows, int cols, const float* weight,
+                                  const float* bias, double eps, int group_size, int bits, uint64_t seed,
+                                  uint64_t offset, int flags, void* y, float* mean, float* rstd, void* packed,
+                                  float* scale, float* min, void* stream);
+ACT_API int act_ln_bwd_from_packed(const void* dy, int dtype, int64_t rows, int cols, const void* packed,
+                                   const float* scale, const float* min, int group_size, int bits,
+                                   const float* mean, const float* rstd, const float* weight, void* dx,
+                                   float* dgamma, float* dbeta, void* stream);
+
+/*
  * act_merge_heads: dst[b, t, s, h, :] = srcs[s][b, h, t, :] for s < parts (1..4); dst is contiguous
  * [B, T, parts, H, Dh]; strides = parts x (element stride of b, of h, of t) of the sources, whose
  * last dimension is contiguous.  Dh * elem_bytes, the sources' byte strides and all bases are

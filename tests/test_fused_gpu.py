@@ -577,3 +577,56 @@ def test_column_reductions_reject_bad_layouts(cuda_device):
     with pytest.raises(ValueError):
         codec.col_sum(torch.randn(16, 32, device=cuda_device)[:, ::2])  # rows not contiguous
     assert codec.col_sum(torch.empty(0, 16, device=cuda_device)).abs().sum() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("bits", [1, 2, 4, 8])
+@pytest.mark.parametrize("shape,gs", [((64, 197, 768), 128), ((3, 5, 256), 256), ((7, 960), 64), ((2, 9, 32), 32),
+                                      ((5, 1024), 128)])
+def test_layer_norm_fused_with_codec(cuda_device, dtype, bits, shape, gs):
+    """act_ln_fwd_quant_pack: the packed input equals act_quant_pack's bit for bit (same seed and
+    offset, stochastic and round-to-nearest), y and the statistics equal ATen's within rounding;
+    act_ln_bwd_from_packed equals ATen's backward on the dequantised input within rounding."""
+    from deep_optimization_b200 import _lib, codec
+    torch.manual_seed(bits * 1000 + shape[-1])
+    C = shape[-1]
+    x = (torch.randn(shape, device=cuda_device) * 1.5 + 0.3).to(dtype)
+    w = (torch.rand(C, device=cuda_device) + 0.5)
+    b = torch.randn(C, device=cuda_device) * 0.1
+    for flags in (0, _lib.ACT_FLAG_ROUND_NEAREST):
+        y, mean, rstd, packed, scale, mn = codec.ln_fwd_quant_pack(x, w, b, 1e-6, bits, gs, seed=77, offset=5, flags=flags)
+        p2, s2, m2 = codec.quant_pack(x, bits, gs, seed=77, offset=5, flags=flags)
+        assert torch.equal(packed, p2) and torch.equal(scale, s2) and torch.equal(mn, m2)
+    yr, mr, rr = torch.ops.aten.native_layer_norm(x.float(), [C], w, b, 1e-6)
+    assert torch.allclose(mean, mr.reshape(-1), atol=1e-5, rtol=1e-5) and torch.allclose(rstd, rr.reshape(-1), rtol=1e-4)
+    tol = {torch.float32: 1e-5, torch.bfloat16: 2.0 ** -7, torch.float16: 2.0 ** -10}[dtype]
+    assert ((y.float() - yr).abs() <= tol * (yr.abs() + 1)).all()
+    # backward
+    dy = torch.randn(shape, device=cuda_device).to(dtype)
+    dx, dg, db = codec.ln_bwd_from_packed(dy, packed, scale, mn, bits, gs, mean, rstd, w)
+    xq = codec.dequant_unpack(packed, scale, mn, bits, gs, out_dtype=torch.bfloat16).reshape(shape)
+    dxr, dgr, dbr = torch.ops.aten.native_layer_norm_backward(dy.double(), xq.double(), [C], mean.double().view(*shape[:-1], 1),
+                                                              rstd.double().view(*shape[:-1], 1), w.double(), b.double(),
+                                                              [True, True, True])
+    assert ((dx.double() - dxr).abs() <= tol * (dxr.abs() + dxr.abs().max())).all()
+    rows = x.numel() // C
+    assert ((dg.double() - dgr).abs() <= 1e-5 * rows ** 0.5 * (dgr.abs() + 1) + 1e-4).all()
+    assert ((db.double() - dbr).abs() <= 1e-5 * rows ** 0.5 * (dbr.abs() + 1) + 1e-4).all()
+
+
+def test_layer_norm_fused_irregular_groups(cuda_device):
+    """Groups with a zero, a denormal, a huge or a non-finite range take the general encoder; the
+    packed bytes still equal act_quant_pack's."""
+    from deep_optimization_b200 import codec
+    x = torch.randn(16, 768, device=cuda_device)
+    x[0, :128] = 3.0
+    x[1, 128:256] *= 1e-42
+    x[2, 0] = 3e38; x[2, 1] = -3e38
+    x[3, 300] = float("inf")
+    x[4, 500] = float("nan")
+    for dtype in (torch.float32, torch.bfloat16):
+        xd = x.to(dtype)
+        _, _, _, packed, scale, mn = codec.ln_fwd_quant_pack(xd, None, None, 1e-5, 2, 128, seed=1, offset=2)
+        p2, s2, m2 = codec.quant_pack(xd, 2, 128, seed=1, offset=2)
+        assert torch.equal(packed, p2)
+        assert torch.equal(scale.view(torch.int32), s2.view(torch.int32)) and torch.equal(mn.view(torch.int32), m2.view(torch.int32))
