@@ -21,6 +21,8 @@
 // The reference has no such operator (it leaves LayerNorm to PyTorch,
 // Activation_Compression/controller.py:87); the evaluation configuration for ViT-B/16 counts
 // LayerNorm inputs among the compressed activations.
+#include <type_traits>
+
 #include "codec_pack_kernel.cuh"
 
 namespace act {
@@ -29,17 +31,36 @@ constexpr int kLnThreads = 256;
 constexpr int kLnWarps = kLnThreads / 32;
 constexpr int kMaxVecs = 4;                // 8-element vectors per lane: C <= 32 * 8 * 4 = 1024
 
-template <int DT> __device__ __forceinline__ void ln_load8(const uint8_t* p, float (&f)[8]) {
+// the 8 elements of one vector as loaded (one 16-byte word, two for fp32) and their fp32 values
+template <int DT> struct RawVec { uint4 q[ElemT<DT>::bytes == 4 ? 2 : 1]; };
+template <int DT> __device__ __forceinline__ void ln_load_raw(const uint8_t* p, RawVec<DT>& r) {
+    r.q[0] = ldg_stream_v4(p);
+    if (ElemT<DT>::bytes == 4) r.q[ElemT<DT>::bytes == 4 ? 1 : 0] = ldg_stream_v4(p + 16);
+}
+template <int DT> __device__ __forceinline__ void ln_widen(const RawVec<DT>& r, float (&f)[8]) {
     if (ElemT<DT>::bytes == 4) {
-        const uint4 a = ldg_stream_v4(p), b = ldg_stream_v4(p + 16);
+        const uint4 a = r.q[0], b = r.q[ElemT<DT>::bytes == 4 ? 1 : 0];
         f[0] = __uint_as_float(a.x); f[1] = __uint_as_float(a.y); f[2] = __uint_as_float(a.z); f[3] = __uint_as_float(a.w);
         f[4] = __uint_as_float(b.x); f[5] = __uint_as_float(b.y); f[6] = __uint_as_float(b.z); f[7] = __uint_as_float(b.w);
     } else {
         constexpr int D16 = (DT == ACT_DTYPE_F32) ? ACT_DTYPE_BF16 : DT;
-        const uint4 a = ldg_stream_v4(p);
-        const uint32_t h[4] = {a.x, a.y, a.z, a.w};
+        const uint32_t h[4] = {r.q[0].x, r.q[0].y, r.q[0].z, r.q[0].w};
 #pragma unroll
         for (int k = 0; k < 4; ++k) { f[2 * k] = widen_lo<D16>(h[k]); f[2 * k + 1] = widen_hi<D16>(h[k]); }
+    }
+}
+template <int DT> __device__ __forceinline__ void ln_zero_raw(RawVec<DT>& r) {
+    r.q[0] = make_uint4(0u, 0u, 0u, 0u);
+    if (ElemT<DT>::bytes == 4) r.q[ElemT<DT>::bytes == 4 ? 1 : 0] = make_uint4(0u, 0u, 0u, 0u);
+}
+// eight fp32 parameters of a vector of columns (cached loads: every row reads the same ones)
+__device__ __forceinline__ void ln_load_param8(const float* p, float fill, float (&f)[8]) {
+    if (p) {
+        const float4 a = __ldg(reinterpret_cast<const float4*>(p)), b = __ldg(reinterpret_cast<const float4*>(p) + 1);
+        f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] = fill;
     }
 }
 
@@ -86,35 +107,31 @@ ln_fwd_pack_kernel(const uint8_t* __restrict__ x, const float* __restrict__ weig
     const int steps = (nvec + 31) >> 5;
     const int L = 1 << log2_L;                               // lanes per group
     const float inv_c = 1.0f / (float)C;
-    // weight and bias of the lane's columns stay in registers for all its rows
-    float w[kMaxVecs][8], b[kMaxVecs][8];
-#pragma unroll
-    for (int k = 0; k < kMaxVecs; ++k) {
-        const int v = k * 32 + lane;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const bool on = k < steps && v < nvec;
-            w[k][i] = (on && weight) ? __ldg(weight + v * 8 + i) : 1.0f;
-            b[k][i] = (on && bias) ? __ldg(bias + v * 8 + i) : 0.0f;
-        }
-    }
     const int64_t warp_stride = (int64_t)gridDim.x * kLnWarps;
-    for (int64_t row = (int64_t)blockIdx.x * kLnWarps + warp; row < rows; row += warp_stride) {
-        const uint8_t* xr = x + row * C * EB;
+    // The next row's vectors are requested before this row is worked on (a warp has one row's
+    // arithmetic between its loads otherwise, and 16 warps per SM do not cover HBM's latency).
+    RawVec<DT> nxt[kMaxVecs];
+    auto request = [&](int64_t r) {
+        const uint8_t* xr = x + r * C * EB;
+#pragma unroll
+        for (int k = 0; k < kMaxVecs; ++k) {
+            const int v = k * 32 + lane;
+            if (k < steps && v < nvec) ln_load_raw<DT>(xr + (int64_t)v * 8 * EB, nxt[k]);
+            else ln_zero_raw<DT>(nxt[k]);
+        }
+    };
+    int64_t row = (int64_t)blockIdx.x * kLnWarps + warp;
+    if (row < rows) request(row);
+    for (; row < rows; row += warp_stride) {
         float xf[kMaxVecs][8];
         float sum = 0.0f;
 #pragma unroll
         for (int k = 0; k < kMaxVecs; ++k) {
-            const int v = k * 32 + lane;
-            if (k < steps && v < nvec) {
-                ln_load8<DT>(xr + (int64_t)v * 8 * EB, xf[k]);
+            ln_widen<DT>(nxt[k], xf[k]);                     // vectors past the row hold zeros
 #pragma unroll
-                for (int i = 0; i < 8; ++i) sum += xf[k][i];
-            } else {
-#pragma unroll
-                for (int i = 0; i < 8; ++i) xf[k][i] = 0.0f;
-            }
+            for (int i = 0; i < 8; ++i) sum += xf[k][i];
         }
+        if (row + warp_stride < rows) request(row + warp_stride);
         const float mean = warp_sum(sum) * inv_c;
         float sq = 0.0f;
 #pragma unroll
@@ -136,9 +153,11 @@ ln_fwd_pack_kernel(const uint8_t* __restrict__ x, const float* __restrict__ weig
             const int v = k * 32 + lane;
             const bool on = v < nvec;
             if (on) {
-                float yv[8];
+                float yv[8], w8[8], b8[8];
+                ln_load_param8(weight ? weight + v * 8 : nullptr, 1.0f, w8);
+                ln_load_param8(bias ? bias + v * 8 : nullptr, 0.0f, b8);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) yv[i] = fmaf((xf[k][i] - mean) * rstd, w[k][i], b[k][i]);
+                for (int i = 0; i < 8; ++i) yv[i] = fmaf((xf[k][i] - mean) * rstd, w8[i], b8[i]);
                 ln_store8<DT>(yr + (int64_t)v * 8 * EB, yv);
             }
             // ---- the codec of x: one group = L neighbouring lanes of this step
@@ -182,13 +201,14 @@ ln_fwd_pack_kernel(const uint8_t* __restrict__ x, const float* __restrict__ weig
 // ------------------------------------------------------------------------------ backward
 // eight codes -> eight values of the input as act_dequant_unpack writes them with a bf16 result:
 // fp32 fma(code, scale, min), rounded to bf16
+template <int BITS> __device__ __forceinline__ uint64_t ln_load_codes(const uint8_t* p) {
+    if (BITS == 1) return __ldg(p);
+    if (BITS == 2) return __ldg(reinterpret_cast<const uint16_t*>(p));
+    if (BITS == 4) return __ldg(reinterpret_cast<const uint32_t*>(p));
+    return __ldg(reinterpret_cast<const unsigned long long*>(p));
+}
 template <int BITS>
-__device__ __forceinline__ void ln_decode8(const uint8_t* p, float s, float m, float (&xv)[8]) {
-    uint64_t wbits;
-    if (BITS == 1) wbits = __ldg(p);
-    else if (BITS == 2) wbits = __ldg(reinterpret_cast<const uint16_t*>(p));
-    else if (BITS == 4) wbits = __ldg(reinterpret_cast<const uint32_t*>(p));
-    else wbits = __ldg(reinterpret_cast<const unsigned long long*>(p));
+__device__ __forceinline__ void ln_decode8(uint64_t wbits, float s, float m, float (&xv)[8]) {
     constexpr uint64_t MASK = (1ull << BITS) - 1ull;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
@@ -210,36 +230,57 @@ ln_bwd_packed_kernel(const uint8_t* __restrict__ dy, const uint8_t* __restrict__
     const int nvec = C >> 3;
     const int steps = (nvec + 31) >> 5;
     const float inv_c = 1.0f / (float)C;
-    float w[kMaxVecs][8], ag[kMaxVecs][8], ab[kMaxVecs][8];
+    float ag[kMaxVecs][8], ab[kMaxVecs][8];
 #pragma unroll
     for (int k = 0; k < kMaxVecs; ++k) {
-        const int v = k * 32 + lane;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            w[k][i] = (k < steps && v < nvec && weight) ? __ldg(weight + v * 8 + i) : 1.0f;
-            ag[k][i] = 0.0f; ab[k][i] = 0.0f;
-        }
+        for (int i = 0; i < 8; ++i) { ag[k][i] = 0.0f; ab[k][i] = 0.0f; }
     }
     const int64_t warp_stride = (int64_t)gridDim.x * kLnWarps;
-    for (int64_t row = (int64_t)blockIdx.x * kLnWarps + warp; row < rows; row += warp_stride) {
-        const float mu = __ldg(mean + row), rs = __ldg(rstd + row);
-        const uint8_t* dyr = dy + row * C * EB;
-        const int64_t piece0 = row * nvec;
-        float xh[kMaxVecs][8], g[kMaxVecs][8];
-        float s1 = 0.0f, s2 = 0.0f;
+    // what the next row needs is requested before this row is worked on: its dy vectors, code
+    // words, group constants and statistics (the kernel holds 64 accumulators per thread, so only
+    // eight warps fit on an SM and each has to keep two rows in flight)
+    typedef typename std::conditional<BITS == 8, uint64_t, uint32_t>::type code_t;
+    RawVec<DT> ndy[kMaxVecs];
+    code_t ncw[kMaxVecs];
+    float nsc[kMaxVecs], nmn[kMaxVecs], nmu = 0.0f, nrs = 0.0f;
+    auto request = [&](int64_t r) {
+        const uint8_t* dyr = dy + r * C * EB;
+        const int64_t piece0 = r * nvec;
+        nmu = __ldg(mean + r); nrs = __ldg(rstd + r);
 #pragma unroll
         for (int k = 0; k < kMaxVecs; ++k) {
             const int v = k * 32 + lane;
             if (k < steps && v < nvec) {
                 const int64_t piece = piece0 + v;
                 const int64_t gi = piece >> log2_L;
-                float xv[8], dv[8];
-                ln_decode8<BITS>(packed + piece * BITS, __ldg(scale + gi), __ldg(mn + gi), xv);
-                ln_load8<DT>(dyr + (int64_t)v * 8 * EB, dv);
+                ln_load_raw<DT>(dyr + (int64_t)v * 8 * EB, ndy[k]);
+                ncw[k] = (code_t)ln_load_codes<BITS>(packed + piece * BITS);
+                nsc[k] = __ldg(scale + gi); nmn[k] = __ldg(mn + gi);
+            } else {
+                ln_zero_raw<DT>(ndy[k]);
+                ncw[k] = 0; nsc[k] = 0.0f; nmn[k] = 0.0f;
+            }
+        }
+    };
+    int64_t row = (int64_t)blockIdx.x * kLnWarps + warp;
+    if (row < rows) request(row);
+    for (; row < rows; row += warp_stride) {
+        const float mu = nmu, rs = nrs;
+        float xh[kMaxVecs][8], g[kMaxVecs][8];
+        float s1 = 0.0f, s2 = 0.0f;
+#pragma unroll
+        for (int k = 0; k < kMaxVecs; ++k) {
+            const int v = k * 32 + lane;
+            if (k < steps && v < nvec) {
+                float xv[8], dv[8], w8[8];
+                ln_decode8<BITS>((uint64_t)ncw[k], nsc[k], nmn[k], xv);
+                ln_widen<DT>(ndy[k], dv);
+                ln_load_param8(weight ? weight + v * 8 : nullptr, 1.0f, w8);
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     xh[k][i] = (xv[i] - mu) * rs;
-                    g[k][i] = dv[i] * w[k][i];
+                    g[k][i] = dv[i] * w8[i];
                     s1 = fmaf(g[k][i], xh[k][i], s1);
                     s2 += g[k][i];
                     ag[k][i] = fmaf(dv[i], xh[k][i], ag[k][i]);
@@ -250,6 +291,7 @@ ln_bwd_packed_kernel(const uint8_t* __restrict__ dy, const uint8_t* __restrict__
                 for (int i = 0; i < 8; ++i) { xh[k][i] = 0.0f; g[k][i] = 0.0f; }
             }
         }
+        if (row + warp_stride < rows) request(row + warp_stride);
         const float c1 = warp_sum(s1) * inv_c, c2 = warp_sum(s2) * inv_c;
         uint8_t* dxr = dx + row * C * EB;
 #pragma unroll
