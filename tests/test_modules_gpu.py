@@ -352,3 +352,28 @@ def test_split_heads_backward_is_one_gather(cuda_device, dtype, dims):
         go = torch.randn_like(oa)
         oa.backward(go); ob.backward(go)
         assert torch.equal(oa, ob) and torch.equal(a.grad, b.grad)
+
+
+@pytest.mark.parametrize("bias", [False, True])
+def test_patch_embedding_conv_runs_as_one_gemm(cuda_device, bias):
+    """A convolution whose windows tile the input (kernel = stride) takes the GEMM path of the conv
+    Function: same output as nn.Conv2d (as a channels-last tensor), input and bias gradients equal
+    cuDNN's within rounding, the weight gradient within the 8-bit codes' error."""
+    from deep_optimization_b200.layers import DOConv2d
+    torch.manual_seed(3)
+    meta = _meta("p", 8, 256, 4)
+    conv = DOConv2d(3, 64, 16, stride=16, bias=bias, target_name="p", meta=meta).to(cuda_device).train()
+    ref = nn.Conv2d(3, 64, 16, stride=16, bias=bias).to(cuda_device)
+    ref.load_state_dict({k: v for k, v in conv.state_dict().items() if k in ref.state_dict()})
+    x = torch.randn(4, 3, 64, 96, device=cuda_device, requires_grad=True)
+    xr = x.detach().clone().requires_grad_()
+    y, yr = conv(x), ref(xr)
+    # fp32 operands: both the GEMM and cuDNN may run in TF32 (10 mantissa bits)
+    assert y.shape == yr.shape and torch.allclose(y, yr, atol=4e-3, rtol=4e-3)
+    assert y.flatten(2).transpose(1, 2).is_contiguous()                 # tokens come out row-major without a copy
+    g = torch.randn_like(yr)
+    y.backward(g); yr.backward(g)
+    assert torch.allclose(x.grad, xr.grad, atol=4e-3, rtol=4e-3)
+    assert _rel(conv.weight.grad, ref.weight.grad) < 0.02
+    if bias:
+        assert torch.allclose(conv.bias.grad, ref.bias.grad, atol=1e-3, rtol=1e-4)
