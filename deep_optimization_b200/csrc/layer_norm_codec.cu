@@ -93,7 +93,7 @@ template <int BITS> __device__ __forceinline__ void store_codes(uint8_t* p, uint
 }
 
 // ------------------------------------------------------------------------------ forward
-template <int DT, int BITS, int NM>
+template <int DT, int BITS, int NM, int VECS>
 __global__ void __launch_bounds__(kLnThreads)
 ln_fwd_pack_kernel(const uint8_t* __restrict__ x, const float* __restrict__ weight, const float* __restrict__ bias,
                    uint8_t* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out,
@@ -110,11 +110,11 @@ ln_fwd_pack_kernel(const uint8_t* __restrict__ x, const float* __restrict__ weig
     const int64_t warp_stride = (int64_t)gridDim.x * kLnWarps;
     // The next row's vectors are requested before this row is worked on (a warp has one row's
     // arithmetic between its loads otherwise, and 16 warps per SM do not cover HBM's latency).
-    RawVec<DT> nxt[kMaxVecs];
+    RawVec<DT> nxt[VECS];
     auto request = [&](int64_t r) {
         const uint8_t* xr = x + r * C * EB;
 #pragma unroll
-        for (int k = 0; k < kMaxVecs; ++k) {
+        for (int k = 0; k < VECS; ++k) {
             const int v = k * 32 + lane;
             if (k < steps && v < nvec) ln_load_raw<DT>(xr + (int64_t)v * 8 * EB, nxt[k]);
             else ln_zero_raw<DT>(nxt[k]);
@@ -123,10 +123,10 @@ ln_fwd_pack_kernel(const uint8_t* __restrict__ x, const float* __restrict__ weig
     int64_t row = (int64_t)blockIdx.x * kLnWarps + warp;
     if (row < rows) request(row);
     for (; row < rows; row += warp_stride) {
-        float xf[kMaxVecs][8];
+        float xf[VECS][8];
         float sum = 0.0f;
 #pragma unroll
-        for (int k = 0; k < kMaxVecs; ++k) {
+        for (int k = 0; k < VECS; ++k) {
             ln_widen<DT>(nxt[k], xf[k]);                     // vectors past the row hold zeros
 #pragma unroll
             for (int i = 0; i < 8; ++i) sum += xf[k][i];
@@ -135,7 +135,7 @@ ln_fwd_pack_kernel(const uint8_t* __restrict__ x, const float* __restrict__ weig
         const float mean = warp_sum(sum) * inv_c;
         float sq = 0.0f;
 #pragma unroll
-        for (int k = 0; k < kMaxVecs; ++k) {
+        for (int k = 0; k < VECS; ++k) {
             const int v = k * 32 + lane;
             if (k < steps && v < nvec) {
 #pragma unroll
@@ -148,7 +148,7 @@ ln_fwd_pack_kernel(const uint8_t* __restrict__ x, const float* __restrict__ weig
         uint8_t* yr = y + row * C * EB;
         const int64_t piece0 = row * nvec;                   // index of the row's first 8-element piece
 #pragma unroll
-        for (int k = 0; k < kMaxVecs; ++k) {
+        for (int k = 0; k < VECS; ++k) {
             if (k >= steps) break;                           // warp-uniform
             const int v = k * 32 + lane;
             const bool on = v < nvec;
@@ -217,8 +217,8 @@ __device__ __forceinline__ void ln_decode8(uint64_t wbits, float s, float m, flo
     }
 }
 
-template <int DT, int BITS>
-__global__ void __launch_bounds__(kLnThreads)
+template <int DT, int BITS, int VECS>
+__global__ void __launch_bounds__(kLnThreads, VECS <= 3 ? 2 : 1)
 ln_bwd_packed_kernel(const uint8_t* __restrict__ dy, const uint8_t* __restrict__ packed, const float* __restrict__ scale,
                      const float* __restrict__ mn, const float* __restrict__ mean, const float* __restrict__ rstd,
                      const float* __restrict__ weight, uint8_t* __restrict__ dx, float* __restrict__ dgamma,
@@ -230,9 +230,9 @@ ln_bwd_packed_kernel(const uint8_t* __restrict__ dy, const uint8_t* __restrict__
     const int nvec = C >> 3;
     const int steps = (nvec + 31) >> 5;
     const float inv_c = 1.0f / (float)C;
-    float ag[kMaxVecs][8], ab[kMaxVecs][8];
+    float ag[VECS][8], ab[VECS][8];
 #pragma unroll
-    for (int k = 0; k < kMaxVecs; ++k) {
+    for (int k = 0; k < VECS; ++k) {
 #pragma unroll
         for (int i = 0; i < 8; ++i) { ag[k][i] = 0.0f; ab[k][i] = 0.0f; }
     }
@@ -241,15 +241,15 @@ ln_bwd_packed_kernel(const uint8_t* __restrict__ dy, const uint8_t* __restrict__
     // words, group constants and statistics (the kernel holds 64 accumulators per thread, so only
     // eight warps fit on an SM and each has to keep two rows in flight)
     typedef typename std::conditional<BITS == 8, uint64_t, uint32_t>::type code_t;
-    RawVec<DT> ndy[kMaxVecs];
-    code_t ncw[kMaxVecs];
-    float nsc[kMaxVecs], nmn[kMaxVecs], nmu = 0.0f, nrs = 0.0f;
+    RawVec<DT> ndy[VECS];
+    code_t ncw[VECS];
+    float nsc[VECS], nmn[VECS], nmu = 0.0f, nrs = 0.0f;
     auto request = [&](int64_t r) {
         const uint8_t* dyr = dy + r * C * EB;
         const int64_t piece0 = r * nvec;
         nmu = __ldg(mean + r); nrs = __ldg(rstd + r);
 #pragma unroll
-        for (int k = 0; k < kMaxVecs; ++k) {
+        for (int k = 0; k < VECS; ++k) {
             const int v = k * 32 + lane;
             if (k < steps && v < nvec) {
                 const int64_t piece = piece0 + v;
@@ -267,10 +267,10 @@ ln_bwd_packed_kernel(const uint8_t* __restrict__ dy, const uint8_t* __restrict__
     if (row < rows) request(row);
     for (; row < rows; row += warp_stride) {
         const float mu = nmu, rs = nrs;
-        float xh[kMaxVecs][8], g[kMaxVecs][8];
+        float xh[VECS][8], g[VECS][8];
         float s1 = 0.0f, s2 = 0.0f;
 #pragma unroll
-        for (int k = 0; k < kMaxVecs; ++k) {
+        for (int k = 0; k < VECS; ++k) {
             const int v = k * 32 + lane;
             if (k < steps && v < nvec) {
                 float xv[8], dv[8], w8[8];
@@ -295,7 +295,7 @@ ln_bwd_packed_kernel(const uint8_t* __restrict__ dy, const uint8_t* __restrict__
         const float c1 = warp_sum(s1) * inv_c, c2 = warp_sum(s2) * inv_c;
         uint8_t* dxr = dx + row * C * EB;
 #pragma unroll
-        for (int k = 0; k < kMaxVecs; ++k) {
+        for (int k = 0; k < VECS; ++k) {
             const int v = k * 32 + lane;
             if (k < steps && v < nvec) {
                 float o[8];
@@ -308,7 +308,7 @@ ln_bwd_packed_kernel(const uint8_t* __restrict__ dy, const uint8_t* __restrict__
     // the block's warps own the same columns: combine them step by step in shared memory, then
     // one atomic per block and column
 #pragma unroll
-    for (int k = 0; k < kMaxVecs; ++k) {
+    for (int k = 0; k < VECS; ++k) {
         if (k >= steps) break;
 #pragma unroll
         for (int i = 0; i < 8; ++i) { s_acc[warp][0][lane * 8 + i] = ag[k][i]; s_acc[warp][1][lane * 8 + i] = ab[k][i]; }
@@ -349,11 +349,16 @@ int ln_fwd_launch(bool nearest, const void* x, const float* weight, const float*
                   uint64_t offset, cudaStream_t st)
 {
     const uint64_t key = hash_key(hash_key(seed) + offset);
-#define ACT_LN_FWD(NM) \
-    ln_fwd_pack_kernel<DT, BITS, NM><<<ln_grid(ln_fwd_pack_kernel<DT, BITS, NM>, rows), kLnThreads, 0, st>>>( \
+    const int vecs = (C / 8 + 31) / 32;                      // 8-element vectors per lane: 1..kMaxVecs
+#define ACT_LN_FWD(NM, V) \
+    ln_fwd_pack_kernel<DT, BITS, NM, V><<<ln_grid(ln_fwd_pack_kernel<DT, BITS, NM, V>, rows), kLnThreads, 0, st>>>( \
         static_cast<const uint8_t*>(x), weight, bias, static_cast<uint8_t*>(y), mean, rstd, static_cast<uint8_t*>(packed), \
         scale, mn, rows, C, eps, log2_L, (uint32_t)key, (uint32_t)(key >> 32))
-    if (nearest) ACT_LN_FWD(kNoiseConst); else ACT_LN_FWD(kNoiseHash);
+#define ACT_LN_FWD_V(NM) \
+    switch (vecs) { case 1: ACT_LN_FWD(NM, 1); break; case 2: ACT_LN_FWD(NM, 2); break; \
+                    case 3: ACT_LN_FWD(NM, 3); break; default: ACT_LN_FWD(NM, 4); break; }
+    if (nearest) { ACT_LN_FWD_V(kNoiseConst) } else { ACT_LN_FWD_V(kNoiseHash) }
+#undef ACT_LN_FWD_V
 #undef ACT_LN_FWD
     return cudaGetLastError() == cudaSuccess ? ACT_OK : ACT_ERR_LAUNCH;
 }
@@ -376,9 +381,13 @@ int ln_bwd_launch(const void* dy, const void* packed, const float* scale, const 
                   const float* rstd, const float* weight, void* dx, float* dgamma, float* dbeta, int64_t rows, int C,
                   int log2_L, cudaStream_t st)
 {
-    ln_bwd_packed_kernel<DT, BITS><<<ln_grid(ln_bwd_packed_kernel<DT, BITS>, rows), kLnThreads, 0, st>>>(
-        static_cast<const uint8_t*>(dy), static_cast<const uint8_t*>(packed), scale, mn, mean, rstd, weight,
-        static_cast<uint8_t*>(dx), dgamma, dbeta, rows, C, log2_L);
+    const int vecs = (C / 8 + 31) / 32;
+#define ACT_LN_BWD(V) \
+    ln_bwd_packed_kernel<DT, BITS, V><<<ln_grid(ln_bwd_packed_kernel<DT, BITS, V>, rows), kLnThreads, 0, st>>>( \
+        static_cast<const uint8_t*>(dy), static_cast<const uint8_t*>(packed), scale, mn, mean, rstd, weight, \
+        static_cast<uint8_t*>(dx), dgamma, dbeta, rows, C, log2_L)
+    switch (vecs) { case 1: ACT_LN_BWD(1); break; case 2: ACT_LN_BWD(2); break; case 3: ACT_LN_BWD(3); break; default: ACT_LN_BWD(4); break; }
+#undef ACT_LN_BWD
     return cudaGetLastError() == cudaSuccess ? ACT_OK : ACT_ERR_LAUNCH;
 }
 
