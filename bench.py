@@ -640,6 +640,29 @@ def run_train(name, dev, world, local, steps=8, warmup=3, act=True, batch=256, c
     return out
 
 
+def _bind_to_gpu_cpus(local):
+    """Multi-rank runs: keep this rank's threads on the CPUs NVML lists as local to its GPU, before
+    any pinned buffer is allocated, so that the e2e leg's host buffers are first touched on the
+    GPU's own memory node (eight ranks that all allocate on one socket share that socket's memory
+    and the inter-socket link: 8 GB/s per rank and direction instead of tens).  Reads NVML only;
+    returns the CPU count it bound to, or None when NVML or the call is unavailable."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        index = int(vis.split(",")[local]) if vis and all(v.strip().isdigit() for v in vis.split(",")) else local
+        handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+        words = pynvml.nvmlDeviceGetCpuAffinity(handle, (os.cpu_count() + 63) // 64)
+        cpus = {64 * w + b for w, word in enumerate(words) for b in range(64) if (int(word) >> b) & 1}
+        cpus &= os.sched_getaffinity(0)
+        if not cpus:
+            return None
+        os.sched_setaffinity(0, cpus)
+        return len(cpus)
+    except Exception:       # noqa: BLE001 - an optimisation of the host side only
+        return None
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -652,6 +675,7 @@ def run_ours(args):
         raise SystemExit("bench.py needs a CUDA device: the codec has no CPU path")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    numa = _bind_to_gpu_cpus(local) if world > 1 else None
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     _lib.load()
@@ -844,6 +868,7 @@ def run_ours(args):
                     "d2h_bytes_per_step": n_elems * 2, "ms_per_step": e2e_ms,
                     "per_rank_h2d_GBps": n_elems * 2 / (e2e_ms * 1e-3) / 1e9,
                     "per_rank_d2h_GBps": n_elems * 2 / (e2e_ms * 1e-3) / 1e9,
+                    "cpus_bound_to_gpu": numa,
                     "bound": "host memory and PCIe: the two copies of a step run concurrently with the kernels"},
             "gpu_launches": 2 * K,        # per timed region of K steps; there are REGIONS of them
             "clocks": clocks,
