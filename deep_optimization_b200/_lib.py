@@ -37,6 +37,7 @@ SIGNATURES = {
     "act_activation_fwd_quant_pack": ([_vp, _i32, _i32, _i64, _i32, _i32, _u64, _u64, _i32, _vp, _vp, _vp, _vp, _vp], _i32),
     "act_relu_fwd_pack": ([_vp, _i32, _i64, _i32, _vp, _vp, _vp], _i32),
     "act_relu_bwd_unpack": ([_vp, _vp, _i32, _i64, _vp, _vp], _i32),
+    "act_relu_bwd_unpack_sum": ([_vp, _vp, _vp, _i32, _i64, _vp, _vp], _i32),
     "act_mul_dequant_unpack": ([_vp, _vp, _vp, _vp, _i32, _i64, _i32, _i32, _vp, _vp], _i32),
     "act_bn_fwd_norm_quant_pack": ([_vp, _i32, _i64, _i32, _i64, _vp, _i32, _i32, _u64, _u64, _i32, _vp, _vp, _vp, _vp, _vp], _i32),
     "act_bn_stats_workspace": ([_i64, _i32], _sz),
@@ -50,7 +51,10 @@ SIGNATURES = {
                         _u64, _u64, _i32, _vp, _vp, _vp, _vp, _vp, _vp], _i32),
     "act_bn_backward": ([_vp, _vp, _vp, _vp, _vp, _i32, _i64, _i32, _i64, _i32, _i32, _vp, _f64, _vp, _vp, _vp, _vp,
                          _vp], _i32),
+    "act_bn_backward_sum": ([_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i64, _i32, _i64, _i32, _i32, _vp, _f64, _vp, _vp, _vp, _vp,
+                         _vp], _i32),
     "act_bn_add_relu_bwd_reduce": ([_vp, _vp, _vp, _vp, _vp, _i32, _i64, _i32, _i64, _i32, _i32, _vp, _vp, _vp], _i32),
+    "act_bn_add_relu_bwd_reduce_sum": ([_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i64, _i32, _i64, _i32, _i32, _vp, _vp, _vp], _i32),
     "act_quant_pack_avg": ([_vp, _i32, _i64, _i32, _i32, _i32, _vp, _u64, _u64, _i32, _f32, _vp, _vp, _vp, _vp], _i32),
     "act_dequant_unpack_avg": ([_vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _vp, _vp], _i32),
     "act_bn_relu_fwd_norm_quant_pack": ([_vp, _i32, _i64, _i32, _i64, _vp, _i32, _i32, _u64, _u64, _i32, _vp, _vp, _vp, _vp, _vp, _vp], _i32),

@@ -640,17 +640,22 @@ def bn_forward(x: torch.Tensor, eps: float, weight: Optional[torch.Tensor], bias
 
 def bn_backward(packed: torch.Tensor, scale: torch.Tensor, mn: torch.Tensor, dy: torch.Tensor,
                 mask: Optional[torch.Tensor], has_residual: bool, bits: int, group_size: int,
-                params: torch.Tensor, count: float):
-    """bn_bwd_reduce, bn_bwd_coef and bn_bwd_dx in one library call (act_bn_backward), dy being
+                params: torch.Tensor, count: float, dy2: Optional[torch.Tensor] = None):
+    """bn_bwd_reduce, bn_bwd_coef and bn_bwd_dx in one library call (act_bn_backward_sum), dy being
     in the memory format of the forward input.  Returns (dx, dgamma, dbeta, dy_masked): with
-    has_residual, dy under the ReLU mask (the residual's gradient), else None."""
+    has_residual, dy under the ReLU mask (the residual's gradient), else None.  dy2 (residual form
+    only; dy's shape, type and strides): a second gradient of the output, summed in the mask pass."""
+    if dy2 is not None and (not has_residual or mask is None or dy2.shape != dy.shape or dy2.dtype != dy.dtype
+                            or dy2.stride() != dy.stride()):
+        raise ValueError("bn_backward: dy2 needs the residual form and dy's shape, type and strides")
     dy, N, C, hw = _bn_layout(dy)
     dev = dy.device
     work = torch.empty((6 * C,), dtype=torch.float32, device=dev)      # sums [2C] and coef [C][4]
     dx = torch.empty_like(dy)
     dym = torch.empty_like(dy) if has_residual else None
     with _device_of(dy):
-        rc = _lib.load().act_bn_backward(packed.data_ptr(), scale.data_ptr(), mn.data_ptr(), dy.data_ptr(),
+        rc = _lib.load().act_bn_backward_sum(packed.data_ptr(), scale.data_ptr(), mn.data_ptr(), dy.data_ptr(),
+                                         None if dy2 is None else dy2.data_ptr(),
                                          None if mask is None else mask.data_ptr(), _DTYPES[dy.dtype], N, C, hw,
                                          group_size, bits, params.data_ptr(), float(count), work.data_ptr(),
                                          work[2 * C:].data_ptr(), None if dym is None else dym.data_ptr(),

@@ -267,6 +267,32 @@ class Controller:
             fused.append(new.target)
         return fused
 
+    @staticmethod
+    def _fork_block_outputs(traced, targets):
+        """A block output relu(batch_norm(x) + skip) usually feeds two consumers, the next block's
+        first convolution and its skip (or its downsample convolution).  Autograd would add their
+        two gradients with a kernel of its own; instead the fused BatchNorm returns its output
+        twice, one value per consumer, and its backward adds the two gradients inside the mask
+        pass it runs anyway.  Applied where the fused node has exactly two users."""
+        import operator
+        forked = []
+        for node in list(traced.graph.nodes):
+            if node.op != "call_module" or node.target not in targets or len(node.users) != 2:
+                continue
+            bn = traced.get_submodule(node.target)
+            if type(bn) is not DOBatchNorm2d or not bn.fuse_relu or len(node.args) != 2:
+                continue
+            users = list(node.users)
+            with traced.graph.inserting_after(node):
+                second = traced.graph.call_function(operator.getitem, (node, 1))
+            with traced.graph.inserting_after(node):
+                first = traced.graph.call_function(operator.getitem, (node, 0))
+            users[0].replace_input_with(node, first)
+            users[1].replace_input_with(node, second)
+            bn.fork = True
+            forked.append(node.target)
+        return forked
+
     # ------------------------------------------------------------------ rewrite
     def warp_model(self, graph_mode=False, quantizer=False):
         traced = FX.symbolic_trace(self.model)
@@ -300,6 +326,9 @@ class Controller:
             if self.config.get("fuse_bn_relu", True):
                 if self.config.get("fuse_bn_add_relu", True):
                     self.fused_bn_add_relu = self._fuse_bn_add_relu(traced)
+                    self.forked_block_outputs = []
+                    if self.config.get("fork_block_outputs", True):
+                        self.forked_block_outputs = self._fork_block_outputs(traced, set(self.fused_bn_add_relu))
                 self.fused_bn_relu = self._fuse_bn_relu(traced)
             traced.graph.eliminate_dead_code()
             traced.graph.lint()

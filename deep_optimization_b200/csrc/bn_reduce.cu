@@ -615,16 +615,25 @@ extern "C" int act_bn_relu_bwd_reduce(const void* packed, const float* scale, co
 // reduction kernel was tried and gained nothing: that kernel is bound by its ALU work, and the
 // extra conversions and stores cost what the separate pass did, 28.8 against 28.6 ms per
 // ResNet-50 step.)
+extern "C" int act_bn_add_relu_bwd_reduce_sum(const void* packed, const float* scale, const float* mn, const void* dy,
+                                              const void* dy2, const void* mask_bits, int dtype, int64_t n_batch,
+                                              int channels, int64_t hw, int group_size, int bits, float* sums,
+                                              void* dy_masked, void* stream)
+{
+    if (!mask_bits || !dy_masked) return n_batch * channels * hw == 0 ? ACT_OK : ACT_ERR_NULL;
+    const int rc = act_relu_bwd_unpack_sum(mask_bits, dy, dy2, dtype, n_batch * channels * hw, dy_masked, stream);
+    if (rc != ACT_OK) return rc;
+    return bn_bwd_reduce_common(packed, scale, mn, dy_masked, nullptr, dtype, n_batch, channels, hw, group_size, bits,
+                                sums, stream);
+}
+
 extern "C" int act_bn_add_relu_bwd_reduce(const void* packed, const float* scale, const float* mn, const void* dy,
                                           const void* mask_bits, int dtype, int64_t n_batch, int channels,
                                           int64_t hw, int group_size, int bits, float* sums, void* dy_masked,
                                           void* stream)
 {
-    if (!mask_bits || !dy_masked) return n_batch * channels * hw == 0 ? ACT_OK : ACT_ERR_NULL;
-    const int rc = act_relu_bwd_unpack(mask_bits, dy, dtype, n_batch * channels * hw, dy_masked, stream);
-    if (rc != ACT_OK) return rc;
-    return bn_bwd_reduce_common(packed, scale, mn, dy_masked, nullptr, dtype, n_batch, channels, hw, group_size, bits,
-                                sums, stream);
+    return act_bn_add_relu_bwd_reduce_sum(packed, scale, mn, dy, nullptr, mask_bits, dtype, n_batch, channels, hw,
+                                          group_size, bits, sums, dy_masked, stream);
 }
 
 extern "C" int act_bn_bwd_coef(const float* sums, const float* params, int channels, double count,

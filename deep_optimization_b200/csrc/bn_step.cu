@@ -32,18 +32,19 @@ extern "C" int act_bn_forward(const void* x, const void* residual, int dtype, in
 // read dy through the mask.  mask_bits with dy_masked: BN + residual + ReLU; dy under the mask
 // is written to dy_masked first (act_bn_add_relu_bwd_reduce; the residual's gradient) and is
 // what the dx kernel reads.
-extern "C" int act_bn_backward(const void* packed, const float* scale, const float* mn, const void* dy,
-                               const void* mask_bits, int dtype, int64_t n_batch, int channels, int64_t hw,
+extern "C" int act_bn_backward_sum(const void* packed, const float* scale, const float* mn, const void* dy,
+                                   const void* dy2, const void* mask_bits, int dtype, int64_t n_batch, int channels, int64_t hw,
                                int group_size, int bits, const float* params, double count, float* sums,
                                float* coef, void* dy_masked, void* dx, void* stream)
 {
     if (channels <= 0 || !sums) return ACT_ERR_NULL;
+    if (dy2 && !(mask_bits && dy_masked)) return ACT_ERR_UNSUPPORTED;     // the second gradient rides in the mask pass
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (cudaMemsetAsync(sums, 0, (size_t)channels * 2 * sizeof(float), st) != cudaSuccess) return ACT_ERR_LAUNCH;
     int rc;
     if (mask_bits && dy_masked) {
-        rc = act_bn_add_relu_bwd_reduce(packed, scale, mn, dy, mask_bits, dtype, n_batch, channels, hw, group_size,
-                                        bits, sums, dy_masked, stream);
+        rc = act_bn_add_relu_bwd_reduce_sum(packed, scale, mn, dy, dy2, mask_bits, dtype, n_batch, channels, hw,
+                                            group_size, bits, sums, dy_masked, stream);
         if (rc != ACT_OK) return rc;
         rc = act_bn_bwd_coef(sums, params, channels, count, coef, stream);
         if (rc != ACT_OK) return rc;
@@ -56,4 +57,13 @@ extern "C" int act_bn_backward(const void* packed, const float* scale, const flo
     if (rc != ACT_OK) return rc;
     if (mask_bits) return act_bn_relu_bwd_dx(packed, scale, mn, dy, mask_bits, dtype, n_batch, channels, hw, group_size, bits, coef, dx, stream);
     return act_bn_bwd_dx(packed, scale, mn, dy, dtype, n_batch, channels, hw, group_size, bits, coef, dx, stream);
+}
+
+extern "C" int act_bn_backward(const void* packed, const float* scale, const float* mn, const void* dy,
+                               const void* mask_bits, int dtype, int64_t n_batch, int channels, int64_t hw,
+                               int group_size, int bits, const float* params, double count, float* sums,
+                               float* coef, void* dy_masked, void* dx, void* stream)
+{
+    return act_bn_backward_sum(packed, scale, mn, dy, nullptr, mask_bits, dtype, n_batch, channels, hw, group_size, bits,
+                               params, count, sums, coef, dy_masked, dx, stream);
 }

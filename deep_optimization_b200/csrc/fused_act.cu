@@ -88,16 +88,19 @@ relu_fwd_pack_kernel(const uint8_t* __restrict__ x, uint8_t* __restrict__ y, uin
 template <int DT>
 __global__ void __launch_bounds__(kFusedThreads)
 relu_bwd_unpack_kernel(const uint8_t* __restrict__ bits, const uint8_t* __restrict__ dy,
-                       uint8_t* __restrict__ dx, int64_t n_elems)
+                       const uint8_t* __restrict__ dy2, uint8_t* __restrict__ dx, int64_t n_elems)
 {
+    // dy2 (optional): a second gradient of the same tensor, added in fp32 before the mask: where
+    // the tensor has two consumers this pass takes the place of autograd's accumulation as well
     const int64_t n_pieces = n_elems >> 3;
     const int64_t stride = (int64_t)gridDim.x * kFusedThreads;
     for (int64_t p0 = (int64_t)blockIdx.x * kFusedThreads + threadIdx.x; p0 < n_pieces; p0 += stride * 4) {
-        Vec8<DT> v[4];
+        Vec8<DT> v[4], v2[4];
         uint32_t m[4];
 #pragma unroll
         for (int k = 0; k < 4; ++k) if (p0 + k * stride < n_pieces) {
             v[k] = load8<DT>(dy, (p0 + k * stride) * 8);
+            if (dy2) v2[k] = load8<DT>(dy2, (p0 + k * stride) * 8);
             m[k] = __ldg(bits + p0 + k * stride);
         }
 #pragma unroll
@@ -106,6 +109,12 @@ relu_bwd_unpack_kernel(const uint8_t* __restrict__ bits, const uint8_t* __restri
             if (p >= n_pieces) break;
             float f[8];
             to_float8<DT>(v[k], f);
+            if (dy2) {
+                float f2[8];
+                to_float8<DT>(v2[k], f2);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) f[i] = __fadd_rn(f[i], f2[i]);
+            }
 #pragma unroll
             for (int i = 0; i < 8; ++i) f[i] = ((m[k] >> i) & 1u) ? f[i] : 0.0f;
             store8<DT>(dx, p * 8, f);
@@ -175,24 +184,31 @@ extern "C" int act_relu_fwd_pack(const void* x, int dtype, int64_t n_elems, int 
     return cudaGetLastError() == cudaSuccess ? ACT_OK : ACT_ERR_LAUNCH;
 }
 
-extern "C" int act_relu_bwd_unpack(const void* mask_bits, const void* dy, int dtype, int64_t n_elems,
-                                   void* dx, void* stream)
+extern "C" int act_relu_bwd_unpack_sum(const void* mask_bits, const void* dy, const void* dy2, int dtype,
+                                       int64_t n_elems, void* dx, void* stream)
 {
     using namespace act;
     if (!dtype_ok(dtype)) return ACT_ERR_DTYPE;
     if (n_elems < 0 || (n_elems & 31)) return ACT_ERR_SIZE;
     if (n_elems == 0) return ACT_OK;
     if (!dy || !dx || !mask_bits) return ACT_ERR_NULL;
-    if (((uintptr_t)dy | (uintptr_t)dx) & 15) return ACT_ERR_ALIGN;
+    if (((uintptr_t)dy | (uintptr_t)dy2 | (uintptr_t)dx) & 15) return ACT_ERR_ALIGN;
     const int grid = stream_grid_for(((n_elems >> 3) + kFusedThreads * 4 - 1) / (kFusedThreads * 4), 6, kDecoderWaves);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const uint8_t* b = static_cast<const uint8_t*>(mask_bits);
     const uint8_t* g = static_cast<const uint8_t*>(dy);
+    const uint8_t* g2 = static_cast<const uint8_t*>(dy2);
     uint8_t* o = static_cast<uint8_t*>(dx);
-    if (dtype == ACT_DTYPE_F32) relu_bwd_unpack_kernel<ACT_DTYPE_F32><<<grid, kFusedThreads, 0, st>>>(b, g, o, n_elems);
-    else if (dtype == ACT_DTYPE_BF16) relu_bwd_unpack_kernel<ACT_DTYPE_BF16><<<grid, kFusedThreads, 0, st>>>(b, g, o, n_elems);
-    else relu_bwd_unpack_kernel<ACT_DTYPE_F16><<<grid, kFusedThreads, 0, st>>>(b, g, o, n_elems);
+    if (dtype == ACT_DTYPE_F32) relu_bwd_unpack_kernel<ACT_DTYPE_F32><<<grid, kFusedThreads, 0, st>>>(b, g, g2, o, n_elems);
+    else if (dtype == ACT_DTYPE_BF16) relu_bwd_unpack_kernel<ACT_DTYPE_BF16><<<grid, kFusedThreads, 0, st>>>(b, g, g2, o, n_elems);
+    else relu_bwd_unpack_kernel<ACT_DTYPE_F16><<<grid, kFusedThreads, 0, st>>>(b, g, g2, o, n_elems);
     return cudaGetLastError() == cudaSuccess ? ACT_OK : ACT_ERR_LAUNCH;
+}
+
+extern "C" int act_relu_bwd_unpack(const void* mask_bits, const void* dy, int dtype, int64_t n_elems,
+                                   void* dx, void* stream)
+{
+    return act_relu_bwd_unpack_sum(mask_bits, dy, nullptr, dtype, n_elems, dx, stream);
 }
 
 namespace act {

@@ -23,6 +23,9 @@ class DOBatchNorm2d(nn.BatchNorm2d):
         # set by the Controller when the only consumer is a ReLU: the module then returns
         # relu(batch_norm(x)) and the ReLU node is taken out of the graph
         self.fuse_relu = False
+        # set by the Controller where the fused output has exactly two consumers: the module then
+        # returns the output twice and its backward adds their two gradients inside its mask pass
+        self.fork = False
 
     def forward(self, x, residual=None):
         # residual: set by the Controller where the graph had relu(batch_norm(x) + residual)
@@ -30,11 +33,12 @@ class DOBatchNorm2d(nn.BatchNorm2d):
             y = super().forward(x)
             if residual is not None:
                 y = y + residual
-            return nn.functional.relu(y) if self.fuse_relu else y
+            y = nn.functional.relu(y) if self.fuse_relu else y
+            return (y, y) if self.fork else y
         self._check_input_dim(x)
         return _DOBatchNorm.apply(x, self.weight, self.bias, self.running_mean, self.running_var,
                                   _ema_factor(self), self.eps, self.target_name, self.meta,
-                                  self.ema_grad_meta, None, 1, self.fuse_relu, residual)
+                                  self.ema_grad_meta, None, 1, self.fuse_relu, residual, self.fork)
 
 
 class DOSyncBatchNorm2d(nn.SyncBatchNorm):

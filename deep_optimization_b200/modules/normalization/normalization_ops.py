@@ -53,14 +53,19 @@ class _DOBatchNorm(Function):
     @custom_fwd(device_type="cuda")
     def forward(ctx, input, weight, bias, running_mean, running_var, exponential_average_factor,
                 eps, target_name, meta, ema_grad_meta, process_group=None, world_size=1, fuse_relu=False,
-                residual=None):
+                residual=None, fork=False):
         # fuse_relu (not in the reference's argument list): the module's output is
         # relu(batch_norm(x)); on the fused path the same three kernels do it and keep the mask.
         # residual (with fuse_relu): the output is relu(batch_norm(x) + residual), the end of a
         # residual block; its gradient is dy under the ReLU mask.
+        # fork (with a residual): the output is returned twice (the second a view of the first) for
+        # a graph in which it has two consumers; backward then receives their two gradients
+        # separately and sums them inside the mask pass it runs anyway, instead of autograd adding
+        # them with a pass of its own.
         ctx.set_materialize_grads(False)
         ctx.relu_mask = False
         ctx.has_residual = residual is not None
+        ctx.fork = bool(fork)
         if residual is not None and not fuse_relu:
             raise ValueError("a residual is fused only together with the ReLU")
         C = input.shape[1]
@@ -93,7 +98,7 @@ class _DOBatchNorm(Function):
                 ctx.save_for_backward(weight, packed, scale, mn, params, out[4])
             else:
                 ctx.save_for_backward(weight, packed, scale, mn, params)
-            return y
+            return (y, y.view_as(y)) if ctx.fork else y
         if world_size == 1:
             # one native kernel: x_hat and the saved statistics (running stats updated in place)
             x_hat, mean, invstd = torch.native_batch_norm(input, None, None, running_mean, running_var,
@@ -127,11 +132,13 @@ class _DOBatchNorm(Function):
             ctx.save_for_backward(weight, q_tensors[0], q_tensors[1], q_tensors[2], invstd, keep)
         else:
             ctx.save_for_backward(weight, q_tensors[0], q_tensors[1], q_tensors[2], invstd)
-        return y
+        return (y, y.view_as(y)) if ctx.fork else y
 
     @staticmethod
     @custom_bwd(device_type="cuda")
-    def backward(ctx, dy):
+    def backward(ctx, dy, dy2=None):
+        if dy is None:
+            dy, dy2 = dy2, None
         mask = None
         if ctx.relu_mask:
             weight, q_out, q_scale, q_min, invstd, mask = ctx.saved_tensors
@@ -141,14 +148,23 @@ class _DOBatchNorm(Function):
         if ctx.fused is not None:
             # two kernels on the packed x_hat: per-channel sums, then dx (normalization_ops.py:145-163)
             bits, gs, count = ctx.fused
-            dyc = dy.contiguous(memory_format=torch.channels_last) if ctx.channels_last else dy.contiguous()
+            fmt = torch.channels_last if ctx.channels_last else torch.contiguous_format
+            dyc = dy.contiguous(memory_format=fmt)
+            dyc2 = None
+            if dy2 is not None:
+                if ctx.has_residual and mask is not None and dy2.dtype == dy.dtype:
+                    dyc2 = dy2.contiguous(memory_format=fmt)      # summed inside the mask pass
+                else:
+                    dyc = dyc + dy2
             # `invstd` is the whole [C, 4] parameter table on this path; with a residual, dy under
             # the mask is the residual's gradient and the batch norm's dy
             dx, dgamma, dbeta, dres = codec.bn_backward(q_out, q_scale, q_min, dyc, mask, ctx.has_residual,
-                                                        bits, gs, invstd, count)
+                                                        bits, gs, invstd, count, dy2=dyc2)
             dw = dgamma.to(weight.dtype) if weight is not None else None
             db = dbeta.to(weight.dtype) if weight is not None else None
-            return dx, dw, db, None, None, None, None, None, None, None, None, None, None, dres
+            return dx, dw, db, None, None, None, None, None, None, None, None, None, None, dres, None
+        if dy2 is not None:
+            dy = dy + dy2
         if mask is not None:
             dy = torch.where(mask, dy, torch.zeros_like(dy))
         dres = dy if ctx.has_residual else None
@@ -165,7 +181,7 @@ class _DOBatchNorm(Function):
             dx = dx * invstd.to(dx.dtype).view(shape)
             dw = dgamma.to(weight.dtype) if weight is not None else None
             db = dbeta.to(weight.dtype) if weight is not None else None
-            return dx, dw, db, None, None, None, None, None, None, None, None, None, None, dres
+            return dx, dw, db, None, None, None, None, None, None, None, None, None, None, dres, None
         g = dy.float()
         x_hat = x_hat.float()
         dims = [0] + list(range(2, g.dim()))
@@ -178,7 +194,7 @@ class _DOBatchNorm(Function):
         dx = (w * invstd / M).view(shape) * (M * g - sum_db.view(shape) - x_hat * sum_dg.view(shape))
         dw = dgamma.to(weight.dtype) if weight is not None else None
         db = dbeta.to(weight.dtype) if weight is not None else None
-        return dx.to(dy.dtype), dw, db, None, None, None, None, None, None, None, None, None, None, dres
+        return dx.to(dy.dtype), dw, db, None, None, None, None, None, None, None, None, None, None, dres, None
 
 
 class _DOSyncBatchNorm:

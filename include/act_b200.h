@@ -290,6 +290,26 @@ ACT_API int act_bn_backward(const void* packed, const float* scale, const float*
                     void* dy_masked, void* dx, void* stream);
 
 /*
+ * The same with a second gradient of the same tensor (dy2, dy's type and layout, or NULL): the
+ * mask pass of the residual form computes mask ? dy + dy2 : 0 (the sum in fp32, rounded once),
+ * so that a block output with two consumers needs no accumulation pass of its own
+ * (autograd otherwise adds the two gradients with a kernel of its own before the backward of the
+ * batch norm runs: 16 such additions per ResNet-50 step).  dy2 is accepted only together with
+ * mask_bits and dy_masked.  act_relu_bwd_unpack_sum and act_bn_add_relu_bwd_reduce_sum are the
+ * two steps on their own.
+ */
+ACT_API int act_relu_bwd_unpack_sum(const void* mask_bits, const void* dy, const void* dy2, int dtype,
+                                    int64_t n_elems, void* dx, void* stream);
+ACT_API int act_bn_add_relu_bwd_reduce_sum(const void* packed, const float* scale, const float* min, const void* dy,
+                                           const void* dy2, const void* mask_bits, int dtype, int64_t n_batch,
+                                           int channels, int64_t hw, int group_size, int bits, float* sums,
+                                           void* dy_masked, void* stream);
+ACT_API int act_bn_backward_sum(const void* packed, const float* scale, const float* min, const void* dy,
+                                const void* dy2, const void* mask_bits, int dtype, int64_t n_batch, int channels,
+                                int64_t hw, int group_size, int bits, const float* params, double count,
+                                float* sums, float* coef, void* dy_masked, void* dx, void* stream);
+
+/*
  * Max pooling on a channels-last activation with a 4-bit argmax saved for backward instead of
  * PyTorch's int64 index per output (no counterpart in the reference, which leaves the pooling
  * layer of its ResNet payload, Model/CNN/ResNetV1.py:63,99, to PyTorch): x [N, H, W, C] with C a

@@ -377,3 +377,77 @@ def test_patch_embedding_conv_runs_as_one_gemm(cuda_device, bias):
     assert _rel(conv.weight.grad, ref.weight.grad) < 0.02
     if bias:
         assert torch.allclose(conv.bias.grad, ref.bias.grad, atol=1e-3, rtol=1e-4)
+
+
+@pytest.mark.parametrize("channels_last", [False, True])
+def test_block_outputs_forked_to_their_two_consumers(cuda_device, channels_last):
+    """With `fork_block_outputs` the fused BatchNorm at the end of a residual block hands its
+    output to its two consumers as two values and adds their gradients inside its own mask pass;
+    without it autograd adds them.  Same forward, same gradients (the sums of the batch-norm
+    reductions are atomics, hence the tolerance), fewer kernels."""
+    from deep_optimization_b200 import codec
+    from deep_optimization_b200.controller import Controller
+
+    class Block(nn.Module):
+        def __init__(self, c):
+            super().__init__()
+            self.conv1 = nn.Conv2d(c, c, 3, padding=1, bias=False); self.bn1 = nn.BatchNorm2d(c); self.relu1 = nn.ReLU()
+            self.conv2 = nn.Conv2d(c, c, 3, padding=1, bias=False); self.bn2 = nn.BatchNorm2d(c); self.relu2 = nn.ReLU()
+
+        def forward(self, x):
+            return self.relu2(self.bn2(self.conv2(self.relu1(self.bn1(self.conv1(x))))) + x)
+
+    class Net(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.stem = nn.Conv2d(3, 32, 3, padding=1, bias=False); self.bn = nn.BatchNorm2d(32); self.relu = nn.ReLU()
+            self.b1, self.b2, self.b3 = Block(32), Block(32), Block(32)
+            self.head = nn.Linear(32, 10)
+
+        def forward(self, x):
+            x = self.b3(self.b2(self.b1(self.relu(self.bn(self.stem(x))))))
+            return self.head(x.mean((2, 3)))
+
+    torch.manual_seed(0)
+    base = Net().to(cuda_device)
+    x = torch.randn(16, 3, 32, 32, device=cuda_device)
+    t = torch.randint(0, 10, (16,), device=cuda_device)
+    grads, outs = {}, {}
+    for fork in (True, False):
+        net = Net().to(cuda_device)
+        net.load_state_dict(base.state_dict())
+        cfg = dict(default_bits=8, auto_precision=None, batch_size=16, min_activation_mib=0.0, fork_block_outputs=fork)
+        c = Controller(net, cfg, input_shape=(3, 32, 32), test=False, device=cuda_device)
+        assert len(c.fused_bn_add_relu) == 3 and len(c.forked_block_outputs) == (2 if fork else 0)
+        m = c.traced_model
+        xi = x
+        if channels_last:
+            m = m.to(memory_format=torch.channels_last)
+            xi = x.contiguous(memory_format=torch.channels_last)
+        codec.manual_seed(21)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            out = m(xi)
+            loss = nn.functional.cross_entropy(out, t)
+        loss.backward()
+        outs[fork] = out.detach().float()
+        grads[fork] = {k: p.grad.detach().float().clone() for k, p in m.named_parameters()}
+    assert torch.equal(outs[True], outs[False])
+    for k in grads[True]:
+        assert _rel(grads[True][k], grads[False][k]) < 1e-2, k      # bf16 gradients: a few last-place differences
+
+
+def test_relu_backward_with_two_gradients(cuda_device):
+    """act_relu_bwd_unpack_sum: mask ? dy + dy2 : 0 with the sum rounded once, i.e. what the
+    framework's addition followed by the mask pass gives, bit for bit."""
+    import ctypes
+    from deep_optimization_b200 import _lib, codec
+    torch.manual_seed(1)
+    for dtype in (torch.bfloat16, torch.float16, torch.float32):
+        x = torch.randn(4, 8, 16, 16, device=cuda_device).to(dtype)
+        _, bits = codec.relu_fwd_pack(x)
+        a = torch.randn_like(x); b = torch.randn_like(x)
+        out = torch.empty_like(x)
+        rc = _lib.load().act_relu_bwd_unpack_sum(bits.data_ptr(), a.data_ptr(), b.data_ptr(), codec._DTYPES[dtype], x.numel(),
+                                                 out.data_ptr(), torch.cuda.current_stream().cuda_stream)
+        assert rc == 0
+        assert torch.equal(out, torch.where(x > 0, a + b, torch.zeros_like(a)))
