@@ -619,6 +619,7 @@ def run_train(name, dev, world, local, steps=8, warmup=3, act=True, batch=256, c
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     out = {"img_per_s": batch * world / (ms[0].item() * 1e-3), "ms_per_step": ms[0].item(),
            "ms_per_step_median": ms[1].item(), "ms_per_step_max": ms[2].item(),
+           "img_per_s_median_step": batch * world / (ms[1].item() * 1e-3),
            "peak_mem_GB": torch.cuda.max_memory_allocated(dev) / 2 ** 30, "final_loss": float(loss.detach())}
     if reduce_grads is not None:
         # what the step pays for the gradient exchange: the all-reduce of the flat buffer alone,
