@@ -898,6 +898,7 @@ def run_only(args):
     --only gemm --shape M K N [--reps R]          the FP8 GEMM on one shape (checked, then timed)
     --only dw --shape M N K [--reps R]            the weight gradient from the packed input on one shape
     --only bn --shape N C H W [--channels-last]   the five kernels of one fused BatchNorm+ReLU layer
+    --only ln --shape R C [--reps R]              LayerNorm fused with the codec, forward and backward
     --only train-profile --model resnet50|vit_b16 [--channels-last] [--no-act] [--rows R]
                                                   two training steps under torch.profiler; under
                                                   torchrun every rank runs them (DDP), rank 0 prints
@@ -930,6 +931,16 @@ def run_only(args):
             codec.bn_bwd_dx(packed, scale, mn, dy, None, None, None, BITS, 256, mask=mask, coef=coef)
         torch.cuda.synchronize()
         print("ok", flush=True)
+    elif args.only == "ln":
+        from deep_optimization_b200 import codec
+        R, C = args.shape
+        x = [torch.randn(R, C, device=dev).to(torch.bfloat16) for _ in range(3)]
+        w, b = torch.ones(C, device=dev), torch.zeros(C, device=dev)
+        for i in range(args.reps):
+            y, mean, rstd, packed, scale, mn = codec.ln_fwd_quant_pack(x[i % 3], w, b, 1e-6, BITS, GROUP)
+            codec.ln_bwd_from_packed(x[(i + 1) % 3], packed, scale, mn, BITS, GROUP, mean, rstd, w)
+        torch.cuda.synchronize()
+        print("ok", flush=True)
     elif args.only == "train-profile":
         import torch.distributed as dist
         from torch.profiler import ProfilerActivity, profile
@@ -956,7 +967,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the fp32 codec and GEMM side measurements")
     ap.add_argument("--no-train", action="store_true", help="skip the ResNet-50 / ViT-B/16 training steps")
-    ap.add_argument("--only", choices=("codec", "gemm", "dw", "bn", "train-profile"),
+    ap.add_argument("--only", choices=("codec", "gemm", "dw", "bn", "ln", "train-profile"),
                     help="codec: the headline alone; the others: small runs for profilers (see run_only)")
     ap.add_argument("--shape", type=int, nargs="+", help="--only gemm: M K N; --only bn: N C H W")
     ap.add_argument("--reps", type=int, default=5)
