@@ -93,7 +93,9 @@ template <int BITS> __device__ __forceinline__ void store_codes(uint8_t* p, uint
 }
 
 // ------------------------------------------------------------------------------ forward
-template <int DT, int BITS, int NM, int VECS>
+// VECS = vectors per lane (the host passes exactly ceil(C / 256)); FULL: C is a multiple of 256, so
+// every lane holds a vector in every step and the per-lane tests (and their branches) fall away.
+template <int DT, int BITS, int NM, int VECS, bool FULL>
 __global__ void __launch_bounds__(kLnThreads)
 ln_fwd_pack_kernel(const uint8_t* __restrict__ x, const float* __restrict__ weight, const float* __restrict__ bias,
                    uint8_t* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out,
@@ -104,7 +106,6 @@ ln_fwd_pack_kernel(const uint8_t* __restrict__ x, const float* __restrict__ weig
     constexpr int EB = ElemT<DT>::bytes;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int nvec = C >> 3;
-    const int steps = (nvec + 31) >> 5;
     const int L = 1 << log2_L;                               // lanes per group
     const float inv_c = 1.0f / (float)C;
     const int64_t warp_stride = (int64_t)gridDim.x * kLnWarps;
@@ -116,7 +117,7 @@ ln_fwd_pack_kernel(const uint8_t* __restrict__ x, const float* __restrict__ weig
 #pragma unroll
         for (int k = 0; k < VECS; ++k) {
             const int v = k * 32 + lane;
-            if (k < steps && v < nvec) ln_load_raw<DT>(xr + (int64_t)v * 8 * EB, nxt[k]);
+            if (FULL || v < nvec) ln_load_raw<DT>(xr + (int64_t)v * 8 * EB, nxt[k]);
             else ln_zero_raw<DT>(nxt[k]);
         }
     };
@@ -137,7 +138,7 @@ ln_fwd_pack_kernel(const uint8_t* __restrict__ x, const float* __restrict__ weig
 #pragma unroll
         for (int k = 0; k < VECS; ++k) {
             const int v = k * 32 + lane;
-            if (k < steps && v < nvec) {
+            if (FULL || v < nvec) {
 #pragma unroll
                 for (int i = 0; i < 8; ++i) { const float d = xf[k][i] - mean; sq = fmaf(d, d, sq); }
             }
@@ -149,9 +150,8 @@ ln_fwd_pack_kernel(const uint8_t* __restrict__ x, const float* __restrict__ weig
         const int64_t piece0 = row * nvec;                   // index of the row's first 8-element piece
 #pragma unroll
         for (int k = 0; k < VECS; ++k) {
-            if (k >= steps) break;                           // warp-uniform
             const int v = k * 32 + lane;
-            const bool on = v < nvec;
+            const bool on = FULL || v < nvec;
             if (on) {
                 float yv[8], w8[8], b8[8];
                 ln_load_param8(weight ? weight + v * 8 : nullptr, 1.0f, w8);
@@ -217,7 +217,7 @@ __device__ __forceinline__ void ln_decode8(uint64_t wbits, float s, float m, flo
     }
 }
 
-template <int DT, int BITS, int VECS>
+template <int DT, int BITS, int VECS, bool FULL>
 __global__ void __launch_bounds__(kLnThreads, VECS <= 3 ? 2 : 1)
 ln_bwd_packed_kernel(const uint8_t* __restrict__ dy, const uint8_t* __restrict__ packed, const float* __restrict__ scale,
                      const float* __restrict__ mn, const float* __restrict__ mean, const float* __restrict__ rstd,
@@ -228,7 +228,6 @@ ln_bwd_packed_kernel(const uint8_t* __restrict__ dy, const uint8_t* __restrict__
     __shared__ float s_acc[kLnWarps][2][32 * 8 + 8];         // one step's partial sums per warp
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int nvec = C >> 3;
-    const int steps = (nvec + 31) >> 5;
     const float inv_c = 1.0f / (float)C;
     float ag[VECS][8], ab[VECS][8];
 #pragma unroll
@@ -251,7 +250,7 @@ ln_bwd_packed_kernel(const uint8_t* __restrict__ dy, const uint8_t* __restrict__
 #pragma unroll
         for (int k = 0; k < VECS; ++k) {
             const int v = k * 32 + lane;
-            if (k < steps && v < nvec) {
+            if (FULL || v < nvec) {
                 const int64_t piece = piece0 + v;
                 const int64_t gi = piece >> log2_L;
                 ln_load_raw<DT>(dyr + (int64_t)v * 8 * EB, ndy[k]);
@@ -272,7 +271,7 @@ ln_bwd_packed_kernel(const uint8_t* __restrict__ dy, const uint8_t* __restrict__
 #pragma unroll
         for (int k = 0; k < VECS; ++k) {
             const int v = k * 32 + lane;
-            if (k < steps && v < nvec) {
+            if (FULL || v < nvec) {
                 float xv[8], dv[8], w8[8];
                 ln_decode8<BITS>((uint64_t)ncw[k], nsc[k], nmn[k], xv);
                 ln_widen<DT>(ndy[k], dv);
@@ -297,7 +296,7 @@ ln_bwd_packed_kernel(const uint8_t* __restrict__ dy, const uint8_t* __restrict__
 #pragma unroll
         for (int k = 0; k < VECS; ++k) {
             const int v = k * 32 + lane;
-            if (k < steps && v < nvec) {
+            if (FULL || v < nvec) {
                 float o[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) o[i] = rs * (g[k][i] - c2 - xh[k][i] * c1);
@@ -309,7 +308,6 @@ ln_bwd_packed_kernel(const uint8_t* __restrict__ dy, const uint8_t* __restrict__
     // one atomic per block and column
 #pragma unroll
     for (int k = 0; k < VECS; ++k) {
-        if (k >= steps) break;
 #pragma unroll
         for (int i = 0; i < 8; ++i) { s_acc[warp][0][lane * 8 + i] = ag[k][i]; s_acc[warp][1][lane * 8 + i] = ab[k][i]; }
         __syncthreads();
@@ -350,16 +348,23 @@ int ln_fwd_launch(bool nearest, const void* x, const float* weight, const float*
 {
     const uint64_t key = hash_key(hash_key(seed) + offset);
     const int vecs = (C / 8 + 31) / 32;                      // 8-element vectors per lane: 1..kMaxVecs
-#define ACT_LN_FWD(NM, V) \
-    ln_fwd_pack_kernel<DT, BITS, NM, V><<<ln_grid(ln_fwd_pack_kernel<DT, BITS, NM, V>, rows), kLnThreads, 0, st>>>( \
+    const bool full = (C % 256) == 0;
+#define ACT_LN_FWD_F(NM, V, F) \
+    ln_fwd_pack_kernel<DT, BITS, NM, V, F><<<ln_grid(ln_fwd_pack_kernel<DT, BITS, NM, V, F>, rows), kLnThreads, 0, st>>>( \
         static_cast<const uint8_t*>(x), weight, bias, static_cast<uint8_t*>(y), mean, rstd, static_cast<uint8_t*>(packed), \
         scale, mn, rows, C, eps, log2_L, (uint32_t)key, (uint32_t)(key >> 32))
+    // the forward kernel keeps its per-lane tests even for full rows: without them it needs 109
+    // registers instead of 78 (two blocks per SM instead of three) and is no faster (62.5 us against
+    // 60.0 on bf16 [50432, 768]; the backward kernel gains, 62.8 -> 52.5-55.6 us)
+    (void)full;
+#define ACT_LN_FWD(NM, V) ACT_LN_FWD_F(NM, V, false)
 #define ACT_LN_FWD_V(NM) \
     switch (vecs) { case 1: ACT_LN_FWD(NM, 1); break; case 2: ACT_LN_FWD(NM, 2); break; \
                     case 3: ACT_LN_FWD(NM, 3); break; default: ACT_LN_FWD(NM, 4); break; }
     if (nearest) { ACT_LN_FWD_V(kNoiseConst) } else { ACT_LN_FWD_V(kNoiseHash) }
 #undef ACT_LN_FWD_V
 #undef ACT_LN_FWD
+#undef ACT_LN_FWD_F
     return cudaGetLastError() == cudaSuccess ? ACT_OK : ACT_ERR_LAUNCH;
 }
 
@@ -382,12 +387,15 @@ int ln_bwd_launch(const void* dy, const void* packed, const float* scale, const 
                   int log2_L, cudaStream_t st)
 {
     const int vecs = (C / 8 + 31) / 32;
-#define ACT_LN_BWD(V) \
-    ln_bwd_packed_kernel<DT, BITS, V><<<ln_grid(ln_bwd_packed_kernel<DT, BITS, V>, rows), kLnThreads, 0, st>>>( \
+    const bool full = (C % 256) == 0;
+#define ACT_LN_BWD_F(V, F) \
+    ln_bwd_packed_kernel<DT, BITS, V, F><<<ln_grid(ln_bwd_packed_kernel<DT, BITS, V, F>, rows), kLnThreads, 0, st>>>( \
         static_cast<const uint8_t*>(dy), static_cast<const uint8_t*>(packed), scale, mn, mean, rstd, weight, \
         static_cast<uint8_t*>(dx), dgamma, dbeta, rows, C, log2_L)
+#define ACT_LN_BWD(V) do { if (full) ACT_LN_BWD_F(V, true); else ACT_LN_BWD_F(V, false); } while (0)
     switch (vecs) { case 1: ACT_LN_BWD(1); break; case 2: ACT_LN_BWD(2); break; case 3: ACT_LN_BWD(3); break; default: ACT_LN_BWD(4); break; }
 #undef ACT_LN_BWD
+#undef ACT_LN_BWD_F
     return cudaGetLastError() == cudaSuccess ? ACT_OK : ACT_ERR_LAUNCH;
 }
 
