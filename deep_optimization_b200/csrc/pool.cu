@@ -142,6 +142,95 @@ maxpool_bwd_cl_kernel(const uint32_t* __restrict__ idx, const uint8_t* __restric
     }
 }
 
+// ---- backward with the operands of a block staged in shared memory -----------------------------
+// A block takes one image, a tile of 8 x 32 input positions and up to 64 channels.  It first copies
+// the gradients and index words of the windows that cover its tile into shared memory, every piece
+// requested once and all requests independent (the kernel above chases an index word and then a
+// gradient, window after window), then every thread gathers from there with the same logic.
+// 534 -> 458 us on ResNet-50's pooling layer at batch 256.  The forward kernel gained nothing from
+// the same treatment (388 against 381 us) and stays as it is: neither is bound by its loads.
+template <int DT> struct PoolVec8 { uint4 q[ElemT<DT>::bytes == 4 ? 2 : 1]; };
+template <int DT> __device__ __forceinline__ PoolVec8<DT> pool_load_raw(const uint8_t* p, int64_t e) {
+    PoolVec8<DT> v;
+    v.q[0] = ldg_nc_v4(p + e * ElemT<DT>::bytes);
+    if (ElemT<DT>::bytes == 4) v.q[ElemT<DT>::bytes == 4 ? 1 : 0] = ldg_nc_v4(p + e * 4 + 16);
+    return v;
+}
+template <int DT> __device__ __forceinline__ void pool_widen(const PoolVec8<DT>& v, float (&f)[8]) {
+    if (ElemT<DT>::bytes == 4) {
+        const uint4 a = v.q[0], b = v.q[ElemT<DT>::bytes == 4 ? 1 : 0];
+        f[0] = __uint_as_float(a.x); f[1] = __uint_as_float(a.y); f[2] = __uint_as_float(a.z); f[3] = __uint_as_float(a.w);
+        f[4] = __uint_as_float(b.x); f[5] = __uint_as_float(b.y); f[6] = __uint_as_float(b.z); f[7] = __uint_as_float(b.w);
+    } else {
+        constexpr int D16 = (DT == ACT_DTYPE_F32) ? ACT_DTYPE_BF16 : DT;
+        const uint4 a = v.q[0];
+        f[0] = widen_lo<D16>(a.x); f[1] = widen_hi<D16>(a.x); f[2] = widen_lo<D16>(a.y); f[3] = widen_hi<D16>(a.y);
+        f[4] = widen_lo<D16>(a.z); f[5] = widen_hi<D16>(a.z); f[6] = widen_lo<D16>(a.w); f[7] = widen_hi<D16>(a.w);
+    }
+}
+
+struct PoolTile { int th, tw, tiles_h, tiles_w, chunks, pc; };   // tile size (positions), tiles per image, channel chunks, pieces per chunk
+
+template <int DT>
+__global__ void __launch_bounds__(kPoolThreads)
+maxpool_bwd_tile_kernel(const uint32_t* __restrict__ idx, const uint8_t* __restrict__ dy, uint8_t* __restrict__ dx,
+                        PoolGeom g, PoolTile t, int max_oh, int max_ow)
+{
+    extern __shared__ __align__(16) uint8_t pool_smem[];
+    PoolVec8<DT>* gtile = reinterpret_cast<PoolVec8<DT>*>(pool_smem);
+    uint32_t* wtile = reinterpret_cast<uint32_t*>(pool_smem + (size_t)max_oh * max_ow * t.pc * sizeof(PoolVec8<DT>));
+    int b = blockIdx.x;
+    const int chunk = b % t.chunks; b /= t.chunks;
+    const int tw = b % t.tiles_w; b /= t.tiles_w;
+    const int th = b % t.tiles_h;
+    const int64_t n = b / t.tiles_h;
+    const int pc = (g.C8 - chunk * t.pc) < t.pc ? (g.C8 - chunk * t.pc) : t.pc;
+    const int ih0 = th * t.th, iw0 = tw * t.tw;
+    // output windows that cover some input position of the tile
+    auto lo = [&](int i) { const int v = i + g.pad - g.k + 1; return v <= 0 ? 0 : (v + g.s - 1) / g.s; };
+    auto hi = [&](int i, int last) { const int v = (i + g.pad) / g.s; return v > last ? last : v; };
+    const int ih1 = (ih0 + t.th < g.H ? ih0 + t.th : g.H) - 1, iw1 = (iw0 + t.tw < g.W ? iw0 + t.tw : g.W) - 1;
+    const int oh_a = lo(ih0), oh_b = hi(ih1, g.OH - 1), ow_a = lo(iw0), ow_b = hi(iw1, g.OW - 1);
+    const int noh = oh_b - oh_a + 1, now = ow_b - ow_a + 1;
+    grid_dependency_wait();
+    grid_launch_dependents();
+    for (int p = threadIdx.x; p < noh * now * pc; p += kPoolThreads) {
+        const int piece = p % pc, pix = p / pc;
+        const int r = pix / now, c = pix - r * now;
+        const int64_t q = ((n * g.OH + oh_a + r) * g.OW + ow_a + c) * g.C8 + chunk * t.pc + piece;
+        gtile[p] = pool_load_raw<DT>(dy, q * 8);
+        wtile[p] = __ldg(idx + q);
+    }
+    __syncthreads();
+    for (int o = threadIdx.x; o < t.th * t.tw * pc; o += kPoolThreads) {
+        const int piece = o % pc, ipix = o / pc;
+        const int irow = ipix / t.tw, icol = ipix - irow * t.tw;
+        const int ih = ih0 + irow, iw = iw0 + icol;
+        if (ih >= g.H || iw >= g.W) continue;
+        const int oh_lo = lo(ih), oh_hi = hi(ih, g.OH - 1), ow_lo = lo(iw), ow_hi = hi(iw, g.OW - 1);
+        float acc[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+        for (int oh = oh_lo; oh <= oh_hi; ++oh) {
+            const uint32_t kh = (uint32_t)(ih - (oh * g.s - g.pad));
+            for (int ow = ow_lo; ow <= ow_hi; ++ow) {
+                const uint32_t pos = kh * (uint32_t)g.k + (uint32_t)(iw - (ow * g.s - g.pad));
+                const int sp = ((oh - oh_a) * now + (ow - ow_a)) * pc + piece;
+                const uint32_t word = wtile[sp];
+                uint32_t hit = 0;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) hit |= (((word >> (4 * i)) & 0xFu) == pos) ? (1u << i) : 0u;
+                if (!hit) continue;
+                float f[8];
+                pool_widen<DT>(gtile[sp], f);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) if ((hit >> i) & 1u) acc[i] = __fadd_rn(acc[i], f[i]);
+            }
+        }
+        pool_store8<DT>(dx, (((n * g.H + ih) * g.W + iw) * g.C8 + chunk * t.pc + piece) * 8, acc);
+    }
+}
+
 int stream_grid_for(int64_t n_blocks_wanted, int blocks_per_sm, int waves = 1);   // cabi.cu
 
 static int pool_check(int dtype, int64_t n, int h, int w, int c, int k, int s, int pad, PoolGeom* g) {
@@ -197,6 +286,23 @@ extern "C" int act_maxpool_bwd_cl(const void* idx, const void* dy, int dtype, in
     const uint32_t* ib = static_cast<const uint32_t*>(idx);
     const uint8_t* gb = static_cast<const uint8_t*>(dy);
     uint8_t* ob = static_cast<uint8_t*>(dx);
+    // tiles of 8 x 32 input positions (8 x 16 for fp32) and up to 64 channels; the gradients and
+    // index words of the windows that cover a tile go to shared memory
+    PoolTile t;
+    t.th = 8; t.tw = dtype == ACT_DTYPE_F32 ? 16 : 32;
+    t.pc = g.C8 < 8 ? g.C8 : 8;
+    t.chunks = (g.C8 + t.pc - 1) / t.pc;
+    t.tiles_h = (g.H + t.th - 1) / t.th; t.tiles_w = (g.W + t.tw - 1) / t.tw;
+    const int max_oh = (t.th + g.k - 2) / g.s + 2, max_ow = (t.tw + g.k - 2) / g.s + 2;
+    const size_t vec = dtype == ACT_DTYPE_F32 ? 32 : 16;
+    const size_t smem = (size_t)max_oh * max_ow * t.pc * (vec + 4);
+    const int64_t blocks = n * t.tiles_h * t.tiles_w * t.chunks;
+    if (smem <= 48 * 1024 && blocks <= INT32_MAX) {
+        if (dtype == ACT_DTYPE_F32) maxpool_bwd_tile_kernel<ACT_DTYPE_F32><<<(unsigned)blocks, kPoolThreads, smem, st>>>(ib, gb, ob, g, t, max_oh, max_ow);
+        else if (dtype == ACT_DTYPE_BF16) maxpool_bwd_tile_kernel<ACT_DTYPE_BF16><<<(unsigned)blocks, kPoolThreads, smem, st>>>(ib, gb, ob, g, t, max_oh, max_ow);
+        else maxpool_bwd_tile_kernel<ACT_DTYPE_F16><<<(unsigned)blocks, kPoolThreads, smem, st>>>(ib, gb, ob, g, t, max_oh, max_ow);
+        return cudaGetLastError() == cudaSuccess ? ACT_OK : ACT_ERR_LAUNCH;
+    }
     cudaError_t e;
     if (dtype == ACT_DTYPE_F32) e = launch_overlapped(maxpool_bwd_cl_kernel<ACT_DTYPE_F32>, grid, kPoolThreads, st, ib, gb, ob, pieces, g);
     else if (dtype == ACT_DTYPE_BF16) e = launch_overlapped(maxpool_bwd_cl_kernel<ACT_DTYPE_BF16>, grid, kPoolThreads, st, ib, gb, ob, pieces, g);
