@@ -48,8 +48,9 @@ template <int DT> __device__ __forceinline__ void pool_store8(uint8_t* p, int64_
 
 struct PoolGeom { int H, W, C8, OH, OW, k, s, pad; };
 
-// one thread per output position and vector of eight channels
-template <int DT>
+// one thread per output position and vector of eight channels.  K > 0: the window size is known at
+// compile time and the scan is unrolled (K = 0: taken from g.k)
+template <int DT, int K = 0>
 __global__ void __launch_bounds__(kPoolThreads)
 maxpool_fwd_cl_kernel(const uint8_t* __restrict__ x, uint8_t* __restrict__ y, uint32_t* __restrict__ idx,
                       int64_t n_out_pieces, PoolGeom g)
@@ -67,15 +68,18 @@ maxpool_fwd_cl_kernel(const uint8_t* __restrict__ x, uint8_t* __restrict__ y, ui
         float best[8];
         uint32_t where[8];
         bool first = true;
-        for (int kh = 0; kh < g.k; ++kh) {
+        const int k = K > 0 ? K : g.k;
+#pragma unroll
+        for (int kh = 0; kh < k; ++kh) {
             const int ih = h0 + kh;
             if (ih < 0 || ih >= g.H) continue;
-            for (int kw = 0; kw < g.k; ++kw) {
+#pragma unroll
+            for (int kw = 0; kw < k; ++kw) {
                 const int iw = w0 + kw;
                 if (iw < 0 || iw >= g.W) continue;
                 float f[8];
                 pool_load8<DT>(x, (((n * g.H + ih) * g.W + iw) * g.C8 + c8) * 8, f);
-                const uint32_t pos = (uint32_t)(kh * g.k + kw);
+                const uint32_t pos = (uint32_t)(kh * k + kw);
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     // the first position in range seeds the index; later ones replace it when
@@ -264,9 +268,13 @@ extern "C" int act_maxpool_fwd_cl(const void* x, int dtype, int64_t n, int h, in
     uint8_t* yb = static_cast<uint8_t*>(y);
     uint32_t* ib = static_cast<uint32_t*>(idx);
     cudaError_t e;
-    if (dtype == ACT_DTYPE_F32) e = launch_overlapped(maxpool_fwd_cl_kernel<ACT_DTYPE_F32>, grid, kPoolThreads, st, xb, yb, ib, pieces, g);
-    else if (dtype == ACT_DTYPE_BF16) e = launch_overlapped(maxpool_fwd_cl_kernel<ACT_DTYPE_BF16>, grid, kPoolThreads, st, xb, yb, ib, pieces, g);
-    else e = launch_overlapped(maxpool_fwd_cl_kernel<ACT_DTYPE_F16>, grid, kPoolThreads, st, xb, yb, ib, pieces, g);
+    if (k == 3) {
+        if (dtype == ACT_DTYPE_F32) e = launch_overlapped(maxpool_fwd_cl_kernel<ACT_DTYPE_F32, 3>, grid, kPoolThreads, st, xb, yb, ib, pieces, g);
+        else if (dtype == ACT_DTYPE_BF16) e = launch_overlapped(maxpool_fwd_cl_kernel<ACT_DTYPE_BF16, 3>, grid, kPoolThreads, st, xb, yb, ib, pieces, g);
+        else e = launch_overlapped(maxpool_fwd_cl_kernel<ACT_DTYPE_F16, 3>, grid, kPoolThreads, st, xb, yb, ib, pieces, g);
+    } else if (dtype == ACT_DTYPE_F32) e = launch_overlapped(maxpool_fwd_cl_kernel<ACT_DTYPE_F32, 0>, grid, kPoolThreads, st, xb, yb, ib, pieces, g);
+    else if (dtype == ACT_DTYPE_BF16) e = launch_overlapped(maxpool_fwd_cl_kernel<ACT_DTYPE_BF16, 0>, grid, kPoolThreads, st, xb, yb, ib, pieces, g);
+    else e = launch_overlapped(maxpool_fwd_cl_kernel<ACT_DTYPE_F16, 0>, grid, kPoolThreads, st, xb, yb, ib, pieces, g);
     return e == cudaSuccess ? ACT_OK : ACT_ERR_LAUNCH;
 }
 
