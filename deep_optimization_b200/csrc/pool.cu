@@ -65,10 +65,54 @@ maxpool_fwd_cl_kernel(const uint8_t* __restrict__ x, uint8_t* __restrict__ y, ui
         const int oh = (int)(t % g.OH);
         const int64_t n = t / g.OH;
         const int h0 = oh * g.s - g.pad, w0 = ow * g.s - g.pad;
+        const int k = K > 0 ? K : g.k;
+        if (ElemT<DT>::bytes == 2) {
+            // 16-bit inputs: the maximum and its position are tracked on the packed pairs as they
+            // were loaded (a comparison of two bf16 or fp16 values is the comparison of their fp32
+            // images): per pair one "greater" mask, one "is NaN" mask and two bit selects, instead
+            // of widening and four compares and selects per element.  The position sits in the low
+            // bits of each 16-bit half of `where`.
+            uint32_t best[4], where[4];
+            bool first = true;
+            const uint32_t ninf2 = (DT == ACT_DTYPE_F16) ? 0xFC00FC00u : 0xFF80FF80u;      // (-inf, -inf)
+#pragma unroll
+            for (int kh = 0; kh < k; ++kh) {
+                const int ih = h0 + kh;
+                if (ih < 0 || ih >= g.H) continue;
+#pragma unroll
+                for (int kw = 0; kw < k; ++kw) {
+                    const int iw = w0 + kw;
+                    if (iw < 0 || iw >= g.W) continue;
+                    const uint4 raw = ldg_nc_v4(x + (((n * g.H + ih) * g.W + iw) * g.C8 + c8) * 16);
+                    const uint32_t v[4] = {raw.x, raw.y, raw.z, raw.w};
+                    const uint32_t pos2 = (uint32_t)(kh * k + kw) * 0x00010001u;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        if (first) { best[i] = ninf2; where[i] = pos2; }
+                        uint32_t m;
+                        if (DT == ACT_DTYPE_F16) {
+                            const __half2 a = *reinterpret_cast<const __half2*>(&v[i]), b = *reinterpret_cast<const __half2*>(&best[i]);
+                            m = __hgt2_mask(a, b) | __hneu2_mask(a, a);
+                        } else {
+                            const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&v[i]), b = *reinterpret_cast<const __nv_bfloat162*>(&best[i]);
+                            m = __hgt2_mask(a, b) | __hneu2_mask(a, a);
+                        }
+                        best[i] = (v[i] & m) | (best[i] & ~m);
+                        where[i] = (pos2 & m) | (where[i] & ~m);
+                    }
+                    first = false;
+                }
+            }
+            uint32_t word = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) word |= ((where[i] & 0xFu) << (8 * i)) | (((where[i] >> 16) & 0xFu) << (8 * i + 4));
+            stg_stream_v4(y + p * 16, make_uint4(best[0], best[1], best[2], best[3]));
+            idx[p] = word;
+            continue;
+        }
         float best[8];
         uint32_t where[8];
         bool first = true;
-        const int k = K > 0 ? K : g.k;
 #pragma unroll
         for (int kh = 0; kh < k; ++kh) {
             const int ih = h0 + kh;

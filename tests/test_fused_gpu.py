@@ -630,3 +630,29 @@ def test_layer_norm_fused_irregular_groups(cuda_device):
         p2, s2, m2 = codec.quant_pack(xd, 2, 128, seed=1, offset=2)
         assert torch.equal(packed, p2)
         assert torch.equal(scale.view(torch.int32), s2.view(torch.int32)) and torch.equal(mn.view(torch.int32), m2.view(torch.int32))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", (torch.bfloat16, torch.float16), ids=("bf16", "f16"))
+def test_maxpool_packed_pairs_nan_and_infinities(cuda_device, dtype):
+    """The 16-bit forward kernel compares packed pairs: NaN, -inf and +inf inside windows and ties
+    give what F.max_pool2d gives, values and gradient routing.  (A window that holds nothing but
+    -inf is left out: there PyTorch's channels-last kernel sends the gradient to position 0 of the
+    plane and its NCHW kernel to the window's first position, which is what this one does.)"""
+    from deep_optimization_b200 import codec
+    g = torch.Generator().manual_seed(77)
+    x = torch.randint(-2, 3, (3, 16, 13, 11), generator=g).to(dtype)
+    x[0, 1, 4, 4] = float("nan"); x[0, 1, 4, 5] = float("nan")          # two NaN in one window
+    x[1, 2, 6, 6] = float("inf"); x[1, 3, 2, 2] = float("-inf")
+    x[2, 6, 0, 0] = float("nan")                                         # NaN at the border
+    x = x.to(cuda_device).contiguous(memory_format=torch.channels_last)
+    for k, s, p in ((3, 2, 1), (2, 2, 0), (3, 1, 1)):
+        y, idx = codec.maxpool_fwd(x, k, s, p)
+        xr = x.detach().clone().requires_grad_()
+        yr = torch.nn.functional.max_pool2d(xr, k, s, p)
+        assert torch.equal(torch.isnan(y), torch.isnan(yr))
+        assert torch.equal(torch.nan_to_num(y.float(), nan=9.0), torch.nan_to_num(yr.float(), nan=9.0))
+        dy = torch.randint(-4, 5, yr.shape, generator=g).to(dtype).to(cuda_device).contiguous(memory_format=torch.channels_last)
+        yr.backward(dy)
+        dx = codec.maxpool_bwd(idx, dy, x.shape, k, s, p)
+        assert torch.equal(dx.float(), xr.grad.float())                  # small integers: sums are exact
