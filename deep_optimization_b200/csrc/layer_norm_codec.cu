@@ -291,7 +291,8 @@ ln_bwd_packed_kernel(const uint8_t* __restrict__ dy, const uint8_t* __restrict__
             }
         }
         if (row + warp_stride < rows) request(row + warp_stride);
-        const float c1 = warp_sum(s1) * inv_c, c2 = warp_sum(s2) * inv_c;
+        // dx = rstd * (g - c2 - xhat * c1) as two fused multiply-adds per element
+        const float nc1 = -(rs * (warp_sum(s1) * inv_c)), nc2 = -(rs * (warp_sum(s2) * inv_c));
         uint8_t* dxr = dx + row * C * EB;
 #pragma unroll
         for (int k = 0; k < VECS; ++k) {
@@ -299,7 +300,7 @@ ln_bwd_packed_kernel(const uint8_t* __restrict__ dy, const uint8_t* __restrict__
             if (FULL || v < nvec) {
                 float o[8];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) o[i] = rs * (g[k][i] - c2 - xh[k][i] * c1);
+                for (int i = 0; i < 8; ++i) o[i] = __fmaf_rn(xh[k][i], nc1, __fmaf_rn(g[k][i], rs, nc2));
                 ln_store8<DT>(dxr + (int64_t)v * 8 * EB, o);
             }
         }
