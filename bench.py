@@ -489,6 +489,7 @@ def run_reference_triton(steps=20, warmup=3):
 
 DDP_BUCKET_MB = 25
 FUSED_DW = True         # Linear weight gradients straight from the packed input (--no-fused-dw: dequantise + cuBLAS)
+FUSE_ADD_LN = True      # x + branch formed inside the following LayerNorm's kernels (--no-fuse-add-ln: separate additions)
 DP_MODE = "flat"         # how the training legs average gradients over ranks; see run_train
 
 
@@ -555,7 +556,8 @@ def run_train(name, dev, world, local, steps=20, warmup=8, act=True, batch=256, 
     torch.manual_seed(0)
     model = (resnet50() if name == "resnet50" else vit_b16()).to(dev)
     if act:
-        cfg = dict(default_bits=2, auto_precision=None, batch_size=batch, fused_dw=FUSED_DW)
+        cfg = dict(default_bits=2, auto_precision=None, batch_size=batch, fused_dw=FUSED_DW,
+                   fuse_add_layer_norm=FUSE_ADD_LN)
         net = Controller(model, cfg, input_shape=(3, 224, 224), test=False, device=dev).traced_model
     else:
         net = model.train()
@@ -985,10 +987,13 @@ def main():
                          "DistributedDataParallel, or DDP with gradients as bucket views")
     ap.add_argument("--no-fused-dw", action="store_true",
                     help="training legs: Linear layers dequantise and call cuBLAS for dW instead of act_dw_from_packed")
+    ap.add_argument("--no-fuse-add-ln", action="store_true",
+                    help="training legs: residual additions in front of a LayerNorm stay separate kernels")
     ap.add_argument("--legs", nargs="+", default=None, help="training legs to run (default: all six)")
     args = ap.parse_args()
-    global DDP_BUCKET_MB, DP_MODE, FUSED_DW
+    global DDP_BUCKET_MB, DP_MODE, FUSED_DW, FUSE_ADD_LN
     FUSED_DW = not args.no_fused_dw
+    FUSE_ADD_LN = not args.no_fuse_add_ln
     if args.ddp_bucket_mb:
         DDP_BUCKET_MB = args.ddp_bucket_mb
     if args.dp_mode:

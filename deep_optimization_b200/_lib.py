@@ -71,6 +71,10 @@ SIGNATURES = {
     "act_ln_fwd_quant_pack": ([_vp, _i32, _i64, _i32, _vp, _vp, ctypes.c_double, _i32, _i32, _u64, _u64,
                                _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp], _i32),
     "act_ln_bwd_from_packed": ([_vp, _i32, _i64, _i32, _vp, _vp, _vp, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp], _i32),
+    "act_ln_add_fwd_quant_pack": ([_vp, _vp, _i32, _i64, _i32, _vp, _vp, ctypes.c_double, _i32, _i32, _u64, _u64,
+                                   _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp], _i32),
+    "act_ln_bwd_from_packed_sum": ([_vp, _vp, _i32, _i64, _i32, _vp, _vp, _vp, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp,
+                                    _vp], _i32),
     "act_merge_heads": ([_vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp], _i32),
     "act_calc_precision": ([_vp, _vp, _vp, _i64, ctypes.c_double], _i32),
     "act_fp8_gemm_workspace": ([_i32, _i32, _i32, _i32], ctypes.c_size_t),

@@ -759,16 +759,27 @@ def ln_fused_applies(x: torch.Tensor, group_size: int, bits: int) -> bool:
             and bits in (1, 2, 4, 8) and group_size in (32, 64, 128, 256) and 0 < C <= 1024 and C % group_size == 0)
 
 
+def ln_residual_applies(x: torch.Tensor, residual: torch.Tensor) -> bool:
+    """act_ln_add_fwd_quant_pack forms x + residual itself: both contiguous, one shape, one 16-bit type."""
+    return (x.dtype in (torch.bfloat16, torch.float16) and residual.dtype == x.dtype and residual.shape == x.shape
+            and residual.is_cuda and residual.device == x.device and residual.is_contiguous()
+            and residual.data_ptr() % 16 == 0)
+
+
 def ln_fwd_quant_pack(x: torch.Tensor, weight: Optional[torch.Tensor], bias: Optional[torch.Tensor], eps: float,
                       bits: int, group_size: int, seed: Optional[int] = None, offset: Optional[int] = None,
-                      flags: int = 0):
+                      flags: int = 0, residual: Optional[torch.Tensor] = None):
     """(y, mean, rstd, packed, scale, min): LayerNorm over the last dimension and the packed input,
-    the latter identical to quant_pack(x, bits, group_size, seed=seed, offset=offset, flags=flags)."""
+    the latter identical to quant_pack(x, bits, group_size, seed=seed, offset=offset, flags=flags).
+    With `residual` (same shape and 16-bit type) the normalised and packed tensor is
+    s = x + residual, rounded to that type, and s is returned first: (s, y, mean, ...)."""
     global _next_offset
     if not x.is_cuda:
         raise RuntimeError("ln_fwd_quant_pack needs a CUDA tensor: there is no CPU path")
     if not ln_fused_applies(x, group_size, bits):
         raise ValueError("ln_fwd_quant_pack: unsupported shape, type or group size")
+    if residual is not None and not ln_residual_applies(x, residual):
+        raise ValueError("ln_fwd_quant_pack: the residual must be a contiguous 16-bit tensor of x's shape and type")
     C = x.shape[-1]
     rows = x.numel() // C
     ng = x.numel() // group_size
@@ -786,6 +797,16 @@ def ln_fwd_quant_pack(x: torch.Tensor, weight: Optional[torch.Tensor], bias: Opt
     if offset is None:
         offset = _next_offset
         _next_offset += 1
+    if residual is not None:
+        total = torch.empty_like(x)
+        with _device_of(x):
+            rc = _lib.load().act_ln_add_fwd_quant_pack(
+                x.data_ptr(), residual.data_ptr(), _DTYPES[x.dtype], rows, C, None if w is None else w.data_ptr(),
+                None if b is None else b.data_ptr(), float(eps), group_size, bits, seed & 0xFFFFFFFFFFFFFFFF,
+                offset & 0xFFFFFFFFFFFFFFFF, flags, total.data_ptr(), y.data_ptr(), mean.data_ptr(), rstd.data_ptr(),
+                packed.data_ptr(), scale.data_ptr(), mn.data_ptr(), _stream_ptr(x))
+        _lib.check(rc, "act_ln_add_fwd_quant_pack")
+        return total, y, mean, rstd, packed, scale, mn
     with _device_of(x):
         rc = _lib.load().act_ln_fwd_quant_pack(
             x.data_ptr(), _DTYPES[x.dtype], rows, C, None if w is None else w.data_ptr(),
@@ -797,8 +818,10 @@ def ln_fwd_quant_pack(x: torch.Tensor, weight: Optional[torch.Tensor], bias: Opt
 
 
 def ln_bwd_from_packed(dy: torch.Tensor, packed: torch.Tensor, scale: torch.Tensor, mn: torch.Tensor, bits: int,
-                       group_size: int, mean: torch.Tensor, rstd: torch.Tensor, weight: Optional[torch.Tensor]):
-    """(dx, dgamma, dbeta) of a LayerNorm over the last dimension whose input is given packed."""
+                       group_size: int, mean: torch.Tensor, rstd: torch.Tensor, weight: Optional[torch.Tensor],
+                       dy2: Optional[torch.Tensor] = None):
+    """(dx, dgamma, dbeta) of a LayerNorm over the last dimension whose input is given packed.
+    `dy2` (dy's shape and type, contiguous): a second gradient of the input, added into dx."""
     if not dy.is_cuda:
         raise RuntimeError("ln_bwd_from_packed needs CUDA tensors: there is no CPU path")
     if not ln_fused_applies(dy, group_size, bits):
@@ -813,10 +836,13 @@ def ln_bwd_from_packed(dy: torch.Tensor, packed: torch.Tensor, scale: torch.Tens
     w = None if weight is None else weight.to(torch.float32).contiguous()
     scale = scale.reshape(-1).contiguous()
     mn = mn.reshape(-1).contiguous()
+    if dy2 is not None and (dy2.shape != dy.shape or dy2.dtype != dy.dtype or not dy2.is_contiguous()
+                            or dy2.device != dy.device):
+        raise ValueError("ln_bwd_from_packed: dy2 must be a contiguous tensor of dy's shape and type")
     with _device_of(dy):
-        rc = _lib.load().act_ln_bwd_from_packed(
-            dy.data_ptr(), _DTYPES[dy.dtype], rows, C, packed.data_ptr(), scale.data_ptr(), mn.data_ptr(), group_size,
-            bits, mean.data_ptr(), rstd.data_ptr(), None if w is None else w.data_ptr(), dx.data_ptr(),
-            dgamma.data_ptr(), dbeta.data_ptr(), _stream_ptr(dy))
-    _lib.check(rc, "act_ln_bwd_from_packed")
+        rc = _lib.load().act_ln_bwd_from_packed_sum(
+            dy.data_ptr(), None if dy2 is None else dy2.data_ptr(), _DTYPES[dy.dtype], rows, C, packed.data_ptr(),
+            scale.data_ptr(), mn.data_ptr(), group_size, bits, mean.data_ptr(), rstd.data_ptr(),
+            None if w is None else w.data_ptr(), dx.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr(), _stream_ptr(dy))
+    _lib.check(rc, "act_ln_bwd_from_packed_sum")
     return dx, dgamma, dbeta

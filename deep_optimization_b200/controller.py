@@ -268,6 +268,43 @@ class Controller:
         return fused
 
     @staticmethod
+    def _fuse_add_layer_norm(traced):
+        """s = a + b; y = layer_norm(s), the pre-norm transformer block (Model/ViT/ViT.py:66-68 of
+        the reference), where s also feeds the next residual addition: the LayerNorm module takes
+        the addition over and returns (y, s).  Its forward kernel then forms s from a and b while it
+        reads them (the separate addition and the re-read of its result fall away), and its backward
+        kernel adds the gradient that reaches s from its other consumers to the LayerNorm's own
+        input gradient, which autograd would do with one more pass.  Operands of different shapes
+        or types are added by the module the ordinary way.  Returns the fused targets."""
+        import operator
+        fused = []
+        for node in list(traced.graph.nodes):
+            if node.op != "call_module" or len(node.args) != 1 or node.kwargs:
+                continue
+            if type(traced.get_submodule(node.target)) is not DOLayerNorm:
+                continue
+            add = node.args[0]
+            if (not isinstance(add, FX.Node) or add.op != "call_function" or add.target not in (operator.add, torch.add)
+                    or len(add.args) != 2 or add.kwargs):
+                continue
+            a, b = add.args
+            if not (isinstance(a, FX.Node) and isinstance(b, FX.Node)):
+                continue
+            # at the addition's place: its other consumers may come before the LayerNorm call
+            with traced.graph.inserting_after(add):
+                new = traced.graph.call_module(node.target, args=(a, b))
+            with traced.graph.inserting_after(new):
+                total = traced.graph.call_function(operator.getitem, (new, 1))
+            with traced.graph.inserting_after(new):
+                y = traced.graph.call_function(operator.getitem, (new, 0))
+            node.replace_all_uses_with(y)
+            traced.graph.erase_node(node)
+            add.replace_all_uses_with(total)
+            traced.graph.erase_node(add)
+            fused.append(new.target)
+        return fused
+
+    @staticmethod
     def _fork_block_outputs(traced, targets):
         """A block output relu(batch_norm(x) + skip) usually feeds two consumers, the next block's
         first convolution and its skip (or its downsample convolution).  Autograd would add their
@@ -322,6 +359,9 @@ class Controller:
                         setattr(traced.get_submodule(parent_path), child,
                                 DOMaxPool2d(mod.kernel_size, mod.stride, mod.padding, mod.dilation,
                                             mod.return_indices, mod.ceil_mode))
+            self.fused_add_layer_norm = []
+            if self.config.get("fuse_add_layer_norm", True):
+                self.fused_add_layer_norm = self._fuse_add_layer_norm(traced)
             self.fused_bn_add_relu = []
             if self.config.get("fuse_bn_relu", True):
                 if self.config.get("fuse_bn_add_relu", True):

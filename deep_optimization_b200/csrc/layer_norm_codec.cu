@@ -79,6 +79,13 @@ template <int DT> __device__ __forceinline__ void ln_store8(uint8_t* p, const fl
     }
 }
 
+// two fp32 values rounded to the 16-bit element type, as one packed word
+template <int DT> __device__ __forceinline__ uint32_t round_pair(float lo, float hi) {
+    if (DT == ACT_DTYPE_F16) { const __half2 t = __floats2half2_rn(lo, hi); return *reinterpret_cast<const uint32_t*>(&t); }
+    const __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&t);
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
@@ -95,9 +102,13 @@ template <int BITS> __device__ __forceinline__ void store_codes(uint8_t* p, uint
 // ------------------------------------------------------------------------------ forward
 // VECS = vectors per lane (the host passes exactly ceil(C / 256)); FULL: C is a multiple of 256, so
 // every lane holds a vector in every step and the per-lane tests (and their branches) fall away.
-template <int DT, int BITS, int NM, int VECS, bool FULL>
+// ADD (16-bit types): the normalised tensor is x + res, rounded to the element type and written to
+// sum_out first (what a separate addition would have produced); statistics, y and the codec then
+// work on that rounded sum.
+template <int DT, int BITS, int NM, int VECS, bool FULL, bool ADD>
 __global__ void __launch_bounds__(kLnThreads)
-ln_fwd_pack_kernel(const uint8_t* __restrict__ x, const float* __restrict__ weight, const float* __restrict__ bias,
+ln_fwd_pack_kernel(const uint8_t* __restrict__ x, const uint8_t* __restrict__ res, uint8_t* __restrict__ sum_out,
+                   const float* __restrict__ weight, const float* __restrict__ bias,
                    uint8_t* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out,
                    uint8_t* __restrict__ packed, float* __restrict__ scale_out, float* __restrict__ min_out,
                    int64_t rows, int C, float eps, int log2_L, uint32_t key_lo, uint32_t key_hi)
@@ -111,14 +122,19 @@ ln_fwd_pack_kernel(const uint8_t* __restrict__ x, const float* __restrict__ weig
     const int64_t warp_stride = (int64_t)gridDim.x * kLnWarps;
     // The next row's vectors are requested before this row is worked on (a warp has one row's
     // arithmetic between its loads otherwise, and 16 warps per SM do not cover HBM's latency).
-    RawVec<DT> nxt[VECS];
+    RawVec<DT> nxt[VECS], nxr[ADD ? VECS : 1];
     auto request = [&](int64_t r) {
         const uint8_t* xr = x + r * C * EB;
 #pragma unroll
         for (int k = 0; k < VECS; ++k) {
             const int v = k * 32 + lane;
-            if (FULL || v < nvec) ln_load_raw<DT>(xr + (int64_t)v * 8 * EB, nxt[k]);
-            else ln_zero_raw<DT>(nxt[k]);
+            if (FULL || v < nvec) {
+                ln_load_raw<DT>(xr + (int64_t)v * 8 * EB, nxt[k]);
+                if (ADD) ln_load_raw<DT>(res + (r * C + (int64_t)v * 8) * EB, nxr[ADD ? k : 0]);
+            } else {
+                ln_zero_raw<DT>(nxt[k]);
+                if (ADD) ln_zero_raw<DT>(nxr[ADD ? k : 0]);
+            }
         }
     };
     int64_t row = (int64_t)blockIdx.x * kLnWarps + warp;
@@ -128,7 +144,19 @@ ln_fwd_pack_kernel(const uint8_t* __restrict__ x, const float* __restrict__ weig
         float sum = 0.0f;
 #pragma unroll
         for (int k = 0; k < VECS; ++k) {
-            ln_widen<DT>(nxt[k], xf[k]);                     // vectors past the row hold zeros
+            if (ADD) {
+                float fa[8], fb[8];
+                ln_widen<DT>(nxt[k], fa);
+                ln_widen<DT>(nxr[ADD ? k : 0], fb);
+                RawVec<DT> sv;
+                sv.q[0] = make_uint4(round_pair<DT>(fa[0] + fb[0], fa[1] + fb[1]), round_pair<DT>(fa[2] + fb[2], fa[3] + fb[3]),
+                                     round_pair<DT>(fa[4] + fb[4], fa[5] + fb[5]), round_pair<DT>(fa[6] + fb[6], fa[7] + fb[7]));
+                const int v = k * 32 + lane;
+                if (FULL || v < nvec) stg_stream_v4(sum_out + (row * C + (int64_t)v * 8) * EB, sv.q[0]);
+                ln_widen<DT>(sv, xf[k]);
+            } else {
+                ln_widen<DT>(nxt[k], xf[k]);                 // vectors past the row hold zeros
+            }
 #pragma unroll
             for (int i = 0; i < 8; ++i) sum += xf[k][i];
         }
@@ -221,8 +249,8 @@ template <int DT, int BITS, int VECS, bool FULL>
 __global__ void __launch_bounds__(kLnThreads, VECS <= 3 ? 2 : 1)
 ln_bwd_packed_kernel(const uint8_t* __restrict__ dy, const uint8_t* __restrict__ packed, const float* __restrict__ scale,
                      const float* __restrict__ mn, const float* __restrict__ mean, const float* __restrict__ rstd,
-                     const float* __restrict__ weight, uint8_t* __restrict__ dx, float* __restrict__ dgamma,
-                     float* __restrict__ dbeta, int64_t rows, int C, int log2_L)
+                     const float* __restrict__ weight, const uint8_t* __restrict__ dres, uint8_t* __restrict__ dx,
+                     float* __restrict__ dgamma, float* __restrict__ dbeta, int64_t rows, int C, int log2_L)
 {
     constexpr int EB = ElemT<DT>::bytes;
     __shared__ float s_acc[kLnWarps][2][32 * 8 + 8];         // one step's partial sums per warp
@@ -266,32 +294,43 @@ ln_bwd_packed_kernel(const uint8_t* __restrict__ dy, const uint8_t* __restrict__
     if (row < rows) request(row);
     for (; row < rows; row += warp_stride) {
         const float mu = nmu, rs = nrs;
-        float xh[VECS][8], g[VECS][8];
+        // the second gradient of this row is requested now and used at the end of the first pass:
+        // asked for where it is added, each row waited for it (87 us against 57 on bf16 [50432, 768])
+        RawVec<DT> rv[VECS];
+#pragma unroll
+        for (int k = 0; k < VECS; ++k) {
+            const int v = k * 32 + lane;
+            if (dres && (FULL || v < nvec)) ln_load_raw<DT>(dres + (row * C + (int64_t)v * 8) * EB, rv[k]);
+            else ln_zero_raw<DT>(rv[k]);
+        }
+        float xh[VECS][8], h[VECS][8];                       // h = rstd * dy * weight + second gradient
         float s1 = 0.0f, s2 = 0.0f;
 #pragma unroll
         for (int k = 0; k < VECS; ++k) {
             const int v = k * 32 + lane;
             if (FULL || v < nvec) {
-                float xv[8], dv[8], w8[8];
+                float xv[8], dv[8], w8[8], rf[8];
                 ln_decode8<BITS>((uint64_t)ncw[k], nsc[k], nmn[k], xv);
                 ln_widen<DT>(ndy[k], dv);
                 ln_load_param8(weight ? weight + v * 8 : nullptr, 1.0f, w8);
+                ln_widen<DT>(rv[k], rf);
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     xh[k][i] = (xv[i] - mu) * rs;
-                    g[k][i] = dv[i] * w8[i];
-                    s1 = fmaf(g[k][i], xh[k][i], s1);
-                    s2 += g[k][i];
+                    const float g = dv[i] * w8[i];
+                    s1 = fmaf(g, xh[k][i], s1);
+                    s2 += g;
+                    h[k][i] = __fmaf_rn(g, rs, rf[i]);
                     ag[k][i] = fmaf(dv[i], xh[k][i], ag[k][i]);
                     ab[k][i] += dv[i];
                 }
             } else {
 #pragma unroll
-                for (int i = 0; i < 8; ++i) { xh[k][i] = 0.0f; g[k][i] = 0.0f; }
+                for (int i = 0; i < 8; ++i) { xh[k][i] = 0.0f; h[k][i] = 0.0f; }
             }
         }
         if (row + warp_stride < rows) request(row + warp_stride);
-        // dx = rstd * (g - c2 - xhat * c1) as two fused multiply-adds per element
+        // dx = rstd * (g - c2 - xhat * c1) + second gradient = h - rstd * c2 - xhat * rstd * c1
         const float nc1 = -(rs * (warp_sum(s1) * inv_c)), nc2 = -(rs * (warp_sum(s2) * inv_c));
         uint8_t* dxr = dx + row * C * EB;
 #pragma unroll
@@ -300,7 +339,7 @@ ln_bwd_packed_kernel(const uint8_t* __restrict__ dy, const uint8_t* __restrict__
             if (FULL || v < nvec) {
                 float o[8];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) o[i] = __fmaf_rn(xh[k][i], nc1, __fmaf_rn(g[k][i], rs, nc2));
+                for (int i = 0; i < 8; ++i) o[i] = __fmaf_rn(xh[k][i], nc1, h[k][i] + nc2);
                 ln_store8<DT>(dxr + (int64_t)v * 8 * EB, o);
             }
         }
@@ -343,26 +382,37 @@ static int ln_check(int dtype, int64_t rows, int C, int group_size, int bits) {
 }
 
 template <int DT, int BITS>
-int ln_fwd_launch(bool nearest, const void* x, const float* weight, const float* bias, void* y, float* mean, float* rstd,
+int ln_fwd_launch(bool nearest, const void* x, const void* res, void* sum_out, const float* weight, const float* bias, void* y, float* mean, float* rstd,
                   void* packed, float* scale, float* mn, int64_t rows, int C, float eps, int log2_L, uint64_t seed,
                   uint64_t offset, cudaStream_t st)
 {
     const uint64_t key = hash_key(hash_key(seed) + offset);
     const int vecs = (C / 8 + 31) / 32;                      // 8-element vectors per lane: 1..kMaxVecs
     const bool full = (C % 256) == 0;
-#define ACT_LN_FWD_F(NM, V, F) \
-    ln_fwd_pack_kernel<DT, BITS, NM, V, F><<<ln_grid(ln_fwd_pack_kernel<DT, BITS, NM, V, F>, rows), kLnThreads, 0, st>>>( \
-        static_cast<const uint8_t*>(x), weight, bias, static_cast<uint8_t*>(y), mean, rstd, static_cast<uint8_t*>(packed), \
+#define ACT_LN_FWD_F(NM, V, F, A) \
+    ln_fwd_pack_kernel<DT, BITS, NM, V, F, A><<<ln_grid(ln_fwd_pack_kernel<DT, BITS, NM, V, F, A>, rows), kLnThreads, 0, st>>>( \
+        static_cast<const uint8_t*>(x), static_cast<const uint8_t*>(res), static_cast<uint8_t*>(sum_out), weight, bias, \
+        static_cast<uint8_t*>(y), mean, rstd, static_cast<uint8_t*>(packed), \
         scale, mn, rows, C, eps, log2_L, (uint32_t)key, (uint32_t)(key >> 32))
     // the forward kernel keeps its per-lane tests even for full rows: without them it needs 109
     // registers instead of 78 (two blocks per SM instead of three) and is no faster (62.5 us against
     // 60.0 on bf16 [50432, 768]; the backward kernel gains, 62.8 -> 52.5-55.6 us)
     (void)full;
-#define ACT_LN_FWD(NM, V) ACT_LN_FWD_F(NM, V, false)
+#define ACT_LN_FWD(NM, V) ACT_LN_FWD_F(NM, V, false, false)
 #define ACT_LN_FWD_V(NM) \
     switch (vecs) { case 1: ACT_LN_FWD(NM, 1); break; case 2: ACT_LN_FWD(NM, 2); break; \
                     case 3: ACT_LN_FWD(NM, 3); break; default: ACT_LN_FWD(NM, 4); break; }
-    if (nearest) { ACT_LN_FWD_V(kNoiseConst) } else { ACT_LN_FWD_V(kNoiseHash) }
+#define ACT_LN_ADD(NM, V) ACT_LN_FWD_F(NM, V, false, true)
+#define ACT_LN_ADD_V(NM) \
+    switch (vecs) { case 1: ACT_LN_ADD(NM, 1); break; case 2: ACT_LN_ADD(NM, 2); break; \
+                    case 3: ACT_LN_ADD(NM, 3); break; default: ACT_LN_ADD(NM, 4); break; }
+    if (res) {
+        // the sum is formed on the packed 16-bit pairs: fp32 callers add first
+        if constexpr (DT == ACT_DTYPE_F32) return ACT_ERR_UNSUPPORTED;
+        else if (nearest) { ACT_LN_ADD_V(kNoiseConst) } else { ACT_LN_ADD_V(kNoiseHash) }
+    } else if (nearest) { ACT_LN_FWD_V(kNoiseConst) } else { ACT_LN_FWD_V(kNoiseHash) }
+#undef ACT_LN_ADD_V
+#undef ACT_LN_ADD
 #undef ACT_LN_FWD_V
 #undef ACT_LN_FWD
 #undef ACT_LN_FWD_F
@@ -370,20 +420,20 @@ int ln_fwd_launch(bool nearest, const void* x, const float* weight, const float*
 }
 
 template <int DT>
-int ln_fwd_bits(int bits, bool nearest, const void* x, const float* weight, const float* bias, void* y, float* mean,
+int ln_fwd_bits(int bits, bool nearest, const void* x, const void* res, void* sum_out, const float* weight, const float* bias, void* y, float* mean,
                 float* rstd, void* packed, float* scale, float* mn, int64_t rows, int C, float eps, int log2_L,
                 uint64_t seed, uint64_t offset, cudaStream_t st)
 {
     switch (bits) {
-        case 1: return ln_fwd_launch<DT, 1>(nearest, x, weight, bias, y, mean, rstd, packed, scale, mn, rows, C, eps, log2_L, seed, offset, st);
-        case 2: return ln_fwd_launch<DT, 2>(nearest, x, weight, bias, y, mean, rstd, packed, scale, mn, rows, C, eps, log2_L, seed, offset, st);
-        case 4: return ln_fwd_launch<DT, 4>(nearest, x, weight, bias, y, mean, rstd, packed, scale, mn, rows, C, eps, log2_L, seed, offset, st);
-        default: return ln_fwd_launch<DT, 8>(nearest, x, weight, bias, y, mean, rstd, packed, scale, mn, rows, C, eps, log2_L, seed, offset, st);
+        case 1: return ln_fwd_launch<DT, 1>(nearest, x, res, sum_out, weight, bias, y, mean, rstd, packed, scale, mn, rows, C, eps, log2_L, seed, offset, st);
+        case 2: return ln_fwd_launch<DT, 2>(nearest, x, res, sum_out, weight, bias, y, mean, rstd, packed, scale, mn, rows, C, eps, log2_L, seed, offset, st);
+        case 4: return ln_fwd_launch<DT, 4>(nearest, x, res, sum_out, weight, bias, y, mean, rstd, packed, scale, mn, rows, C, eps, log2_L, seed, offset, st);
+        default: return ln_fwd_launch<DT, 8>(nearest, x, res, sum_out, weight, bias, y, mean, rstd, packed, scale, mn, rows, C, eps, log2_L, seed, offset, st);
     }
 }
 
 template <int DT, int BITS>
-int ln_bwd_launch(const void* dy, const void* packed, const float* scale, const float* mn, const float* mean,
+int ln_bwd_launch(const void* dy, const void* dres, const void* packed, const float* scale, const float* mn, const float* mean,
                   const float* rstd, const float* weight, void* dx, float* dgamma, float* dbeta, int64_t rows, int C,
                   int log2_L, cudaStream_t st)
 {
@@ -392,7 +442,7 @@ int ln_bwd_launch(const void* dy, const void* packed, const float* scale, const 
 #define ACT_LN_BWD_F(V, F) \
     ln_bwd_packed_kernel<DT, BITS, V, F><<<ln_grid(ln_bwd_packed_kernel<DT, BITS, V, F>, rows), kLnThreads, 0, st>>>( \
         static_cast<const uint8_t*>(dy), static_cast<const uint8_t*>(packed), scale, mn, mean, rstd, weight, \
-        static_cast<uint8_t*>(dx), dgamma, dbeta, rows, C, log2_L)
+        static_cast<const uint8_t*>(dres), static_cast<uint8_t*>(dx), dgamma, dbeta, rows, C, log2_L)
 #define ACT_LN_BWD(V) do { if (full) ACT_LN_BWD_F(V, true); else ACT_LN_BWD_F(V, false); } while (0)
     switch (vecs) { case 1: ACT_LN_BWD(1); break; case 2: ACT_LN_BWD(2); break; case 3: ACT_LN_BWD(3); break; default: ACT_LN_BWD(4); break; }
 #undef ACT_LN_BWD
@@ -401,47 +451,67 @@ int ln_bwd_launch(const void* dy, const void* packed, const float* scale, const 
 }
 
 template <int DT>
-int ln_bwd_bits(int bits, const void* dy, const void* packed, const float* scale, const float* mn, const float* mean,
+int ln_bwd_bits(int bits, const void* dy, const void* dres, const void* packed, const float* scale, const float* mn, const float* mean,
                 const float* rstd, const float* weight, void* dx, float* dgamma, float* dbeta, int64_t rows, int C,
                 int log2_L, cudaStream_t st)
 {
     switch (bits) {
-        case 1: return ln_bwd_launch<DT, 1>(dy, packed, scale, mn, mean, rstd, weight, dx, dgamma, dbeta, rows, C, log2_L, st);
-        case 2: return ln_bwd_launch<DT, 2>(dy, packed, scale, mn, mean, rstd, weight, dx, dgamma, dbeta, rows, C, log2_L, st);
-        case 4: return ln_bwd_launch<DT, 4>(dy, packed, scale, mn, mean, rstd, weight, dx, dgamma, dbeta, rows, C, log2_L, st);
-        default: return ln_bwd_launch<DT, 8>(dy, packed, scale, mn, mean, rstd, weight, dx, dgamma, dbeta, rows, C, log2_L, st);
+        case 1: return ln_bwd_launch<DT, 1>(dy, dres, packed, scale, mn, mean, rstd, weight, dx, dgamma, dbeta, rows, C, log2_L, st);
+        case 2: return ln_bwd_launch<DT, 2>(dy, dres, packed, scale, mn, mean, rstd, weight, dx, dgamma, dbeta, rows, C, log2_L, st);
+        case 4: return ln_bwd_launch<DT, 4>(dy, dres, packed, scale, mn, mean, rstd, weight, dx, dgamma, dbeta, rows, C, log2_L, st);
+        default: return ln_bwd_launch<DT, 8>(dy, dres, packed, scale, mn, mean, rstd, weight, dx, dgamma, dbeta, rows, C, log2_L, st);
     }
 }
 
 }  // namespace act
+
+static int ln_fwd_entry(const void* x, const void* res, void* sum_out, int dtype, int64_t rows, int cols,
+                        const float* weight, const float* bias, double eps, int group_size, int bits, uint64_t seed,
+                        uint64_t offset, int flags, void* y, float* mean, float* rstd, void* packed, float* scale,
+                        float* min, void* stream)
+{
+    using namespace act;
+    const int rc = ln_check(dtype, rows, cols, group_size, bits);
+    if (rc != ACT_OK) return rc;
+    if (flags & ~ACT_FLAG_ROUND_NEAREST) return ACT_ERR_UNSUPPORTED;
+    if (res && dtype == ACT_DTYPE_F32) return ACT_ERR_UNSUPPORTED;
+    if (rows == 0) return ACT_OK;
+    if (!x || !y || !mean || !rstd || !packed || !scale || !min) return ACT_ERR_NULL;
+    if (((uintptr_t)x | (uintptr_t)y | (uintptr_t)packed | (uintptr_t)res | (uintptr_t)sum_out) & 15) return ACT_ERR_ALIGN;
+    int log2_L = 0;
+    while ((8 << log2_L) < group_size) ++log2_L;
+    const bool nearest = (flags & ACT_FLAG_ROUND_NEAREST) != 0;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    switch (dtype) {
+        case ACT_DTYPE_F32: return ln_fwd_bits<ACT_DTYPE_F32>(bits, nearest, x, res, sum_out, weight, bias, y, mean, rstd, packed, scale, min, rows, cols, (float)eps, log2_L, seed, offset, st);
+        case ACT_DTYPE_BF16: return ln_fwd_bits<ACT_DTYPE_BF16>(bits, nearest, x, res, sum_out, weight, bias, y, mean, rstd, packed, scale, min, rows, cols, (float)eps, log2_L, seed, offset, st);
+        default: return ln_fwd_bits<ACT_DTYPE_F16>(bits, nearest, x, res, sum_out, weight, bias, y, mean, rstd, packed, scale, min, rows, cols, (float)eps, log2_L, seed, offset, st);
+    }
+}
 
 extern "C" int act_ln_fwd_quant_pack(const void* x, int dtype, int64_t rows, int cols, const float* weight,
                                      const float* bias, double eps, int group_size, int bits, uint64_t seed,
                                      uint64_t offset, int flags, void* y, float* mean, float* rstd, void* packed,
                                      float* scale, float* min, void* stream)
 {
-    using namespace act;
-    const int rc = ln_check(dtype, rows, cols, group_size, bits);
-    if (rc != ACT_OK) return rc;
-    if (flags & ~ACT_FLAG_ROUND_NEAREST) return ACT_ERR_UNSUPPORTED;
-    if (rows == 0) return ACT_OK;
-    if (!x || !y || !mean || !rstd || !packed || !scale || !min) return ACT_ERR_NULL;
-    if (((uintptr_t)x | (uintptr_t)y | (uintptr_t)packed) & 15) return ACT_ERR_ALIGN;
-    int log2_L = 0;
-    while ((8 << log2_L) < group_size) ++log2_L;
-    const bool nearest = (flags & ACT_FLAG_ROUND_NEAREST) != 0;
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-    switch (dtype) {
-        case ACT_DTYPE_F32: return ln_fwd_bits<ACT_DTYPE_F32>(bits, nearest, x, weight, bias, y, mean, rstd, packed, scale, min, rows, cols, (float)eps, log2_L, seed, offset, st);
-        case ACT_DTYPE_BF16: return ln_fwd_bits<ACT_DTYPE_BF16>(bits, nearest, x, weight, bias, y, mean, rstd, packed, scale, min, rows, cols, (float)eps, log2_L, seed, offset, st);
-        default: return ln_fwd_bits<ACT_DTYPE_F16>(bits, nearest, x, weight, bias, y, mean, rstd, packed, scale, min, rows, cols, (float)eps, log2_L, seed, offset, st);
-    }
+    return ln_fwd_entry(x, nullptr, nullptr, dtype, rows, cols, weight, bias, eps, group_size, bits, seed, offset, flags,
+                        y, mean, rstd, packed, scale, min, stream);
 }
 
-extern "C" int act_ln_bwd_from_packed(const void* dy, int dtype, int64_t rows, int cols, const void* packed,
-                                      const float* scale, const float* min, int group_size, int bits,
-                                      const float* mean, const float* rstd, const float* weight, void* dx,
-                                      float* dgamma, float* dbeta, void* stream)
+extern "C" int act_ln_add_fwd_quant_pack(const void* x, const void* res, int dtype, int64_t rows, int cols,
+                                         const float* weight, const float* bias, double eps, int group_size, int bits,
+                                         uint64_t seed, uint64_t offset, int flags, void* sum, void* y, float* mean,
+                                         float* rstd, void* packed, float* scale, float* min, void* stream)
+{
+    if (rows > 0 && cols > 0 && (!res || !sum)) return ACT_ERR_NULL;
+    return ln_fwd_entry(x, res, sum, dtype, rows, cols, weight, bias, eps, group_size, bits, seed, offset, flags,
+                        y, mean, rstd, packed, scale, min, stream);
+}
+
+static int ln_bwd_entry(const void* dy, const void* dres, int dtype, int64_t rows, int cols, const void* packed,
+                        const float* scale, const float* min, int group_size, int bits,
+                        const float* mean, const float* rstd, const float* weight, void* dx,
+                        float* dgamma, float* dbeta, void* stream)
 {
     using namespace act;
     const int rc = ln_check(dtype, rows, cols, group_size, bits);
@@ -452,13 +522,31 @@ extern "C" int act_ln_bwd_from_packed(const void* dy, int dtype, int64_t rows, i
         cudaMemsetAsync(dbeta, 0, (size_t)cols * sizeof(float), st) != cudaSuccess) return ACT_ERR_LAUNCH;
     if (rows == 0) return ACT_OK;
     if (!dy || !packed || !scale || !min || !mean || !rstd || !dx) return ACT_ERR_NULL;
-    if (((uintptr_t)dy | (uintptr_t)dx) & 15) return ACT_ERR_ALIGN;
+    if (((uintptr_t)dy | (uintptr_t)dx | (uintptr_t)dres) & 15) return ACT_ERR_ALIGN;
     if ((uintptr_t)packed & 7) return ACT_ERR_ALIGN;
     int log2_L = 0;
     while ((8 << log2_L) < group_size) ++log2_L;
     switch (dtype) {
-        case ACT_DTYPE_F32: return ln_bwd_bits<ACT_DTYPE_F32>(bits, dy, packed, scale, min, mean, rstd, weight, dx, dgamma, dbeta, rows, cols, log2_L, st);
-        case ACT_DTYPE_BF16: return ln_bwd_bits<ACT_DTYPE_BF16>(bits, dy, packed, scale, min, mean, rstd, weight, dx, dgamma, dbeta, rows, cols, log2_L, st);
-        default: return ln_bwd_bits<ACT_DTYPE_F16>(bits, dy, packed, scale, min, mean, rstd, weight, dx, dgamma, dbeta, rows, cols, log2_L, st);
+        case ACT_DTYPE_F32: return ln_bwd_bits<ACT_DTYPE_F32>(bits, dy, dres, packed, scale, min, mean, rstd, weight, dx, dgamma, dbeta, rows, cols, log2_L, st);
+        case ACT_DTYPE_BF16: return ln_bwd_bits<ACT_DTYPE_BF16>(bits, dy, dres, packed, scale, min, mean, rstd, weight, dx, dgamma, dbeta, rows, cols, log2_L, st);
+        default: return ln_bwd_bits<ACT_DTYPE_F16>(bits, dy, dres, packed, scale, min, mean, rstd, weight, dx, dgamma, dbeta, rows, cols, log2_L, st);
     }
+}
+
+extern "C" int act_ln_bwd_from_packed(const void* dy, int dtype, int64_t rows, int cols, const void* packed,
+                                      const float* scale, const float* min, int group_size, int bits,
+                                      const float* mean, const float* rstd, const float* weight, void* dx,
+                                      float* dgamma, float* dbeta, void* stream)
+{
+    return ln_bwd_entry(dy, nullptr, dtype, rows, cols, packed, scale, min, group_size, bits, mean, rstd, weight, dx,
+                        dgamma, dbeta, stream);
+}
+
+extern "C" int act_ln_bwd_from_packed_sum(const void* dy, const void* dy2, int dtype, int64_t rows, int cols,
+                                          const void* packed, const float* scale, const float* min, int group_size,
+                                          int bits, const float* mean, const float* rstd, const float* weight,
+                                          void* dx, float* dgamma, float* dbeta, void* stream)
+{
+    return ln_bwd_entry(dy, dy2, dtype, rows, cols, packed, scale, min, group_size, bits, mean, rstd, weight, dx,
+                        dgamma, dbeta, stream);
 }

@@ -74,8 +74,19 @@ class DOLayerNorm(nn.LayerNorm):
         super().__init__(normalized_shape, eps, elementwise_affine, bias)
         self.target_name, self.meta = target_name, meta
 
-    def forward(self, x):
+    def forward(self, x, residual=None):
+        """With `residual` the layer normalises s = x + residual and returns (y, s): the Controller
+        rewrites `s = a + b; y = norm(s)` into this call, so that the addition happens inside the
+        forward kernel and the gradient s receives from its other consumer is added inside the
+        backward kernel."""
         if not self.training:
-            return super().forward(x)
+            if residual is None:
+                return super().forward(x)
+            s = x + residual
+            return super().forward(s), s
+        if residual is not None and (residual.shape != x.shape or residual.dtype != x.dtype):
+            s = x + residual                                 # broadcast or promoted: autograd's own addition
+            return _DOLayerNorm.apply(s, self.normalized_shape, self.weight, self.bias, self.eps,
+                                      self.target_name, self.meta, None), s
         return _DOLayerNorm.apply(x, self.normalized_shape, self.weight, self.bias, self.eps,
-                                  self.target_name, self.meta)
+                                  self.target_name, self.meta, residual)

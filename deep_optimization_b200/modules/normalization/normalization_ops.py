@@ -228,15 +228,30 @@ class _DOLayerNorm(Function):
 
     @staticmethod
     @custom_fwd(device_type="cuda")
-    def forward(ctx, input, normalized_shape, weight, bias, eps, target_name, meta):
+    def forward(ctx, input, normalized_shape, weight, bias, eps, target_name, meta, residual=None):
+        """`residual`: the layer normalises (and saves) input + residual and returns that sum as a
+        second output; backward then takes the sum's other gradient as a second argument."""
         m = meta[f"{target_name}"]
         ctx.normalized_shape = list(normalized_shape)
         ctx.param_dtypes = (None if weight is None else weight.dtype, None if bias is None else bias.dtype)
+        ctx.with_residual = residual is not None
+        ctx.set_materialize_grads(False)                     # an unused output brings None, not a tensor of zeros
         input = input.contiguous()
+        total = None
+        if residual is not None:
+            residual = residual.contiguous()
+            if not (_DOLayerNorm._fused(input, ctx.normalized_shape, m) and codec.ln_residual_applies(input, residual)):
+                input = total = input + residual          # the kernel cannot take the pair: add first
+                residual = None
+        done = lambda y: (y, total) if ctx.with_residual else y
         if _DOLayerNorm._fused(input, ctx.normalized_shape, m):
             flags = _lib.ACT_FLAG_ROUND_NEAREST if act_kernels.get_mode() == "nearest" else 0
-            y, mean, rstd, packed, scale, mn = codec.ln_fwd_quant_pack(input, weight, bias, eps, m["bits"],
-                                                                       m["group_size"], flags=flags)
+            if residual is not None:
+                total, y, mean, rstd, packed, scale, mn = codec.ln_fwd_quant_pack(
+                    input, weight, bias, eps, m["bits"], m["group_size"], flags=flags, residual=residual)
+            else:
+                y, mean, rstd, packed, scale, mn = codec.ln_fwd_quant_pack(input, weight, bias, eps, m["bits"],
+                                                                           m["group_size"], flags=flags)
             # the tensors and the 14-entry meta `quantize` returns for a flat grouping of this input
             n = input.shape[0]
             G = input.numel() // n // m["group_size"]
@@ -244,7 +259,7 @@ class _DOLayerNorm(Function):
                           m["AVG_ALAM"], m["ALAM_BITS"], input.shape)
             ctx.fused = True
             ctx.save_for_backward(packed, scale.view(n, G), mn.view(n, G), mean, rstd, weight, bias)
-            return y
+            return done(y)
         w = None if weight is None else weight.to(input.dtype)
         b = None if bias is None else bias.to(input.dtype)
         # in the input's own type (statistics are fp32 inside the kernel): under autocast the stock
@@ -256,20 +271,36 @@ class _DOLayerNorm(Function):
         ctx.q_meta = q_meta
         ctx.fused = False
         ctx.save_for_backward(q_tensors[0], q_tensors[1], q_tensors[2], mean, rstd, weight, bias)
-        return y
+        return done(y)
 
     @staticmethod
     @custom_bwd(device_type="cuda")
-    def backward(ctx, dy):
+    def backward(ctx, dy, dtotal=None):
         packed, scale, mn, mean, rstd, weight, bias = ctx.saved_tensors
-        mask = [bool(ctx.needs_input_grad[0]), weight is not None and bool(ctx.needs_input_grad[2]),
+        wants_x = bool(ctx.needs_input_grad[0]) or (ctx.with_residual and bool(ctx.needs_input_grad[7]))
+        mask = [wants_x, weight is not None and bool(ctx.needs_input_grad[2]),
                 bias is not None and bool(ctx.needs_input_grad[3])]
+        if dy is None:                                       # only the sum was used downstream
+            return (dtotal if ctx.needs_input_grad[0] else None, None, None, None, None, None, None,
+                    dtotal if ctx.with_residual and ctx.needs_input_grad[7] else None)
         dy = dy.contiguous()
-        if ctx.fused and codec.ln_fused_applies(dy, ctx.q_meta[2], ctx.q_meta[0]):
-            dx, dw, db = codec.ln_bwd_from_packed(dy, packed, scale, mn, ctx.q_meta[0], ctx.q_meta[2], mean, rstd, weight)
+
+        def result(dx, dw, db):
             wd, bd = ctx.param_dtypes
-            return (dx if mask[0] else None, None, dw.to(wd) if mask[1] else None, db.to(bd) if mask[2] else None,
-                    None, None, None)
+            out = (dx if ctx.needs_input_grad[0] else None, None, dw.to(wd) if mask[1] else None,
+                   db.to(bd) if mask[2] else None, None, None, None)
+            # the sum's gradient goes to both of its operands
+            return out + ((dx if ctx.needs_input_grad[7] else None,) if ctx.with_residual else (None,))
+
+        if ctx.fused and codec.ln_fused_applies(dy, ctx.q_meta[2], ctx.q_meta[0]):
+            dy2 = None
+            if dtotal is not None:
+                dy2 = dtotal.to(dy.dtype).contiguous()
+                if dy2.data_ptr() % 16:
+                    dy2 = dy2.clone()
+            dx, dw, db = codec.ln_bwd_from_packed(dy, packed, scale, mn, ctx.q_meta[0], ctx.q_meta[2], mean, rstd,
+                                                  weight, dy2=dy2)
+            return result(dx, dw, db)
         x = unified_dequantize((packed, scale, mn), ctx.q_meta, None).to(dy.dtype).contiguous()
         w = None if weight is None else weight.to(dy.dtype)
         b = None if bias is None else bias.to(dy.dtype)
@@ -285,6 +316,6 @@ class _DOLayerNorm(Function):
                 dw, db = codec.ln_bwd_params(dy, x, mean, rstd)
             else:
                 dx, dw, db = torch.ops.aten.native_layer_norm_backward(dy, x, ctx.normalized_shape, mean, rstd, w, b, mask)
-        wd, bd = ctx.param_dtypes
-        return (dx if mask[0] else None, None, dw.to(wd) if mask[1] else None, db.to(bd) if mask[2] else None,
-                None, None, None)
+        if dtotal is not None and dx is not None:
+            dx = dx + dtotal.to(dx.dtype)
+        return result(dx, dw, db)

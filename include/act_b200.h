@@ -406,6 +406,25 @@ ACT_API int act_ln_bwd_from_packed(const void* dy, int dtype, int64_t rows, int 
                                    float* dgamma, float* dbeta, void* stream);
 
 /*
+ * The same pair for a LayerNorm that follows a residual addition, s = x + res (the pre-norm
+ * transformer block: s feeds the LayerNorm and the next addition).  16-bit types only.
+ *   act_ln_add_fwd_quant_pack: sum = x + res rounded to the element type (what a separate
+ *       addition writes), then y, mean, rstd and the packed sum exactly as act_ln_fwd_quant_pack
+ *       gives them for x = sum: the addition's kernel and the LayerNorm's read of its result fall away.
+ *   act_ln_bwd_from_packed_sum: dx = LayerNorm's input gradient + dy2, where dy2 (dy's type, same
+ *       shape, or NULL) is the gradient that reached the sum along its other consumer; added in
+ *       fp32 before the one rounding.  The caller hands dx to both x and res.
+ */
+ACT_API int act_ln_add_fwd_quant_pack(const void* x, const void* res, int dtype, int64_t rows, int cols,
+                                      const float* weight, const float* bias, double eps, int group_size, int bits,
+                                      uint64_t seed, uint64_t offset, int flags, void* sum, void* y, float* mean,
+                                      float* rstd, void* packed, float* scale, float* min, void* stream);
+ACT_API int act_ln_bwd_from_packed_sum(const void* dy, const void* dy2, int dtype, int64_t rows, int cols,
+                                       const void* packed, const float* scale, const float* min, int group_size,
+                                       int bits, const float* mean, const float* rstd, const float* weight,
+                                       void* dx, float* dgamma, float* dbeta, void* stream);
+
+/*
  * act_merge_heads: dst[b, t, s, h, :] = srcs[s][b, h, t, :] for s < parts (1..4); dst is contiguous
  * [B, T, parts, H, Dh]; strides = parts x (element stride of b, of h, of t) of the sources, whose
  * last dimension is contiguous.  Dh * elem_bytes, the sources' byte strides and all bases are

@@ -614,6 +614,44 @@ def test_layer_norm_fused_with_codec(cuda_device, dtype, bits, shape, gs):
     assert ((db.double() - dbr).abs() <= 1e-5 * rows ** 0.5 * (dbr.abs() + 1) + 1e-4).all()
 
 
+@pytest.mark.parametrize("dtype", (torch.bfloat16, torch.float16), ids=("bf16", "f16"))
+@pytest.mark.parametrize("bits", (1, 2, 4, 8))
+@pytest.mark.parametrize("shape,gs", [((64, 197, 768), 128), ((37, 960), 64), ((5, 7, 256), 256), ((300, 64), 32),
+                                      ((129, 1024), 128)])
+def test_layer_norm_with_residual_addition(cuda_device, dtype, bits, shape, gs):
+    """act_ln_add_fwd_quant_pack: the sum it writes equals the separate addition bit for bit, and
+    y, the statistics and the packed sum equal act_ln_fwd_quant_pack's on that sum bit for bit;
+    act_ln_bwd_from_packed_sum equals act_ln_bwd_from_packed's dx plus the second gradient to
+    within one rounding of the element type, with the parameter gradients unchanged."""
+    from deep_optimization_b200 import _lib, codec
+    torch.manual_seed(bits * 100 + shape[-1])
+    C = shape[-1]
+    a = (torch.randn(shape, device=cuda_device) * 1.5 + 0.3).to(dtype)
+    r = (torch.randn(shape, device=cuda_device) * 0.7).to(dtype)
+    w = (torch.rand(C, device=cuda_device) + 0.5)
+    b = torch.randn(C, device=cuda_device) * 0.1
+    for flags in (0, _lib.ACT_FLAG_ROUND_NEAREST):
+        got = codec.ln_fwd_quant_pack(a, w, b, 1e-6, bits, gs, seed=9, offset=3, flags=flags, residual=r)
+        total = a + r
+        assert torch.equal(got[0], total)
+        want = codec.ln_fwd_quant_pack(total, w, b, 1e-6, bits, gs, seed=9, offset=3, flags=flags)
+        for g, t in zip(got[1:], want):
+            assert torch.equal(g.view(torch.uint8), t.view(torch.uint8))
+    _, y, mean, rstd, packed, scale, mn = got
+    dy = torch.randn(shape, device=cuda_device).to(dtype)
+    dy2 = torch.randn(shape, device=cuda_device).to(dtype)
+    dx, dg, db = codec.ln_bwd_from_packed(dy, packed, scale, mn, bits, gs, mean, rstd, w)
+    dx2, dg2, db2 = codec.ln_bwd_from_packed(dy, packed, scale, mn, bits, gs, mean, rstd, w, dy2=dy2)
+    ulp = {torch.bfloat16: 2.0 ** -8, torch.float16: 2.0 ** -11}[dtype]
+    want = dx.double() + dy2.double()                    # dx carries one rounding of its own
+    assert ((dx2.double() - want).abs() <= ulp * (want.abs() + dx.double().abs()) + 1e-6).all()
+    assert torch.allclose(dg2, dg, rtol=1e-4, atol=1e-3) and torch.allclose(db2, db, rtol=1e-4, atol=1e-3)
+    with pytest.raises(ValueError):
+        codec.ln_fwd_quant_pack(a, w, b, 1e-6, bits, gs, residual=r.float())
+    with pytest.raises(ValueError):
+        codec.ln_bwd_from_packed(dy, packed, scale, mn, bits, gs, mean, rstd, w, dy2=dy2[..., : C // 2])
+
+
 def test_layer_norm_fused_irregular_groups(cuda_device):
     """Groups with a zero, a denormal, a huge or a non-finite range take the general encoder; the
     packed bytes still equal act_quant_pack's."""

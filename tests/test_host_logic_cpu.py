@@ -120,6 +120,33 @@ def test_controller_fuses_bn_add_relu():
     assert off.fused_bn_add_relu == []
 
 
+def test_controller_fuses_add_layer_norm():
+    """s = a + b; y = norm(s) in a pre-norm transformer block becomes one LayerNorm call on (a, b)
+    returning (y, s); an addition with a broadcast operand is rewritten too and added by the
+    module the ordinary way; the eval-mode output is unchanged."""
+    from deep_optimization_b200.controller import Controller
+    from deep_optimization_b200.payload.vit import VisionTransformer
+
+    torch.manual_seed(0)
+    model = VisionTransformer(image=32, patch=8, dim=64, depth=2, heads=2, mlp_dim=128, num_classes=10)
+    ref = copy.deepcopy(model).eval()
+    cfg = dict(default_bits=2, auto_precision=None, batch_size=8, min_activation_mib=0.0)
+    c = Controller(model, cfg, input_shape=(3, 32, 32), test=False, device="cpu")
+    net = c.traced_model
+    # every LayerNorm follows an addition: the position embedding (broadcast), the blocks' two
+    assert sorted(c.fused_add_layer_norm) == ["blocks.0.norm1", "blocks.0.norm2", "blocks.1.norm1", "blocks.1.norm2", "norm"]
+    for n in net.graph.nodes:
+        if n.op == "call_module" and n.target in c.fused_add_layer_norm:
+            assert len(n.args) == 2
+    net.eval()
+    x = torch.randn(2, 3, 32, 32)
+    with torch.no_grad():
+        assert torch.allclose(net(x), ref(x), atol=1e-5)
+    off = Controller(copy.deepcopy(ref).train(), dict(cfg, fuse_add_layer_norm=False), input_shape=(3, 32, 32),
+                     test=False, device="cpu")
+    assert off.fused_add_layer_norm == []
+
+
 def test_controller_fuses_bn_relu():
     """A BatchNorm whose only consumer is a ReLU takes the ReLU over (the default); one with a
     second consumer, or followed by ReLU6, keeps its ReLU node."""

@@ -436,6 +436,39 @@ def test_block_outputs_forked_to_their_two_consumers(cuda_device, channels_last)
         assert _rel(grads[True][k], grads[False][k]) < 1e-2, k      # bf16 gradients: a few last-place differences
 
 
+def test_residual_addition_inside_layer_norm(cuda_device):
+    """With `fuse_add_layer_norm` the LayerNorm of a pre-norm block forms x + branch itself and its
+    backward adds the skip path's gradient: same forward bit for bit (the sum is rounded as the
+    separate addition rounds it, the hash offsets advance alike), same gradients to within the
+    16-bit rounding of the activations' gradients, and no `add` left in front of a LayerNorm."""
+    from deep_optimization_b200 import codec
+    from deep_optimization_b200.controller import Controller
+    from deep_optimization_b200.payload.vit import VisionTransformer
+
+    torch.manual_seed(0)
+    base = VisionTransformer(image=32, patch=4, dim=128, depth=3, heads=4, mlp_dim=256, num_classes=10).to(cuda_device)
+    x = torch.randn(16, 3, 32, 32, device=cuda_device)
+    t = torch.randint(0, 10, (16,), device=cuda_device)
+    grads, outs = {}, {}
+    for fuse in (True, False):
+        net = VisionTransformer(image=32, patch=4, dim=128, depth=3, heads=4, mlp_dim=256, num_classes=10).to(cuda_device)
+        net.load_state_dict(base.state_dict())
+        cfg = dict(default_bits=8, auto_precision=None, batch_size=16, min_activation_mib=0.0, fuse_add_layer_norm=fuse)
+        c = Controller(net, cfg, input_shape=(3, 32, 32), test=False, device=cuda_device)
+        assert len(c.fused_add_layer_norm) == (7 if fuse else 0)
+        m = c.traced_model
+        codec.manual_seed(21)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            out = m(x)
+            loss = nn.functional.cross_entropy(out, t)
+        loss.backward()
+        outs[fuse] = out.detach().float()
+        grads[fuse] = {k: p.grad.detach().float().clone() for k, p in m.named_parameters()}
+    assert torch.equal(outs[True], outs[False])
+    for k in grads[True]:
+        assert _rel(grads[True][k], grads[False][k]) < 2e-2, k
+
+
 def test_relu_backward_with_two_gradients(cuda_device):
     """act_relu_bwd_unpack_sum: mask ? dy + dy2 : 0 with the sum rounded once, i.e. what the
     framework's addition followed by the mask pass gives, bit for bit."""
