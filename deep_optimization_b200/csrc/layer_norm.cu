@@ -117,7 +117,18 @@ int launch_col_reduce(const void* a, const void* b, const float* mean, const flo
         per_sm = n;
     }
     const uint32_t vecs = (uint32_t)C / 8u;
-    const uint32_t tpr = vecs < (uint32_t)kColThreads ? vecs : (uint32_t)kColThreads;
+    // threads per row: the width that leaves the fewest threads idle (row lanes that do not fit a
+    // block, vectors past the last column), the widest such one.  With min(vecs, 256): 288 vectors
+    // ran two blocks of which the second used 32 of its 256 threads.
+    uint32_t tpr = 1;
+    {
+        const uint32_t T = (uint32_t)kColThreads, hi = vecs < T ? vecs : T;
+        uint64_t best_num = 0, best_den = 1;
+        for (uint32_t t = 1; t <= hi; ++t) {
+            const uint64_t num = (uint64_t)t * (T / t) * vecs, den = (uint64_t)T * ((vecs + t - 1) / t) * t;
+            if (num * best_den >= best_num * den) { best_num = num; best_den = den; tpr = t; }
+        }
+    }
     const uint32_t gx = (vecs + tpr - 1) / tpr;
     const uint32_t rpi = kColThreads / tpr;
     // slices of the rows: one resident wave of blocks, never a slice shorter than one block step
