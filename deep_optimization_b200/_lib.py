@@ -116,3 +116,24 @@ def check(code: int, what: str) -> None:
     if code != 0:
         msg = load().act_strerror(code).decode()
         raise ActLibraryError(f"{what}: {msg} (code {code})")
+
+
+_NO_SWITCH = None
+
+
+def stream_ptr(t) -> int:
+    """Raw handle of PyTorch's current stream on t's device (no Stream object is built)."""
+    import torch
+    return torch._C._cuda_getCurrentRawStream(t.device.index)
+
+
+def device_of(t):
+    """Context that makes t's device current for a launch; free when it already is."""
+    import contextlib
+    import torch
+    global _NO_SWITCH
+    if t.device.index == torch.cuda.current_device():
+        if _NO_SWITCH is None:
+            _NO_SWITCH = contextlib.nullcontext()
+        return _NO_SWITCH
+    return torch.cuda.device(t.device)

@@ -53,10 +53,10 @@ def fp8_gemm(A8: torch.Tensor, B8: torch.Tensor, sa: torch.Tensor, sb: torch.Ten
         if workspace is None or workspace.numel() * workspace.element_size() < need:
             workspace = torch.empty(need, dtype=torch.uint8, device=A8.device)
         ws_ptr, ws_len = workspace.data_ptr(), workspace.numel() * workspace.element_size()
-    with torch.cuda.device(A8.device):
+    with _lib.device_of(A8):
         rc = _lib.load().act_fp8_gemm(A8.data_ptr(), B8.data_ptr(), sa.data_ptr(), sb.data_ptr(), C.data_ptr(),
                                       M, N, K, A8.stride(0), B8.stride(0), C.stride(0), flags, ws_ptr, ws_len,
-                                      torch.cuda.current_stream(A8.device).cuda_stream)
+                                      _lib.stream_ptr(A8))
     _lib.check(rc, "act_fp8_gemm")
     return C
 
@@ -91,10 +91,10 @@ def dw_from_packed(dy: torch.Tensor, packed: torch.Tensor, scale: torch.Tensor, 
     dw = out if out is not None else torch.empty((N, K), dtype=torch.float32, device=dy.device)
     if dw.dtype != torch.float32 or dw.shape != (N, K) or dw.stride(1) != 1:
         raise ValueError("out must be a float32 [N, K] tensor with unit column stride")
-    with torch.cuda.device(dy.device):
+    with _lib.device_of(dy):
         rc = _lib.load().act_dw_from_packed(dy.data_ptr(), packed.data_ptr(), scale.data_ptr(), mn.data_ptr(), bits,
                                             group_size, M, N, K, dy.stride(0), dw.data_ptr(), dw.stride(0),
-                                            torch.cuda.current_stream(dy.device).cuda_stream)
+                                            _lib.stream_ptr(dy))
     _lib.check(rc, "act_dw_from_packed")
     return dw
 

@@ -19,9 +19,9 @@ def _merge_heads(grads, B, H, T, Dh, dtype, device):
     out = torch.empty((B, T, len(grads) * H * Dh), dtype=dtype, device=device)
     ptrs = (ctypes.c_void_p * len(grads))(*[g.data_ptr() for g in grads])
     strides = (ctypes.c_int64 * (3 * len(grads)))(*[s for g in grads for s in (g.stride(0), g.stride(1), g.stride(2))])
-    with torch.cuda.device(device):
+    with _lib.device_of(out):
         rc = _lib.load().act_merge_heads(ptrs, strides, len(grads), B, H, T, Dh, out.element_size(), out.data_ptr(),
-                                         torch.cuda.current_stream(device).cuda_stream)
+                                         _lib.stream_ptr(out))
     _lib.check(rc, "act_merge_heads")
     return out
 

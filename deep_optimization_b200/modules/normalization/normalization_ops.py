@@ -238,13 +238,15 @@ class _DOLayerNorm(Function):
         ctx.set_materialize_grads(False)                     # an unused output brings None, not a tensor of zeros
         input = input.contiguous()
         total = None
+        fused = _DOLayerNorm._fused(input, ctx.normalized_shape, m)
         if residual is not None:
             residual = residual.contiguous()
-            if not (_DOLayerNorm._fused(input, ctx.normalized_shape, m) and codec.ln_residual_applies(input, residual)):
+            if not (fused and codec.ln_residual_applies(input, residual)):
                 input = total = input + residual          # the kernel cannot take the pair: add first
                 residual = None
+                fused = _DOLayerNorm._fused(input, ctx.normalized_shape, m)
         done = lambda y: (y, total) if ctx.with_residual else y
-        if _DOLayerNorm._fused(input, ctx.normalized_shape, m):
+        if fused:
             flags = _lib.ACT_FLAG_ROUND_NEAREST if act_kernels.get_mode() == "nearest" else 0
             if residual is not None:
                 total, y, mean, rstd, packed, scale, mn = codec.ln_fwd_quant_pack(
