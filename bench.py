@@ -945,6 +945,11 @@ def run_only(args):
         x = [torch.randn(R, C, device=dev).to(torch.bfloat16) for _ in range(3)]
         w, b = torch.ones(C, device=dev), torch.zeros(C, device=dev)
         for i in range(args.reps):
+            if args.residual:       # the pair with the residual addition in front of the LayerNorm
+                _, y, mean, rstd, packed, scale, mn = codec.ln_fwd_quant_pack(x[i % 3], w, b, 1e-6, BITS, GROUP,
+                                                                              residual=x[(i + 2) % 3])
+                codec.ln_bwd_from_packed(x[(i + 1) % 3], packed, scale, mn, BITS, GROUP, mean, rstd, w, dy2=x[i % 3])
+                continue
             y, mean, rstd, packed, scale, mn = codec.ln_fwd_quant_pack(x[i % 3], w, b, 1e-6, BITS, GROUP)
             codec.ln_bwd_from_packed(x[(i + 1) % 3], packed, scale, mn, BITS, GROUP, mean, rstd, w)
         torch.cuda.synchronize()
@@ -989,6 +994,8 @@ def main():
                          "DistributedDataParallel, or DDP with gradients as bucket views")
     ap.add_argument("--no-fused-dw", action="store_true",
                     help="training legs: Linear layers dequantise and call cuBLAS for dW instead of act_dw_from_packed")
+    ap.add_argument("--residual", action="store_true",
+                    help="--only ln: the kernels that take the residual addition / the second gradient")
     ap.add_argument("--no-fuse-add-ln", action="store_true",
                     help="training legs: residual additions in front of a LayerNorm stay separate kernels")
     ap.add_argument("--legs", nargs="+", default=None, help="training legs to run (default: all six)")
