@@ -831,8 +831,8 @@ def ln_bwd_from_packed(dy: torch.Tensor, packed: torch.Tensor, scale: torch.Tens
     if scale.numel() * group_size != dy.numel() or mean.numel() != rows or rstd.numel() != rows:
         raise ValueError("ln_bwd_from_packed: packed input and statistics do not match dy")
     dx = torch.empty_like(dy)
-    dgamma = torch.empty(C, dtype=torch.float32, device=dy.device)
-    dbeta = torch.empty(C, dtype=torch.float32, device=dy.device)
+    both = torch.empty((2, C), dtype=torch.float32, device=dy.device)    # adjacent: the library clears them in one pass
+    dgamma, dbeta = both[0], both[1]
     w = None if weight is None else weight.to(torch.float32).contiguous()
     scale = scale.reshape(-1).contiguous()
     mn = mn.reshape(-1).contiguous()

@@ -518,8 +518,12 @@ static int ln_bwd_entry(const void* dy, const void* dres, int dtype, int64_t row
     if (rc != ACT_OK) return rc;
     if (!dgamma || !dbeta) return ACT_ERR_NULL;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (cudaMemsetAsync(dgamma, 0, (size_t)cols * sizeof(float), st) != cudaSuccess ||
-        cudaMemsetAsync(dbeta, 0, (size_t)cols * sizeof(float), st) != cudaSuccess) return ACT_ERR_LAUNCH;
+    if (dbeta == dgamma + cols) {                            // one buffer [2, cols]: one clearing pass
+        if (cudaMemsetAsync(dgamma, 0, (size_t)cols * 2 * sizeof(float), st) != cudaSuccess) return ACT_ERR_LAUNCH;
+    } else if (cudaMemsetAsync(dgamma, 0, (size_t)cols * sizeof(float), st) != cudaSuccess ||
+               cudaMemsetAsync(dbeta, 0, (size_t)cols * sizeof(float), st) != cudaSuccess) {
+        return ACT_ERR_LAUNCH;
+    }
     if (rows == 0) return ACT_OK;
     if (!dy || !packed || !scale || !min || !mean || !rstd || !dx) return ACT_ERR_NULL;
     if (((uintptr_t)dy | (uintptr_t)dx | (uintptr_t)dres) & 15) return ACT_ERR_ALIGN;
