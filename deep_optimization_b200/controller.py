@@ -269,7 +269,7 @@ class Controller:
 
     @staticmethod
     def _fuse_add_layer_norm(traced):
-        """s = a + b; y = layer_norm(s), the pre-norm transformer block (Model/ViT/ViT.py:66-68 of
+        """s = a + b; y = layer_norm(s), the pre-norm transformer block (Model/ViT/ViT.py:84-86 of
         the reference), where s also feeds the next residual addition: the LayerNorm module takes
         the addition over and returns (y, s).  Its forward kernel then forms s from a and b while it
         reads them (the separate addition and the re-read of its result fall away), and its backward
