@@ -489,6 +489,7 @@ def run_reference_triton(steps=20, warmup=3):
 
 DDP_BUCKET_MB = 25
 FUSED_DW = True         # Linear weight gradients straight from the packed input (--no-fused-dw: dequantise + cuBLAS)
+STALL_RATIO = 2.0       # a training-leg region whose slowest step exceeds this multiple of its median is timed once more
 FUSE_ADD_LN = True      # x + branch formed inside the following LayerNorm's kernels (--no-fuse-add-ln: separate additions)
 DP_MODE = "flat"         # how the training legs average gradients over ranks; see run_train
 
@@ -628,7 +629,7 @@ def run_train(name, dev, world, local, steps=20, warmup=12, act=True, batch=256,
     # A region with a stalled step is timed once more, and says so: now and then one early step of a
     # region takes 0.2-0.4 s (seen at the second timed step of a leg, in about one leg in ten, on any
     # model; its cause is not known), which would stand for a third of a 20-step mean.
-    stall = torch.tensor([1.0 if per_step[-1] > 3.0 * per_step[steps // 2] else 0.0], device=dev)
+    stall = torch.tensor([1.0 if per_step[-1] > STALL_RATIO * per_step[steps // 2] else 0.0], device=dev)
     if world > 1:
         dist.all_reduce(stall, op=dist.ReduceOp.MAX)
     discarded = None
@@ -1014,11 +1015,15 @@ def main():
                     help="training legs: Linear layers dequantise and call cuBLAS for dW instead of act_dw_from_packed")
     ap.add_argument("--residual", action="store_true",
                     help="--only ln: the kernels that take the residual addition / the second gradient")
+    ap.add_argument("--stall-ratio", type=float, default=None,
+                    help="training legs: re-time a region whose slowest step exceeds this multiple of the median (default 2)")
     ap.add_argument("--no-fuse-add-ln", action="store_true",
                     help="training legs: residual additions in front of a LayerNorm stay separate kernels")
     ap.add_argument("--legs", nargs="+", default=None, help="training legs to run (default: all six)")
     args = ap.parse_args()
-    global DDP_BUCKET_MB, DP_MODE, FUSED_DW, FUSE_ADD_LN
+    global DDP_BUCKET_MB, DP_MODE, FUSED_DW, FUSE_ADD_LN, STALL_RATIO
+    if args.stall_ratio:
+        STALL_RATIO = args.stall_ratio
     FUSED_DW = not args.no_fused_dw
     FUSE_ADD_LN = not args.no_fuse_add_ln
     if args.ddp_bucket_mb:
