@@ -554,6 +554,11 @@ def run_train(name, dev, world, local, steps=20, warmup=12, act=True, batch=256,
     from deep_optimization_b200 import codec
     from deep_optimization_b200.controller import Controller
     from deep_optimization_b200.payload import resnet50, vit_b16
+    # what earlier legs left behind (their traced modules sit in reference cycles, and with them
+    # their device memory) is collected and handed back before this leg allocates anything
+    import gc
+    gc.collect()
+    torch.cuda.empty_cache()
     torch.manual_seed(0)
     model = (resnet50() if name == "resnet50" else vit_b16()).to(dev)
     if act:
