@@ -147,6 +147,41 @@ def test_controller_fuses_add_layer_norm():
     assert off.fused_add_layer_norm == []
 
 
+def test_add_layer_norm_rewrite_keeps_order_and_skips_scaled_additions():
+    """The LayerNorm call moves to the addition's place, so a consumer of the sum that the trace
+    lists before the LayerNorm still finds it; torch.add is rewritten like `+`; an addition with
+    `alpha` is left alone."""
+    from deep_optimization_b200.controller import Controller
+
+    class Net(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.inp = nn.Linear(64, 64)
+            self.n1, self.n2, self.n3 = nn.LayerNorm(64), nn.LayerNorm(64), nn.LayerNorm(64)
+            self.f1, self.f2, self.f3 = nn.Linear(64, 64), nn.Linear(64, 64), nn.Linear(64, 10)
+
+        def forward(self, x):
+            h = self.inp(x)
+            s = torch.add(h, self.f1(h))
+            early = s * 2.0                       # a consumer of the sum ahead of its LayerNorm
+            y = self.n1(s)
+            t = torch.add(y, early, alpha=0.5)    # scaled: not the pattern
+            z = self.n2(t)
+            u = z + self.f2(z)
+            return self.f3(self.n3(u))
+
+    torch.manual_seed(0)
+    model = Net()
+    ref = copy.deepcopy(model).eval()
+    cfg = dict(default_bits=2, auto_precision=None, batch_size=8, min_activation_mib=0.0)
+    c = Controller(model, cfg, input_shape=(16, 64), test=False, device="cpu")
+    assert sorted(c.fused_add_layer_norm) == ["n1", "n3"]
+    net = c.traced_model.eval()
+    x = torch.randn(8, 16, 64)
+    with torch.no_grad():
+        assert torch.allclose(net(x), ref(x), atol=1e-5)
+
+
 def test_controller_fuses_bn_relu():
     """A BatchNorm whose only consumer is a ReLU takes the ReLU over (the default); one with a
     second consumer, or followed by ReLU6, keeps its ReLU node."""
